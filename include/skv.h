@@ -1,0 +1,183 @@
+/* skv.h - C ABI of the B200 (sm_100a) clustered sparse KV-cache decode-attention library.
+ *
+ * Every entry point takes raw device pointers, element strides and sizes; none takes a framework
+ * type.  Unless stated otherwise a call allocates nothing, never synchronises and reads nothing back
+ * to the host, so it can be recorded into a CUDA graph; all work is ordered on the `stream` argument
+ * (a cudaStream_t passed as void*).  Return value: 0 on success, a negative SKV_E_* code when an
+ * argument is rejected on the host (nothing is launched then).  Problems met on the device (no spare
+ * slot, a cluster too large to split, an index out of range) are recorded per head in the
+ * caller-owned `status` words of skv_state and never fault.
+ *
+ * Each declaration names the interface of the reference project (aaholmes/sparse-kv-reads, package
+ * `ssa`) that it replaces, as file:line within that project.
+ */
+#ifndef SKV_H
+#define SKV_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define SKV_VERSION 100
+
+/* host-side argument errors */
+#define SKV_OK            0
+#define SKV_E_NULL       -1   /* a required pointer is null */
+#define SKV_E_DIM        -2   /* head_dim, group size or slot count not supported */
+#define SKV_E_DTYPE      -3   /* unknown element type */
+#define SKV_E_ALIGN      -4   /* pointer or stride not 16-byte aligned */
+#define SKV_E_RANGE      -5   /* size or option out of range */
+#define SKV_E_WORKSPACE  -6   /* workspace too small */
+#define SKV_E_CUDA       -7   /* a CUDA runtime call failed (see skv_last_cuda_error) */
+#define SKV_E_TOO_LARGE  -8   /* beyond the fixed capacity of a no-allocation entry point */
+
+/* element types of q / K / V / out */
+#define SKV_BF16 0
+#define SKV_F32  1
+
+/* bits of skv_state.flags (the reference's: ssa/kernels/sphere_fused.py:226-227) */
+#define SKV_FLAG_DRIFT 1      /* the running key mean moved more than delta * rbar from mu_ref */
+#define SKV_FLAG_RESET 2      /* the cluster count reached reset_at */
+/* bits of skv_state.status (device-side problems; sticky until the host clears them) */
+#define SKV_ST_NO_SLOT      1 /* a cluster passed its cap but every slot is in use */
+#define SKV_ST_SPLIT_TOO_BIG 2 /* a cluster over the cap has more members than the split can stage */
+#define SKV_ST_BAD_INDEX    4 /* a listed position or a label was out of range and was skipped */
+
+/* Cluster state of `heads` independent (layer, sequence, KV head) entries, structure of arrays.
+ * Arrays are contiguous over heads: x[head][...].  Mirrors the tensors of
+ * ssa/attn/sphere_gpu.py:145-164 plus ssa/kernels/sphere_fused.py:363-378 and
+ * ssa/kernels/graph_kernels.py:204-216 (end_dev, need_dev). */
+typedef struct skv_state {
+    int32_t heads;        /* entries in this view */
+    int32_t C;            /* slots per head (power of two >= 16) */
+    int32_t d;            /* head dimension (128) */
+    int32_t capacity;     /* positions per head in `labels` */
+    int32_t summary_bits; /* 8: score/search the int8 copies; 32: the float32 vectors */
+    int32_t reserved;
+    float   *sum_dir;     /* [heads, C, d]  sum of member unit directions */
+    float   *cent;        /* [heads, C, d]  unit centroids searched by the insert */
+    int8_t  *dir8;        /* [heads, C, d]  round(unit(sum_dir) * 127); null when summary_bits == 32 */
+    int8_t  *cent8;       /* [heads, C, d]  round(cent * 127);          null when summary_bits == 32 */
+    float   *mmax;        /* [heads, C]     longest member key (about mu_ref) */
+    float   *mmin;        /* [heads, C]     shortest member key, +inf when empty */
+    float   *count;       /* [heads, C]     member count */
+    int32_t *n_c;         /* [heads]        slots in use */
+    float   *cap;         /* [heads]        split a cluster holding more keys than this (+inf: never) */
+    float   *rbar;        /* [heads]        rms key length at the last (re)build */
+    float   *ksum;        /* [heads, d]     running sum of clustered keys */
+    float   *mu_ref;      /* [heads, d]     reference mean the keys are centred with */
+    int32_t *flags;       /* [heads]        SKV_FLAG_* */
+    int32_t *status;      /* [heads]        SKV_ST_* */
+    int32_t *nsplit;      /* [heads]        splits done on the device */
+    int32_t *end;         /* [heads]        clustered positions are [1, end) */
+    int32_t *need;        /* [heads]        keys the selection must cover: ceil(budget * (end - 1)) */
+    int16_t *labels;      /* [heads, capacity]  slot of each position; C = always read */
+} skv_state;
+
+int skv_version(void);
+const char *skv_error_string(int code);
+/* last cudaError_t seen by a call that returned SKV_E_CUDA, as text */
+const char *skv_last_cuda_error(void);
+
+/* Number of split partials skv_attend uses for `heads` KV heads on the current device
+ * (replaces the split count of ssa/kernels/graph_kernels.py:218). */
+int skv_attend_splits(int heads);
+
+/* Bytes of the float workspace skv_attend needs for (heads, G, d, splits):
+ * partial outputs, partial (max, sum) pairs and one ticket word per head. */
+int64_t skv_attend_workspace_bytes(int heads, int G, int d, int splits);
+
+/* Exact softmax attention of one query per query head over a LIST of cached rows, split over
+ * CTAs, merged by log-sum-exp by the last CTA of each head.
+ * Replaces _list_kernel + _merge_kernel (ssa/kernels/labeled_attn.py:202-245, :123-140); with
+ * idx == NULL it attends over rows [0, n_dev[0]) and replaces _dense_dev_kernel
+ * (ssa/kernels/graph_kernels.py:27-59).
+ *   q    [heads*G, d]            one query per query head, contiguous, dtype
+ *   K, V [heads, rows, d]        read in place: element strides *_head_stride, *_row_stride, unit last stride
+ *   idx  [heads, idx_stride]     int32 row positions (any order); cnt [heads] rows listed per head
+ *   out  [heads*G, d]            dtype
+ *   workspace                    skv_attend_workspace_bytes(...) bytes, zero-initialised ONCE by the
+ *                                caller (the ticket words return to zero after every call)
+ *   rows_limit                   positions >= rows_limit are skipped and flagged in status (may be null)
+ */
+int skv_attend(const void *q, const void *K, const void *V, const int32_t *idx, const int32_t *cnt,
+               const int32_t *n_dev, void *out, void *workspace, int32_t *status,
+               int heads, int G, int d, int dtype,
+               int64_t k_head_stride, int64_t k_row_stride, int64_t v_head_stride, int64_t v_row_stride,
+               int64_t idx_stride, int rows_limit, int splits, float scale, void *stream);
+
+/* Log-sum-exp merge of caller-provided partials (natural-log maxima), float32 output.
+ * Replaces merge_splits (ssa/kernels/labeled_attn.py:143-151).
+ *   m, l [heads, S, G], a [heads, S, G, d] -> out [heads*G, d] */
+int skv_merge(const float *m, const float *l, const float *a, float *out, int heads, int S, int G, int d,
+              void *stream);
+
+/* Score clusters from their summaries once per KV head for its G query heads, form the shared score
+ * (sum over the group of each head's softmax over clusters), take clusters in decreasing shared
+ * score (equal scores: lower slot first) until their key counts reach state.need, and list the
+ * positions to read in ascending order (position 0 and the recent window carry label C and are
+ * always listed).
+ * Replaces _score_kernel, _shared_pick/_pick_dev_kernel (ssa/kernels/sphere_fused.py:230-289,
+ * ssa/kernels/graph_kernels.py:133-141) and _compact_dev_kernel (graph_kernels.py:144-155);
+ * selection rule of SphereIndexGPU._rank_mask (ssa/attn/sphere_gpu.py:402-410).
+ *   q          [heads*G, d] dtype
+ *   n_dev      [1] cached positions (all heads)
+ *   w          [heads, C+1] float32 0/1 weights out (column C = 1)
+ *   idx, cnt   row list out: idx [heads, idx_stride] int32, cnt [heads]
+ *   shared_in  optional [heads, C] float32: use these shared scores instead of scoring (tests)
+ *   shared_out optional [heads, C] float32: the shared scores used
+ *   e_out      optional [heads, G, C] float32: per-query-head cluster scores (before the 1/sqrt(d) scale)
+ */
+int skv_select(const skv_state *st, const void *q, int dtype, int G, const int32_t *n_dev,
+               float *w, int32_t *idx, int64_t idx_stride, int32_t *cnt,
+               const float *shared_in, float *shared_out, float *e_out, float scale, void *stream);
+
+/* Insert the keys that left the recent window since the last call (positions [end, max(1, n-window)))
+ * into their nearest clusters, one CTA per entry of `st` (all layers of a model in one launch),
+ * splitting a cluster in two inside the kernel when it passes its head's cap; then update end, need,
+ * the drift flag and the status word.
+ * Replaces _bin_kernel/_bin_dev_kernel + _split_cluster (ssa/kernels/sphere_fused.py:48-227,
+ * ssa/kernels/graph_kernels.py:62-130) and AllLayerInsert (graph_kernels.py:286-325); split rule of
+ * _bisect_padded (ssa/attn/sphere_gpu.py:76-102).
+ *   k_layers        device array [heads / heads_per_layer] of K base addresses (one cache tensor per layer)
+ *   heads_per_layer entries of st per cache tensor; entry e reads head (e % heads_per_layer) of layer (e / heads_per_layer)
+ *   budget          fraction of the clustered keys to cover (need = ceil(budget * (end-1)), in double)
+ *   delta           drift threshold in units of rbar;  reset_at: 0 = never
+ *   max_members     largest cluster the in-kernel split stages (<= skv_insert_max_members())
+ */
+int skv_insert(const skv_state *st, const void *const *k_layers, int heads_per_layer, int dtype,
+               int64_t k_head_stride, int64_t k_row_stride, const int32_t *n_dev, int window,
+               double budget, float delta, int reset_at, int max_members, void *stream);
+int skv_insert_max_members(void);
+
+/* Workspace bytes of skv_fit / skv_rebin for `heads` heads of `m` clustered keys. */
+int64_t skv_fit_workspace_bytes(int heads, int m, int C, int d);
+
+/* Prompt fit of `st` from positions [1, end) of K, end = max(1, n - window): mean, centring, cosine
+ * k-means with C_init centroids started from rows init_pos (device int32 [C_init], positions within
+ * the clustered keys) and `iters` Lloyd steps, summaries, cap, then division of every cluster over
+ * the cap (k-means over its members into ceil(count*split_factor/cap) parts, then two-way splits
+ * until none is over the cap or the slots run out), and the 8-bit copies.
+ * Synchronises the stream between split rounds; not for graph capture.
+ * Replaces spherical_kmeans (ssa/attn/clusterkv.py:27-46), SphereIndexGPU._build/_bin
+ * (ssa/attn/sphere_gpu.py:166-219), _split_after_fit/_split_overflow/_split_batch (:302-391) and
+ * _refresh8 (ssa/kernels/sphere_fused.py:398-406).
+ *   cap_keys > 0: absolute cap; else cap = split_factor * m / C_init when split_factor > 0; else no cap
+ */
+int skv_fit(const skv_state *st, const void *K, int dtype, int64_t k_head_stride, int64_t k_row_stride,
+            int n, int window, int C_init, int iters, const int32_t *init_pos, float cap_keys,
+            float split_factor, void *workspace, int64_t workspace_bytes, void *stream);
+
+/* Recentre and rebin selected heads with their centroids kept (new mean = ksum / (end-1)):
+ * replaces the recentring branch of SphereIndexGPU._build (ssa/attn/sphere_gpu.py:187-219 with mu given;
+ * callers ssa/kernels/sphere_fused.py:453-464).  `head_list` device int32 [n_list] entries of st;
+ * `end`: clustered positions are [1, end) (the host's copy of state.end).  Workspace as for a fit of n_list heads. */
+int skv_rebin(const skv_state *st, const int32_t *head_list, int n_list, int end, const void *K, int dtype,
+              int64_t k_head_stride, int64_t k_row_stride, void *workspace, int64_t workspace_bytes, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SKV_H */

@@ -1,0 +1,106 @@
+"""ctypes binding of ``libskv.so`` (the C ABI declared in ``include/skv.h``).
+
+There is no fallback: if the library is missing or a call returns an error code, an exception is
+raised.  Tensors are passed as raw device addresses (``tensor.data_ptr()``)."""
+
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+import torch
+
+_PKG = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_PKG, "libskv.so")
+
+SKV_BF16, SKV_F32 = 0, 1
+FLAG_DRIFT, FLAG_RESET = 1, 2
+ST_NO_SLOT, ST_SPLIT_TOO_BIG, ST_BAD_INDEX = 1, 2, 4
+
+EXPORTS = ("skv_version", "skv_error_string", "skv_last_cuda_error", "skv_attend_splits",
+           "skv_attend_workspace_bytes", "skv_attend", "skv_merge", "skv_select", "skv_insert",
+           "skv_insert_max_members", "skv_fit_workspace_bytes", "skv_fit", "skv_rebin")
+
+
+class SkvError(RuntimeError):
+    pass
+
+
+class SkvState(C.Structure):
+    """Mirror of ``struct skv_state``."""
+    _fields_ = [("heads", C.c_int32), ("C", C.c_int32), ("d", C.c_int32), ("capacity", C.c_int32),
+                ("summary_bits", C.c_int32), ("reserved", C.c_int32),
+                ("sum_dir", C.c_void_p), ("cent", C.c_void_p), ("dir8", C.c_void_p), ("cent8", C.c_void_p),
+                ("mmax", C.c_void_p), ("mmin", C.c_void_p), ("count", C.c_void_p), ("n_c", C.c_void_p),
+                ("cap", C.c_void_p), ("rbar", C.c_void_p), ("ksum", C.c_void_p), ("mu_ref", C.c_void_p),
+                ("flags", C.c_void_p), ("status", C.c_void_p), ("nsplit", C.c_void_p), ("end", C.c_void_p),
+                ("need", C.c_void_p), ("labels", C.c_void_p)]
+
+
+_lib = None
+
+
+def _declare(lib) -> None:
+    vp, i32, i64, f32, f64 = C.c_void_p, C.c_int, C.c_int64, C.c_float, C.c_double
+    lib.skv_version.restype = i32
+    lib.skv_error_string.restype = C.c_char_p
+    lib.skv_error_string.argtypes = [i32]
+    lib.skv_last_cuda_error.restype = C.c_char_p
+    lib.skv_attend_splits.restype = i32
+    lib.skv_attend_splits.argtypes = [i32]
+    lib.skv_attend_workspace_bytes.restype = i64
+    lib.skv_attend_workspace_bytes.argtypes = [i32, i32, i32, i32]
+    lib.skv_attend.restype = i32
+    lib.skv_attend.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i64, i64, i64, i64, i64, i32,
+                               i32, f32, vp]
+    lib.skv_merge.restype = i32
+    lib.skv_merge.argtypes = [vp, vp, vp, vp, i32, i32, i32, i32, vp]
+    lib.skv_select.restype = i32
+    lib.skv_select.argtypes = [C.POINTER(SkvState), vp, i32, i32, vp, vp, vp, i64, vp, vp, vp, vp, f32, vp]
+    lib.skv_insert.restype = i32
+    lib.skv_insert.argtypes = [C.POINTER(SkvState), vp, i32, i32, i64, i64, vp, i32, f64, f32, i32, i32, vp]
+    lib.skv_insert_max_members.restype = i32
+    lib.skv_fit_workspace_bytes.restype = i64
+    lib.skv_fit_workspace_bytes.argtypes = [i32, i32, i32, i32]
+    lib.skv_fit.restype = i32
+    lib.skv_fit.argtypes = [C.POINTER(SkvState), vp, i32, i64, i64, i32, i32, i32, i32, vp, f32, f32, vp, i64, vp]
+    lib.skv_rebin.restype = i32
+    lib.skv_rebin.argtypes = [C.POINTER(SkvState), vp, i32, i32, vp, i32, i64, i64, vp, i64, vp]
+
+
+def lib():
+    """The loaded library; raises when it has not been built."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise SkvError(f"{LIB_PATH} is missing: build it with `python -m sparse_kv_reads_b200.build` "
+                           "(there is no CPU or PyTorch fallback for the CUDA kernels)")
+        handle = C.CDLL(LIB_PATH)
+        _declare(handle)
+        _lib = handle
+    return _lib
+
+
+def check(code: int, what: str) -> None:
+    if code != 0:
+        L = lib()
+        msg = L.skv_error_string(code).decode()
+        if code == -7:
+            msg += ": " + L.skv_last_cuda_error().decode()
+        raise SkvError(f"{what} failed ({code}): {msg}")
+
+
+def ptr(t: torch.Tensor | None) -> int | None:
+    return None if t is None else t.data_ptr()
+
+
+def dtype_code(dt: torch.dtype) -> int:
+    if dt == torch.bfloat16:
+        return SKV_BF16
+    if dt == torch.float32:
+        return SKV_F32
+    raise ValueError(f"unsupported cache dtype {dt}; the kernels take bfloat16 or float32")
+
+
+def stream_ptr(device=None) -> int:
+    return torch.cuda.current_stream(device).cuda_stream

@@ -1,0 +1,432 @@
+"""Device-resident cluster state of one attention layer and the per-step calls on it.
+
+Host-side mirror of the reference's state objects for this path, collapsed into one class with the
+reference's names: ``SphereIndexGPU`` (ssa/attn/sphere_gpu.py:113-442), ``SphereIndexFused``
+(ssa/kernels/sphere_fused.py:316-518) and ``SphereIndexGraph`` (ssa/kernels/graph_kernels.py:192-279).
+Every computation is a call into the CUDA library through its C ABI; there is no PyTorch fallback.
+Only the k-means partition, the shared (``sum_share``) selection, the size cap and recentring are
+built; the reference's other options raise ``ValueError``.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import math
+
+import torch
+
+from . import _lib
+from ._lib import SkvState, check, dtype_code, lib, ptr, stream_ptr
+
+GROUPS = ("sum_share",)
+
+# state arrays: name -> (trailing shape as a function of (C, d, capacity), dtype, fill value)
+_FIELDS = {
+    "sum_dir": (lambda C, d, cap: (C, d), torch.float32, 0.0),
+    "cent": (lambda C, d, cap: (C, d), torch.float32, 0.0),
+    "dir8": (lambda C, d, cap: (C, d), torch.int8, 0),
+    "cent8": (lambda C, d, cap: (C, d), torch.int8, 0),
+    "mmax": (lambda C, d, cap: (C,), torch.float32, 0.0),
+    "mmin": (lambda C, d, cap: (C,), torch.float32, math.inf),
+    "count": (lambda C, d, cap: (C,), torch.float32, 0.0),
+    "n_c": (lambda C, d, cap: (), torch.int32, 0),
+    "cap": (lambda C, d, cap: (), torch.float32, math.inf),
+    "rbar": (lambda C, d, cap: (), torch.float32, 0.0),
+    "ksum": (lambda C, d, cap: (d,), torch.float32, 0.0),
+    "mu_ref": (lambda C, d, cap: (d,), torch.float32, 0.0),
+    "flags": (lambda C, d, cap: (), torch.int32, 0),
+    "status": (lambda C, d, cap: (), torch.int32, 0),
+    "nsplit": (lambda C, d, cap: (), torch.int32, 0),
+    "end_dev": (lambda C, d, cap: (), torch.int32, 1),
+    "need_dev": (lambda C, d, cap: (), torch.int32, 0),
+    "labels": (lambda C, d, cap: (cap,), torch.int16, None),       # filled with C
+}
+_STRUCT_NAME = {"end_dev": "end", "need_dev": "need"}
+
+_workspaces: dict = {}
+
+
+def _workspace(device, nbytes: int) -> torch.Tensor:
+    """Grow-only scratch buffer per device for the prompt fit (never used inside a graph)."""
+    key = str(device)
+    buf = _workspaces.get(key)
+    if buf is None or buf.numel() < nbytes:
+        _workspaces[key] = buf = None
+        buf = torch.empty(int(nbytes), dtype=torch.uint8, device=device)
+        _workspaces[key] = buf
+    return buf
+
+
+def release_workspaces() -> None:
+    """Free the fit scratch buffers (they can be several GB after a long prompt)."""
+    _workspaces.clear()
+
+
+class ClusterArena:
+    """State arrays of ``layers`` layers x ``h`` heads stacked over layers, so that one insertion
+    launch covers the whole model (the stacking ssa/kernels/graph_kernels.py:296-314 does after the
+    fact is the allocation layout here)."""
+
+    def __init__(self, *, layers: int, h: int, C: int, d: int, capacity: int, summary_bits: int, device):
+        if capacity % 8:
+            raise ValueError("capacity must be a multiple of 8 (labels are read in 16-byte vectors)")
+        self.layers, self.h, self.C, self.d, self.capacity = layers, h, C, d, capacity
+        self.summary_bits, self.device = summary_bits, device
+        self.t: dict[str, torch.Tensor] = {}
+        for name, (shape, dt, fill) in _FIELDS.items():
+            if summary_bits == 32 and name in ("dir8", "cent8"):
+                continue
+            full = (layers * h, *shape(C, d, capacity))
+            self.t[name] = torch.full(full, C if fill is None else fill, dtype=dt, device=device)
+
+    def views(self, layer: int) -> dict[str, torch.Tensor]:
+        return {k: v[layer * self.h:(layer + 1) * self.h] for k, v in self.t.items()}
+
+    def struct(self, lo: int, hi: int) -> SkvState:
+        """``skv_state`` over entries ``[lo, hi)`` of the stacked arrays."""
+        s = SkvState()
+        s.heads, s.C, s.d, s.capacity, s.summary_bits = hi - lo, self.C, self.d, self.capacity, self.summary_bits
+        for name, t in self.t.items():
+            setattr(s, _STRUCT_NAME.get(name, name), t[lo:hi].data_ptr())
+        if self.summary_bits == 32:
+            s.dir8 = s.cent8 = None
+        return s
+
+
+class SphereIndexGraph:
+    """Cluster state of one layer for ``h`` (sequence, KV head) pairs, with the eager calls
+    (``observe``, ``labels_and_weights``, ``attend``) and the graph-safe ones (``prepare``, ``step``,
+    ``after_replay``)."""
+
+    def __init__(self, *, budget: float = 0.2, C: int = 256, window: int = 64, delta: float = 0.03,
+                 capacity: int = 65536, check_every: int = 16, seed: int = 0, kind: str = "random",
+                 partition: str = "kmeans", kmeans_iters: int = 10, C_init: int | None = None,
+                 split_factor: float = 0.0, grow_cap: bool = False, reset_at: int = 0, cap_keys: float = 0.0,
+                 var_factor: float = 0.0, var_min: int = 8, async_check: bool = True, max_lag: int = 2,
+                 split_scratch: int = 8192, summary_bits: int = 8, block_n: int = 32, compact_block: int = 1024,
+                 refit_every: int = 0, arena: ClusterArena | None = None, layer: int = 0):
+        if partition != "kmeans":
+            raise ValueError(f"unknown partition {partition!r}: only 'kmeans' is built")
+        if summary_bits not in (8, 32):
+            raise ValueError("summary_bits must be 8 or 32")
+        if grow_cap or reset_at or var_factor:
+            raise ValueError("grow_cap, reset_at and var_factor are not built")
+        assert C >= 16 and C & (C - 1) == 0, "C must be a power of two >= 16"
+        self.partition, self.kmeans_iters, self.kind = partition, kmeans_iters, kind
+        self.C_init = C if C_init is None else C_init
+        self.cap_keys = float(cap_keys)
+        self.split_factor = float(split_factor) if split_factor or not cap_keys else 2.0
+        self.splitting = self.split_factor > 0
+        if self.C_init > C:
+            raise ValueError("C_init must be <= C, and splitting needs partition='kmeans'")
+        self.C, self.window, self.delta, self.capacity = C, window, delta, capacity
+        self.check_every, self.seed, self.budget = check_every, seed, budget
+        self.async_check, self.max_lag, self.split_scratch = async_check, max_lag, split_scratch
+        self.summary_bits, self.refit_every = summary_bits, refit_every
+        self.reset_at, self.var_min = 0, var_min
+        self.initialized = False
+        self.n = 0
+        self.start, self.end = 1, 0
+        self.rebuilds = self.resets = self.refits = self.head_steps = 0
+        self._steps = 0
+        self._splits_host = 0
+        self._arena, self._layer = arena, layer
+        self._pending = None
+        self._waited = 0
+        self._ktab = {}
+        self.G = None
+
+    # ---- allocation ------------------------------------------------------------------------------
+    def _alloc(self, h: int, d: int, device) -> None:
+        if d != 128:
+            raise ValueError("the kernels are built for head_dim 128")
+        if self._arena is None:
+            self._arena = ClusterArena(layers=1, h=h, C=self.C, d=d, capacity=self.capacity,
+                                       summary_bits=self.summary_bits, device=device)
+            self._layer = 0
+        a = self._arena
+        if (a.h, a.C, a.d, a.capacity) != (h, self.C, d, self.capacity):
+            raise ValueError("the shared arena was laid out for a different shape")
+        for name, t in a.views(self._layer).items():
+            setattr(self, name, t)
+        if self.summary_bits == 32:
+            self.dir8 = self.cent8 = None
+        self.H_kv, self.d, self.device, self.dtype = h, d, device, torch.float32
+        self._st = a.struct(self._layer * h, (self._layer + 1) * h)
+        self._n_scalar = torch.zeros(1, dtype=torch.int32, device=device)
+        self._flags_host = torch.zeros(h, dtype=torch.int32).pin_memory() if device.type == "cuda" else None
+        self.idx = torch.empty(h, self.capacity, dtype=torch.int32, device=device)
+        self.cnt = torch.zeros(h, dtype=torch.int32, device=device)
+        self.wbuf = torch.zeros(h, self.C + 1, dtype=torch.float32, device=device)
+        self.wbuf[:, self.C] = 1.0
+        self._attn_ws = None
+        self._max_members = None
+
+    def _members_limit(self) -> int:
+        """Largest cluster the in-kernel split has to stage: one key over the largest cap."""
+        if self._max_members is None:
+            lim = lib().skv_insert_max_members()
+            cap = float(self.cap.max()) if self.splitting else 0.0
+            want = int(cap) + 2 if math.isfinite(cap) else 2
+            self._max_members = max(2, min(lim, want))
+        return self._max_members
+
+    def _ktable(self, K: torch.Tensor) -> torch.Tensor:
+        key = K.data_ptr()
+        t = self._ktab.get(key)
+        if t is None:
+            t = torch.tensor([key], dtype=torch.int64, device=K.device)
+            self._ktab = {key: t}
+        return t
+
+    @staticmethod
+    def _check_cache(K: torch.Tensor) -> None:
+        if K.dim() != 3 or K.stride(2) != 1:
+            raise ValueError("the cache must be [heads, positions, d] with a unit last stride")
+
+    # ---- prompt fit ------------------------------------------------------------------------------
+    def _init(self, K: torch.Tensor, n: int) -> None:
+        self._check_cache(K)
+        if n > self.capacity:
+            raise ValueError(f"n={n} exceeds capacity {self.capacity}")
+        if not self.initialized or K.shape[0] != getattr(self, "H_kv", -1):
+            self._alloc(K.shape[0], K.shape[2], K.device)
+        self.start, self.end = 1, max(1, n - self.window)
+        self._fitted = False
+        self.labels.fill_(self.C)
+        self.n_c.zero_()
+        self.end_dev.fill_(self.end)
+        self._build_all(K, n)
+        self.initialized = True
+
+    def _build_all(self, K: torch.Tensor, n: int) -> None:
+        """Fit every head from positions [1, end) (ssa/attn/sphere_gpu.py:187-230, :302-391)."""
+        m = self.end - 1
+        if m < 1:
+            return                                          # nothing to cluster yet: fitted on a later call
+        g = torch.Generator(device="cpu").manual_seed(self.seed)
+        init = torch.randperm(m, generator=g)[torch.arange(self.C_init) % m].to(torch.int32).to(K.device)
+        L = lib()
+        nbytes = L.skv_fit_workspace_bytes(self.H_kv, m, self.C, self.d)
+        ws = _workspace(K.device, nbytes)
+        check(L.skv_fit(ctypes.byref(self._st), K.data_ptr(), dtype_code(K.dtype), K.stride(0), K.stride(1), n,
+                        self.window, self.C_init, self.kmeans_iters, init.data_ptr(), self.cap_keys,
+                        self.split_factor if self.splitting else 0.0, ws.data_ptr(), ws.numel(),
+                        stream_ptr(K.device)), "skv_fit")
+        self._fitted = True
+        self._max_members = None
+        self._splits_host += int(self.nsplit.sum())
+        self.nsplit.zero_()
+
+    # ---- per-step maintenance (eager: lengths known on the host) -----------------------------------
+    def observe(self, K: torch.Tensor, n: int) -> None:
+        """Bring the state up to ``n`` cached positions of ``K [h, >=n, d]`` (sphere_gpu.py:393-399)."""
+        if not self.initialized or n < self.n or K.shape[0] != getattr(self, "H_kv", -1):
+            self._init(K, n)
+        else:
+            self._advance(K, n)
+        self.n = n
+
+    def _launch_insert(self, K: torch.Tensor, n_dev: torch.Tensor, budget: float) -> None:
+        check(lib().skv_insert(ctypes.byref(self._st), self._ktable(K).data_ptr(), self.H_kv, dtype_code(K.dtype),
+                               K.stride(0), K.stride(1), n_dev.data_ptr(), self.window, float(budget),
+                               float(min(self.delta, 3.0e38)), 0, self._members_limit(), stream_ptr(K.device)),
+              "skv_insert")
+
+    def _advance(self, K: torch.Tensor, n: int) -> None:
+        self._check_cache(K)
+        if n > self.capacity:
+            raise ValueError(f"n={n} exceeds capacity {self.capacity}")
+        new_end = max(1, n - self.window)
+        if not self._fitted:
+            if new_end > self.end:                          # nothing was clustered at the first build
+                self.end = new_end
+                self.end_dev.fill_(self.end)
+                self._build_all(K, n)
+        elif new_end > self.end:
+            self._n_scalar.fill_(n)
+            self._launch_insert(K, self._n_scalar, self.budget)
+            self.end = new_end
+        self.head_steps += self.H_kv
+        if self.end - 1 <= 0:
+            return
+        self._steps += 1
+        if self._steps % self.check_every == 0:
+            self._check_flags(K)
+
+    # ---- recentring (host side, between steps) ------------------------------------------------------
+    def _check_flags(self, K: torch.Tensor) -> None:
+        """Read the drift flags and recentre the flagged heads.  With ``async_check`` the flags travel
+        to pinned memory without a synchronisation and are acted on at a later check
+        (protocol of ssa/kernels/sphere_fused.py:434-451)."""
+        if not self.async_check:
+            self._act_on(K, self.flags.cpu())
+            self.flags.zero_()
+            return
+        if self._pending is not None:
+            self._waited += 1
+            if self._waited > self.max_lag and not self._pending.query():
+                self._pending.synchronize()
+            if self._pending.query():
+                self._pending = None
+                self._act_on(K, self._flags_host.clone())
+        if self._pending is None:
+            self._flags_host.copy_(self.flags, non_blocking=True)
+            self._pending = torch.cuda.Event()
+            self._pending.record()
+            self._waited = 0
+            self.flags.zero_()
+
+    def _act_on(self, K: torch.Tensor, flags_host: torch.Tensor) -> None:
+        heads = (flags_host & _lib.FLAG_DRIFT).nonzero().flatten()
+        if heads.numel():
+            self._rebuild(K, heads)
+
+    def _host_end(self) -> None:
+        """Refresh the host copy of ``end`` from the device (a synchronisation; only before host work)."""
+        self.end = int(self.end_dev[0])
+
+    def _rebuild(self, K: torch.Tensor, heads: torch.Tensor) -> None:
+        """Recentre ``heads`` about their running mean and rebin their keys, centroids kept
+        (ssa/attn/sphere_gpu.py:187-219 with the mean given; ssa/kernels/sphere_fused.py:459-464)."""
+        self._host_end()
+        if self.end < 2:
+            return
+        L = lib()
+        hl = heads.to(torch.int32).to(K.device)
+        nbytes = L.skv_fit_workspace_bytes(int(hl.numel()), self.end - 1, self.C, self.d)
+        ws = _workspace(K.device, nbytes)
+        check(L.skv_rebin(ctypes.byref(self._st), hl.data_ptr(), int(hl.numel()), self.end, K.data_ptr(),
+                          dtype_code(K.dtype), K.stride(0), K.stride(1), ws.data_ptr(), ws.numel(),
+                          stream_ptr(K.device)), "skv_rebin")
+        self.rebuilds += int(hl.numel())
+
+    # ---- selection -------------------------------------------------------------------------------
+    def _select(self, q: torch.Tensor, n_dev: torch.Tensor, *, shared_in=None, shared_out=None, e_out=None) -> None:
+        H, d = q.shape
+        G = H // self.H_kv
+        if not q.is_contiguous():
+            q = q.contiguous()
+        check(lib().skv_select(ctypes.byref(self._st), q.data_ptr(), dtype_code(q.dtype), G, n_dev.data_ptr(),
+                               self.wbuf.data_ptr(), self.idx.data_ptr(), self.idx.stride(0), self.cnt.data_ptr(),
+                               ptr(shared_in), ptr(shared_out), ptr(e_out), 1.0 / math.sqrt(d),
+                               stream_ptr(q.device)), "skv_select")
+
+    def labels_and_weights(self, q: torch.Tensor, *, n: int, budget: float, group: str = "sum_share",
+                           shared_in=None, shared_out=None, e_out=None):
+        """``labels [h, n]`` int16 (label ``C`` = always read) and the 0/1 weights ``w [h, C+1]``; also
+        fills ``idx``/``cnt`` with the positions to read.  Persistent buffers, overwritten by the next
+        call (ssa/attn/sphere_gpu.py:412-442, ssa/kernels/sphere_fused.py:466-492)."""
+        if group not in GROUPS:
+            raise ValueError(f"unknown group mode {group!r}")
+        self.need_dev.fill_(math.ceil(budget * (self.end - 1)) if self.end > 1 else 0)
+        self._n_scalar.fill_(n)
+        self._select(q, self._n_scalar, shared_in=shared_in, shared_out=shared_out, e_out=e_out)
+        return self.labels[:, :n], self.wbuf
+
+    # ---- attention -------------------------------------------------------------------------------
+    def _attend(self, q: torch.Tensor, K: torch.Tensor, V: torch.Tensor, *, dense_n=None, force_simple=False):
+        H, d = q.shape
+        G = H // self.H_kv
+        L = lib()
+        if not q.is_contiguous():
+            q = q.contiguous()
+        if self._attn_ws is None or self.G != G:
+            self.G = G
+            self.num_splits = L.skv_attend_splits(self.H_kv)
+            nbytes = L.skv_attend_workspace_bytes(self.H_kv, G, d, self.num_splits)
+            self._attn_ws = torch.zeros(nbytes, dtype=torch.uint8, device=q.device)
+            self.out = torch.empty(H, d, dtype=q.dtype, device=q.device)
+        code = dtype_code(K.dtype) | (256 if force_simple else 0)
+        check(L.skv_attend(q.data_ptr(), K.data_ptr(), V.data_ptr(),
+                           None if dense_n is not None else self.idx.data_ptr(),
+                           None if dense_n is not None else self.cnt.data_ptr(), ptr(dense_n), self.out.data_ptr(),
+                           self._attn_ws.data_ptr(), self.status.data_ptr(), self.H_kv, G, d, code, K.stride(0),
+                           K.stride(1), V.stride(0), V.stride(1), self.idx.stride(0), K.shape[1], self.num_splits,
+                           1.0 / math.sqrt(d), stream_ptr(q.device)), "skv_attend")
+        return self.out
+
+    def attend(self, q: torch.Tensor, K: torch.Tensor, V: torch.Tensor, *, n: int, budget: float,
+               group: str = "sum_share"):
+        """One eager decode step of this layer: update the clusters, select, attend over the selected
+        rows.  ``K, V [h, >=n, d]`` in place.  Returns ``(out [H, d], labels, w)``
+        (ssa/kernels/sphere_fused.py:494-501)."""
+        self.observe(K, n)
+        labels, w = self.labels_and_weights(q, n=n, budget=budget, group=group)
+        return self._attend(q, K, V), labels, w
+
+    # ---- graph-safe calls --------------------------------------------------------------------------
+    def prepare(self, K: torch.Tensor, n: int, H: int) -> None:
+        """Build from the prefilled cache holding ``n`` positions (eager) and allocate the step's fixed
+        buffers (ssa/kernels/graph_kernels.py:204-218)."""
+        self.observe(K, n)
+        if not self._fitted:
+            raise ValueError(f"n={n} leaves nothing to cluster behind a window of {self.window}")
+        G = H // self.H_kv
+        self.G = None
+        q0 = torch.zeros(H, self.d, dtype=K.dtype, device=K.device)
+        self._n_scalar.fill_(n)
+        self.need_dev.fill_(math.ceil(self.budget * (self.end - 1)))
+        self._select(q0, self._n_scalar)
+        self._attend(q0, K, K)                               # sizes the workspace and the output
+        self._members_limit()
+        self._ktable(K)
+        assert self.G == G
+
+    def step(self, q: torch.Tensor, K: torch.Tensor, V: torch.Tensor, n_dev: torch.Tensor, insert: bool = True):
+        """One decode step with every length on the device; position ``n-1`` of ``K, V`` is already
+        written.  ``insert=False`` when one launch inserted for all layers
+        (ssa/kernels/graph_kernels.py:220-244)."""
+        if insert:
+            self._launch_insert(K, n_dev, self.budget)
+        self._select(q, n_dev)
+        return self._attend(q, K, V)
+
+    def after_replay(self, K: torch.Tensor) -> None:
+        """Between graph replays: every ``check_every`` steps look at the drift flags
+        (ssa/kernels/graph_kernels.py:260-269)."""
+        self.head_steps += self.H_kv
+        self._steps += 1
+        if self.refit_every and self._steps % self.refit_every == 0:
+            self._refit(K)
+        elif self._steps % self.check_every == 0:
+            self._check_flags(K)
+
+    def _refit(self, K: torch.Tensor) -> None:
+        """Fit again on every clustered key with a fresh mean (graph_kernels.py:271-279)."""
+        self._host_end()
+        n = self.end + self.window
+        self.labels[:, 1:self.end].fill_(self.C)
+        self._build_all(K, n)
+        self.flags.zero_()
+        self._pending = None
+        self.refits += 1
+
+    # ---- bookkeeping ------------------------------------------------------------------------------
+    @property
+    def splits(self) -> int:
+        """Clusters created by splitting (reads a device counter)."""
+        return self._splits_host + (int(self.nsplit.sum()) if self.initialized else 0)
+
+    @property
+    def active_clusters(self) -> float:
+        return float(self.n_c.float().mean()) if self.initialized else float(self.C)
+
+    def _cap_now(self) -> torch.Tensor:
+        return self.cap
+
+    def _spread(self) -> torch.Tensor:
+        """Variance of each cluster's unit directions about their mean (sphere_gpu.py:276-279)."""
+        return (1 - self.sum_dir.pow(2).sum(-1) / self.count.clamp_min(1).pow(2)).clamp_min(0) * (self.count > 0)
+
+    def check_status(self) -> int:
+        """OR of the device status words (synchronises); 0 means no device-side problem was recorded."""
+        word = 0
+        if self.initialized:
+            for x in self.status.cpu().tolist():
+                word |= int(x)
+        return word
+
+
+# the reference's intermediate class name
+SphereIndexFused = SphereIndexGraph

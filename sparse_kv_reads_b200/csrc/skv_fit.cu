@@ -1,0 +1,776 @@
+// Prompt fit of the cluster state: mean and centring, cosine k-means (float32 FFMA GEMM with a fused
+// arg-max), position-ordered accumulation of the summaries, division of the clusters over the cap, the
+// 8-bit copies; and the recentring rebuild that keeps the centroids.  Host-orchestrated (several
+// launches, one device->host read per split round), used at the end of the prompt, never inside
+// the decode graph.
+//
+// Numerics: the assignment needs float32-grade dot products (a 1e-5 relative error already moves
+// percents of the labels after ten Lloyd steps), so the [keys x 128] . [128 x centroids] product
+// runs on the CUDA cores in float32 with sequential-k accumulation, not on reduced-precision tensor
+// tiles.  Every per-cluster sum is taken in position order by one warp, so reruns are bit-identical.
+#include "skv_common.cuh"
+
+namespace skv {
+
+constexpr int MEAN_CHUNKS = 64;          // row chunks of the two-level column sums
+constexpr int KWAY_MAX = 128;            // most parts one cluster is divided into at the fit
+
+struct FitView {
+    skv_state st;
+    const int32_t *list;      // entry -> head of st (null: identity)
+    int entries;
+    int end;                  // clustered positions are [1, end)
+    int m;                    // end - 1
+    int64_t ksh, ksr;
+    const void *K;
+    // workspace
+    float *Xn;                // [entries, m, 128]
+    float *mag;               // [entries, m]
+    float *colpart;           // [entries, MEAN_CHUNKS, 128]
+    float *sqpart;            // [entries, MEAN_CHUNKS]
+    int32_t *members;         // [entries, m]
+    int16_t *part;            // [entries, m]
+    int32_t *cand;            // [entries, C]
+    int32_t *moff;            // [entries, C + 1]
+    int32_t *extra;           // [entries, C]
+    int32_t *base;            // [entries, C]
+    int32_t *ncand;           // [entries]
+    int32_t *counters;        // [4]: candidates this round, clusters split this round
+};
+
+__device__ __forceinline__ int head_of(const FitView &v, int e) { return v.list ? v.list[e] : e; }
+
+// ---- column sums of the clustered keys (two levels, fixed order) -----------------------------------
+template <typename T>
+__global__ void __launch_bounds__(128) colsum_kernel(const FitView v) {
+    const int e = blockIdx.y, chunk = blockIdx.x, t = threadIdx.x;
+    const int h = head_of(v, e);
+    const T *Kh = static_cast<const T *>(v.K) + (int64_t)h * v.ksh;
+    const int per = (v.m + MEAN_CHUNKS - 1) / MEAN_CHUNKS;
+    const int i0 = chunk * per, i1 = min(i0 + per, v.m);
+    float s = 0.f;
+    for (int i = i0; i < i1; ++i) s += load_as_float(Kh + (int64_t)(i + 1) * v.ksr + t);
+    v.colpart[((int64_t)e * MEAN_CHUNKS + chunk) * HEAD_DIM + t] = s;
+}
+
+// mu = mean (or ksum / m of the running sum when recentring), ksum = column sum; stats zeroed.
+__global__ void __launch_bounds__(128) mean_kernel(const FitView v, int recentre) {
+    const int e = blockIdx.x, t = threadIdx.x;
+    const int h = head_of(v, e);
+    float s = 0.f;
+    for (int c = 0; c < MEAN_CHUNKS; ++c) s += v.colpart[((int64_t)e * MEAN_CHUNKS + c) * HEAD_DIM + t];
+    const float old = v.st.ksum[(int64_t)h * HEAD_DIM + t];
+    const float mu = v.m > 0 ? (recentre ? old : s) / (float)v.m : 0.f;
+    v.st.mu_ref[(int64_t)h * HEAD_DIM + t] = mu;
+    v.st.ksum[(int64_t)h * HEAD_DIM + t] = s;
+}
+
+// unit directions and lengths about mu; per-chunk sums of squared lengths
+template <typename T>
+__global__ void __launch_bounds__(256) centre_kernel(const FitView v) {
+    __shared__ float s_sq[8];
+    const int e = blockIdx.y, chunk = blockIdx.x, lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    const int h = head_of(v, e);
+    const T *Kh = static_cast<const T *>(v.K) + (int64_t)h * v.ksh;
+    const float4 mu = *reinterpret_cast<const float4 *>(v.st.mu_ref + (int64_t)h * HEAD_DIM + lane * 4);
+    const int per = (v.m + MEAN_CHUNKS - 1) / MEAN_CHUNKS;
+    const int i0 = chunk * per, i1 = min(i0 + per, v.m);
+    float sq = 0.f;
+    for (int i = i0 + wid; i < i1; i += 8) {
+        float4 k = load4(Kh + (int64_t)(i + 1) * v.ksr + lane * 4);
+        k.x -= mu.x; k.y -= mu.y; k.z -= mu.z; k.w -= mu.w;
+        const float n2 = warp_sum(k.x * k.x + k.y * k.y + k.z * k.z + k.w * k.w);
+        const float mg = sqrtf(n2);
+        const float inv = 1.0f / fmaxf(mg, 1e-12f);
+        *reinterpret_cast<float4 *>(v.Xn + ((int64_t)e * v.m + i) * HEAD_DIM + lane * 4) =
+            make_float4(k.x * inv, k.y * inv, k.z * inv, k.w * inv);
+        if (lane == 0) v.mag[(int64_t)e * v.m + i] = mg;
+        sq += n2;
+    }
+    if (lane == 0) s_sq[wid] = sq;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float s = 0.f;
+        for (int w = 0; w < 8; ++w) s += s_sq[w];
+        v.sqpart[(int64_t)e * MEAN_CHUNKS + chunk] = s;
+    }
+}
+
+__global__ void rbar_kernel(const FitView v) {
+    const int e = blockIdx.x * blockDim.x + threadIdx.x;
+    if (e >= v.entries) return;
+    float s = 0.f;
+    for (int c = 0; c < MEAN_CHUNKS; ++c) s += v.sqpart[(int64_t)e * MEAN_CHUNKS + c];
+    v.st.rbar[head_of(v, e)] = v.m > 0 ? sqrtf(s / (float)v.m) : 0.f;
+}
+
+// starting centroids: the unit directions at the given clustered-key indices
+__global__ void __launch_bounds__(128) seed_kernel(const FitView v, const int32_t *init_pos, int C_init) {
+    const int e = blockIdx.y, j = blockIdx.x, t = threadIdx.x;
+    const int h = head_of(v, e);
+    const int i = min(max(init_pos[j], 0), v.m - 1);
+    v.st.cent[((int64_t)h * v.st.C + j) * HEAD_DIM + t] = v.Xn[((int64_t)e * v.m + i) * HEAD_DIM + t];
+    if (j == 0 && t == 0) v.st.n_c[h] = C_init;
+}
+
+// ---- nearest centroid of every clustered key: float32 GEMM tile with a fused arg-max ---------------
+// CTA = 64 keys x all n_c centroids in chunks of 64; 256 threads, each 4 keys x 4 centroids.
+// Both tiles sit in shared memory k-contiguous (row stride 132 floats); a thread's centroids are
+// tx, tx+16, tx+32, tx+48 so that a quarter-warp's 128-bit loads cover all banks.
+constexpr int AS_ROWS = 64, AS_COLS = 64, AS_LD = 132;
+constexpr int AS_SMEM = (AS_ROWS + AS_COLS) * AS_LD * 4;
+
+struct Arg {
+    float v;
+    int i;
+};
+__device__ __forceinline__ void arg_take(Arg &a, float v, int i) {
+    if (v > a.v || (v == a.v && i < a.i)) { a.v = v; a.i = i; }
+}
+
+__global__ void __launch_bounds__(256) assign_kernel(const FitView v) {
+    extern __shared__ __align__(16) float smem_f[];
+    float *Xs = smem_f, *Cs = smem_f + AS_ROWS * AS_LD;
+    const int e = blockIdx.y, tile = blockIdx.x, tid = threadIdx.x;
+    const int h = head_of(v, e);
+    const int tx = tid & 15, ty = tid >> 4;
+    const int n_c = min(max(v.st.n_c[h], 0), v.st.C);
+    const int r0 = tile * AS_ROWS;
+    const float *X = v.Xn + ((int64_t)e * v.m + r0) * HEAD_DIM;
+    const int rows = min(AS_ROWS, v.m - r0);
+    for (int i = tid; i < AS_ROWS * 32; i += 256) {
+        const int r = i >> 5, k4 = i & 31;
+        float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (r < rows) x = *reinterpret_cast<const float4 *>(X + (int64_t)r * HEAD_DIM + k4 * 4);
+        *reinterpret_cast<float4 *>(Xs + r * AS_LD + k4 * 4) = x;
+    }
+    Arg best[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) best[i] = Arg{-INFINITY, 0x7fffffff};
+    const float *cent = v.st.cent + (int64_t)h * v.st.C * HEAD_DIM;
+    for (int c0 = 0; c0 < n_c; c0 += AS_COLS) {
+        __syncthreads();
+        for (int i = tid; i < AS_COLS * 32; i += 256) {
+            const int c = i >> 5, k4 = i & 31;
+            float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (c0 + c < n_c) x = *reinterpret_cast<const float4 *>(cent + (int64_t)(c0 + c) * HEAD_DIM + k4 * 4);
+            *reinterpret_cast<float4 *>(Cs + c * AS_LD + k4 * 4) = x;
+        }
+        __syncthreads();
+        float acc[4][4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+#pragma unroll 4
+        for (int k = 0; k < HEAD_DIM; k += 4) {
+            float4 xr[4], cr[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) xr[i] = *reinterpret_cast<const float4 *>(Xs + (ty * 4 + i) * AS_LD + k);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) cr[j] = *reinterpret_cast<const float4 *>(Cs + (tx + 16 * j) * AS_LD + k);
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    acc[i][j] = fmaf(xr[i].x, cr[j].x, acc[i][j]);
+                    acc[i][j] = fmaf(xr[i].y, cr[j].y, acc[i][j]);
+                    acc[i][j] = fmaf(xr[i].z, cr[j].z, acc[i][j]);
+                    acc[i][j] = fmaf(xr[i].w, cr[j].w, acc[i][j]);
+                }
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int c = c0 + tx + 16 * j;
+            if (c < n_c)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) arg_take(best[i], acc[i][j], c);
+        }
+    }
+    int16_t *lab = v.st.labels + (int64_t)h * v.st.capacity + 1;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        Arg b = best[i];
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, b.v, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, b.i, o);
+            arg_take(b, ov, oi);
+        }
+        const int r = ty * 4 + i;
+        if (tx == 0 && r < rows) lab[r0 + r] = (int16_t)(b.i == 0x7fffffff ? 0 : b.i);
+    }
+}
+
+// ---- summaries of every slot from the labels, members taken in position order by one warp --------------
+// lloyd != 0: write cent = unit(sum) where the slot has members (a Lloyd update) instead of the summaries.
+__global__ void __launch_bounds__(256) accumulate_kernel(const FitView v, int lloyd, int slots) {
+    const int e = blockIdx.y, lane = threadIdx.x & 31;
+    const int c = blockIdx.x * 8 + (threadIdx.x >> 5);
+    const int h = head_of(v, e);
+    if (c >= slots) return;
+    const int16_t *lab = v.st.labels + (int64_t)h * v.st.capacity + 1;
+    const float *X = v.Xn + (int64_t)e * v.m * HEAD_DIM;
+    const float *mg = v.mag + (int64_t)e * v.m;
+    float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+    float mx = 0.f, mn = INFINITY;
+    int cnt = 0;
+    const bool live = c < v.st.n_c[h];
+    if (live)
+        for (int i0 = 0; i0 < v.m; i0 += 32) {
+            const int i = i0 + lane;
+            const bool hit = i < v.m && lab[i] == c;
+            unsigned b = __ballot_sync(0xffffffffu, hit);
+            cnt += __popc(b);
+            while (b) {
+                const int j = i0 + __ffs(b) - 1;
+                b &= b - 1;
+                const float4 x = *reinterpret_cast<const float4 *>(X + (int64_t)j * HEAD_DIM + lane * 4);
+                s.x += x.x; s.y += x.y; s.z += x.z; s.w += x.w;
+                const float g = mg[j];
+                mx = fmaxf(mx, g);
+                mn = fminf(mn, g);
+            }
+        }
+    const int64_t row = (int64_t)h * v.st.C + c;
+    if (lloyd) {
+        if (cnt > 0) {
+            const float n2 = warp_sum(s.x * s.x + s.y * s.y + s.z * s.z + s.w * s.w);
+            const float inv = 1.0f / fmaxf(sqrtf(n2), 1e-12f);
+            *reinterpret_cast<float4 *>(v.st.cent + row * HEAD_DIM + lane * 4) =
+                make_float4(s.x * inv, s.y * inv, s.z * inv, s.w * inv);
+        }
+        return;
+    }
+    *reinterpret_cast<float4 *>(v.st.sum_dir + row * HEAD_DIM + lane * 4) = s;
+    if (lane == 0) {
+        v.st.mmax[row] = mx;
+        v.st.mmin[row] = mn;
+        v.st.count[row] = (float)cnt;
+    }
+}
+
+// cap of each head after a fit, flags cleared, slots beyond n_c wiped
+__global__ void finish_fit_kernel(const FitView v, float cap_keys, float split_factor, int C_init, int fitted) {
+    const int e = blockIdx.x * blockDim.x + threadIdx.x;
+    if (e >= v.entries) return;
+    const int h = head_of(v, e);
+    if (fitted) {
+        float cap = INFINITY;
+        if (split_factor > 0.f) cap = cap_keys > 0.f ? cap_keys : split_factor * (float)v.m / (float)C_init;
+        v.st.cap[h] = cap;
+        v.st.nsplit[h] = 0;
+        v.st.status[h] = 0;
+    }
+    v.st.flags[h] = 0;
+    v.st.end[h] = v.end;
+}
+
+// 8-bit copies of the direction sums and centroids of every slot
+__global__ void __launch_bounds__(256) refresh8_kernel(const FitView v) {
+    const int e = blockIdx.y, lane = threadIdx.x & 31;
+    const int c = blockIdx.x * 8 + (threadIdx.x >> 5);
+    const int h = head_of(v, e);
+    if (c >= v.st.C) return;
+    const int64_t row = ((int64_t)h * v.st.C + c) * HEAD_DIM + lane * 4;
+    const float4 a = *reinterpret_cast<const float4 *>(v.st.sum_dir + row);
+    const float4 b = *reinterpret_cast<const float4 *>(v.st.cent + row);
+    const float ia = 1.0f / fmaxf(sqrtf(warp_sum(a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w)), 1e-12f);
+    const float ib = 1.0f / fmaxf(sqrtf(warp_sum(b.x * b.x + b.y * b.y + b.z * b.z + b.w * b.w)), 1e-12f);
+    char4 qa, qb;
+    qa.x = quant8(a.x * ia); qa.y = quant8(a.y * ia); qa.z = quant8(a.z * ia); qa.w = quant8(a.w * ia);
+    qb.x = quant8(b.x * ib); qb.y = quant8(b.y * ib); qb.z = quant8(b.z * ib); qb.w = quant8(b.w * ib);
+    *reinterpret_cast<char4 *>(v.st.dir8 + row) = qa;
+    *reinterpret_cast<char4 *>(v.st.cent8 + row) = qb;
+}
+
+// ---- division of the clusters over the cap, one round ----------------------------------------------
+// counters: [0] candidates over all entries, [1] clusters split, [2] most candidates in one entry,
+//           [3] most parts asked for one cluster
+__global__ void __launch_bounds__(256) find_over_kernel(const FitView v, int kway, float split_factor) {
+    __shared__ int ired[40];
+    const int e = blockIdx.x, tid = threadIdx.x;
+    const int h = head_of(v, e);
+    const int C = v.st.C;
+    const int n_c = min(max(v.st.n_c[h], 0), C);
+    const float cap = v.st.cap[h];
+    const float *count = v.st.count + (int64_t)h * C;
+    const int per = (C + 255) / 256;
+    const int c0 = min(tid * per, n_c), c1 = min(c0 + per, n_c);
+    int mine = 0;
+    for (int c = c0; c < c1; ++c) mine += (count[c] > cap && count[c] >= 2.0f);
+    int total;
+    int off = block_excl_scan(mine, ired, total);
+    int32_t *cand = v.cand + (int64_t)e * C;
+    for (int c = c0; c < c1; ++c)
+        if (count[c] > cap && count[c] >= 2.0f) cand[off++] = c;
+    __syncthreads();
+    if (tid == 0) {
+        int32_t *moff = v.moff + (int64_t)e * (C + 1);
+        int run = 0, kmax = 2;
+        for (int j = 0; j < total; ++j) {
+            moff[j] = run;
+            const float cn = count[cand[j]];
+            run += (int)cn;
+            if (kway) kmax = max(kmax, (int)ceilf(cn * split_factor / cap));
+        }
+        moff[total] = run;
+        v.ncand[e] = total;
+        if (total) {
+            atomicAdd(v.counters + 0, total);
+            atomicMax(v.counters + 2, total);
+            atomicMax(v.counters + 3, kmax);
+        }
+    }
+}
+
+// member lists of the candidates, in position order: one warp per candidate
+__global__ void __launch_bounds__(256) members_kernel(const FitView v) {
+    const int e = blockIdx.y, lane = threadIdx.x & 31;
+    const int j = blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (j >= v.ncand[e]) return;
+    const int h = head_of(v, e);
+    const int c = v.cand[(int64_t)e * v.st.C + j];
+    const int16_t *lab = v.st.labels + (int64_t)h * v.st.capacity + 1;
+    int32_t *mem = v.members + (int64_t)e * v.m + v.moff[(int64_t)e * (v.st.C + 1) + j];
+    int run = 0;
+    for (int i0 = 0; i0 < v.m; i0 += 32) {
+        const int i = i0 + lane;
+        const bool hit = i < v.m && lab[i] == c;
+        const unsigned b = __ballot_sync(0xffffffffu, hit);
+        if (hit) mem[run + __popc(b & ((1u << lane) - 1u))] = i;
+        run += __popc(b);
+    }
+}
+
+struct PartSmem {
+    float *cents;   // [k][128]
+    float *sums;    // [k][128]
+    int *sizes;     // [k]
+    int *newid;     // [k]
+};
+
+// Partition the members of one candidate cluster: k-way cosine k-means from evenly spaced members
+// (kway) or the two-way split with the median-cut fallback.  One CTA per candidate.
+__global__ void __launch_bounds__(256) partition_kernel(const FitView v, int kway, float split_factor, int iters,
+                                                        int kcap, float *projbuf) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    __shared__ float fred[32];
+    __shared__ int ired[40];
+    const int e = blockIdx.y, j = blockIdx.x, tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
+    if (j >= v.ncand[e]) return;
+    const int h = head_of(v, e);
+    const int C = v.st.C;
+    const int c = v.cand[(int64_t)e * C + j];
+    const int o0 = v.moff[(int64_t)e * (C + 1) + j];
+    const int cnt = v.moff[(int64_t)e * (C + 1) + j + 1] - o0;
+    const int32_t *mem = v.members + (int64_t)e * v.m + o0;
+    int16_t *prt = v.part + (int64_t)e * v.m + o0;
+    float *proj = projbuf + (int64_t)e * v.m + o0;
+    const float *X = v.Xn + (int64_t)e * v.m * HEAD_DIM;
+    (void)c;
+    if (kway) {
+        const float cap = v.st.cap[h];
+        int k = (int)ceilf((float)cnt * split_factor / cap);
+        k = min(max(k, 2), kcap);
+        float *cents = reinterpret_cast<float *>(smem_raw);
+        float *sums = cents + (size_t)kcap * HEAD_DIM;
+        int *sizes = reinterpret_cast<int *>(sums + (size_t)kcap * HEAD_DIM);
+        int *newid = sizes + kcap;
+        for (int i = tid; i < k * HEAD_DIM; i += 256) {
+            const int jj = i >> 7, t = i & 127;
+            const int seed = min((int)(((int64_t)jj * cnt) / k), cnt - 1);
+            cents[i] = X[(int64_t)mem[seed] * HEAD_DIM + t];
+        }
+        __syncthreads();
+        for (int it = 0; it <= iters; ++it) {
+            for (int r = wid; r < cnt; r += 8) {
+                const float4 x = *reinterpret_cast<const float4 *>(X + (int64_t)mem[r] * HEAD_DIM + lane * 4);
+                float bv = -INFINITY;
+                int bi = 0;
+                for (int jj = 0; jj < k; ++jj) {
+                    const float4 cc = *reinterpret_cast<const float4 *>(cents + jj * HEAD_DIM + lane * 4);
+                    const float dot = warp_sum(x.x * cc.x + x.y * cc.y + x.z * cc.z + x.w * cc.w);
+                    if (dot > bv) { bv = dot; bi = jj; }
+                }
+                if (lane == 0) prt[r] = (int16_t)bi;
+            }
+            __syncthreads();
+            if (it == iters) break;
+            for (int i = tid; i < k * HEAD_DIM; i += 256) sums[i] = 0.f;
+            for (int i = tid; i < k; i += 256) sizes[i] = 0;
+            __syncthreads();
+            if (tid < HEAD_DIM) {
+#pragma unroll 4
+                for (int r = 0; r < cnt; ++r) sums[prt[r] * HEAD_DIM + tid] += X[(int64_t)mem[r] * HEAD_DIM + tid];
+            } else if (tid == HEAD_DIM) {
+                for (int r = 0; r < cnt; ++r) sizes[prt[r]] += 1;
+            }
+            __syncthreads();
+            for (int jj = wid; jj < k; jj += 8) {
+                const float4 s = *reinterpret_cast<const float4 *>(sums + jj * HEAD_DIM + lane * 4);
+                const float n2 = warp_sum(s.x * s.x + s.y * s.y + s.z * s.z + s.w * s.w);
+                if (sizes[jj] > 0) {
+                    const float inv = 1.0f / fmaxf(sqrtf(n2), 1e-12f);
+                    *reinterpret_cast<float4 *>(cents + jj * HEAD_DIM + lane * 4) =
+                        make_float4(s.x * inv, s.y * inv, s.z * inv, s.w * inv);
+                }
+            }
+            __syncthreads();
+        }
+        // number the non-empty parts 0, 1, ... in part order
+        for (int i = tid; i < k; i += 256) sizes[i] = 0;
+        __syncthreads();
+        if (tid == 0) {
+            for (int r = 0; r < cnt; ++r) sizes[prt[r]] += 1;
+            int run = 0;
+            for (int jj = 0; jj < k; ++jj) { newid[jj] = run; run += sizes[jj] > 0; }
+            v.extra[(int64_t)e * C + j] = run - 1;
+        }
+        __syncthreads();
+        for (int r = tid; r < cnt; r += 256) prt[r] = (int16_t)newid[prt[r]];
+        return;
+    }
+    // ---- two-way split -------------------------------------------------------------------------
+    float *sa = reinterpret_cast<float *>(smem_raw), *sb = sa + HEAD_DIM, *sdiff = sb + HEAD_DIM;
+    if (tid < HEAD_DIM) sa[tid] = X[(int64_t)mem[0] * HEAD_DIM + tid];
+    __syncthreads();
+    {
+        const float4 a4 = *reinterpret_cast<const float4 *>(sa + lane * 4);
+        for (int r = wid; r < cnt; r += 8) {
+            const float4 x = *reinterpret_cast<const float4 *>(X + (int64_t)mem[r] * HEAD_DIM + lane * 4);
+            const float s = warp_sum(x.x * a4.x + x.y * a4.y + x.z * a4.z + x.w * a4.w);
+            if (lane == 0) proj[r] = s;
+        }
+    }
+    __syncthreads();
+    if (wid == 0) {
+        float bv = INFINITY;
+        int bi = 0x7fffffff;
+        for (int r = lane; r < cnt; r += 32) {
+            const float s = proj[r];
+            if (s < bv || (s == bv && r < bi)) { bv = s; bi = r; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ov < bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+        }
+        if (lane == 0) ired[0] = bi;
+    }
+    __syncthreads();
+    if (tid < HEAD_DIM) sb[tid] = X[(int64_t)mem[ired[0]] * HEAD_DIM + tid];
+    __syncthreads();
+    for (int it = 0; it <= 4; ++it) {
+        if (it == 4 && tid < HEAD_DIM) sdiff[tid] = sb[tid] - sa[tid];
+        if (it == 4) __syncthreads();
+        {
+            const float4 a4 = *reinterpret_cast<const float4 *>(sa + lane * 4);
+            const float4 b4 = *reinterpret_cast<const float4 *>(sb + lane * 4);
+            const float4 d4 = *reinterpret_cast<const float4 *>(sdiff + lane * 4);
+            for (int r = wid; r < cnt; r += 8) {
+                const float4 x = *reinterpret_cast<const float4 *>(X + (int64_t)mem[r] * HEAD_DIM + lane * 4);
+                const float da = warp_sum(x.x * a4.x + x.y * a4.y + x.z * a4.z + x.w * a4.w);
+                const float db = warp_sum(x.x * b4.x + x.y * b4.y + x.z * b4.z + x.w * b4.w);
+                if (it == 4) {
+                    const float pj = warp_sum(x.x * d4.x + x.y * d4.y + x.z * d4.z + x.w * d4.w);
+                    if (lane == 0) proj[r] = pj;
+                }
+                if (lane == 0) prt[r] = db > da;
+            }
+        }
+        __syncthreads();
+        if (it == 4) break;
+        float s0 = 0.f, s1 = 0.f;
+        int n1 = 0;
+        if (tid < HEAD_DIM) {
+#pragma unroll 4
+            for (int r = 0; r < cnt; ++r) {
+                const float u = X[(int64_t)mem[r] * HEAD_DIM + tid];
+                if (prt[r]) { s1 += u; ++n1; } else s0 += u;
+            }
+        }
+        const float q0 = block_sum(tid < HEAD_DIM ? s0 * s0 : 0.f, fred);
+        const float q1 = block_sum(tid < HEAD_DIM ? s1 * s1 : 0.f, fred);
+        if (tid == 0) ired[1] = n1;
+        __syncthreads();
+        n1 = ired[1];
+        if (tid < HEAD_DIM) {
+            if (cnt - n1 > 0) sa[tid] = s0 / fmaxf(sqrtf(q0), 1e-12f);
+            if (n1 > 0) sb[tid] = s1 / fmaxf(sqrtf(q1), 1e-12f);
+        }
+        __syncthreads();
+    }
+    int n1 = 0;
+    for (int r = tid; r < cnt; r += 256) n1 += prt[r];
+    n1 = warp_sum_int(n1);
+    if (lane == 0) ired[2 + wid] = n1;
+    __syncthreads();
+    n1 = 0;
+    for (int w = 0; w < 8; ++w) n1 += ired[2 + w];
+    __syncthreads();
+    if ((float)n1 < 0.25f * (float)cnt || (float)n1 > 0.75f * (float)cnt) {
+        const int halfm = cnt / 2;
+        for (int r = tid; r < cnt; r += 256) {
+            const float pj = proj[r];
+            int rank = 0;
+            for (int i = 0; i < cnt; ++i) {
+                const float pi = proj[i];
+                rank += (pi < pj) || (pi == pj && i < r);
+            }
+            prt[r] = rank >= halfm;
+        }
+        n1 = cnt - halfm;
+    }
+    if (tid == 0) v.extra[(int64_t)e * C + j] = (n1 > 0 && n1 < cnt) ? 1 : 0;
+}
+
+// spare slots in candidate order; a cluster whose run of new slots would pass C waits for a later round
+__global__ void slots_kernel(const FitView v) {
+    const int e = blockIdx.x * blockDim.x + threadIdx.x;
+    if (e >= v.entries) return;
+    const int h = head_of(v, e);
+    const int C = v.st.C, nc = v.ncand[e];
+    int run = v.st.n_c[h], taken = 0, kept = 0;
+    for (int j = 0; j < nc; ++j) {
+        const int ex = v.extra[(int64_t)e * C + j];
+        const bool keep = ex > 0 && run + ex <= C;
+        v.base[(int64_t)e * C + j] = keep ? run : -1;
+        if (keep) { taken += ex; ++kept; }
+        run += ex;
+    }
+    if (kept) {
+        v.st.n_c[h] += taken;
+        v.st.nsplit[h] += taken;
+        atomicAdd(v.counters + 1, kept);
+    } else if (nc > 0 && v.st.status) {
+        atomicOr(v.st.status + h, SKV_ST_NO_SLOT);
+    }
+}
+
+// rewrite the summaries, centroids and labels of a split cluster: one warp per part, members in order
+__global__ void __launch_bounds__(256) apply_kernel(const FitView v) {
+    const int e = blockIdx.y, j = blockIdx.x, lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    if (j >= v.ncand[e]) return;
+    const int C = v.st.C;
+    const int base = v.base[(int64_t)e * C + j];
+    if (base < 0) return;
+    const int h = head_of(v, e);
+    const int c = v.cand[(int64_t)e * C + j];
+    const int parts = v.extra[(int64_t)e * C + j] + 1;
+    const int o0 = v.moff[(int64_t)e * (C + 1) + j];
+    const int cnt = v.moff[(int64_t)e * (C + 1) + j + 1] - o0;
+    const int32_t *mem = v.members + (int64_t)e * v.m + o0;
+    const int16_t *prt = v.part + (int64_t)e * v.m + o0;
+    const float *X = v.Xn + (int64_t)e * v.m * HEAD_DIM;
+    const float *mg = v.mag + (int64_t)e * v.m;
+    int16_t *lab = v.st.labels + (int64_t)h * v.st.capacity + 1;
+    for (int pn = wid; pn < parts; pn += 8) {
+        const int slot = pn == 0 ? c : base + pn - 1;
+        float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+        float mx = 0.f, mn = INFINITY;
+        int n = 0;
+        for (int r0 = 0; r0 < cnt; r0 += 32) {
+            const int r = r0 + lane;
+            const bool hit = r < cnt && prt[r] == pn;
+            if (hit) lab[mem[r]] = (int16_t)slot;
+            unsigned b = __ballot_sync(0xffffffffu, hit);
+            n += __popc(b);
+            while (b) {
+                const int rr = r0 + __ffs(b) - 1;
+                b &= b - 1;
+                const int i = mem[rr];
+                const float4 x = *reinterpret_cast<const float4 *>(X + (int64_t)i * HEAD_DIM + lane * 4);
+                s.x += x.x; s.y += x.y; s.z += x.z; s.w += x.w;
+                const float g = mg[i];
+                mx = fmaxf(mx, g);
+                mn = fminf(mn, g);
+            }
+        }
+        const int64_t row = (int64_t)h * C + slot;
+        *reinterpret_cast<float4 *>(v.st.sum_dir + row * HEAD_DIM + lane * 4) = s;
+        const float inv = 1.0f / fmaxf(sqrtf(warp_sum(s.x * s.x + s.y * s.y + s.z * s.z + s.w * s.w)), 1e-12f);
+        *reinterpret_cast<float4 *>(v.st.cent + row * HEAD_DIM + lane * 4) =
+            make_float4(s.x * inv, s.y * inv, s.z * inv, s.w * inv);
+        if (lane == 0) {
+            v.st.mmax[row] = mx;
+            v.st.mmin[row] = mn;
+            v.st.count[row] = (float)n;
+        }
+    }
+}
+
+// ---- host orchestration ---------------------------------------------------------------------------
+static int64_t align256(int64_t x) { return (x + 255) / 256 * 256; }
+
+static int64_t carve(FitView &v, char *base, int entries, int m, int C) {
+    int64_t o = 0;
+    auto take = [&](int64_t bytes) { char *p = base ? base + o : nullptr; o += align256(bytes); return p; };
+    v.Xn = reinterpret_cast<float *>(take((int64_t)entries * m * HEAD_DIM * 4));
+    v.mag = reinterpret_cast<float *>(take((int64_t)entries * m * 4));
+    v.colpart = reinterpret_cast<float *>(take((int64_t)entries * MEAN_CHUNKS * HEAD_DIM * 4));
+    v.sqpart = reinterpret_cast<float *>(take((int64_t)entries * MEAN_CHUNKS * 4));
+    v.members = reinterpret_cast<int32_t *>(take((int64_t)entries * m * 4));
+    v.part = reinterpret_cast<int16_t *>(take((int64_t)entries * m * 2));
+    v.cand = reinterpret_cast<int32_t *>(take((int64_t)entries * C * 4));
+    v.moff = reinterpret_cast<int32_t *>(take((int64_t)entries * (C + 1) * 4));
+    v.extra = reinterpret_cast<int32_t *>(take((int64_t)entries * C * 4));
+    v.base = reinterpret_cast<int32_t *>(take((int64_t)entries * C * 4));
+    v.ncand = reinterpret_cast<int32_t *>(take((int64_t)entries * 4));
+    v.counters = reinterpret_cast<int32_t *>(take(64));
+    return o;
+}
+
+static int64_t fit_bytes(int entries, int m, int C) {
+    FitView v;
+    int64_t o = carve(v, nullptr, entries, m, C);
+    return o + align256((int64_t)entries * m * 4);      // + projections of the two-way split
+}
+
+static int check_state(const skv_state *st) {
+    if (!st) return SKV_E_NULL;
+    if (!st->sum_dir || !st->cent || !st->mmax || !st->mmin || !st->count || !st->n_c || !st->cap || !st->rbar ||
+        !st->ksum || !st->mu_ref || !st->flags || !st->status || !st->nsplit || !st->end || !st->need || !st->labels)
+        return SKV_E_NULL;
+    if (st->d != HEAD_DIM) return SKV_E_DIM;
+    if (st->C < 16 || (st->C & (st->C - 1)) || st->C > 16384) return SKV_E_DIM;
+    if (st->summary_bits != 8 && st->summary_bits != 32) return SKV_E_RANGE;
+    if (st->summary_bits == 8 && (!st->dir8 || !st->cent8)) return SKV_E_NULL;
+    if (st->heads <= 0 || st->capacity <= 0) return SKV_E_RANGE;
+    if (st->capacity % 8 || !aligned16(st->labels) || !aligned16(st->sum_dir) || !aligned16(st->cent) ||
+        !aligned16(st->mu_ref))
+        return SKV_E_ALIGN;
+    return SKV_OK;
+}
+
+template <typename T>
+static int centre_and_assign(FitView &v, int recentre, cudaStream_t s) {
+    colsum_kernel<T><<<dim3(MEAN_CHUNKS, v.entries), 128, 0, s>>>(v);
+    mean_kernel<<<v.entries, 128, 0, s>>>(v, recentre);
+    centre_kernel<T><<<dim3(MEAN_CHUNKS, v.entries), 256, 0, s>>>(v);
+    rbar_kernel<<<(v.entries + 127) / 128, 128, 0, s>>>(v);
+    SKV_CUDA_OK(cudaGetLastError());
+    return SKV_OK;
+}
+
+static int launch_assign(const FitView &v, cudaStream_t s) {
+    static bool configured[64] = {};
+    int dev = 0;
+    SKV_CUDA_OK(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return SKV_E_RANGE;
+    if (!configured[dev]) {
+        SKV_CUDA_OK(cudaFuncSetAttribute(assign_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AS_SMEM));
+        configured[dev] = true;
+    }
+    assign_kernel<<<dim3((v.m + AS_ROWS - 1) / AS_ROWS, v.entries), 256, AS_SMEM, s>>>(v);
+    SKV_CUDA_OK(cudaGetLastError());
+    return SKV_OK;
+}
+
+static int split_rounds(FitView &v, float *projbuf, float split_factor, int iters, cudaStream_t s) {
+    bool kway = true;
+    for (int round = 0; round < 256; ++round) {
+        int32_t host[4] = {0, 0, 0, 0};
+        SKV_CUDA_OK(cudaMemsetAsync(v.counters, 0, 16, s));
+        find_over_kernel<<<v.entries, 256, 0, s>>>(v, kway ? 1 : 0, split_factor);
+        SKV_CUDA_OK(cudaMemcpyAsync(host, v.counters, 16, cudaMemcpyDeviceToHost, s));
+        SKV_CUDA_OK(cudaStreamSynchronize(s));
+        if (host[0] == 0) break;
+        const int maxc = host[2];
+        const int kcap = kway ? (host[3] < 2 ? 2 : (host[3] > KWAY_MAX ? KWAY_MAX : host[3])) : 2;
+        members_kernel<<<dim3((maxc + 7) / 8, v.entries), 256, 0, s>>>(v);
+        const size_t smem = kway ? (size_t)kcap * (2 * HEAD_DIM * 4 + 8) + 64 : 3 * HEAD_DIM * 4;
+        if (smem > 48 * 1024)
+            SKV_CUDA_OK(cudaFuncSetAttribute(partition_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        partition_kernel<<<dim3(maxc, v.entries), 256, smem, s>>>(v, kway ? 1 : 0, split_factor, iters, kcap, projbuf);
+        slots_kernel<<<(v.entries + 127) / 128, 128, 0, s>>>(v);
+        apply_kernel<<<dim3(maxc, v.entries), 256, 0, s>>>(v);
+        SKV_CUDA_OK(cudaMemcpyAsync(host, v.counters, 16, cudaMemcpyDeviceToHost, s));
+        SKV_CUDA_OK(cudaStreamSynchronize(s));
+        if (host[1] == 0 && !kway) break;
+        kway = false;
+    }
+    return SKV_OK;
+}
+
+}  // namespace skv
+
+using namespace skv;
+
+extern "C" int64_t skv_fit_workspace_bytes(int heads, int m, int C, int d) {
+    if (heads <= 0 || m < 0 || C < 16 || d != HEAD_DIM) return SKV_E_RANGE;
+    return fit_bytes(heads, m < 1 ? 1 : m, C);
+}
+
+extern "C" int skv_fit(const skv_state *st, const void *K, int dtype, int64_t k_head_stride, int64_t k_row_stride,
+                       int n, int window, int C_init, int iters, const int32_t *init_pos, float cap_keys,
+                       float split_factor, void *workspace, int64_t workspace_bytes, void *stream) {
+    int rc = check_state(st);
+    if (rc) return rc;
+    if (!K || !init_pos || !workspace) return SKV_E_NULL;
+    if (dtype != SKV_BF16 && dtype != SKV_F32) return SKV_E_DTYPE;
+    if (n < 0 || n > st->capacity || window < 0 || iters < 0 || C_init < 1 || C_init > st->C || cap_keys < 0.f ||
+        split_factor < 0.f)
+        return SKV_E_RANGE;
+    const int esz = dtype == SKV_BF16 ? 2 : 4;
+    if (!aligned16(K) || !aligned16(workspace) || (k_row_stride * esz) % 16 || (k_head_stride * esz) % 16 ||
+        k_row_stride < HEAD_DIM)
+        return SKV_E_ALIGN;
+    const int end = n - window > 1 ? n - window : 1;
+    const int m = end - 1;
+    if (m < 1) return SKV_E_RANGE;                      // nothing to cluster yet
+    if (workspace_bytes < fit_bytes(st->heads, m, st->C)) return SKV_E_WORKSPACE;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    FitView v;
+    v.st = *st; v.list = nullptr; v.entries = st->heads; v.end = end; v.m = m;
+    v.ksh = k_head_stride; v.ksr = k_row_stride; v.K = K;
+    const int64_t used = carve(v, static_cast<char *>(workspace), st->heads, m, st->C);
+    float *projbuf = reinterpret_cast<float *>(static_cast<char *>(workspace) + used);
+    rc = dtype == SKV_BF16 ? centre_and_assign<__nv_bfloat16>(v, 0, s) : centre_and_assign<float>(v, 0, s);
+    if (rc) return rc;
+    // slots beyond C_init start empty; labels of unclustered positions say "always read"
+    SKV_CUDA_OK(cudaMemsetAsync(st->cent, 0, (size_t)st->heads * st->C * HEAD_DIM * 4, s));
+    seed_kernel<<<dim3(C_init, st->heads), 128, 0, s>>>(v, init_pos, C_init);
+    for (int it = 0; it < iters; ++it) {
+        if ((rc = launch_assign(v, s))) return rc;
+        accumulate_kernel<<<dim3((C_init + 7) / 8, st->heads), 256, 0, s>>>(v, 1, C_init);
+    }
+    if ((rc = launch_assign(v, s))) return rc;
+    accumulate_kernel<<<dim3((st->C + 7) / 8, st->heads), 256, 0, s>>>(v, 0, st->C);
+    finish_fit_kernel<<<(st->heads + 127) / 128, 128, 0, s>>>(v, cap_keys, split_factor, C_init, 1);
+    SKV_CUDA_OK(cudaGetLastError());
+    if (split_factor > 0.f && (rc = split_rounds(v, projbuf, split_factor, iters, s))) return rc;
+    if (st->summary_bits == 8) refresh8_kernel<<<dim3((st->C + 7) / 8, st->heads), 256, 0, s>>>(v);
+    SKV_CUDA_OK(cudaGetLastError());
+    return SKV_OK;
+}
+
+extern "C" int skv_rebin(const skv_state *st, const int32_t *head_list, int n_list, int end, const void *K, int dtype,
+                         int64_t k_head_stride, int64_t k_row_stride, void *workspace, int64_t workspace_bytes,
+                         void *stream) {
+    int rc = check_state(st);
+    if (rc) return rc;
+    if (!K || !workspace || !head_list) return SKV_E_NULL;
+    if (dtype != SKV_BF16 && dtype != SKV_F32) return SKV_E_DTYPE;
+    if (n_list < 1 || n_list > st->heads || end < 2 || end > st->capacity) return SKV_E_RANGE;
+    const int esz = dtype == SKV_BF16 ? 2 : 4;
+    if (!aligned16(K) || !aligned16(workspace) || (k_row_stride * esz) % 16 || (k_head_stride * esz) % 16 ||
+        k_row_stride < HEAD_DIM)
+        return SKV_E_ALIGN;
+    const int m = end - 1;
+    if (workspace_bytes < fit_bytes(n_list, m, st->C)) return SKV_E_WORKSPACE;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    FitView v;
+    v.st = *st; v.list = head_list; v.entries = n_list; v.end = end; v.m = m;
+    v.ksh = k_head_stride; v.ksr = k_row_stride; v.K = K;
+    carve(v, static_cast<char *>(workspace), n_list, m, st->C);
+    rc = dtype == SKV_BF16 ? centre_and_assign<__nv_bfloat16>(v, 1, s) : centre_and_assign<float>(v, 1, s);
+    if (rc) return rc;
+    if ((rc = launch_assign(v, s))) return rc;
+    accumulate_kernel<<<dim3((st->C + 7) / 8, n_list), 256, 0, s>>>(v, 0, st->C);
+    finish_fit_kernel<<<(n_list + 127) / 128, 128, 0, s>>>(v, 0.f, 0.f, 1, 0);
+    if (st->summary_bits == 8) refresh8_kernel<<<dim3((st->C + 7) / 8, n_list), 256, 0, s>>>(v);
+    SKV_CUDA_OK(cudaGetLastError());
+    return SKV_OK;
+}
