@@ -1,0 +1,333 @@
+"""Benchmark of the clustered sparse decode-attention path inside a Qwen3 CUDA-graph decode loop.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl reference]
+
+One "step" is one decode step of the whole model (every layer's insert / select / attend inside one CUDA
+graph).  Default workload: Qwen3-0.6B architecture, random weights, bf16, batch 1, a 32,768-token random
+prompt, 20 % budget, 256 clusters per KV head fitted at the prompt, cap 64.  Prints one JSON line.
+With N > 1 (launched through torch.distributed.run) the KV heads, MLP columns and vocabulary are
+sharded over the ranks; the attention needs no communication, NCCL carries the o_proj / MLP all-reduces.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+WORKLOADS = {
+    # name: (model, batch, prompt, budget, slots)
+    "qwen3-0.6b_b1_32k_budget20": ("0.6b", 1, 32768, 0.20, 2048),
+    "qwen3-0.6b_b8_8k_budget5": ("0.6b", 8, 8192, 0.05, 1024),
+    "qwen3-4b_b1_32k_budget20": ("4b", 1, 32768, 0.20, 2048),
+    "qwen3-4b_b4_8k_budget10": ("4b", 4, 8192, 0.10, 1024),
+    "qwen3-0.6b_b1_4k_budget20": ("0.6b", 1, 4096, 0.20, 1024),          # quick check
+}
+DEFAULT = "qwen3-0.6b_b1_32k_budget20"
+
+
+def peaks() -> tuple[float, str]:
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as fh:
+            return float(json.load(fh)["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons sampled while the timed region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            time.sleep(0.15)
+            self.proc.terminate()
+            self.thread.join(timeout=2)
+
+    def summary(self) -> dict:
+        sm, mx, reasons = [], [], set()
+        for r in self.rows:
+            try:
+                sm.append(float(r[1]))
+                mx.append(float(r[2]))
+            except (ValueError, IndexError):
+                continue
+            for name, col in (("hw_slowdown", 5), ("hw_thermal_slowdown", 6), ("sw_thermal_slowdown", 7),
+                              ("sw_power_cap", 8)):
+                if len(r) > col and r[col].lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ---------------------------------------------------------------------------------------------
+# reference arm / CPU baseline: the oracle's attention path on the host cores
+# ---------------------------------------------------------------------------------------------
+def cpu_attention_path(n: int, budget: float, slots: int, layers: int, steps: int, warmup: int, h: int = 8, G: int = 2):
+    """Time the CPU oracle (restatement of the reference's PyTorch path) on ONE layer of ``h`` KV heads at
+    context ``n``: prompt fit once, then ``warmup + steps`` decode steps of insert + select + attention over
+    the selected rows.  Returns (seconds per layer-step, fit seconds, cores)."""
+    from oracle import cluster_oracle as oc
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    total = warmup + steps
+    K, V = oc.clustered_keys(h, n + total, 128, seed=1)
+    K, V = K.to(torch.bfloat16), V.to(torch.bfloat16)
+    Q = torch.randn(total + 1, h * G, 128, generator=torch.Generator().manual_seed(2)).to(torch.bfloat16)
+    st = oc.ClusterOracle(C=slots, C_init=256, cap_keys=64.0, window=64, delta=0.03, capacity=n + total + 8)
+    t0 = time.perf_counter()
+    st.observe(K, n)
+    fit_s = time.perf_counter() - t0
+    times = []
+    for t in range(1, total + 1):
+        t0 = time.perf_counter()
+        st.observe(K, n + t)
+        labels, w = st.select(Q[t].float(), n=n + t, budget=budget)
+        oc.attend_rows(Q[t], K, V, st.positions(w, n + t), dtype=torch.float32)
+        times.append(time.perf_counter() - t0)
+    timed = times[warmup:]
+    return sum(timed) / len(timed), fit_s, cores
+
+
+def reference_arm(args, wl) -> None:
+    """``--impl reference``: the reference's algorithm for this path on the host CPU (its Python
+    implementation cannot travel to the GPU box; the oracle is its pinned restatement)."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    model, B, n, budget, slots = wl
+    layers = 28 if model == "0.6b" else 36
+    G = 2 if model == "0.6b" else 4
+    steps, warmup = max(1, min(args.steps, 8)), max(1, min(args.warmup, 2))
+    per_layer, fit_s, cores = cpu_attention_path(min(n, 32768), budget, slots, layers, steps, warmup, h=8, G=G)
+    ms = per_layer * layers * B * 1e3
+    value = B / (per_layer * layers * B)
+    sample = (f"oracle attention path only (insert+select+attend), 1 layer x 8 KV heads at n={min(n, 32768)}, "
+              f"{steps} timed steps, scaled x{layers} layers x batch {B}; dense layers excluded; fit {fit_s:.2f}s")
+    line = {"impl": "reference", "metric": "qwen3_decode_tokens_per_s", "value": value, "unit": "tok/s",
+            "n_gpus": args.gpus, "steps": steps, "warmup": warmup, "ms_per_step": ms, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": args.workload, "batch": B, "prompt": n, "budget": budget},
+            "cpu_baseline": {"value": value, "unit": "tok/s", "cores": cores, "kind": "port", "sample": sample},
+            "e2e": {"value": value, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+# ---------------------------------------------------------------------------------------------
+# GPU arm
+# ---------------------------------------------------------------------------------------------
+def build_decoder(wl, dev, tp_group, tp_size, tp_rank, decode_steps):
+    from sparse_kv_reads_b200 import GraphDecoder, Qwen3Config, Qwen3Model
+    model_name, B, n, budget, slots = wl
+    cfg = Qwen3Config.qwen3_0_6b() if model_name == "0.6b" else Qwen3Config.qwen3_4b()
+    with torch.device(dev):
+        model = Qwen3Model(cfg, tp_group=tp_group, tp_size=tp_size, tp_rank=tp_rank)
+    model = model.to(torch.bfloat16).eval()
+    model.init_random(seed=0)
+    cap = -(-(n + decode_steps + 8) // 16) * 16
+    cache = model.alloc_cache(cap, max_batch=B)
+    ids = torch.randint(0, cfg.vocab_size, (B, n + decode_steps + 1), generator=torch.Generator().manual_seed(1))
+    with torch.no_grad():
+        model.prefill(ids[:, :n].to(dev), cache, chunk=2048)
+    dec = GraphDecoder(model, cache, mode="cluster", budget=budget, C=slots, C_init=256, cap_keys=64.0, window=64,
+                       summary_bits=8)
+    t0 = time.perf_counter()
+    dec.prepare(n)
+    torch.cuda.synchronize()
+    fit_s = time.perf_counter() - t0
+    dec.capture()
+    return model, cache, dec, ids, fit_s
+
+
+def kernel_roofline(dec, n_now, peak_gbs, which):
+    """Per-launch duration of the attention kernel measured with CUDA events, layer by layer, outside the
+    graph (each layer's rows are cold: the layers' caches together are far larger than L2), and of the
+    three kernels of a layer step together.  Bytes: K and V rows read plus their 4-byte positions for the
+    attention kernel; the full accounting formula for the layer step."""
+    from sparse_kv_reads_b200.accounting import step_bytes
+    B, H, H_kv, d = dec.B, dec.H, dec.H_kv, dec.d
+    dev = dec.tok.device
+    layers = dec.attn
+    q = torch.randn(B * H, d, device=dev).to(torch.bfloat16)
+    flush = torch.empty(512 * 1024 * 1024, dtype=torch.uint8, device=dev)
+    att_ms, step_ms = [], []
+    ev = lambda: torch.cuda.Event(enable_timing=True)
+    for rep in range(3):
+        for i, ix in enumerate(layers):
+            K, V = dec._heads(dec.cache.k[i]), dec._heads(dec.cache.v[i])
+            flush.zero_()
+            a, b, c = ev(), ev(), ev()
+            a.record()
+            ix._select(q, dec.n_dev)
+            b.record()
+            ix._attend(q, K, V)
+            c.record()
+            torch.cuda.synchronize()
+            if rep:
+                att_ms.append(b.elapsed_time(c))
+                step_ms.append(a.elapsed_time(c))
+    rows = torch.stack([ix.cnt for ix in layers]).float()              # [layers, heads]
+    n_c = torch.stack([ix.n_c for ix in layers]).float()
+    att_bytes = float((rows * (2 * 256 + 4)).sum(1).mean())
+    stp_bytes = float(step_bytes(n=n_now, rows=rows, clusters=n_c, d=d, summary_bits=8).sum(1).mean())
+    att_t = sum(att_ms) / len(att_ms) * 1e-3
+    stp_t = sum(step_ms) / len(step_ms) * 1e-3
+    roof = {"bound": "hbm", "kernel": "attend_mma_kernel", "achieved": att_bytes / att_t / 1e9, "peak": peak_gbs,
+            "unit": "GB/s", "frac": att_bytes / att_t / 1e9 / peak_gbs, "traffic": None, "peak_source": which,
+            "us_per_launch": att_t * 1e6, "bytes_per_launch": att_bytes}
+    layer = {"kernels": "select + attend (insert runs once for all layers)", "us_per_layer": stp_t * 1e6,
+             "bytes_per_layer": stp_bytes, "achieved": stp_bytes / stp_t / 1e9, "unit": "GB/s",
+             "frac": stp_bytes / stp_t / 1e9 / peak_gbs, "rows_per_head": float(rows.mean()),
+             "clusters_per_head": float(n_c.mean())}
+    del flush
+    return roof, layer
+
+
+def gpu_arm(args, wl) -> None:
+    import torch.distributed as dist
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the kernels have no CPU fallback")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    group = None
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+        group = dist.group.WORLD
+    model_name, B, n, budget, slots = wl
+    K_steps, W = args.steps, args.warmup
+    total = 2 * (K_steps + W) + 4
+    model, cache, dec, ids, fit_s = build_decoder(wl, dev, group, world, rank, total)
+    ids_dev = ids.to(dev)
+    pinned = ids.pin_memory()
+    result_host = torch.zeros(B, dtype=torch.long).pin_memory()
+    pos = n
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- device-resident leg: token ids already in HBM ------------------------------------------
+    for _ in range(W):
+        dec.step(ids_dev[:, pos:pos + 1], pos)
+        pos += 1
+    barrier()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local) as clocks:
+        start.record()
+        for _ in range(K_steps):
+            dec.step(ids_dev[:, pos:pos + 1], pos)
+            pos += 1
+        stop.record()
+        barrier()
+    dev_ms = start.elapsed_time(stop)
+    # ---- end-to-end leg: ids from pinned host memory, next-token ids read back every step ----------
+    for _ in range(W):
+        logits = dec.step(pinned[:, pos:pos + 1].to(dev, non_blocking=True), pos)
+        result_host.copy_(logits[:, -1].argmax(-1), non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        pos += 1
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(K_steps):
+        logits = dec.step(pinned[:, pos:pos + 1].to(dev, non_blocking=True), pos)
+        result_host.copy_(logits[:, -1].argmax(-1), non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        pos += 1
+    e1.record()
+    barrier()
+    e2e_ms = e0.elapsed_time(e1)
+    t = torch.tensor([dev_ms, e2e_ms], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    dev_ms, e2e_ms = float(t[0]), float(t[1])
+    status = 0
+    for ix in dec.attn:
+        status |= ix.check_status()
+    if rank == 0:
+        peak, which = peaks()
+        roof, layer = kernel_roofline(dec, pos, peak, which)
+        line = {"metric": "qwen3_decode_tokens_per_s", "value": B * K_steps / (dev_ms * 1e-3), "unit": "tok/s",
+                "n_gpus": world, "steps": K_steps, "warmup": W, "ms_per_step": dev_ms / K_steps,
+                "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
+                "data": "synthetic",
+                "config": {"workload": args.workload, "model": f"qwen3-{model_name} architecture, random weights",
+                           "batch": B, "prompt": n, "budget": budget, "slots": slots, "clusters_fitted": 256,
+                           "cap_keys": 64, "window": 64, "summary_bits": 8,
+                           "parallelism": f"tp{world} (KV heads sharded)" if world > 1 else "single GPU",
+                           "l2": "per-layer caches total far more than L2; the kernel leg also flushes 512 MB"},
+                "e2e": {"value": B * K_steps / (e2e_ms * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": 8 * B,
+                        "d2h_bytes_per_step": 8 * B, "ms_per_step": e2e_ms / K_steps},
+                "gpu_launches": K_steps * (1 + 2 * len(dec.attn)),
+                "clocks": clocks.summary(), "roofline": roof, "layer_step": layer,
+                "prompt_fit_s": fit_s, "device_status": status,
+                "splits": sum(ix.splits for ix in dec.attn)}
+        if world == 1 and not args.no_cpu:
+            per_layer, cfit, cores = cpu_attention_path(min(n, 32768), budget, slots, len(dec.attn), 4, 1,
+                                                        h=8, G=dec.H // dec.H_kv)
+            line["cpu_baseline"] = {"value": 1.0 / (per_layer * len(dec.attn) * B), "unit": "tok/s", "cores": cores,
+                                    "kind": "port",
+                                    "sample": f"oracle attention path only, 1 layer x 8 KV heads at n={min(n, 32768)}, 4 "
+                                              f"timed steps, scaled x{len(dec.attn)} layers x batch {B}; dense layers "
+                                              f"excluded; CPU fit {cfit:.2f}s"}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--workload", default=DEFAULT, choices=sorted(WORKLOADS))
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    wl = WORKLOADS[args.workload]
+    if args.impl == "reference":
+        reference_arm(args, wl)
+    else:
+        gpu_arm(args, wl)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,188 @@
+"""Whole decode step as one CUDA graph, with the clustered sparse attention inside it.
+
+Mirror of the reference's ``GraphDecoder`` (ssa/models/graph_decode.py:29-157): same constructor
+keywords, ``prepare(n)``, ``capture()``, ``step(token, pos)``, the attributes ``attn``, ``insert_all``,
+``H, H_kv, d, B`` and ``_heads(cache)``.  The position lives in device memory, so a step is a single
+graph launch; the batch is folded into the KV heads (``B`` sequences x ``H_kv`` heads are ``B*H_kv``
+independent heads for every attention kernel).  Modes: ``"cluster"`` (aliases ``"sphere"``,
+``"voronoi"``) and ``"dense"`` (exact attention by the same gather kernel in its dense mode).
+"""
+
+from __future__ import annotations
+
+import ctypes
+import math
+
+import torch
+
+from ._lib import check, dtype_code, lib, stream_ptr
+from .cluster_state import ClusterArena, SphereIndexGraph
+from .qwen3 import apply_rope
+
+
+class DenseAttentionGraph:
+    """Exact decode attention over ``[0, n)`` with ``n`` in device memory
+    (ssa/kernels/graph_kernels.py:171-189)."""
+
+    def __init__(self, *, H: int, H_kv: int, d: int, dtype, device):
+        L = lib()
+        self.H, self.H_kv, self.d, self.G = H, H_kv, d, H // H_kv
+        self.num_splits = L.skv_attend_splits(H_kv)
+        self.ws = torch.zeros(L.skv_attend_workspace_bytes(H_kv, self.G, d, self.num_splits), dtype=torch.uint8,
+                              device=device)
+        self.out = torch.empty(H, d, dtype=dtype, device=device)
+
+    def __call__(self, q: torch.Tensor, K: torch.Tensor, V: torch.Tensor, n_dev: torch.Tensor) -> torch.Tensor:
+        if not q.is_contiguous():
+            q = q.contiguous()
+        check(lib().skv_attend(q.data_ptr(), K.data_ptr(), V.data_ptr(), None, None, n_dev.data_ptr(),
+                               self.out.data_ptr(), self.ws.data_ptr(), None, self.H_kv, self.G, self.d,
+                               dtype_code(K.dtype), K.stride(0), K.stride(1), V.stride(0), V.stride(1), 0, K.shape[1],
+                               self.num_splits, 1.0 / math.sqrt(self.d), stream_ptr(q.device)), "skv_attend")
+        return self.out
+
+
+class AllLayerInsert:
+    """One insertion launch for every layer: the key that leaves the recent window at a step was written
+    ``window`` steps earlier at every layer, so all layers insert (and split) together before the first
+    layer runs (ssa/kernels/graph_kernels.py:286-325).  The layers' state already sits in one stacked
+    arena; this object holds the table of per-layer cache addresses."""
+
+    def __init__(self, layers: list, caches: list):
+        first = layers[0]
+        assert first.window >= 1, "with no recent window the key to insert is not yet written at later layers"
+        assert all(i._arena is first._arena and i.end == first.end for i in layers)
+        k0 = caches[0]
+        assert all(k.stride() == k0.stride() and k.dtype == k0.dtype for k in caches)
+        self.layers, self.L = layers, len(layers)
+        self.arena = first._arena
+        self.k0 = k0
+        self.table = torch.tensor([k.data_ptr() for k in caches], dtype=torch.int64, device=k0.device)
+        self.st = self.arena.struct(0, self.L * first.H_kv)
+        self.max_members = max(i._members_limit() for i in layers)
+
+    def __call__(self, n_dev: torch.Tensor) -> None:
+        f = self.layers[0]
+        check(lib().skv_insert(ctypes.byref(self.st), self.table.data_ptr(), f.H_kv, dtype_code(self.k0.dtype),
+                               self.k0.stride(0), self.k0.stride(1), n_dev.data_ptr(), f.window, float(f.budget),
+                               float(min(f.delta, 3.0e38)), 0, self.max_members, stream_ptr(self.k0.device)),
+              "skv_insert")
+
+
+class GraphDecoder:
+    def __init__(self, model, cache, *, mode: str = "dense", budget: float = 0.2, C: int | None = None,
+                 window: int = 64, delta: float = 0.03, check_every: int = 16, partition: str = "kmeans",
+                 C_init: int | None = None, split_factor: float | None = None, refit_every: int = 0,
+                 grow_cap: bool = False, reset_at: int = 0, summary_bits: int = 8, cap_keys: float = 0.0,
+                 fused_insert: bool = True, var_factor: float = 0.0, var_min: int = 8, **_):
+        cfg = model.cfg
+        # no slot count given: 1,024 slots, 256 fitted at the prompt, split over twice the mean size
+        # (ssa/models/graph_decode.py:38-43)
+        if C is None:
+            C = 1024
+            C_init = 256 if C_init is None else C_init
+            split_factor = 2.0 if split_factor is None else split_factor
+        split_factor = 0.0 if split_factor is None else split_factor
+        mode = "cluster" if mode in ("sphere", "voronoi") else mode
+        if mode not in ("dense", "cluster"):
+            raise ValueError(f"unknown mode {mode!r}")
+        self.model, self.cache, self.mode = model, cache, mode
+        self.H, self.H_kv, self.d = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
+        self.B = B = cache.k[0].shape[0]
+        p = next(model.parameters())
+        dev, dtype = p.device, p.dtype
+        self.tok = torch.zeros(B, 1, dtype=torch.long, device=dev)
+        self.pos = torch.zeros(1, dtype=torch.long, device=dev)
+        self.n_dev = torch.zeros(1, dtype=torch.int32, device=dev)
+        cap = cache.max_seq_len
+        nl = len(model.layers)
+        if mode == "dense":
+            self.attn = [DenseAttentionGraph(H=B * self.H, H_kv=B * self.H_kv, d=self.d, dtype=dtype, device=dev)
+                         for _ in range(nl)]
+        else:
+            arena = ClusterArena(layers=nl, h=B * self.H_kv, C=C, d=self.d, capacity=cap, summary_bits=summary_bits,
+                                 device=dev)
+            self.attn = [SphereIndexGraph(budget=budget, C=C, window=window, delta=delta, capacity=cap,
+                                          check_every=check_every, partition=partition, C_init=C_init,
+                                          split_factor=split_factor, refit_every=refit_every, grow_cap=grow_cap,
+                                          reset_at=reset_at, summary_bits=summary_bits, cap_keys=cap_keys,
+                                          var_factor=var_factor, var_min=var_min, arena=arena, layer=i)
+                         for i in range(nl)]
+        self.graph = None
+        self.logits = None
+        self.fused_insert = fused_insert and mode == "cluster" and window >= 1
+        self.insert_all = None
+
+    def _heads(self, c: torch.Tensor) -> torch.Tensor:
+        """Cache ``[B, H_kv, L, d]`` -> ``[B*H_kv, L, d]`` (a view)."""
+        return c.view(-1, c.shape[2], c.shape[3])
+
+    def prepare(self, n: int) -> None:
+        """Build the attention state from the first ``n`` cached positions (after the prompt)."""
+        if self.mode != "cluster":
+            return
+        for i, idx in enumerate(self.attn):
+            idx.prepare(self._heads(self.cache.k[i]), n, self.B * self.H)
+        if self.fused_insert:
+            self.insert_all = AllLayerInsert(self.attn, [self._heads(k) for k in self.cache.k[:len(self.attn)]])
+
+    def _body(self) -> torch.Tensor:
+        m, H, H_kv, d, B = self.model, self.H, self.H_kv, self.d, self.B
+        torch.add(self.pos, 1, out=self.n_dev)
+        if self.insert_all is not None:
+            self.insert_all(self.n_dev)
+        h = m.embed(self.tok)
+        cos = m.rope_cos.index_select(0, self.pos)
+        sin = m.rope_sin.index_select(0, self.pos)
+        for i, layer in enumerate(m.layers):
+            a = layer.attn
+            x = layer.norm1(h)
+            q = a.q_norm(a.q(x).view(B, 1, H, d)).transpose(1, 2)
+            k = a.k_norm(a.k(x).view(B, 1, H_kv, d)).transpose(1, 2)
+            v = a.v(x).view(B, 1, H_kv, d).transpose(1, 2)
+            q, k = apply_rope(q, k, cos, sin)
+            kc, vc = self.cache.k[i], self.cache.v[i]
+            kc.index_copy_(2, self.pos, k)
+            vc.index_copy_(2, self.pos, v)
+            qh = q.reshape(B * H, d)
+            if self.mode == "dense":
+                out = self.attn[i](qh, self._heads(kc), self._heads(vc), self.n_dev)
+            else:
+                out = self.attn[i].step(qh, self._heads(kc), self._heads(vc), self.n_dev,
+                                        insert=self.insert_all is None)
+            h = h + a.tp.all_reduce(a.o(out.view(B, 1, H * d)))
+            h = h + layer.ffn(layer.norm2(h))
+        return m.logits(m.final_norm(h))
+
+    def capture(self) -> None:
+        """Record one decode step.  Call after ``prepare`` and before the first ``step``; the warm-up
+        runs write a placeholder at the current position, which the first real step overwrites."""
+        self.pos.fill_(self.cache.cur_len)
+        s = torch.cuda.Stream()
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s), torch.no_grad():
+            for _ in range(2):
+                self._body()
+        torch.cuda.current_stream().wait_stream(s)
+        if self.mode == "cluster":                     # the warm-up steps must not have advanced the clusters
+            torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.no_grad(), torch.cuda.graph(g):
+            self.logits = self._body()
+        self.graph = g
+
+    @torch.no_grad()
+    def step(self, token: torch.Tensor, pos: int) -> torch.Tensor:
+        """Decode ``token [B, 1]`` at position ``pos``; returns logits ``[B, 1, vocab]`` (a buffer the
+        next step overwrites)."""
+        self.tok.copy_(token)
+        self.pos.fill_(pos)
+        if self.graph is not None:
+            self.graph.replay()
+        else:
+            self.logits = self._body()
+        if self.mode == "cluster":
+            for i, idx in enumerate(self.attn):
+                idx.after_replay(self._heads(self.cache.k[i]))
+        self.cache.cur_len = pos + 1
+        return self.logits

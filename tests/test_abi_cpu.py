@@ -1,0 +1,129 @@
+"""The C-ABI library on a machine without a GPU: it loads, exports every declared symbol and rejects
+bad arguments on the host with the documented codes (no kernel is launched here)."""
+
+from __future__ import annotations
+
+import ctypes
+import os
+import re
+
+import pytest
+import torch
+
+from sparse_kv_reads_b200 import _lib
+from sparse_kv_reads_b200.build import build
+from sparse_kv_reads_b200.cluster_state import ClusterArena, SphereIndexGraph
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def L():
+    build()
+    return _lib.lib()
+
+
+def declared_functions():
+    text = open(os.path.join(ROOT, "include", "skv.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(skv_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_every_declared_entry_point_is_exported(L):
+    names = declared_functions()
+    assert len(names) >= 13
+    for name in names:
+        assert hasattr(L, name), name
+    assert set(names) == set(_lib.EXPORTS)
+    assert L.skv_version() == 100
+    assert L.skv_error_string(-4).decode().startswith("pointer or stride")
+
+
+def test_struct_layout_matches_the_header():
+    text = open(os.path.join(ROOT, "include", "skv.h")).read()
+    body = text[text.index("typedef struct skv_state {"):text.index("} skv_state;")]
+    fields = re.findall(r"^\s+(?:int32_t|float|int8_t|int16_t)\s+\*?([A-Za-z0-9_]+);", body, flags=re.M)
+    assert fields == [f[0] for f in _lib.SkvState._fields_]
+    assert ctypes.sizeof(_lib.SkvState) == 6 * 4 + 18 * 8
+
+
+def fake_state(C=64, cap=64, bits=32, heads=2):
+    """A state whose pointers are aligned non-null fakes: validation must reject before use."""
+    s = _lib.SkvState()
+    s.heads, s.C, s.d, s.capacity, s.summary_bits = heads, C, 128, cap, bits
+    for name, _ in _lib.SkvState._fields_[6:]:
+        setattr(s, name, 0x1000)
+    return s
+
+
+def test_attend_rejects_bad_arguments(L):
+    ok = 0x1000
+    args = dict(q=ok, K=ok, V=ok, idx=ok, cnt=ok, n_dev=None, out=ok, ws=ok, status=None, heads=2, G=2, d=128, dtype=0,
+                ksh=128 * 64, ksr=128, vsh=128 * 64, vsr=128, istr=64, lim=64, splits=4)
+
+    def call(**over):
+        a = {**args, **over}
+        return L.skv_attend(a["q"], a["K"], a["V"], a["idx"], a["cnt"], a["n_dev"], a["out"], a["ws"], a["status"],
+                            a["heads"], a["G"], a["d"], a["dtype"], a["ksh"], a["ksr"], a["vsh"], a["vsr"], a["istr"],
+                            a["lim"], a["splits"], 0.1, None)
+
+    assert call(q=None) == -1 and call(cnt=None) == -1 and call(idx=None, n_dev=None) == -1
+    assert call(d=64) == -2 and call(G=17) == -2 and call(dtype=1, G=9) == -2
+    assert call(dtype=7) == -3
+    assert call(K=0x1008) == -4 and call(ksr=100) == -4 and call(ksr=132) == -4
+    assert call(heads=0) == -5 and call(splits=0) == -5
+    assert L.skv_attend_splits(8) == 37 and L.skv_attend_splits(0) == -5        # 2 CTAs per SM of 148
+    assert L.skv_attend_workspace_bytes(8, 2, 128, 37) == 8 * 37 * 2 * 130 * 4 + 256
+    assert L.skv_attend_workspace_bytes(8, 2, 64, 37) == -5
+
+
+def test_state_calls_reject_bad_arguments(L):
+    ok = 0x1000
+    st = fake_state()
+    sel = lambda s, **o: L.skv_select(ctypes.byref(s), o.get("q", ok), o.get("dtype", 0), o.get("G", 2), ok, ok, ok,
+                                      o.get("istr", 64), ok, None, None, None, 0.1, None)
+    assert sel(fake_state(C=48)) == -2 and sel(fake_state(C=8)) == -2 and sel(st, G=0) == -2
+    assert sel(st, q=None) == -1 and sel(st, dtype=5) == -3 and sel(st, istr=8) == -5
+    assert sel(fake_state(cap=60)) == -4 and sel(fake_state(bits=16)) == -5
+    bad = fake_state(bits=8)
+    bad.dir8 = None
+    assert sel(bad) == -1
+    ins = lambda s, **o: L.skv_insert(ctypes.byref(s), ok, o.get("hpl", 2), 0, 128 * 64, o.get("ksr", 128), ok, 64, 0.2,
+                                      0.03, 0, o.get("mm", 66), None)
+    assert ins(st, hpl=3) == -5 and ins(st, mm=1) == -5 and ins(st, mm=10 ** 6) == -5 and ins(st, ksr=120) == -4
+    assert L.skv_insert_max_members() >= 400
+    fit = lambda s, **o: L.skv_fit(ctypes.byref(s), ok, 0, 128 * 64, 128, o.get("n", 64), o.get("window", 8),
+                                   o.get("C_init", 16), 10, ok, 0.0, 0.0, ok, o.get("bytes", 1 << 40), None)
+    assert fit(st, n=100) == -5 and fit(st, C_init=128) == -5 and fit(st, n=8, window=8) == -5
+    assert fit(st, bytes=16) == -6
+    assert L.skv_fit_workspace_bytes(2, 55, 64, 128) > 2 * 55 * 512
+    assert L.skv_rebin(ctypes.byref(st), ok, 3, 32, ok, 0, 128 * 64, 128, ok, 1 << 40, None) == -5
+    assert L.skv_merge(None, ok, ok, ok, 1, 1, 1, 128, None) == -1
+
+
+def test_host_class_options_follow_the_reference():
+    with pytest.raises(ValueError):
+        SphereIndexGraph(partition="spiral")
+    with pytest.raises(ValueError):
+        SphereIndexGraph(summary_bits=16)
+    with pytest.raises(ValueError):
+        SphereIndexGraph(C=64, C_init=128)
+    with pytest.raises(AssertionError):
+        SphereIndexGraph(C=48)
+    ix = SphereIndexGraph(C=1024, C_init=256, cap_keys=64.0)
+    assert ix.split_factor == 2.0 and ix.splitting                   # an absolute cap turns splitting on
+    assert not SphereIndexGraph(C=256).splitting
+    arena = ClusterArena(layers=3, h=2, C=16, d=128, capacity=64, summary_bits=8, device=torch.device("cpu"))
+    v = arena.views(1)
+    assert v["labels"].shape == (2, 64) and int(v["labels"][0, 0]) == 16 and torch.isinf(v["mmin"]).all()
+    s = arena.struct(2, 4)
+    assert s.heads == 2 and s.labels == arena.t["labels"][2:4].data_ptr()
+    with pytest.raises(ValueError):
+        ClusterArena(layers=1, h=1, C=16, d=128, capacity=60, summary_bits=8, device=torch.device("cpu"))
+
+
+def test_a_missing_library_is_a_loud_error(monkeypatch):
+    monkeypatch.setattr(_lib, "_lib", None)
+    monkeypatch.setattr(_lib, "LIB_PATH", "/nonexistent/libskv.so")
+    with pytest.raises(_lib.SkvError):
+        _lib.lib()
