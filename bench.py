@@ -183,34 +183,50 @@ def kernel_roofline(dec, n_now, peak_gbs, which):
     layers = dec.attn
     q = torch.randn(B * H, d, device=dev).to(torch.bfloat16)
     flush = torch.empty(512 * 1024 * 1024, dtype=torch.uint8, device=dev)
-    att_ms, step_ms = [], []
-    ev = lambda: torch.cuda.Event(enable_timing=True)
-    for rep in range(3):
-        for i, ix in enumerate(layers):
-            K, V = dec._heads(dec.cache.k[i]), dec._heads(dec.cache.v[i])
+    heads = [(dec._heads(dec.cache.k[i]), dec._heads(dec.cache.v[i])) for i in range(len(layers))]
+
+    def graph_of(fn):
+        """One launch of ``fn`` per layer, back to back in a CUDA graph (no host gaps between launches)."""
+        s = torch.cuda.Stream()
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            for ix, kv in zip(layers, heads):
+                fn(ix, kv)
+        torch.cuda.current_stream().wait_stream(s)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for ix, kv in zip(layers, heads):
+                fn(ix, kv)
+        return g
+
+    def timed(g, reps=7):
+        out = []
+        for _ in range(reps):
             flush.zero_()
-            a, b, c = ev(), ev(), ev()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             a.record()
-            ix._select(q, dec.n_dev)
+            g.replay()
             b.record()
-            ix._attend(q, K, V)
-            c.record()
             torch.cuda.synchronize()
-            if rep:
-                att_ms.append(b.elapsed_time(c))
-                step_ms.append(a.elapsed_time(c))
+            out.append(a.elapsed_time(b))
+        out.sort()
+        return out[len(out) // 2] * 1e-3 / len(layers)
+
+    sel_t = timed(graph_of(lambda ix, kv: ix._select(q, dec.n_dev)))
+    att_t = timed(graph_of(lambda ix, kv: ix._attend(q, kv[0], kv[1])))
+    stp_t = timed(graph_of(lambda ix, kv: (ix._select(q, dec.n_dev), ix._attend(q, kv[0], kv[1]))))
     rows = torch.stack([ix.cnt for ix in layers]).float()              # [layers, heads]
     n_c = torch.stack([ix.n_c for ix in layers]).float()
     att_bytes = float((rows * (2 * 256 + 4)).sum(1).mean())
     stp_bytes = float(step_bytes(n=n_now, rows=rows, clusters=n_c, d=d, summary_bits=8).sum(1).mean())
-    att_t = sum(att_ms) / len(att_ms) * 1e-3
-    stp_t = sum(step_ms) / len(step_ms) * 1e-3
     roof = {"bound": "hbm", "kernel": "attend_mma_kernel", "achieved": att_bytes / att_t / 1e9, "peak": peak_gbs,
             "unit": "GB/s", "frac": att_bytes / att_t / 1e9 / peak_gbs, "traffic": None, "peak_source": which,
             "us_per_launch": att_t * 1e6, "bytes_per_launch": att_bytes}
     layer = {"kernels": "select + attend (insert runs once for all layers)", "us_per_layer": stp_t * 1e6,
              "bytes_per_layer": stp_bytes, "achieved": stp_bytes / stp_t / 1e9, "unit": "GB/s",
-             "frac": stp_bytes / stp_t / 1e9 / peak_gbs, "rows_per_head": float(rows.mean()),
+             "frac": stp_bytes / stp_t / 1e9 / peak_gbs, "select_us": sel_t * 1e6, "attend_us": att_t * 1e6,
+             "rows_per_head": float(rows.mean()),
              "clusters_per_head": float(n_c.mean())}
     del flush
     return roof, layer
@@ -250,12 +266,16 @@ def gpu_arm(args, wl) -> None:
     barrier()
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with ClockSampler(local) as clocks:
+        if args.ncu_range:
+            torch.cuda.profiler.start()
         start.record()
         for _ in range(K_steps):
             dec.step(ids_dev[:, pos:pos + 1], pos)
             pos += 1
         stop.record()
         barrier()
+        if args.ncu_range:
+            torch.cuda.profiler.stop()
     dev_ms = start.elapsed_time(stop)
     # ---- end-to-end leg: ids from pinned host memory, next-token ids read back every step ----------
     for _ in range(W):
@@ -321,6 +341,8 @@ def main() -> None:
     ap.add_argument("--workload", default=DEFAULT, choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--ncu-range", action="store_true",
+                    help="bracket the timed device leg with cudaProfilerStart/Stop (for ncu --profile-from-start off)")
     args = ap.parse_args()
     wl = WORKLOADS[args.workload]
     if args.impl == "reference":

@@ -64,7 +64,8 @@ def test_scores_and_full_selection_match_the_oracle(bits, G):
         live = (st.count > 0).unsqueeze(1).expand_as(e)
         got = e_out.cpu()
         assert torch.isinf(got[~live]).all() and (got[~live] < 0).all()
-        torch.testing.assert_close(got[live], e[live], rtol=1e-5, atol=1e-5)
+        scale = float(e[live].abs().max())                 # 1e-5 of the score scale: values near 0 are differences
+        torch.testing.assert_close(got[live], e[live], rtol=1e-5, atol=1e-5 * max(1.0, scale))
         torch.testing.assert_close(s_out.cpu()[st.count > 0], st.shared_score(e)[st.count > 0], rtol=1e-5, atol=1e-7)
         diff = max(diff, int((w.cpu() != w_ref).sum(1).max()))
     assert diff <= 1                     # rounding of the scores may move the single boundary cluster
@@ -195,7 +196,7 @@ def test_each_split_follows_the_two_way_rule_on_the_same_members():
 @pytest.mark.parametrize("case", ["fixed", "cap_keys", "split_factor"])
 def test_fit_matches_the_oracle(case, dtype):
     kw = {"fixed": dict(C=64), "cap_keys": dict(C=256, C_init=32, cap_keys=24.0),
-          "split_factor": dict(C=128, C_init=32, split_factor=2.0)}[case]
+          "split_factor": dict(C=256, C_init=32, split_factor=1.2)}[case]
     h, n = 4, 2100
     K, V = oc.clustered_keys(h, n, 128, seed=31)
     K = K.to(dtype)
