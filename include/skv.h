@@ -108,6 +108,29 @@ int skv_attend(const void *q, const void *K, const void *V, const int32_t *idx, 
                int64_t k_head_stride, int64_t k_row_stride, int64_t v_head_stride, int64_t v_row_stride,
                int64_t idx_stride, int rows_limit, int splits, float scale, void *stream);
 
+/* Fixed capacity, in bytes, of the scratch array behind skv_attend_static. */
+#define SKV_STATIC_SCRATCH_BYTES (8 * 1024 * 1024)
+
+/* skv_attend for callers that cannot allocate device memory.  No counterpart in the reference (its
+ * Python side always allocates through the framework); it exists for hosts that hand the library
+ * only the buffers they were given: a serving process that reserved all of HBM for its KV-cache
+ * pool at start-up and has no headroom left for a workspace, a latency-critical decode loop that
+ * must not pay the device-wide stall of a cudaMalloc, or a foreign-function caller (cgo, JNI) with
+ * no CUDA allocator of its own.
+ * Same arguments and result as skv_attend, minus the workspace: the split partials and ticket words
+ * live in a SKV_STATIC_SCRATCH_BYTES array inside the library (held by every GPU that loads the
+ * library, until exit).  Returns SKV_E_TOO_LARGE when skv_attend_workspace_bytes(heads, G, d, splits)
+ * exceeds that; lower `splits` or use skv_attend.  The call itself allocates nothing.
+ * The first call on each device looks the array's device address up (cudaGetSymbolAddress, with that
+ * device current); make that first call before any stream capture.
+ * All calls share the one array: two calls whose kernels overlap on the GPU (different streams, or
+ * several host threads) race on it and give wrong results - serialise them. */
+int skv_attend_static(const void *q, const void *K, const void *V, const int32_t *idx, const int32_t *cnt,
+                      const int32_t *n_dev, void *out, int32_t *status,
+                      int heads, int G, int d, int dtype,
+                      int64_t k_head_stride, int64_t k_row_stride, int64_t v_head_stride, int64_t v_row_stride,
+                      int64_t idx_stride, int rows_limit, int splits, float scale, void *stream);
+
 /* Log-sum-exp merge of caller-provided partials (natural-log maxima), float32 output.
  * Replaces merge_splits (ssa/kernels/labeled_attn.py:143-151).
  *   m, l [heads, S, G], a [heads, S, G, d] -> out [heads*G, d] */

@@ -528,3 +528,46 @@ extern "C" int skv_merge(const float *m, const float *l, const float *a, float *
     SKV_CUDA_OK(cudaGetLastError());
     return SKV_OK;
 }
+
+// ---------------------------------------------------------------------------------------------
+// Attention with library-owned scratch: for callers that cannot allocate device memory
+// ---------------------------------------------------------------------------------------------
+// The split partials and ticket words of this variant live in a fixed array that is part of the
+// library image, so every GPU that loads the library carries these 8 MiB until the process exits.
+static __device__ __align__(256) unsigned char g_attend_scratch[SKV_STATIC_SCRATCH_BYTES];
+
+// Device address of g_attend_scratch on the current device.  In host code the array's name is only a
+// stand-in for the symbol, not something a kernel can dereference; the address has to be asked for,
+// once per device, with that device current.
+static int static_scratch(void **out) {
+    static void *cached[64] = {};
+    int dev = 0;
+    SKV_CUDA_OK(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return SKV_E_RANGE;
+    if (!cached[dev]) {
+        void *p = nullptr;
+        SKV_CUDA_OK(cudaGetSymbolAddress(&p, g_attend_scratch));
+        cached[dev] = p;
+    }
+    *out = cached[dev];
+    return SKV_OK;
+}
+
+extern "C" int skv_attend_static(const void *q, const void *K, const void *V, const int32_t *idx, const int32_t *cnt,
+                                 const int32_t *n_dev, void *out, int32_t *status, int heads, int G, int d, int dtype,
+                                 int64_t k_head_stride, int64_t k_row_stride, int64_t v_head_stride,
+                                 int64_t v_row_stride, int64_t idx_stride, int rows_limit, int splits, float scale,
+                                 void *stream) {
+    const int64_t need = skv_attend_workspace_bytes(heads, G, d, splits);
+    if (need < 0) return (int)need;
+    if (need > (int64_t)SKV_STATIC_SCRATCH_BYTES) return SKV_E_TOO_LARGE;
+    void *scratch = nullptr;
+    int rc = static_scratch(&scratch);
+    if (rc) return rc;
+    // Earlier calls with other shapes left their partials here.  Only the ticket words have to start at
+    // zero (partials are always written before they are read); they sit at the end of the layout.
+    unsigned char *tickets = static_cast<unsigned char *>(scratch) + (int64_t)heads * splits * G * (d + 2) * 4;
+    SKV_CUDA_OK(cudaMemsetAsync(tickets, 0, (size_t)heads * 4, static_cast<cudaStream_t>(stream)));
+    return skv_attend(q, K, V, idx, cnt, n_dev, out, scratch, status, heads, G, d, dtype, k_head_stride, k_row_stride,
+                      v_head_stride, v_row_stride, idx_stride, rows_limit, splits, scale, stream);
+}
