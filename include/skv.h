@@ -138,24 +138,40 @@ int skv_merge(const float *m, const float *l, const float *a, float *out, int he
               void *stream);
 
 /* Score clusters from their summaries once per KV head for its G query heads, form the shared score
- * (sum over the group of each head's softmax over clusters), take clusters in decreasing shared
- * score (equal scores: lower slot first) until their key counts reach state.need, and list the
- * positions to read in ascending order (position 0 and the recent window carry label C and are
- * always listed).
+ * (sum over the group of each head's softmax over clusters) and take clusters in decreasing shared
+ * score (equal scores: lower slot first) until their key counts reach state.need.  Several CTAs score
+ * a head's clusters in parallel; the last one to finish picks.  Outputs the 0/1 weights, the same
+ * selection as a bit set (bit C = always-read rows: position 0 and the recent window carry label C),
+ * and - only when `idx` is given - the list of positions to read in ascending order.
  * Replaces _score_kernel, _shared_pick/_pick_dev_kernel (ssa/kernels/sphere_fused.py:230-289,
  * ssa/kernels/graph_kernels.py:133-141) and _compact_dev_kernel (graph_kernels.py:144-155);
  * selection rule of SphereIndexGPU._rank_mask (ssa/attn/sphere_gpu.py:402-410).
  *   q          [heads*G, d] dtype
  *   n_dev      [1] cached positions (all heads)
  *   w          [heads, C+1] float32 0/1 weights out (column C = 1)
- *   idx, cnt   row list out: idx [heads, idx_stride] int32, cnt [heads]
+ *   selbits    [heads, C/32+1] uint32 out, or null (kept in the workspace then)
+ *   idx, cnt   idx [heads, idx_stride] int32 or null; cnt [heads]: rows listed, or 0 when idx is null
+ *              (skv_attend_labels then adds the rows it reads)
  *   shared_in  optional [heads, C] float32: use these shared scores instead of scoring (tests)
  *   shared_out optional [heads, C] float32: the shared scores used
  *   e_out      optional [heads, G, C] float32: per-query-head cluster scores (before the 1/sqrt(d) scale)
+ *   workspace  skv_select_workspace_bytes(heads, G, C) bytes, zero-initialised once by the caller
  */
+int64_t skv_select_workspace_bytes(int heads, int G, int C);
 int skv_select(const skv_state *st, const void *q, int dtype, int G, const int32_t *n_dev,
-               float *w, int32_t *idx, int64_t idx_stride, int32_t *cnt,
-               const float *shared_in, float *shared_out, float *e_out, float scale, void *stream);
+               float *w, uint32_t *selbits, int32_t *idx, int64_t idx_stride, int32_t *cnt,
+               const float *shared_in, float *shared_out, float *e_out, void *workspace, float scale, void *stream);
+
+/* skv_attend without a row list: every CTA owns a range of positions, reads their int16 labels, keeps
+ * the positions whose label's bit is set in `selbits` (from skv_select) and attends over them; `cnt`
+ * (zeroed by skv_select) receives the rows read per head.  bf16 caches only.  Replaces
+ * _compact_dev_kernel + _list_kernel + _merge_kernel (ssa/kernels/graph_kernels.py:144-155,
+ * ssa/kernels/labeled_attn.py:202-245, :123-140) in one launch.  label_stride a multiple of 16. */
+int skv_attend_labels(const void *q, const void *K, const void *V, const int16_t *labels, int64_t label_stride,
+                      const uint32_t *selbits, int C, const int32_t *n_dev, void *out, void *workspace,
+                      int32_t *cnt, int32_t *status, int heads, int G, int d, int dtype,
+                      int64_t k_head_stride, int64_t k_row_stride, int64_t v_head_stride, int64_t v_row_stride,
+                      int splits, float scale, void *stream);
 
 /* Insert the keys that left the recent window since the last call (positions [end, max(1, n-window)))
  * into their nearest clusters, one CTA per entry of `st` (all layers of a model in one launch),

@@ -159,7 +159,9 @@ class SphereIndexGraph:
         self.cnt = torch.zeros(h, dtype=torch.int32, device=device)
         self.wbuf = torch.zeros(h, self.C + 1, dtype=torch.float32, device=device)
         self.wbuf[:, self.C] = 1.0
+        self.selbits = torch.zeros(h, self.C // 32 + 1, dtype=torch.int32, device=device)
         self._attn_ws = None
+        self._sel_ws = None
         self._max_members = None
 
     def _members_limit(self) -> int:
@@ -302,15 +304,23 @@ class SphereIndexGraph:
         self.rebuilds += int(hl.numel())
 
     # ---- selection -------------------------------------------------------------------------------
-    def _select(self, q: torch.Tensor, n_dev: torch.Tensor, *, shared_in=None, shared_out=None, e_out=None) -> None:
+    def _select(self, q: torch.Tensor, n_dev: torch.Tensor, *, shared_in=None, shared_out=None, e_out=None,
+                listed: bool = True) -> None:
+        """Score and pick; with ``listed`` also build the ascending row list ``idx``/``cnt`` (otherwise
+        ``cnt`` is zeroed and the label-driven attention kernel fills it)."""
         H, d = q.shape
         G = H // self.H_kv
+        L = lib()
         if not q.is_contiguous():
             q = q.contiguous()
-        check(lib().skv_select(ctypes.byref(self._st), q.data_ptr(), dtype_code(q.dtype), G, n_dev.data_ptr(),
-                               self.wbuf.data_ptr(), self.idx.data_ptr(), self.idx.stride(0), self.cnt.data_ptr(),
-                               ptr(shared_in), ptr(shared_out), ptr(e_out), 1.0 / math.sqrt(d),
-                               stream_ptr(q.device)), "skv_select")
+        if self._sel_ws is None or self._sel_G != G:
+            self._sel_G = G
+            self._sel_ws = torch.zeros(L.skv_select_workspace_bytes(self.H_kv, G, self.C), dtype=torch.uint8,
+                                       device=q.device)
+        check(L.skv_select(ctypes.byref(self._st), q.data_ptr(), dtype_code(q.dtype), G, n_dev.data_ptr(),
+                           self.wbuf.data_ptr(), self.selbits.data_ptr(), self.idx.data_ptr() if listed else None,
+                           self.idx.stride(0), self.cnt.data_ptr(), ptr(shared_in), ptr(shared_out), ptr(e_out),
+                           self._sel_ws.data_ptr(), 1.0 / math.sqrt(d), stream_ptr(q.device)), "skv_select")
 
     def labels_and_weights(self, q: torch.Tensor, *, n: int, budget: float, group: str = "sum_share",
                            shared_in=None, shared_out=None, e_out=None):
@@ -325,26 +335,51 @@ class SphereIndexGraph:
         return self.labels[:, :n], self.wbuf
 
     # ---- attention -------------------------------------------------------------------------------
-    def _attend(self, q: torch.Tensor, K: torch.Tensor, V: torch.Tensor, *, dense_n=None, force_simple=False):
+    def _attend_buffers(self, q: torch.Tensor) -> int:
         H, d = q.shape
         G = H // self.H_kv
-        L = lib()
-        if not q.is_contiguous():
-            q = q.contiguous()
         if self._attn_ws is None or self.G != G:
+            L = lib()
             self.G = G
             self.num_splits = L.skv_attend_splits(self.H_kv)
             nbytes = L.skv_attend_workspace_bytes(self.H_kv, G, d, self.num_splits)
             self._attn_ws = torch.zeros(nbytes, dtype=torch.uint8, device=q.device)
             self.out = torch.empty(H, d, dtype=q.dtype, device=q.device)
+        return G
+
+    def _attend(self, q: torch.Tensor, K: torch.Tensor, V: torch.Tensor, *, dense_n=None, force_simple=False):
+        """Attention over the listed rows ``idx[:cnt]`` (or over ``[0, dense_n)``)."""
+        H, d = q.shape
+        if not q.is_contiguous():
+            q = q.contiguous()
+        G = self._attend_buffers(q)
         code = dtype_code(K.dtype) | (256 if force_simple else 0)
-        check(L.skv_attend(q.data_ptr(), K.data_ptr(), V.data_ptr(),
-                           None if dense_n is not None else self.idx.data_ptr(),
-                           None if dense_n is not None else self.cnt.data_ptr(), ptr(dense_n), self.out.data_ptr(),
-                           self._attn_ws.data_ptr(), self.status.data_ptr(), self.H_kv, G, d, code, K.stride(0),
-                           K.stride(1), V.stride(0), V.stride(1), self.idx.stride(0), K.shape[1], self.num_splits,
-                           1.0 / math.sqrt(d), stream_ptr(q.device)), "skv_attend")
+        check(lib().skv_attend(q.data_ptr(), K.data_ptr(), V.data_ptr(),
+                               None if dense_n is not None else self.idx.data_ptr(),
+                               None if dense_n is not None else self.cnt.data_ptr(), ptr(dense_n),
+                               self.out.data_ptr(), self._attn_ws.data_ptr(), self.status.data_ptr(), self.H_kv, G, d,
+                               code, K.stride(0), K.stride(1), V.stride(0), V.stride(1), self.idx.stride(0),
+                               K.shape[1], self.num_splits, 1.0 / math.sqrt(d), stream_ptr(q.device)), "skv_attend")
         return self.out
+
+    def _attend_labels(self, q: torch.Tensor, K: torch.Tensor, V: torch.Tensor, n_dev: torch.Tensor):
+        """Attention over the rows whose label is selected in ``selbits``, read straight from the labels
+        (no row list); adds the rows read to ``cnt``."""
+        H, d = q.shape
+        if not q.is_contiguous():
+            q = q.contiguous()
+        G = self._attend_buffers(q)
+        check(lib().skv_attend_labels(q.data_ptr(), K.data_ptr(), V.data_ptr(), self.labels.data_ptr(),
+                                      self.labels.stride(0), self.selbits.data_ptr(), self.C, n_dev.data_ptr(),
+                                      self.out.data_ptr(), self._attn_ws.data_ptr(), self.cnt.data_ptr(),
+                                      self.status.data_ptr(), self.H_kv, G, d, dtype_code(K.dtype), K.stride(0),
+                                      K.stride(1), V.stride(0), V.stride(1), self.num_splits, 1.0 / math.sqrt(d),
+                                      stream_ptr(q.device)), "skv_attend_labels")
+        return self.out
+
+    def _fused_rows(self, K: torch.Tensor) -> bool:
+        """Whether the list-free attention applies: bf16 cache and labels laid out in 32-byte groups."""
+        return K.dtype == torch.bfloat16 and self.capacity % 16 == 0
 
     def attend(self, q: torch.Tensor, K: torch.Tensor, V: torch.Tensor, *, n: int, budget: float,
                group: str = "sum_share"):
@@ -368,7 +403,10 @@ class SphereIndexGraph:
         self._n_scalar.fill_(n)
         self.need_dev.fill_(math.ceil(self.budget * (self.end - 1)))
         self._select(q0, self._n_scalar)
-        self._attend(q0, K, K)                               # sizes the workspace and the output
+        self._attend(q0, K, K)                               # sizes the workspaces and the output
+        if self._fused_rows(K):
+            self._select(q0, self._n_scalar, listed=False)
+            self._attend_labels(q0, K, K, self._n_scalar)
         self._members_limit()
         self._ktable(K)
         assert self.G == G
@@ -379,6 +417,9 @@ class SphereIndexGraph:
         (ssa/kernels/graph_kernels.py:220-244)."""
         if insert:
             self._launch_insert(K, n_dev, self.budget)
+        if self._fused_rows(K):
+            self._select(q, n_dev, listed=False)
+            return self._attend_labels(q, K, V, n_dev)
         self._select(q, n_dev)
         return self._attend(q, K, V)
 

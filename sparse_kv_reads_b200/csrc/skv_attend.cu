@@ -9,6 +9,7 @@
 // heads of the group on the M side, fp32 accumulation and a per-warp online softmax in base 2.
 // The work is HBM-bound (G flop per byte); the tensor-core tiles only keep the issue slots free
 // for the gathers.  float32 caches take a plain CUDA-core path with float32 arithmetic throughout.
+#include "skv_attend_core.cuh"
 #include "skv_common.cuh"
 
 namespace skv {
@@ -25,37 +26,13 @@ struct AttendParams {
     int64_t ksh, ksr, vsh, vsr, idx_stride;
     int rows_limit, splits;
     float scale_log2;  // softmax scale * log2(e)
+    // rows taken straight from the labels (no list): position p < n is read iff its label's bit is set
+    const int16_t *labels;     // [heads, lab_stride]
+    const uint32_t *selbits;   // [heads, sel_words], bit C = always-read rows
+    int32_t *cnt_out;          // [heads] rows read, accumulated (zeroed by the selection kernel)
+    int64_t lab_stride;
+    int sel_words, C;
 };
-
-constexpr int TILE_ROWS = 16;
-
-__device__ __forceinline__ float fast_exp2(float x) {
-    float y;
-    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-    return y;
-}
-
-__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
-    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-    return *reinterpret_cast<uint32_t *>(&v);
-}
-
-__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
-        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
-__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void *smem) {
-    unsigned s = static_cast<unsigned>(__cvta_generic_to_shared(smem));
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
-}
-__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void *smem) {
-    unsigned s = static_cast<unsigned>(__cvta_generic_to_shared(smem));
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
-}
 
 // Which tiles a warp owns: contiguous runs, identical arithmetic in every CTA of the head.
 struct Share {
@@ -128,26 +105,47 @@ __device__ __forceinline__ void finish_head(const AttendParams &p, const float *
     __syncthreads();
     if (!*sh_flag) return;
     __threadfence();
+    // Merge of the head's partials by this (last) CTA.  Loads are spread over the four warps (warp w takes
+    // splits w, w+4, ...; a lane owns four output columns) and issued eight at a time, so the pass costs a
+    // few L2 round trips instead of one per split.
+    __shared__ float s_max[4][16];
+    __shared__ __align__(16) float s_sum[4][132];
+    const int lane = tid & 31, wid = tid >> 5;
     const float *qa = p.part_acc + (int64_t)head * p.splits * G * HEAD_DIM;
     const float *qm = p.part_ml + (int64_t)head * p.splits * G * 2;
+    for (int g = 0; g < G; ++g) {
+        float mx = NEG_BIG;
+        for (int s = tid; s < s_eff; s += 128) mx = fmaxf(mx, __ldcg(qm + (s * G + g) * 2));
+        mx = warp_max(mx);
+        if (lane == 0) s_max[wid][g] = mx;
+    }
+    __syncthreads();
 #pragma unroll 1
     for (int g = 0; g < G; ++g) {
-        float M = NEG_BIG;
-        for (int s = 0; s < s_eff; ++s) M = fmaxf(M, __ldcg(qm + (s * G + g) * 2));
-        float dn = 0.f, nm = 0.f;
-#pragma unroll 4
-        for (int s = 0; s < s_eff; ++s) {
-            float f = fast_exp2(__ldcg(qm + (s * G + g) * 2) - M);
-            dn += f * __ldcg(qm + (s * G + g) * 2 + 1);
-            nm += f * __ldcg(qa + (s * G + g) * HEAD_DIM + tid);
+        const float M = fmaxf(fmaxf(s_max[0][g], s_max[1][g]), fmaxf(s_max[2][g], s_max[3][g]));
+        float4 nm = make_float4(0.f, 0.f, 0.f, 0.f);
+        float dn = 0.f;
+#pragma unroll 8
+        for (int s = wid; s < s_eff; s += 4) {
+            const float2 ml = __ldcg(reinterpret_cast<const float2 *>(qm + (s * G + g) * 2));
+            const float4 a = __ldcg(reinterpret_cast<const float4 *>(qa + (s * G + g) * HEAD_DIM + lane * 4));
+            const float f = fast_exp2(ml.x - M);
+            dn += f * ml.y;
+            nm.x += f * a.x; nm.y += f * a.y; nm.z += f * a.z; nm.w += f * a.w;
         }
-        store_out(out + ((int64_t)head * G + g) * HEAD_DIM + tid, dn > 0.f ? nm / dn : 0.f);
+        *reinterpret_cast<float4 *>(&s_sum[wid][lane * 4]) = nm;
+        if (lane == 0) s_sum[wid][128] = dn;
+        __syncthreads();
+        const float num = s_sum[0][tid] + s_sum[1][tid] + s_sum[2][tid] + s_sum[3][tid];
+        const float den = s_sum[0][128] + s_sum[1][128] + s_sum[2][128] + s_sum[3][128];
+        store_out(out + ((int64_t)head * G + g) * HEAD_DIM + tid, den > 0.f ? num / den : 0.f);
+        __syncthreads();
     }
     if (tid == 0) p.ticket[head] = 0;     // ready for the next call on this stream
 }
 
 // ---------------------------------------------------------------------------------------------
-// bf16 tensor-core path
+// bf16 tensor-core path over a list of rows
 // ---------------------------------------------------------------------------------------------
 template <int WARPS, int STAGES, bool HI>
 __global__ void __launch_bounds__(WARPS * 32) attend_mma_kernel(const AttendParams p) {
@@ -155,199 +153,95 @@ __global__ void __launch_bounds__(WARPS * 32) attend_mma_kernel(const AttendPara
     extern __shared__ __align__(128) unsigned char smem[];
     __shared__ uint32_t s_vmask[WARPS][STAGES];
     __shared__ int s_flag;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
     const int head = blockIdx.y, split = blockIdx.x;
     const int G = p.G;
     const Share sh = my_share(p, head, split, warp, WARPS);
     if (split >= sh.s_eff) return;
-
-    unsigned char *ring = smem + warp * (STAGES * 8192);
-    const __nv_bfloat16 *q = static_cast<const __nv_bfloat16 *>(p.q) + (int64_t)head * G * HEAD_DIM;
-    const char *Kb = static_cast<const char *>(p.K) + (int64_t)head * p.ksh * 2;
-    const char *Vb = static_cast<const char *>(p.V) + (int64_t)head * p.vsh * 2;
-    const int64_t krow = p.ksr * 2, vrow = p.vsr * 2;
-
-    // query fragments (A operand), rows = query heads of the group, zero beyond G
-    uint32_t qa[8][4];
-    {
-        const int r0 = lane >> 2, r1 = r0 + 8, c = 2 * (lane & 3);
-#pragma unroll
-        for (int ks = 0; ks < 8; ++ks) {
-            const int col = 16 * ks + c;
-            qa[ks][0] = r0 < G ? *reinterpret_cast<const uint32_t *>(q + r0 * HEAD_DIM + col) : 0u;
-            qa[ks][2] = r0 < G ? *reinterpret_cast<const uint32_t *>(q + r0 * HEAD_DIM + col + 8) : 0u;
-            qa[ks][1] = (HI && r1 < G) ? *reinterpret_cast<const uint32_t *>(q + r1 * HEAD_DIM + col) : 0u;
-            qa[ks][3] = (HI && r1 < G) ? *reinterpret_cast<const uint32_t *>(q + r1 * HEAD_DIM + col + 8) : 0u;
-        }
-    }
-
-    float acc[16][4];
-#pragma unroll
-    for (int j = 0; j < 16; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
-    float m0 = NEG_BIG, m1 = NEG_BIG, l0 = 0.f, l1 = 0.f;
-
-    const int sub = lane & 15, half = lane >> 4;
-    auto issue = [&](int tile, int stage, int mypos) {
-        unsigned char *kb = ring + stage * 8192, *vb = kb + 4096;
-        const uint32_t vm = __ballot_sync(0xffffffffu, mypos >= 0) & 0xffffu;
-        if (lane == 0) s_vmask[warp][stage] = vm;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            const int r = half + 2 * i;
-            const int pos = __shfl_sync(0xffffffffu, mypos, r);
-            const int off = r * 256 + ((sub ^ (r & 7)) << 4);
-            const bool ok = pos >= 0;
-            cp_async16(kb + off, ok ? Kb + (int64_t)pos * krow + sub * 16 : Kb, ok ? 16 : 0);
-            cp_async16(vb + off, ok ? Vb + (int64_t)pos * vrow + sub * 16 : Vb, ok ? 16 : 0);
-        }
-    };
-
-    int it = sh.t0;
-    int pos_next = (it < sh.t1) ? fetch_pos(p, head, it * TILE_ROWS + sub, sh.count) : -1;
-#pragma unroll
-    for (int s = 0; s < STAGES - 1; ++s) {
-        if (it < sh.t1) {
-            const int mypos = pos_next;
-            ++it;
-            pos_next = (it < sh.t1) ? fetch_pos(p, head, it * TILE_ROWS + sub, sh.count) : -1;
-            issue(it - 1, s, mypos);
-        }
-        cp_async_commit();
-    }
-
-    for (int t = sh.t0; t < sh.t1; ++t) {
-        const int stage = (t - sh.t0) % STAGES;
-        if (it < sh.t1) {
-            const int mypos = pos_next;
-            ++it;
-            pos_next = (it < sh.t1) ? fetch_pos(p, head, it * TILE_ROWS + sub, sh.count) : -1;
-            issue(it - 1, (t - sh.t0 + STAGES - 1) % STAGES, mypos);
-        }
-        cp_async_commit();
-        cp_async_wait<STAGES - 1>();
-        __syncwarp();
-
-        const unsigned char *kb = ring + stage * 8192, *vb = kb + 4096;
-        const uint32_t vmask = s_vmask[warp][stage];
-        float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-        {
-            const int row = (lane & 7) + ((lane >> 4) << 3);
-            const int csel = (lane >> 3) & 1;
-#pragma unroll
-            for (int ks = 0; ks < 8; ++ks) {
-                uint32_t b[4];
-                ldmatrix_x4(b, kb + row * 256 + (((2 * ks + csel) ^ (row & 7)) << 4));
-                mma_bf16_16816(s[0], qa[ks], b[0], b[1]);
-                mma_bf16_16816(s[1], qa[ks], b[2], b[3]);
-            }
-        }
-        // online softmax in base 2; columns of s are the tile's rows (keys)
-        const int kc = 2 * (lane & 3);
-        bool ok[2][2];
-#pragma unroll
-        for (int nt = 0; nt < 2; ++nt)
-#pragma unroll
-            for (int i = 0; i < 2; ++i) ok[nt][i] = (vmask >> (nt * 8 + kc + i)) & 1u;
-        float z0[2][2], z1[2][2];
-        float mt0 = NEG_BIG, mt1 = NEG_BIG;
-#pragma unroll
-        for (int nt = 0; nt < 2; ++nt)
-#pragma unroll
-            for (int i = 0; i < 2; ++i) {
-                z0[nt][i] = ok[nt][i] ? s[nt][i] * p.scale_log2 : NEG_BIG;
-                mt0 = fmaxf(mt0, z0[nt][i]);
-                if (HI) {
-                    z1[nt][i] = ok[nt][i] ? s[nt][2 + i] * p.scale_log2 : NEG_BIG;
-                    mt1 = fmaxf(mt1, z1[nt][i]);
-                }
-            }
-        mt0 = fmaxf(mt0, __shfl_xor_sync(0xffffffffu, mt0, 1));
-        mt0 = fmaxf(mt0, __shfl_xor_sync(0xffffffffu, mt0, 2));
-        const float mn0 = fmaxf(m0, mt0);
-        const float al0 = fast_exp2(m0 - mn0);
-        m0 = mn0;
-        float al1 = 1.f;
-        if (HI) {
-            mt1 = fmaxf(mt1, __shfl_xor_sync(0xffffffffu, mt1, 1));
-            mt1 = fmaxf(mt1, __shfl_xor_sync(0xffffffffu, mt1, 2));
-            const float mn1 = fmaxf(m1, mt1);
-            al1 = fast_exp2(m1 - mn1);
-            m1 = mn1;
-        }
-        float p0[2][2], p1[2][2];
-        float rs0 = 0.f, rs1 = 0.f;
-#pragma unroll
-        for (int nt = 0; nt < 2; ++nt)
-#pragma unroll
-            for (int i = 0; i < 2; ++i) {
-                p0[nt][i] = ok[nt][i] ? fast_exp2(z0[nt][i] - m0) : 0.f;
-                rs0 += p0[nt][i];
-                if (HI) {
-                    p1[nt][i] = ok[nt][i] ? fast_exp2(z1[nt][i] - m1) : 0.f;
-                    rs1 += p1[nt][i];
-                }
-            }
-        l0 = l0 * al0 + rs0;
-        if (HI) l1 = l1 * al1 + rs1;
-        uint32_t pa[4];
-        pa[0] = pack_bf16(p0[0][0], p0[0][1]);
-        pa[2] = pack_bf16(p0[1][0], p0[1][1]);
-        pa[1] = HI ? pack_bf16(p1[0][0], p1[0][1]) : 0u;
-        pa[3] = HI ? pack_bf16(p1[1][0], p1[1][1]) : 0u;
-#pragma unroll
-        for (int j = 0; j < 16; ++j) {
-            acc[j][0] *= al0;
-            acc[j][1] *= al0;
-            if (HI) {
-                acc[j][2] *= al1;
-                acc[j][3] *= al1;
-            }
-        }
-        {
-            const int row = (lane & 7) + (((lane >> 3) & 1) << 3);
-            const int csel = lane >> 4;
-#pragma unroll
-            for (int jj = 0; jj < 8; ++jj) {
-                uint32_t b[4];
-                ldmatrix_x4_trans(b, vb + row * 256 + (((2 * jj + csel) ^ (row & 7)) << 4));
-                mma_bf16_16816(acc[2 * jj], pa, b[0], b[1]);
-                mma_bf16_16816(acc[2 * jj + 1], pa, b[2], b[3]);
-            }
-        }
-        __syncwarp();
-    }
-    cp_async_wait<0>();
-    l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
-    l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
-    if (HI) {
-        l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
-        l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
-    }
+    WarpAttend<STAGES, HI> wa;
+    wa.init(static_cast<const __nv_bfloat16 *>(p.q) + (int64_t)head * G * HEAD_DIM, G, smem + warp * (STAGES * 8192),
+            s_vmask[warp], static_cast<const char *>(p.K) + (int64_t)head * p.ksh * 2,
+            static_cast<const char *>(p.V) + (int64_t)head * p.vsh * 2, p.ksr * 2, p.vsr * 2, p.scale_log2);
+    wa.run(sh.t0, sh.t1, [&](int row) { return fetch_pos(p, head, row, sh.count); });
     __syncthreads();                       // every warp is done with its ring: reuse it
     float *red = reinterpret_cast<float *>(smem);
-    {
-        const int r0 = lane >> 2, r1 = r0 + 8, c = 2 * (lane & 3);
-        if (r0 < G) {
-            float *r = red + (warp * G + r0) * 132;
-#pragma unroll
-            for (int j = 0; j < 16; ++j) {
-                r[8 * j + c] = acc[j][0];
-                r[8 * j + c + 1] = acc[j][1];
-            }
-            if ((lane & 3) == 0) { r[128] = m0; r[129] = l0; }
-        }
-        if (HI && r1 < G) {
-            float *r = red + (warp * G + r1) * 132;
-#pragma unroll
-            for (int j = 0; j < 16; ++j) {
-                r[8 * j + c] = acc[j][2];
-                r[8 * j + c + 1] = acc[j][3];
-            }
-            if ((lane & 3) == 0) { r[128] = m1; r[129] = l1; }
-        }
-    }
+    wa.store_partial(red, warp, G);
     __syncthreads();
     finish_head<__nv_bfloat16>(p, red, WARPS, head, split, sh.s_eff, &s_flag);
+}
+
+// ---------------------------------------------------------------------------------------------
+// bf16 tensor-core path straight from the labels: every CTA owns a contiguous range of positions,
+// lists the selected ones of 2,048 positions at a time in shared memory (ascending), and attends over
+// them.  No global row list is written or read; cnt_out receives the number of rows read.
+// ---------------------------------------------------------------------------------------------
+constexpr int LAB_SUB = 2048;              // positions listed per pass (16 per thread)
+
+template <int WARPS, int STAGES, bool HI>
+__global__ void __launch_bounds__(WARPS * 32) attend_labels_kernel(const AttendParams p) {
+    static_assert(WARPS == 4, "finish_head expects 128 threads");
+    extern __shared__ __align__(128) unsigned char smem[];
+    __shared__ uint32_t s_vmask[WARPS][STAGES];
+    __shared__ int s_flag;
+    __shared__ int s_scan[40];
+    __shared__ int s_rows[LAB_SUB];
+    const int warp = threadIdx.x >> 5, tid = threadIdx.x;
+    const int head = blockIdx.y, split = blockIdx.x;
+    const int G = p.G, C = p.C;
+    const int n = min(max(p.n_dev[0], 0), (int)p.lab_stride);
+    // position ranges: multiples of 16 so that a thread's 16 labels are two aligned 16-byte loads
+    const int chunk = max(16, (((n + p.splits - 1) / p.splits + 15) >> 4) << 4);
+    const int s_eff = max(1, (n + chunk - 1) / chunk);
+    if (split >= s_eff) return;
+    const int p0 = split * chunk, p1 = min(p0 + chunk, n);
+    uint32_t *s_bits = reinterpret_cast<uint32_t *>(smem + WARPS * STAGES * 8192);
+    for (int i = tid; i < p.sel_words; i += WARPS * 32) s_bits[i] = p.selbits[(int64_t)head * p.sel_words + i];
+    WarpAttend<STAGES, HI> wa;
+    wa.init(static_cast<const __nv_bfloat16 *>(p.q) + (int64_t)head * G * HEAD_DIM, G, smem + warp * (STAGES * 8192),
+            s_vmask[warp], static_cast<const char *>(p.K) + (int64_t)head * p.ksh * 2,
+            static_cast<const char *>(p.V) + (int64_t)head * p.vsh * 2, p.ksr * 2, p.vsr * 2, p.scale_log2);
+    const int16_t *lab = p.labels + (int64_t)head * p.lab_stride;
+    int read_rows = 0;
+    bool bad = false;
+    __syncthreads();
+    for (int sub0 = p0; sub0 < p1; sub0 += LAB_SUB) {
+        const int base = sub0 + tid * 16;
+        uint32_t take = 0;
+        if (base < p1) {
+            uint4 raw[2];
+            raw[0] = *reinterpret_cast<const uint4 *>(lab + base);
+            raw[1] = *reinterpret_cast<const uint4 *>(lab + base + 8);
+            const int16_t *l16 = reinterpret_cast<const int16_t *>(raw);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                const unsigned l = (unsigned)(int)l16[i];
+                if (base + i < p1) {
+                    if (l <= (unsigned)C) take |= ((s_bits[l >> 5] >> (l & 31)) & 1u) << i;
+                    else bad = true;
+                }
+            }
+        }
+        int total;
+        int off = block_excl_scan(__popc(take), s_scan, total);
+        while (take) {
+            const int i = __ffs(take) - 1;
+            take &= take - 1;
+            s_rows[off++] = base + i;
+        }
+        __syncthreads();
+        read_rows += total;
+        const int tiles = (total + TILE_ROWS - 1) / TILE_ROWS;
+        const int per = (tiles + WARPS - 1) / WARPS;
+        const int t0 = min(warp * per, tiles), t1 = min(t0 + per, tiles);
+        wa.run(t0, t1, [&](int row) { return row < total ? s_rows[row] : -1; });
+        __syncthreads();                   // the list is rewritten by the next pass
+    }
+    if (tid == 0 && p.cnt_out) atomicAdd(p.cnt_out + head, read_rows);
+    if (bad && p.status) atomicOr(p.status + head, SKV_ST_BAD_INDEX);
+    float *red = reinterpret_cast<float *>(smem);
+    wa.store_partial(red, warp, G);
+    __syncthreads();
+    finish_head<__nv_bfloat16>(p, red, WARPS, head, split, s_eff, &s_flag);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -455,6 +349,23 @@ static int launch_mma(const AttendParams &p, dim3 grid, cudaStream_t st) {
     return SKV_OK;
 }
 
+template <bool HI>
+static int launch_labels(const AttendParams &p, dim3 grid, cudaStream_t st) {
+    auto kern = attend_labels_kernel<MMA_WARPS, MMA_STAGES, HI>;
+    static size_t configured[64] = {};
+    const size_t smem = MMA_SMEM + (size_t)p.sel_words * 4;
+    int dev = 0;
+    SKV_CUDA_OK(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return SKV_E_RANGE;
+    if (configured[dev] < smem) {
+        SKV_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        configured[dev] = smem;
+    }
+    kern<<<grid, MMA_WARPS * 32, smem, st>>>(p);
+    SKV_CUDA_OK(cudaGetLastError());
+    return SKV_OK;
+}
+
 template <typename T>
 static int launch_simple(const AttendParams &p, dim3 grid, cudaStream_t st) {
     if (p.G <= 1) attend_simple_kernel<T, 1><<<grid, 128, 0, st>>>(p);
@@ -512,11 +423,44 @@ extern "C" int skv_attend(const void *q, const void *K, const void *V, const int
     p.ksh = k_head_stride; p.ksr = k_row_stride; p.vsh = v_head_stride; p.vsr = v_row_stride;
     p.idx_stride = idx_stride; p.rows_limit = rows_limit; p.splits = splits;
     p.scale_log2 = scale * LOG2E;
+    p.labels = nullptr; p.selbits = nullptr; p.cnt_out = nullptr; p.lab_stride = 0; p.sel_words = 0; p.C = 0;
     dim3 grid(splits, heads);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (base == SKV_F32) return launch_simple<float>(p, grid, st);
     if (force_simple) return launch_simple<__nv_bfloat16>(p, grid, st);
     return G > 8 ? launch_mma<true>(p, grid, st) : launch_mma<false>(p, grid, st);
+}
+
+extern "C" int skv_attend_labels(const void *q, const void *K, const void *V, const int16_t *labels,
+                                 int64_t label_stride, const uint32_t *selbits, int C, const int32_t *n_dev, void *out,
+                                 void *workspace, int32_t *cnt, int32_t *status, int heads, int G, int d, int dtype,
+                                 int64_t k_head_stride, int64_t k_row_stride, int64_t v_head_stride,
+                                 int64_t v_row_stride, int splits, float scale, void *stream) {
+    if (!q || !K || !V || !labels || !selbits || !n_dev || !out || !workspace) return SKV_E_NULL;
+    if (d != HEAD_DIM) return SKV_E_DIM;
+    if (dtype != SKV_BF16) return SKV_E_DTYPE;                   // float32 caches take the list path
+    if (G < 1 || G > 16 || C < 16 || (C & (C - 1)) || C > 16384) return SKV_E_DIM;
+    if (heads <= 0 || heads > 65535 || splits <= 0 || splits > 65535 || label_stride <= 0) return SKV_E_RANGE;
+    if (!aligned16(q) || !aligned16(K) || !aligned16(V) || !aligned16(out) || !aligned16(workspace) ||
+        !aligned16(labels) || label_stride % 16)
+        return SKV_E_ALIGN;
+    if ((k_row_stride * 2) % 16 || (v_row_stride * 2) % 16 || (k_head_stride * 2) % 16 || (v_head_stride * 2) % 16 ||
+        k_row_stride < d || v_row_stride < d)
+        return SKV_E_ALIGN;
+    AttendParams p;
+    p.q = q; p.K = K; p.V = V; p.idx = nullptr; p.cnt = nullptr; p.n_dev = n_dev; p.out = out; p.status = status;
+    p.part_acc = static_cast<float *>(workspace);
+    p.part_ml = p.part_acc + (int64_t)heads * splits * G * d;
+    p.ticket = reinterpret_cast<int32_t *>(p.part_ml + (int64_t)heads * splits * G * 2);
+    p.heads = heads; p.G = G;
+    p.ksh = k_head_stride; p.ksr = k_row_stride; p.vsh = v_head_stride; p.vsr = v_row_stride;
+    p.idx_stride = 0; p.rows_limit = 0; p.splits = splits;
+    p.scale_log2 = scale * LOG2E;
+    p.labels = labels; p.selbits = selbits; p.cnt_out = cnt; p.lab_stride = label_stride;
+    p.sel_words = C / 32 + 1; p.C = C;
+    dim3 grid(splits, heads);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    return G > 8 ? launch_labels<true>(p, grid, st) : launch_labels<false>(p, grid, st);
 }
 
 extern "C" int skv_merge(const float *m, const float *l, const float *a, float *out, int heads, int S, int G, int d,

@@ -10,8 +10,9 @@
 
 namespace skv {
 
-constexpr int SEL_THREADS = 512;
+constexpr int SEL_THREADS = 256;
 constexpr int SEL_WARPS = SEL_THREADS / 32;
+constexpr int SEL_MAX_CTAS = 16;          // CTAs that score one head's clusters in parallel
 
 struct SelectParams {
     skv_state st;
@@ -19,12 +20,15 @@ struct SelectParams {
     int G;
     const int32_t *n_dev;
     float *w;
-    int32_t *idx;
+    uint32_t *selbits;        // [heads, C/32 + 1]
+    int32_t *idx;             // null: no row list is built
     int64_t idx_stride;
     int32_t *cnt;
     const float *shared_in;
     float *shared_out;
     float *e_out;
+    float *zbuf;              // [heads, G, C] scaled scores handed from the scoring CTAs to the picking CTA
+    int32_t *ticket;          // [heads]
     float scale;
 };
 
@@ -44,16 +48,20 @@ __device__ __forceinline__ void block_reduce_vec(float *v, int nv, float *red /*
     __syncthreads();
 }
 
+// Grid (ctas, heads).  Every CTA scores a slice of the head's clusters and leaves the scaled scores in
+// zbuf; the last CTA of the head to finish (atomic ticket, no waiting) forms the shared score, finds
+// the threshold and writes the weights and the selection bits.
 template <typename TQ>
-__global__ void __launch_bounds__(SEL_THREADS) select_kernel(const SelectParams p) {
+__global__ void __launch_bounds__(SEL_THREADS) score_pick_kernel(const SelectParams p) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
+    __shared__ int s_last;
     const int C = p.st.C, G = p.G, d = HEAD_DIM;
-    const int h = blockIdx.x, tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
-    // shared-memory carve-up
-    float *z = reinterpret_cast<float *>(smem_raw);                 // [G][C] scaled scores (unused with shared_in)
+    const int h = blockIdx.y, b = blockIdx.x, nb = gridDim.x;
+    const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
+    float *z = reinterpret_cast<float *>(smem_raw);                 // [G][C] (picking CTA)
     const int zfloats = p.shared_in ? 0 : G * C;
     uint32_t *key = reinterpret_cast<uint32_t *>(z + zfloats);      // [C]
-    int *ci = reinterpret_cast<int *>(key + C);                     // [C] member counts
+    int *ci = reinterpret_cast<int *>(key + C);                     // [C]
     float *sq = reinterpret_cast<float *>(ci + C);                  // [G][128]
     float *red = sq + G * d;                                        // [16][SEL_WARPS]
     int *hist = reinterpret_cast<int *>(red + 16 * SEL_WARPS);      // [256]
@@ -63,33 +71,35 @@ __global__ void __launch_bounds__(SEL_THREADS) select_kernel(const SelectParams 
     const int n_c = min(max(p.st.n_c[h], 0), C);
     const int end = p.st.end[h];
     const int need = p.st.need[h];
-    const int n = p.n_dev[0];
     const bool active = end > 1 && need > 0;
+    const bool scoring = active && !p.shared_in;
+    if (!scoring && b != 0) return;
     const float *count = p.st.count + (int64_t)h * C;
+    float *zg = p.zbuf + (int64_t)h * G * C;
 
-    for (int c = tid; c < C; c += SEL_THREADS) {
-        ci[c] = c < n_c ? (int)count[c] : 0;
-        sel[c] = 0;
-    }
-    if (tid == 0) sel[C] = 1;
-
-    if (active && !p.shared_in) {
-        // ---- scores e[g][c] from the summaries --------------------------------------------
+    if (scoring) {
+        // ---- scores of this CTA's slice of clusters ------------------------------------------
         const TQ *q = static_cast<const TQ *>(p.q) + (int64_t)h * G * d;
         for (int i = tid; i < G * d; i += SEL_THREADS) sq[i] = load_as_float(q + i);
         __syncthreads();
+        const int per = (((n_c + nb - 1) / nb) + 3) & ~3;
+        const int c_lo = min(b * per, n_c), c_hi = min(c_lo + per, n_c);
         const float *mmax = p.st.mmax + (int64_t)h * C, *mmin = p.st.mmin + (int64_t)h * C;
         if (p.st.summary_bits == 8) {
             const int8_t *dir8 = p.st.dir8 + (int64_t)h * C * d;
             const int part = lane & 7, grp = lane >> 3;
-            for (int c0 = wid * 4; c0 < n_c; c0 += SEL_WARPS * 4) {
+#pragma unroll 2
+            for (int c0 = c_lo + wid * 4; c0 < c_hi; c0 += SEL_WARPS * 4) {
                 const int c = c0 + grp;
+                const bool live = c < c_hi;
                 float v[16];
-                if (c < n_c) {
-                    const int4 raw = *reinterpret_cast<const int4 *>(dir8 + (int64_t)c * d + part * 16);
-                    const int8_t *b = reinterpret_cast<const int8_t *>(&raw);
+                float cn = 0.f, mx = 0.f, mn = 0.f;
+                if (live) {
+                    const int4 raw = __ldg(reinterpret_cast<const int4 *>(dir8 + (int64_t)c * d + part * 16));
+                    cn = count[c]; mx = mmax[c]; mn = mmin[c];
+                    const int8_t *bb = reinterpret_cast<const int8_t *>(&raw);
 #pragma unroll
-                    for (int i = 0; i < 16; ++i) v[i] = (float)b[i];
+                    for (int i = 0; i < 16; ++i) v[i] = (float)bb[i];
                 } else {
 #pragma unroll
                     for (int i = 0; i < 16; ++i) v[i] = 0.f;
@@ -115,19 +125,20 @@ __global__ void __launch_bounds__(SEL_THREADS) select_kernel(const SelectParams 
                     dot += __shfl_xor_sync(0xffffffffu, dot, 1);
                     dot += __shfl_xor_sync(0xffffffffu, dot, 2);
                     dot += __shfl_xor_sync(0xffffffffu, dot, 4);
-                    if (part == 0 && c < n_c) {
+                    if (part == 0 && live) {
                         const float pr = dot * inv;
-                        float e = pr >= 0.f ? mmax[c] * pr : mmin[c] * pr;
-                        if (ci[c] == 0) e = -INFINITY;
-                        z[g * C + c] = e * p.scale;
+                        float e = pr >= 0.f ? mx * pr : mn * pr;
+                        if (cn == 0.f) e = -INFINITY;
+                        __stcg(zg + g * C + c, e * p.scale);
                         if (p.e_out) p.e_out[((int64_t)h * G + g) * C + c] = e;
                     }
                 }
             }
         } else {
             const float *sd = p.st.sum_dir + (int64_t)h * C * d;
-            for (int c = wid; c < n_c; c += SEL_WARPS) {
-                const float4 v = *reinterpret_cast<const float4 *>(sd + (int64_t)c * d + lane * 4);
+#pragma unroll 2
+            for (int c = c_lo + wid; c < c_hi; c += SEL_WARPS) {
+                const float4 v = __ldg(reinterpret_cast<const float4 *>(sd + (int64_t)c * d + lane * 4));
                 const float n2 = warp_sum(v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w);
                 const float inv = 1.0f / fmaxf(sqrtf(n2), 1e-12f);
                 for (int g = 0; g < G; ++g) {
@@ -136,14 +147,42 @@ __global__ void __launch_bounds__(SEL_THREADS) select_kernel(const SelectParams 
                     if (lane == 0) {
                         const float pr = dot * inv;
                         float e = pr >= 0.f ? mmax[c] * pr : mmin[c] * pr;
-                        if (ci[c] == 0) e = -INFINITY;
-                        z[g * C + c] = e * p.scale;
+                        if (count[c] == 0.f) e = -INFINITY;
+                        __stcg(zg + g * C + c, e * p.scale);
                         if (p.e_out) p.e_out[((int64_t)h * G + g) * C + c] = e;
                     }
                 }
             }
         }
-        __syncthreads();
+        if (nb > 1) {
+            __threadfence();
+            __syncthreads();
+            if (tid == 0) s_last = atomicAdd(p.ticket + h, 1) == nb - 1;
+            __syncthreads();
+            if (!s_last) return;
+            __threadfence();
+            if (tid == 0) p.ticket[h] = 0;
+        } else {
+            __syncthreads();
+        }
+    }
+    // ---- the head's picking CTA from here on ---------------------------------------------------------
+    for (int c = tid; c < C; c += SEL_THREADS) {
+        ci[c] = c < n_c ? (int)count[c] : 0;
+        sel[c] = 0;
+    }
+    if (tid == 0) {
+        sel[C] = 1;
+        if (!p.idx) p.cnt[h] = 0;                     // the attention kernel adds the rows it reads
+    }
+    if (scoring) {
+        for (int i = tid; i < G * n_c; i += SEL_THREADS) {
+            const int g = i / n_c, c = i - g * n_c;
+            z[g * C + c] = __ldcg(zg + g * C + c);
+        }
+    }
+    __syncthreads();
+    if (scoring) {
         // ---- shared score: sum over the group of each query head's softmax over clusters ----
         float zm[16], tot[16];
         for (int g = 0; g < G; ++g) {
@@ -260,15 +299,34 @@ __global__ void __launch_bounds__(SEL_THREADS) select_kernel(const SelectParams 
         }
         __syncthreads();
     }
-    // ---- weights out ---------------------------------------------------------------------
+    // ---- weights and selection bits out ---------------------------------------------------------
     float *w = p.w + (int64_t)h * (C + 1);
     for (int c = tid; c <= C; c += SEL_THREADS) w[c] = sel[c] ? 1.f : 0.f;
+    const int words = C / 32 + 1;
+    uint32_t *bits = p.selbits + (int64_t)h * words;
+    for (int wd = tid; wd < words; wd += SEL_THREADS) {
+        uint32_t v = 0;
+        for (int i = 0; i < 32; ++i) {
+            const int c = wd * 32 + i;
+            if (c <= C && sel[c]) v |= 1u << i;
+        }
+        bits[wd] = v;
+    }
+}
 
-    // ---- ordered list of the positions to read ---------------------------------------------
+// Ordered list of the positions to read, one CTA per head (only when a caller asks for the list).
+__global__ void __launch_bounds__(512) list_kernel(const SelectParams p) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    __shared__ int ired[40];
+    const int C = p.st.C, h = blockIdx.x, tid = threadIdx.x;
+    const int words = C / 32 + 1;
+    uint32_t *bits = reinterpret_cast<uint32_t *>(smem_raw);
+    for (int i = tid; i < words; i += 512) bits[i] = p.selbits[(int64_t)h * words + i];
+    __syncthreads();
     const int16_t *lab = p.st.labels + (int64_t)h * p.st.capacity;
-    const int nn = min(max(n, 0), p.st.capacity);
-    const int vecs = (nn + 7) >> 3;                               // 8 labels per 16-byte vector
-    const int per = (vecs + SEL_THREADS - 1) / SEL_THREADS;
+    const int nn = min(max(p.n_dev[0], 0), p.st.capacity);
+    const int vecs = (nn + 7) >> 3;
+    const int per = (vecs + 511) / 512;
     const int v0 = min(tid * per, vecs), v1 = min(v0 + per, vecs);
     int mine = 0;
     bool bad = false;
@@ -280,7 +338,7 @@ __global__ void __launch_bounds__(SEL_THREADS) select_kernel(const SelectParams 
             const int pos = v * 8 + i;
             const unsigned l = (unsigned)(int)l8[i];
             if (pos < nn) {
-                if (l <= (unsigned)C) mine += sel[l];
+                if (l <= (unsigned)C) mine += (bits[l >> 5] >> (l & 31)) & 1u;
                 else bad = true;
             }
         }
@@ -295,7 +353,7 @@ __global__ void __launch_bounds__(SEL_THREADS) select_kernel(const SelectParams 
         for (int i = 0; i < 8; ++i) {
             const int pos = v * 8 + i;
             const unsigned l = (unsigned)(int)l8[i];
-            if (pos < nn && l <= (unsigned)C && sel[l]) out[off++] = pos;
+            if (pos < nn && l <= (unsigned)C && ((bits[l >> 5] >> (l & 31)) & 1u)) out[off++] = pos;
         }
     }
     if (tid == 0) p.cnt[h] = total;
@@ -312,14 +370,26 @@ static size_t select_smem(int G, int C, bool scored) {
     return (b + 15) & ~size_t(15);
 }
 
+static int64_t select_ws_bytes(int heads, int G, int C) {
+    int64_t z = ((int64_t)heads * G * C * 4 + 255) / 256 * 256;
+    int64_t t = ((int64_t)heads * 4 + 255) / 256 * 256;
+    int64_t bits = ((int64_t)heads * (C / 32 + 1) * 4 + 255) / 256 * 256;
+    return z + t + bits;
+}
+
 }  // namespace skv
 
 using namespace skv;
 
+extern "C" int64_t skv_select_workspace_bytes(int heads, int G, int C) {
+    if (heads <= 0 || G < 1 || G > 16 || C < 16 || (C & (C - 1)) || C > 16384) return SKV_E_RANGE;
+    return select_ws_bytes(heads, G, C);
+}
+
 extern "C" int skv_select(const skv_state *st, const void *q, int dtype, int G, const int32_t *n_dev, float *w,
-                          int32_t *idx, int64_t idx_stride, int32_t *cnt, const float *shared_in, float *shared_out,
-                          float *e_out, float scale, void *stream) {
-    if (!st || !n_dev || !w || !idx || !cnt) return SKV_E_NULL;
+                          uint32_t *selbits, int32_t *idx, int64_t idx_stride, int32_t *cnt, const float *shared_in,
+                          float *shared_out, float *e_out, void *workspace, float scale, void *stream) {
+    if (!st || !n_dev || !w || !cnt || !workspace) return SKV_E_NULL;
     if (!shared_in && !q) return SKV_E_NULL;
     if (!st->count || !st->n_c || !st->end || !st->need || !st->labels || !st->mmax || !st->mmin) return SKV_E_NULL;
     if (st->d != HEAD_DIM) return SKV_E_DIM;
@@ -328,16 +398,22 @@ extern "C" int skv_select(const skv_state *st, const void *q, int dtype, int G, 
     if (dtype != SKV_BF16 && dtype != SKV_F32) return SKV_E_DTYPE;
     if (st->summary_bits != 8 && st->summary_bits != 32) return SKV_E_RANGE;
     if (st->summary_bits == 8 ? !st->dir8 : !st->sum_dir) return SKV_E_NULL;
-    if (st->heads <= 0 || st->capacity <= 0 || idx_stride < st->capacity) return SKV_E_RANGE;
-    if (st->capacity % 8 || !aligned16(st->labels)) return SKV_E_ALIGN;
+    if (st->heads <= 0 || st->heads > 65535 || st->capacity <= 0 || (idx && idx_stride < st->capacity)) return SKV_E_RANGE;
+    if (st->capacity % 8 || !aligned16(st->labels) || !aligned16(workspace)) return SKV_E_ALIGN;
     if (st->summary_bits == 8 ? !aligned16(st->dir8) : !aligned16(st->sum_dir)) return SKV_E_ALIGN;
     const size_t smem = select_smem(G, st->C, shared_in == nullptr);
     if ((int)smem > device_max_smem_optin()) return SKV_E_DIM;
     SelectParams p;
     p.st = *st; p.q = q; p.G = G; p.n_dev = n_dev; p.w = w; p.idx = idx; p.idx_stride = idx_stride; p.cnt = cnt;
     p.shared_in = shared_in; p.shared_out = shared_out; p.e_out = e_out; p.scale = scale;
+    char *ws = static_cast<char *>(workspace);
+    p.zbuf = reinterpret_cast<float *>(ws);
+    ws += ((int64_t)st->heads * G * st->C * 4 + 255) / 256 * 256;
+    p.ticket = reinterpret_cast<int32_t *>(ws);
+    ws += ((int64_t)st->heads * 4 + 255) / 256 * 256;
+    p.selbits = selbits ? selbits : reinterpret_cast<uint32_t *>(ws);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    auto kern = dtype == SKV_BF16 ? select_kernel<__nv_bfloat16> : select_kernel<float>;
+    auto kern = dtype == SKV_BF16 ? score_pick_kernel<__nv_bfloat16> : score_pick_kernel<float>;
     static size_t configured[64][2] = {};
     int dev = 0;
     SKV_CUDA_OK(cudaGetDevice(&dev));
@@ -346,7 +422,11 @@ extern "C" int skv_select(const skv_state *st, const void *q, int dtype, int G, 
         SKV_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         configured[dev][dtype] = smem;
     }
-    kern<<<st->heads, SEL_THREADS, smem, s>>>(p);
+    int ctas = (2 * device_sm_count() + st->heads - 1) / st->heads;
+    ctas = ctas < 1 ? 1 : (ctas > SEL_MAX_CTAS ? SEL_MAX_CTAS : ctas);
+    if (shared_in) ctas = 1;
+    kern<<<dim3(ctas, st->heads), SEL_THREADS, smem, s>>>(p);
+    if (idx) list_kernel<<<st->heads, 512, (st->C / 32 + 1) * 4, s>>>(p);
     SKV_CUDA_OK(cudaGetLastError());
     return SKV_OK;
 }

@@ -1,0 +1,115 @@
+"""Whole decode step on the GPU: list-free attention equals the listed one, sparse at budget 1 equals
+dense, graph replay equals eager, a batch equals separate runs, the engine-seam patch equals the decoder."""
+
+from __future__ import annotations
+
+import math
+
+import pytest
+import torch
+
+from oracle import cluster_oracle as oc
+from sparse_kv_reads_b200 import GraphDecoder, Qwen3Config, Qwen3Model, install, uninstall
+from sparse_kv_reads_b200.cluster_state import SphereIndexGraph
+from _helpers import DEV, isotropic_stream, row_sets
+
+pytestmark = pytest.mark.gpu
+
+TINY = dict(hidden_size=256, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=128,
+            intermediate_size=512, vocab_size=1000, max_position_embeddings=2048)
+
+
+def tiny_model(seed=3):
+    with torch.device(DEV):
+        m = Qwen3Model(Qwen3Config(**TINY))
+    return m.to(torch.bfloat16).eval().init_random(seed=seed, std=0.05)
+
+
+@pytest.mark.parametrize("G", [2, 4])
+def test_attention_from_labels_equals_attention_over_the_list(G):
+    h, n = 6, 3000
+    Q, K, V = isotropic_stream(h, 3008, h * G, seed=11)
+    ix = SphereIndexGraph(C=256, C_init=64, cap_keys=32.0, window=64, delta=math.inf, capacity=3008, budget=0.2)
+    Kd, Vd = K.to(DEV), V.to(DEV)
+    ix.observe(Kd, n)
+    for t in range(5):
+        ix.observe(Kd, n + t)
+        q = Q[t].to(DEV)
+        labels, w = ix.labels_and_weights(q, n=n + t, budget=0.2)
+        want = ix._attend(q, Kd, Vd).clone()
+        cnt = ix.cnt.clone()
+        sets, lists = row_sets(ix)
+        ix._select(q, ix._n_scalar, listed=False)
+        assert int(ix.cnt.abs().sum()) == 0
+        got = ix._attend_labels(q, Kd, Vd, ix._n_scalar)
+        assert torch.equal(ix.cnt, cnt)
+        assert float((got.float() - want.float()).abs().max()) <= 1e-2
+        ref = oc.attend_rows(Q[t], K, V, [l.long() for l in lists])
+        assert float((got.cpu().double() - ref).abs().max()) <= 1e-2
+        bits = ix.selbits.cpu()
+        for i in range(h):
+            on = [(int(bits[i, c // 32]) >> (c % 32)) & 1 for c in range(257)]
+            assert on == [int(x > 0) for x in w[i].cpu().tolist()]
+    assert ix.check_status() == 0
+
+
+def run_decoder(model, ids, P, T, capture, **kw):
+    B = ids.shape[0]
+    cache = model.alloc_cache(-(-(P + T + 2) // 16) * 16, max_batch=B)
+    out = []
+    with torch.no_grad():
+        model.prefill(ids[:, :P], cache, chunk=128)
+        dec = GraphDecoder(model, cache, **kw)
+        dec.prepare(P)
+        if capture:
+            dec.capture()
+        for t in range(P, P + T):
+            out.append(dec.step(ids[:, t:t + 1], t)[:, -1].float().clone())
+    return torch.stack(out, 1), dec
+
+
+def test_budget_one_equals_dense_and_graph_equals_eager():
+    model = tiny_model()
+    P, T = 300, 80
+    ids = torch.randint(0, 1000, (1, P + T + 1), generator=torch.Generator().manual_seed(3)).to(DEV)
+    kw = dict(mode="cluster", budget=1.0, C=64, C_init=16, split_factor=2.0, window=4, delta=float("inf"),
+              check_every=4, summary_bits=32)
+    dense, _ = run_decoder(model, ids, P, T, True, mode="dense")
+    eager, d0 = run_decoder(model, ids, P, T, False, **kw)
+    graph, d1 = run_decoder(model, ids, P, T, True, **kw)
+    torch.testing.assert_close(eager, dense, rtol=2e-2, atol=2e-2)
+    assert torch.equal(graph, eager)                                 # replay is the same arithmetic
+    assert sum(i.splits for i in d1.attn) > 0 and all(int(i.n_c.max()) <= 64 for i in d1.attn)
+    assert all(i.check_status() in (0, 1) for i in d1.attn)          # 1 = a head used up its 64 slots
+    with torch.no_grad():                                            # the model's own dense decode agrees too
+        cache = model.alloc_cache(400)
+        model.prefill(ids[:, :P], cache, chunk=128)
+        own = torch.stack([model(ids[:, t:t + 1], cache, start_pos=t)[:, -1].float() for t in range(P, P + 8)], 1)
+    torch.testing.assert_close(own, dense[:, :8], rtol=2e-2, atol=2e-2)
+
+
+def test_a_batch_equals_separate_sequences():
+    model = tiny_model(seed=5)
+    P, T = 260, 24
+    ids = torch.randint(0, 1000, (2, P + T + 1), generator=torch.Generator().manual_seed(4)).to(DEV)
+    kw = dict(mode="cluster", budget=0.3, C=64, C_init=16, cap_keys=24.0, window=16, delta=0.03, summary_bits=8)
+    both, _ = run_decoder(model, ids, P, T, True, **kw)
+    for b in range(2):
+        one, _ = run_decoder(model, ids[b:b + 1], P, T, True, **kw)
+        torch.testing.assert_close(both[b:b + 1], one, rtol=2e-2, atol=2e-2)
+
+
+def test_installed_decode_op_matches_the_graph_decoder_and_tracks_reads():
+    model = tiny_model(seed=7)
+    P, T = 300, 12
+    ids = torch.randint(0, 1000, (1, P + T + 1), generator=torch.Generator().manual_seed(5)).to(DEV)
+    kw = dict(budget=0.25, C=64, C_init=16, cap_keys=32.0, window=16, delta=float("inf"), summary_bits=32)
+    want, _ = run_decoder(model, ids, P, T, False, mode="cluster", **kw)
+    stats = install(model, "cluster_fused", capacity=512, **kw)
+    with torch.no_grad():
+        cache = model.alloc_cache(512)
+        model.prefill(ids[:, :P], cache, chunk=128)
+        got = torch.stack([model(ids[:, t:t + 1], cache, start_pos=t)[:, -1].float() for t in range(P, P + T)], 1)
+    uninstall(model)
+    torch.testing.assert_close(got, want, rtol=2e-2, atol=2e-2)
+    assert stats.steps == T * 2 and 0.2 < stats.read_fraction < 0.6 and stats.kv_read_fraction > stats.read_fraction
