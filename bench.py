@@ -176,7 +176,7 @@ def kernel_roofline(dec, n_now, peak_gbs, which):
     """Per-launch duration of the attention kernel measured with CUDA events, layer by layer, outside the
     graph (each layer's rows are cold: the layers' caches together are far larger than L2), and of the
     three kernels of a layer step together.  Bytes: K and V rows read plus their 4-byte positions for the
-    attention kernel; the full accounting formula for the layer step."""
+    attention kernel (plus the labels it scans); the full accounting formula for the layer step."""
     from sparse_kv_reads_b200.accounting import step_bytes
     B, H, H_kv, d = dec.B, dec.H, dec.H_kv, dec.d
     dev = dec.tok.device
@@ -213,14 +213,17 @@ def kernel_roofline(dec, n_now, peak_gbs, which):
         out.sort()
         return out[len(out) // 2] * 1e-3 / len(layers)
 
-    sel_t = timed(graph_of(lambda ix, kv: ix._select(q, dec.n_dev)))
-    att_t = timed(graph_of(lambda ix, kv: ix._attend(q, kv[0], kv[1])))
-    stp_t = timed(graph_of(lambda ix, kv: (ix._select(q, dec.n_dev), ix._attend(q, kv[0], kv[1]))))
+    # the two launches a layer step makes: score + pick, then attention straight from the labels
+    sel_t = timed(graph_of(lambda ix, kv: ix._select(q, dec.n_dev, listed=False)))
+    att_t = timed(graph_of(lambda ix, kv: ix._attend_labels(q, kv[0], kv[1], dec.n_dev)))
+    stp_t = timed(graph_of(lambda ix, kv: (ix._select(q, dec.n_dev, listed=False),
+                                           ix._attend_labels(q, kv[0], kv[1], dec.n_dev))))
     rows = torch.stack([ix.cnt for ix in layers]).float()              # [layers, heads]
     n_c = torch.stack([ix.n_c for ix in layers]).float()
-    att_bytes = float((rows * (2 * 256 + 4)).sum(1).mean())
+    # attention kernel: K and V rows, the int16 label of every cached position, the selection bits
+    att_bytes = float((rows * 2 * 256).sum(1).mean()) + rows.shape[1] * (2 * n_now + 4 * (layers[0].C // 32 + 1))
     stp_bytes = float(step_bytes(n=n_now, rows=rows, clusters=n_c, d=d, summary_bits=8).sum(1).mean())
-    roof = {"bound": "hbm", "kernel": "attend_mma_kernel", "achieved": att_bytes / att_t / 1e9, "peak": peak_gbs,
+    roof = {"bound": "hbm", "kernel": "attend_labels_kernel", "achieved": att_bytes / att_t / 1e9, "peak": peak_gbs,
             "unit": "GB/s", "frac": att_bytes / att_t / 1e9 / peak_gbs, "traffic": None, "peak_source": which,
             "us_per_launch": att_t * 1e6, "bytes_per_launch": att_bytes}
     layer = {"kernels": "select + attend (insert runs once for all layers)", "us_per_layer": stp_t * 1e6,
