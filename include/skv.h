@@ -216,6 +216,28 @@ int skv_fit(const skv_state *st, const void *K, int dtype, int64_t k_head_stride
 int skv_rebin(const skv_state *st, const int32_t *head_list, int n_list, int end, const void *K, int dtype,
               int64_t k_head_stride, int64_t k_row_stride, void *workspace, int64_t workspace_bytes, void *stream);
 
+/* ---- single-token forward around the attention (bf16) ------------------------------------------------
+ * The decode graph of the reference runs the engine's modules one framework op at a time
+ * (ssa/models/graph_decode.py:98-117: norm1, q/k/v, q_norm, k_norm, apply_rope, index_copy_, o, norm2, ffn).
+ * These three launches replace the element-wise ops among them; the matrix products stay library GEMVs. */
+
+/* h [B, hidden] += delta (delta may be null), stored in bf16; out = RMSNorm(h) * w.  Replaces the residual
+ * add and layer.norm1 / layer.norm2 / final_norm (graph_decode.py:100,116-118). */
+int skv_add_rmsnorm(void *h, const void *delta, const void *w, void *out, int B, int hidden, float eps, void *stream);
+
+/* qkv [B, (H + 2*H_kv) * d] (query heads, then key heads, then value heads) -> q_out [B*H, d] with the per-head
+ * RMSNorm and the rotary embedding applied, and the new key (normed, rotated) and value written into the caches
+ * [B, H_kv, L, d] at row pos_dev[0].  cos/sin tables [positions, d] bf16.  Replaces q_norm, k_norm, apply_rope
+ * and the two index_copy_ calls (graph_decode.py:101-108). */
+int skv_qk_rope_cache(const void *qkv, const void *q_norm_w, const void *k_norm_w, const void *cos_table,
+                      const void *sin_table, const int64_t *pos_dev, void *q_out, void *k_cache, void *v_cache,
+                      int B, int H, int H_kv, int d, int64_t cache_batch_stride, int64_t cache_head_stride,
+                      int64_t cache_row_stride, float eps, void *stream);
+
+/* gate_up [B, 2*inter] (gate columns first) -> out [B, inter] = silu(gate) * up: the element-wise middle of
+ * layer.ffn (graph_decode.py:117). */
+int skv_silu_mul(const void *gate_up, void *out, int B, int inter, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

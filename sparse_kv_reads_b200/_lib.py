@@ -19,7 +19,8 @@ ST_NO_SLOT, ST_SPLIT_TOO_BIG, ST_BAD_INDEX = 1, 2, 4
 
 EXPORTS = ("skv_version", "skv_error_string", "skv_last_cuda_error", "skv_attend_splits",
            "skv_attend_workspace_bytes", "skv_attend", "skv_attend_static", "skv_attend_labels", "skv_merge", "skv_select_workspace_bytes", "skv_select", "skv_insert",
-           "skv_insert_max_members", "skv_fit_workspace_bytes", "skv_fit", "skv_rebin")
+           "skv_insert_max_members", "skv_fit_workspace_bytes", "skv_fit", "skv_rebin",
+           "skv_add_rmsnorm", "skv_qk_rope_cache", "skv_silu_mul")
 
 
 class SkvError(RuntimeError):
@@ -72,6 +73,12 @@ def _declare(lib) -> None:
     lib.skv_fit_workspace_bytes.argtypes = [i32, i32, i32, i32]
     lib.skv_fit.restype = i32
     lib.skv_fit.argtypes = [C.POINTER(SkvState), vp, i32, i64, i64, i32, i32, i32, i32, vp, f32, f32, vp, i64, vp]
+    lib.skv_add_rmsnorm.restype = i32
+    lib.skv_add_rmsnorm.argtypes = [vp, vp, vp, vp, i32, i32, f32, vp]
+    lib.skv_qk_rope_cache.restype = i32
+    lib.skv_qk_rope_cache.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i64, i64, i64, f32, vp]
+    lib.skv_silu_mul.restype = i32
+    lib.skv_silu_mul.argtypes = [vp, vp, i32, i32, vp]
     lib.skv_rebin.restype = i32
     lib.skv_rebin.argtypes = [C.POINTER(SkvState), vp, i32, i32, vp, i32, i64, i64, vp, i64, vp]
 

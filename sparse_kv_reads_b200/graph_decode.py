@@ -15,9 +15,11 @@ import math
 
 import torch
 
+import torch.nn.functional as F
+
 from ._lib import check, dtype_code, lib, stream_ptr
 from .cluster_state import ClusterArena, SphereIndexGraph
-from .qwen3 import apply_rope
+from .qwen3 import Qwen3Model, apply_rope
 
 
 class DenseAttentionGraph:
@@ -74,7 +76,7 @@ class GraphDecoder:
                  window: int = 64, delta: float = 0.03, check_every: int = 16, partition: str = "kmeans",
                  C_init: int | None = None, split_factor: float | None = None, refit_every: int = 0,
                  grow_cap: bool = False, reset_at: int = 0, summary_bits: int = 8, cap_keys: float = 0.0,
-                 fused_insert: bool = True, var_factor: float = 0.0, var_min: int = 8, **_):
+                 fused_insert: bool = True, var_factor: float = 0.0, var_min: int = 8, fused_dense: bool = True, **_):
         cfg = model.cfg
         # no slot count given: 1,024 slots, 256 fitted at the prompt, split over twice the mean size
         # (ssa/models/graph_decode.py:38-43)
@@ -110,6 +112,11 @@ class GraphDecoder:
                          for i in range(nl)]
         self.graph = None
         self.logits = None
+        # the bundled bf16 model runs its element-wise decode ops as three fused launches per layer
+        self.fused_dense = fused_dense and isinstance(model, Qwen3Model) and dtype == torch.bfloat16 \
+            and dev.type == "cuda"
+        if self.fused_dense:
+            self._fuse_weights()
         self.fused_insert = fused_insert and mode == "cluster" and window >= 1
         self.insert_all = None
 
@@ -127,6 +134,8 @@ class GraphDecoder:
             self.insert_all = AllLayerInsert(self.attn, [self._heads(k) for k in self.cache.k[:len(self.attn)]])
 
     def _body(self) -> torch.Tensor:
+        if self.fused_dense:
+            return self._body_fused()
         m, H, H_kv, d, B = self.model, self.H, self.H_kv, self.d, self.B
         torch.add(self.pos, 1, out=self.n_dev)
         if self.insert_all is not None:
@@ -153,6 +162,61 @@ class GraphDecoder:
             h = h + a.tp.all_reduce(a.o(out.view(B, 1, H * d)))
             h = h + layer.ffn(layer.norm2(h))
         return m.logits(m.final_norm(h))
+
+    def _fuse_weights(self) -> None:
+        """Lay q/k/v and gate/up weights of every layer out as one matrix each (the modules keep working:
+        their weights become views of the fused tensors), so a layer needs four matrix products."""
+        self._wqkv, self._wgu = [], []
+        with torch.no_grad():
+            for layer in self.model.layers:
+                a, f = layer.attn, layer.ffn
+                wqkv = torch.cat([a.q.weight, a.k.weight, a.v.weight], 0).contiguous()
+                nq, nk = a.q.weight.shape[0], a.k.weight.shape[0]
+                a.q.weight.data, a.k.weight.data, a.v.weight.data = wqkv[:nq], wqkv[nq:nq + nk], wqkv[nq + nk:]
+                wgu = torch.cat([f.gate.weight, f.up.weight], 0).contiguous()
+                ni = f.gate.weight.shape[0]
+                f.gate.weight.data, f.up.weight.data = wgu[:ni], wgu[ni:]
+                self._wqkv.append(wqkv)
+                self._wgu.append(wgu)
+
+    def _body_fused(self) -> torch.Tensor:
+        m, H, H_kv, d, B = self.model, self.H, self.H_kv, self.d, self.B
+        L = lib()
+        st = stream_ptr(self.tok.device)
+        torch.add(self.pos, 1, out=self.n_dev)
+        if self.insert_all is not None:
+            self.insert_all(self.n_dev)
+        h = m.embed(self.tok).view(B, -1).contiguous()
+        hidden = h.shape[1]
+        eps = m.final_norm.eps
+        delta = None
+        xn = torch.empty_like(h)
+        qh = torch.empty(B * H, d, dtype=h.dtype, device=h.device)
+        for i, layer in enumerate(m.layers):
+            a, f = layer.attn, layer.ffn
+            check(L.skv_add_rmsnorm(h.data_ptr(), None if delta is None else delta.data_ptr(),
+                                    layer.norm1.weight.data_ptr(), xn.data_ptr(), B, hidden, eps, st), "skv_add_rmsnorm")
+            qkv = F.linear(xn, self._wqkv[i])
+            kc, vc = self.cache.k[i], self.cache.v[i]
+            check(L.skv_qk_rope_cache(qkv.data_ptr(), a.q_norm.weight.data_ptr(), a.k_norm.weight.data_ptr(),
+                                      m.rope_cos.data_ptr(), m.rope_sin.data_ptr(), self.pos.data_ptr(),
+                                      qh.data_ptr(), kc.data_ptr(), vc.data_ptr(), B, H, H_kv, d, kc.stride(0),
+                                      kc.stride(1), kc.stride(2), a.q_norm.eps, st), "skv_qk_rope_cache")
+            if self.mode == "dense":
+                out = self.attn[i](qh, self._heads(kc), self._heads(vc), self.n_dev)
+            else:
+                out = self.attn[i].step(qh, self._heads(kc), self._heads(vc), self.n_dev,
+                                        insert=self.insert_all is None)
+            o = a.tp.all_reduce(F.linear(out.view(B, H * d), a.o.weight))
+            check(L.skv_add_rmsnorm(h.data_ptr(), o.data_ptr(), layer.norm2.weight.data_ptr(), xn.data_ptr(), B,
+                                    hidden, eps, st), "skv_add_rmsnorm")
+            gu = F.linear(xn, self._wgu[i])
+            act = torch.empty(B, gu.shape[1] // 2, dtype=gu.dtype, device=gu.device)
+            check(L.skv_silu_mul(gu.data_ptr(), act.data_ptr(), B, act.shape[1], st), "skv_silu_mul")
+            delta = f.tp.all_reduce(F.linear(act, f.down.weight))
+        check(L.skv_add_rmsnorm(h.data_ptr(), delta.data_ptr(), m.final_norm.weight.data_ptr(), xn.data_ptr(), B,
+                                hidden, eps, st), "skv_add_rmsnorm")
+        return m.logits(xn.view(B, 1, hidden))
 
     def capture(self) -> None:
         """Record one decode step.  Call after ``prepare`` and before the first ``step``; the warm-up

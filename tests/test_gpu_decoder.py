@@ -112,4 +112,17 @@ def test_installed_decode_op_matches_the_graph_decoder_and_tracks_reads():
         got = torch.stack([model(ids[:, t:t + 1], cache, start_pos=t)[:, -1].float() for t in range(P, P + T)], 1)
     uninstall(model)
     torch.testing.assert_close(got, want, rtol=2e-2, atol=2e-2)
-    assert stats.steps == T * 2 and 0.2 < stats.read_fraction < 0.6 and stats.kv_read_fraction > stats.read_fraction
+    assert stats.steps == T * 2, stats.steps
+    assert 0.2 < stats.read_fraction < 0.6, stats.read_fraction
+    assert stats.kv_read_fraction > stats.read_fraction
+
+
+def test_fused_dense_layers_match_the_module_by_module_forward():
+    model = tiny_model(seed=9)
+    P, T = 280, 16
+    ids = torch.randint(0, 1000, (2, P + T + 1), generator=torch.Generator().manual_seed(6)).to(DEV)
+    kw = dict(mode="cluster", budget=0.3, C=64, C_init=16, cap_keys=24.0, window=16, delta=float("inf"))
+    plain, _ = run_decoder(model, ids, P, T, True, fused_dense=False, **kw)
+    fused, dec = run_decoder(model, ids, P, T, True, **kw)
+    assert dec.fused_dense
+    torch.testing.assert_close(fused, plain, rtol=3e-2, atol=3e-2)
