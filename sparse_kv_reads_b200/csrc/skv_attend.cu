@@ -195,12 +195,20 @@ __global__ void __launch_bounds__(WARPS * 32) attend_labels_kernel(const AttendP
     if (split >= s_eff) return;
     const int p0 = split * chunk, p1 = min(p0 + chunk, n);
     uint32_t *s_bits = reinterpret_cast<uint32_t *>(smem + WARPS * STAGES * 8192);
+    const int16_t *lab = p.labels + (int64_t)head * p.lab_stride;
+    // the first pass's labels are requested before anything else so that their latency overlaps the
+    // loads of the selection bits and of the query
+    uint4 raw[2];
+    raw[0] = raw[1] = make_uint4(0u, 0u, 0u, 0u);
+    if (p0 + tid * 16 < p1) {
+        raw[0] = __ldg(reinterpret_cast<const uint4 *>(lab + p0 + tid * 16));
+        raw[1] = __ldg(reinterpret_cast<const uint4 *>(lab + p0 + tid * 16 + 8));
+    }
     for (int i = tid; i < p.sel_words; i += WARPS * 32) s_bits[i] = p.selbits[(int64_t)head * p.sel_words + i];
     WarpAttend<STAGES, HI> wa;
     wa.init(static_cast<const __nv_bfloat16 *>(p.q) + (int64_t)head * G * HEAD_DIM, G, smem + warp * (STAGES * 8192),
             s_vmask[warp], static_cast<const char *>(p.K) + (int64_t)head * p.ksh * 2,
             static_cast<const char *>(p.V) + (int64_t)head * p.vsh * 2, p.ksr * 2, p.vsr * 2, p.scale_log2);
-    const int16_t *lab = p.labels + (int64_t)head * p.lab_stride;
     int read_rows = 0;
     bool bad = false;
     __syncthreads();
@@ -208,9 +216,6 @@ __global__ void __launch_bounds__(WARPS * 32) attend_labels_kernel(const AttendP
         const int base = sub0 + tid * 16;
         uint32_t take = 0;
         if (base < p1) {
-            uint4 raw[2];
-            raw[0] = *reinterpret_cast<const uint4 *>(lab + base);
-            raw[1] = *reinterpret_cast<const uint4 *>(lab + base + 8);
             const int16_t *l16 = reinterpret_cast<const int16_t *>(raw);
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
@@ -220,6 +225,10 @@ __global__ void __launch_bounds__(WARPS * 32) attend_labels_kernel(const AttendP
                     else bad = true;
                 }
             }
+        }
+        if (base + LAB_SUB < p1) {                       // next pass's labels, in flight during this pass's attention
+            raw[0] = __ldg(reinterpret_cast<const uint4 *>(lab + base + LAB_SUB));
+            raw[1] = __ldg(reinterpret_cast<const uint4 *>(lab + base + LAB_SUB + 8));
         }
         int total;
         int off = block_excl_scan(__popc(take), s_scan, total);
@@ -382,8 +391,11 @@ using namespace skv;
 
 extern "C" int skv_attend_splits(int heads) {
     if (heads <= 0) return SKV_E_RANGE;
-    const int sms = device_sm_count();
-    int s = (2 * sms + heads - 1) / heads;
+    // Two CTAs fit an SM.  Few heads: one wave, as many CTAs per head as fill it.  Many heads: about four
+    // waves, so that the last, partly filled wave costs little.
+    const int wave = 2 * device_sm_count();
+    const int waves = heads * 4 > wave ? 4 : 1;
+    int s = (wave * waves + heads - 1) / heads;
     return s < 1 ? 1 : s;
 }
 
