@@ -12,7 +12,7 @@ namespace skv {
 
 constexpr int SEL_THREADS = 256;
 constexpr int SEL_WARPS = SEL_THREADS / 32;
-constexpr int SEL_MAX_CTAS = 16;          // CTAs that score one head's clusters in parallel
+constexpr int SEL_MAX_CTAS = 64;          // CTAs that score one head's clusters in parallel
 
 struct SelectParams {
     skv_state st;
@@ -191,11 +191,13 @@ __global__ void __launch_bounds__(SEL_THREADS) score_pick_kernel(const SelectPar
             zm[g] = m;
         }
         block_reduce_vec<true>(zm, G, red);
-        for (int g = 0; g < G; ++g) {
+        for (int g = 0; g < G; ++g) {                     // z becomes exp(z - max): one exponential per score
             float s = 0.f;
-            if (zm[g] > -INFINITY)
-                for (int c = tid; c < n_c; c += SEL_THREADS)
-                    if (ci[c] > 0) s += expf(z[g * C + c] - zm[g]);
+            for (int c = tid; c < n_c; c += SEL_THREADS) {
+                const float ex = (ci[c] > 0 && zm[g] > -INFINITY) ? expf(z[g * C + c] - zm[g]) : 0.f;
+                z[g * C + c] = ex;
+                s += ex;
+            }
             tot[g] = s;
         }
         block_reduce_vec<false>(tot, G, red);
@@ -203,7 +205,7 @@ __global__ void __launch_bounds__(SEL_THREADS) score_pick_kernel(const SelectPar
             float s = -INFINITY;
             if (c < n_c && ci[c] > 0) {
                 s = 0.f;
-                for (int g = 0; g < G; ++g) s += expf(z[g * C + c] - zm[g]) / tot[g];
+                for (int g = 0; g < G; ++g) s += z[g * C + c] / tot[g];
             }
             key[c] = float_key(s);
             if (p.shared_out) p.shared_out[(int64_t)h * C + c] = s;
@@ -226,10 +228,19 @@ __global__ void __launch_bounds__(SEL_THREADS) score_pick_kernel(const SelectPar
             const int shift = level * 8;
             for (int i = tid; i < 256; i += SEL_THREADS) hist[i] = 0;
             __syncthreads();
-            for (int c = tid; c < n_c; c += SEL_THREADS) {
-                const uint32_t k = key[c];
-                const bool match = level == 3 || (k >> (shift + 8)) == (prefix >> (shift + 8));
-                if (match && ci[c] > 0) atomicAdd(&hist[(k >> shift) & 255u], ci[c]);
+            for (int c0 = wid * 32; c0 < n_c; c0 += SEL_THREADS) {
+                // keys of one warp mostly share a digit: lanes with equal digits add up first, one atomic per digit
+                const int c = c0 + lane;
+                const uint32_t k = c < n_c ? key[c] : 0u;
+                const bool match = c < n_c && ci[c] > 0 &&
+                                   (level == 3 || (k >> (shift + 8)) == (prefix >> (shift + 8)));
+                const unsigned live = __ballot_sync(0xffffffffu, match);
+                if (match) {
+                    const uint32_t dg = (k >> shift) & 255u;
+                    const unsigned peers = __match_any_sync(live, dg);
+                    const int sum = __reduce_add_sync(peers, ci[c]);
+                    if (lane == __ffs(peers) - 1) atomicAdd(&hist[dg], sum);
+                }
             }
             __syncthreads();
             if (wid == 0) {
