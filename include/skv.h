@@ -162,6 +162,10 @@ int skv_select(const skv_state *st, const void *q, int dtype, int G, const int32
                float *w, uint32_t *selbits, int32_t *idx, int64_t idx_stride, int32_t *cnt,
                const float *shared_in, float *shared_out, float *e_out, void *workspace, float scale, void *stream);
 
+/* Tuning aid without a counterpart in the reference: `dev_ptr` is a device array of 16 uint64 that receives
+ * nanosecond time stamps of the phases of skv_select's kernel for head 0 (null switches it off). */
+void skv_debug_select_probe(void *dev_ptr);
+
 /* skv_attend without a row list: every CTA owns a range of positions, reads their int16 labels, keeps
  * the positions whose label's bit is set in `selbits` (from skv_select) and attends over them; `cnt`
  * (zeroed by skv_select) receives the rows read per head.  bf16 caches only.  Replaces

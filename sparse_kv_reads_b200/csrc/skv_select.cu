@@ -29,8 +29,20 @@ struct SelectParams {
     float *e_out;
     float *zbuf;              // [heads, G, C] scaled scores handed from the scoring CTAs to the picking CTA
     int32_t *ticket;          // [heads]
+    float *pstat;             // [heads, SEL_MAX_CTAS, 16, 2] slice (max, sum of exp) per query head
     float scale;
+    unsigned long long *probe;  // optional [16] phase time stamps (ns) of head 0's picking CTA, for tuning
 };
+
+static unsigned long long *g_probe = nullptr;
+
+__device__ __forceinline__ void stamp(const SelectParams &p, int h, int slot) {
+    if (p.probe && h == 0 && threadIdx.x == 0) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+        p.probe[slot] = t;
+    }
+}
 
 // Reduce `nv` (<= 16) per-thread values at once over the block: op = max (IS_MAX) or sum.
 template <bool IS_MAX>
@@ -48,9 +60,12 @@ __device__ __forceinline__ void block_reduce_vec(float *v, int nv, float *red /*
     __syncthreads();
 }
 
-// Grid (ctas, heads).  Every CTA scores a slice of the head's clusters and leaves the scaled scores in
-// zbuf; the last CTA of the head to finish (atomic ticket, no waiting) forms the shared score, finds
-// the threshold and writes the weights and the selection bits.
+// Grid (ctas, heads).  Every CTA scores a slice of the head's clusters: e = (longest or shortest key) x
+// projection of the query on the cluster's mean direction, scaled by 1/sqrt(d); it then leaves
+// exp(z - slice max) in zbuf and its (max, sum) per query head in pstat.  The last CTA of the head to
+// finish (atomic ticket, no waiting) combines the slices' statistics into the shared score
+// sum_g softmax_g(z)[c] without another exponential, finds the threshold key by a weighted radix select
+// and writes the weights and the selection bits.
 template <typename TQ>
 __global__ void __launch_bounds__(SEL_THREADS) score_pick_kernel(const SelectParams p) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -58,15 +73,16 @@ __global__ void __launch_bounds__(SEL_THREADS) score_pick_kernel(const SelectPar
     const int C = p.st.C, G = p.G, d = HEAD_DIM;
     const int h = blockIdx.y, b = blockIdx.x, nb = gridDim.x;
     const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
-    float *z = reinterpret_cast<float *>(smem_raw);                 // [G][C] (picking CTA)
+    float *z = reinterpret_cast<float *>(smem_raw);                 // [G][C]: slice scores, later exp values
     const int zfloats = p.shared_in ? 0 : G * C;
     uint32_t *key = reinterpret_cast<uint32_t *>(z + zfloats);      // [C]
     int *ci = reinterpret_cast<int *>(key + C);                     // [C]
     float *sq = reinterpret_cast<float *>(ci + C);                  // [G][128]
     float *red = sq + G * d;                                        // [16][SEL_WARPS]
-    int *hist = reinterpret_cast<int *>(red + 16 * SEL_WARPS);      // [256]
-    int *ired = hist + 256;                                         // [40]
-    uint8_t *sel = reinterpret_cast<uint8_t *>(ired + 40);          // [C + 1]
+    int *hist = reinterpret_cast<int *>(red + 16 * SEL_WARPS);      // [4][256]
+    int *ired = hist + 4 * 256;                                     // [40]
+    float *fb = reinterpret_cast<float *>(ired + 40);               // [SEL_MAX_CTAS][16] slice factors
+    uint8_t *sel = reinterpret_cast<uint8_t *>(fb + SEL_MAX_CTAS * 16);   // [C + 1]
 
     const int n_c = min(max(p.st.n_c[h], 0), C);
     const int end = p.st.end[h];
@@ -76,34 +92,42 @@ __global__ void __launch_bounds__(SEL_THREADS) score_pick_kernel(const SelectPar
     if (!scoring && b != 0) return;
     const float *count = p.st.count + (int64_t)h * C;
     float *zg = p.zbuf + (int64_t)h * G * C;
+    float *ps = p.pstat + (int64_t)h * SEL_MAX_CTAS * 32;          // [ctas][G][2]
+    const int per = (((n_c + nb - 1) / nb) + 3) & ~3;              // clusters per scoring CTA
+    if (b == 0) stamp(p, h, 0);
 
     if (scoring) {
-        // ---- scores of this CTA's slice of clusters ------------------------------------------
+        const int c_lo = min(b * per, n_c), c_hi = min(c_lo + per, n_c), mine = c_hi - c_lo;
+        const float *mmax = p.st.mmax + (int64_t)h * C, *mmin = p.st.mmin + (int64_t)h * C;
         const TQ *q = static_cast<const TQ *>(p.q) + (int64_t)h * G * d;
+        const bool q8 = p.st.summary_bits == 8;
+        const int part = lane & 7, grp = lane >> 3;
+        // first pass's summaries are requested before the query is staged: two latencies overlap
+        int4 raw0 = make_int4(0, 0, 0, 0);
+        float4 rawf = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (q8) {
+            const int c = c_lo + wid * 4 + grp;
+            if (c < c_hi) raw0 = __ldg(reinterpret_cast<const int4 *>(p.st.dir8 + ((int64_t)h * C + c) * d + part * 16));
+        } else {
+            const int c = c_lo + wid;
+            if (c < c_hi) rawf = __ldg(reinterpret_cast<const float4 *>(p.st.sum_dir + ((int64_t)h * C + c) * d + lane * 4));
+        }
         for (int i = tid; i < G * d; i += SEL_THREADS) sq[i] = load_as_float(q + i);
         __syncthreads();
-        const int per = (((n_c + nb - 1) / nb) + 3) & ~3;
-        const int c_lo = min(b * per, n_c), c_hi = min(c_lo + per, n_c);
-        const float *mmax = p.st.mmax + (int64_t)h * C, *mmin = p.st.mmin + (int64_t)h * C;
-        if (p.st.summary_bits == 8) {
+        if (q8) {
             const int8_t *dir8 = p.st.dir8 + (int64_t)h * C * d;
-            const int part = lane & 7, grp = lane >> 3;
-#pragma unroll 2
             for (int c0 = c_lo + wid * 4; c0 < c_hi; c0 += SEL_WARPS * 4) {
                 const int c = c0 + grp;
                 const bool live = c < c_hi;
-                float v[16];
+                const int4 raw = raw0;
+                const int cn_ = c0 + SEL_WARPS * 4 + grp;             // next pass, in flight during this one
+                if (cn_ < c_hi) raw0 = __ldg(reinterpret_cast<const int4 *>(dir8 + (int64_t)cn_ * d + part * 16));
                 float cn = 0.f, mx = 0.f, mn = 0.f;
-                if (live) {
-                    const int4 raw = __ldg(reinterpret_cast<const int4 *>(dir8 + (int64_t)c * d + part * 16));
-                    cn = count[c]; mx = mmax[c]; mn = mmin[c];
-                    const int8_t *bb = reinterpret_cast<const int8_t *>(&raw);
+                if (live) { cn = count[c]; mx = mmax[c]; mn = mmin[c]; }
+                float v[16];
+                const int8_t *bb = reinterpret_cast<const int8_t *>(&raw);
 #pragma unroll
-                    for (int i = 0; i < 16; ++i) v[i] = (float)bb[i];
-                } else {
-#pragma unroll
-                    for (int i = 0; i < 16; ++i) v[i] = 0.f;
-                }
+                for (int i = 0; i < 16; ++i) v[i] = live ? (float)bb[i] : 0.f;
                 float n2 = 0.f;
 #pragma unroll
                 for (int i = 0; i < 16; ++i) n2 = fmaf(v[i], v[i], n2);
@@ -129,16 +153,17 @@ __global__ void __launch_bounds__(SEL_THREADS) score_pick_kernel(const SelectPar
                         const float pr = dot * inv;
                         float e = pr >= 0.f ? mx * pr : mn * pr;
                         if (cn == 0.f) e = -INFINITY;
-                        __stcg(zg + g * C + c, e * p.scale);
+                        z[g * C + (c - c_lo)] = e * p.scale;
                         if (p.e_out) p.e_out[((int64_t)h * G + g) * C + c] = e;
                     }
                 }
             }
         } else {
             const float *sd = p.st.sum_dir + (int64_t)h * C * d;
-#pragma unroll 2
             for (int c = c_lo + wid; c < c_hi; c += SEL_WARPS) {
-                const float4 v = __ldg(reinterpret_cast<const float4 *>(sd + (int64_t)c * d + lane * 4));
+                const float4 v = rawf;
+                if (c + SEL_WARPS < c_hi)
+                    rawf = __ldg(reinterpret_cast<const float4 *>(sd + (int64_t)(c + SEL_WARPS) * d + lane * 4));
                 const float n2 = warp_sum(v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w);
                 const float inv = 1.0f / fmaxf(sqrtf(n2), 1e-12f);
                 for (int g = 0; g < G; ++g) {
@@ -148,12 +173,37 @@ __global__ void __launch_bounds__(SEL_THREADS) score_pick_kernel(const SelectPar
                         const float pr = dot * inv;
                         float e = pr >= 0.f ? mmax[c] * pr : mmin[c] * pr;
                         if (count[c] == 0.f) e = -INFINITY;
-                        __stcg(zg + g * C + c, e * p.scale);
+                        z[g * C + (c - c_lo)] = e * p.scale;
                         if (p.e_out) p.e_out[((int64_t)h * G + g) * C + c] = e;
                     }
                 }
             }
         }
+        __syncthreads();
+        // slice statistics: max and sum of exp(z - max) per query head; zbuf <- exp(z - max)
+        float zm[16], tot[16];
+        for (int g = 0; g < G; ++g) {
+            float m = -INFINITY;
+            for (int c = tid; c < mine; c += SEL_THREADS) m = fmaxf(m, z[g * C + c]);
+            zm[g] = m;
+        }
+        block_reduce_vec<true>(zm, G, red);
+        for (int g = 0; g < G; ++g) {
+            float s = 0.f;
+            for (int c = tid; c < mine; c += SEL_THREADS) {
+                const float zz = z[g * C + c];
+                const float ex = zz > -INFINITY ? expf(zz - zm[g]) : 0.f;
+                __stcg(zg + g * C + c_lo + c, ex);
+                s += ex;
+            }
+            tot[g] = s;
+        }
+        block_reduce_vec<false>(tot, G, red);
+        if (tid < G) {
+            __stcg(ps + (b * 16 + tid) * 2, zm[tid]);
+            __stcg(ps + (b * 16 + tid) * 2 + 1, tot[tid]);
+        }
+        if (b == 0) stamp(p, h, 1);
         if (nb > 1) {
             __threadfence();
             __syncthreads();
@@ -162,50 +212,48 @@ __global__ void __launch_bounds__(SEL_THREADS) score_pick_kernel(const SelectPar
             if (!s_last) return;
             __threadfence();
             if (tid == 0) p.ticket[h] = 0;
-        } else {
-            __syncthreads();
         }
     }
+    stamp(p, h, 2);
     // ---- the head's picking CTA from here on ---------------------------------------------------------
     for (int c = tid; c < C; c += SEL_THREADS) {
         ci[c] = c < n_c ? (int)count[c] : 0;
         sel[c] = 0;
     }
+    for (int i = tid; i < 4 * 256; i += SEL_THREADS) hist[i] = 0;
     if (tid == 0) {
         sel[C] = 1;
         if (!p.idx) p.cnt[h] = 0;                     // the attention kernel adds the rows it reads
     }
     if (scoring) {
-        for (int i = tid; i < G * n_c; i += SEL_THREADS) {
-            const int g = i / n_c, c = i - g * n_c;
-            z[g * C + c] = __ldcg(zg + g * C + c);
+        // slice factors exp(max_b - max) / total per query head
+        for (int g = wid; g < G; g += SEL_WARPS) {
+            float m = -INFINITY;
+            for (int bb = lane; bb < nb; bb += 32) m = fmaxf(m, __ldcg(ps + (bb * 16 + g) * 2));
+            m = warp_max(m);
+            float t = 0.f;
+            for (int bb = lane; bb < nb; bb += 32) {
+                const float mb = __ldcg(ps + (bb * 16 + g) * 2);
+                if (mb > -INFINITY) t += __ldcg(ps + (bb * 16 + g) * 2 + 1) * expf(mb - m);
+            }
+            t = warp_sum(t);
+            for (int bb = lane; bb < nb; bb += 32) {
+                const float mb = __ldcg(ps + (bb * 16 + g) * 2);
+                fb[bb * 16 + g] = mb > -INFINITY ? expf(mb - m) / t : 0.f;
+            }
         }
+        for (int g = 0; g < G; ++g)
+            for (int c = tid; c < n_c; c += SEL_THREADS) z[g * C + c] = __ldcg(zg + g * C + c);
     }
     __syncthreads();
+    stamp(p, h, 3);
     if (scoring) {
-        // ---- shared score: sum over the group of each query head's softmax over clusters ----
-        float zm[16], tot[16];
-        for (int g = 0; g < G; ++g) {
-            float m = -INFINITY;
-            for (int c = tid; c < n_c; c += SEL_THREADS) m = fmaxf(m, z[g * C + c]);
-            zm[g] = m;
-        }
-        block_reduce_vec<true>(zm, G, red);
-        for (int g = 0; g < G; ++g) {                     // z becomes exp(z - max): one exponential per score
-            float s = 0.f;
-            for (int c = tid; c < n_c; c += SEL_THREADS) {
-                const float ex = (ci[c] > 0 && zm[g] > -INFINITY) ? expf(z[g * C + c] - zm[g]) : 0.f;
-                z[g * C + c] = ex;
-                s += ex;
-            }
-            tot[g] = s;
-        }
-        block_reduce_vec<false>(tot, G, red);
         for (int c = tid; c < C; c += SEL_THREADS) {
             float s = -INFINITY;
             if (c < n_c && ci[c] > 0) {
+                const float *f = fb + (c / per) * 16;
                 s = 0.f;
-                for (int g = 0; g < G; ++g) s += z[g * C + c] / tot[g];
+                for (int g = 0; g < G; ++g) s += z[g * C + c] * f[g];
             }
             key[c] = float_key(s);
             if (p.shared_out) p.shared_out[(int64_t)h * C + c] = s;
@@ -219,110 +267,92 @@ __global__ void __launch_bounds__(SEL_THREADS) score_pick_kernel(const SelectPar
         }
     }
     __syncthreads();
-
+    stamp(p, h, 4);
     if (active) {
-        // ---- threshold: smallest key t with sum(count | key > t) < need ----------------------
+        // ---- threshold: smallest key t with sum(count | key > t) < need; one barrier per level, every
+        // warp scans the level's histogram for itself -----------------------------------------------
         uint32_t prefix = 0;
         int above = 0;
         for (int level = 3; level >= 0; --level) {
             const int shift = level * 8;
-            for (int i = tid; i < 256; i += SEL_THREADS) hist[i] = 0;
-            __syncthreads();
-            for (int c0 = wid * 32; c0 < n_c; c0 += SEL_THREADS) {
-                // keys of one warp mostly share a digit: lanes with equal digits add up first, one atomic per digit
-                const int c = c0 + lane;
-                const uint32_t k = c < n_c ? key[c] : 0u;
-                const bool match = c < n_c && ci[c] > 0 &&
-                                   (level == 3 || (k >> (shift + 8)) == (prefix >> (shift + 8)));
-                const unsigned live = __ballot_sync(0xffffffffu, match);
-                if (match) {
-                    const uint32_t dg = (k >> shift) & 255u;
-                    const unsigned peers = __match_any_sync(live, dg);
-                    const int sum = __reduce_add_sync(peers, ci[c]);
-                    if (lane == __ffs(peers) - 1) atomicAdd(&hist[dg], sum);
-                }
+            int *hl = hist + level * 256;
+            for (int c = tid; c < n_c; c += SEL_THREADS) {
+                const uint32_t k = key[c];
+                const bool match = level == 3 || (k >> (shift + 8)) == (prefix >> (shift + 8));
+                if (match && ci[c] > 0) atomicAdd(&hl[(k >> shift) & 255u], ci[c]);
             }
             __syncthreads();
-            if (wid == 0) {
-                // lane owns digits [8*lane, 8*lane+8); suffix sums from the top digit down
-                int loc[8], mine = 0;
+            int loc[8], mine = 0;                     // lane owns digits [8*lane, 8*lane+8)
 #pragma unroll
-                for (int i = 0; i < 8; ++i) { loc[i] = hist[lane * 8 + i]; mine += loc[i]; }
-                int suf = mine;                               // inclusive suffix over lanes >= lane
+            for (int i = 0; i < 8; ++i) { loc[i] = hl[lane * 8 + i]; mine += loc[i]; }
+            int suf = mine;                           // inclusive suffix over lanes >= lane
 #pragma unroll
-                for (int o = 1; o < 32; o <<= 1) {
-                    int t = __shfl_down_sync(0xffffffffu, suf, o);
-                    if (lane + o < 32) suf += t;
-                }
-                int higher = suf - mine;                      // counts in digits above this lane's range
-                // A(dg) = above + counts of digits > dg; smallest dg with A(dg) < need
-                int best = 256;
-                int run = higher;
-#pragma unroll
-                for (int i = 7; i >= 0; --i) {
-                    if (above + run < need) best = lane * 8 + i;
-                    run += loc[i];
-                }
-                // digits scanned top-down inside the lane, so `best` is the lowest passing digit of the lane
-#pragma unroll
-                for (int o = 16; o > 0; o >>= 1) best = min(best, __shfl_xor_sync(0xffffffffu, best, o));
-                // counts strictly above digit `best`
-                int gt = 0;
-#pragma unroll
-                for (int i = 0; i < 8; ++i) gt += (lane * 8 + i > best) ? loc[i] : 0;
-                gt = warp_sum_int(gt);
-                if (lane == 0) { ired[0] = best; ired[1] = gt; }
+            for (int o = 1; o < 32; o <<= 1) {
+                const int t = __shfl_down_sync(0xffffffffu, suf, o);
+                if (lane + o < 32) suf += t;
             }
-            __syncthreads();
-            prefix |= (uint32_t)ired[0] << shift;
-            above += ired[1];
-            __syncthreads();
+            int run = suf - mine;                     // counts in digits above this lane's range
+            int best = 256;                           // smallest digit dg with above + count(digits > dg) < need
+#pragma unroll
+            for (int i = 7; i >= 0; --i) {
+                if (above + run < need) best = lane * 8 + i;
+                run += loc[i];
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) best = min(best, __shfl_xor_sync(0xffffffffu, best, o));
+            int gt = 0;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) gt += (lane * 8 + i > best) ? loc[i] : 0;
+            gt = warp_sum_int(gt);
+            prefix |= (uint32_t)best << shift;
+            above += gt;
         }
+        stamp(p, h, 5);
         const uint32_t tau = prefix;
         int ties = 0;
         for (int c = tid; c < n_c; c += SEL_THREADS) {
             const uint32_t k = key[c];
-            sel[c] = k > tau;
+            sel[c] = k >= tau;                        // a lone cluster at the threshold is taken: above < need
             ties += (k == tau);
         }
         ties = warp_sum_int(ties);
         if (lane == 0) ired[2 + wid] = ties;
         __syncthreads();
-        if (wid == 0) {
-            int t = lane < SEL_WARPS ? ired[2 + lane] : 0;
-            t = warp_sum_int(t);
-            // equal keys: slot order, each taken while the keys ranked before it stay under need
+        int t = 0;
+        for (int w = 0; w < SEL_WARPS; ++w) t += ired[2 + w];
+        if (t > 1 && wid == 0) {
+            // several clusters share the threshold key: slot order, each taken while the keys ranked before
+            // it stay under need
             int running = above;
-            if (t > 0)
-                for (int base = 0; base < n_c; base += 32) {
-                    const int c = base + lane;
-                    const bool tie = c < n_c && key[c] == tau;
-                    const int mine = tie ? ci[c] : 0;
-                    int inc = mine;
+            for (int base = 0; base < n_c; base += 32) {
+                const int c = base + lane;
+                const bool tie = c < n_c && key[c] == tau;
+                if (!__any_sync(0xffffffffu, tie)) continue;
+                const int mine = tie ? ci[c] : 0;
+                int inc = mine;
 #pragma unroll
-                    for (int o = 1; o < 32; o <<= 1) {
-                        int u = __shfl_up_sync(0xffffffffu, inc, o);
-                        if (lane >= o) inc += u;
-                    }
-                    if (tie) sel[c] = (running + inc - mine) < need;
-                    running += __shfl_sync(0xffffffffu, inc, 31);
+                for (int o = 1; o < 32; o <<= 1) {
+                    const int u = __shfl_up_sync(0xffffffffu, inc, o);
+                    if (lane >= o) inc += u;
                 }
+                if (tie) sel[c] = (running + inc - mine) < need;
+                running += __shfl_sync(0xffffffffu, inc, 31);
+            }
         }
         __syncthreads();
     }
+    stamp(p, h, 6);
     // ---- weights and selection bits out ---------------------------------------------------------
     float *w = p.w + (int64_t)h * (C + 1);
     for (int c = tid; c <= C; c += SEL_THREADS) w[c] = sel[c] ? 1.f : 0.f;
     const int words = C / 32 + 1;
     uint32_t *bits = p.selbits + (int64_t)h * words;
-    for (int wd = tid; wd < words; wd += SEL_THREADS) {
-        uint32_t v = 0;
-        for (int i = 0; i < 32; ++i) {
-            const int c = wd * 32 + i;
-            if (c <= C && sel[c]) v |= 1u << i;
-        }
-        bits[wd] = v;
+    for (int wd = wid; wd < words; wd += SEL_WARPS) {
+        const int c = wd * 32 + lane;
+        const unsigned v = __ballot_sync(0xffffffffu, c <= C && sel[c]);
+        if (lane == 0) bits[wd] = v;
     }
+    stamp(p, h, 7);
 }
 
 // Ordered list of the positions to read, one CTA per head (only when a caller asks for the list).
@@ -376,7 +406,7 @@ static size_t select_smem(int G, int C, bool scored) {
     if (scored) b += (size_t)G * C * 4;
     b += (size_t)C * 4 * 2;                 // key, ci
     b += (size_t)G * HEAD_DIM * 4;          // sq
-    b += 16 * SEL_WARPS * 4 + 256 * 4 + 40 * 4;
+    b += 16 * SEL_WARPS * 4 + 4 * 256 * 4 + 40 * 4 + SEL_MAX_CTAS * 16 * 4;
     b += C + 1 + 16;
     return (b + 15) & ~size_t(15);
 }
@@ -385,12 +415,16 @@ static int64_t select_ws_bytes(int heads, int G, int C) {
     int64_t z = ((int64_t)heads * G * C * 4 + 255) / 256 * 256;
     int64_t t = ((int64_t)heads * 4 + 255) / 256 * 256;
     int64_t bits = ((int64_t)heads * (C / 32 + 1) * 4 + 255) / 256 * 256;
-    return z + t + bits;
+    int64_t ps = (int64_t)heads * SEL_MAX_CTAS * 32 * 4;
+    return z + t + bits + ps;
 }
 
 }  // namespace skv
 
 using namespace skv;
+
+// Tuning aid: a device array of 16 uint64 that receives phase time stamps of the selection kernel (null: off).
+extern "C" void skv_debug_select_probe(void *dev_ptr) { skv::g_probe = static_cast<unsigned long long *>(dev_ptr); }
 
 extern "C" int64_t skv_select_workspace_bytes(int heads, int G, int C) {
     if (heads <= 0 || G < 1 || G > 16 || C < 16 || (C & (C - 1)) || C > 16384) return SKV_E_RANGE;
@@ -417,12 +451,15 @@ extern "C" int skv_select(const skv_state *st, const void *q, int dtype, int G, 
     SelectParams p;
     p.st = *st; p.q = q; p.G = G; p.n_dev = n_dev; p.w = w; p.idx = idx; p.idx_stride = idx_stride; p.cnt = cnt;
     p.shared_in = shared_in; p.shared_out = shared_out; p.e_out = e_out; p.scale = scale;
+    p.probe = g_probe;
     char *ws = static_cast<char *>(workspace);
     p.zbuf = reinterpret_cast<float *>(ws);
     ws += ((int64_t)st->heads * G * st->C * 4 + 255) / 256 * 256;
     p.ticket = reinterpret_cast<int32_t *>(ws);
     ws += ((int64_t)st->heads * 4 + 255) / 256 * 256;
     p.selbits = selbits ? selbits : reinterpret_cast<uint32_t *>(ws);
+    ws += ((int64_t)st->heads * (st->C / 32 + 1) * 4 + 255) / 256 * 256;
+    p.pstat = reinterpret_cast<float *>(ws);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     auto kern = dtype == SKV_BF16 ? score_pick_kernel<__nv_bfloat16> : score_pick_kernel<float>;
     static size_t configured[64][2] = {};
