@@ -45,18 +45,31 @@ __device__ __forceinline__ void stamp(const SelectParams &p, int h, int slot) {
 }
 
 // Reduce `nv` (<= 16) per-thread values at once over the block: op = max (IS_MAX) or sum.
-template <bool IS_MAX>
-__device__ __forceinline__ void block_reduce_vec(float *v, int nv, float *red /* [16][SEL_WARPS] */) {
+template <bool IS_MAX, int NV>
+__device__ __forceinline__ void block_reduce_vec(float (&v)[NV], float *red /* [16][SEL_WARPS] */) {
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
-    for (int g = 0; g < nv; ++g) {
-        float x = IS_MAX ? warp_max(v[g]) : warp_sum(v[g]);
-        if (lane == 0) red[g * SEL_WARPS + wid] = x;
-    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+        for (int g = 0; g < NV; ++g) {                 // the NV butterflies are independent: they overlap
+            const float y = __shfl_xor_sync(0xffffffffu, v[g], o);
+            v[g] = IS_MAX ? fmaxf(v[g], y) : v[g] + y;
+        }
+    if (lane == 0)
+#pragma unroll
+        for (int g = 0; g < NV; ++g) red[g * SEL_WARPS + wid] = v[g];
     __syncthreads();
-    for (int g = 0; g < nv; ++g) {
-        float x = (lane < SEL_WARPS) ? red[g * SEL_WARPS + lane] : (IS_MAX ? -INFINITY : 0.f);
-        v[g] = IS_MAX ? warp_max(x) : warp_sum(x);
-    }
+#pragma unroll
+    for (int g = 0; g < NV; ++g) v[g] = (lane < SEL_WARPS) ? red[g * SEL_WARPS + lane] : (IS_MAX ? -INFINITY : 0.f);
+#pragma unroll
+    for (int o = SEL_WARPS / 2; o > 0; o >>= 1)
+#pragma unroll
+        for (int g = 0; g < NV; ++g) {
+            const float y = __shfl_xor_sync(0xffffffffu, v[g], o);
+            v[g] = IS_MAX ? fmaxf(v[g], y) : v[g] + y;
+        }
+#pragma unroll
+    for (int g = 0; g < NV; ++g) v[g] = __shfl_sync(0xffffffffu, v[g], 0);
     __syncthreads();
 }
 
@@ -66,7 +79,7 @@ __device__ __forceinline__ void block_reduce_vec(float *v, int nv, float *red /*
 // finish (atomic ticket, no waiting) combines the slices' statistics into the shared score
 // sum_g softmax_g(z)[c] without another exponential, finds the threshold key by a weighted radix select
 // and writes the weights and the selection bits.
-template <typename TQ>
+template <typename TQ, int GP>
 __global__ void __launch_bounds__(SEL_THREADS) score_pick_kernel(const SelectParams p) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __shared__ int s_last;
@@ -94,6 +107,7 @@ __global__ void __launch_bounds__(SEL_THREADS) score_pick_kernel(const SelectPar
     float *zg = p.zbuf + (int64_t)h * G * C;
     float *ps = p.pstat + (int64_t)h * SEL_MAX_CTAS * 32;          // [ctas][G][2]
     const int per = (((n_c + nb - 1) / nb) + 3) & ~3;              // clusters per scoring CTA
+    const float inv_per = 1.0f / (float)max(per, 1);
     if (b == 0) stamp(p, h, 0);
 
     if (scoring) {
@@ -181,28 +195,35 @@ __global__ void __launch_bounds__(SEL_THREADS) score_pick_kernel(const SelectPar
         }
         __syncthreads();
         // slice statistics: max and sum of exp(z - max) per query head; zbuf <- exp(z - max)
-        float zm[16], tot[16];
-        for (int g = 0; g < G; ++g) {
+        float zm[GP], tot[GP];
+#pragma unroll
+        for (int g = 0; g < GP; ++g) {
             float m = -INFINITY;
-            for (int c = tid; c < mine; c += SEL_THREADS) m = fmaxf(m, z[g * C + c]);
+            if (g < G)
+                for (int c = tid; c < mine; c += SEL_THREADS) m = fmaxf(m, z[g * C + c]);
             zm[g] = m;
         }
-        block_reduce_vec<true>(zm, G, red);
-        for (int g = 0; g < G; ++g) {
+        block_reduce_vec<true, GP>(zm, red);
+#pragma unroll
+        for (int g = 0; g < GP; ++g) {
             float s = 0.f;
-            for (int c = tid; c < mine; c += SEL_THREADS) {
-                const float zz = z[g * C + c];
-                const float ex = zz > -INFINITY ? expf(zz - zm[g]) : 0.f;
-                __stcg(zg + g * C + c_lo + c, ex);
-                s += ex;
-            }
+            if (g < G)
+                for (int c = tid; c < mine; c += SEL_THREADS) {
+                    const float zz = z[g * C + c];
+                    const float ex = zz > -INFINITY ? expf(zz - zm[g]) : 0.f;
+                    __stcg(zg + g * C + c_lo + c, ex);
+                    s += ex;
+                }
             tot[g] = s;
         }
-        block_reduce_vec<false>(tot, G, red);
-        if (tid < G) {
-            __stcg(ps + (b * 16 + tid) * 2, zm[tid]);
-            __stcg(ps + (b * 16 + tid) * 2 + 1, tot[tid]);
-        }
+        block_reduce_vec<false, GP>(tot, red);
+        if (tid == 0)
+#pragma unroll
+            for (int g = 0; g < GP; ++g)
+                if (g < G) {
+                    __stcg(ps + (b * 16 + g) * 2, zm[g]);
+                    __stcg(ps + (b * 16 + g) * 2 + 1, tot[g]);
+                }
         if (b == 0) stamp(p, h, 1);
         if (nb > 1) {
             __threadfence();
@@ -227,23 +248,18 @@ __global__ void __launch_bounds__(SEL_THREADS) score_pick_kernel(const SelectPar
     }
     if (scoring) {
         // slice factors exp(max_b - max) / total per query head
-        for (int g = wid; g < G; g += SEL_WARPS) {
-            float m = -INFINITY;
-            for (int bb = lane; bb < nb; bb += 32) m = fmaxf(m, __ldcg(ps + (bb * 16 + g) * 2));
-            m = warp_max(m);
-            float t = 0.f;
-            for (int bb = lane; bb < nb; bb += 32) {
-                const float mb = __ldcg(ps + (bb * 16 + g) * 2);
-                if (mb > -INFINITY) t += __ldcg(ps + (bb * 16 + g) * 2 + 1) * expf(mb - m);
-            }
-            t = warp_sum(t);
-            for (int bb = lane; bb < nb; bb += 32) {
-                const float mb = __ldcg(ps + (bb * 16 + g) * 2);
-                fb[bb * 16 + g] = mb > -INFINITY ? expf(mb - m) / t : 0.f;
-            }
-        }
-        for (int g = 0; g < G; ++g)
+        for (int g = 0; g < G; ++g)                    // requested first: in flight during the combine below
             for (int c = tid; c < n_c; c += SEL_THREADS) z[g * C + c] = __ldcg(zg + g * C + c);
+        for (int g = wid; g < G; g += SEL_WARPS) {     // one warp per query head; a lane holds up to two slices
+            float2 s0 = make_float2(-INFINITY, 0.f), s1 = s0;
+            if (lane < nb) s0 = __ldcg(reinterpret_cast<const float2 *>(ps + (lane * 16 + g) * 2));
+            if (lane + 32 < nb) s1 = __ldcg(reinterpret_cast<const float2 *>(ps + ((lane + 32) * 16 + g) * 2));
+            const float m = warp_max(fmaxf(s0.x, s1.x));
+            const float e0 = s0.x > -INFINITY ? expf(s0.x - m) : 0.f, e1 = s1.x > -INFINITY ? expf(s1.x - m) : 0.f;
+            const float t = warp_sum(e0 * s0.y + e1 * s1.y);
+            if (lane < nb) fb[lane * 16 + g] = e0 / t;
+            if (lane + 32 < nb) fb[(lane + 32) * 16 + g] = e1 / t;
+        }
     }
     __syncthreads();
     stamp(p, h, 3);
@@ -251,7 +267,9 @@ __global__ void __launch_bounds__(SEL_THREADS) score_pick_kernel(const SelectPar
         for (int c = tid; c < C; c += SEL_THREADS) {
             float s = -INFINITY;
             if (c < n_c && ci[c] > 0) {
-                const float *f = fb + (c / per) * 16;
+                int sl = (int)((float)c * inv_per);            // slice of cluster c, without an integer division
+                sl += ((sl + 1) * per <= c) - (sl * per > c);
+                const float *f = fb + sl * 16;
                 s = 0.f;
                 for (int g = 0; g < G; ++g) s += z[g * C + c] * f[g];
             }
@@ -461,14 +479,21 @@ extern "C" int skv_select(const skv_state *st, const void *q, int dtype, int G, 
     ws += ((int64_t)st->heads * (st->C / 32 + 1) * 4 + 255) / 256 * 256;
     p.pstat = reinterpret_cast<float *>(ws);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    auto kern = dtype == SKV_BF16 ? score_pick_kernel<__nv_bfloat16> : score_pick_kernel<float>;
-    static size_t configured[64][2] = {};
+    using Kern = void (*)(const SelectParams);
+    const int gsel = G <= 1 ? 0 : G <= 2 ? 1 : G <= 4 ? 2 : G <= 8 ? 3 : 4;
+    static const Kern table[2][5] = {
+        {score_pick_kernel<__nv_bfloat16, 1>, score_pick_kernel<__nv_bfloat16, 2>, score_pick_kernel<__nv_bfloat16, 4>,
+         score_pick_kernel<__nv_bfloat16, 8>, score_pick_kernel<__nv_bfloat16, 16>},
+        {score_pick_kernel<float, 1>, score_pick_kernel<float, 2>, score_pick_kernel<float, 4>,
+         score_pick_kernel<float, 8>, score_pick_kernel<float, 16>}};
+    Kern kern = table[dtype][gsel];
+    static size_t configured[64][2][5] = {};
     int dev = 0;
     SKV_CUDA_OK(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64) return SKV_E_RANGE;
-    if (smem > 48 * 1024 && configured[dev][dtype] < smem) {
+    if (smem > 48 * 1024 && configured[dev][dtype][gsel] < smem) {
         SKV_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        configured[dev][dtype] = smem;
+        configured[dev][dtype][gsel] = smem;
     }
     int ctas = (2 * device_sm_count() + st->heads - 1) / st->heads;
     ctas = ctas < 1 ? 1 : (ctas > SEL_MAX_CTAS ? SEL_MAX_CTAS : ctas);
