@@ -332,8 +332,12 @@ def gpu_arm(args, wl) -> None:
                                               f"excluded; CPU fit {cfit:.2f}s"}
         print(json.dumps(line), flush=True)
     if world > 1:
+        # The captured decode graph holds NCCL collectives; tearing the communicator down under it can block for
+        # good.  Every rank is done once the barrier returns, so leave without the teardown.
         dist.barrier()
-        dist.destroy_process_group()
+        torch.cuda.synchronize()
+        sys.stdout.flush()
+        os._exit(0)
 
 
 def main() -> None:
