@@ -170,7 +170,7 @@ void skv_debug_select_probe(void *dev_ptr);
  * the positions whose label's bit is set in `selbits` (from skv_select) and attends over them; `cnt`
  * (zeroed by skv_select) receives the rows read per head.  bf16 caches only.  Replaces
  * _compact_dev_kernel + _list_kernel + _merge_kernel (ssa/kernels/graph_kernels.py:144-155,
- * ssa/kernels/labeled_attn.py:202-245, :123-140) in one launch.  label_stride a multiple of 16. */
+ * ssa/kernels/labeled_attn.py:202-245, :123-140) in one launch.  label_stride a multiple of 8. */
 int skv_attend_labels(const void *q, const void *K, const void *V, const int16_t *labels, int64_t label_stride,
                       const uint32_t *selbits, int C, const int32_t *n_dev, void *out, void *workspace,
                       int32_t *cnt, int32_t *status, int heads, int G, int d, int dtype,

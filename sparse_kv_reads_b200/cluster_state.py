@@ -378,8 +378,8 @@ class SphereIndexGraph:
         return self.out
 
     def _fused_rows(self, K: torch.Tensor) -> bool:
-        """Whether the list-free attention applies: bf16 cache and labels laid out in 32-byte groups."""
-        return K.dtype == torch.bfloat16 and self.capacity % 16 == 0
+        """Whether the list-free attention applies (bf16 caches)."""
+        return K.dtype == torch.bfloat16
 
     def attend(self, q: torch.Tensor, K: torch.Tensor, V: torch.Tensor, *, n: int, budget: float,
                group: str = "sum_share"):

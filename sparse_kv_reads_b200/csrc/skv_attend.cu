@@ -175,7 +175,7 @@ __global__ void __launch_bounds__(WARPS * 32) attend_mma_kernel(const AttendPara
 // lists the selected ones of 2,048 positions at a time in shared memory (ascending), and attends over
 // them.  No global row list is written or read; cnt_out receives the number of rows read.
 // ---------------------------------------------------------------------------------------------
-constexpr int LAB_SUB = 2048;              // positions listed per pass (16 per thread)
+constexpr int LAB_SUB = 4096;              // positions listed per pass (32 per thread)
 
 template <int WARPS, int STAGES, bool HI>
 __global__ void __launch_bounds__(WARPS * 32) attend_labels_kernel(const AttendParams p) {
@@ -184,13 +184,13 @@ __global__ void __launch_bounds__(WARPS * 32) attend_labels_kernel(const AttendP
     __shared__ uint32_t s_vmask[WARPS][STAGES];
     __shared__ int s_flag;
     __shared__ int s_scan[40];
-    __shared__ int s_rows[LAB_SUB];
+    __shared__ uint16_t s_rows[LAB_SUB];   // offsets from the pass start, ascending
     const int warp = threadIdx.x >> 5, tid = threadIdx.x;
     const int head = blockIdx.y, split = blockIdx.x;
     const int G = p.G, C = p.C;
     const int n = min(max(p.n_dev[0], 0), (int)p.lab_stride);
-    // position ranges: multiples of 16 so that a thread's 16 labels are two aligned 16-byte loads
-    const int chunk = max(16, (((n + p.splits - 1) / p.splits + 15) >> 4) << 4);
+    // position ranges: multiples of 32 so that a thread's 32 labels are four aligned 16-byte loads
+    const int chunk = max(32, (((n + p.splits - 1) / p.splits + 31) >> 5) << 5);
     const int s_eff = max(1, (n + chunk - 1) / chunk);
     if (split >= s_eff) return;
     const int p0 = split * chunk, p1 = min(p0 + chunk, n);
@@ -198,11 +198,11 @@ __global__ void __launch_bounds__(WARPS * 32) attend_labels_kernel(const AttendP
     const int16_t *lab = p.labels + (int64_t)head * p.lab_stride;
     // the first pass's labels are requested before anything else so that their latency overlaps the
     // loads of the selection bits and of the query
-    uint4 raw[2];
-    raw[0] = raw[1] = make_uint4(0u, 0u, 0u, 0u);
-    if (p0 + tid * 16 < p1) {
-        raw[0] = __ldg(reinterpret_cast<const uint4 *>(lab + p0 + tid * 16));
-        raw[1] = __ldg(reinterpret_cast<const uint4 *>(lab + p0 + tid * 16 + 8));
+    uint4 raw[4];
+#pragma unroll
+    for (int v = 0; v < 4; ++v) {
+        raw[v] = make_uint4(0u, 0u, 0u, 0u);
+        if (p0 + tid * 32 + v * 8 < p1) raw[v] = __ldg(reinterpret_cast<const uint4 *>(lab + p0 + tid * 32 + v * 8));
     }
     for (int i = tid; i < p.sel_words; i += WARPS * 32) s_bits[i] = p.selbits[(int64_t)head * p.sel_words + i];
     WarpAttend<STAGES, HI> wa;
@@ -213,12 +213,12 @@ __global__ void __launch_bounds__(WARPS * 32) attend_labels_kernel(const AttendP
     bool bad = false;
     __syncthreads();
     for (int sub0 = p0; sub0 < p1; sub0 += LAB_SUB) {
-        const int base = sub0 + tid * 16;
+        const int base = sub0 + tid * 32;
         uint32_t take = 0;
         if (base < p1) {
             const int16_t *l16 = reinterpret_cast<const int16_t *>(raw);
 #pragma unroll
-            for (int i = 0; i < 16; ++i) {
+            for (int i = 0; i < 32; ++i) {
                 const unsigned l = (unsigned)(int)l16[i];
                 if (base + i < p1) {
                     if (l <= (unsigned)C) take |= ((s_bits[l >> 5] >> (l & 31)) & 1u) << i;
@@ -226,23 +226,23 @@ __global__ void __launch_bounds__(WARPS * 32) attend_labels_kernel(const AttendP
                 }
             }
         }
-        if (base + LAB_SUB < p1) {                       // next pass's labels, in flight during this pass's attention
-            raw[0] = __ldg(reinterpret_cast<const uint4 *>(lab + base + LAB_SUB));
-            raw[1] = __ldg(reinterpret_cast<const uint4 *>(lab + base + LAB_SUB + 8));
-        }
+#pragma unroll
+        for (int v = 0; v < 4; ++v)                      // next pass's labels, in flight during this pass's attention
+            if (base + LAB_SUB + v * 8 < p1)
+                raw[v] = __ldg(reinterpret_cast<const uint4 *>(lab + base + LAB_SUB + v * 8));
         int total;
         int off = block_excl_scan(__popc(take), s_scan, total);
         while (take) {
             const int i = __ffs(take) - 1;
             take &= take - 1;
-            s_rows[off++] = base + i;
+            s_rows[off++] = (uint16_t)(tid * 32 + i);
         }
         __syncthreads();
         read_rows += total;
         const int tiles = (total + TILE_ROWS - 1) / TILE_ROWS;
         const int per = (tiles + WARPS - 1) / WARPS;
         const int t0 = min(warp * per, tiles), t1 = min(t0 + per, tiles);
-        wa.run(t0, t1, [&](int row) { return row < total ? s_rows[row] : -1; });
+        wa.run(t0, t1, [&](int row) { return row < total ? sub0 + (int)s_rows[row] : -1; });
         __syncthreads();                   // the list is rewritten by the next pass
     }
     if (tid == 0 && p.cnt_out) atomicAdd(p.cnt_out + head, read_rows);
@@ -454,7 +454,7 @@ extern "C" int skv_attend_labels(const void *q, const void *K, const void *V, co
     if (G < 1 || G > 16 || C < 16 || (C & (C - 1)) || C > 16384) return SKV_E_DIM;
     if (heads <= 0 || heads > 65535 || splits <= 0 || splits > 65535 || label_stride <= 0) return SKV_E_RANGE;
     if (!aligned16(q) || !aligned16(K) || !aligned16(V) || !aligned16(out) || !aligned16(workspace) ||
-        !aligned16(labels) || label_stride % 16)
+        !aligned16(labels) || label_stride % 8)
         return SKV_E_ALIGN;
     if ((k_row_stride * 2) % 16 || (v_row_stride * 2) % 16 || (k_head_stride * 2) % 16 || (v_head_stride * 2) % 16 ||
         k_row_stride < d || v_row_stride < d)

@@ -495,8 +495,9 @@ extern "C" int skv_select(const skv_state *st, const void *q, int dtype, int G, 
         SKV_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         configured[dev][dtype][gsel] = smem;
     }
+    // enough CTAs per head to fill the GPU when heads are few; at least eight so that a slice stays a few passes
     int ctas = (2 * device_sm_count() + st->heads - 1) / st->heads;
-    ctas = ctas < 1 ? 1 : (ctas > SEL_MAX_CTAS ? SEL_MAX_CTAS : ctas);
+    ctas = ctas < 8 ? 8 : (ctas > SEL_MAX_CTAS ? SEL_MAX_CTAS : ctas);
     if (shared_in) ctas = 1;
     kern<<<dim3(ctas, st->heads), SEL_THREADS, smem, s>>>(p);
     if (idx) list_kernel<<<st->heads, 512, (st->C / 32 + 1) * 4, s>>>(p);

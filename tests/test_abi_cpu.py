@@ -88,11 +88,11 @@ def test_state_calls_reject_bad_arguments(L):
     bad = fake_state(bits=8)
     bad.dir8 = None
     assert sel(bad) == -1 and sel(st, ws=None) == -1
-    assert L.skv_select_workspace_bytes(8, 2, 2048) == 8 * 2 * 2048 * 4 + 256 + 2304
+    assert L.skv_select_workspace_bytes(8, 2, 2048) == 8 * 2 * 2048 * 4 + 256 + 2304 + 8 * 64 * 32 * 4
     assert L.skv_select_workspace_bytes(8, 2, 100) == -5
     lab = lambda **o: L.skv_attend_labels(ok, ok, ok, ok, o.get("ls", 64), ok, o.get("C", 64), ok, ok, ok, None, None, 2,
                                           o.get("G", 2), 128, o.get("dtype", 0), 128 * 64, 128, 128 * 64, 128, 4, 0.1, None)
-    assert lab(ls=40) == -4 and lab(C=48) == -2 and lab(dtype=1) == -3 and lab(G=17) == -2
+    assert lab(ls=36) == -4 and lab(C=48) == -2 and lab(dtype=1) == -3 and lab(G=17) == -2
     ins = lambda s, **o: L.skv_insert(ctypes.byref(s), ok, o.get("hpl", 2), 0, 128 * 64, o.get("ksr", 128), ok, 64, 0.2,
                                       0.03, 0, o.get("mm", 66), None)
     assert ins(st, hpl=3) == -5 and ins(st, mm=1) == -5 and ins(st, mm=10 ** 6) == -5 and ins(st, ksr=120) == -4
