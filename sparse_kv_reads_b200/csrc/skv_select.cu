@@ -116,12 +116,26 @@ __global__ void __launch_bounds__(SEL_THREADS) score_pick_kernel(const SelectPar
         const TQ *q = static_cast<const TQ *>(p.q) + (int64_t)h * G * d;
         const bool q8 = p.st.summary_bits == 8;
         const int part = lane & 7, grp = lane >> 3;
-        // first pass's summaries are requested before the query is staged: two latencies overlap
-        int4 raw0 = make_int4(0, 0, 0, 0);
+        // The CTA takes 128 clusters per iteration, a warp 16 of them (8 lanes, one 16-byte load each, per
+        // cluster): all loads of an iteration are requested before the query is staged, so the two latencies overlap and enough
+        // bytes are in flight to stream the summaries at memory speed.
+        int4 raw[4];
+        float rawc[4], rawx[4], rawn[4];
         float4 rawf = make_float4(0.f, 0.f, 0.f, 0.f);
+        auto fetch8 = [&](int c0) {
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const int c = c0 + (k * SEL_WARPS + wid) * 4 + grp;
+                raw[k] = make_int4(0, 0, 0, 0);
+                rawc[k] = rawx[k] = rawn[k] = 0.f;
+                if (c < c_hi) {
+                    raw[k] = __ldg(reinterpret_cast<const int4 *>(p.st.dir8 + ((int64_t)h * C + c) * d + part * 16));
+                    rawc[k] = count[c]; rawx[k] = mmax[c]; rawn[k] = mmin[c];
+                }
+            }
+        };
         if (q8) {
-            const int c = c_lo + wid * 4 + grp;
-            if (c < c_hi) raw0 = __ldg(reinterpret_cast<const int4 *>(p.st.dir8 + ((int64_t)h * C + c) * d + part * 16));
+            fetch8(c_lo);
         } else {
             const int c = c_lo + wid;
             if (c < c_hi) rawf = __ldg(reinterpret_cast<const float4 *>(p.st.sum_dir + ((int64_t)h * C + c) * d + lane * 4));
@@ -129,46 +143,45 @@ __global__ void __launch_bounds__(SEL_THREADS) score_pick_kernel(const SelectPar
         for (int i = tid; i < G * d; i += SEL_THREADS) sq[i] = load_as_float(q + i);
         __syncthreads();
         if (q8) {
-            const int8_t *dir8 = p.st.dir8 + (int64_t)h * C * d;
-            for (int c0 = c_lo + wid * 4; c0 < c_hi; c0 += SEL_WARPS * 4) {
-                const int c = c0 + grp;
-                const bool live = c < c_hi;
-                const int4 raw = raw0;
-                const int cn_ = c0 + SEL_WARPS * 4 + grp;             // next pass, in flight during this one
-                if (cn_ < c_hi) raw0 = __ldg(reinterpret_cast<const int4 *>(dir8 + (int64_t)cn_ * d + part * 16));
-                float cn = 0.f, mx = 0.f, mn = 0.f;
-                if (live) { cn = count[c]; mx = mmax[c]; mn = mmin[c]; }
-                float v[16];
-                const int8_t *bb = reinterpret_cast<const int8_t *>(&raw);
+            for (int c0 = c_lo; c0 < c_hi; c0 += SEL_WARPS * 16) {
+                if (c0 != c_lo) fetch8(c0);
 #pragma unroll
-                for (int i = 0; i < 16; ++i) v[i] = live ? (float)bb[i] : 0.f;
-                float n2 = 0.f;
+                for (int k = 0; k < 4; ++k) {
+                    const int c = c0 + (k * SEL_WARPS + wid) * 4 + grp;
+                    const bool live = c < c_hi;
+                    const float cn = rawc[k], mx = rawx[k], mn = rawn[k];
+                    float v[16];
+                    const int8_t *bb = reinterpret_cast<const int8_t *>(&raw[k]);
 #pragma unroll
-                for (int i = 0; i < 16; ++i) n2 = fmaf(v[i], v[i], n2);
-                n2 += __shfl_xor_sync(0xffffffffu, n2, 1);
-                n2 += __shfl_xor_sync(0xffffffffu, n2, 2);
-                n2 += __shfl_xor_sync(0xffffffffu, n2, 4);
-                const float inv = 1.0f / fmaxf(sqrtf(n2), 1e-12f);
-                for (int g = 0; g < G; ++g) {
-                    const float4 *qs = reinterpret_cast<const float4 *>(sq + g * d + part * 16);
-                    float dot = 0.f;
+                    for (int i = 0; i < 16; ++i) v[i] = (float)bb[i];
+                    float n2 = 0.f;
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        const float4 t = qs[i];
-                        dot = fmaf(v[4 * i], t.x, dot);
-                        dot = fmaf(v[4 * i + 1], t.y, dot);
-                        dot = fmaf(v[4 * i + 2], t.z, dot);
-                        dot = fmaf(v[4 * i + 3], t.w, dot);
-                    }
-                    dot += __shfl_xor_sync(0xffffffffu, dot, 1);
-                    dot += __shfl_xor_sync(0xffffffffu, dot, 2);
-                    dot += __shfl_xor_sync(0xffffffffu, dot, 4);
-                    if (part == 0 && live) {
-                        const float pr = dot * inv;
-                        float e = pr >= 0.f ? mx * pr : mn * pr;
-                        if (cn == 0.f) e = -INFINITY;
-                        z[g * C + (c - c_lo)] = e * p.scale;
-                        if (p.e_out) p.e_out[((int64_t)h * G + g) * C + c] = e;
+                    for (int i = 0; i < 16; ++i) n2 = fmaf(v[i], v[i], n2);
+                    n2 += __shfl_xor_sync(0xffffffffu, n2, 1);
+                    n2 += __shfl_xor_sync(0xffffffffu, n2, 2);
+                    n2 += __shfl_xor_sync(0xffffffffu, n2, 4);
+                    const float inv = 1.0f / fmaxf(sqrtf(n2), 1e-12f);
+                    for (int g = 0; g < G; ++g) {
+                        const float4 *qs = reinterpret_cast<const float4 *>(sq + g * d + part * 16);
+                        float dot = 0.f;
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const float4 t = qs[i];
+                            dot = fmaf(v[4 * i], t.x, dot);
+                            dot = fmaf(v[4 * i + 1], t.y, dot);
+                            dot = fmaf(v[4 * i + 2], t.z, dot);
+                            dot = fmaf(v[4 * i + 3], t.w, dot);
+                        }
+                        dot += __shfl_xor_sync(0xffffffffu, dot, 1);
+                        dot += __shfl_xor_sync(0xffffffffu, dot, 2);
+                        dot += __shfl_xor_sync(0xffffffffu, dot, 4);
+                        if (part == 0 && live) {
+                            const float pr = dot * inv;
+                            float e = pr >= 0.f ? mx * pr : mn * pr;
+                            if (cn == 0.f) e = -INFINITY;
+                            z[g * C + (c - c_lo)] = e * p.scale;
+                            if (p.e_out) p.e_out[((int64_t)h * G + g) * C + c] = e;
+                        }
                     }
                 }
             }
