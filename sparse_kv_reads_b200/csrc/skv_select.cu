@@ -6,6 +6,8 @@
 // the threshold key t with  sum(count | key > t) < need  by four 8-bit radix passes over
 // order-preserving integer keys, then settles exact ties in slot order, which reproduces "take
 // clusters in decreasing score, lower slot first among equals, until the counts reach need".
+#include <cuda_fp16.h>
+
 #include "skv_common.cuh"
 
 namespace skv {
@@ -73,6 +75,29 @@ __device__ __forceinline__ void block_reduce_vec(float (&v)[NV], float *red /* [
     __syncthreads();
 }
 
+// ---- tensor-core scoring of 8-bit summaries against a bf16 query -------------------------------------
+// scores[g][c] = q_g . dir8_c for 8 clusters per warp as one m16n8k16 chain (k = 128): the query heads sit
+// on the M side (zero rows beyond G), the int8 directions are widened to fp16 in registers (exact), the
+// bf16 query is exact in fp16 too, accumulation is fp32.  The k index is permuted the same way on both
+// operands so that lane (n, j) reads bytes [32j, 32j+32) of cluster n with two 16-byte loads.
+__device__ __forceinline__ void mma_f16_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+// two int8 (bytes `lo`, `lo`+1 of w, already biased by +128) -> packed fp16 pair holding their signed values
+__device__ __forceinline__ uint32_t bytes_to_half2(uint32_t biased, uint32_t selector) {
+    uint32_t h;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(h) : "r"(biased), "r"(0x64646464u), "r"(selector));   // 1024 + u
+    const __half2 v = __hsub2(*reinterpret_cast<__half2 *>(&h), __half2half2(__ushort_as_half((unsigned short)0x6480)));
+    return *reinterpret_cast<const uint32_t *>(&v);
+}
+__device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
+    const __half2 v = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t *>(&v);
+}
+
 // Grid (ctas, heads).  Every CTA scores a slice of the head's clusters: e = (longest or shortest key) x
 // projection of the query on the cluster's mean direction, scaled by 1/sqrt(d); it then leaves
 // exp(z - slice max) in zbuf and its (max, sum) per query head in pstat.  The last CTA of the head to
@@ -134,7 +159,24 @@ __global__ void __launch_bounds__(SEL_THREADS) score_pick_kernel(const SelectPar
                 }
             }
         };
-        if (q8) {
+        constexpr bool TC = sizeof(TQ) == 2;               // bf16 query: tensor-core scoring of 8-bit summaries
+        int4 rawa[4], rawb[4];                            // TC path: bytes [32j, 32j+32) of this lane's clusters
+        const int nrow = lane >> 2, jq = lane & 3;
+        auto fetch_tc = [&](int c0) {
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const int c = c0 + (k * SEL_WARPS + wid) * 8 + nrow;
+                rawa[k] = rawb[k] = make_int4(0, 0, 0, 0);
+                if (c < c_hi) {
+                    const int4 *src = reinterpret_cast<const int4 *>(p.st.dir8 + ((int64_t)h * C + c) * d + jq * 32);
+                    rawa[k] = __ldg(src);
+                    rawb[k] = __ldg(src + 1);
+                }
+            }
+        };
+        if (q8 && TC) {
+            fetch_tc(c_lo);
+        } else if (q8) {
             fetch8(c_lo);
         } else {
             const int c = c_lo + wid;
@@ -142,7 +184,62 @@ __global__ void __launch_bounds__(SEL_THREADS) score_pick_kernel(const SelectPar
         }
         for (int i = tid; i < G * d; i += SEL_THREADS) sq[i] = load_as_float(q + i);
         __syncthreads();
-        if (q8) {
+        if (q8 && TC) {
+            // query fragments (A): rows = query heads, k permuted as described above
+            uint32_t qa[8][4];
+            const int g0 = nrow, g1 = nrow + 8;
+#pragma unroll
+            for (int ks = 0; ks < 8; ++ks) {
+                const float *q0 = sq + g0 * d + 32 * jq + 4 * ks, *q1 = sq + g1 * d + 32 * jq + 4 * ks;
+                qa[ks][0] = g0 < G ? pack_half2(q0[0], q0[1]) : 0u;
+                qa[ks][2] = g0 < G ? pack_half2(q0[2], q0[3]) : 0u;
+                qa[ks][1] = (GP > 8 && g1 < G) ? pack_half2(q1[0], q1[1]) : 0u;
+                qa[ks][3] = (GP > 8 && g1 < G) ? pack_half2(q1[2], q1[3]) : 0u;
+            }
+            for (int c0 = c_lo; c0 < c_hi; c0 += SEL_WARPS * 32) {
+                if (c0 != c_lo) fetch_tc(c0);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const int cbase = c0 + (k * SEL_WARPS + wid) * 8;
+                    if (cbase >= c_hi) continue;                        // warp-uniform
+                    const uint32_t w[8] = {(uint32_t)rawa[k].x, (uint32_t)rawa[k].y, (uint32_t)rawa[k].z,
+                                           (uint32_t)rawa[k].w, (uint32_t)rawb[k].x, (uint32_t)rawb[k].y,
+                                           (uint32_t)rawb[k].z, (uint32_t)rawb[k].w};
+                    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+                    int n2i = 0;
+#pragma unroll
+                    for (int ks = 0; ks < 8; ++ks) {
+                        n2i = __dp4a((int)w[ks], (int)w[ks], n2i);
+                        const uint32_t biased = w[ks] ^ 0x80808080u;
+                        mma_f16_16816(acc, qa[ks], bytes_to_half2(biased, 0x4140u), bytes_to_half2(biased, 0x4342u));
+                    }
+                    n2i += __shfl_xor_sync(0xffffffffu, n2i, 1);
+                    n2i += __shfl_xor_sync(0xffffffffu, n2i, 2);            // |dir8|^2 of cluster cbase + nrow
+                    // lane (g, j) holds the dots of clusters cbase + 2j, 2j + 1: fetch their norms
+                    const int na = __shfl_sync(0xffffffffu, n2i, (2 * jq) * 4);
+                    const int nb2 = __shfl_sync(0xffffffffu, n2i, (2 * jq + 1) * 4);
+#pragma unroll
+                    for (int i = 0; i < 2; ++i) {
+                        const int c = cbase + 2 * jq + i;
+                        if (c < c_hi) {
+                            const float inv = 1.0f / fmaxf(sqrtf((float)(i ? nb2 : na)), 1e-12f);
+                            const float cn = count[c], mx = mmax[c], mn = mmin[c];
+#pragma unroll
+                            for (int r = 0; r < (GP > 8 ? 2 : 1); ++r) {
+                                const int g = nrow + 8 * r;
+                                if (g < G) {
+                                    const float pr = acc[2 * r + i] * inv;
+                                    float e = pr >= 0.f ? mx * pr : mn * pr;
+                                    if (cn == 0.f) e = -INFINITY;
+                                    z[g * C + (c - c_lo)] = e * p.scale;
+                                    if (p.e_out) p.e_out[((int64_t)h * G + g) * C + c] = e;
+                                }
+                            }
+                        }
+                    }
+                }
+            }
+        } else if (q8) {
             for (int c0 = c_lo; c0 < c_hi; c0 += SEL_WARPS * 16) {
                 if (c0 != c_lo) fetch8(c0);
 #pragma unroll

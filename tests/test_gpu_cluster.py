@@ -47,9 +47,10 @@ def test_pick_is_bit_exact_given_the_oracle_scores(budget, bits):
             assert torch.equal(w.cpu()[:, :st.C] > 0, st.count > 0)
 
 
+@pytest.mark.parametrize("qdtype", [torch.float32, torch.bfloat16])     # bf16 queries + 8-bit summaries: tensor cores
 @pytest.mark.parametrize("bits", [32, 8])
-@pytest.mark.parametrize("G", [1, 2, 4, 8])
-def test_scores_and_full_selection_match_the_oracle(bits, G):
+@pytest.mark.parametrize("G", [1, 2, 4, 8, 16])
+def test_scores_and_full_selection_match_the_oracle(bits, G, qdtype):
     st, Q, K, V = fitted_oracle(h=4, H=4 * G, summary_bits=bits, seed=3)
     ix = device_index_from_oracle(st)
     n = st.n
@@ -60,7 +61,7 @@ def test_scores_and_full_selection_match_the_oracle(bits, G):
         q = Q[t].float()
         e = st.scores(q)
         _, w_ref = st.select(q, n=n, budget=0.2)
-        _, w = ix.labels_and_weights(q.to(DEV), n=n, budget=0.2, shared_out=s_out, e_out=e_out)
+        _, w = ix.labels_and_weights(Q[t].to(qdtype).to(DEV), n=n, budget=0.2, shared_out=s_out, e_out=e_out)
         live = (st.count > 0).unsqueeze(1).expand_as(e)
         got = e_out.cpu()
         assert torch.isinf(got[~live]).all() and (got[~live] < 0).all()
