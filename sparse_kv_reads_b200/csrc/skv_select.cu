@@ -321,7 +321,8 @@ __global__ void __launch_bounds__(SEL_THREADS) score_pick_kernel(const SelectPar
                 for (int c = tid; c < mine; c += SEL_THREADS) {
                     const float zz = z[g * C + c];
                     const float ex = zz > -INFINITY ? expf(zz - zm[g]) : 0.f;
-                    __stcg(zg + g * C + c_lo + c, ex);
+                    if (nb > 1) __stcg(zg + g * C + c_lo + c, ex);
+                    else z[g * C + c] = ex;                 // a lone CTA keeps the values where the pick reads them
                     s += ex;
                 }
             tot[g] = s;
@@ -358,8 +359,9 @@ __global__ void __launch_bounds__(SEL_THREADS) score_pick_kernel(const SelectPar
     }
     if (scoring) {
         // slice factors exp(max_b - max) / total per query head
-        for (int g = 0; g < G; ++g)                    // requested first: in flight during the combine below
-            for (int c = tid; c < n_c; c += SEL_THREADS) z[g * C + c] = __ldcg(zg + g * C + c);
+        if (nb > 1)
+            for (int g = 0; g < G; ++g)                // requested first: in flight during the combine below
+                for (int c = tid; c < n_c; c += SEL_THREADS) z[g * C + c] = __ldcg(zg + g * C + c);
         for (int g = wid; g < G; g += SEL_WARPS) {     // one warp per query head; a lane holds up to two slices
             float2 s0 = make_float2(-INFINITY, 0.f), s1 = s0;
             if (lane < nb) s0 = __ldcg(reinterpret_cast<const float2 *>(ps + (lane * 16 + g) * 2));
@@ -605,9 +607,10 @@ extern "C" int skv_select(const skv_state *st, const void *q, int dtype, int G, 
         SKV_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         configured[dev][dtype][gsel] = smem;
     }
-    // enough CTAs per head to fill the GPU when heads are few; at least eight so that a slice stays a few passes
-    int ctas = (2 * device_sm_count() + st->heads - 1) / st->heads;
-    ctas = ctas < 8 ? 8 : (ctas > SEL_MAX_CTAS ? SEL_MAX_CTAS : ctas);
+    // As many CTAs per head as fit ONE wave of two CTAs per SM: a CTA's cost is mostly a fixed chain of
+    // latencies, so a second wave costs more than longer slices do.  Many heads: one CTA per head.
+    int ctas = 2 * device_sm_count() / st->heads;
+    ctas = ctas < 1 ? 1 : (ctas > SEL_MAX_CTAS ? SEL_MAX_CTAS : ctas);
     if (shared_in) ctas = 1;
     kern<<<dim3(ctas, st->heads), SEL_THREADS, smem, s>>>(p);
     if (idx) list_kernel<<<st->heads, 512, (st->C / 32 + 1) * 4, s>>>(p);

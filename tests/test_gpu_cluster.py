@@ -58,7 +58,7 @@ def test_scores_and_full_selection_match_the_oracle(bits, G, qdtype):
     s_out = torch.full((st.h, st.C), float("nan"), device=DEV)
     diff = 0
     for t in (1401, 1480):
-        q = Q[t].float()
+        q = Q[t].to(qdtype).float()                       # the oracle sees the query as the kernel does
         e = st.scores(q)
         _, w_ref = st.select(q, n=n, budget=0.2)
         _, w = ix.labels_and_weights(Q[t].to(qdtype).to(DEV), n=n, budget=0.2, shared_out=s_out, e_out=e_out)
