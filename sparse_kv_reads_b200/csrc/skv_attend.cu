@@ -148,7 +148,7 @@ __device__ __forceinline__ void finish_head(const AttendParams &p, const float *
 // bf16 tensor-core path over a list of rows
 // ---------------------------------------------------------------------------------------------
 template <int WARPS, int STAGES, bool HI>
-__global__ void __launch_bounds__(WARPS * 32) attend_mma_kernel(const AttendParams p) {
+__global__ void __launch_bounds__(WARPS * 32, 3) attend_mma_kernel(const AttendParams p) {
     static_assert(WARPS == 4, "finish_head expects 128 threads");
     extern __shared__ __align__(128) unsigned char smem[];
     __shared__ uint32_t s_vmask[WARPS][STAGES];
@@ -175,10 +175,10 @@ __global__ void __launch_bounds__(WARPS * 32) attend_mma_kernel(const AttendPara
 // lists the selected ones of 2,048 positions at a time in shared memory (ascending), and attends over
 // them.  No global row list is written or read; cnt_out receives the number of rows read.
 // ---------------------------------------------------------------------------------------------
-constexpr int LAB_SUB = 4096;              // positions listed per pass (32 per thread)
+constexpr int LAB_SUB = 2048;              // positions listed per pass (16 per thread)
 
 template <int WARPS, int STAGES, bool HI>
-__global__ void __launch_bounds__(WARPS * 32) attend_labels_kernel(const AttendParams p) {
+__global__ void __launch_bounds__(WARPS * 32, 3) attend_labels_kernel(const AttendParams p) {
     static_assert(WARPS == 4, "finish_head expects 128 threads");
     extern __shared__ __align__(128) unsigned char smem[];
     __shared__ uint32_t s_vmask[WARPS][STAGES];
@@ -189,8 +189,8 @@ __global__ void __launch_bounds__(WARPS * 32) attend_labels_kernel(const AttendP
     const int head = blockIdx.y, split = blockIdx.x;
     const int G = p.G, C = p.C;
     const int n = min(max(p.n_dev[0], 0), (int)p.lab_stride);
-    // position ranges: multiples of 32 so that a thread's 32 labels are four aligned 16-byte loads
-    const int chunk = max(32, (((n + p.splits - 1) / p.splits + 31) >> 5) << 5);
+    // position ranges: multiples of 16 so that a thread's 16 labels are two aligned 16-byte loads
+    const int chunk = max(16, (((n + p.splits - 1) / p.splits + 15) >> 4) << 4);
     const int s_eff = max(1, (n + chunk - 1) / chunk);
     if (split >= s_eff) return;
     const int p0 = split * chunk, p1 = min(p0 + chunk, n);
@@ -198,11 +198,11 @@ __global__ void __launch_bounds__(WARPS * 32) attend_labels_kernel(const AttendP
     const int16_t *lab = p.labels + (int64_t)head * p.lab_stride;
     // the first pass's labels are requested before anything else so that their latency overlaps the
     // loads of the selection bits and of the query
-    uint4 raw[4];
+    uint4 raw[2];
 #pragma unroll
-    for (int v = 0; v < 4; ++v) {
+    for (int v = 0; v < 2; ++v) {
         raw[v] = make_uint4(0u, 0u, 0u, 0u);
-        if (p0 + tid * 32 + v * 8 < p1) raw[v] = __ldg(reinterpret_cast<const uint4 *>(lab + p0 + tid * 32 + v * 8));
+        if (p0 + tid * 16 + v * 8 < p1) raw[v] = __ldg(reinterpret_cast<const uint4 *>(lab + p0 + tid * 16 + v * 8));
     }
     for (int i = tid; i < p.sel_words; i += WARPS * 32) s_bits[i] = p.selbits[(int64_t)head * p.sel_words + i];
     WarpAttend<STAGES, HI> wa;
@@ -213,12 +213,12 @@ __global__ void __launch_bounds__(WARPS * 32) attend_labels_kernel(const AttendP
     bool bad = false;
     __syncthreads();
     for (int sub0 = p0; sub0 < p1; sub0 += LAB_SUB) {
-        const int base = sub0 + tid * 32;
+        const int base = sub0 + tid * 16;
         uint32_t take = 0;
         if (base < p1) {
             const int16_t *l16 = reinterpret_cast<const int16_t *>(raw);
 #pragma unroll
-            for (int i = 0; i < 32; ++i) {
+            for (int i = 0; i < 16; ++i) {
                 const unsigned l = (unsigned)(int)l16[i];
                 if (base + i < p1) {
                     if (l <= (unsigned)C) take |= ((s_bits[l >> 5] >> (l & 31)) & 1u) << i;
@@ -227,7 +227,7 @@ __global__ void __launch_bounds__(WARPS * 32) attend_labels_kernel(const AttendP
             }
         }
 #pragma unroll
-        for (int v = 0; v < 4; ++v)                      // next pass's labels, in flight during this pass's attention
+        for (int v = 0; v < 2; ++v)                      // next pass's labels, in flight during this pass's attention
             if (base + LAB_SUB + v * 8 < p1)
                 raw[v] = __ldg(reinterpret_cast<const uint4 *>(lab + base + LAB_SUB + v * 8));
         int total;
@@ -235,7 +235,7 @@ __global__ void __launch_bounds__(WARPS * 32) attend_labels_kernel(const AttendP
         while (take) {
             const int i = __ffs(take) - 1;
             take &= take - 1;
-            s_rows[off++] = (uint16_t)(tid * 32 + i);
+            s_rows[off++] = (uint16_t)(tid * 16 + i);
         }
         __syncthreads();
         read_rows += total;
@@ -339,7 +339,7 @@ __global__ void merge_kernel(const float *m, const float *l, const float *a, flo
     }
 }
 
-constexpr int MMA_WARPS = 4, MMA_STAGES = 3;
+constexpr int MMA_WARPS = 4, MMA_STAGES = 2;   // 64 KB of rings per CTA: three CTAs (12 warps) per SM
 constexpr int MMA_SMEM = MMA_WARPS * MMA_STAGES * 8192;
 
 template <bool HI>
@@ -391,11 +391,12 @@ using namespace skv;
 
 extern "C" int skv_attend_splits(int heads) {
     if (heads <= 0) return SKV_E_RANGE;
-    // Two CTAs fit an SM.  Few heads: one wave, as many CTAs per head as fill it.  Many heads: about four
-    // waves, so that the last, partly filled wave costs little.
-    const int wave = 2 * device_sm_count();
-    const int waves = heads * 4 > wave ? 4 : 1;
-    int s = (wave * waves + heads - 1) / heads;
+    // Three CTAs fit an SM.  Few heads: one wave, as many CTAs per head as fit it (never more CTAs than the
+    // wave, or a nearly empty second wave doubles the time).  Many heads: about four waves, so that the
+    // last, partly filled one costs little.
+    const int wave = 3 * device_sm_count();
+    int s = wave / heads;
+    if (s < 12) s = (4 * wave + heads - 1) / heads;
     return s < 1 ? 1 : s;
 }
 
