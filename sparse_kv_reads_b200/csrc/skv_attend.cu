@@ -391,12 +391,13 @@ using namespace skv;
 
 extern "C" int skv_attend_splits(int heads) {
     if (heads <= 0) return SKV_E_RANGE;
-    // Three CTAs fit an SM.  Few heads: one wave, as many CTAs per head as fit it (never more CTAs than the
-    // wave, or a nearly empty second wave doubles the time).  Many heads: about four waves, so that the
-    // last, partly filled one costs little.
-    const int wave = 3 * device_sm_count();
-    int s = wave / heads;
-    if (s < 12) s = (4 * wave + heads - 1) / heads;
+    // One wave of CTAs, never more: a CTA's cost has a large fixed part (prologue, partial merge), so a
+    // second, nearly empty wave costs more than it spreads.  Three CTAs fit an SM; with few heads the
+    // partials to merge are what costs, so two per SM are enough there.  Measured on B200 at 32k / 20 %:
+    // 8 heads 37 splits, 64 heads 6, 256 heads 1 were the fastest of the values tried.
+    const int sms = device_sm_count();
+    int s = 3 * sms / heads;
+    if (s > 8) s = 2 * sms / heads;
     return s < 1 ? 1 : s;
 }
 
