@@ -242,18 +242,6 @@ int skv_qk_rope_cache(const void *qkv, const void *q_norm_w, const void *k_norm_
  * layer.ffn (graph_decode.py:117). */
 int skv_silu_mul(const void *gate_up, void *out, int B, int inter, void *stream);
 
-/* y [B, N] = x [B, K] . W[N, K]^T for up to 8 sequences: bf16 in and out, fp32 accumulation, the weights streamed
- * once at memory speed.  Replaces the module calls a.o(...) and ffn.down(...) of the decode step
- * (ssa/models/graph_decode.py:116-117), which are framework GEMVs in the reference. */
-int skv_gemv(const void *W, const void *x, void *y, int B, int N, int K, void *stream);
-
-/* The same product with the residual add and RMSNorm fused in front: the activation is
- * RMSNorm(h + delta) * norm_w (delta may be null), h + delta is also stored to h_out (a different buffer than h
- * and delta).  gated != 0: W holds 2N rows, gate rows first, and y [B, N] = silu(gate) * up.
- * Replaces norm1 + q/k/v, norm2 + gate/up + activation, final_norm + lm_head (graph_decode.py:100-103,117-119). */
-int skv_norm_gemv(const void *W, const void *h, const void *delta, const void *norm_w, void *h_out, void *y,
-                  int B, int N, int K, float eps, int gated, void *stream);
-
 #ifdef __cplusplus
 }
 #endif

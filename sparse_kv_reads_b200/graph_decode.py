@@ -117,9 +117,6 @@ class GraphDecoder:
             and dev.type == "cuda"
         if self.fused_dense:
             self._fuse_weights()
-        # up to eight sequences: the matrix products are the library's own weight-streaming GEMVs with the
-        # norms and the activation fused in; larger batches keep the framework GEMMs
-        self.fused_gemv = self.fused_dense and B <= 8
         self.fused_insert = fused_insert and mode == "cluster" and window >= 1
         self.insert_all = None
 
@@ -137,8 +134,6 @@ class GraphDecoder:
             self.insert_all = AllLayerInsert(self.attn, [self._heads(k) for k in self.cache.k[:len(self.attn)]])
 
     def _body(self) -> torch.Tensor:
-        if self.fused_gemv:
-            return self._body_gemv()
         if self.fused_dense:
             return self._body_fused()
         m, H, H_kv, d, B = self.model, self.H, self.H_kv, self.d, self.B
@@ -222,63 +217,6 @@ class GraphDecoder:
         check(L.skv_add_rmsnorm(h.data_ptr(), delta.data_ptr(), m.final_norm.weight.data_ptr(), xn.data_ptr(), B,
                                 hidden, eps, st), "skv_add_rmsnorm")
         return m.logits(xn.view(B, 1, hidden))
-
-    def _body_gemv(self) -> torch.Tensor:
-        """Decode step with seven launches per layer: norm + qkv GEMV, QK-norm/rope/cache write, select, attend,
-        o GEMV, norm + gate/up GEMV + activation, down GEMV.  The residual stream alternates between two
-        buffers because every CTA of a fused-norm GEMV reads the old stream while one CTA writes the new one."""
-        m, H, H_kv, d, B = self.model, self.H, self.H_kv, self.d, self.B
-        L = lib()
-        dev = self.tok.device
-        st = stream_ptr(dev)
-        torch.add(self.pos, 1, out=self.n_dev)
-        if self.insert_all is not None:
-            self.insert_all(self.n_dev)
-        h_a = m.embed(self.tok).view(B, -1).contiguous()
-        h_b = torch.empty_like(h_a)
-        hidden = h_a.shape[1]
-        eps = m.final_norm.eps
-        bf = h_a.dtype
-        delta = None
-        nqkv = self._wqkv[0].shape[0]
-        inter = self._wgu[0].shape[0] // 2
-        qkv = torch.empty(B, nqkv, dtype=bf, device=dev)
-        qh = torch.empty(B * H, d, dtype=bf, device=dev)
-        o = torch.empty(B, hidden, dtype=bf, device=dev)
-        act = torch.empty(B, inter, dtype=bf, device=dev)
-        dn = torch.empty(B, hidden, dtype=bf, device=dev)
-        for i, layer in enumerate(m.layers):
-            a, f = layer.attn, layer.ffn
-            check(L.skv_norm_gemv(self._wqkv[i].data_ptr(), h_a.data_ptr(), None if delta is None else delta.data_ptr(),
-                                  layer.norm1.weight.data_ptr(), h_b.data_ptr(), qkv.data_ptr(), B, nqkv, hidden, eps,
-                                  0, st), "skv_norm_gemv")
-            kc, vc = self.cache.k[i], self.cache.v[i]
-            check(L.skv_qk_rope_cache(qkv.data_ptr(), a.q_norm.weight.data_ptr(), a.k_norm.weight.data_ptr(),
-                                      m.rope_cos.data_ptr(), m.rope_sin.data_ptr(), self.pos.data_ptr(),
-                                      qh.data_ptr(), kc.data_ptr(), vc.data_ptr(), B, H, H_kv, d, kc.stride(0),
-                                      kc.stride(1), kc.stride(2), a.q_norm.eps, st), "skv_qk_rope_cache")
-            if self.mode == "dense":
-                out = self.attn[i](qh, self._heads(kc), self._heads(vc), self.n_dev)
-            else:
-                out = self.attn[i].step(qh, self._heads(kc), self._heads(vc), self.n_dev,
-                                        insert=self.insert_all is None)
-            check(L.skv_gemv(a.o.weight.data_ptr(), out.data_ptr(), o.data_ptr(), B, hidden, H * d, st), "skv_gemv")
-            a.tp.all_reduce(o)
-            check(L.skv_norm_gemv(self._wgu[i].data_ptr(), h_b.data_ptr(), o.data_ptr(), layer.norm2.weight.data_ptr(),
-                                  h_a.data_ptr(), act.data_ptr(), B, inter, hidden, eps, 1, st), "skv_norm_gemv")
-            check(L.skv_gemv(f.down.weight.data_ptr(), act.data_ptr(), dn.data_ptr(), B, hidden, inter, st), "skv_gemv")
-            f.tp.all_reduce(dn)
-            delta = dn
-        head = m.embed.weight if m.lm_head is None else m.lm_head.weight
-        logits = torch.empty(B, head.shape[0], dtype=bf, device=dev)
-        check(L.skv_norm_gemv(head.data_ptr(), h_a.data_ptr(), delta.data_ptr(), m.final_norm.weight.data_ptr(),
-                              h_b.data_ptr(), logits.data_ptr(), B, head.shape[0], hidden, eps, 0, st), "skv_norm_gemv")
-        logits = logits.view(B, 1, -1)
-        if m.tp.size > 1:
-            parts = [torch.empty_like(logits) for _ in range(m.tp.size)]
-            torch.distributed.all_gather(parts, logits, group=m.tp.group)
-            logits = torch.cat(parts, dim=-1)
-        return logits
 
     def capture(self) -> None:
         """Record one decode step.  Call after ``prepare`` and before the first ``step``; the warm-up

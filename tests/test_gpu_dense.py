@@ -73,36 +73,3 @@ def test_silu_mul():
     want = torch.nn.functional.silu(gu[:, :inter]) * gu[:, inter:]
     torch.testing.assert_close(out.float(), want.float(), rtol=1e-2, atol=1e-2)
 
-
-@pytest.mark.parametrize("B", [1, 3, 8])
-def test_gemv_and_fused_norm_gemv(B):
-    g = torch.Generator().manual_seed(3)
-    K, N = 1024, 520
-    W = (torch.randn(2 * N, K, generator=g) * 0.05).to(torch.bfloat16).to(DEV)
-    x = torch.randn(B, K, generator=g).to(torch.bfloat16).to(DEV)
-    y = torch.empty(B, N, dtype=torch.bfloat16, device=DEV)
-    check(lib().skv_gemv(W.data_ptr(), x.data_ptr(), y.data_ptr(), B, N, K, stream()), "skv_gemv")
-    torch.testing.assert_close(y.float(), (x.float() @ W[:N].float().T), rtol=2e-2, atol=2e-2)
-    # residual add + norm in front; plain and gated
-    h = torch.randn(B, K, generator=g).to(torch.bfloat16).to(DEV)
-    delta = torch.randn(B, K, generator=g).to(torch.bfloat16).to(DEV)
-    norm = RMSNorm(K, 1e-6).to(DEV).to(torch.bfloat16)
-    norm.weight.data = (1 + 0.1 * torch.randn(K, generator=g)).to(torch.bfloat16).to(DEV)
-    h_new = h + delta
-    xn = norm(h_new)
-    for dl, want_h in ((delta, h_new), (None, h)):
-        xn = norm(want_h)
-        h_out = torch.zeros_like(h)
-        check(lib().skv_norm_gemv(W.data_ptr(), h.data_ptr(), None if dl is None else dl.data_ptr(),
-                                  norm.weight.data_ptr(), h_out.data_ptr(), y.data_ptr(), B, N, K, 1e-6, 0, stream()),
-              "skv_norm_gemv")
-        assert torch.equal(h_out, want_h)
-        torch.testing.assert_close(y.float(), xn.float() @ W[:N].float().T, rtol=2e-2, atol=3e-2)
-    check(lib().skv_norm_gemv(W.data_ptr(), h.data_ptr(), delta.data_ptr(), norm.weight.data_ptr(), h_out.data_ptr(),
-                              y.data_ptr(), B, N, K, 1e-6, 1, stream()), "skv_norm_gemv")
-    xn = norm(h_new)
-    gate, up = torch.nn.functional.linear(xn, W[:N]), torch.nn.functional.linear(xn, W[N:])
-    torch.testing.assert_close(y.float(), (torch.nn.functional.silu(gate) * up).float(), rtol=3e-2, atol=3e-2)
-    assert lib().skv_norm_gemv(W.data_ptr(), h.data_ptr(), None, norm.weight.data_ptr(), h.data_ptr(), y.data_ptr(), B,
-                               N, K, 1e-6, 0, stream()) == -5
-    assert lib().skv_gemv(W.data_ptr(), x.data_ptr(), y.data_ptr(), 9, N, K, stream()) == -5
