@@ -35,6 +35,9 @@ WORKLOADS = {
     "qwen3-0.6b_b1_4k_budget20": ("0.6b", 1, 4096, 0.20, 1024),          # quick check
 }
 DEFAULT = "qwen3-0.6b_b1_32k_budget20"
+# dram__bytes_read.sum + dram__bytes_write.sum of one attention launch from an `ncu --set full` capture of this
+# workload (profiles/attend_labels_kernel_qwen3-0.6b_b1_32k.md); other workloads have no capture yet
+NCU_TRAFFIC = {"qwen3-0.6b_b1_32k_budget20": 27.72e6}
 
 
 def peaks() -> tuple[float, str]:
@@ -172,7 +175,7 @@ def build_decoder(wl, dev, tp_group, tp_size, tp_rank, decode_steps):
     return model, cache, dec, ids, fit_s
 
 
-def kernel_roofline(dec, n_now, peak_gbs, which):
+def kernel_roofline(dec, n_now, peak_gbs, which, traffic=None):
     """Per-launch duration of the attention kernel measured with CUDA events, layer by layer, outside the
     graph (each layer's rows are cold: the layers' caches together are far larger than L2), and of the
     three kernels of a layer step together.  Bytes: K and V rows read plus their 4-byte positions for the
@@ -224,7 +227,7 @@ def kernel_roofline(dec, n_now, peak_gbs, which):
     att_bytes = float((rows * 2 * 256).sum(1).mean()) + rows.shape[1] * (2 * n_now + 4 * (layers[0].C // 32 + 1))
     stp_bytes = float(step_bytes(n=n_now, rows=rows, clusters=n_c, d=d, summary_bits=8).sum(1).mean())
     roof = {"bound": "hbm", "kernel": "attend_labels_kernel", "achieved": att_bytes / att_t / 1e9, "peak": peak_gbs,
-            "unit": "GB/s", "frac": att_bytes / att_t / 1e9 / peak_gbs, "traffic": None, "peak_source": which,
+            "unit": "GB/s", "frac": att_bytes / att_t / 1e9 / peak_gbs, "traffic": traffic, "peak_source": which,
             "us_per_launch": att_t * 1e6, "bytes_per_launch": att_bytes}
     layer = {"kernels": "select + attend (insert runs once for all layers)", "us_per_layer": stp_t * 1e6,
              "bytes_per_layer": stp_bytes, "achieved": stp_bytes / stp_t / 1e9, "unit": "GB/s",
@@ -306,7 +309,7 @@ def gpu_arm(args, wl) -> None:
         status |= ix.check_status()
     if rank == 0:
         peak, which = peaks()
-        roof, layer = kernel_roofline(dec, pos, peak, which)
+        roof, layer = kernel_roofline(dec, pos, peak, which, NCU_TRAFFIC.get(args.workload) if world == 1 else None)
         line = {"metric": "qwen3_decode_tokens_per_s", "value": B * K_steps / (dev_ms * 1e-3), "unit": "tok/s",
                 "n_gpus": world, "steps": K_steps, "warmup": W, "ms_per_step": dev_ms / K_steps,
                 "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
