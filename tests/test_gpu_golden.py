@@ -1,0 +1,93 @@
+"""The CUDA path against the golden vectors of the reference's own classes, and size-independent properties
+at the full benchmark context (32,768 tokens)."""
+
+from __future__ import annotations
+
+import math
+
+import pytest
+import torch
+
+from oracle import cluster_oracle as oc
+from sparse_kv_reads_b200.cluster_state import SphereIndexGraph
+from _helpers import DEV, row_sets
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("case", ["small_cap", "small_fixed", "config1"])
+def test_cuda_stream_against_the_reference_golden_vectors(golden_small, golden_config1, case):
+    g = golden_config1["config1"] if case == "config1" else golden_small[case]
+    c = g["cfg"]
+    n_end = c["n0"] + c["steps"]
+    K, V = oc.clustered_keys(c["h"], n_end, 128, seed=c["seed"])
+    assert abs(float(K.double().sum()) - g["input_sum"]) < 1e-6
+    Q = torch.randn(c["steps"] + 1, c["h"] * c["G"], 128, generator=torch.Generator().manual_seed(c["seed"] + 1000))
+    cap = -(-n_end // 8) * 8
+    ix = SphereIndexGraph(C=c["C"], C_init=c["C_init"], cap_keys=c["cap_keys"], split_factor=c["split_factor"],
+                          window=c["window"], delta=c["delta"], capacity=cap, check_every=c["check_every"], seed=0,
+                          summary_bits=32, async_check=False)
+    Kd, Vd = K.to(DEV), V.to(DEV)
+    ix.observe(Kd, c["n0"])
+    fit = g["fit"]
+    same = (ix.labels.cpu()[:, :c["n0"]] == fit["labels"]).float().mean().item()
+    assert same >= 0.999, same
+    assert int((ix.n_c.cpu() - fit["n_c"]).abs().max()) <= (0 if same == 1.0 else 3)
+    torch.testing.assert_close(ix.mu_ref.cpu(), fit["mu_ref"], rtol=1e-5, atol=1e-5)
+    worst, boundary = 0.0, 0
+    for t in range(c["steps"] + 1):
+        n = c["n0"] + t
+        if t:
+            ix.observe(Kd, n)
+        if t in g["probes"]:
+            p = g["probes"][t]
+            out, labels, w = ix.attend(Q[t].to(DEV), Kd, Vd, n=n, budget=c["budget"])
+            diff = int((w.cpu().to(torch.uint8) != p["w"]).sum(1).max())
+            boundary = max(boundary, diff)
+            if diff == 0:                                   # same selection: the attention must match to fp32 accuracy
+                worst = max(worst, float((out.cpu() - p["out"]).abs().max()))
+            assert int((ix.n_c.cpu() - p["n_c"]).abs().max()) <= 3
+    fin = g["final"]
+    same = (ix.labels.cpu()[:, :n_end] == fin["labels"]).float().mean().item()
+    assert same >= 0.999, same
+    assert boundary <= 2 and worst <= 1e-5, (boundary, worst)
+    assert abs(ix.splits - fin["splits"]) <= max(2, 0.02 * fin["splits"])
+    assert ix.check_status() == 0
+
+
+def test_full_context_properties_at_32k():
+    """32,768 cached tokens, 8 KV heads, cap 64 (the benchmark's headline shape): invariants of the fit, the
+    selection covers the budget with less than one cluster of overshoot, attention equals the oracle on the
+    rows the kernel chose, budget 1 reads every row and equals exact attention."""
+    h, G, n = 8, 2, 32768
+    K, V = oc.clustered_keys(h, n + 8, 128, seed=77)
+    Kb, Vb = K.to(torch.bfloat16), V.to(torch.bfloat16)
+    q = (torch.randn(h * G, 128, generator=torch.Generator().manual_seed(78)) * 2).to(torch.bfloat16)
+    ix = SphereIndexGraph(C=2048, C_init=256, cap_keys=64.0, window=64, delta=0.03, capacity=n + 8, budget=0.2)
+    Kd, Vd = Kb.to(DEV), Vb.to(DEV)
+    ix.observe(Kd, n)
+    end = ix.end
+    lab = ix.labels.cpu()
+    counts = torch.stack([torch.bincount(lab[i, 1:end].long(), minlength=2048) for i in range(h)])
+    assert torch.equal(ix.count.cpu(), counts.float())
+    assert float(ix.count.max()) <= 64 and int(ix.n_c.min()) > 900 and int(ix.n_c.max()) < 2048
+    assert torch.all(lab[:, end:] == 2048) and torch.all(lab[:, 0] == 2048)
+    assert torch.equal(ix.dir8.cpu(), oc.to_int8_direction(ix.sum_dir.cpu())) or \
+        int((ix.dir8.cpu().int() - oc.to_int8_direction(ix.sum_dir.cpu()).int()).abs().max()) <= 1
+    out, labels, w = ix.attend(q.to(DEV), Kd, Vd, n=n, budget=0.2)
+    sets, lists = row_sets(ix)
+    need = math.ceil(0.2 * (end - 1))
+    for i in range(h):
+        got = len(sets[i]) - (n - end) - 1
+        assert need <= got < need + 64 and 0 in sets[i] and set(range(end, n)) <= sets[i]
+        assert lists[i].tolist() == sorted(lists[i].tolist())
+    ref = oc.attend_rows(q, Kb, Vb, [l.long() for l in lists])
+    assert float((out.cpu().double() - ref).abs().max()) <= 1e-2
+    fused = ix.step(q.to(DEV), Kd, Vd, ix._n_scalar, insert=False).clone()      # list-free path, same rows
+    assert float((fused.float() - out.float()).abs().max()) <= 1e-2
+    assert torch.equal(ix.cnt.cpu(), torch.tensor([len(s) for s in sets], dtype=torch.int32))
+    full, _, w1 = ix.attend(q.to(DEV), Kd, Vd, n=n, budget=1.0)
+    assert torch.equal(ix.cnt.cpu(), torch.full((h,), n, dtype=torch.int32))
+    dense = oc.attend_rows(q, Kb, Vb, [torch.arange(n)] * h)
+    assert float((full.cpu().double() - dense).abs().max()) <= 1e-2
+    assert ix.check_status() == 0
