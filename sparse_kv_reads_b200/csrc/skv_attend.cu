@@ -9,6 +9,8 @@
 // heads of the group on the M side, fp32 accumulation and a per-warp online softmax in base 2.
 // The work is HBM-bound (G flop per byte); the tensor-core tiles only keep the issue slots free
 // for the gathers.  float32 caches take a plain CUDA-core path with float32 arithmetic throughout.
+#include <type_traits>
+
 #include "skv_attend_core.cuh"
 #include "skv_common.cuh"
 
@@ -158,7 +160,7 @@ __global__ void __launch_bounds__(WARPS * 32, 3) attend_mma_kernel(const AttendP
     const int G = p.G;
     const Share sh = my_share(p, head, split, warp, WARPS);
     if (split >= sh.s_eff) return;
-    WarpAttend<STAGES, HI> wa;
+    typename std::conditional<HI, WarpAttend<STAGES, true>, WarpAttendT<STAGES>>::type wa;
     wa.init(static_cast<const __nv_bfloat16 *>(p.q) + (int64_t)head * G * HEAD_DIM, G, smem + warp * (STAGES * 8192),
             s_vmask[warp], static_cast<const char *>(p.K) + (int64_t)head * p.ksh * 2,
             static_cast<const char *>(p.V) + (int64_t)head * p.vsh * 2, p.ksr * 2, p.vsr * 2, p.scale_log2);
@@ -205,7 +207,7 @@ __global__ void __launch_bounds__(WARPS * 32, 3) attend_labels_kernel(const Atte
         if (p0 + tid * 16 + v * 8 < p1) raw[v] = __ldg(reinterpret_cast<const uint4 *>(lab + p0 + tid * 16 + v * 8));
     }
     for (int i = tid; i < p.sel_words; i += WARPS * 32) s_bits[i] = p.selbits[(int64_t)head * p.sel_words + i];
-    WarpAttend<STAGES, HI> wa;
+    typename std::conditional<HI, WarpAttend<STAGES, true>, WarpAttendT<STAGES>>::type wa;
     wa.init(static_cast<const __nv_bfloat16 *>(p.q) + (int64_t)head * G * HEAD_DIM, G, smem + warp * (STAGES * 8192),
             s_vmask[warp], static_cast<const char *>(p.K) + (int64_t)head * p.ksh * 2,
             static_cast<const char *>(p.V) + (int64_t)head * p.vsh * 2, p.ksr * 2, p.vsr * 2, p.scale_log2);

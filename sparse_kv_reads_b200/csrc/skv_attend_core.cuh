@@ -239,4 +239,166 @@ struct WarpAttend {
     }
 };
 
+// The same warp worker for groups of at most 8 query heads, with the operand roles swapped: the 16 keys of
+// a tile sit on the M side of S^T = K Q^T and the (<= 8) heads on N, so no accumulator row is padding; P is
+// turned into the B operand of O^T = V^T P with two movmatrix transposes.  Half the MMAs and 32 fewer
+// registers than the heads-on-M layout.
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t x) {
+    uint32_t y;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;\n" : "=r"(y) : "r"(x));
+    return y;
+}
+
+template <int STAGES>
+struct WarpAttendT {
+    uint32_t qb[8][2];                   // Q^T fragments: [k-step][d, d + 8], column = head
+    float acc[8][4];                     // O^T: [16-row d tile]: (d, hA), (d, hB), (d + 8, hA), (d + 8, hB)
+    float mA, mB, lA, lB;                // running max / partial sum of heads hA = 2 (lane % 4), hB = hA + 1
+    unsigned char *ring;
+    volatile uint32_t *vmask;
+    const char *Kb, *Vb;
+    int64_t krow, vrow;
+    float scale_log2;
+    int lane;
+
+    __device__ __forceinline__ void init(const __nv_bfloat16 *q, int G, unsigned char *ring_, uint32_t *vmask_,
+                                         const char *Kb_, const char *Vb_, int64_t krow_, int64_t vrow_,
+                                         float scale_log2_) {
+        lane = threadIdx.x & 31;
+        ring = ring_; vmask = vmask_; Kb = Kb_; Vb = Vb_; krow = krow_; vrow = vrow_; scale_log2 = scale_log2_;
+        const int head = lane >> 2, c = 2 * (lane & 3);
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+            const int col = 16 * ks + c;
+            qb[ks][0] = head < G ? *reinterpret_cast<const uint32_t *>(q + head * HEAD_DIM + col) : 0u;
+            qb[ks][1] = head < G ? *reinterpret_cast<const uint32_t *>(q + head * HEAD_DIM + col + 8) : 0u;
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+        mA = mB = NEG_BIG;
+        lA = lB = 0.f;
+    }
+
+    __device__ __forceinline__ void issue(int stage, int mypos) {
+        unsigned char *kb = ring + stage * 8192, *vb = kb + 4096;
+        const int sub = lane & 15, half = lane >> 4;
+        const uint32_t vm = __ballot_sync(0xffffffffu, mypos >= 0) & 0xffffu;
+        if (lane == 0) vmask[stage] = vm;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int r = half + 2 * i;
+            const int pos = __shfl_sync(0xffffffffu, mypos, r);
+            const int off = r * 256 + ((sub ^ (r & 7)) << 4);
+            const bool ok = pos >= 0;
+            cp_async16(kb + off, ok ? Kb + (int64_t)pos * krow + sub * 16 : Kb, ok ? 16 : 0);
+            cp_async16(vb + off, ok ? Vb + (int64_t)pos * vrow + sub * 16 : Vb, ok ? 16 : 0);
+        }
+    }
+
+    __device__ __forceinline__ void consume(int stage) {
+        const unsigned char *kb = ring + stage * 8192, *vb = kb + 4096;
+        const uint32_t vm = vmask[stage];
+        float s[4] = {0.f, 0.f, 0.f, 0.f};
+        {
+            const int mi = lane >> 3;
+            const int row = (lane & 7) + ((mi & 1) << 3), csel = mi >> 1;
+#pragma unroll
+            for (int ks = 0; ks < 8; ++ks) {
+                uint32_t a[4];
+                ldmatrix_x4(a, kb + row * 256 + (((2 * ks + csel) ^ (row & 7)) << 4));
+                mma_bf16_16816(s, a, qb[ks][0], qb[ks][1]);
+            }
+        }
+        const int k0 = lane >> 2;                        // this lane's keys: k0 and k0 + 8
+        const bool ok0 = (vm >> k0) & 1u, ok1 = (vm >> (k0 + 8)) & 1u;
+        const float zA0 = ok0 ? s[0] * scale_log2 : NEG_BIG, zB0 = ok0 ? s[1] * scale_log2 : NEG_BIG;
+        const float zA1 = ok1 ? s[2] * scale_log2 : NEG_BIG, zB1 = ok1 ? s[3] * scale_log2 : NEG_BIG;
+        float tA = fmaxf(zA0, zA1), tB = fmaxf(zB0, zB1);
+#pragma unroll
+        for (int o = 4; o < 32; o <<= 1) {               // over the 8 lanes that share lane % 4
+            tA = fmaxf(tA, __shfl_xor_sync(0xffffffffu, tA, o));
+            tB = fmaxf(tB, __shfl_xor_sync(0xffffffffu, tB, o));
+        }
+        const float nA = fmaxf(mA, tA), nB = fmaxf(mB, tB);
+        const float alA = fast_exp2(mA - nA), alB = fast_exp2(mB - nB);
+        mA = nA; mB = nB;
+        const float pA0 = ok0 ? fast_exp2(zA0 - nA) : 0.f, pB0 = ok0 ? fast_exp2(zB0 - nB) : 0.f;
+        const float pA1 = ok1 ? fast_exp2(zA1 - nA) : 0.f, pB1 = ok1 ? fast_exp2(zB1 - nB) : 0.f;
+        lA = lA * alA + pA0 + pA1;
+        lB = lB * alB + pB0 + pB1;
+        const uint32_t b0 = movmatrix_trans(pack_bf16(pA0, pB0));      // keys 0-7   -> k = 2 (lane % 4) + {0, 1}
+        const uint32_t b1 = movmatrix_trans(pack_bf16(pA1, pB1));      // keys 8-15
+        if (__any_sync(0xffffffffu, alA != 1.f || alB != 1.f)) {       // the maxima settle after a few tiles
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                acc[j][0] *= alA; acc[j][1] *= alB;
+                acc[j][2] *= alA; acc[j][3] *= alB;
+            }
+        }
+        {
+            const int mi = lane >> 3;
+            const int row = (lane & 7) + ((mi >> 1) << 3), csel = mi & 1;
+#pragma unroll
+            for (int mt = 0; mt < 8; ++mt) {
+                uint32_t a[4];
+                ldmatrix_x4_trans(a, vb + row * 256 + (((2 * mt + csel) ^ (row & 7)) << 4));
+                mma_bf16_16816(acc[mt], a, b0, b1);
+            }
+        }
+    }
+
+    template <typename PosFn>
+    __device__ __forceinline__ void run(int t0, int t1, PosFn pos_of) {
+        const int sub = lane & 15;
+        int it = t0;
+        int pos_next = (it < t1) ? pos_of(it * TILE_ROWS + sub) : -1;
+#pragma unroll
+        for (int s = 0; s < STAGES - 1; ++s) {
+            if (it < t1) {
+                const int mypos = pos_next;
+                ++it;
+                pos_next = (it < t1) ? pos_of(it * TILE_ROWS + sub) : -1;
+                issue(s, mypos);
+            }
+            cp_async_commit();
+        }
+        for (int t = t0; t < t1; ++t) {
+            const int stage = (t - t0) % STAGES;
+            if (it < t1) {
+                const int mypos = pos_next;
+                ++it;
+                pos_next = (it < t1) ? pos_of(it * TILE_ROWS + sub) : -1;
+                issue((t - t0 + STAGES - 1) % STAGES, mypos);
+            }
+            cp_async_commit();
+            cp_async_wait<STAGES - 1>();
+            __syncwarp();
+            consume(stage);
+            __syncwarp();
+        }
+        cp_async_wait<0>();
+    }
+
+    __device__ __forceinline__ void store_partial(float *red, int warp, int G) {
+#pragma unroll
+        for (int o = 4; o < 32; o <<= 1) {
+            lA += __shfl_xor_sync(0xffffffffu, lA, o);
+            lB += __shfl_xor_sync(0xffffffffu, lB, o);
+        }
+        const int hA = 2 * (lane & 3), hB = hA + 1, d0 = lane >> 2;
+        if (hA < G) {
+            float *r = red + (warp * G + hA) * 132;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) { r[16 * j + d0] = acc[j][0]; r[16 * j + d0 + 8] = acc[j][2]; }
+            if (d0 == 0) { r[128] = mA; r[129] = lA; }
+        }
+        if (hB < G) {
+            float *r = red + (warp * G + hB) * 132;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) { r[16 * j + d0] = acc[j][1]; r[16 * j + d0 + 8] = acc[j][3]; }
+            if (d0 == 0) { r[128] = mB; r[129] = lB; }
+        }
+    }
+};
+
 }  // namespace skv
