@@ -161,21 +161,22 @@ __global__ void __launch_bounds__(SEL_THREADS) score_pick_kernel(const SelectPar
         };
         constexpr bool TC = sizeof(TQ) == 2;               // bf16 query: tensor-core scoring of 8-bit summaries
         int4 rawa[4], rawb[4];                            // TC path: bytes [32j, 32j+32) of this lane's clusters
+        int4 nxta[4], nxtb[4];                            // the next iteration's, requested one iteration ahead
         const int nrow = lane >> 2, jq = lane & 3;
-        auto fetch_tc = [&](int c0) {
+        auto fetch_tc = [&](int c0, int4 (&da)[4], int4 (&db)[4]) {
 #pragma unroll
             for (int k = 0; k < 4; ++k) {
                 const int c = c0 + (k * SEL_WARPS + wid) * 8 + nrow;
-                rawa[k] = rawb[k] = make_int4(0, 0, 0, 0);
+                da[k] = db[k] = make_int4(0, 0, 0, 0);
                 if (c < c_hi) {
                     const int4 *src = reinterpret_cast<const int4 *>(p.st.dir8 + ((int64_t)h * C + c) * d + jq * 32);
-                    rawa[k] = __ldg(src);
-                    rawb[k] = __ldg(src + 1);
+                    da[k] = __ldg(src);
+                    db[k] = __ldg(src + 1);
                 }
             }
         };
         if (q8 && TC) {
-            fetch_tc(c_lo);
+            fetch_tc(c_lo, rawa, rawb);
         } else if (q8) {
             fetch8(c_lo);
         } else {
@@ -197,7 +198,11 @@ __global__ void __launch_bounds__(SEL_THREADS) score_pick_kernel(const SelectPar
                 qa[ks][3] = (GP > 8 && g1 < G) ? pack_half2(q1[2], q1[3]) : 0u;
             }
             for (int c0 = c_lo; c0 < c_hi; c0 += SEL_WARPS * 32) {
-                if (c0 != c_lo) fetch_tc(c0);
+                if (c0 != c_lo) {
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) { rawa[k] = nxta[k]; rawb[k] = nxtb[k]; }
+                }
+                if (c0 + SEL_WARPS * 32 < c_hi) fetch_tc(c0 + SEL_WARPS * 32, nxta, nxtb);
 #pragma unroll
                 for (int k = 0; k < 4; ++k) {
                     const int cbase = c0 + (k * SEL_WARPS + wid) * 8;
