@@ -134,3 +134,21 @@ def test_fused_dense_layers_match_the_module_by_module_forward():
     fused, dec = run_decoder(model, ids, P, T, True, **kw)
     assert dec.fused_dense
     torch.testing.assert_close(fused, plain, rtol=3e-2, atol=3e-2)
+
+
+def test_recentring_between_graph_replays_keeps_budget_one_exact():
+    """A small drift threshold makes heads recentre between replays (flags read without a synchronisation);
+    at budget 1 every row is read whatever the clustering, so the logits must still equal dense attention."""
+    model = tiny_model(seed=11)
+    P, T = 200, 120
+    ids = torch.randint(0, 1000, (1, P + T + 1), generator=torch.Generator().manual_seed(8)).to(DEV)
+    dense, _ = run_decoder(model, ids, P, T, True, mode="dense")
+    got, dec = run_decoder(model, ids, P, T, True, mode="cluster", budget=1.0, C=64, C_init=16, split_factor=2.0,
+                           window=8, delta=0.002, check_every=4, summary_bits=8)
+    torch.testing.assert_close(got, dense, rtol=2e-2, atol=2e-2)
+    assert sum(i.rebuilds for i in dec.attn) > 0
+    for i in dec.attn:
+        end = int(i.end_dev[0])
+        lab = i.labels.cpu()
+        counts = torch.stack([torch.bincount(lab[k, 1:end].long(), minlength=64) for k in range(i.H_kv)])
+        assert torch.equal(i.count.cpu(), counts.float())
