@@ -460,6 +460,36 @@ class SphereIndexGraph:
         """Variance of each cluster's unit directions about their mean (sphere_gpu.py:276-279)."""
         return (1 - self.sum_dir.pow(2).sum(-1) / self.count.clamp_min(1).pow(2)).clamp_min(0) * (self.count > 0)
 
+    # ---- checkpoint / resume --------------------------------------------------------------------------
+    _HOST_FIELDS = ("n", "end", "rebuilds", "resets", "refits", "head_steps", "_steps", "_splits_host", "_fitted")
+
+    def state_dict(self) -> dict:
+        """Everything needed to resume decoding with this layer's clusters: the device arrays of the state
+        (copied to the CPU) and the host counters.  The caller keeps the KV cache itself."""
+        if not self.initialized:
+            raise ValueError("nothing to save before the first observe()/prepare()")
+        self._host_end()
+        arrays = {name: getattr(self, name).detach().cpu().clone() for name in _FIELDS
+                  if getattr(self, name, None) is not None}
+        return {"arrays": arrays, "host": {k: getattr(self, k) for k in self._HOST_FIELDS},
+                "shape": {"H_kv": self.H_kv, "d": self.d, "C": self.C, "capacity": self.capacity,
+                          "summary_bits": self.summary_bits}}
+
+    def load_state_dict(self, sd: dict, device) -> None:
+        """Restore a state saved by ``state_dict`` onto ``device`` (the options given at construction must
+        describe the same slot count, capacity and summary width)."""
+        shp = sd["shape"]
+        if (shp["C"], shp["capacity"], shp["summary_bits"]) != (self.C, self.capacity, self.summary_bits):
+            raise ValueError("the saved state was built with a different C, capacity or summary_bits")
+        self._alloc(shp["H_kv"], shp["d"], torch.device(device))
+        for name, t in sd["arrays"].items():
+            getattr(self, name).copy_(t)
+        for k, v in sd["host"].items():
+            setattr(self, k, v)
+        self.initialized = True
+        self._pending = None
+        self._max_members = None
+
     def check_status(self) -> int:
         """OR of the device status words (synchronises); 0 means no device-side problem was recorded."""
         word = 0

@@ -18,6 +18,7 @@ import torch
 
 from .accounting import step_bytes
 from .cluster_state import SphereIndexGraph, release_workspaces
+from .stamp import stamp
 
 
 def synthetic_cache(heads: int, n: int, *, seed: int, device, centres: int = 64):
@@ -111,7 +112,7 @@ def main() -> None:
                 torch.cuda.empty_cache()
     if args.out:
         with open(args.out, "w") as fh:
-            json.dump({"peak_gbs": peak, "rows": rows}, fh, indent=1)
+            json.dump({"stamp": stamp(), "peak_gbs": peak, "rows": rows}, fh, indent=1)
 
 
 if __name__ == "__main__":

@@ -133,3 +133,29 @@ def test_a_missing_library_is_a_loud_error(monkeypatch):
     monkeypatch.setattr(_lib, "LIB_PATH", "/nonexistent/libskv.so")
     with pytest.raises(_lib.SkvError):
         _lib.lib()
+
+
+def test_state_dict_round_trip_on_the_cpu():
+    """Checkpoint / resume of one layer's cluster state: arrays and counters survive a save and a load."""
+    dev = torch.device("cpu")
+    a = SphereIndexGraph(C=16, window=4, capacity=64, summary_bits=8)
+    with pytest.raises(ValueError):
+        a.state_dict()
+    a._alloc(2, 128, dev)
+    a.sum_dir.normal_()
+    a.count.fill_(3.0)
+    a.n_c.fill_(7)
+    a.labels[:, 1:20] = 5
+    a.end_dev.fill_(20)
+    a.initialized, a._fitted, a.n, a.rebuilds, a._steps = True, True, 24, 2, 9
+    sd = a.state_dict()
+    assert sd["host"]["end"] == 20 and sd["arrays"]["labels"].dtype == torch.int16
+    b = SphereIndexGraph(C=16, window=4, capacity=64, summary_bits=8)
+    b.load_state_dict(sd, dev)
+    for name in ("sum_dir", "count", "n_c", "labels", "dir8", "end_dev"):
+        assert torch.equal(getattr(a, name), getattr(b, name)), name
+    assert (b.n, b.end, b.rebuilds, b._steps, b.initialized) == (24, 20, 2, 9, True)
+    with pytest.raises(ValueError):
+        SphereIndexGraph(C=32, window=4, capacity=64).load_state_dict(sd, dev)
+    from sparse_kv_reads_b200.stamp import stamp
+    assert {"time", "host_cores", "torch"} <= set(stamp())

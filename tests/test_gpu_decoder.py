@@ -152,3 +152,14 @@ def test_recentring_between_graph_replays_keeps_budget_one_exact():
         lab = i.labels.cpu()
         counts = torch.stack([torch.bincount(lab[k, 1:end].long(), minlength=64) for k in range(i.H_kv)])
         assert torch.equal(i.count.cpu(), counts.float())
+
+
+def test_total_variation_distance_to_exact_attention_shrinks_to_zero_at_full_budget():
+    from sparse_kv_reads_b200.long_gen_tvd import decode_logits, tvd
+    model = tiny_model(seed=13)
+    P, T = 400, 32
+    ids = torch.randint(0, 1000, (1, P + T + 1), generator=torch.Generator().manual_seed(9)).to(DEV)
+    exact = decode_logits(model, ids, P, T, mode="dense")
+    kw = dict(mode="cluster", C=128, C_init=16, cap_keys=32.0, window=16)
+    d = {b: tvd(decode_logits(model, ids, P, T, budget=b, **kw), exact) for b in (0.1, 0.5, 1.0)}
+    assert d[1.0] < 0.02 and d[1.0] <= d[0.5] + 0.01 and d[0.5] <= d[0.1] + 0.01, d
