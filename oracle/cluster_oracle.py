@@ -122,13 +122,18 @@ class ClusterOracle:
 
     def __init__(self, *, C: int, C_init: int | None = None, window: int = 64, delta: float = 0.03,
                  capacity: int = 65536, check_every: int = 16, seed: int = 0, kmeans_iters: int = 10,
-                 split_factor: float = 0.0, cap_keys: float = 0.0, summary_bits: int = 32):
+                 split_factor: float = 0.0, cap_keys: float = 0.0, summary_bits: int = 32, grow_cap: bool = False,
+                 reset_at: int = 0, var_factor: float = 0.0, var_min: int = 8):
         self.C, self.C_init = C, (C if C_init is None else C_init)
         self.window, self.delta, self.capacity = window, delta, capacity
         self.check_every, self.seed, self.kmeans_iters = check_every, seed, kmeans_iters
         self.cap_keys = float(cap_keys)
         self.split_factor = float(split_factor) if split_factor or not cap_keys else 2.0   # sphere_gpu.py:123-124
-        self.splitting = self.split_factor > 0
+        self.var_factor, self.var_min = float(var_factor), int(var_min)
+        self.splitting = self.split_factor > 0 or self.var_factor > 0
+        self.capk = self.split_factor / self.C_init if grow_cap else 0.0       # sphere_gpu.py:130
+        self.reset_at = reset_at
+        self.resets = 0
         self.summary_bits = summary_bits
         if self.C_init > C:
             raise ValueError("C_init must be <= C")
@@ -147,6 +152,7 @@ class ClusterOracle:
         self.count = torch.zeros(h, C)
         self.n_c = torch.full((h,), self.C_init, dtype=torch.long)
         self.cap = torch.full((h,), math.inf)
+        self.vthr = torch.full((h,), math.inf)
         self.ksum = torch.zeros(h, d)
         self.mu_ref = torch.zeros(h, d)
         self.rbar = torch.zeros(h)
@@ -219,8 +225,30 @@ class ClusterOracle:
                 self.cent8.copy_(to_int8_direction(self.cent))
         self.rbar[heads] = Kr.pow(2).sum(-1).mean(1).sqrt()
         self.labels[heads, 1:self.end] = self._fold(Kr, heads).to(torch.int16)
+        if self.var_factor > 0 and bool(todo.any()):              # threshold from the fit's own clusters (:214-217)
+            fit = heads[todo]
+            used = (self.count[fit] > 0).float()
+            self.vthr[fit] = self.var_factor * (self.spread()[fit] * used).sum(1) / used.sum(1).clamp_min(1)
         self._refresh8()
         return fresh
+
+    def cap_now(self) -> torch.Tensor:
+        """Each head's cap in keys; it grows with the clustered keys under ``grow_cap`` (sphere_gpu.py:270-273)."""
+        return torch.clamp(self.cap, min=self.capk * (self.end - 1))
+
+    def spread(self) -> torch.Tensor:
+        """Variance of each cluster's unit directions about their mean (sphere_gpu.py:275-278)."""
+        return (1 - self.sum_dir.pow(2).sum(-1) / self.count.clamp_min(1).pow(2)).clamp_min(0) * (self.count > 0)
+
+    def reset_heads(self, K: torch.Tensor, heads: torch.Tensor) -> None:
+        """Fit ``heads`` again from all their clustered keys, back to ``C_init`` clusters (sphere_gpu.py:283-293)."""
+        if heads.numel() == 0:
+            return
+        self.fitted[heads] = False
+        self.n_c[heads] = self.C_init
+        if self._build(K, heads, None):
+            self.split_overflow(K, None, kway=True)
+        self.resets += int(heads.numel())
 
     # ---- splits ---------------------------------------------------------------------------
     def _split_group(self, K: torch.Tensor, hc: torch.Tensor, kway: bool) -> int:
@@ -242,7 +270,7 @@ class ClusterOracle:
         mag = Kr.norm(dim=-1)
         U = Kr / mag.clamp_min(1e-12).unsqueeze(-1)
         if kway:
-            k = torch.ceil(cnt * self.split_factor / self.cap[hd]).long().clamp(min=2)
+            k = torch.ceil(cnt * self.split_factor / self.cap_now()[hd]).long().clamp(min=2)
             part = kway_partition(U, valid, k, self.kmeans_iters)
         else:
             part = bisect_partition(U, valid)
@@ -284,8 +312,13 @@ class ClusterOracle:
         if not self.splitting:
             return
         slots = torch.arange(self.C).unsqueeze(0)
+        by_spread = cand is not None                  # a spread over the threshold splits once, on receiving a key
         while True:
-            over = (self.count > self.cap.unsqueeze(1)) & (slots < self.n_c.unsqueeze(1)) & (self.count >= 2)
+            over = self.count > self.cap_now().unsqueeze(1)
+            if by_spread:
+                over |= (self.spread() > self.vthr.unsqueeze(1)) & (self.count >= self.var_min)
+                by_spread = False
+            over &= (slots < self.n_c.unsqueeze(1)) & (self.count >= 2)
             if cand is not None:
                 over &= cand
             hc = over.nonzero()
@@ -336,6 +369,8 @@ class ClusterOracle:
             if self.splitting:
                 got = torch.zeros(self.h, self.C, dtype=torch.bool).scatter_(1, lab, True)
                 self.split_overflow(K, got, kway=False)
+                if self.reset_at:
+                    self.reset_heads(K, (self.n_c >= self.reset_at).nonzero().squeeze(1))
         nb = self.end - 1
         if nb <= 0:
             return

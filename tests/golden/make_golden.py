@@ -27,7 +27,8 @@ def snapshot(ix, *, full: bool) -> dict:
     out = {"labels": ix.labels[:, :ix.n].clone(), "n_c": ix.n_c.clone(), "count": ix.count.clone(),
            "mmax": ix.mmax.clone(), "mmin": ix.mmin.clone(), "mu_ref": ix.mu_ref.clone(), "ksum": ix.ksum.clone(),
            "rbar": ix.rbar.clone(), "cap": ix.cap.clone(), "end": ix.end, "splits": ix.splits,
-           "rebuilds": ix.rebuilds, "sum_dir_norm": ix.sum_dir.norm(dim=-1)}
+           "rebuilds": ix.rebuilds, "resets": ix.resets, "vthr": ix.vthr.clone(),
+           "sum_dir_norm": ix.sum_dir.norm(dim=-1)}
     if full:
         out["sum_dir"] = ix.sum_dir.clone()
         out["cent"] = ix.cent.clone()
@@ -47,18 +48,18 @@ def case_kmeans(ref) -> dict:
 
 
 def case_stream(ref, *, h, G, n0, steps, C, C_init, cap_keys, split_factor, window, delta, check_every, seed, budget,
-                full, probe_every) -> dict:
+                full, probe_every, **extra) -> dict:
     """SphereIndexGPU: fit at n0, then one key per step; selection and the attention spec at probes."""
     d = 128
     K, V = clustered_keys(h, n0 + steps, d, seed=seed)
     Q = queries(h * G, d, steps + 1, seed + 1000)
     ix = ref["SphereIndexGPU"](C=C, C_init=C_init, cap_keys=cap_keys, split_factor=split_factor, window=window,
                                delta=delta, capacity=n0 + steps, check_every=check_every, seed=0,
-                               partition="kmeans", kmeans_iters=10)
+                               partition="kmeans", kmeans_iters=10, **extra)
     ix.observe(K, n0)
     gold = {"input_sum": float(K.double().sum()), "cfg": dict(h=h, G=G, n0=n0, steps=steps, C=C, C_init=C_init,
             cap_keys=cap_keys, split_factor=split_factor, window=window, delta=delta, check_every=check_every,
-            seed=seed, budget=budget), "fit": snapshot(ix, full=full), "probes": {}}
+            seed=seed, budget=budget, **extra), "fit": snapshot(ix, full=full), "probes": {}}
     for t in range(steps + 1):
         n = n0 + t
         if t:
@@ -123,6 +124,16 @@ def main() -> None:
         "small_fixed": case_stream(ref, h=3, G=2, n0=400, steps=64, C=32, C_init=None, cap_keys=0.0, split_factor=0.0,
                                    window=64, delta=math.inf, check_every=16, seed=23, budget=0.5, full=False,
                                    probe_every=16),
+        # options that bound or redirect the splitting: growing cap, spread trigger, reset of a head
+        "small_grow": case_stream(ref, h=2, G=2, n0=400, steps=300, C=64, C_init=16, cap_keys=0.0, split_factor=1.5,
+                                  window=8, delta=math.inf, check_every=16, seed=24, budget=0.3, full=False,
+                                  probe_every=100, grow_cap=True),
+        "small_var": case_stream(ref, h=2, G=2, n0=400, steps=300, C=128, C_init=16, cap_keys=0.0, split_factor=0.0,
+                                 window=8, delta=math.inf, check_every=16, seed=25, budget=0.3, full=False,
+                                 probe_every=100, var_factor=0.9, var_min=8),
+        "small_reset": case_stream(ref, h=2, G=2, n0=400, steps=300, C=64, C_init=16, cap_keys=24.0, split_factor=0.0,
+                                   window=8, delta=math.inf, check_every=16, seed=26, budget=0.3, full=False,
+                                   probe_every=100, reset_at=40),
     }
     torch.save(gold, os.path.join(HERE, "small.pt"))
     # the CPU-runnable benchmark configuration: 8 KV heads, 16 query heads, n 4096 + 512, 256 -> cap 64

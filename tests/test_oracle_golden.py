@@ -16,9 +16,10 @@ def _replay(g, *, summary_bits=32):
     K, V = oc.clustered_keys(c["h"], c["n0"] + c["steps"], 128, seed=c["seed"])
     assert abs(float(K.double().sum()) - g["input_sum"]) < 1e-6, "seeded inputs differ from the stored checksum"
     Q = torch.randn(c["steps"] + 1, c["h"] * c["G"], 128, generator=torch.Generator().manual_seed(c["seed"] + 1000))
+    extra = {k: c[k] for k in ("grow_cap", "reset_at", "var_factor", "var_min") if k in c}
     st = oc.ClusterOracle(C=c["C"], C_init=c["C_init"], cap_keys=c["cap_keys"], split_factor=c["split_factor"],
                           window=c["window"], delta=c["delta"], capacity=c["n0"] + c["steps"],
-                          check_every=c["check_every"], seed=0, summary_bits=summary_bits)
+                          check_every=c["check_every"], seed=0, summary_bits=summary_bits, **extra)
     st.observe(K, c["n0"])
     yield -1, st, None, K, V
     for t in range(c["steps"] + 1):
@@ -41,12 +42,14 @@ def _same_state(st, snap):
     torch.testing.assert_close(st.cap, snap["cap"], rtol=0, atol=0)
     torch.testing.assert_close(st.sum_dir.norm(dim=-1), snap["sum_dir_norm"], rtol=0, atol=0)
     assert st.end == snap["end"] and st.splits == snap["splits"] and st.rebuilds == snap["rebuilds"]
+    assert st.resets == snap["resets"]
+    torch.testing.assert_close(st.vthr, snap["vthr"], rtol=0, atol=0)
     if "sum_dir" in snap:
         torch.testing.assert_close(st.sum_dir, snap["sum_dir"], rtol=0, atol=0)
         torch.testing.assert_close(st.cent, snap["cent"], rtol=0, atol=0)
 
 
-@pytest.mark.parametrize("case", ["small_cap", "small_drift", "small_fixed"])
+@pytest.mark.parametrize("case", ["small_cap", "small_drift", "small_fixed", "small_grow", "small_var", "small_reset"])
 def test_stream_cases_reproduce_the_reference_bit_for_bit(golden_small, case):
     g = golden_small[case]
     for t, st, q, K, V in _replay(g):
@@ -65,6 +68,8 @@ def test_stream_cases_reproduce_the_reference_bit_for_bit(golden_small, case):
     _same_state(st, g["final"])
     if case != "small_fixed":
         assert g["final"]["splits"] > 0
+    if case == "small_reset":
+        assert g["final"]["resets"] > 0
     if case == "small_drift":
         assert g["final"]["rebuilds"] > 0
 
