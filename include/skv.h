@@ -65,6 +65,7 @@ typedef struct skv_state {
     float   *count;       /* [heads, C]     member count */
     int32_t *n_c;         /* [heads]        slots in use */
     float   *cap;         /* [heads]        split a cluster holding more keys than this (+inf: never) */
+    float   *vthr;        /* [heads]        ... or whose directions spread more than this (+inf: never) */
     float   *rbar;        /* [heads]        rms key length at the last (re)build */
     float   *ksum;        /* [heads, d]     running sum of clustered keys */
     float   *mu_ref;      /* [heads, d]     reference mean the keys are centred with */
@@ -189,10 +190,13 @@ int skv_attend_labels(const void *q, const void *K, const void *V, const int16_t
  *   budget          fraction of the clustered keys to cover (need = ceil(budget * (end-1)), in double)
  *   delta           drift threshold in units of rbar;  reset_at: 0 = never
  *   max_members     largest cluster the in-kernel split stages (<= skv_insert_max_members())
+ *   capk            cap per clustered key when the cap grows with the context (a cluster splits above
+ *                   max(cap, capk * clustered keys)); 0 = fixed cap
+ *   var_min         fewest keys a cluster must hold to split on the spread threshold state.vthr
  */
 int skv_insert(const skv_state *st, const void *const *k_layers, int heads_per_layer, int dtype,
                int64_t k_head_stride, int64_t k_row_stride, const int32_t *n_dev, int window,
-               double budget, float delta, int reset_at, int max_members, void *stream);
+               double budget, float delta, int reset_at, int max_members, float capk, int var_min, void *stream);
 int skv_insert_max_members(void);
 
 /* Workspace bytes of skv_fit / skv_rebin for `heads` heads of `m` clustered keys. */
@@ -208,10 +212,15 @@ int64_t skv_fit_workspace_bytes(int heads, int m, int C, int d);
  * (ssa/attn/sphere_gpu.py:166-219), _split_after_fit/_split_overflow/_split_batch (:302-391) and
  * _refresh8 (ssa/kernels/sphere_fused.py:398-406).
  *   cap_keys > 0: absolute cap; else cap = split_factor * m / C_init when split_factor > 0; else no cap
+ *   capk        growing cap (see skv_insert); var_factor > 0: state.vthr = var_factor x the mean spread of the
+ *               fitted clusters (ssa/attn/sphere_gpu.py:214-217), else +inf
+ *   head_list   optional device int32 [n_list]: fit only these entries of st (a head that reached reset_at,
+ *               SphereIndexGPU._reset_heads, sphere_gpu.py:283-293); null = all heads.  Workspace for n_list heads.
  */
 int skv_fit(const skv_state *st, const void *K, int dtype, int64_t k_head_stride, int64_t k_row_stride,
             int n, int window, int C_init, int iters, const int32_t *init_pos, float cap_keys,
-            float split_factor, void *workspace, int64_t workspace_bytes, void *stream);
+            float split_factor, float capk, float var_factor, const int32_t *head_list, int n_list,
+            void *workspace, int64_t workspace_bytes, void *stream);
 
 /* Recentre and rebin selected heads with their centroids kept (new mean = ksum / (end-1)):
  * replaces the recentring branch of SphereIndexGPU._build (ssa/attn/sphere_gpu.py:187-219 with mu given;

@@ -33,7 +33,7 @@ class SkvState(C.Structure):
                 ("summary_bits", C.c_int32), ("reserved", C.c_int32),
                 ("sum_dir", C.c_void_p), ("cent", C.c_void_p), ("dir8", C.c_void_p), ("cent8", C.c_void_p),
                 ("mmax", C.c_void_p), ("mmin", C.c_void_p), ("count", C.c_void_p), ("n_c", C.c_void_p),
-                ("cap", C.c_void_p), ("rbar", C.c_void_p), ("ksum", C.c_void_p), ("mu_ref", C.c_void_p),
+                ("cap", C.c_void_p), ("vthr", C.c_void_p), ("rbar", C.c_void_p), ("ksum", C.c_void_p), ("mu_ref", C.c_void_p),
                 ("flags", C.c_void_p), ("status", C.c_void_p), ("nsplit", C.c_void_p), ("end", C.c_void_p),
                 ("need", C.c_void_p), ("labels", C.c_void_p)]
 
@@ -69,12 +69,13 @@ def _declare(lib) -> None:
     lib.skv_attend_labels.argtypes = [vp, vp, vp, vp, i64, vp, i32, vp, vp, vp, vp, vp, i32, i32, i32, i32, i64, i64,
                                       i64, i64, i32, f32, vp]
     lib.skv_insert.restype = i32
-    lib.skv_insert.argtypes = [C.POINTER(SkvState), vp, i32, i32, i64, i64, vp, i32, f64, f32, i32, i32, vp]
+    lib.skv_insert.argtypes = [C.POINTER(SkvState), vp, i32, i32, i64, i64, vp, i32, f64, f32, i32, i32, f32, i32, vp]
     lib.skv_insert_max_members.restype = i32
     lib.skv_fit_workspace_bytes.restype = i64
     lib.skv_fit_workspace_bytes.argtypes = [i32, i32, i32, i32]
     lib.skv_fit.restype = i32
-    lib.skv_fit.argtypes = [C.POINTER(SkvState), vp, i32, i64, i64, i32, i32, i32, i32, vp, f32, f32, vp, i64, vp]
+    lib.skv_fit.argtypes = [C.POINTER(SkvState), vp, i32, i64, i64, i32, i32, i32, i32, vp, f32, f32, f32, f32, vp, i32,
+                            vp, i64, vp]
     lib.skv_add_rmsnorm.restype = i32
     lib.skv_add_rmsnorm.argtypes = [vp, vp, vp, vp, i32, i32, f32, vp]
     lib.skv_qk_rope_cache.restype = i32

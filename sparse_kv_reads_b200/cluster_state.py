@@ -4,8 +4,9 @@ Host-side mirror of the reference's state objects for this path, collapsed into 
 reference's names: ``SphereIndexGPU`` (ssa/attn/sphere_gpu.py:113-442), ``SphereIndexFused``
 (ssa/kernels/sphere_fused.py:316-518) and ``SphereIndexGraph`` (ssa/kernels/graph_kernels.py:192-279).
 Every computation is a call into the CUDA library through its C ABI; there is no PyTorch fallback.
-Only the k-means partition, the shared (``sum_share``) selection, the size cap and recentring are
-built; the reference's other options raise ``ValueError``.
+Built: the k-means partition, the shared (``sum_share``) selection, the size cap (fixed, or growing with
+the context under ``grow_cap``), splits on the spread of a cluster (``var_factor``), the refit of a head
+that ran out of clusters (``reset_at``) and recentring; the reference's other options raise ``ValueError``.
 """
 
 from __future__ import annotations
@@ -31,6 +32,7 @@ _FIELDS = {
     "count": (lambda C, d, cap: (C,), torch.float32, 0.0),
     "n_c": (lambda C, d, cap: (), torch.int32, 0),
     "cap": (lambda C, d, cap: (), torch.float32, math.inf),
+    "vthr": (lambda C, d, cap: (), torch.float32, math.inf),
     "rbar": (lambda C, d, cap: (), torch.float32, 0.0),
     "ksum": (lambda C, d, cap: (d,), torch.float32, 0.0),
     "mu_ref": (lambda C, d, cap: (d,), torch.float32, 0.0),
@@ -109,21 +111,22 @@ class SphereIndexGraph:
             raise ValueError(f"unknown partition {partition!r}: only 'kmeans' is built")
         if summary_bits not in (8, 32):
             raise ValueError("summary_bits must be 8 or 32")
-        if grow_cap or reset_at or var_factor:
-            raise ValueError("grow_cap, reset_at and var_factor are not built")
         assert C >= 16 and C & (C - 1) == 0, "C must be a power of two >= 16"
         self.partition, self.kmeans_iters, self.kind = partition, kmeans_iters, kind
         self.C_init = C if C_init is None else C_init
         self.cap_keys = float(cap_keys)
         self.split_factor = float(split_factor) if split_factor or not cap_keys else 2.0
-        self.splitting = self.split_factor > 0
+        self.var_factor = float(var_factor)
+        self.splitting = self.split_factor > 0 or self.var_factor > 0
+        # cap per clustered key when the cap follows the context (ssa/attn/sphere_gpu.py:130)
+        self.capk = self.split_factor / self.C_init if grow_cap else 0.0
         if self.C_init > C:
             raise ValueError("C_init must be <= C, and splitting needs partition='kmeans'")
         self.C, self.window, self.delta, self.capacity = C, window, delta, capacity
         self.check_every, self.seed, self.budget = check_every, seed, budget
         self.async_check, self.max_lag, self.split_scratch = async_check, max_lag, split_scratch
         self.summary_bits, self.refit_every = summary_bits, refit_every
-        self.reset_at, self.var_min = 0, var_min
+        self.reset_at, self.var_min = (int(reset_at) if self.splitting else 0), int(var_min)
         self.initialized = False
         self.n = 0
         self.start, self.end = 1, 0
@@ -169,7 +172,10 @@ class SphereIndexGraph:
         if self._max_members is None:
             lim = lib().skv_insert_max_members()
             cap = float(self.cap.max()) if self.splitting else 0.0
+            cap = max(cap, self.capk * self.capacity)
             want = int(cap) + 2 if math.isfinite(cap) else 2
+            if self.var_factor > 0 and not math.isfinite(cap):
+                want = lim                                  # split on spread alone: no bound on a cluster's size
             self._max_members = max(2, min(lim, want))
         return self._max_members
 
@@ -201,24 +207,34 @@ class SphereIndexGraph:
         self._build_all(K, n)
         self.initialized = True
 
-    def _build_all(self, K: torch.Tensor, n: int) -> None:
-        """Fit every head from positions [1, end) (ssa/attn/sphere_gpu.py:187-230, :302-391)."""
+    def _build_all(self, K: torch.Tensor, n: int, heads: torch.Tensor | None = None) -> None:
+        """Fit every head (or only ``heads``) from positions [1, end)
+        (ssa/attn/sphere_gpu.py:187-230, :302-391)."""
         m = self.end - 1
         if m < 1:
             return                                          # nothing to cluster yet: fitted on a later call
         g = torch.Generator(device="cpu").manual_seed(self.seed)
         init = torch.randperm(m, generator=g)[torch.arange(self.C_init) % m].to(torch.int32).to(K.device)
         L = lib()
-        nbytes = L.skv_fit_workspace_bytes(self.H_kv, m, self.C, self.d)
+        hl = None if heads is None else heads.to(torch.int32).to(K.device)
+        entries = self.H_kv if hl is None else int(hl.numel())
+        nbytes = L.skv_fit_workspace_bytes(entries, m, self.C, self.d)
         ws = _workspace(K.device, nbytes)
+        splits_kept = self.nsplit.clone() if hl is not None else None
         check(L.skv_fit(ctypes.byref(self._st), K.data_ptr(), dtype_code(K.dtype), K.stride(0), K.stride(1), n,
                         self.window, self.C_init, self.kmeans_iters, init.data_ptr(), self.cap_keys,
-                        self.split_factor if self.splitting else 0.0, ws.data_ptr(), ws.numel(),
+                        self.split_factor, self.capk, self.var_factor,
+                        None if hl is None else hl.data_ptr(), entries, ws.data_ptr(), ws.numel(),
                         stream_ptr(K.device)), "skv_fit")
         self._fitted = True
         self._max_members = None
-        self._splits_host += int(self.nsplit.sum())
-        self.nsplit.zero_()
+        if hl is None:
+            self._splits_host += int(self.nsplit.sum())
+            self.nsplit.zero_()
+        else:                                               # the fit restarted the listed heads' counters
+            idx = hl.long()
+            self._splits_host += int(splits_kept[idx].sum()) + int(self.nsplit[idx].sum())
+            self.nsplit[idx] = 0
 
     # ---- per-step maintenance (eager: lengths known on the host) -----------------------------------
     def observe(self, K: torch.Tensor, n: int) -> None:
@@ -232,7 +248,8 @@ class SphereIndexGraph:
     def _launch_insert(self, K: torch.Tensor, n_dev: torch.Tensor, budget: float) -> None:
         check(lib().skv_insert(ctypes.byref(self._st), self._ktable(K).data_ptr(), self.H_kv, dtype_code(K.dtype),
                                K.stride(0), K.stride(1), n_dev.data_ptr(), self.window, float(budget),
-                               float(min(self.delta, 3.0e38)), 0, self._members_limit(), stream_ptr(K.device)),
+                               float(min(self.delta, 3.0e38)), self.reset_at, self._members_limit(), self.capk,
+                               self.var_min, stream_ptr(K.device)),
               "skv_insert")
 
     def _advance(self, K: torch.Tensor, n: int) -> None:
@@ -280,9 +297,23 @@ class SphereIndexGraph:
             self.flags.zero_()
 
     def _act_on(self, K: torch.Tensor, flags_host: torch.Tensor) -> None:
-        heads = (flags_host & _lib.FLAG_DRIFT).nonzero().flatten()
+        """Refit the heads whose cluster count reached ``reset_at``; recentre the others that drifted
+        (ssa/kernels/sphere_fused.py:453-457)."""
+        reset = (flags_host & _lib.FLAG_RESET) != 0
+        if bool(reset.any()):
+            self._reset_heads(K, reset.nonzero().flatten())
+        heads = (((flags_host & _lib.FLAG_DRIFT) != 0) & ~reset).nonzero().flatten()
         if heads.numel():
             self._rebuild(K, heads)
+
+    def _reset_heads(self, K: torch.Tensor, heads: torch.Tensor) -> None:
+        """Fit ``heads`` again from all their clustered keys, back to ``C_init`` clusters and then the
+        after-fit splits (ssa/attn/sphere_gpu.py:283-293)."""
+        self._host_end()
+        if self.end < 2:
+            return
+        self._build_all(K, self.end + self.window, heads)
+        self.resets += int(heads.numel())
 
     def _host_end(self) -> None:
         """Refresh the host copy of ``end`` from the device (a synchronisation; only before host work)."""
@@ -454,7 +485,8 @@ class SphereIndexGraph:
         return float(self.n_c.float().mean()) if self.initialized else float(self.C)
 
     def _cap_now(self) -> torch.Tensor:
-        return self.cap
+        """Each head's cap in keys; it grows with the clustered keys under ``grow_cap`` (sphere_gpu.py:270-273)."""
+        return torch.clamp(self.cap, min=self.capk * (self.end - 1))
 
     def _spread(self) -> torch.Tensor:
         """Variance of each cluster's unit directions about their mean (sphere_gpu.py:276-279)."""

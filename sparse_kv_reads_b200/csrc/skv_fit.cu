@@ -108,6 +108,10 @@ __global__ void rbar_kernel(const FitView v) {
 __global__ void __launch_bounds__(128) seed_kernel(const FitView v, const int32_t *init_pos, int C_init) {
     const int e = blockIdx.y, j = blockIdx.x, t = threadIdx.x;
     const int h = head_of(v, e);
+    if (j >= C_init) {                                   // slots beyond the fitted ones start empty
+        v.st.cent[((int64_t)h * v.st.C + j) * HEAD_DIM + t] = 0.f;
+        return;
+    }
     const int i = min(max(init_pos[j], 0), v.m - 1);
     v.st.cent[((int64_t)h * v.st.C + j) * HEAD_DIM + t] = v.Xn[((int64_t)e * v.m + i) * HEAD_DIM + t];
     if (j == 0 && t == 0) v.st.n_c[h] = C_init;
@@ -251,7 +255,8 @@ __global__ void __launch_bounds__(256) accumulate_kernel(const FitView v, int ll
 }
 
 // cap of each head after a fit, flags cleared, slots beyond n_c wiped
-__global__ void finish_fit_kernel(const FitView v, float cap_keys, float split_factor, int C_init, int fitted) {
+__global__ void finish_fit_kernel(const FitView v, float cap_keys, float split_factor, int C_init, int fitted,
+                                  float var_factor) {
     const int e = blockIdx.x * blockDim.x + threadIdx.x;
     if (e >= v.entries) return;
     const int h = head_of(v, e);
@@ -261,6 +266,25 @@ __global__ void finish_fit_kernel(const FitView v, float cap_keys, float split_f
         v.st.cap[h] = cap;
         v.st.nsplit[h] = 0;
         v.st.status[h] = 0;
+        if (v.st.vthr) {
+            // spread threshold: var_factor x the mean over the fitted clusters in use of 1 - |sum_dir|^2 / count^2
+            float thr = INFINITY;
+            if (var_factor > 0.f) {
+                float sum = 0.f, used = 0.f;
+                for (int c = 0; c < C_init; ++c) {
+                    const float cn = v.st.count[(int64_t)h * v.st.C + c];
+                    if (cn > 0.f) {
+                        const float *sd = v.st.sum_dir + ((int64_t)h * v.st.C + c) * HEAD_DIM;
+                        float n2 = 0.f;
+                        for (int i = 0; i < HEAD_DIM; ++i) n2 = fmaf(sd[i], sd[i], n2);
+                        sum += fmaxf(1.0f - n2 / (cn * cn), 0.f);
+                        used += 1.f;
+                    }
+                }
+                thr = var_factor * sum / fmaxf(used, 1.f);
+            }
+            v.st.vthr[h] = thr;
+        }
     }
     v.st.flags[h] = 0;
     v.st.end[h] = v.end;
@@ -287,13 +311,13 @@ __global__ void __launch_bounds__(256) refresh8_kernel(const FitView v) {
 // ---- division of the clusters over the cap, one round ----------------------------------------------
 // counters: [0] candidates over all entries, [1] clusters split, [2] most candidates in one entry,
 //           [3] most parts asked for one cluster
-__global__ void __launch_bounds__(256) find_over_kernel(const FitView v, int kway, float split_factor) {
+__global__ void __launch_bounds__(256) find_over_kernel(const FitView v, int kway, float split_factor, float capk) {
     __shared__ int ired[40];
     const int e = blockIdx.x, tid = threadIdx.x;
     const int h = head_of(v, e);
     const int C = v.st.C;
     const int n_c = min(max(v.st.n_c[h], 0), C);
-    const float cap = v.st.cap[h];
+    const float cap = fmaxf(v.st.cap[h], capk * (float)v.m);
     const float *count = v.st.count + (int64_t)h * C;
     const int per = (C + 255) / 256;
     const int c0 = min(tid * per, n_c), c1 = min(c0 + per, n_c);
@@ -353,7 +377,7 @@ struct PartSmem {
 // Partition the members of one candidate cluster: k-way cosine k-means from evenly spaced members
 // (kway) or the two-way split with the median-cut fallback.  One CTA per candidate.
 __global__ void __launch_bounds__(256) partition_kernel(const FitView v, int kway, float split_factor, int iters,
-                                                        int kcap, float *projbuf) {
+                                                        int kcap, float *projbuf, float capk) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __shared__ float fred[32];
     __shared__ int ired[40];
@@ -370,7 +394,7 @@ __global__ void __launch_bounds__(256) partition_kernel(const FitView v, int kwa
     const float *X = v.Xn + (int64_t)e * v.m * HEAD_DIM;
     (void)c;
     if (kway) {
-        const float cap = v.st.cap[h];
+        const float cap = fmaxf(v.st.cap[h], capk * (float)v.m);
         int k = (int)ceilf((float)cnt * split_factor / cap);
         k = min(max(k, 2), kcap);
         float *cents = reinterpret_cast<float *>(smem_raw);
@@ -668,12 +692,12 @@ static int launch_assign(const FitView &v, cudaStream_t s) {
     return SKV_OK;
 }
 
-static int split_rounds(FitView &v, float *projbuf, float split_factor, int iters, cudaStream_t s) {
+static int split_rounds(FitView &v, float *projbuf, float split_factor, int iters, float capk, cudaStream_t s) {
     bool kway = true;
     for (int round = 0; round < 256; ++round) {
         int32_t host[4] = {0, 0, 0, 0};
         SKV_CUDA_OK(cudaMemsetAsync(v.counters, 0, 16, s));
-        find_over_kernel<<<v.entries, 256, 0, s>>>(v, kway ? 1 : 0, split_factor);
+        find_over_kernel<<<v.entries, 256, 0, s>>>(v, kway ? 1 : 0, split_factor, capk);
         SKV_CUDA_OK(cudaMemcpyAsync(host, v.counters, 16, cudaMemcpyDeviceToHost, s));
         SKV_CUDA_OK(cudaStreamSynchronize(s));
         if (host[0] == 0) break;
@@ -683,7 +707,8 @@ static int split_rounds(FitView &v, float *projbuf, float split_factor, int iter
         const size_t smem = kway ? (size_t)kcap * (2 * HEAD_DIM * 4 + 8) + 64 : 3 * HEAD_DIM * 4;
         if (smem > 48 * 1024)
             SKV_CUDA_OK(cudaFuncSetAttribute(partition_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        partition_kernel<<<dim3(maxc, v.entries), 256, smem, s>>>(v, kway ? 1 : 0, split_factor, iters, kcap, projbuf);
+        partition_kernel<<<dim3(maxc, v.entries), 256, smem, s>>>(v, kway ? 1 : 0, split_factor, iters, kcap, projbuf,
+                                                                  capk);
         slots_kernel<<<(v.entries + 127) / 128, 128, 0, s>>>(v);
         apply_kernel<<<dim3(maxc, v.entries), 256, 0, s>>>(v);
         SKV_CUDA_OK(cudaMemcpyAsync(host, v.counters, 16, cudaMemcpyDeviceToHost, s));
@@ -705,14 +730,16 @@ extern "C" int64_t skv_fit_workspace_bytes(int heads, int m, int C, int d) {
 
 extern "C" int skv_fit(const skv_state *st, const void *K, int dtype, int64_t k_head_stride, int64_t k_row_stride,
                        int n, int window, int C_init, int iters, const int32_t *init_pos, float cap_keys,
-                       float split_factor, void *workspace, int64_t workspace_bytes, void *stream) {
+                       float split_factor, float capk, float var_factor, const int32_t *head_list, int n_list,
+                       void *workspace, int64_t workspace_bytes, void *stream) {
     int rc = check_state(st);
     if (rc) return rc;
     if (!K || !init_pos || !workspace) return SKV_E_NULL;
     if (dtype != SKV_BF16 && dtype != SKV_F32) return SKV_E_DTYPE;
     if (n < 0 || n > st->capacity || window < 0 || iters < 0 || C_init < 1 || C_init > st->C || cap_keys < 0.f ||
-        split_factor < 0.f)
+        split_factor < 0.f || capk < 0.f || var_factor < 0.f)
         return SKV_E_RANGE;
+    if (head_list && (n_list < 1 || n_list > st->heads)) return SKV_E_RANGE;
     const int esz = dtype == SKV_BF16 ? 2 : 4;
     if (!aligned16(K) || !aligned16(workspace) || (k_row_stride * esz) % 16 || (k_head_stride * esz) % 16 ||
         k_row_stride < HEAD_DIM)
@@ -720,28 +747,27 @@ extern "C" int skv_fit(const skv_state *st, const void *K, int dtype, int64_t k_
     const int end = n - window > 1 ? n - window : 1;
     const int m = end - 1;
     if (m < 1) return SKV_E_RANGE;                      // nothing to cluster yet
-    if (workspace_bytes < fit_bytes(st->heads, m, st->C)) return SKV_E_WORKSPACE;
+    const int entries = head_list ? n_list : st->heads;
+    if (workspace_bytes < fit_bytes(entries, m, st->C)) return SKV_E_WORKSPACE;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     FitView v;
-    v.st = *st; v.list = nullptr; v.entries = st->heads; v.end = end; v.m = m;
+    v.st = *st; v.list = head_list; v.entries = entries; v.end = end; v.m = m;
     v.ksh = k_head_stride; v.ksr = k_row_stride; v.K = K;
-    const int64_t used = carve(v, static_cast<char *>(workspace), st->heads, m, st->C);
+    const int64_t used = carve(v, static_cast<char *>(workspace), entries, m, st->C);
     float *projbuf = reinterpret_cast<float *>(static_cast<char *>(workspace) + used);
     rc = dtype == SKV_BF16 ? centre_and_assign<__nv_bfloat16>(v, 0, s) : centre_and_assign<float>(v, 0, s);
     if (rc) return rc;
-    // slots beyond C_init start empty; labels of unclustered positions say "always read"
-    SKV_CUDA_OK(cudaMemsetAsync(st->cent, 0, (size_t)st->heads * st->C * HEAD_DIM * 4, s));
-    seed_kernel<<<dim3(C_init, st->heads), 128, 0, s>>>(v, init_pos, C_init);
+    seed_kernel<<<dim3(st->C, entries), 128, 0, s>>>(v, init_pos, C_init);
     for (int it = 0; it < iters; ++it) {
         if ((rc = launch_assign(v, s))) return rc;
-        accumulate_kernel<<<dim3((C_init + 7) / 8, st->heads), 256, 0, s>>>(v, 1, C_init);
+        accumulate_kernel<<<dim3((C_init + 7) / 8, entries), 256, 0, s>>>(v, 1, C_init);
     }
     if ((rc = launch_assign(v, s))) return rc;
-    accumulate_kernel<<<dim3((st->C + 7) / 8, st->heads), 256, 0, s>>>(v, 0, st->C);
-    finish_fit_kernel<<<(st->heads + 127) / 128, 128, 0, s>>>(v, cap_keys, split_factor, C_init, 1);
+    accumulate_kernel<<<dim3((st->C + 7) / 8, entries), 256, 0, s>>>(v, 0, st->C);
+    finish_fit_kernel<<<(entries + 127) / 128, 128, 0, s>>>(v, cap_keys, split_factor, C_init, 1, var_factor);
     SKV_CUDA_OK(cudaGetLastError());
-    if (split_factor > 0.f && (rc = split_rounds(v, projbuf, split_factor, iters, s))) return rc;
-    if (st->summary_bits == 8) refresh8_kernel<<<dim3((st->C + 7) / 8, st->heads), 256, 0, s>>>(v);
+    if (split_factor > 0.f && (rc = split_rounds(v, projbuf, split_factor, iters, capk, s))) return rc;
+    if (st->summary_bits == 8) refresh8_kernel<<<dim3((st->C + 7) / 8, entries), 256, 0, s>>>(v);
     SKV_CUDA_OK(cudaGetLastError());
     return SKV_OK;
 }
@@ -769,7 +795,7 @@ extern "C" int skv_rebin(const skv_state *st, const int32_t *head_list, int n_li
     if (rc) return rc;
     if ((rc = launch_assign(v, s))) return rc;
     accumulate_kernel<<<dim3((st->C + 7) / 8, n_list), 256, 0, s>>>(v, 0, st->C);
-    finish_fit_kernel<<<(n_list + 127) / 128, 128, 0, s>>>(v, 0.f, 0.f, 1, 0);
+    finish_fit_kernel<<<(n_list + 127) / 128, 128, 0, s>>>(v, 0.f, 0.f, 1, 0, 0.f);
     if (st->summary_bits == 8) refresh8_kernel<<<dim3((st->C + 7) / 8, n_list), 256, 0, s>>>(v);
     SKV_CUDA_OK(cudaGetLastError());
     return SKV_OK;

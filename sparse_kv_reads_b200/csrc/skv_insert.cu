@@ -24,6 +24,8 @@ struct InsertParams {
     float delta;
     int reset_at;
     int max_members;
+    float capk;
+    int var_min;
 };
 
 // shared-memory views used by the split
@@ -269,6 +271,8 @@ __global__ void __launch_bounds__(INS_THREADS) insert_kernel(const InsertParams 
     new_end = min(new_end, p.st.capacity);
     if (n_act <= 0) new_end = old_end;                    // nothing fitted yet: the host builds first
     const float cap = p.st.cap[e];
+    const float vthr = p.st.vthr ? p.st.vthr[e] : INFINITY;
+    const bool by_spread = vthr < INFINITY;
     float mu = 0.f, ks = 0.f;
     if (tid < HEAD_DIM) {
         mu = p.st.mu_ref[(int64_t)e * HEAD_DIM + tid];
@@ -338,10 +342,9 @@ __global__ void __launch_bounds__(INS_THREADS) insert_kernel(const InsertParams 
             sd = p.st.sum_dir[row * HEAD_DIM + tid] + s_kn[tid];
             p.st.sum_dir[row * HEAD_DIM + tid] = sd;
         }
-        if (q8) {
-            const float n2 = block_sum(sd * sd, fred);
-            if (tid < HEAD_DIM) p.st.dir8[row * HEAD_DIM + tid] = quant8(sd / fmaxf(sqrtf(n2), 1e-12f));
-        }
+        float n2 = 0.f;
+        if (q8 || by_spread) n2 = block_sum(sd * sd, fred);
+        if (q8 && tid < HEAD_DIM) p.st.dir8[row * HEAD_DIM + tid] = quant8(sd / fmaxf(sqrtf(n2), 1e-12f));
         if (tid == 0) {
             p.st.mmax[row] = fmaxf(p.st.mmax[row], mag);
             p.st.mmin[row] = fminf(p.st.mmin[row], mag);
@@ -349,7 +352,9 @@ __global__ void __launch_bounds__(INS_THREADS) insert_kernel(const InsertParams 
             p.st.count[row] = cn;
             lab[pos] = (int16_t)bi;
             int dec = 0;
-            if (cn > cap && cn >= 2.0f) {
+            // over the size cap (which may grow with the clustered keys), or its directions spread too widely
+            const bool wide = by_spread && (1.0f - n2 / (cn * cn) > vthr) && cn >= (float)p.var_min;
+            if ((cn > fmaxf(cap, p.capk * (float)pos) || wide) && cn >= 2.0f) {
                 if (n_act < C) dec = 1;
                 else if (p.st.status) atomicOr(p.st.status + e, SKV_ST_NO_SLOT);
             }
@@ -393,7 +398,7 @@ extern "C" int skv_insert_max_members(void) {
 
 extern "C" int skv_insert(const skv_state *st, const void *const *k_layers, int heads_per_layer, int dtype,
                           int64_t k_head_stride, int64_t k_row_stride, const int32_t *n_dev, int window, double budget,
-                          float delta, int reset_at, int max_members, void *stream) {
+                          float delta, int reset_at, int max_members, float capk, int var_min, void *stream) {
     if (!st || !k_layers || !n_dev) return SKV_E_NULL;
     if (!st->sum_dir || !st->cent || !st->mmax || !st->mmin || !st->count || !st->n_c || !st->cap || !st->rbar ||
         !st->ksum || !st->mu_ref || !st->flags || !st->nsplit || !st->end || !st->need || !st->labels)
@@ -404,7 +409,7 @@ extern "C" int skv_insert(const skv_state *st, const void *const *k_layers, int 
     if (st->summary_bits != 8 && st->summary_bits != 32) return SKV_E_RANGE;
     if (st->summary_bits == 8 && (!st->dir8 || !st->cent8)) return SKV_E_NULL;
     if (st->heads <= 0 || heads_per_layer <= 0 || st->heads % heads_per_layer || window < 0 || budget < 0.0 ||
-        st->capacity <= 0 || reset_at < 0)
+        st->capacity <= 0 || reset_at < 0 || capk < 0.f || var_min < 0)
         return SKV_E_RANGE;
     if (max_members < 2 || max_members > skv_insert_max_members()) return SKV_E_RANGE;
     const int esz = dtype == SKV_BF16 ? 2 : 4;
@@ -414,7 +419,7 @@ extern "C" int skv_insert(const skv_state *st, const void *const *k_layers, int 
     InsertParams p;
     p.st = *st; p.k_layers = k_layers; p.hpl = heads_per_layer; p.ksh = k_head_stride; p.ksr = k_row_stride;
     p.n_dev = n_dev; p.window = window; p.budget = budget; p.delta = delta; p.reset_at = reset_at;
-    p.max_members = max_members;
+    p.max_members = max_members; p.capk = capk; p.var_min = var_min;
     const size_t smem = insert_smem(max_members);
     auto kern = dtype == SKV_BF16 ? insert_kernel<__nv_bfloat16> : insert_kernel<float>;
     static size_t configured[64][2] = {};

@@ -67,7 +67,8 @@ class AllLayerInsert:
         f = self.layers[0]
         check(lib().skv_insert(ctypes.byref(self.st), self.table.data_ptr(), f.H_kv, dtype_code(self.k0.dtype),
                                self.k0.stride(0), self.k0.stride(1), n_dev.data_ptr(), f.window, float(f.budget),
-                               float(min(f.delta, 3.0e38)), 0, self.max_members, stream_ptr(self.k0.device)),
+                               float(min(f.delta, 3.0e38)), f.reset_at, self.max_members, f.capk, f.var_min,
+                               stream_ptr(self.k0.device)),
               "skv_insert")
 
 

@@ -27,7 +27,7 @@ def device_index_from_oracle(st: oc.ClusterOracle, **kw) -> SphereIndexGraph:
                           split_factor=st.split_factor if st.splitting and not st.cap_keys else 0.0,
                           summary_bits=st.summary_bits, **kw)
     ix._alloc(st.h, st.d, DEV)
-    for name in ("sum_dir", "cent", "mmax", "mmin", "count", "cap", "rbar", "ksum", "mu_ref", "labels"):
+    for name in ("sum_dir", "cent", "mmax", "mmin", "count", "cap", "vthr", "rbar", "ksum", "mu_ref", "labels"):
         getattr(ix, name).copy_(getattr(st, name))
     ix.n_c.copy_(st.n_c.to(torch.int32))
     if st.summary_bits == 8:

@@ -44,7 +44,7 @@ def test_struct_layout_matches_the_header():
     body = text[text.index("typedef struct skv_state {"):text.index("} skv_state;")]
     fields = re.findall(r"^\s+(?:int32_t|float|int8_t|int16_t)\s+\*?([A-Za-z0-9_]+);", body, flags=re.M)
     assert fields == [f[0] for f in _lib.SkvState._fields_]
-    assert ctypes.sizeof(_lib.SkvState) == 6 * 4 + 18 * 8
+    assert ctypes.sizeof(_lib.SkvState) == 6 * 4 + 19 * 8
 
 
 def fake_state(C=64, cap=64, bits=32, heads=2):
@@ -95,12 +95,16 @@ def test_state_calls_reject_bad_arguments(L):
                                           o.get("G", 2), 128, o.get("dtype", 0), 128 * 64, 128, 128 * 64, 128, 4, 0.1, None)
     assert lab(ls=36) == -4 and lab(C=48) == -2 and lab(dtype=1) == -3 and lab(G=17) == -2
     ins = lambda s, **o: L.skv_insert(ctypes.byref(s), ok, o.get("hpl", 2), 0, 128 * 64, o.get("ksr", 128), ok, 64, 0.2,
-                                      0.03, 0, o.get("mm", 66), None)
+                                      0.03, o.get("reset_at", 0), o.get("mm", 66), o.get("capk", 0.0),
+                                      o.get("var_min", 8), None)
     assert ins(st, hpl=3) == -5 and ins(st, mm=1) == -5 and ins(st, mm=10 ** 6) == -5 and ins(st, ksr=120) == -4
+    assert ins(st, capk=-1.0) == -5 and ins(st, var_min=-1) == -5 and ins(st, reset_at=-1) == -5
     assert L.skv_insert_max_members() >= 400
     fit = lambda s, **o: L.skv_fit(ctypes.byref(s), ok, 0, 128 * 64, 128, o.get("n", 64), o.get("window", 8),
-                                   o.get("C_init", 16), 10, ok, 0.0, 0.0, ok, o.get("bytes", 1 << 40), None)
+                                   o.get("C_init", 16), 10, ok, 0.0, 0.0, o.get("capk", 0.0), o.get("vf", 0.0),
+                                   o.get("hl", None), o.get("nl", 0), ok, o.get("bytes", 1 << 40), None)
     assert fit(st, n=100) == -5 and fit(st, C_init=128) == -5 and fit(st, n=8, window=8) == -5
+    assert fit(st, capk=-1.0) == -5 and fit(st, vf=-0.5) == -5 and fit(st, hl=ok, nl=0) == -5 and fit(st, hl=ok, nl=3) == -5
     assert fit(st, bytes=16) == -6
     assert L.skv_fit_workspace_bytes(2, 55, 64, 128) > 2 * 55 * 512
     assert L.skv_rebin(ctypes.byref(st), ok, 3, 32, ok, 0, 128 * 64, 128, ok, 1 << 40, None) == -5
