@@ -238,6 +238,19 @@ def kernel_roofline(dec, n_now, peak_gbs, which, traffic=None):
     return roof, layer
 
 
+def own_launches(dec) -> int:
+    """Launches of this library's kernels in one decode step: the all-layer insert, then per layer the
+    selection and the attention, and with the bundled model's fused layers also QK-norm/rotary/cache write and
+    either the four matrix-vector products (norms and activation folded in) or the three element-wise kernels
+    around cuBLAS products; one more norm ahead of the vocabulary projection."""
+    per_layer = 2
+    extra = 1
+    if dec.fused_dense:
+        per_layer += 1 + (4 if dec.own_gemv and dec.B <= 8 else 3)
+        extra += 1
+    return extra + per_layer * len(dec.attn)
+
+
 def gpu_arm(args, wl) -> None:
     import torch.distributed as dist
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -321,7 +334,7 @@ def gpu_arm(args, wl) -> None:
                            "l2": "per-layer caches total far more than L2; the kernel leg also flushes 512 MB"},
                 "e2e": {"value": B * K_steps / (e2e_ms * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": 8 * B,
                         "d2h_bytes_per_step": 8 * B, "ms_per_step": e2e_ms / K_steps},
-                "gpu_launches": K_steps * (1 + 2 * len(dec.attn)),
+                "gpu_launches": K_steps * own_launches(dec),
                 "clocks": clocks.summary(), "roofline": roof, "layer_step": layer,
                 "prompt_fit_s": fit_s, "device_status": status,
                 "splits": sum(ix.splits for ix in dec.attn)}

@@ -166,6 +166,15 @@ int skv_select(const skv_state *st, const void *q, int dtype, int G, const int32
 /* Tuning aid without a counterpart in the reference: `dev_ptr` is a device array of 16 uint64 that receives
  * nanosecond time stamps of the phases of skv_select's kernel for head 0 (null switches it off). */
 void skv_debug_select_probe(void *dev_ptr);
+/* Overlap of consecutive launches (programmatic dependent launch).  When on, skv_qk_rope_cache, skv_select and
+ * skv_attend_labels may be scheduled before the kernel ahead of them on the stream has ended; they load what no
+ * kernel of the same decode step writes (cluster summaries, labels) and then wait for that kernel.  The caller
+ * turns it on only where this holds: the cluster state (skv_insert, skv_fit, skv_rebin) must not be written by
+ * the launch directly ahead of skv_select or skv_attend_labels.  Off by default; SKV_PDL=0 in the environment
+ * keeps it off.  Process-wide switch, read at launch time. */
+void skv_set_overlap(int on);
+/* Same for skv_attend_labels: device uint64 [CTAs][8] phase stamps of every CTA (null = off). */
+void skv_debug_attend_probe(void *dev_ptr);
 
 /* skv_attend without a row list: every CTA owns a range of positions, reads their int16 labels, keeps
  * the positions whose label's bit is set in `selbits` (from skv_select) and attends over them; `cnt`
@@ -250,6 +259,18 @@ int skv_qk_rope_cache(const void *qkv, const void *q_norm_w, const void *k_norm_
 /* gate_up [B, 2*inter] (gate columns first) -> out [B, inter] = silu(gate) * up: the element-wise middle of
  * layer.ffn (graph_decode.py:117). */
 int skv_silu_mul(const void *gate_up, void *out, int B, int inter, void *stream);
+
+/* y[B, N] = x[B, K] . W[N, K]^T for B <= 8 sequences (bf16, float32 accumulation): the projections of a decode
+ * step (the reference runs them as the engine's nn.Linear modules, models/graph_decode.py:100-121).  The input
+ * is built inside the kernel:
+ *   mode 0  x [B, K] as given;
+ *   mode 1  h_out = h_in + delta (delta may be null), x = RMSNorm(h_out) * norm_w: the residual add and norm of
+ *           skv_add_rmsnorm, out of place (h_out must not alias h_in; h_out may be null);
+ *   mode 2  x = silu(gate) * up from x = gate_up [B, 2K], as skv_silu_mul.
+ * W row-major [N, K], K a multiple of 8 and at most 49,152; all pointers 16-byte aligned.  Takes part in
+ * skv_set_overlap: the weights are requested before the wait for the launch ahead. */
+int skv_gemv(const void *W, int N, int K, void *y, int B, int mode, const void *x, const void *h_in,
+             const void *delta, const void *norm_w, void *h_out, float eps, void *stream);
 
 #ifdef __cplusplus
 }

@@ -31,6 +31,11 @@ static const DevProps &props() {
 }
 
 int device_sm_count() { return props().sms; }
+static bool g_pdl = false;
+bool pdl_enabled() {
+    static const bool allowed = [] { const char *e = getenv("SKV_PDL"); return !(e && e[0] == '0'); }();
+    return allowed && g_pdl;
+}
 int device_max_smem_optin() { return props().smem_optin; }
 
 }  // namespace skv
@@ -53,3 +58,5 @@ extern "C" const char *skv_error_string(int code) {
 }
 
 extern "C" const char *skv_last_cuda_error(void) { return cudaGetErrorString(skv::g_last_cuda_error); }
+
+extern "C" void skv_set_overlap(int on) { skv::g_pdl = on != 0; }

@@ -16,12 +16,13 @@
 
 namespace skv {
 
+constexpr int PART_LD = 132;               // floats per partial row: 128 sums, max, sum, 2 unused
+
 struct AttendParams {
     const void *q, *K, *V;
     const int32_t *idx, *cnt, *n_dev;
     void *out;
-    float *part_acc;   // [heads, splits, G, 128]
-    float *part_ml;    // [heads, splits, G, 2]   (max in base-2 units, sum)
+    float *part;       // [heads, splits, G, 132]: 128 sums, max (base-2 units), sum of weights, 2 unused
     int32_t *ticket;   // [heads]
     int32_t *status;   // [heads] or null
     int heads, G;
@@ -34,7 +35,18 @@ struct AttendParams {
     int32_t *cnt_out;          // [heads] rows read, accumulated (zeroed by the selection kernel)
     int64_t lab_stride;
     int sel_words, C;
+    unsigned long long *probe;  // optional [CTAs][8] phase time stamps (ns), for tuning
 };
+
+static unsigned long long *g_attend_probe = nullptr;
+
+__device__ __forceinline__ void stamp(const AttendParams &p, int slot) {
+    if (p.probe && threadIdx.x == 0) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+        p.probe[(size_t)(blockIdx.y * gridDim.x + blockIdx.x) * 8 + slot] = t;
+    }
+}
 
 // Which tiles a warp owns: contiguous runs, identical arithmetic in every CTA of the head.
 struct Share {
@@ -71,11 +83,10 @@ __device__ __forceinline__ int fetch_pos(const AttendParams &p, int head, int ro
 // head merge all partials into `out`.  blockDim.x must be 128 (one thread per output column).
 template <typename T>
 __device__ __forceinline__ void finish_head(const AttendParams &p, const float *red, int sets, int head, int split,
-                                            int s_eff, int *sh_flag) {
+                                            int s_eff, int *sh_flag, float *stage, int stage_rows) {
     const int G = p.G, tid = threadIdx.x;
     T *out = static_cast<T *>(p.out);
-    float *pa = p.part_acc + ((int64_t)head * p.splits + split) * G * HEAD_DIM;
-    float *pm = p.part_ml + ((int64_t)head * p.splits + split) * G * 2;
+    float *pa = p.part + ((int64_t)head * p.splits + split) * G * PART_LD;
 #pragma unroll 1
     for (int g = 0; g < G; ++g) {
         float M = NEG_BIG;
@@ -90,11 +101,8 @@ __device__ __forceinline__ void finish_head(const AttendParams &p, const float *
         if (s_eff == 1) {
             store_out(out + ((int64_t)head * G + g) * HEAD_DIM + tid, dn > 0.f ? nm / dn : 0.f);
         } else {
-            __stcg(pa + g * HEAD_DIM + tid, nm);
-            if (tid == 0) {
-                __stcg(pm + 2 * g, M);
-                __stcg(pm + 2 * g + 1, dn);
-            }
+            __stcg(pa + g * PART_LD + tid, nm);
+            if (tid == 0) __stcg(reinterpret_cast<float2 *>(pa + g * PART_LD + HEAD_DIM), make_float2(M, dn));
         }
     }
     if (s_eff == 1) return;
@@ -105,45 +113,86 @@ __device__ __forceinline__ void finish_head(const AttendParams &p, const float *
         *sh_flag = (t == s_eff - 1);
     }
     __syncthreads();
+    stamp(p, 5);
     if (!*sh_flag) return;
     __threadfence();
-    // Merge of the head's partials by this (last) CTA.  Loads are spread over the four warps (warp w takes
-    // splits w, w+4, ...; a lane owns four output columns) and issued eight at a time, so the pass costs a
-    // few L2 round trips instead of one per split.
-    __shared__ float s_max[4][16];
-    __shared__ __align__(16) float s_sum[4][132];
+    // Merge of the head's partials by this (last) CTA.  The partial rows are copied into the shared memory
+    // the CTA no longer needs with asynchronous 16-byte copies, all requested before any is used: one round
+    // trip to L2 where they fit (stage_rows rows), chunks of one query head's splits with a running maximum
+    // otherwise.  Up to four query heads are then folded at once, each by 4 / (their number) warps that share
+    // its rows; a lane owns four columns.
+    float *stg = stage;
+    __shared__ __align__(16) float s_sum[4][PART_LD];
     const int lane = tid & 31, wid = tid >> 5;
-    const float *qa = p.part_acc + (int64_t)head * p.splits * G * HEAD_DIM;
-    const float *qm = p.part_ml + (int64_t)head * p.splits * G * 2;
-    for (int g = 0; g < G; ++g) {
-        float mx = NEG_BIG;
-        for (int s = tid; s < s_eff; s += 128) mx = fmaxf(mx, __ldcg(qm + (s * G + g) * 2));
-        mx = warp_max(mx);
-        if (lane == 0) s_max[wid][g] = mx;
-    }
-    __syncthreads();
-#pragma unroll 1
-    for (int g = 0; g < G; ++g) {
-        const float M = fmaxf(fmaxf(s_max[0][g], s_max[1][g]), fmaxf(s_max[2][g], s_max[3][g]));
+    const float *src = p.part + (int64_t)head * p.splits * G * PART_LD;
+    const int gc = max(1, min(G, stage_rows / s_eff));        // query heads staged together
+    const int cs = gc > 1 ? s_eff : min(s_eff, stage_rows);   // splits per chunk
+    for (int g0 = 0; g0 < G; g0 += gc) {
+        const int ng = min(gc, G - g0);
+        float M = NEG_BIG, dn = 0.f;                           // carried over chunks only when ng == 1
         float4 nm = make_float4(0.f, 0.f, 0.f, 0.f);
-        float dn = 0.f;
-#pragma unroll 8
-        for (int s = wid; s < s_eff; s += 4) {
-            const float2 ml = __ldcg(reinterpret_cast<const float2 *>(qm + (s * G + g) * 2));
-            const float4 a = __ldcg(reinterpret_cast<const float4 *>(qa + (s * G + g) * HEAD_DIM + lane * 4));
-            const float f = fast_exp2(ml.x - M);
-            dn += f * ml.y;
-            nm.x += f * a.x; nm.y += f * a.y; nm.z += f * a.z; nm.w += f * a.w;
+        for (int s0 = 0; s0 < s_eff; s0 += cs) {
+            const int ns = min(cs, s_eff - s0);
+            if (ng == G) {                                     // every row of the head: one contiguous block
+                const int chunks = ns * G * (PART_LD / 4);
+                const float *blk = src + (int64_t)s0 * G * PART_LD;
+                for (int c = tid; c < chunks; c += 128) cp_async16(stg + c * 4, blk + c * 4, 16);
+            } else {                                           // rows of query heads [g0, g0 + ng) only
+                for (int gi = 0; gi < ng; ++gi)
+                    for (int i = wid; i < ns; i += 4) {
+                        const float *row = src + ((int64_t)(s0 + i) * G + g0 + gi) * PART_LD;
+                        float *dst = stg + (i * ng + gi) * PART_LD;
+                        cp_async16(dst + lane * 4, row + lane * 4, 16);
+                        if (lane == 0) cp_async16(dst + HEAD_DIM, row + HEAD_DIM, 16);
+                    }
+            }
+            cp_async_commit();
+            cp_async_wait<0>();
+            __syncthreads();
+            stamp(p, 7);
+            // staged row of (split i, query head gi): stg + (i * ng + gi) * PART_LD
+            const bool last_chunk = s0 + cs >= s_eff;
+            for (int gb = 0; gb < ng; gb += 4) {
+                const int nq = min(4, ng - gb), wpg = 4 / nq;
+                const int gi = gb + wid / wpg, sub = wid % wpg;
+                if (wid < nq * wpg) {
+                    if (ng > 1) { M = NEG_BIG; dn = 0.f; nm = make_float4(0.f, 0.f, 0.f, 0.f); }
+                    const float *rows = stg + gi * PART_LD;
+                    const int ld = ng * PART_LD;
+                    float mb = NEG_BIG;
+                    for (int i = lane; i < ns; i += 32) mb = fmaxf(mb, rows[i * ld + HEAD_DIM]);
+                    mb = fmaxf(M, warp_max(mb));
+                    const float al = fast_exp2(M - mb);
+                    M = mb;
+                    dn *= al; nm.x *= al; nm.y *= al; nm.z *= al; nm.w *= al;
+#pragma unroll 4
+                    for (int i = sub; i < ns; i += wpg) {
+                        const float2 ml = *reinterpret_cast<const float2 *>(rows + i * ld + HEAD_DIM);
+                        const float4 a = *reinterpret_cast<const float4 *>(rows + i * ld + lane * 4);
+                        const float f = fast_exp2(ml.x - M);
+                        dn = fmaf(f, ml.y, dn);
+                        nm.x = fmaf(f, a.x, nm.x); nm.y = fmaf(f, a.y, nm.y);
+                        nm.z = fmaf(f, a.z, nm.z); nm.w = fmaf(f, a.w, nm.w);
+                    }
+                    *reinterpret_cast<float4 *>(&s_sum[wid][lane * 4]) = nm;
+                    if (lane == 0) s_sum[wid][HEAD_DIM] = dn;
+                }
+                __syncthreads();
+                if (ng > 1 || last_chunk)
+                    for (int qi = 0; qi < nq; ++qi) {
+                        float num = 0.f, den = 0.f;
+                        for (int w = 0; w < wpg; ++w) {
+                            num += s_sum[qi * wpg + w][tid];
+                            den += s_sum[qi * wpg + w][HEAD_DIM];
+                        }
+                        store_out(out + ((int64_t)head * G + g0 + gb + qi) * HEAD_DIM + tid, den > 0.f ? num / den : 0.f);
+                    }
+                __syncthreads();
+            }
         }
-        *reinterpret_cast<float4 *>(&s_sum[wid][lane * 4]) = nm;
-        if (lane == 0) s_sum[wid][128] = dn;
-        __syncthreads();
-        const float num = s_sum[0][tid] + s_sum[1][tid] + s_sum[2][tid] + s_sum[3][tid];
-        const float den = s_sum[0][128] + s_sum[1][128] + s_sum[2][128] + s_sum[3][128];
-        store_out(out + ((int64_t)head * G + g) * HEAD_DIM + tid, den > 0.f ? num / den : 0.f);
-        __syncthreads();
     }
     if (tid == 0) p.ticket[head] = 0;     // ready for the next call on this stream
+    stamp(p, 6);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -169,7 +218,7 @@ __global__ void __launch_bounds__(WARPS * 32, 3) attend_mma_kernel(const AttendP
     float *red = reinterpret_cast<float *>(smem);
     wa.store_partial(red, warp, G);
     __syncthreads();
-    finish_head<__nv_bfloat16>(p, red, WARPS, head, split, sh.s_eff, &s_flag);
+    finish_head<__nv_bfloat16>(p, red, WARPS, head, split, sh.s_eff, &s_flag, red, WARPS * STAGES * 8192 / (PART_LD * 4));
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -177,11 +226,13 @@ __global__ void __launch_bounds__(WARPS * 32, 3) attend_mma_kernel(const AttendP
 // lists the selected ones of 2,048 positions at a time in shared memory (ascending), and attends over
 // them.  No global row list is written or read; cnt_out receives the number of rows read.
 // ---------------------------------------------------------------------------------------------
-constexpr int LAB_SUB = 2048;              // positions listed per pass (16 per thread)
-
-template <int WARPS, int STAGES, bool HI>
+// LPT = labels a thread tests per pass (8 or 16): short ranges (many CTAs per head) use 8 so that every thread
+// of the CTA takes part in listing; a pass covers LAB_SUB = 128 x LPT positions.
+template <int WARPS, int STAGES, bool HI, int LPT>
 __global__ void __launch_bounds__(WARPS * 32, 3) attend_labels_kernel(const AttendParams p) {
     static_assert(WARPS == 4, "finish_head expects 128 threads");
+    static_assert(LPT == 8 || LPT == 16, "a thread's labels are one or two 16-byte loads");
+    constexpr int LAB_SUB = WARPS * 32 * LPT, LV = LPT / 8;
     extern __shared__ __align__(128) unsigned char smem[];
     __shared__ uint32_t s_vmask[WARPS][STAGES];
     __shared__ int s_flag;
@@ -198,14 +249,17 @@ __global__ void __launch_bounds__(WARPS * 32, 3) attend_labels_kernel(const Atte
     const int p0 = split * chunk, p1 = min(p0 + chunk, n);
     uint32_t *s_bits = reinterpret_cast<uint32_t *>(smem + WARPS * STAGES * 8192);
     const int16_t *lab = p.labels + (int64_t)head * p.lab_stride;
+    stamp(p, 0);
     // the first pass's labels are requested before anything else so that their latency overlaps the
     // loads of the selection bits and of the query
-    uint4 raw[2];
+    uint4 raw[LV];
 #pragma unroll
-    for (int v = 0; v < 2; ++v) {
+    for (int v = 0; v < LV; ++v) {
         raw[v] = make_uint4(0u, 0u, 0u, 0u);
-        if (p0 + tid * 16 + v * 8 < p1) raw[v] = __ldg(reinterpret_cast<const uint4 *>(lab + p0 + tid * 16 + v * 8));
+        if (p0 + tid * LPT + v * 8 < p1) raw[v] = __ldg(reinterpret_cast<const uint4 *>(lab + p0 + tid * LPT + v * 8));
     }
+    pdl_wait();                            // selection bits and query come from the kernels before this one
+    pdl_trigger();
     for (int i = tid; i < p.sel_words; i += WARPS * 32) s_bits[i] = p.selbits[(int64_t)head * p.sel_words + i];
     typename std::conditional<HI, WarpAttend<STAGES, true>, WarpAttendT<STAGES>>::type wa;
     wa.init(static_cast<const __nv_bfloat16 *>(p.q) + (int64_t)head * G * HEAD_DIM, G, smem + warp * (STAGES * 8192),
@@ -214,13 +268,14 @@ __global__ void __launch_bounds__(WARPS * 32, 3) attend_labels_kernel(const Atte
     int read_rows = 0;
     bool bad = false;
     __syncthreads();
+    stamp(p, 1);
     for (int sub0 = p0; sub0 < p1; sub0 += LAB_SUB) {
-        const int base = sub0 + tid * 16;
+        const int base = sub0 + tid * LPT;
         uint32_t take = 0;
         if (base < p1) {
             const int16_t *l16 = reinterpret_cast<const int16_t *>(raw);
 #pragma unroll
-            for (int i = 0; i < 16; ++i) {
+            for (int i = 0; i < LPT; ++i) {
                 const unsigned l = (unsigned)(int)l16[i];
                 if (base + i < p1) {
                     if (l <= (unsigned)C) take |= ((s_bits[l >> 5] >> (l & 31)) & 1u) << i;
@@ -229,7 +284,7 @@ __global__ void __launch_bounds__(WARPS * 32, 3) attend_labels_kernel(const Atte
             }
         }
 #pragma unroll
-        for (int v = 0; v < 2; ++v)                      // next pass's labels, in flight during this pass's attention
+        for (int v = 0; v < LV; ++v)                     // next pass's labels, in flight during this pass's attention
             if (base + LAB_SUB + v * 8 < p1)
                 raw[v] = __ldg(reinterpret_cast<const uint4 *>(lab + base + LAB_SUB + v * 8));
         int total;
@@ -237,22 +292,25 @@ __global__ void __launch_bounds__(WARPS * 32, 3) attend_labels_kernel(const Atte
         while (take) {
             const int i = __ffs(take) - 1;
             take &= take - 1;
-            s_rows[off++] = (uint16_t)(tid * 16 + i);
+            s_rows[off++] = (uint16_t)(tid * LPT + i);
         }
         __syncthreads();
+        stamp(p, 2);
         read_rows += total;
         const int tiles = (total + TILE_ROWS - 1) / TILE_ROWS;
         const int per = (tiles + WARPS - 1) / WARPS;
         const int t0 = min(warp * per, tiles), t1 = min(t0 + per, tiles);
         wa.run(t0, t1, [&](int row) { return row < total ? sub0 + (int)s_rows[row] : -1; });
         __syncthreads();                   // the list is rewritten by the next pass
+        stamp(p, 3);
     }
     if (tid == 0 && p.cnt_out) atomicAdd(p.cnt_out + head, read_rows);
     if (bad && p.status) atomicOr(p.status + head, SKV_ST_BAD_INDEX);
     float *red = reinterpret_cast<float *>(smem);
     wa.store_partial(red, warp, G);
     __syncthreads();
-    finish_head<__nv_bfloat16>(p, red, WARPS, head, split, s_eff, &s_flag);
+    stamp(p, 4);
+    finish_head<__nv_bfloat16>(p, red, WARPS, head, split, s_eff, &s_flag, red, WARPS * STAGES * 8192 / (PART_LD * 4));
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -321,7 +379,7 @@ __global__ void __launch_bounds__(128) attend_simple_kernel(const AttendParams p
         if (sub == 0) { r[128] = m[g]; r[129] = l[g]; }
     }
     __syncthreads();
-    finish_head<T>(p, red, 2 * WARPS, head, split, sh.s_eff, &s_flag);
+    finish_head<T>(p, red, 2 * WARPS, head, split, sh.s_eff, &s_flag, red, 2 * WARPS * GP);
 }
 
 // natural-log merge of caller-provided partials
@@ -360,11 +418,11 @@ static int launch_mma(const AttendParams &p, dim3 grid, cudaStream_t st) {
     return SKV_OK;
 }
 
-template <bool HI>
-static int launch_labels(const AttendParams &p, dim3 grid, cudaStream_t st) {
-    auto kern = attend_labels_kernel<MMA_WARPS, MMA_STAGES, HI>;
+template <bool HI, int STAGES, int LPT>
+static int launch_labels_as(const AttendParams &p, dim3 grid, cudaStream_t st) {
+    auto kern = attend_labels_kernel<MMA_WARPS, STAGES, HI, LPT>;
     static size_t configured[64] = {};
-    const size_t smem = MMA_SMEM + (size_t)p.sel_words * 4;
+    const size_t smem = (size_t)MMA_WARPS * STAGES * 8192 + (size_t)p.sel_words * 4;
     int dev = 0;
     SKV_CUDA_OK(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64) return SKV_E_RANGE;
@@ -372,9 +430,16 @@ static int launch_labels(const AttendParams &p, dim3 grid, cudaStream_t st) {
         SKV_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         configured[dev] = smem;
     }
-    kern<<<grid, MMA_WARPS * 32, smem, st>>>(p);
+    SKV_CUDA_OK(launch_pdl(kern, grid, dim3(MMA_WARPS * 32), smem, st, p));
     SKV_CUDA_OK(cudaGetLastError());
     return SKV_OK;
+}
+
+// Short position ranges (many CTAs per head) list 8 labels per thread, long ones 16.
+template <bool HI>
+static int launch_labels(const AttendParams &p, dim3 grid, cudaStream_t st) {
+    const bool lpt8 = (p.lab_stride + p.splits - 1) / p.splits <= MMA_WARPS * 32 * 8;
+    return lpt8 ? launch_labels_as<HI, MMA_STAGES, 8>(p, grid, st) : launch_labels_as<HI, MMA_STAGES, 16>(p, grid, st);
 }
 
 template <typename T>
@@ -391,6 +456,8 @@ static int launch_simple(const AttendParams &p, dim3 grid, cudaStream_t st) {
 
 using namespace skv;
 
+extern "C" void skv_debug_attend_probe(void *dev_ptr) { skv::g_attend_probe = static_cast<unsigned long long *>(dev_ptr); }
+
 extern "C" int skv_attend_splits(int heads) {
     if (heads <= 0) return SKV_E_RANGE;
     // One wave of CTAs, never more: a CTA's cost has a large fixed part (prologue, partial merge), so a
@@ -405,10 +472,9 @@ extern "C" int skv_attend_splits(int heads) {
 
 extern "C" int64_t skv_attend_workspace_bytes(int heads, int G, int d, int splits) {
     if (heads <= 0 || G <= 0 || d != HEAD_DIM || splits <= 0) return SKV_E_RANGE;
-    int64_t acc = (int64_t)heads * splits * G * d * 4;
-    int64_t ml = (int64_t)heads * splits * G * 2 * 4;
+    int64_t part = (int64_t)heads * splits * G * PART_LD * 4;
     int64_t tk = (((int64_t)heads * 4) + 255) / 256 * 256;
-    return acc + ml + tk;
+    return part + tk;
 }
 
 // mode bit 0 of `dtype >> 8` forces the CUDA-core path for bf16 (cross-checks)
@@ -432,14 +498,14 @@ extern "C" int skv_attend(const void *q, const void *K, const void *V, const int
         return SKV_E_ALIGN;
     AttendParams p;
     p.q = q; p.K = K; p.V = V; p.idx = idx; p.cnt = cnt; p.n_dev = n_dev; p.out = out; p.status = status;
-    p.part_acc = static_cast<float *>(workspace);
-    p.part_ml = p.part_acc + (int64_t)heads * splits * G * d;
-    p.ticket = reinterpret_cast<int32_t *>(p.part_ml + (int64_t)heads * splits * G * 2);
+    p.part = static_cast<float *>(workspace);
+    p.ticket = reinterpret_cast<int32_t *>(p.part + (int64_t)heads * splits * G * PART_LD);
     p.heads = heads; p.G = G;
     p.ksh = k_head_stride; p.ksr = k_row_stride; p.vsh = v_head_stride; p.vsr = v_row_stride;
     p.idx_stride = idx_stride; p.rows_limit = rows_limit; p.splits = splits;
     p.scale_log2 = scale * LOG2E;
     p.labels = nullptr; p.selbits = nullptr; p.cnt_out = nullptr; p.lab_stride = 0; p.sel_words = 0; p.C = 0;
+    p.probe = nullptr;
     dim3 grid(splits, heads);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (base == SKV_F32) return launch_simple<float>(p, grid, st);
@@ -465,13 +531,13 @@ extern "C" int skv_attend_labels(const void *q, const void *K, const void *V, co
         return SKV_E_ALIGN;
     AttendParams p;
     p.q = q; p.K = K; p.V = V; p.idx = nullptr; p.cnt = nullptr; p.n_dev = n_dev; p.out = out; p.status = status;
-    p.part_acc = static_cast<float *>(workspace);
-    p.part_ml = p.part_acc + (int64_t)heads * splits * G * d;
-    p.ticket = reinterpret_cast<int32_t *>(p.part_ml + (int64_t)heads * splits * G * 2);
+    p.part = static_cast<float *>(workspace);
+    p.ticket = reinterpret_cast<int32_t *>(p.part + (int64_t)heads * splits * G * PART_LD);
     p.heads = heads; p.G = G;
     p.ksh = k_head_stride; p.ksr = k_row_stride; p.vsh = v_head_stride; p.vsr = v_row_stride;
     p.idx_stride = 0; p.rows_limit = 0; p.splits = splits;
     p.scale_log2 = scale * LOG2E;
+    p.probe = g_attend_probe;
     p.labels = labels; p.selbits = selbits; p.cnt_out = cnt; p.lab_stride = label_stride;
     p.sel_words = C / 32 + 1; p.C = C;
     dim3 grid(splits, heads);
@@ -526,7 +592,7 @@ extern "C" int skv_attend_static(const void *q, const void *K, const void *V, co
     if (rc) return rc;
     // Earlier calls with other shapes left their partials here.  Only the ticket words have to start at
     // zero (partials are always written before they are read); they sit at the end of the layout.
-    unsigned char *tickets = static_cast<unsigned char *>(scratch) + (int64_t)heads * splits * G * (d + 2) * 4;
+    unsigned char *tickets = static_cast<unsigned char *>(scratch) + (int64_t)heads * splits * G * PART_LD * 4;
     SKV_CUDA_OK(cudaMemsetAsync(tickets, 0, (size_t)heads * 4, static_cast<cudaStream_t>(stream)));
     return skv_attend(q, K, V, idx, cnt, n_dev, out, scratch, status, heads, G, d, dtype, k_head_stride, k_row_stride,
                       v_head_stride, v_row_stride, idx_stride, rows_limit, splits, scale, stream);

@@ -29,6 +29,30 @@ static inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t
 
 int device_sm_count();
 int device_max_smem_optin();
+bool pdl_enabled();
+
+// Programmatic dependent launch.  A kernel launched through launch_pdl may start while the kernel before it
+// on the stream is still running; everything it reads from that kernel (and every write it makes) must come
+// after pdl_wait(), which returns once the earlier kernel has completed and its writes are visible.  What it
+// does before the wait - loading data no kernel of the same step writes - overlaps the earlier kernel's tail.
+// pdl_trigger() in the earlier kernel allows the later one to be scheduled; without it the later kernel
+// starts when the earlier one ends, as in a plain launch.  Every kernel launched this way executes
+// pdl_wait() before it finishes, so that completion stays transitive along the stream.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+static inline cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                     Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
 
 // ---------------------------------------------------------------------------------------------
 __device__ __forceinline__ float warp_sum(float v) {

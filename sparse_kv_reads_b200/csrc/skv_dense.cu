@@ -58,6 +58,8 @@ __global__ void __launch_bounds__(128) qk_rope_cache_kernel(const __nv_bfloat16 
                                                             __nv_bfloat16 *v_cache, int B, int H, int H_kv,
                                                             int64_t cache_b_stride, int64_t cache_h_stride,
                                                             int64_t cache_row_stride, float eps) {
+    pdl_wait();
+    pdl_trigger();
     const int lane = threadIdx.x & 31;
     const int item = blockIdx.x * 4 + (threadIdx.x >> 5);
     const int per = H + 2 * H_kv;
@@ -139,12 +141,12 @@ extern "C" int skv_qk_rope_cache(const void *qkv, const void *q_norm_w, const vo
         !aligned16(sin_table) || cache_row_stride % 8 || cache_head_stride % 8 || cache_batch_stride % 8)
         return SKV_E_ALIGN;
     const int items = B * (H + 2 * H_kv);
-    qk_rope_cache_kernel<<<(items + 3) / 4, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+    SKV_CUDA_OK(launch_pdl(qk_rope_cache_kernel, dim3((items + 3) / 4), dim3(128), 0, static_cast<cudaStream_t>(stream),
         static_cast<const __nv_bfloat16 *>(qkv), static_cast<const __nv_bfloat16 *>(q_norm_w),
         static_cast<const __nv_bfloat16 *>(k_norm_w), static_cast<const __nv_bfloat16 *>(cos_table),
         static_cast<const __nv_bfloat16 *>(sin_table), pos_dev, static_cast<__nv_bfloat16 *>(q_out),
         static_cast<__nv_bfloat16 *>(k_cache), static_cast<__nv_bfloat16 *>(v_cache), B, H, H_kv, cache_batch_stride,
-        cache_head_stride, cache_row_stride, eps);
+        cache_head_stride, cache_row_stride, eps));
     SKV_CUDA_OK(cudaGetLastError());
     return SKV_OK;
 }

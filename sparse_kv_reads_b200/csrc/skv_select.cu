@@ -134,6 +134,7 @@ __global__ void __launch_bounds__(SEL_THREADS) score_pick_kernel(const SelectPar
     const int per = (((n_c + nb - 1) / nb) + 3) & ~3;              // clusters per scoring CTA
     const float inv_per = 1.0f / (float)max(per, 1);
     if (b == 0) stamp(p, h, 0);
+    if (!scoring) { pdl_wait(); pdl_trigger(); }
 
     if (scoring) {
         const int c_lo = min(b * per, n_c), c_hi = min(c_lo + per, n_c), mine = c_hi - c_lo;
@@ -183,6 +184,8 @@ __global__ void __launch_bounds__(SEL_THREADS) score_pick_kernel(const SelectPar
             const int c = c_lo + wid;
             if (c < c_hi) rawf = __ldg(reinterpret_cast<const float4 *>(p.st.sum_dir + ((int64_t)h * C + c) * d + lane * 4));
         }
+        pdl_wait();                                        // the query comes from the kernel before this one
+        pdl_trigger();
         for (int i = tid; i < G * d; i += SEL_THREADS) sq[i] = load_as_float(q + i);
         __syncthreads();
         if (q8 && TC) {
@@ -617,7 +620,7 @@ extern "C" int skv_select(const skv_state *st, const void *q, int dtype, int G, 
     int ctas = 2 * device_sm_count() / st->heads;
     ctas = ctas < 1 ? 1 : (ctas > SEL_MAX_CTAS ? SEL_MAX_CTAS : ctas);
     if (shared_in) ctas = 1;
-    kern<<<dim3(ctas, st->heads), SEL_THREADS, smem, s>>>(p);
+    SKV_CUDA_OK(launch_pdl(kern, dim3(ctas, st->heads), dim3(SEL_THREADS), smem, s, p));
     if (idx) list_kernel<<<st->heads, 512, (st->C / 32 + 1) * 4, s>>>(p);
     SKV_CUDA_OK(cudaGetLastError());
     return SKV_OK;

@@ -10,6 +10,8 @@ independent heads for every attention kernel).  Modes: ``"cluster"`` (aliases ``
 
 from __future__ import annotations
 
+import os
+
 import ctypes
 import math
 
@@ -77,7 +79,8 @@ class GraphDecoder:
                  window: int = 64, delta: float = 0.03, check_every: int = 16, partition: str = "kmeans",
                  C_init: int | None = None, split_factor: float | None = None, refit_every: int = 0,
                  grow_cap: bool = False, reset_at: int = 0, summary_bits: int = 8, cap_keys: float = 0.0,
-                 fused_insert: bool = True, var_factor: float = 0.0, var_min: int = 8, fused_dense: bool = True, **_):
+                 fused_insert: bool = True, var_factor: float = 0.0, var_min: int = 8, fused_dense: bool = True,
+                 own_gemv: bool = True, **_):
         cfg = model.cfg
         # no slot count given: 1,024 slots, 256 fitted at the prompt, split over twice the mean size
         # (ssa/models/graph_decode.py:38-43)
@@ -118,6 +121,8 @@ class GraphDecoder:
             and dev.type == "cuda"
         if self.fused_dense:
             self._fuse_weights()
+        # ... and, up to 8 sequences, its projections as the library's matrix-vector products
+        self.own_gemv = own_gemv and os.environ.get("SKV_OWN_GEMV", "1") != "0"
         self.fused_insert = fused_insert and mode == "cluster" and window >= 1
         self.insert_all = None
 
@@ -181,6 +186,18 @@ class GraphDecoder:
                 self._wgu.append(wgu)
 
     def _body_fused(self) -> torch.Tensor:
+        # the cluster state is written once per step, ahead of every layer, so the selection and attention
+        # launches may overlap the tails of the launches before them
+        L = lib()
+        L.skv_set_overlap(1 if self.insert_all is not None or self.mode == "dense" else 0)
+        try:
+            return self._layers_fused()
+        finally:
+            L.skv_set_overlap(0)
+
+    def _layers_fused(self) -> torch.Tensor:
+        if self.B <= 8 and self.own_gemv:
+            return self._layers_gemv()
         m, H, H_kv, d, B = self.model, self.H, self.H_kv, self.d, self.B
         L = lib()
         st = stream_ptr(self.tok.device)
@@ -215,6 +232,60 @@ class GraphDecoder:
             act = torch.empty(B, gu.shape[1] // 2, dtype=gu.dtype, device=gu.device)
             check(L.skv_silu_mul(gu.data_ptr(), act.data_ptr(), B, act.shape[1], st), "skv_silu_mul")
             delta = f.tp.all_reduce(F.linear(act, f.down.weight))
+        check(L.skv_add_rmsnorm(h.data_ptr(), delta.data_ptr(), m.final_norm.weight.data_ptr(), xn.data_ptr(), B,
+                                hidden, eps, st), "skv_add_rmsnorm")
+        return m.logits(xn.view(B, 1, hidden))
+
+    def _layers_gemv(self) -> torch.Tensor:
+        """The layers with the library's own matrix-vector products (up to 8 sequences): a layer is seven
+        launches - q/k/v product with the residual add and norm folded into its input, QK-norm + rotary +
+        cache write, selection, attention, output product, gate/up product (add and norm folded in), down
+        product (SiLU x up folded in) - each requesting its weights while the launch ahead of it finishes."""
+        m, H, H_kv, d, B = self.model, self.H, self.H_kv, self.d, self.B
+        L = lib()
+        st = stream_ptr(self.tok.device)
+        torch.add(self.pos, 1, out=self.n_dev)
+        if self.insert_all is not None:
+            self.insert_all(self.n_dev)
+        h = m.embed(self.tok).view(B, -1).contiguous()
+        hidden = h.shape[1]
+        eps = m.final_norm.eps
+        h2 = torch.empty_like(h)                           # the residual stream alternates between two buffers
+        dev, dt = h.device, h.dtype
+        qh = torch.empty(B * H, d, dtype=dt, device=dev)
+        nqkv, ngu = self._wqkv[0].shape[0], self._wgu[0].shape[0]
+        inter = ngu // 2
+        qkv = torch.empty(B, nqkv, dtype=dt, device=dev)
+        o = torch.empty(B, hidden, dtype=dt, device=dev)
+        gu = torch.empty(B, ngu, dtype=dt, device=dev)
+        delta = None
+
+        def gemv(W, y, mode, x=None, h_in=None, dl=None, g=None, h_out=None):
+            check(L.skv_gemv(W.data_ptr(), W.shape[0], W.shape[1], y.data_ptr(), B, mode,
+                             None if x is None else x.data_ptr(), None if h_in is None else h_in.data_ptr(),
+                             None if dl is None else dl.data_ptr(), None if g is None else g.data_ptr(),
+                             None if h_out is None else h_out.data_ptr(), eps, st), "skv_gemv")
+
+        for i, layer in enumerate(m.layers):
+            a, f = layer.attn, layer.ffn
+            gemv(self._wqkv[i], qkv, 1, h_in=h, dl=delta, g=layer.norm1.weight, h_out=h2)
+            kc, vc = self.cache.k[i], self.cache.v[i]
+            check(L.skv_qk_rope_cache(qkv.data_ptr(), a.q_norm.weight.data_ptr(), a.k_norm.weight.data_ptr(),
+                                      m.rope_cos.data_ptr(), m.rope_sin.data_ptr(), self.pos.data_ptr(),
+                                      qh.data_ptr(), kc.data_ptr(), vc.data_ptr(), B, H, H_kv, d, kc.stride(0),
+                                      kc.stride(1), kc.stride(2), a.q_norm.eps, st), "skv_qk_rope_cache")
+            if self.mode == "dense":
+                out = self.attn[i](qh, self._heads(kc), self._heads(vc), self.n_dev)
+            else:
+                out = self.attn[i].step(qh, self._heads(kc), self._heads(vc), self.n_dev,
+                                        insert=self.insert_all is None)
+            gemv(a.o.weight, o, 0, x=out)
+            o_red = a.tp.all_reduce(o)
+            gemv(self._wgu[i], gu, 1, h_in=h2, dl=o_red, g=layer.norm2.weight, h_out=h)
+            dn = torch.empty(B, hidden, dtype=dt, device=dev)
+            gemv(f.down.weight, dn, 2, x=gu)
+            delta = f.tp.all_reduce(dn)
+        xn = torch.empty_like(h)
         check(L.skv_add_rmsnorm(h.data_ptr(), delta.data_ptr(), m.final_norm.weight.data_ptr(), xn.data_ptr(), B,
                                 hidden, eps, st), "skv_add_rmsnorm")
         return m.logits(xn.view(B, 1, hidden))

@@ -74,7 +74,7 @@ def test_attend_rejects_bad_arguments(L):
     assert call(heads=0) == -5 and call(splits=0) == -5
     assert L.skv_attend_splits(8) == 37 and L.skv_attend_splits(0) == -5        # one wave of 148 SMs
     assert L.skv_attend_splits(64) == 6 and L.skv_attend_splits(256) == 1 and L.skv_attend_splits(1000) == 1
-    assert L.skv_attend_workspace_bytes(8, 2, 128, 37) == 8 * 37 * 2 * 130 * 4 + 256
+    assert L.skv_attend_workspace_bytes(8, 2, 128, 37) == 8 * 37 * 2 * 132 * 4 + 256
     assert L.skv_attend_workspace_bytes(8, 2, 64, 37) == -5
 
 

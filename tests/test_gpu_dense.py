@@ -73,3 +73,41 @@ def test_silu_mul():
     want = torch.nn.functional.silu(gu[:, :inter]) * gu[:, inter:]
     torch.testing.assert_close(out.float(), want.float(), rtol=1e-2, atol=1e-2)
 
+
+
+@pytest.mark.parametrize("B", [1, 2, 3, 8])
+def test_gemv_with_the_three_input_modes(B):
+    """y = x W^T against float32 matmul of the same bf16 operands, for the projection shapes of the two models
+    and a few awkward ones (rows not a multiple of the CTA count, one row, a long row)."""
+    g = torch.Generator().manual_seed(B)
+    L = lib()
+    for N, K in ((4096, 1024), (1024, 2048), (6144, 1024), (1024, 3072), (1000, 2560), (1, 64)) + (((300, 9728),) if B <= 4 else ()):
+        W = (torch.randn(N, K, generator=g) / K ** 0.5).to(torch.bfloat16).to(DEV)
+        x = torch.randn(B, K, generator=g).to(torch.bfloat16).to(DEV)
+        y = torch.full((B, N), 7.0, dtype=torch.bfloat16, device=DEV)
+        check(L.skv_gemv(W.data_ptr(), N, K, y.data_ptr(), B, 0, x.data_ptr(), None, None, None, None, 0.0, stream()),
+              "skv_gemv")
+        want = x.float() @ W.float().T
+        torch.testing.assert_close(y.float(), want, rtol=1e-2, atol=1e-2)
+        # mode 1: residual add + RMSNorm feeding the product, h_out out of place
+        h = torch.randn(B, K, generator=g).to(torch.bfloat16).to(DEV)
+        delta = torch.randn(B, K, generator=g).to(torch.bfloat16).to(DEV)
+        gw = (1 + 0.1 * torch.randn(K, generator=g)).to(torch.bfloat16).to(DEV)
+        for dl in (delta, None):
+            h_out = torch.zeros_like(h)
+            check(L.skv_gemv(W.data_ptr(), N, K, y.data_ptr(), B, 1, None, h.data_ptr(),
+                             None if dl is None else dl.data_ptr(), gw.data_ptr(), h_out.data_ptr(), 1e-6, stream()),
+                  "skv_gemv")
+            hs = h + dl if dl is not None else h
+            assert torch.equal(h_out, hs)
+            xn = torch.empty_like(h)
+            check(L.skv_add_rmsnorm(hs.clone().data_ptr(), None, gw.data_ptr(), xn.data_ptr(), B, K, 1e-6, stream()),
+                  "skv_add_rmsnorm")
+            torch.testing.assert_close(y.float(), xn.float() @ W.float().T, rtol=2e-2, atol=2e-2)
+        # mode 2: silu(gate) * up feeding the product
+        gu = torch.randn(B, 2 * K, generator=g).to(torch.bfloat16).to(DEV)
+        act = torch.empty(B, K, dtype=torch.bfloat16, device=DEV)
+        check(L.skv_silu_mul(gu.data_ptr(), act.data_ptr(), B, K, stream()), "skv_silu_mul")
+        check(L.skv_gemv(W.data_ptr(), N, K, y.data_ptr(), B, 2, gu.data_ptr(), None, None, None, None, 0.0, stream()),
+              "skv_gemv")
+        torch.testing.assert_close(y.float(), act.float() @ W.float().T, rtol=1e-2, atol=1e-2)
