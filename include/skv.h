@@ -271,6 +271,9 @@ int skv_silu_mul(const void *gate_up, void *out, int B, int inter, void *stream)
  * skv_set_overlap: the weights are requested before the wait for the launch ahead. */
 int skv_gemv(const void *W, int N, int K, void *y, int B, int mode, const void *x, const void *h_in,
              const void *delta, const void *norm_w, void *h_out, float eps, void *stream);
+/* 1 when skv_gemv serves this shape well; 0 when it cannot run it or when the inputs every CTA rebuilds would
+ * outweigh the weights it multiplies them with (many sequences of a long row: use a library GEMM there). */
+int skv_gemv_supported(int N, int K, int B, int mode);
 
 #ifdef __cplusplus
 }

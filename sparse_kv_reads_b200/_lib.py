@@ -20,7 +20,7 @@ ST_NO_SLOT, ST_SPLIT_TOO_BIG, ST_BAD_INDEX = 1, 2, 4
 EXPORTS = ("skv_version", "skv_error_string", "skv_last_cuda_error", "skv_attend_splits",
            "skv_attend_workspace_bytes", "skv_attend", "skv_attend_static", "skv_attend_labels", "skv_merge", "skv_select_workspace_bytes", "skv_select", "skv_debug_select_probe", "skv_debug_attend_probe", "skv_set_overlap", "skv_insert",
            "skv_insert_max_members", "skv_fit_workspace_bytes", "skv_fit", "skv_rebin",
-           "skv_add_rmsnorm", "skv_qk_rope_cache", "skv_silu_mul", "skv_gemv")
+           "skv_add_rmsnorm", "skv_qk_rope_cache", "skv_silu_mul", "skv_gemv", "skv_gemv_supported")
 
 
 class SkvError(RuntimeError):
@@ -86,6 +86,8 @@ def _declare(lib) -> None:
     lib.skv_qk_rope_cache.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i64, i64, i64, f32, vp]
     lib.skv_silu_mul.restype = i32
     lib.skv_silu_mul.argtypes = [vp, vp, i32, i32, vp]
+    lib.skv_gemv_supported.restype = i32
+    lib.skv_gemv_supported.argtypes = [i32, i32, i32, i32]
     lib.skv_gemv.restype = i32
     lib.skv_gemv.argtypes = [vp, i32, i32, vp, i32, i32, vp, vp, vp, vp, vp, f32, vp]
     lib.skv_rebin.restype = i32

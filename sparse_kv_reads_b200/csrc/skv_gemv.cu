@@ -13,9 +13,13 @@
 //           (CTA 0 also stores h_out, out of place because the other CTAs still read h_in);
 //   mode 2  x = bf16(bf16(silu(gate)) * up) from gate_up[B, 2K].
 // The roundings are those of the separate kernels (skv_dense.cu) and of the unfused module forward.
-// Warp w of the CTA then takes rows w, w + 8, ... of the slab: a lane multiplies 16-byte pieces of the row with
-// the matching pieces of every sequence's input, and the warp reduces the B sums.
-#include "skv_common.cuh"
+// The products themselves run on the tensor cores where K is a multiple of 64: 16 rows of the slab x 16 inputs
+// are one mma.sync m16n8k16 A tile (ldmatrix from the slab, stored with its 16-byte pieces XOR-swizzled by the
+// row so that the eight rows of a matrix fall into different banks), the B tile holds up to 8 sequences, so 1
+// and 8 sequences cost the same.  The 8 warps share the slab's 16-row tiles and, when there are fewer than 8
+// tiles, ranges of K; partial sums meet in shared memory.  Other K take a plain float path: warp w multiplies
+// rows w, w + 8, ... piece by piece with every sequence's input and reduces the sums over its lanes.
+#include "skv_attend_core.cuh"
 
 namespace skv {
 
@@ -34,17 +38,19 @@ struct GemvParams {
 
 __device__ __forceinline__ float bf16r(float x) { return __bfloat162float(__float2bfloat16(x)); }
 
-template <int BP>
+template <int BP, bool TC>
 __global__ void __launch_bounds__(GEMV_THREADS) gemv_kernel(const GemvParams p) {
     extern __shared__ __align__(16) unsigned char smem[];
     __shared__ float s_part[8][GEMV_WARPS];
+    __shared__ __align__(16) float s_red[GEMV_WARPS][16 * 8];
     const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
     const int K = p.K, kv = K >> 3;                         // 16-byte pieces per row
+    const int xld = TC ? K + 8 : K;                         // input row stride: 16 bytes of padding spread the banks
     const int r0 = blockIdx.x * p.rows_per_cta;
     const int R = min(p.rows_per_cta, p.N - r0);
     __nv_bfloat16 *ws = reinterpret_cast<__nv_bfloat16 *>(smem);                      // [rows_per_cta][K]
-    __nv_bfloat16 *xs = ws + (size_t)p.rows_per_cta * K;                              // [BP][K]
-    __nv_bfloat16 *gs = xs + (size_t)BP * K;                                          // [K] (mode 1)
+    __nv_bfloat16 *xs = ws + (size_t)p.rows_per_cta * K;                              // [BP][xld]
+    __nv_bfloat16 *gs = xs + (size_t)BP * xld;                                        // [K] (mode 1)
 
     // 1. the slab (and the norm weights): requested before anything else, also before the producer ends
     {
@@ -52,8 +58,17 @@ __global__ void __launch_bounds__(GEMV_THREADS) gemv_kernel(const GemvParams p) 
             for (int c = tid; c < kv; c += GEMV_THREADS) cp_async16(gs + c * 8, p.g + c * 8, 16);
         cp_async_commit();                                  // group 0: norm weights (empty otherwise)
         const __nv_bfloat16 *src = p.W + (size_t)r0 * K;
-        const int pieces = R * kv;
-        for (int c = tid; c < pieces; c += GEMV_THREADS) cp_async16(ws + (size_t)c * 8, src + (size_t)c * 8, 16);
+        if (TC) {                                           // pieces swizzled by their row
+            const unsigned inv = (unsigned)((0x100000000ull + kv - 1) / kv);   // c / kv by multiplication: exact for c < 2^16
+            const int pieces = R * kv;
+            for (int c = tid; c < pieces; c += GEMV_THREADS) {
+                const int r = (int)__umulhi((unsigned)c, inv), col = c - r * kv;
+                cp_async16(ws + (size_t)r * K + ((col ^ (r & 7)) << 3), src + (size_t)c * 8, 16);
+            }
+        } else {
+            const int pieces = R * kv;
+            for (int c = tid; c < pieces; c += GEMV_THREADS) cp_async16(ws + (size_t)c * 8, src + (size_t)c * 8, 16);
+        }
         cp_async_commit();                                  // group 1: the slab
     }
     pdl_wait();
@@ -65,7 +80,7 @@ __global__ void __launch_bounds__(GEMV_THREADS) gemv_kernel(const GemvParams p) 
             const int b = c / kv, v = c - b * kv;
             uint4 val = make_uint4(0u, 0u, 0u, 0u);
             if (b < p.B) val = __ldg(reinterpret_cast<const uint4 *>(p.x + (size_t)b * K + v * 8));
-            *reinterpret_cast<uint4 *>(xs + (size_t)b * K + v * 8) = val;
+            *reinterpret_cast<uint4 *>(xs + (size_t)b * xld + v * 8) = val;
         }
     } else if (p.mode == 2) {
         for (int c = tid; c < BP * kv; c += GEMV_THREADS) {
@@ -81,7 +96,7 @@ __global__ void __launch_bounds__(GEMV_THREADS) gemv_kernel(const GemvParams p) 
 #pragma unroll
                 for (int k = 0; k < 8; ++k) o[k] = __float2bfloat16(0.f);
             }
-            *reinterpret_cast<uint4 *>(xs + (size_t)b * K + v * 8) = *reinterpret_cast<const uint4 *>(o);
+            *reinterpret_cast<uint4 *>(xs + (size_t)b * xld + v * 8) = *reinterpret_cast<const uint4 *>(o);
         }
     } else {
         // BP sequences share the 8 warps: wpr warps per sequence, each a contiguous range of the row
@@ -111,12 +126,12 @@ __global__ void __launch_bounds__(GEMV_THREADS) gemv_kernel(const GemvParams p) 
                 }
 #pragma unroll
                 for (int i = 0; i < 8; ++i) ss = fmaf(a[i], a[i], ss);
-                *reinterpret_cast<uint4 *>(xs + (size_t)b * K + v * 8) = *reinterpret_cast<const uint4 *>(o);
+                *reinterpret_cast<uint4 *>(xs + (size_t)b * xld + v * 8) = *reinterpret_cast<const uint4 *>(o);
                 if (blockIdx.x == 0 && p.h_out)
                     *reinterpret_cast<uint4 *>(p.h_out + (size_t)b * K + v * 8) = *reinterpret_cast<const uint4 *>(o);
             }
         } else if (b < BP) {
-            for (int v = v0 + lane; v < v1; v += 32) *reinterpret_cast<uint4 *>(xs + (size_t)b * K + v * 8) = make_uint4(0u, 0u, 0u, 0u);
+            for (int v = v0 + lane; v < v1; v += 32) *reinterpret_cast<uint4 *>(xs + (size_t)b * xld + v * 8) = make_uint4(0u, 0u, 0u, 0u);
         }
         ss = warp_sum(ss);
         if (lane == 0) s_part[wid / wpr][sub] = ss;
@@ -129,12 +144,12 @@ __global__ void __launch_bounds__(GEMV_THREADS) gemv_kernel(const GemvParams p) 
             const float inv = rsqrtf(tot / (float)K + p.eps);
             for (int v = v0 + lane; v < v1; v += 32) {
                 float a[8], g[8];
-                load8(xs + (size_t)b * K + v * 8, a);
+                load8(xs + (size_t)b * xld + v * 8, a);
                 load8(gs + v * 8, g);
                 __align__(16) __nv_bfloat16 o[8];
 #pragma unroll
                 for (int i = 0; i < 8; ++i) o[i] = __float2bfloat16(a[i] * inv * g[i]);
-                *reinterpret_cast<uint4 *>(xs + (size_t)b * K + v * 8) = *reinterpret_cast<const uint4 *>(o);
+                *reinterpret_cast<uint4 *>(xs + (size_t)b * xld + v * 8) = *reinterpret_cast<const uint4 *>(o);
             }
         }
     }
@@ -142,6 +157,61 @@ __global__ void __launch_bounds__(GEMV_THREADS) gemv_kernel(const GemvParams p) 
     __syncthreads();
 
     // 3. rows of the slab
+    if (TC) {
+        const int ntiles = (R + 15) >> 4;
+        const int ks = ntiles >= GEMV_WARPS ? 1 : GEMV_WARPS / ntiles;      // ranges of K per tile
+        const int steps = K >> 4, per = (steps + ks - 1) / ks;
+        const int n = lane >> 2, kq = 2 * (lane & 3);                        // B fragment: sequence n, inputs kq, kq + 1
+        const __nv_bfloat16 *xrow = xs + (size_t)n * xld + kq;
+        const int arow = (lane & 7) + ((lane >> 3) & 1) * 8, apiece = lane >> 4;
+        for (int item = wid; item < ntiles * ks; item += GEMV_WARPS) {
+            const int t = item % ntiles, sp = item / ntiles;
+            float acc[4] = {0.f, 0.f, 0.f, 0.f};
+            const int row = min(t * 16 + arow, R - 1);      // rows past the slab repeat its last row; their sums are dropped
+            const __nv_bfloat16 *abase = ws + (size_t)row * K;
+            const int s1 = min((sp + 1) * per, steps);
+#pragma unroll 4
+            for (int st = sp * per; st < s1; ++st) {
+                uint32_t a[4];
+                ldmatrix_x4(a, abase + (((2 * st + apiece) ^ (row & 7)) << 3));
+                uint32_t b0 = 0u, b1 = 0u;
+                if (n < BP) {
+                    b0 = *reinterpret_cast<const uint32_t *>(xrow + st * 16);
+                    b1 = *reinterpret_cast<const uint32_t *>(xrow + st * 16 + 8);
+                }
+                mma_bf16_16816(acc, a, b0, b1);
+            }
+            // D fragment: rows lane / 4 and + 8 of the tile, sequences kq and kq + 1
+            if (ks == 1) {
+                const int ra = r0 + t * 16 + (lane >> 2), rb = ra + 8;
+                if (kq < p.B) {
+                    if (ra < r0 + R) p.y[(size_t)kq * p.N + ra] = __float2bfloat16(acc[0]);
+                    if (rb < r0 + R) p.y[(size_t)kq * p.N + rb] = __float2bfloat16(acc[2]);
+                }
+                if (kq + 1 < p.B) {
+                    if (ra < r0 + R) p.y[(size_t)(kq + 1) * p.N + ra] = __float2bfloat16(acc[1]);
+                    if (rb < r0 + R) p.y[(size_t)(kq + 1) * p.N + rb] = __float2bfloat16(acc[3]);
+                }
+            } else {
+                float *d = s_red[item];                    // [row in tile][sequence]
+                d[(lane >> 2) * 8 + kq] = acc[0];
+                d[(lane >> 2) * 8 + kq + 1] = acc[1];
+                d[((lane >> 2) + 8) * 8 + kq] = acc[2];
+                d[((lane >> 2) + 8) * 8 + kq + 1] = acc[3];
+            }
+        }
+        if (ks > 1) {                                       // fewer than 8 tiles: one pass, sum the K ranges
+            __syncthreads();
+            for (int o = tid; o < ntiles * 128; o += GEMV_THREADS) {
+                const int t = o >> 7, e = o & 127, rr = e >> 3, b = e & 7;
+                float sum = 0.f;
+                for (int sp = 0; sp < ks; ++sp) sum += s_red[sp * ntiles + t][e];
+                const int rg = t * 16 + rr;
+                if (rg < R && b < p.B) p.y[(size_t)b * p.N + r0 + rg] = __float2bfloat16(sum);
+            }
+        }
+        return;
+    }
     for (int r = wid; r < R; r += GEMV_WARPS) {
         float acc[BP];
 #pragma unroll
@@ -167,9 +237,56 @@ __global__ void __launch_bounds__(GEMV_THREADS) gemv_kernel(const GemvParams p) 
     }
 }
 
+struct GemvPlan {
+    int BP, rows;
+    bool tc, worthwhile;
+    size_t smem;
+};
+
+// Rows per CTA and shared memory.  Two CTAs share an SM so that one computes while the other loads; the slab
+// takes what the inputs leave, at most 96 KB, and one wave of CTAs covers the matrix where that is enough.
+// `worthwhile` is false when the inputs every CTA rebuilds outweigh the slab it multiplies them with (many
+// sequences of a long row): a library GEMM serves those shapes better.
+static int plan_gemv(int N, int K, int B, int mode, GemvPlan &pl) {
+    if (B < 1 || B > 8 || N < 1 || K < 8 || K % 8 || mode < 0 || mode > 2) return SKV_E_RANGE;
+    pl.BP = B <= 1 ? 1 : (B <= 2 ? 2 : (B <= 4 ? 4 : 8));
+    pl.tc = K % 64 == 0 && pl.BP > 1;                 // one sequence: the float path is as fast and needs no reduction
+    const size_t row = (size_t)K * 2;
+    const size_t fixed = (size_t)pl.BP * (row + (pl.tc ? 16 : 0)) + (mode == 1 ? row : 0);   // inputs (+ norm weights)
+    const size_t optin = (size_t)device_max_smem_optin();
+    const size_t per_cta = optin / 2 - 2048;
+    size_t slab = per_cta > fixed ? per_cta - fixed : 0;
+    if (slab > (size_t)GEMV_SLAB_MAX) slab = GEMV_SLAB_MAX;
+    pl.worthwhile = slab >= 2 * fixed && slab >= row;
+    if (slab < row) slab = optin > fixed + row + 1024 ? row : 0;          // one row, one CTA per SM
+    if (!slab) return SKV_E_TOO_LARGE;
+    // One CTA per SM where the matrix fits one such wave; else whole rounds of two CTAs per SM, so that no
+    // round is left nearly empty.
+    const int sms = device_sm_count();
+    const int fit = (int)(slab / row);
+    int rows = (N + sms - 1) / sms;
+    if (rows > fit) {
+        const int64_t round = 2LL * sms * fit;
+        const int k = (int)((N + round - 1) / round);
+        rows = (N + 2 * sms * k - 1) / (2 * sms * k);
+        // the CTAs of a round load together and compute together, so memory idles while they compute: beyond
+        // two rounds (one with several sequences) a library GEMM streamed faster when measured on B200
+        // (99.6 MB: 18 us against 25 us)
+        if (k > (pl.BP == 1 ? 2 : 1)) pl.worthwhile = false;
+    }
+    pl.rows = rows;
+    pl.smem = (size_t)rows * row + fixed;
+    return pl.smem > optin ? SKV_E_TOO_LARGE : SKV_OK;
+}
+
 }  // namespace skv
 
 using namespace skv;
+
+extern "C" int skv_gemv_supported(int N, int K, int B, int mode) {
+    GemvPlan pl;
+    return plan_gemv(N, K, B, mode, pl) == SKV_OK && pl.worthwhile ? 1 : 0;
+}
 
 extern "C" int skv_gemv(const void *W, int N, int K, void *y, int B, int mode, const void *x, const void *h_in,
                         const void *delta, const void *norm_w, void *h_out, float eps, void *stream) {
@@ -180,15 +297,12 @@ extern "C" int skv_gemv(const void *W, int N, int K, void *y, int B, int mode, c
     if (!aligned16(W) || !aligned16(y) || (x && !aligned16(x)) || (h_in && !aligned16(h_in)) ||
         (delta && !aligned16(delta)) || (norm_w && !aligned16(norm_w)) || (h_out && !aligned16(h_out)))
         return SKV_E_ALIGN;
-    const int BP = B <= 1 ? 1 : (B <= 2 ? 2 : (B <= 4 ? 4 : 8));
-    const size_t row = (size_t)K * 2;
-    if (row > (size_t)GEMV_SLAB_MAX) return SKV_E_TOO_LARGE;
-    // one wave of CTAs where the slab allows it, else slabs of the largest size (two of them share an SM)
-    int rows = (N + device_sm_count() - 1) / device_sm_count();
-    const int fit = (int)(GEMV_SLAB_MAX / row);
-    if (rows > fit) rows = fit;
-    const size_t smem = (size_t)rows * row + (size_t)BP * row + (mode == 1 ? row : 0);
-    if (smem > (size_t)device_max_smem_optin()) return SKV_E_TOO_LARGE;
+    GemvPlan pl;
+    const int rc = plan_gemv(N, K, B, mode, pl);
+    if (rc) return rc;
+    const int BP = pl.BP, rows = pl.rows;
+    const bool tc = pl.tc;
+    const size_t smem = pl.smem;
     GemvParams p;
     p.W = static_cast<const __nv_bfloat16 *>(W); p.y = static_cast<__nv_bfloat16 *>(y);
     p.N = N; p.K = K; p.B = B; p.mode = mode; p.rows_per_cta = rows;
@@ -196,9 +310,10 @@ extern "C" int skv_gemv(const void *W, int N, int K, void *y, int B, int mode, c
     p.delta = static_cast<const __nv_bfloat16 *>(delta); p.g = static_cast<const __nv_bfloat16 *>(norm_w);
     p.h_out = static_cast<__nv_bfloat16 *>(h_out); p.eps = eps;
     typedef void (*Kern)(const GemvParams);
-    const int bi = BP == 1 ? 0 : (BP == 2 ? 1 : (BP == 4 ? 2 : 3));
-    const Kern table[4] = {gemv_kernel<1>, gemv_kernel<2>, gemv_kernel<4>, gemv_kernel<8>};
-    static size_t configured[64][4] = {};
+    const int bi = (BP == 1 ? 0 : (BP == 2 ? 1 : (BP == 4 ? 2 : 3))) + (tc ? 4 : 0);
+    const Kern table[8] = {gemv_kernel<1, false>, gemv_kernel<2, false>, gemv_kernel<4, false>, gemv_kernel<8, false>,
+                           gemv_kernel<1, true>,  gemv_kernel<2, true>,  gemv_kernel<4, true>,  gemv_kernel<8, true>};
+    static size_t configured[64][8] = {};
     int dev = 0;
     SKV_CUDA_OK(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64) return SKV_E_RANGE;

@@ -251,6 +251,7 @@ class GraphDecoder:
         hidden = h.shape[1]
         eps = m.final_norm.eps
         h2 = torch.empty_like(h)                           # the residual stream alternates between two buffers
+        buf_a, buf_b = h, h2
         dev, dt = h.device, h.dtype
         qh = torch.empty(B * H, d, dtype=dt, device=dev)
         nqkv, ngu = self._wqkv[0].shape[0], self._wgu[0].shape[0]
@@ -260,15 +261,32 @@ class GraphDecoder:
         gu = torch.empty(B, ngu, dtype=dt, device=dev)
         delta = None
 
+        xn = torch.empty_like(h)
+
         def gemv(W, y, mode, x=None, h_in=None, dl=None, g=None, h_out=None):
-            check(L.skv_gemv(W.data_ptr(), W.shape[0], W.shape[1], y.data_ptr(), B, mode,
-                             None if x is None else x.data_ptr(), None if h_in is None else h_in.data_ptr(),
-                             None if dl is None else dl.data_ptr(), None if g is None else g.data_ptr(),
-                             None if h_out is None else h_out.data_ptr(), eps, st), "skv_gemv")
+            N, K = W.shape
+            if L.skv_gemv_supported(N, K, B, mode):
+                check(L.skv_gemv(W.data_ptr(), N, K, y.data_ptr(), B, mode,
+                                 None if x is None else x.data_ptr(), None if h_in is None else h_in.data_ptr(),
+                                 None if dl is None else dl.data_ptr(), None if g is None else g.data_ptr(),
+                                 None if h_out is None else h_out.data_ptr(), eps, st), "skv_gemv")
+                return h_out
+            # shapes the library product does not serve well: the separate element-wise kernel, then cuBLAS
+            if mode == 1:                                   # in place: the residual stays in h_in
+                check(L.skv_add_rmsnorm(h_in.data_ptr(), None if dl is None else dl.data_ptr(), g.data_ptr(),
+                                        xn.data_ptr(), B, K, eps, st), "skv_add_rmsnorm")
+                x = xn
+            elif mode == 2:
+                act = torch.empty(B, K, dtype=dt, device=dev)
+                check(L.skv_silu_mul(x.data_ptr(), act.data_ptr(), B, K, st), "skv_silu_mul")
+                x = act
+            torch.matmul(x.view(B, K), W.t(), out=y)
+            return h_in
 
         for i, layer in enumerate(m.layers):
             a, f = layer.attn, layer.ffn
-            gemv(self._wqkv[i], qkv, 1, h_in=h, dl=delta, g=layer.norm1.weight, h_out=h2)
+            h = gemv(self._wqkv[i], qkv, 1, h_in=h, dl=delta, g=layer.norm1.weight, h_out=h2)
+            h2 = buf_b if h is buf_a else buf_a
             kc, vc = self.cache.k[i], self.cache.v[i]
             check(L.skv_qk_rope_cache(qkv.data_ptr(), a.q_norm.weight.data_ptr(), a.k_norm.weight.data_ptr(),
                                       m.rope_cos.data_ptr(), m.rope_sin.data_ptr(), self.pos.data_ptr(),
@@ -281,11 +299,11 @@ class GraphDecoder:
                                         insert=self.insert_all is None)
             gemv(a.o.weight, o, 0, x=out)
             o_red = a.tp.all_reduce(o)
-            gemv(self._wgu[i], gu, 1, h_in=h2, dl=o_red, g=layer.norm2.weight, h_out=h)
+            h = gemv(self._wgu[i], gu, 1, h_in=h, dl=o_red, g=layer.norm2.weight, h_out=h2)
+            h2 = buf_b if h is buf_a else buf_a
             dn = torch.empty(B, hidden, dtype=dt, device=dev)
             gemv(f.down.weight, dn, 2, x=gu)
             delta = f.tp.all_reduce(dn)
-        xn = torch.empty_like(h)
         check(L.skv_add_rmsnorm(h.data_ptr(), delta.data_ptr(), m.final_norm.weight.data_ptr(), xn.data_ptr(), B,
                                 hidden, eps, st), "skv_add_rmsnorm")
         return m.logits(xn.view(B, 1, hidden))
