@@ -44,6 +44,7 @@ extern "C" {
 #define SKV_ST_NO_SLOT      1 /* a cluster passed its cap but every slot is in use */
 #define SKV_ST_SPLIT_TOO_BIG 2 /* a cluster over the cap has more members than the split can stage */
 #define SKV_ST_BAD_INDEX    4 /* a listed position or a label was out of range and was skipped */
+#define SKV_ST_WAIT_TIMEOUT 8 /* a bounded wait for another GPU's partial sums gave up (skv_comm.status) */
 
 /* Cluster state of `heads` independent (layer, sequence, KV head) entries, structure of arrays.
  * Arrays are contiguous over heads: x[head][...].  Mirrors the tensors of
@@ -271,6 +272,50 @@ int skv_silu_mul(const void *gate_up, void *out, int B, int inter, void *stream)
  * skv_set_overlap: the weights are requested before the wait for the launch ahead. */
 int skv_gemv(const void *W, int N, int K, void *y, int B, int mode, const void *x, const void *h_in,
              const void *delta, const void *norm_w, void *h_out, float eps, void *stream);
+/* ---- sum of row-parallel products over the GPUs of a tensor-parallel group, through peer memory ----------------
+ * Replaces the all-reduce after the row-parallel `o` and `down` products of a tensor-parallel decode step (the
+ * reference decodes on one GPU; its host model's layers are models/graph_decode.py:100-121).  Every GPU of the
+ * group owns one exchange buffer, mapped into the other processes (skv_comm_alloc / export / open):
+ *   data   float32 [2 slots][world][cap_elems]   slot s, source rank r: the partial sums r computed
+ *   flags  uint32  [2 slots][world]              CTAs of rank r that have delivered into slot s, ever
+ *   uses   uint32  [2]                           launches of the local producer of slot s, ever
+ *   nctas  uint32  [2]                           CTAs of that producer
+ * The producing product (skv_gemv with `out` set) stores its float32 sums into slot s / row `rank` of EVERY
+ * GPU's buffer over NVLink and then adds one to that GPU's flag.  The consuming product (mode 3) waits until
+ * each flag of the slot has reached uses x nctas - a bounded wait of about a second, after which it sets
+ * SKV_ST_WAIT_TIMEOUT in *status and carries on - and sums the `world` partials in rank order, so every GPU
+ * obtains the same bits.  Two slots are enough for a decoder layer (`o`, `down`): a slot's next producer cannot
+ * start anywhere before every GPU has consumed the other slot, which each does after its use of this one. */
+typedef struct skv_comm {
+    int32_t world, rank;
+    int32_t cap_elems;        /* floats per (slot, source rank) */
+    int32_t reserved;
+    float    *data[8];        /* data region of every rank's buffer, as mapped in this process */
+    uint32_t *flags[8];       /* flag words of every rank's buffer */
+    uint32_t *uses, *nctas;   /* local counters */
+    int32_t  *status;         /* local, one word */
+} skv_comm;
+/* Bytes of one exchange buffer; its regions sit at fixed offsets (data first, then flags, uses, nctas, status). */
+int64_t skv_comm_bytes(int world, int cap_elems);
+/* cudaMalloc + zero fill of an exchange buffer on the current device; 64-byte handle for the other processes
+ * (cudaIpcGetMemHandle); mapping of another process's buffer (cudaIpcOpenMemHandle); unmapping; release. */
+int skv_comm_alloc(int64_t bytes, void **ptr);
+int skv_comm_export(const void *ptr, void *handle64);
+int skv_comm_open(const void *handle64, void **ptr);
+int skv_comm_close(void *ptr);
+int skv_comm_free(void *ptr);
+/* Fills `c` for buffers `bases[0..world)` (bases[rank] is the local one). */
+int skv_comm_view(skv_comm *c, void *const *bases, int world, int rank, int cap_elems);
+/* skv_gemv with the exchange: `out` non-null -> the sums go to slot `out_slot` of every GPU instead of y;
+ * mode 3 -> as mode 1 with delta = the sum over ranks of slot `in_slot` of `in` (delta argument unused). */
+int skv_gemv_tp(const void *W, int N, int K, void *y, int B, int mode, const void *x, const void *h_in,
+                const void *norm_w, void *h_out, float eps, const skv_comm *in, int in_slot,
+                const skv_comm *out, int out_slot, void *stream);
+/* delta[B, N] (bf16) = sum over ranks of slot `slot`, after the same wait: for consumers other than skv_gemv. */
+int skv_comm_reduce(const skv_comm *c, int slot, void *delta, int B, int N, void *stream);
+/* The buffer's status word (SKV_ST_WAIT_TIMEOUT), read back with a synchronising copy; negative on error. */
+int skv_comm_status(const skv_comm *c);
+
 /* 1 when skv_gemv serves this shape well; 0 when it cannot run it or when the inputs every CTA rebuilds would
  * outweigh the weights it multiplies them with (many sequences of a long row: use a library GEMM there). */
 int skv_gemv_supported(int N, int K, int B, int mode);

@@ -15,16 +15,24 @@ LIB_PATH = os.path.join(_PKG, "libskv.so")
 
 SKV_BF16, SKV_F32 = 0, 1
 FLAG_DRIFT, FLAG_RESET = 1, 2
-ST_NO_SLOT, ST_SPLIT_TOO_BIG, ST_BAD_INDEX = 1, 2, 4
+ST_NO_SLOT, ST_SPLIT_TOO_BIG, ST_BAD_INDEX, ST_WAIT_TIMEOUT = 1, 2, 4, 8
 
 EXPORTS = ("skv_version", "skv_error_string", "skv_last_cuda_error", "skv_attend_splits",
            "skv_attend_workspace_bytes", "skv_attend", "skv_attend_static", "skv_attend_labels", "skv_merge", "skv_select_workspace_bytes", "skv_select", "skv_debug_select_probe", "skv_debug_attend_probe", "skv_set_overlap", "skv_insert",
            "skv_insert_max_members", "skv_fit_workspace_bytes", "skv_fit", "skv_rebin",
-           "skv_add_rmsnorm", "skv_qk_rope_cache", "skv_silu_mul", "skv_gemv", "skv_gemv_supported")
+           "skv_add_rmsnorm", "skv_qk_rope_cache", "skv_silu_mul", "skv_gemv", "skv_gemv_supported", "skv_gemv_tp", "skv_comm_bytes", "skv_comm_alloc",
+           "skv_comm_export", "skv_comm_open", "skv_comm_close", "skv_comm_free", "skv_comm_view", "skv_comm_reduce", "skv_comm_status")
 
 
 class SkvError(RuntimeError):
     pass
+
+
+class SkvComm(C.Structure):
+    """``skv_comm`` of include/skv.h: one rank's view of the exchange buffers of a tensor-parallel group."""
+    _fields_ = [("world", C.c_int32), ("rank", C.c_int32), ("cap_elems", C.c_int32), ("reserved", C.c_int32),
+                ("data", C.c_void_p * 8), ("flags", C.c_void_p * 8), ("uses", C.c_void_p), ("nctas", C.c_void_p),
+                ("status", C.c_void_p)]
 
 
 class SkvState(C.Structure):
@@ -86,6 +94,27 @@ def _declare(lib) -> None:
     lib.skv_qk_rope_cache.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i64, i64, i64, f32, vp]
     lib.skv_silu_mul.restype = i32
     lib.skv_silu_mul.argtypes = [vp, vp, i32, i32, vp]
+    lib.skv_gemv_tp.restype = i32
+    lib.skv_gemv_tp.argtypes = [vp, i32, i32, vp, i32, i32, vp, vp, vp, vp, f32, C.POINTER(SkvComm), i32,
+                                C.POINTER(SkvComm), i32, vp]
+    lib.skv_comm_bytes.restype = i64
+    lib.skv_comm_bytes.argtypes = [i32, i32]
+    lib.skv_comm_alloc.restype = i32
+    lib.skv_comm_alloc.argtypes = [i64, C.POINTER(C.c_void_p)]
+    lib.skv_comm_export.restype = i32
+    lib.skv_comm_export.argtypes = [vp, vp]
+    lib.skv_comm_open.restype = i32
+    lib.skv_comm_open.argtypes = [vp, C.POINTER(C.c_void_p)]
+    lib.skv_comm_close.restype = i32
+    lib.skv_comm_close.argtypes = [vp]
+    lib.skv_comm_free.restype = i32
+    lib.skv_comm_free.argtypes = [vp]
+    lib.skv_comm_view.restype = i32
+    lib.skv_comm_view.argtypes = [C.POINTER(SkvComm), C.POINTER(C.c_void_p), i32, i32, i32]
+    lib.skv_comm_status.restype = i32
+    lib.skv_comm_status.argtypes = [C.POINTER(SkvComm)]
+    lib.skv_comm_reduce.restype = i32
+    lib.skv_comm_reduce.argtypes = [C.POINTER(SkvComm), i32, vp, i32, i32, vp]
     lib.skv_gemv_supported.restype = i32
     lib.skv_gemv_supported.argtypes = [i32, i32, i32, i32]
     lib.skv_gemv.restype = i32

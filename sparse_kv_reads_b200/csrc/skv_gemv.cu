@@ -21,6 +21,8 @@
 // rows w, w + 8, ... piece by piece with every sequence's input and reduces the sums over its lanes.
 #include "skv_attend_core.cuh"
 
+#include <cstring>
+
 namespace skv {
 
 constexpr int GEMV_THREADS = 256, GEMV_WARPS = 8;
@@ -34,7 +36,49 @@ struct GemvParams {
     const __nv_bfloat16 *h_in, *delta, *g;
     __nv_bfloat16 *h_out;
     float eps;
+    // exchange through peer memory (row-parallel products of a tensor-parallel group); world 0 = unused
+    float *out_data[8];            // every rank's data region
+    uint32_t *out_flags[8];        // every rank's flag words
+    uint32_t *out_uses, *out_nctas;
+    int out_world, out_rank, out_slot, out_cap;
+    const float *in_data;          // the local buffer
+    const uint32_t *in_flags, *in_uses, *in_nctas;
+    int in_world, in_slot, in_cap;
+    int32_t *status;
 };
+
+constexpr int WAIT_LIMIT = 1 << 20;     // polls of about a microsecond each: gives up after about a second
+
+// Wait (bounded) until every rank's CTAs have delivered into `slot` of the local buffer as often as the local
+// producer of that slot has been launched.  Threads 0..world-1 poll one flag each.
+__device__ __forceinline__ void wait_partials(const uint32_t *flags, const uint32_t *uses, const uint32_t *nctas,
+                                              int world, int slot, int32_t *status) {
+    if ((int)threadIdx.x < world) {
+        const uint32_t target = uses[slot] * nctas[slot];
+        const uint32_t *f = flags + slot * world + threadIdx.x;
+        uint32_t v;
+        int it = 0;
+        for (;;) {
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
+            if ((int32_t)(v - target) >= 0 || ++it >= WAIT_LIMIT) break;
+            __nanosleep(100);
+        }
+        if ((int32_t)(v - target) < 0 && status) atomicOr(status, SKV_ST_WAIT_TIMEOUT);
+    }
+    __syncthreads();
+}
+
+// One output value: to y, or as a float partial into slot/rank of every GPU's buffer.
+__device__ __forceinline__ void emit(const GemvParams &p, int b, int row, float v) {
+    if (p.out_world == 0) {
+        p.y[(size_t)b * p.N + row] = __float2bfloat16(v);
+        return;
+    }
+    const size_t off = (size_t)(p.out_slot * p.out_world + p.out_rank) * p.out_cap + (size_t)b * p.N + row;
+#pragma unroll
+    for (int r = 0; r < 8; ++r)
+        if (r < p.out_world) p.out_data[r][off] = v;
+}
 
 __device__ __forceinline__ float bf16r(float x) { return __bfloat162float(__float2bfloat16(x)); }
 
@@ -54,7 +98,7 @@ __global__ void __launch_bounds__(GEMV_THREADS) gemv_kernel(const GemvParams p) 
 
     // 1. the slab (and the norm weights): requested before anything else, also before the producer ends
     {
-        if (p.mode == 1)
+        if (p.mode == 1 || p.mode == 3)
             for (int c = tid; c < kv; c += GEMV_THREADS) cp_async16(gs + c * 8, p.g + c * 8, 16);
         cp_async_commit();                                  // group 0: norm weights (empty otherwise)
         const __nv_bfloat16 *src = p.W + (size_t)r0 * K;
@@ -73,6 +117,11 @@ __global__ void __launch_bounds__(GEMV_THREADS) gemv_kernel(const GemvParams p) 
     }
     pdl_wait();
     pdl_trigger();
+    if (p.out_world && blockIdx.x == 0 && tid == 0) {       // read by the consumer of this slot, a later launch
+        p.out_uses[p.out_slot] += 1u;
+        p.out_nctas[p.out_slot] = gridDim.x;
+    }
+    if (p.mode == 3) wait_partials(p.in_flags, p.in_uses, p.in_nctas, p.in_world, p.in_slot, p.status);
 
     // 2. the input of every sequence, in shared memory as bf16
     if (p.mode == 0) {
@@ -108,13 +157,26 @@ __global__ void __launch_bounds__(GEMV_THREADS) gemv_kernel(const GemvParams p) 
         if (b < p.B) {
             const __nv_bfloat16 *hr = p.h_in + (size_t)b * K;
             const __nv_bfloat16 *dr = p.delta ? p.delta + (size_t)b * K : nullptr;
+            const bool summed = p.mode == 3;                 // delta = sum of the ranks' partials, in rank order
             for (int v = v0 + lane; v < v1; v += 32) {
                 float a[8];
                 load8(hr + v * 8, a);
                 __align__(16) __nv_bfloat16 o[8];
-                if (dr) {
+                if (dr || summed) {
                     float d[8];
-                    load8(dr + v * 8, d);
+                    if (summed) {
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) d[i] = 0.f;
+                        for (int r = 0; r < p.in_world; ++r) {
+                            const float *src = p.in_data + (size_t)(p.in_slot * p.in_world + r) * p.in_cap + (size_t)b * K + v * 8;
+                            const float4 lo = __ldcg(reinterpret_cast<const float4 *>(src));
+                            const float4 hi = __ldcg(reinterpret_cast<const float4 *>(src) + 1);
+                            d[0] += lo.x; d[1] += lo.y; d[2] += lo.z; d[3] += lo.w;
+                            d[4] += hi.x; d[5] += hi.y; d[6] += hi.z; d[7] += hi.w;
+                        }
+                    } else {
+                        load8(dr + v * 8, d);
+                    }
 #pragma unroll
                     for (int i = 0; i < 8; ++i) {
                         o[i] = __float2bfloat16(a[i] + d[i]);
@@ -185,12 +247,12 @@ __global__ void __launch_bounds__(GEMV_THREADS) gemv_kernel(const GemvParams p) 
             if (ks == 1) {
                 const int ra = r0 + t * 16 + (lane >> 2), rb = ra + 8;
                 if (kq < p.B) {
-                    if (ra < r0 + R) p.y[(size_t)kq * p.N + ra] = __float2bfloat16(acc[0]);
-                    if (rb < r0 + R) p.y[(size_t)kq * p.N + rb] = __float2bfloat16(acc[2]);
+                    if (ra < r0 + R) emit(p, kq, ra, acc[0]);
+                    if (rb < r0 + R) emit(p, kq, rb, acc[2]);
                 }
                 if (kq + 1 < p.B) {
-                    if (ra < r0 + R) p.y[(size_t)(kq + 1) * p.N + ra] = __float2bfloat16(acc[1]);
-                    if (rb < r0 + R) p.y[(size_t)(kq + 1) * p.N + rb] = __float2bfloat16(acc[3]);
+                    if (ra < r0 + R) emit(p, kq + 1, ra, acc[1]);
+                    if (rb < r0 + R) emit(p, kq + 1, rb, acc[3]);
                 }
             } else {
                 float *d = s_red[item];                    // [row in tile][sequence]
@@ -207,11 +269,10 @@ __global__ void __launch_bounds__(GEMV_THREADS) gemv_kernel(const GemvParams p) 
                 float sum = 0.f;
                 for (int sp = 0; sp < ks; ++sp) sum += s_red[sp * ntiles + t][e];
                 const int rg = t * 16 + rr;
-                if (rg < R && b < p.B) p.y[(size_t)b * p.N + r0 + rg] = __float2bfloat16(sum);
+                if (rg < R && b < p.B) emit(p, b, r0 + rg, sum);
             }
         }
-        return;
-    }
+    } else
     for (int r = wid; r < R; r += GEMV_WARPS) {
         float acc[BP];
 #pragma unroll
@@ -232,8 +293,30 @@ __global__ void __launch_bounds__(GEMV_THREADS) gemv_kernel(const GemvParams p) 
 #pragma unroll
         for (int b = 0; b < BP; ++b) {
             const float s = warp_sum(acc[b]);
-            if (lane == 0 && b < p.B) p.y[(size_t)b * p.N + r0 + r] = __float2bfloat16(s);
+            if (lane == 0 && b < p.B) emit(p, b, r0 + r, s);
         }
+    }
+    // 4. tell every GPU that this CTA's sums have arrived
+    if (p.out_world) {
+        __threadfence_system();
+        __syncthreads();
+#pragma unroll
+        for (int r = 0; r < 8; ++r)
+            if (tid == r && r < p.out_world) atomicAdd_system(p.out_flags[r] + p.out_slot * p.out_world + p.out_rank, 1u);
+    }
+}
+
+// delta[B, N] = sum over ranks of a slot's partials (for consumers that are not a product of this file)
+__global__ void __launch_bounds__(256) comm_reduce_kernel(const float *data, const uint32_t *flags, const uint32_t *uses,
+                                                          const uint32_t *nctas, int world, int slot, int cap,
+                                                          int32_t *status, __nv_bfloat16 *delta, int total) {
+    pdl_wait();
+    pdl_trigger();
+    wait_partials(flags, uses, nctas, world, slot, status);
+    for (int i = blockIdx.x * 256 + threadIdx.x; i < total; i += gridDim.x * 256) {
+        float s = 0.f;
+        for (int r = 0; r < world; ++r) s += __ldcg(data + (size_t)(slot * world + r) * cap + i);
+        delta[i] = __float2bfloat16(s);
     }
 }
 
@@ -248,11 +331,11 @@ struct GemvPlan {
 // `worthwhile` is false when the inputs every CTA rebuilds outweigh the slab it multiplies them with (many
 // sequences of a long row): a library GEMM serves those shapes better.
 static int plan_gemv(int N, int K, int B, int mode, GemvPlan &pl) {
-    if (B < 1 || B > 8 || N < 1 || K < 8 || K % 8 || mode < 0 || mode > 2) return SKV_E_RANGE;
+    if (B < 1 || B > 8 || N < 1 || K < 8 || K % 8 || mode < 0 || mode > 3) return SKV_E_RANGE;
     pl.BP = B <= 1 ? 1 : (B <= 2 ? 2 : (B <= 4 ? 4 : 8));
     pl.tc = K % 64 == 0 && pl.BP > 1;                 // one sequence: the float path is as fast and needs no reduction
     const size_t row = (size_t)K * 2;
-    const size_t fixed = (size_t)pl.BP * (row + (pl.tc ? 16 : 0)) + (mode == 1 ? row : 0);   // inputs (+ norm weights)
+    const size_t fixed = (size_t)pl.BP * (row + (pl.tc ? 16 : 0)) + (mode == 1 || mode == 3 ? row : 0);   // inputs (+ norm weights)
     const size_t optin = (size_t)device_max_smem_optin();
     const size_t per_cta = optin / 2 - 2048;
     size_t slab = per_cta > fixed ? per_cta - fixed : 0;
@@ -288,27 +371,51 @@ extern "C" int skv_gemv_supported(int N, int K, int B, int mode) {
     return plan_gemv(N, K, B, mode, pl) == SKV_OK && pl.worthwhile ? 1 : 0;
 }
 
-extern "C" int skv_gemv(const void *W, int N, int K, void *y, int B, int mode, const void *x, const void *h_in,
-                        const void *delta, const void *norm_w, void *h_out, float eps, void *stream) {
-    if (!W || !y) return SKV_E_NULL;
-    if (mode < 0 || mode > 2) return SKV_E_RANGE;
-    if (mode == 1 ? (!h_in || !norm_w) : !x) return SKV_E_NULL;
+// Layout of an exchange buffer: data [2][world][cap] float, flags [2][world], uses [2], nctas [2], status [1]
+static int64_t comm_data_bytes(int world, int cap) { return ((int64_t)2 * world * cap * 4 + 255) / 256 * 256; }
+
+static int gemv_launch(const void *W, int N, int K, void *y, int B, int mode, const void *x, const void *h_in,
+                       const void *delta, const void *norm_w, void *h_out, float eps, const skv_comm *in, int in_slot,
+                       const skv_comm *out, int out_slot, void *stream) {
+    if (!W || (!y && !out)) return SKV_E_NULL;
+    if (mode < 0 || mode > 3 || (mode == 3) != (in != nullptr)) return SKV_E_RANGE;
+    if (mode == 1 || mode == 3 ? (!h_in || !norm_w) : !x) return SKV_E_NULL;
     if (B < 1 || B > 8 || N < 1 || K < 8 || K % 8) return SKV_E_RANGE;
-    if (!aligned16(W) || !aligned16(y) || (x && !aligned16(x)) || (h_in && !aligned16(h_in)) ||
+    if (!aligned16(W) || (y && !aligned16(y)) || (x && !aligned16(x)) || (h_in && !aligned16(h_in)) ||
         (delta && !aligned16(delta)) || (norm_w && !aligned16(norm_w)) || (h_out && !aligned16(h_out)))
         return SKV_E_ALIGN;
+    for (const skv_comm *c : {in, out}) {
+        if (!c) continue;
+        if (c->world < 1 || c->world > 8 || c->rank < 0 || c->rank >= c->world || c->cap_elems < 8 || c->cap_elems % 4)
+            return SKV_E_RANGE;
+        if (!c->uses || !c->nctas || !c->status) return SKV_E_NULL;
+        for (int r = 0; r < c->world; ++r)
+            if (!c->data[r] || !c->flags[r]) return SKV_E_NULL;
+    }
+    if ((in && (in_slot < 0 || in_slot > 1 || (int64_t)B * K > in->cap_elems)) ||
+        (out && (out_slot < 0 || out_slot > 1 || (int64_t)B * N > out->cap_elems)))
+        return SKV_E_RANGE;
     GemvPlan pl;
     const int rc = plan_gemv(N, K, B, mode, pl);
     if (rc) return rc;
     const int BP = pl.BP, rows = pl.rows;
     const bool tc = pl.tc;
     const size_t smem = pl.smem;
-    GemvParams p;
+    GemvParams p = {};
     p.W = static_cast<const __nv_bfloat16 *>(W); p.y = static_cast<__nv_bfloat16 *>(y);
     p.N = N; p.K = K; p.B = B; p.mode = mode; p.rows_per_cta = rows;
     p.x = static_cast<const __nv_bfloat16 *>(x); p.h_in = static_cast<const __nv_bfloat16 *>(h_in);
     p.delta = static_cast<const __nv_bfloat16 *>(delta); p.g = static_cast<const __nv_bfloat16 *>(norm_w);
     p.h_out = static_cast<__nv_bfloat16 *>(h_out); p.eps = eps;
+    if (out) {
+        for (int r = 0; r < out->world; ++r) { p.out_data[r] = out->data[r]; p.out_flags[r] = out->flags[r]; }
+        p.out_uses = out->uses; p.out_nctas = out->nctas;
+        p.out_world = out->world; p.out_rank = out->rank; p.out_slot = out_slot; p.out_cap = out->cap_elems;
+    }
+    if (in) {
+        p.in_data = in->data[in->rank]; p.in_flags = in->flags[in->rank]; p.in_uses = in->uses; p.in_nctas = in->nctas;
+        p.in_world = in->world; p.in_slot = in_slot; p.in_cap = in->cap_elems; p.status = in->status;
+    }
     typedef void (*Kern)(const GemvParams);
     const int bi = (BP == 1 ? 0 : (BP == 2 ? 1 : (BP == 4 ? 2 : 3))) + (tc ? 4 : 0);
     const Kern table[8] = {gemv_kernel<1, false>, gemv_kernel<2, false>, gemv_kernel<4, false>, gemv_kernel<8, false>,
@@ -324,4 +431,91 @@ extern "C" int skv_gemv(const void *W, int N, int K, void *y, int B, int mode, c
     const int ctas = (N + rows - 1) / rows;
     SKV_CUDA_OK(launch_pdl(table[bi], dim3(ctas), dim3(GEMV_THREADS), smem, static_cast<cudaStream_t>(stream), p));
     return SKV_OK;
+}
+
+extern "C" int skv_gemv(const void *W, int N, int K, void *y, int B, int mode, const void *x, const void *h_in,
+                        const void *delta, const void *norm_w, void *h_out, float eps, void *stream) {
+    if (mode == 3) return SKV_E_RANGE;
+    return gemv_launch(W, N, K, y, B, mode, x, h_in, delta, norm_w, h_out, eps, nullptr, 0, nullptr, 0, stream);
+}
+
+extern "C" int skv_gemv_tp(const void *W, int N, int K, void *y, int B, int mode, const void *x, const void *h_in,
+                           const void *norm_w, void *h_out, float eps, const skv_comm *in, int in_slot,
+                           const skv_comm *out, int out_slot, void *stream) {
+    return gemv_launch(W, N, K, y, B, mode, x, h_in, nullptr, norm_w, h_out, eps, in, in_slot, out, out_slot, stream);
+}
+
+extern "C" int64_t skv_comm_bytes(int world, int cap_elems) {
+    if (world < 1 || world > 8 || cap_elems < 8 || cap_elems % 4) return SKV_E_RANGE;
+    return comm_data_bytes(world, cap_elems) + 256;       // flags (<= 64 B), uses, nctas, status
+}
+
+extern "C" int skv_comm_view(skv_comm *c, void *const *bases, int world, int rank, int cap_elems) {
+    if (!c || !bases) return SKV_E_NULL;
+    if (world < 1 || world > 8 || rank < 0 || rank >= world || cap_elems < 8 || cap_elems % 4) return SKV_E_RANGE;
+    const int64_t db = comm_data_bytes(world, cap_elems);
+    *c = skv_comm{};
+    c->world = world; c->rank = rank; c->cap_elems = cap_elems;
+    for (int r = 0; r < world; ++r) {
+        if (!bases[r]) return SKV_E_NULL;
+        char *b = static_cast<char *>(bases[r]);
+        c->data[r] = reinterpret_cast<float *>(b);
+        c->flags[r] = reinterpret_cast<uint32_t *>(b + db);
+    }
+    char *own = static_cast<char *>(bases[rank]) + db;
+    c->uses = reinterpret_cast<uint32_t *>(own + 64);
+    c->nctas = reinterpret_cast<uint32_t *>(own + 72);
+    c->status = reinterpret_cast<int32_t *>(own + 80);
+    return SKV_OK;
+}
+
+extern "C" int skv_comm_alloc(int64_t bytes, void **ptr) {
+    if (!ptr) return SKV_E_NULL;
+    if (bytes <= 0) return SKV_E_RANGE;
+    SKV_CUDA_OK(cudaMalloc(ptr, (size_t)bytes));
+    SKV_CUDA_OK(cudaMemset(*ptr, 0, (size_t)bytes));
+    SKV_CUDA_OK(cudaDeviceSynchronize());
+    return SKV_OK;
+}
+extern "C" int skv_comm_export(const void *ptr, void *handle64) {
+    if (!ptr || !handle64) return SKV_E_NULL;
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size");
+    SKV_CUDA_OK(cudaIpcGetMemHandle(static_cast<cudaIpcMemHandle_t *>(handle64), const_cast<void *>(ptr)));
+    return SKV_OK;
+}
+extern "C" int skv_comm_open(const void *handle64, void **ptr) {
+    if (!ptr || !handle64) return SKV_E_NULL;
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle64, 64);
+    SKV_CUDA_OK(cudaIpcOpenMemHandle(ptr, h, cudaIpcMemLazyEnablePeerAccess));
+    return SKV_OK;
+}
+extern "C" int skv_comm_close(void *ptr) {
+    if (!ptr) return SKV_E_NULL;
+    SKV_CUDA_OK(cudaIpcCloseMemHandle(ptr));
+    return SKV_OK;
+}
+extern "C" int skv_comm_free(void *ptr) {
+    if (!ptr) return SKV_E_NULL;
+    SKV_CUDA_OK(cudaFree(ptr));
+    return SKV_OK;
+}
+
+extern "C" int skv_comm_reduce(const skv_comm *c, int slot, void *delta, int B, int N, void *stream) {
+    if (!c || !delta) return SKV_E_NULL;
+    if (c->world < 1 || c->world > 8 || slot < 0 || slot > 1 || B < 1 || N < 1 || (int64_t)B * N > c->cap_elems)
+        return SKV_E_RANGE;
+    const int total = B * N;
+    SKV_CUDA_OK(launch_pdl(comm_reduce_kernel, dim3((total + 255) / 256 > 8 ? 8 : (total + 255) / 256), dim3(256), 0,
+                           static_cast<cudaStream_t>(stream), (const float *)c->data[c->rank],
+                           (const uint32_t *)c->flags[c->rank], (const uint32_t *)c->uses, (const uint32_t *)c->nctas,
+                           c->world, slot, c->cap_elems, c->status, static_cast<__nv_bfloat16 *>(delta), total));
+    return SKV_OK;
+}
+
+extern "C" int skv_comm_status(const skv_comm *c) {
+    if (!c || !c->status) return SKV_E_NULL;
+    int32_t word = 0;
+    SKV_CUDA_OK(cudaMemcpy(&word, c->status, 4, cudaMemcpyDeviceToHost));
+    return word & 0x7fffffff;
 }

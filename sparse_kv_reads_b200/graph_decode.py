@@ -123,6 +123,7 @@ class GraphDecoder:
             self._fuse_weights()
         # ... and, up to 8 sequences, its projections as the library's matrix-vector products
         self.own_gemv = own_gemv and os.environ.get("SKV_OWN_GEMV", "1") != "0"
+        self._peer = None
         self.fused_insert = fused_insert and mode == "cluster" and window >= 1
         self.insert_all = None
 
@@ -240,7 +241,9 @@ class GraphDecoder:
         """The layers with the library's own matrix-vector products (up to 8 sequences): a layer is seven
         launches - q/k/v product with the residual add and norm folded into its input, QK-norm + rotary +
         cache write, selection, attention, output product, gate/up product (add and norm folded in), down
-        product (SiLU x up folded in) - each requesting its weights while the launch ahead of it finishes."""
+        product (SiLU x up folded in) - each requesting its weights while the launch ahead of it finishes.
+        In a tensor-parallel group the row-parallel products (output, down) store their partial sums into every
+        GPU's exchange buffer and the product after them adds the partials up: no all-reduce launch."""
         m, H, H_kv, d, B = self.model, self.H, self.H_kv, self.d, self.B
         L = lib()
         st = stream_ptr(self.tok.device)
@@ -255,37 +258,62 @@ class GraphDecoder:
         dev, dt = h.device, h.dtype
         qh = torch.empty(B * H, d, dtype=dt, device=dev)
         nqkv, ngu = self._wqkv[0].shape[0], self._wgu[0].shape[0]
-        inter = ngu // 2
         qkv = torch.empty(B, nqkv, dtype=dt, device=dev)
         o = torch.empty(B, hidden, dtype=dt, device=dev)
         gu = torch.empty(B, ngu, dtype=dt, device=dev)
-        delta = None
-
         xn = torch.empty_like(h)
+        peer = self._exchange()
+        SLOT_O, SLOT_DOWN = 0, 1
 
-        def gemv(W, y, mode, x=None, h_in=None, dl=None, g=None, h_out=None):
+        def ptr_of(t):
+            return None if t is None else t.data_ptr()
+
+        def product(W, y, mode, x=None, h_in=None, dl=None, g=None, h_out=None, tp=None, slot_out=None):
+            """One projection.  ``dl`` is the delta to add to the residual (mode 1): a tensor, or the number of
+            the exchange slot that holds its partial sums.  ``slot_out``: deliver the result as partial sums into
+            that slot instead of ``y`` (returns the slot), else all-reduce ``y`` over ``tp`` when given.
+            Returns (residual buffer now current, result: tensor or slot)."""
             N, K = W.shape
-            if L.skv_gemv_supported(N, K, B, mode):
-                check(L.skv_gemv(W.data_ptr(), N, K, y.data_ptr(), B, mode,
-                                 None if x is None else x.data_ptr(), None if h_in is None else h_in.data_ptr(),
-                                 None if dl is None else dl.data_ptr(), None if g is None else g.data_ptr(),
-                                 None if h_out is None else h_out.data_ptr(), eps, st), "skv_gemv")
-                return h_out
+            from_slot = isinstance(dl, int)
+            own = bool(L.skv_gemv_supported(N, K, B, 3 if from_slot else mode))
+            if from_slot and not own:                      # the sum as a tensor, for the separate kernels below
+                red = torch.empty(B, K, dtype=dt, device=dev)
+                check(L.skv_comm_reduce(peer.ref(), dl, red.data_ptr(), B, K, st), "skv_comm_reduce")
+                dl, from_slot = red, False
+                own = bool(L.skv_gemv_supported(N, K, B, mode))
+            if own:
+                to_slot = slot_out is not None
+                if from_slot or to_slot:
+                    check(L.skv_gemv_tp(W.data_ptr(), N, K, None if to_slot else y.data_ptr(), B,
+                                        3 if from_slot else mode, ptr_of(x), ptr_of(h_in), ptr_of(g), ptr_of(h_out), eps,
+                                        peer.ref() if from_slot else None, dl if from_slot else 0,
+                                        peer.ref() if to_slot else None, slot_out if to_slot else 0, st), "skv_gemv_tp")
+                else:
+                    check(L.skv_gemv(W.data_ptr(), N, K, y.data_ptr(), B, mode, ptr_of(x), ptr_of(h_in), ptr_of(dl),
+                                     ptr_of(g), ptr_of(h_out), eps, st), "skv_gemv")
+                if to_slot:
+                    return h_out, slot_out
+                return h_out, (tp.all_reduce(y) if tp is not None else y)
             # shapes the library product does not serve well: the separate element-wise kernel, then cuBLAS
             if mode == 1:                                   # in place: the residual stays in h_in
-                check(L.skv_add_rmsnorm(h_in.data_ptr(), None if dl is None else dl.data_ptr(), g.data_ptr(),
-                                        xn.data_ptr(), B, K, eps, st), "skv_add_rmsnorm")
+                check(L.skv_add_rmsnorm(h_in.data_ptr(), ptr_of(dl), g.data_ptr(), xn.data_ptr(), B, K, eps, st),
+                      "skv_add_rmsnorm")
                 x = xn
             elif mode == 2:
                 act = torch.empty(B, K, dtype=dt, device=dev)
                 check(L.skv_silu_mul(x.data_ptr(), act.data_ptr(), B, K, st), "skv_silu_mul")
                 x = act
             torch.matmul(x.view(B, K), W.t(), out=y)
-            return h_in
+            return h_in, (tp.all_reduce(y) if tp is not None else y)
 
+        def peer_ok(W, mode):
+            return peer is not None and bool(L.skv_gemv_supported(W.shape[0], W.shape[1], B, mode))
+
+        delta = None
         for i, layer in enumerate(m.layers):
             a, f = layer.attn, layer.ffn
-            h = gemv(self._wqkv[i], qkv, 1, h_in=h, dl=delta, g=layer.norm1.weight, h_out=h2)
+            res, _ = product(self._wqkv[i], qkv, 1, h_in=h, dl=delta, g=layer.norm1.weight, h_out=h2)
+            h = res if res is not None else h
             h2 = buf_b if h is buf_a else buf_a
             kc, vc = self.cache.k[i], self.cache.v[i]
             check(L.skv_qk_rope_cache(qkv.data_ptr(), a.q_norm.weight.data_ptr(), a.k_norm.weight.data_ptr(),
@@ -297,16 +325,32 @@ class GraphDecoder:
             else:
                 out = self.attn[i].step(qh, self._heads(kc), self._heads(vc), self.n_dev,
                                         insert=self.insert_all is None)
-            gemv(a.o.weight, o, 0, x=out)
-            o_red = a.tp.all_reduce(o)
-            h = gemv(self._wgu[i], gu, 1, h_in=h, dl=o_red, g=layer.norm2.weight, h_out=h2)
+            _, o_red = product(a.o.weight, o, 0, x=out, tp=a.tp,
+                               slot_out=SLOT_O if peer_ok(a.o.weight, 0) else None)
+            res, _ = product(self._wgu[i], gu, 1, h_in=h, dl=o_red, g=layer.norm2.weight, h_out=h2)
+            h = res if res is not None else h
             h2 = buf_b if h is buf_a else buf_a
             dn = torch.empty(B, hidden, dtype=dt, device=dev)
-            gemv(f.down.weight, dn, 2, x=gu)
-            delta = f.tp.all_reduce(dn)
+            _, delta = product(f.down.weight, dn, 2, x=gu, tp=f.tp,
+                               slot_out=SLOT_DOWN if peer_ok(f.down.weight, 2) else None)
+        if isinstance(delta, int):
+            red = torch.empty(B, hidden, dtype=dt, device=dev)
+            check(L.skv_comm_reduce(peer.ref(), delta, red.data_ptr(), B, hidden, st), "skv_comm_reduce")
+            delta = red
         check(L.skv_add_rmsnorm(h.data_ptr(), delta.data_ptr(), m.final_norm.weight.data_ptr(), xn.data_ptr(), B,
                                 hidden, eps, st), "skv_add_rmsnorm")
         return m.logits(xn.view(B, 1, hidden))
+
+    def _exchange(self):
+        """The tensor-parallel group's exchange buffers (made on first use), or None on a single GPU."""
+        tp = self.model.layers[0].attn.tp
+        if tp.size <= 1 or os.environ.get("SKV_PEER_REDUCE", "1") == "0":
+            return None
+        if self._peer is None:
+            from .peer_reduce import PeerExchange
+            hidden = self.model.cfg.hidden_size
+            self._peer = PeerExchange(tp.group, self.B * hidden, self.tok.device)
+        return self._peer
 
     def capture(self) -> None:
         """Record one decode step.  Call after ``prepare`` and before the first ``step``; the warm-up

@@ -111,3 +111,80 @@ def test_gemv_with_the_three_input_modes(B):
         check(L.skv_gemv(W.data_ptr(), N, K, y.data_ptr(), B, 2, gu.data_ptr(), None, None, None, None, 0.0, stream()),
               "skv_gemv")
         torch.testing.assert_close(y.float(), act.float() @ W.float().T, rtol=1e-2, atol=1e-2)
+
+
+def _rms(x, g, eps=1e-6):
+    xf = x.float()
+    return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps) * g.float()).to(torch.bfloat16)
+
+
+@pytest.mark.parametrize("B", [1, 4])
+def test_row_parallel_product_summed_through_exchange_buffers(B):
+    """Two ranks emulated on one device (their kernels run one after the other): each multiplies its half of
+    the inputs, the partial sums land in both exchange buffers, and the next product of either rank adds them."""
+    import ctypes
+    from sparse_kv_reads_b200._lib import ST_WAIT_TIMEOUT
+    from sparse_kv_reads_b200.peer_reduce import PeerExchange
+    L = lib()
+    g = torch.Generator().manual_seed(40 + B)
+    world, N, K, N2 = 2, 1024, 2048, 512
+    ex = PeerExchange.emulated(world, B * N, DEV)
+    W = (torch.randn(N, K, generator=g) / K ** 0.5).to(torch.bfloat16).to(DEV)
+    W2 = (torch.randn(N2, N, generator=g) / N ** 0.5).to(torch.bfloat16).to(DEV)
+    gw = (1 + 0.1 * torch.randn(N, generator=g)).to(torch.bfloat16).to(DEV)
+    Ks = K // world
+    Wr = [W[:, r * Ks:(r + 1) * Ks].contiguous() for r in range(world)]
+    for use in range(3):                                  # the counters only ever grow: several uses of a slot
+        slot = use % 2
+        x = torch.randn(B, K, generator=g).to(torch.bfloat16).to(DEV)
+        h = torch.randn(B, N, generator=g).to(torch.bfloat16).to(DEV)
+        for r in range(world):
+            xr = x[:, r * Ks:(r + 1) * Ks].contiguous()
+            check(L.skv_gemv_tp(Wr[r].data_ptr(), N, Ks, None, B, 0, xr.data_ptr(), None, None, None, 0.0, None, 0,
+                                ex[r].ref(), slot, stream()), "skv_gemv_tp")
+        parts = torch.stack([xr.float() @ wr.float().T for xr, wr in
+                             ((x[:, r * Ks:(r + 1) * Ks], Wr[r]) for r in range(world))])
+        h_new = (h.float() + parts.sum(0)).to(torch.bfloat16)
+        want = _rms(h_new, gw).float() @ W2.float().T
+        outs = []
+        for r in range(world):
+            y = torch.empty(B, N2, dtype=torch.bfloat16, device=DEV)
+            h_out = torch.empty_like(h)
+            check(L.skv_gemv_tp(W2.data_ptr(), N2, N, y.data_ptr(), B, 3, None, h.data_ptr(), gw.data_ptr(),
+                                h_out.data_ptr(), 1e-6, ex[r].ref(), slot, None, 0, stream()), "skv_gemv_tp")
+            assert (h_out.float() - h_new.float()).abs().max() <= 0.07      # one unit in the last place of a bf16 near 8
+            torch.testing.assert_close(y.float(), want, rtol=3e-2, atol=3e-2)
+            outs.append((y, h_out))
+            delta = torch.empty(B, N, dtype=torch.bfloat16, device=DEV)
+            check(L.skv_comm_reduce(ex[r].ref(), slot, delta.data_ptr(), B, N, stream()), "skv_comm_reduce")
+            torch.testing.assert_close(delta.float(), parts.sum(0), rtol=1e-2, atol=1e-2)
+        assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])   # same bits on every rank
+    assert all(e.status() == 0 for e in ex)
+    assert L.skv_gemv_tp(W2.data_ptr(), N2, N, None, B, 0, h.data_ptr(), None, None, None, 0.0, None, 0, None, 0,
+                         stream()) == -1                 # neither y nor an exchange to write to
+    assert L.skv_gemv_tp(W2.data_ptr(), N2, 4096, None, B, 3, None, h.data_ptr(), gw.data_ptr(), None, 0.0,
+                         ex[0].ref(), 0, None, 0, stream()) == -1
+    for e in ex:
+        e.close()
+
+
+def test_wait_for_a_rank_that_never_delivers_gives_up_and_reports():
+    """A bounded wait: rank 0 has produced, rank 1 never does; rank 0's consumer polls for about a second, sets
+    the time-out bit in its status word and finishes (nothing hangs, the context stays usable)."""
+    from sparse_kv_reads_b200._lib import ST_WAIT_TIMEOUT
+    from sparse_kv_reads_b200.peer_reduce import PeerExchange
+    L = lib()
+    B, N, K = 1, 256, 512
+    ex = PeerExchange.emulated(2, B * N, DEV)
+    W = torch.randn(N, K, device=DEV).to(torch.bfloat16)
+    x = torch.randn(B, K, device=DEV).to(torch.bfloat16)
+    check(L.skv_gemv_tp(W.data_ptr(), N, K, None, B, 0, x.data_ptr(), None, None, None, 0.0, None, 0, ex[0].ref(), 0,
+                        stream()), "skv_gemv_tp")
+    delta = torch.empty(B, N, dtype=torch.bfloat16, device=DEV)
+    check(L.skv_comm_reduce(ex[0].ref(), 0, delta.data_ptr(), B, N, stream()), "skv_comm_reduce")
+    torch.cuda.synchronize()
+    assert ex[0].status() & ST_WAIT_TIMEOUT
+    assert ex[1].status() == 0
+    assert float(torch.ones(4, device=DEV).sum()) == 4.0      # the device still answers
+    for e in ex:
+        e.close()
