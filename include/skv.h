@@ -139,8 +139,13 @@ int skv_attend_static(const void *q, const void *K, const void *V, const int32_t
 int skv_merge(const float *m, const float *l, const float *a, float *out, int heads, int S, int G, int d,
               void *stream);
 
+/* How the G query heads of a KV head share one ranking of its clusters (ssa/attn/sphere_gpu.py:431-439) */
+#define SKV_GROUP_SUM_SHARE 0   /* sum over the heads of each head's softmax over clusters */
+#define SKV_GROUP_MAX       1   /* largest scaled score of any head */
+#define SKV_GROUP_MAX_REL   2   /* largest score relative to that head's best cluster */
+
 /* Score clusters from their summaries once per KV head for its G query heads, form the shared score
- * (sum over the group of each head's softmax over clusters) and take clusters in decreasing shared
+ * (`group`: SKV_GROUP_*) and take clusters in decreasing shared
  * score (equal scores: lower slot first) until their key counts reach state.need.  Several CTAs score
  * a head's clusters in parallel; the last one to finish picks.  Outputs the 0/1 weights, the same
  * selection as a bit set (bit C = always-read rows: position 0 and the recent window carry label C),
@@ -158,11 +163,13 @@ int skv_merge(const float *m, const float *l, const float *a, float *out, int he
  *   shared_out optional [heads, C] float32: the shared scores used
  *   e_out      optional [heads, G, C] float32: per-query-head cluster scores (before the 1/sqrt(d) scale)
  *   workspace  skv_select_workspace_bytes(heads, G, C) bytes, zero-initialised once by the caller
+ *   group      SKV_GROUP_* (shared_in, when given, is ranked as it is)
  */
 int64_t skv_select_workspace_bytes(int heads, int G, int C);
 int skv_select(const skv_state *st, const void *q, int dtype, int G, const int32_t *n_dev,
                float *w, uint32_t *selbits, int32_t *idx, int64_t idx_stride, int32_t *cnt,
-               const float *shared_in, float *shared_out, float *e_out, void *workspace, float scale, void *stream);
+               const float *shared_in, float *shared_out, float *e_out, void *workspace, float scale, int group,
+               void *stream);
 
 /* Tuning aid without a counterpart in the reference: `dev_ptr` is a device array of 16 uint64 that receives
  * nanosecond time stamps of the phases of skv_select's kernel for head 0 (null switches it off). */
@@ -221,6 +228,9 @@ int64_t skv_fit_workspace_bytes(int heads, int m, int C, int d);
  * Replaces spherical_kmeans (ssa/attn/clusterkv.py:27-46), SphereIndexGPU._build/_bin
  * (ssa/attn/sphere_gpu.py:166-219), _split_after_fit/_split_overflow/_split_batch (:302-391) and
  * _refresh8 (ssa/kernels/sphere_fused.py:398-406).
+ *   init_pos    device int32 [C_init]: clustered-key indices whose directions start the k-means; null: keep the
+ *               centroids the caller put into state.cent[:, :C_init] and fit nothing (`partition="random"`:
+ *               fixed directions shared by all heads, ssa/attn/sphere_gpu.py:13-14,:147)
  *   cap_keys > 0: absolute cap; else cap = split_factor * m / C_init when split_factor > 0; else no cap
  *   capk        growing cap (see skv_insert); var_factor > 0: state.vthr = var_factor x the mean spread of the
  *               fitted clusters (ssa/attn/sphere_gpu.py:214-217), else +inf

@@ -105,6 +105,13 @@ def bisect_partition(U: torch.Tensor, valid: torch.Tensor, min_share: float = 0.
     return torch.where(lopsided.unsqueeze(1), upper, side).long()
 
 
+def fixed_directions(C: int, d: int, seed: int) -> torch.Tensor:
+    """``C`` unit vectors uniform on the sphere, the same for every head: the bins of ``partition="random"``
+    (ssa/attn/sphere_skip.py:54-56,:67 with ``kind="random"``)."""
+    x = torch.randn(C, d, generator=torch.Generator().manual_seed(seed), dtype=torch.float64)
+    return (x / x.norm(dim=1, keepdim=True)).float()
+
+
 def to_int8_direction(x: torch.Tensor) -> torch.Tensor:
     """8-bit copy of a direction: unit vector x 127, rounded half up (sphere_fused.py:394-396)."""
     return torch.floor(F.normalize(x, dim=-1) * 127 + 0.5).to(torch.int8)
@@ -123,18 +130,23 @@ class ClusterOracle:
     def __init__(self, *, C: int, C_init: int | None = None, window: int = 64, delta: float = 0.03,
                  capacity: int = 65536, check_every: int = 16, seed: int = 0, kmeans_iters: int = 10,
                  split_factor: float = 0.0, cap_keys: float = 0.0, summary_bits: int = 32, grow_cap: bool = False,
-                 reset_at: int = 0, var_factor: float = 0.0, var_min: int = 8):
+                 reset_at: int = 0, var_factor: float = 0.0, var_min: int = 8, partition: str = "kmeans"):
+        if partition not in ("kmeans", "random"):
+            raise ValueError(f"unknown partition {partition!r}")
+        self.partition = partition
         self.C, self.C_init = C, (C if C_init is None else C_init)
         self.window, self.delta, self.capacity = window, delta, capacity
         self.check_every, self.seed, self.kmeans_iters = check_every, seed, kmeans_iters
         self.cap_keys = float(cap_keys)
         self.split_factor = float(split_factor) if split_factor or not cap_keys else 2.0   # sphere_gpu.py:123-124
         self.var_factor, self.var_min = float(var_factor), int(var_min)
-        self.splitting = self.split_factor > 0 or self.var_factor > 0
+        self.splitting = (self.split_factor > 0 or self.var_factor > 0) and partition == "kmeans"
         self.capk = self.split_factor / self.C_init if grow_cap else 0.0       # sphere_gpu.py:130
         self.reset_at = reset_at
         self.resets = 0
         self.summary_bits = summary_bits
+        if partition == "random":                                   # every slot is a fixed direction: nothing to fit or split
+            self.C_init, self.split_factor, self.var_factor, self.capk = C, 0.0, 0.0, 0.0
         if self.C_init > C:
             raise ValueError("C_init must be <= C")
         self.initialized = False
@@ -214,7 +226,10 @@ class ClusterOracle:
         Kr = Kb - mu.unsqueeze(1)
         todo = ~self.fitted[heads]
         if todo.any():
-            _, cent = kmeans_cosine(Kr[todo], self.C_init, self.kmeans_iters, self.seed)
+            if self.partition == "random":                          # sphere_gpu.py:147, sphere_skip.py:54-67
+                cent = fixed_directions(self.C, self.d, self.seed).expand(int(todo.sum()), -1, -1)
+            else:
+                _, cent = kmeans_cosine(Kr[todo], self.C_init, self.kmeans_iters, self.seed)
             self.cent[heads[todo], :self.C_init] = cent
             self.n_c[heads[todo]] = self.C_init
             self.fitted[heads[todo]] = True
@@ -399,9 +414,17 @@ class ClusterOracle:
         e = torch.where(p >= 0, self.mmax.unsqueeze(1) * p, self.mmin.unsqueeze(1) * p)
         return e.masked_fill((self.count == 0).unsqueeze(1), -math.inf)
 
-    def shared_score(self, e: torch.Tensor) -> torch.Tensor:
-        """Sum over a group's query heads of each head's softmax over clusters (sphere_gpu.py:431,:439)."""
+    def shared_score(self, e: torch.Tensor, group: str = "sum_share") -> torch.Tensor:
+        """One score per cluster for a group's query heads (sphere_gpu.py:431-439): the sum over the heads of
+        each head's softmax over clusters (``sum_share``), the largest scaled score (``max``), or the largest
+        score relative to its head's best cluster (``max_rel``)."""
         z = e * (1.0 / math.sqrt(self.d))
+        if group == "max":
+            return z.max(1).values
+        if group == "max_rel":
+            return (z - z.max(2, keepdim=True).values).max(1).values
+        if group != "sum_share":
+            raise ValueError(f"unknown group mode {group!r}")
         return torch.softmax(z, dim=2).sum(1).masked_fill(self.count == 0, -math.inf)
 
     @staticmethod
@@ -415,14 +438,14 @@ class ClusterOracle:
         rank = torch.empty_like(order).scatter_(1, order, torch.arange(C).expand(R, C))
         return rank < n_sel.unsqueeze(1)
 
-    def select(self, q: torch.Tensor, *, n: int, budget: float):
+    def select(self, q: torch.Tensor, *, n: int, budget: float, group: str = "sum_share"):
         """``labels [h, n]`` and 0/1 weights ``w [h, C+1]`` (column ``C`` = always-read rows)
-        for ``group="sum_share"`` (sphere_gpu.py:412-442)."""
+        for the shared group modes (sphere_gpu.py:412-442)."""
         w = torch.zeros(self.h, self.C + 1)
         w[:, self.C] = 1.0
         need = self.need(budget)
         if self.end > 1 and need > 0:
-            w[:, :self.C] = self.take_until(self.shared_score(self.scores(q)), self.count, need).float()
+            w[:, :self.C] = self.take_until(self.shared_score(self.scores(q), group), self.count, need).float()
         return self.labels[:, :n], w
 
     def positions(self, w: torch.Tensor, n: int) -> list[torch.Tensor]:

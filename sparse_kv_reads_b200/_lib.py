@@ -68,7 +68,7 @@ def _declare(lib) -> None:
     lib.skv_merge.restype = i32
     lib.skv_merge.argtypes = [vp, vp, vp, vp, i32, i32, i32, i32, vp]
     lib.skv_select.restype = i32
-    lib.skv_select.argtypes = [C.POINTER(SkvState), vp, i32, i32, vp, vp, vp, vp, i64, vp, vp, vp, vp, vp, f32, vp]
+    lib.skv_select.argtypes = [C.POINTER(SkvState), vp, i32, i32, vp, vp, vp, vp, i64, vp, vp, vp, vp, vp, f32, i32, vp]
     lib.skv_select_workspace_bytes.restype = i64
     lib.skv_select_workspace_bytes.argtypes = [i32, i32, i32]
     lib.skv_debug_select_probe.restype = None

@@ -4,7 +4,7 @@ Host-side mirror of the reference's state objects for this path, collapsed into 
 reference's names: ``SphereIndexGPU`` (ssa/attn/sphere_gpu.py:113-442), ``SphereIndexFused``
 (ssa/kernels/sphere_fused.py:316-518) and ``SphereIndexGraph`` (ssa/kernels/graph_kernels.py:192-279).
 Every computation is a call into the CUDA library through its C ABI; there is no PyTorch fallback.
-Built: the k-means partition, the shared (``sum_share``) selection, the size cap (fixed, or growing with
+Built: the k-means and fixed-random-direction partitions, the shared selections (``sum_share``, ``max``, ``max_rel``), the size cap (fixed, or growing with
 the context under ``grow_cap``), splits on the spread of a cluster (``var_factor``), the refit of a head
 that ran out of clusters (``reset_at``) and recentring; the reference's other options raise ``ValueError``.
 """
@@ -19,7 +19,7 @@ import torch
 from . import _lib
 from ._lib import SkvState, check, dtype_code, lib, ptr, stream_ptr
 
-GROUPS = ("sum_share",)
+GROUPS = {"sum_share": 0, "max": 1, "max_rel": 2}     # SKV_GROUP_* of the C ABI; "per_head" is not built
 
 # state arrays: name -> (trailing shape as a function of (C, d, capacity), dtype, fill value)
 _FIELDS = {
@@ -107,8 +107,10 @@ class SphereIndexGraph:
                  var_factor: float = 0.0, var_min: int = 8, async_check: bool = True, max_lag: int = 2,
                  split_scratch: int = 8192, summary_bits: int = 8, block_n: int = 32, compact_block: int = 1024,
                  refit_every: int = 0, arena: ClusterArena | None = None, layer: int = 0):
-        if partition != "kmeans":
-            raise ValueError(f"unknown partition {partition!r}: only 'kmeans' is built")
+        if partition not in ("kmeans", "random"):
+            raise ValueError(f"unknown partition {partition!r}")
+        if partition == "random" and kind != "random":
+            raise ValueError(f"direction kind {kind!r} is not built (only 'random')")
         if summary_bits not in (8, 32):
             raise ValueError("summary_bits must be 8 or 32")
         assert C >= 16 and C & (C - 1) == 0, "C must be a power of two >= 16"
@@ -120,6 +122,10 @@ class SphereIndexGraph:
         self.splitting = self.split_factor > 0 or self.var_factor > 0
         # cap per clustered key when the cap follows the context (ssa/attn/sphere_gpu.py:130)
         self.capk = self.split_factor / self.C_init if grow_cap else 0.0
+        if partition == "random":                           # every slot is a fixed direction: no fit, no splits
+            if self.splitting and (split_factor or var_factor or cap_keys):
+                raise ValueError("C_init must be <= C, and splitting needs partition='kmeans'")
+            self.C_init, self.split_factor, self.var_factor, self.capk, self.splitting = C, 0.0, 0.0, 0.0, False
         if self.C_init > C:
             raise ValueError("C_init must be <= C, and splitting needs partition='kmeans'")
         self.C, self.window, self.delta, self.capacity = C, window, delta, capacity
@@ -214,7 +220,13 @@ class SphereIndexGraph:
         if m < 1:
             return                                          # nothing to cluster yet: fitted on a later call
         g = torch.Generator(device="cpu").manual_seed(self.seed)
-        init = torch.randperm(m, generator=g)[torch.arange(self.C_init) % m].to(torch.int32).to(K.device)
+        if self.partition == "random":
+            # fixed unit directions, the same for every head (ssa/attn/sphere_skip.py:54-56,:67)
+            x = torch.randn(self.C, self.d, generator=g, dtype=torch.float64)
+            self.cent.copy_((x / x.norm(dim=1, keepdim=True)).float().to(K.device).expand(self.H_kv, -1, -1))
+            init = None
+        else:
+            init = torch.randperm(m, generator=g)[torch.arange(self.C_init) % m].to(torch.int32).to(K.device)
         L = lib()
         hl = None if heads is None else heads.to(torch.int32).to(K.device)
         entries = self.H_kv if hl is None else int(hl.numel())
@@ -222,7 +234,7 @@ class SphereIndexGraph:
         ws = _workspace(K.device, nbytes)
         splits_kept = self.nsplit.clone() if hl is not None else None
         check(L.skv_fit(ctypes.byref(self._st), K.data_ptr(), dtype_code(K.dtype), K.stride(0), K.stride(1), n,
-                        self.window, self.C_init, self.kmeans_iters, init.data_ptr(), self.cap_keys,
+                        self.window, self.C_init, self.kmeans_iters, ptr(init), self.cap_keys,
                         self.split_factor, self.capk, self.var_factor,
                         None if hl is None else hl.data_ptr(), entries, ws.data_ptr(), ws.numel(),
                         stream_ptr(K.device)), "skv_fit")
@@ -336,7 +348,7 @@ class SphereIndexGraph:
 
     # ---- selection -------------------------------------------------------------------------------
     def _select(self, q: torch.Tensor, n_dev: torch.Tensor, *, shared_in=None, shared_out=None, e_out=None,
-                listed: bool = True) -> None:
+                listed: bool = True, group: str = "sum_share") -> None:
         """Score and pick; with ``listed`` also build the ascending row list ``idx``/``cnt`` (otherwise
         ``cnt`` is zeroed and the label-driven attention kernel fills it)."""
         H, d = q.shape
@@ -351,7 +363,8 @@ class SphereIndexGraph:
         check(L.skv_select(ctypes.byref(self._st), q.data_ptr(), dtype_code(q.dtype), G, n_dev.data_ptr(),
                            self.wbuf.data_ptr(), self.selbits.data_ptr(), self.idx.data_ptr() if listed else None,
                            self.idx.stride(0), self.cnt.data_ptr(), ptr(shared_in), ptr(shared_out), ptr(e_out),
-                           self._sel_ws.data_ptr(), 1.0 / math.sqrt(d), stream_ptr(q.device)), "skv_select")
+                           self._sel_ws.data_ptr(), 1.0 / math.sqrt(d), GROUPS[group], stream_ptr(q.device)),
+              "skv_select")
 
     def labels_and_weights(self, q: torch.Tensor, *, n: int, budget: float, group: str = "sum_share",
                            shared_in=None, shared_out=None, e_out=None):
@@ -362,7 +375,7 @@ class SphereIndexGraph:
             raise ValueError(f"unknown group mode {group!r}")
         self.need_dev.fill_(math.ceil(budget * (self.end - 1)) if self.end > 1 else 0)
         self._n_scalar.fill_(n)
-        self._select(q, self._n_scalar, shared_in=shared_in, shared_out=shared_out, e_out=e_out)
+        self._select(q, self._n_scalar, shared_in=shared_in, shared_out=shared_out, e_out=e_out, group=group)
         return self.labels[:, :n], self.wbuf
 
     # ---- attention -------------------------------------------------------------------------------

@@ -112,8 +112,10 @@ __global__ void __launch_bounds__(128) seed_kernel(const FitView v, const int32_
         v.st.cent[((int64_t)h * v.st.C + j) * HEAD_DIM + t] = 0.f;
         return;
     }
-    const int i = min(max(init_pos[j], 0), v.m - 1);
-    v.st.cent[((int64_t)h * v.st.C + j) * HEAD_DIM + t] = v.Xn[((int64_t)e * v.m + i) * HEAD_DIM + t];
+    if (init_pos) {                                      // null: the caller's centroids stay as they are
+        const int i = min(max(init_pos[j], 0), v.m - 1);
+        v.st.cent[((int64_t)h * v.st.C + j) * HEAD_DIM + t] = v.Xn[((int64_t)e * v.m + i) * HEAD_DIM + t];
+    }
     if (j == 0 && t == 0) v.st.n_c[h] = C_init;
 }
 
@@ -734,7 +736,8 @@ extern "C" int skv_fit(const skv_state *st, const void *K, int dtype, int64_t k_
                        void *workspace, int64_t workspace_bytes, void *stream) {
     int rc = check_state(st);
     if (rc) return rc;
-    if (!K || !init_pos || !workspace) return SKV_E_NULL;
+    if (!K || !workspace) return SKV_E_NULL;
+    if (!init_pos) iters = 0;                            // given centroids are kept: no Lloyd step
     if (dtype != SKV_BF16 && dtype != SKV_F32) return SKV_E_DTYPE;
     if (n < 0 || n > st->capacity || window < 0 || iters < 0 || C_init < 1 || C_init > st->C || cap_keys < 0.f ||
         split_factor < 0.f || capk < 0.f || var_factor < 0.f)

@@ -33,6 +33,7 @@ struct SelectParams {
     int32_t *ticket;          // [heads]
     float *pstat;             // [heads, SEL_MAX_CTAS, 16, 2] slice (max, sum of exp) per query head
     float scale;
+    int group;                // how a group's query heads share one ranking: SKV_GROUP_*
     unsigned long long *probe;  // optional [16] phase time stamps (ns) of head 0's picking CTA, for tuning
 };
 
@@ -328,7 +329,8 @@ __global__ void __launch_bounds__(SEL_THREADS) score_pick_kernel(const SelectPar
             if (g < G)
                 for (int c = tid; c < mine; c += SEL_THREADS) {
                     const float zz = z[g * C + c];
-                    const float ex = zz > -INFINITY ? expf(zz - zm[g]) : 0.f;
+                    // the max modes rank the scaled scores themselves; sum_share hands on exp(z - slice max)
+                    const float ex = p.group != SKV_GROUP_SUM_SHARE ? zz : (zz > -INFINITY ? expf(zz - zm[g]) : 0.f);
                     if (nb > 1) __stcg(zg + g * C + c_lo + c, ex);
                     else z[g * C + c] = ex;                 // a lone CTA keeps the values where the pick reads them
                     s += ex;
@@ -352,6 +354,8 @@ __global__ void __launch_bounds__(SEL_THREADS) score_pick_kernel(const SelectPar
             if (!s_last) return;
             __threadfence();
             if (tid == 0) p.ticket[h] = 0;
+        } else {
+            __syncthreads();                               // thread 0's statistics are read by other warps below
         }
     }
     stamp(p, h, 2);
@@ -375,6 +379,10 @@ __global__ void __launch_bounds__(SEL_THREADS) score_pick_kernel(const SelectPar
             if (lane < nb) s0 = __ldcg(reinterpret_cast<const float2 *>(ps + (lane * 16 + g) * 2));
             if (lane + 32 < nb) s1 = __ldcg(reinterpret_cast<const float2 *>(ps + ((lane + 32) * 16 + g) * 2));
             const float m = warp_max(fmaxf(s0.x, s1.x));
+            if (p.group != SKV_GROUP_SUM_SHARE) {          // only the head's best score is needed (max_rel)
+                if (lane == 0) fb[g] = m;
+                continue;
+            }
             const float e0 = s0.x > -INFINITY ? expf(s0.x - m) : 0.f, e1 = s1.x > -INFINITY ? expf(s1.x - m) : 0.f;
             const float t = warp_sum(e0 * s0.y + e1 * s1.y);
             if (lane < nb) fb[lane * 16 + g] = e0 / t;
@@ -386,7 +394,10 @@ __global__ void __launch_bounds__(SEL_THREADS) score_pick_kernel(const SelectPar
     if (scoring) {
         for (int c = tid; c < C; c += SEL_THREADS) {
             float s = -INFINITY;
-            if (c < n_c && ci[c] > 0) {
+            if (c < n_c && ci[c] > 0 && p.group != SKV_GROUP_SUM_SHARE) {
+                for (int g = 0; g < G; ++g)
+                    s = fmaxf(s, z[g * C + c] - (p.group == SKV_GROUP_MAX_REL ? fb[g] : 0.f));
+            } else if (c < n_c && ci[c] > 0) {
                 int sl = (int)((float)c * inv_per);            // slice of cluster c, without an integer division
                 sl += ((sl + 1) * per <= c) - (sl * per > c);
                 const float *f = fb + sl * 16;
@@ -571,7 +582,7 @@ extern "C" int64_t skv_select_workspace_bytes(int heads, int G, int C) {
 
 extern "C" int skv_select(const skv_state *st, const void *q, int dtype, int G, const int32_t *n_dev, float *w,
                           uint32_t *selbits, int32_t *idx, int64_t idx_stride, int32_t *cnt, const float *shared_in,
-                          float *shared_out, float *e_out, void *workspace, float scale, void *stream) {
+                          float *shared_out, float *e_out, void *workspace, float scale, int group, void *stream) {
     if (!st || !n_dev || !w || !cnt || !workspace) return SKV_E_NULL;
     if (!shared_in && !q) return SKV_E_NULL;
     if (!st->count || !st->n_c || !st->end || !st->need || !st->labels || !st->mmax || !st->mmin) return SKV_E_NULL;
@@ -580,6 +591,7 @@ extern "C" int skv_select(const skv_state *st, const void *q, int dtype, int G, 
     if (G < 1 || G > 16) return SKV_E_DIM;
     if (dtype != SKV_BF16 && dtype != SKV_F32) return SKV_E_DTYPE;
     if (st->summary_bits != 8 && st->summary_bits != 32) return SKV_E_RANGE;
+    if (group < SKV_GROUP_SUM_SHARE || group > SKV_GROUP_MAX_REL) return SKV_E_RANGE;
     if (st->summary_bits == 8 ? !st->dir8 : !st->sum_dir) return SKV_E_NULL;
     if (st->heads <= 0 || st->heads > 65535 || st->capacity <= 0 || (idx && idx_stride < st->capacity)) return SKV_E_RANGE;
     if (st->capacity % 8 || !aligned16(st->labels) || !aligned16(workspace)) return SKV_E_ALIGN;
@@ -588,7 +600,7 @@ extern "C" int skv_select(const skv_state *st, const void *q, int dtype, int G, 
     if ((int)smem > device_max_smem_optin()) return SKV_E_DIM;
     SelectParams p;
     p.st = *st; p.q = q; p.G = G; p.n_dev = n_dev; p.w = w; p.idx = idx; p.idx_stride = idx_stride; p.cnt = cnt;
-    p.shared_in = shared_in; p.shared_out = shared_out; p.e_out = e_out; p.scale = scale;
+    p.shared_in = shared_in; p.shared_out = shared_out; p.e_out = e_out; p.scale = scale; p.group = group;
     p.probe = g_probe;
     char *ws = static_cast<char *>(workspace);
     p.zbuf = reinterpret_cast<float *>(ws);

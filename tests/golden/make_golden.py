@@ -53,9 +53,10 @@ def case_stream(ref, *, h, G, n0, steps, C, C_init, cap_keys, split_factor, wind
     d = 128
     K, V = clustered_keys(h, n0 + steps, d, seed=seed)
     Q = queries(h * G, d, steps + 1, seed + 1000)
+    opts = {"partition": "kmeans", **extra}
     ix = ref["SphereIndexGPU"](C=C, C_init=C_init, cap_keys=cap_keys, split_factor=split_factor, window=window,
                                delta=delta, capacity=n0 + steps, check_every=check_every, seed=0,
-                               partition="kmeans", kmeans_iters=10, **extra)
+                               kmeans_iters=10, **opts)
     ix.observe(K, n0)
     gold = {"input_sum": float(K.double().sum()), "cfg": dict(h=h, G=G, n0=n0, steps=steps, C=C, C_init=C_init,
             cap_keys=cap_keys, split_factor=split_factor, window=window, delta=delta, check_every=check_every,
@@ -69,6 +70,8 @@ def case_stream(ref, *, h, G, n0, steps, C, C_init, cap_keys, split_factor, wind
             out = ref["label_weighted_attention"](Q[t].double(), K[:, :n].double(), V[:, :n].double(), labels, w.double())
             gold["probes"][t] = {"w": w.to(torch.uint8), "out": out.float(), "n_c": ix.n_c.clone(),
                                  "splits": ix.splits, "rebuilds": ix.rebuilds}
+            for grp in ("max", "max_rel"):                  # the other shared ways of ranking clusters
+                gold["probes"][t]["w_" + grp] = ix.labels_and_weights(Q[t], n=n, budget=budget, group=grp)[1].to(torch.uint8)
     gold["final"] = snapshot(ix, full=full)
     return gold
 
@@ -134,6 +137,10 @@ def main() -> None:
         "small_reset": case_stream(ref, h=2, G=2, n0=400, steps=300, C=64, C_init=16, cap_keys=24.0, split_factor=0.0,
                                    window=8, delta=math.inf, check_every=16, seed=26, budget=0.3, full=False,
                                    probe_every=100, reset_at=40),
+        # fixed random directions instead of fitted centroids, with recentring
+        "small_random": case_stream(ref, h=2, G=2, n0=400, steps=120, C=32, C_init=None, cap_keys=0.0, split_factor=0.0,
+                                    window=8, delta=0.003, check_every=4, seed=27, budget=0.3, full=False,
+                                    probe_every=40, partition="random"),
     }
     torch.save(gold, os.path.join(HERE, "small.pt"))
     # the CPU-runnable benchmark configuration: 8 KV heads, 16 query heads, n 4096 + 512, 256 -> cap 64

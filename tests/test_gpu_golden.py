@@ -16,7 +16,8 @@ from _helpers import DEV, row_sets
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("case", ["small_cap", "small_fixed", "small_grow", "small_var", "small_reset", "config1"])
+@pytest.mark.parametrize("case", ["small_cap", "small_fixed", "small_grow", "small_var", "small_reset", "small_random",
+                                  "config1"])
 def test_cuda_stream_against_the_reference_golden_vectors(golden_small, golden_config1, case):
     g = golden_config1["config1"] if case == "config1" else golden_small[case]
     c = g["cfg"]
@@ -25,7 +26,7 @@ def test_cuda_stream_against_the_reference_golden_vectors(golden_small, golden_c
     assert abs(float(K.double().sum()) - g["input_sum"]) < 1e-6
     Q = torch.randn(c["steps"] + 1, c["h"] * c["G"], 128, generator=torch.Generator().manual_seed(c["seed"] + 1000))
     cap = -(-n_end // 8) * 8
-    extra = {k: c[k] for k in ("grow_cap", "reset_at", "var_factor", "var_min") if k in c}
+    extra = {k: c[k] for k in ("grow_cap", "reset_at", "var_factor", "var_min", "partition") if k in c}
     # the reference's PyTorch class refits a head the moment it reaches reset_at; the flag protocol does so at
     # the next check, so check after every step (the drift test is off in that case: delta = inf)
     every = 1 if c.get("reset_at") and math.isinf(c["delta"]) else c["check_every"]
@@ -53,6 +54,9 @@ def test_cuda_stream_against_the_reference_golden_vectors(golden_small, golden_c
             boundary = max(boundary, diff)
             if diff == 0:                                   # same selection: the attention must match to fp32 accuracy
                 worst = max(worst, float((out.cpu() - p["out"]).abs().max()))
+            for grp in ("max", "max_rel"):                  # the other shared rankings (exact ties may fall either way)
+                _, wg = ix.labels_and_weights(Q[t].to(DEV), n=n, budget=c["budget"], group=grp)
+                boundary = max(boundary, int((wg.cpu().to(torch.uint8) != p["w_" + grp]).sum(1).max()))
             assert int((ix.n_c.cpu() - p["n_c"]).abs().max()) <= 3
     fin = g["final"]
     same = (ix.labels.cpu()[:, :n_end] == fin["labels"]).float().mean().item()
