@@ -632,6 +632,7 @@ extern "C" int skv_select(const skv_state *st, const void *q, int dtype, int G, 
     int ctas = 2 * device_sm_count() / st->heads;
     ctas = ctas < 1 ? 1 : (ctas > SEL_MAX_CTAS ? SEL_MAX_CTAS : ctas);
     if (shared_in) ctas = 1;
+    if (const char *e = getenv("SKV_SEL_CTAS")) { const int v = atoi(e); if (v >= 1 && v <= SEL_MAX_CTAS) ctas = v; }
     SKV_CUDA_OK(launch_pdl(kern, dim3(ctas, st->heads), dim3(SEL_THREADS), smem, s, p));
     if (idx) list_kernel<<<st->heads, 512, (st->C / 32 + 1) * 4, s>>>(p);
     SKV_CUDA_OK(cudaGetLastError());
