@@ -286,26 +286,25 @@ int skv_gemv(const void *W, int N, int K, void *y, int B, int mode, const void *
  * Replaces the all-reduce after the row-parallel `o` and `down` products of a tensor-parallel decode step (the
  * reference decodes on one GPU; its host model's layers are models/graph_decode.py:100-121).  Every GPU of the
  * group owns one exchange buffer, mapped into the other processes (skv_comm_alloc / export / open):
- *   data   float32 [2 slots][world][cap_elems]   slot s, source rank r: the partial sums r computed
- *   flags  uint32  [2 slots][world]              CTAs of rank r that have delivered into slot s, ever
- *   uses   uint32  [2]                           launches of the local producer of slot s, ever
- *   nctas  uint32  [2]                           CTAs of that producer
- * The producing product (skv_gemv with `out` set) stores its float32 sums into slot s / row `rank` of EVERY
- * GPU's buffer over NVLink and then adds one to that GPU's flag.  The consuming product (mode 3) waits until
- * each flag of the slot has reached uses x nctas - a bounded wait of about a second, after which it sets
- * SKV_ST_WAIT_TIMEOUT in *status and carries on - and sums the `world` partials in rank order, so every GPU
- * obtains the same bits.  Two slots are enough for a decoder layer (`o`, `down`): a slot's next producer cannot
- * start anywhere before every GPU has consumed the other slot, which each does after its use of this one. */
+ *   data   [2 slots][world][cap_elems] of 8-byte pairs {float32 bits, epoch}
+ *   tick   uint32, advanced once per decode step on every GPU (skv_comm_tick)
+ * The producing product (skv_gemv_tp with `out` set) stores each of its float32 sums, paired with the epoch
+ * tick x 256 + seq + 1, into slot seq % 2 / row `rank` of EVERY GPU's buffer with one aligned 8-byte store over
+ * NVLink: no fence and no flag, a reader that finds the epoch has the value.  The consuming product (mode 3)
+ * polls the `world` partials of each input element until they carry the epoch - a bounded wait of about a
+ * second, after which it sets SKV_ST_WAIT_TIMEOUT in *status and carries on - and adds them in rank order, so
+ * every GPU obtains the same bits.  `seq` numbers the exchanges of a step (0..254), the same on every GPU; two
+ * slots are enough for a decoder layer (`o`, `down` alternate): a slot's next producer cannot start anywhere
+ * before every GPU has consumed the other slot, which each does after its use of this one. */
 typedef struct skv_comm {
     int32_t world, rank;
-    int32_t cap_elems;        /* floats per (slot, source rank) */
+    int32_t cap_elems;        /* pairs per (slot, source rank); a multiple of 8 */
     int32_t reserved;
-    float    *data[8];        /* data region of every rank's buffer, as mapped in this process */
-    uint32_t *flags[8];       /* flag words of every rank's buffer */
-    uint32_t *uses, *nctas;   /* local counters */
+    void     *data[8];        /* every rank's buffer, as mapped in this process */
+    uint32_t *tick;           /* local */
     int32_t  *status;         /* local, one word */
 } skv_comm;
-/* Bytes of one exchange buffer; its regions sit at fixed offsets (data first, then flags, uses, nctas, status). */
+/* Bytes of one exchange buffer (data, then tick and status of the owner). */
 int64_t skv_comm_bytes(int world, int cap_elems);
 /* cudaMalloc + zero fill of an exchange buffer on the current device; 64-byte handle for the other processes
  * (cudaIpcGetMemHandle); mapping of another process's buffer (cudaIpcOpenMemHandle); unmapping; release. */
@@ -316,13 +315,15 @@ int skv_comm_close(void *ptr);
 int skv_comm_free(void *ptr);
 /* Fills `c` for buffers `bases[0..world)` (bases[rank] is the local one). */
 int skv_comm_view(skv_comm *c, void *const *bases, int world, int rank, int cap_elems);
-/* skv_gemv with the exchange: `out` non-null -> the sums go to slot `out_slot` of every GPU instead of y;
- * mode 3 -> as mode 1 with delta = the sum over ranks of slot `in_slot` of `in` (delta argument unused). */
+/* Advances the local tick (one tiny launch): once per decode step, on every GPU, ahead of the step's exchanges. */
+int skv_comm_tick(const skv_comm *c, void *stream);
+/* skv_gemv with the exchange: `out` non-null -> the sums go to every GPU's buffer as exchange `out_seq` instead of
+ * y; mode 3 -> as mode 1 with delta = the sum over ranks of exchange `in_seq` of `in` (no delta argument). */
 int skv_gemv_tp(const void *W, int N, int K, void *y, int B, int mode, const void *x, const void *h_in,
-                const void *norm_w, void *h_out, float eps, const skv_comm *in, int in_slot,
-                const skv_comm *out, int out_slot, void *stream);
-/* delta[B, N] (bf16) = sum over ranks of slot `slot`, after the same wait: for consumers other than skv_gemv. */
-int skv_comm_reduce(const skv_comm *c, int slot, void *delta, int B, int N, void *stream);
+                const void *norm_w, void *h_out, float eps, const skv_comm *in, int in_seq,
+                const skv_comm *out, int out_seq, void *stream);
+/* delta[B, N] (bf16) = sum over ranks of exchange `seq`, after the same wait: for consumers other than skv_gemv. */
+int skv_comm_reduce(const skv_comm *c, int seq, void *delta, int B, int N, void *stream);
 /* The buffer's status word (SKV_ST_WAIT_TIMEOUT), read back with a synchronising copy; negative on error. */
 int skv_comm_status(const skv_comm *c);
 

@@ -21,7 +21,7 @@ EXPORTS = ("skv_version", "skv_error_string", "skv_last_cuda_error", "skv_attend
            "skv_attend_workspace_bytes", "skv_attend", "skv_attend_static", "skv_attend_labels", "skv_merge", "skv_select_workspace_bytes", "skv_select", "skv_debug_select_probe", "skv_debug_attend_probe", "skv_set_overlap", "skv_insert",
            "skv_insert_max_members", "skv_fit_workspace_bytes", "skv_fit", "skv_rebin",
            "skv_add_rmsnorm", "skv_qk_rope_cache", "skv_silu_mul", "skv_gemv", "skv_gemv_supported", "skv_gemv_tp", "skv_comm_bytes", "skv_comm_alloc",
-           "skv_comm_export", "skv_comm_open", "skv_comm_close", "skv_comm_free", "skv_comm_view", "skv_comm_reduce", "skv_comm_status")
+           "skv_comm_export", "skv_comm_open", "skv_comm_close", "skv_comm_free", "skv_comm_view", "skv_comm_tick", "skv_comm_reduce", "skv_comm_status")
 
 
 class SkvError(RuntimeError):
@@ -31,8 +31,7 @@ class SkvError(RuntimeError):
 class SkvComm(C.Structure):
     """``skv_comm`` of include/skv.h: one rank's view of the exchange buffers of a tensor-parallel group."""
     _fields_ = [("world", C.c_int32), ("rank", C.c_int32), ("cap_elems", C.c_int32), ("reserved", C.c_int32),
-                ("data", C.c_void_p * 8), ("flags", C.c_void_p * 8), ("uses", C.c_void_p), ("nctas", C.c_void_p),
-                ("status", C.c_void_p)]
+                ("data", C.c_void_p * 8), ("tick", C.c_void_p), ("status", C.c_void_p)]
 
 
 class SkvState(C.Structure):
@@ -111,6 +110,8 @@ def _declare(lib) -> None:
     lib.skv_comm_free.argtypes = [vp]
     lib.skv_comm_view.restype = i32
     lib.skv_comm_view.argtypes = [C.POINTER(SkvComm), C.POINTER(C.c_void_p), i32, i32, i32]
+    lib.skv_comm_tick.restype = i32
+    lib.skv_comm_tick.argtypes = [C.POINTER(SkvComm), vp]
     lib.skv_comm_status.restype = i32
     lib.skv_comm_status.argtypes = [C.POINTER(SkvComm)]
     lib.skv_comm_reduce.restype = i32

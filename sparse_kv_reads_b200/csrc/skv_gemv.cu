@@ -37,50 +37,67 @@ struct GemvParams {
     __nv_bfloat16 *h_out;
     float eps;
     // exchange through peer memory (row-parallel products of a tensor-parallel group); world 0 = unused
-    float *out_data[8];            // every rank's data region
-    uint32_t *out_flags[8];        // every rank's flag words
-    uint32_t *out_uses, *out_nctas;
-    int out_world, out_rank, out_slot, out_cap;
-    const float *in_data;          // the local buffer
-    const uint32_t *in_flags, *in_uses, *in_nctas;
-    int in_world, in_slot, in_cap;
+    uint2 *out_data[8];            // every rank's buffer: [2 slots][world][cap] of {value bits, epoch}
+    const uint32_t *out_tick;
+    int out_world, out_rank, out_seq, out_cap;
+    const uint2 *in_data;          // the local buffer
+    const uint32_t *in_tick;
+    int in_world, in_seq, in_cap;
     int32_t *status;
 };
 
+__device__ __forceinline__ float bf16r(float x) { return __bfloat162float(__float2bfloat16(x)); }
+
 constexpr int WAIT_LIMIT = 1 << 20;     // polls of about a microsecond each: gives up after about a second
 
-// Wait (bounded) until every rank's CTAs have delivered into `slot` of the local buffer as often as the local
-// producer of that slot has been launched.  Threads 0..world-1 poll one flag each.
-__device__ __forceinline__ void wait_partials(const uint32_t *flags, const uint32_t *uses, const uint32_t *nctas,
-                                              int world, int slot, int32_t *status) {
-    if ((int)threadIdx.x < world) {
-        const uint32_t target = uses[slot] * nctas[slot];
-        const uint32_t *f = flags + slot * world + threadIdx.x;
-        uint32_t v;
-        int it = 0;
-        for (;;) {
-            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
-            if ((int32_t)(v - target) >= 0 || ++it >= WAIT_LIMIT) break;
-            __nanosleep(100);
+// Every exchanged value travels as one aligned 8-byte store {float bits, epoch}: the epoch names the decode step
+// (the buffer's tick) and the exchange within it, so a reader that finds the epoch it expects has the value too -
+// no fence, no separate flag, one NVLink flight.
+__device__ __forceinline__ uint32_t epoch_of(const uint32_t *tick, int seq) { return tick[0] * 256u + (uint32_t)seq + 1u; }
+
+__device__ __forceinline__ void store_pair(uint2 *dst, float v, uint32_t epoch) {
+    asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1, %2};" ::"l"(dst), "r"(__float_as_uint(v)), "r"(epoch) : "memory");
+}
+
+// Eight consecutive partial sums of one rank (64 bytes = four 16-byte loads of two pairs each), polled until
+// all eight carry `epoch`; bounded: on expiry *status gets SKV_ST_WAIT_TIMEOUT and whatever is there is used.
+__device__ __forceinline__ void load_pairs8(const uint2 *src, uint32_t epoch, int32_t *status, float (&out)[8]) {
+    uint4 q[4];
+    int it = 0;
+    for (;;) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+            asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+                         : "=r"(q[i].x), "=r"(q[i].y), "=r"(q[i].z), "=r"(q[i].w)
+                         : "l"(reinterpret_cast<const uint4 *>(src) + i) : "memory");
+        bool ok = true;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) ok = ok && q[i].y == epoch && q[i].w == epoch;
+        if (ok) break;
+        if (++it >= WAIT_LIMIT) {
+            if (status) atomicOr(status, SKV_ST_WAIT_TIMEOUT);
+            break;
         }
-        if ((int32_t)(v - target) < 0 && status) atomicOr(status, SKV_ST_WAIT_TIMEOUT);
+        __nanosleep(40);
     }
-    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        out[2 * i] = __uint_as_float(q[i].x);
+        out[2 * i + 1] = __uint_as_float(q[i].z);
+    }
 }
 
 // One output value: to y, or as a float partial into slot/rank of every GPU's buffer.
-__device__ __forceinline__ void emit(const GemvParams &p, int b, int row, float v) {
+__device__ __forceinline__ void emit(const GemvParams &p, int b, int row, float v, uint32_t epoch) {
     if (p.out_world == 0) {
         p.y[(size_t)b * p.N + row] = __float2bfloat16(v);
         return;
     }
-    const size_t off = (size_t)(p.out_slot * p.out_world + p.out_rank) * p.out_cap + (size_t)b * p.N + row;
+    const size_t off = (size_t)((p.out_seq & 1) * p.out_world + p.out_rank) * p.out_cap + (size_t)b * p.N + row;
 #pragma unroll
     for (int r = 0; r < 8; ++r)
-        if (r < p.out_world) p.out_data[r][off] = v;
+        if (r < p.out_world) store_pair(p.out_data[r] + off, v, epoch);
 }
-
-__device__ __forceinline__ float bf16r(float x) { return __bfloat162float(__float2bfloat16(x)); }
 
 template <int BP, bool TC>
 __global__ void __launch_bounds__(GEMV_THREADS) gemv_kernel(const GemvParams p) {
@@ -117,11 +134,8 @@ __global__ void __launch_bounds__(GEMV_THREADS) gemv_kernel(const GemvParams p) 
     }
     pdl_wait();
     pdl_trigger();
-    if (p.out_world && blockIdx.x == 0 && tid == 0) {       // read by the consumer of this slot, a later launch
-        p.out_uses[p.out_slot] += 1u;
-        p.out_nctas[p.out_slot] = gridDim.x;
-    }
-    if (p.mode == 3) wait_partials(p.in_flags, p.in_uses, p.in_nctas, p.in_world, p.in_slot, p.status);
+    const uint32_t out_epoch = p.out_world ? epoch_of(p.out_tick, p.out_seq) : 0u;
+    const uint32_t in_epoch = p.mode == 3 ? epoch_of(p.in_tick, p.in_seq) : 0u;
 
     // 2. the input of every sequence, in shared memory as bf16
     if (p.mode == 0) {
@@ -168,11 +182,11 @@ __global__ void __launch_bounds__(GEMV_THREADS) gemv_kernel(const GemvParams p) 
 #pragma unroll
                         for (int i = 0; i < 8; ++i) d[i] = 0.f;
                         for (int r = 0; r < p.in_world; ++r) {
-                            const float *src = p.in_data + (size_t)(p.in_slot * p.in_world + r) * p.in_cap + (size_t)b * K + v * 8;
-                            const float4 lo = __ldcg(reinterpret_cast<const float4 *>(src));
-                            const float4 hi = __ldcg(reinterpret_cast<const float4 *>(src) + 1);
-                            d[0] += lo.x; d[1] += lo.y; d[2] += lo.z; d[3] += lo.w;
-                            d[4] += hi.x; d[5] += hi.y; d[6] += hi.z; d[7] += hi.w;
+                            float part[8];
+                            load_pairs8(p.in_data + (size_t)((p.in_seq & 1) * p.in_world + r) * p.in_cap + (size_t)b * K + v * 8,
+                                        in_epoch, p.status, part);
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) d[i] += part[i];
                         }
                     } else {
                         load8(dr + v * 8, d);
@@ -247,12 +261,12 @@ __global__ void __launch_bounds__(GEMV_THREADS) gemv_kernel(const GemvParams p) 
             if (ks == 1) {
                 const int ra = r0 + t * 16 + (lane >> 2), rb = ra + 8;
                 if (kq < p.B) {
-                    if (ra < r0 + R) emit(p, kq, ra, acc[0]);
-                    if (rb < r0 + R) emit(p, kq, rb, acc[2]);
+                    if (ra < r0 + R) emit(p, kq, ra, acc[0], out_epoch);
+                    if (rb < r0 + R) emit(p, kq, rb, acc[2], out_epoch);
                 }
                 if (kq + 1 < p.B) {
-                    if (ra < r0 + R) emit(p, kq + 1, ra, acc[1]);
-                    if (rb < r0 + R) emit(p, kq + 1, rb, acc[3]);
+                    if (ra < r0 + R) emit(p, kq + 1, ra, acc[1], out_epoch);
+                    if (rb < r0 + R) emit(p, kq + 1, rb, acc[3], out_epoch);
                 }
             } else {
                 float *d = s_red[item];                    // [row in tile][sequence]
@@ -269,7 +283,7 @@ __global__ void __launch_bounds__(GEMV_THREADS) gemv_kernel(const GemvParams p) 
                 float sum = 0.f;
                 for (int sp = 0; sp < ks; ++sp) sum += s_red[sp * ntiles + t][e];
                 const int rg = t * 16 + rr;
-                if (rg < R && b < p.B) emit(p, b, r0 + rg, sum);
+                if (rg < R && b < p.B) emit(p, b, r0 + rg, sum, out_epoch);
             }
         }
     } else
@@ -293,32 +307,33 @@ __global__ void __launch_bounds__(GEMV_THREADS) gemv_kernel(const GemvParams p) 
 #pragma unroll
         for (int b = 0; b < BP; ++b) {
             const float s = warp_sum(acc[b]);
-            if (lane == 0 && b < p.B) emit(p, b, r0 + r, s);
+            if (lane == 0 && b < p.B) emit(p, b, r0 + r, s, out_epoch);
         }
-    }
-    // 4. tell every GPU that this CTA's sums have arrived
-    if (p.out_world) {
-        __threadfence_system();
-        __syncthreads();
-#pragma unroll
-        for (int r = 0; r < 8; ++r)
-            if (tid == r && r < p.out_world) atomicAdd_system(p.out_flags[r] + p.out_slot * p.out_world + p.out_rank, 1u);
     }
 }
 
-// delta[B, N] = sum over ranks of a slot's partials (for consumers that are not a product of this file)
-__global__ void __launch_bounds__(256) comm_reduce_kernel(const float *data, const uint32_t *flags, const uint32_t *uses,
-                                                          const uint32_t *nctas, int world, int slot, int cap,
-                                                          int32_t *status, __nv_bfloat16 *delta, int total) {
+// delta[B, N] = sum over ranks of an exchange's partials (for consumers that are not a product of this file)
+__global__ void __launch_bounds__(256) comm_reduce_kernel(const uint2 *data, const uint32_t *tick, int world, int seq,
+                                                          int cap, int32_t *status, __nv_bfloat16 *delta, int total) {
     pdl_wait();
     pdl_trigger();
-    wait_partials(flags, uses, nctas, world, slot, status);
-    for (int i = blockIdx.x * 256 + threadIdx.x; i < total; i += gridDim.x * 256) {
-        float s = 0.f;
-        for (int r = 0; r < world; ++r) s += __ldcg(data + (size_t)(slot * world + r) * cap + i);
-        delta[i] = __float2bfloat16(s);
+    const uint32_t epoch = epoch_of(tick, seq);
+    for (int v = blockIdx.x * 256 + threadIdx.x; v < total / 8; v += gridDim.x * 256) {
+        float d[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        for (int r = 0; r < world; ++r) {
+            float part[8];
+            load_pairs8(data + (size_t)((seq & 1) * world + r) * cap + (size_t)v * 8, epoch, status, part);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) d[i] += part[i];
+        }
+        __align__(16) __nv_bfloat16 o[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o[i] = __float2bfloat16(d[i]);
+        *reinterpret_cast<uint4 *>(delta + (size_t)v * 8) = *reinterpret_cast<const uint4 *>(o);
     }
 }
+
+__global__ void comm_tick_kernel(uint32_t *tick) { tick[0] += 1u; }
 
 struct GemvPlan {
     int BP, rows;
@@ -371,12 +386,22 @@ extern "C" int skv_gemv_supported(int N, int K, int B, int mode) {
     return plan_gemv(N, K, B, mode, pl) == SKV_OK && pl.worthwhile ? 1 : 0;
 }
 
-// Layout of an exchange buffer: data [2][world][cap] float, flags [2][world], uses [2], nctas [2], status [1]
-static int64_t comm_data_bytes(int world, int cap) { return ((int64_t)2 * world * cap * 4 + 255) / 256 * 256; }
+// Layout of an exchange buffer: data [2 slots][world][cap] of 8-byte {value, epoch} pairs, then the tick and the
+// status word of the owning rank
+static int64_t comm_data_bytes(int world, int cap) { return ((int64_t)2 * world * cap * 8 + 255) / 256 * 256; }
+
+static int check_comm(const skv_comm *c) {
+    if (c->world < 1 || c->world > 8 || c->rank < 0 || c->rank >= c->world || c->cap_elems < 8 || c->cap_elems % 8)
+        return SKV_E_RANGE;
+    if (!c->tick || !c->status) return SKV_E_NULL;
+    for (int r = 0; r < c->world; ++r)
+        if (!c->data[r]) return SKV_E_NULL;
+    return SKV_OK;
+}
 
 static int gemv_launch(const void *W, int N, int K, void *y, int B, int mode, const void *x, const void *h_in,
-                       const void *delta, const void *norm_w, void *h_out, float eps, const skv_comm *in, int in_slot,
-                       const skv_comm *out, int out_slot, void *stream) {
+                       const void *delta, const void *norm_w, void *h_out, float eps, const skv_comm *in, int in_seq,
+                       const skv_comm *out, int out_seq, void *stream) {
     if (!W || (!y && !out)) return SKV_E_NULL;
     if (mode < 0 || mode > 3 || (mode == 3) != (in != nullptr)) return SKV_E_RANGE;
     if (mode == 1 || mode == 3 ? (!h_in || !norm_w) : !x) return SKV_E_NULL;
@@ -386,14 +411,11 @@ static int gemv_launch(const void *W, int N, int K, void *y, int B, int mode, co
         return SKV_E_ALIGN;
     for (const skv_comm *c : {in, out}) {
         if (!c) continue;
-        if (c->world < 1 || c->world > 8 || c->rank < 0 || c->rank >= c->world || c->cap_elems < 8 || c->cap_elems % 4)
-            return SKV_E_RANGE;
-        if (!c->uses || !c->nctas || !c->status) return SKV_E_NULL;
-        for (int r = 0; r < c->world; ++r)
-            if (!c->data[r] || !c->flags[r]) return SKV_E_NULL;
+        const int rc = check_comm(c);
+        if (rc) return rc;
     }
-    if ((in && (in_slot < 0 || in_slot > 1 || (int64_t)B * K > in->cap_elems)) ||
-        (out && (out_slot < 0 || out_slot > 1 || (int64_t)B * N > out->cap_elems)))
+    if ((in && (in_seq < 0 || in_seq > 254 || (int64_t)B * K > in->cap_elems)) ||
+        (out && (out_seq < 0 || out_seq > 254 || (int64_t)B * N > out->cap_elems)))
         return SKV_E_RANGE;
     GemvPlan pl;
     const int rc = plan_gemv(N, K, B, mode, pl);
@@ -408,13 +430,13 @@ static int gemv_launch(const void *W, int N, int K, void *y, int B, int mode, co
     p.delta = static_cast<const __nv_bfloat16 *>(delta); p.g = static_cast<const __nv_bfloat16 *>(norm_w);
     p.h_out = static_cast<__nv_bfloat16 *>(h_out); p.eps = eps;
     if (out) {
-        for (int r = 0; r < out->world; ++r) { p.out_data[r] = out->data[r]; p.out_flags[r] = out->flags[r]; }
-        p.out_uses = out->uses; p.out_nctas = out->nctas;
-        p.out_world = out->world; p.out_rank = out->rank; p.out_slot = out_slot; p.out_cap = out->cap_elems;
+        for (int r = 0; r < out->world; ++r) p.out_data[r] = static_cast<uint2 *>(out->data[r]);
+        p.out_tick = out->tick;
+        p.out_world = out->world; p.out_rank = out->rank; p.out_seq = out_seq; p.out_cap = out->cap_elems;
     }
     if (in) {
-        p.in_data = in->data[in->rank]; p.in_flags = in->flags[in->rank]; p.in_uses = in->uses; p.in_nctas = in->nctas;
-        p.in_world = in->world; p.in_slot = in_slot; p.in_cap = in->cap_elems; p.status = in->status;
+        p.in_data = static_cast<const uint2 *>(in->data[in->rank]); p.in_tick = in->tick;
+        p.in_world = in->world; p.in_seq = in_seq; p.in_cap = in->cap_elems; p.status = in->status;
     }
     typedef void (*Kern)(const GemvParams);
     const int bi = (BP == 1 ? 0 : (BP == 2 ? 1 : (BP == 4 ? 2 : 3))) + (tc ? 4 : 0);
@@ -440,32 +462,29 @@ extern "C" int skv_gemv(const void *W, int N, int K, void *y, int B, int mode, c
 }
 
 extern "C" int skv_gemv_tp(const void *W, int N, int K, void *y, int B, int mode, const void *x, const void *h_in,
-                           const void *norm_w, void *h_out, float eps, const skv_comm *in, int in_slot,
-                           const skv_comm *out, int out_slot, void *stream) {
-    return gemv_launch(W, N, K, y, B, mode, x, h_in, nullptr, norm_w, h_out, eps, in, in_slot, out, out_slot, stream);
+                           const void *norm_w, void *h_out, float eps, const skv_comm *in, int in_seq,
+                           const skv_comm *out, int out_seq, void *stream) {
+    return gemv_launch(W, N, K, y, B, mode, x, h_in, nullptr, norm_w, h_out, eps, in, in_seq, out, out_seq, stream);
 }
 
 extern "C" int64_t skv_comm_bytes(int world, int cap_elems) {
-    if (world < 1 || world > 8 || cap_elems < 8 || cap_elems % 4) return SKV_E_RANGE;
-    return comm_data_bytes(world, cap_elems) + 256;       // flags (<= 64 B), uses, nctas, status
+    if (world < 1 || world > 8 || cap_elems < 8 || cap_elems % 8) return SKV_E_RANGE;
+    return comm_data_bytes(world, cap_elems) + 256;       // tick, status
 }
 
 extern "C" int skv_comm_view(skv_comm *c, void *const *bases, int world, int rank, int cap_elems) {
     if (!c || !bases) return SKV_E_NULL;
-    if (world < 1 || world > 8 || rank < 0 || rank >= world || cap_elems < 8 || cap_elems % 4) return SKV_E_RANGE;
+    if (world < 1 || world > 8 || rank < 0 || rank >= world || cap_elems < 8 || cap_elems % 8) return SKV_E_RANGE;
     const int64_t db = comm_data_bytes(world, cap_elems);
     *c = skv_comm{};
     c->world = world; c->rank = rank; c->cap_elems = cap_elems;
     for (int r = 0; r < world; ++r) {
         if (!bases[r]) return SKV_E_NULL;
-        char *b = static_cast<char *>(bases[r]);
-        c->data[r] = reinterpret_cast<float *>(b);
-        c->flags[r] = reinterpret_cast<uint32_t *>(b + db);
+        c->data[r] = bases[r];
     }
     char *own = static_cast<char *>(bases[rank]) + db;
-    c->uses = reinterpret_cast<uint32_t *>(own + 64);
-    c->nctas = reinterpret_cast<uint32_t *>(own + 72);
-    c->status = reinterpret_cast<int32_t *>(own + 80);
+    c->tick = reinterpret_cast<uint32_t *>(own);
+    c->status = reinterpret_cast<int32_t *>(own + 64);
     return SKV_OK;
 }
 
@@ -501,15 +520,24 @@ extern "C" int skv_comm_free(void *ptr) {
     return SKV_OK;
 }
 
-extern "C" int skv_comm_reduce(const skv_comm *c, int slot, void *delta, int B, int N, void *stream) {
+extern "C" int skv_comm_tick(const skv_comm *c, void *stream) {
+    if (!c || !c->tick) return SKV_E_NULL;
+    comm_tick_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(c->tick);
+    SKV_CUDA_OK(cudaGetLastError());
+    return SKV_OK;
+}
+
+extern "C" int skv_comm_reduce(const skv_comm *c, int seq, void *delta, int B, int N, void *stream) {
     if (!c || !delta) return SKV_E_NULL;
-    if (c->world < 1 || c->world > 8 || slot < 0 || slot > 1 || B < 1 || N < 1 || (int64_t)B * N > c->cap_elems)
-        return SKV_E_RANGE;
-    const int total = B * N;
-    SKV_CUDA_OK(launch_pdl(comm_reduce_kernel, dim3((total + 255) / 256 > 8 ? 8 : (total + 255) / 256), dim3(256), 0,
-                           static_cast<cudaStream_t>(stream), (const float *)c->data[c->rank],
-                           (const uint32_t *)c->flags[c->rank], (const uint32_t *)c->uses, (const uint32_t *)c->nctas,
-                           c->world, slot, c->cap_elems, c->status, static_cast<__nv_bfloat16 *>(delta), total));
+    const int rc = check_comm(c);
+    if (rc) return rc;
+    if (seq < 0 || seq > 254 || B < 1 || N < 8 || N % 8 || (int64_t)B * N > c->cap_elems) return SKV_E_RANGE;
+    if (!aligned16(delta)) return SKV_E_ALIGN;
+    const int total = B * N, blocks = (total / 8 + 255) / 256;
+    SKV_CUDA_OK(launch_pdl(comm_reduce_kernel, dim3(blocks > 8 ? 8 : blocks), dim3(256), 0,
+                           static_cast<cudaStream_t>(stream), static_cast<const uint2 *>(c->data[c->rank]),
+                           (const uint32_t *)c->tick, c->world, seq, c->cap_elems, c->status,
+                           static_cast<__nv_bfloat16 *>(delta), total));
     return SKV_OK;
 }
 

@@ -263,16 +263,17 @@ class GraphDecoder:
         gu = torch.empty(B, ngu, dtype=dt, device=dev)
         xn = torch.empty_like(h)
         peer = self._exchange()
-        SLOT_O, SLOT_DOWN = 0, 1
+        if peer is not None:
+            peer.tick(st)                                  # stamps this step's exchanges
 
         def ptr_of(t):
             return None if t is None else t.data_ptr()
 
         def product(W, y, mode, x=None, h_in=None, dl=None, g=None, h_out=None, tp=None, slot_out=None):
             """One projection.  ``dl`` is the delta to add to the residual (mode 1): a tensor, or the number of
-            the exchange slot that holds its partial sums.  ``slot_out``: deliver the result as partial sums into
-            that slot instead of ``y`` (returns the slot), else all-reduce ``y`` over ``tp`` when given.
-            Returns (residual buffer now current, result: tensor or slot)."""
+            the exchange that holds its partial sums.  ``slot_out``: deliver the result as partial sums under
+            that exchange number instead of ``y`` (returns the number), else all-reduce ``y`` over ``tp`` when
+            given.  Returns (residual buffer now current, result: tensor or exchange number)."""
             N, K = W.shape
             from_slot = isinstance(dl, int)
             own = bool(L.skv_gemv_supported(N, K, B, 3 if from_slot else mode))
@@ -326,13 +327,13 @@ class GraphDecoder:
                 out = self.attn[i].step(qh, self._heads(kc), self._heads(vc), self.n_dev,
                                         insert=self.insert_all is None)
             _, o_red = product(a.o.weight, o, 0, x=out, tp=a.tp,
-                               slot_out=SLOT_O if peer_ok(a.o.weight, 0) else None)
+                               slot_out=2 * i if peer_ok(a.o.weight, 0) else None)
             res, _ = product(self._wgu[i], gu, 1, h_in=h, dl=o_red, g=layer.norm2.weight, h_out=h2)
             h = res if res is not None else h
             h2 = buf_b if h is buf_a else buf_a
             dn = torch.empty(B, hidden, dtype=dt, device=dev)
             _, delta = product(f.down.weight, dn, 2, x=gu, tp=f.tp,
-                               slot_out=SLOT_DOWN if peer_ok(f.down.weight, 2) else None)
+                               slot_out=2 * i + 1 if peer_ok(f.down.weight, 2) else None)
         if isinstance(delta, int):
             red = torch.empty(B, hidden, dtype=dt, device=dev)
             check(L.skv_comm_reduce(peer.ref(), delta, red.data_ptr(), B, hidden, st), "skv_comm_reduce")

@@ -2,8 +2,8 @@
 
 Every rank allocates one buffer with ``cudaMalloc``, hands its 64-byte IPC handle to the other ranks over
 ``torch.distributed`` and maps theirs; the row-parallel products of a decode step (``skv_gemv_tp``) then store
-their partial sums straight into every GPU's buffer over NVLink, and the next product adds them up, in place of
-an all-reduce launch.  ``PeerExchange.emulated`` builds the same views for several "ranks" on one device inside one
+their partial sums - each value paired with an epoch in one 8-byte store - straight into every GPU's buffer over
+NVLink, and the next product polls for the epoch and adds them up, in place of an all-reduce launch.  ``PeerExchange.emulated`` builds the same views for several "ranks" on one device inside one
 process: kernels of different ranks then run one after the other on a stream, which is how the single-GPU tests
 drive the protocol (no kernel ever waits for one that has not been launched).
 """
@@ -22,7 +22,7 @@ class PeerExchange:
     def __init__(self, group, cap_elems: int, device: torch.device):
         L = lib()
         self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
-        self.cap_elems = -(-int(cap_elems) // 4) * 4
+        self.cap_elems = -(-int(cap_elems) // 8) * 8
         self.device = device
         torch.cuda.set_device(device)
         nbytes = L.skv_comm_bytes(self.world, self.cap_elems)
@@ -51,7 +51,7 @@ class PeerExchange:
     def emulated(cls, world: int, cap_elems: int, device: torch.device) -> list["PeerExchange"]:
         """``world`` views over buffers that all live on ``device`` (one process, for tests)."""
         L = lib()
-        cap = -(-int(cap_elems) // 4) * 4
+        cap = -(-int(cap_elems) // 8) * 8
         nbytes = L.skv_comm_bytes(world, cap)
         torch.cuda.set_device(device)
         bases = (ctypes.c_void_p * world)()
@@ -71,6 +71,10 @@ class PeerExchange:
 
     def ref(self):
         return ctypes.byref(self.view)
+
+    def tick(self, stream: int | None) -> None:
+        """Advance the step counter that stamps this step's exchanges (once per decode step, on every rank)."""
+        check(lib().skv_comm_tick(ctypes.byref(self.view), stream), "skv_comm_tick")
 
     def status(self) -> int:
         """The buffer's status word (``ST_WAIT_TIMEOUT`` when a wait for another GPU gave up); synchronises."""

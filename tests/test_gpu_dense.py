@@ -134,8 +134,10 @@ def test_row_parallel_product_summed_through_exchange_buffers(B):
     gw = (1 + 0.1 * torch.randn(N, generator=g)).to(torch.bfloat16).to(DEV)
     Ks = K // world
     Wr = [W[:, r * Ks:(r + 1) * Ks].contiguous() for r in range(world)]
-    for use in range(3):                                  # the counters only ever grow: several uses of a slot
-        slot = use % 2
+    for use in range(3):                                  # several steps, both slots
+        slot = use
+        for e in ex:
+            e.tick(stream())
         x = torch.randn(B, K, generator=g).to(torch.bfloat16).to(DEV)
         h = torch.randn(B, N, generator=g).to(torch.bfloat16).to(DEV)
         for r in range(world):
@@ -169,13 +171,15 @@ def test_row_parallel_product_summed_through_exchange_buffers(B):
 
 
 def test_wait_for_a_rank_that_never_delivers_gives_up_and_reports():
-    """A bounded wait: rank 0 has produced, rank 1 never does; rank 0's consumer polls for about a second, sets
-    the time-out bit in its status word and finishes (nothing hangs, the context stays usable)."""
+    """A bounded wait: rank 0 has produced, rank 1 never does; rank 0's consumer polls rank 1's values for about
+    a second, sets the time-out bit in its status word and finishes (nothing hangs, the context stays usable)."""
     from sparse_kv_reads_b200._lib import ST_WAIT_TIMEOUT
     from sparse_kv_reads_b200.peer_reduce import PeerExchange
     L = lib()
     B, N, K = 1, 256, 512
     ex = PeerExchange.emulated(2, B * N, DEV)
+    for e in ex:
+        e.tick(stream())
     W = torch.randn(N, K, device=DEV).to(torch.bfloat16)
     x = torch.randn(B, K, device=DEV).to(torch.bfloat16)
     check(L.skv_gemv_tp(W.data_ptr(), N, K, None, B, 0, x.data_ptr(), None, None, None, 0.0, None, 0, ex[0].ref(), 0,
