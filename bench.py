@@ -59,6 +59,8 @@ class ClockSampler:
         self.index, self.rows, self.proc = index, [], None
 
     def __enter__(self):
+        if self.index is None or self.proc is not None:
+            return self
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}",
                                           "--format=csv,noheader,nounits", "-lms", "100"], stdout=subprocess.PIPE,
@@ -72,6 +74,12 @@ class ClockSampler:
     def _read(self):
         for line in self.proc.stdout:
             self.rows.append([c.strip() for c in line.split(",")])
+
+    def wait_first(self, seconds: float) -> None:
+        """Give the sampler up to ``seconds`` to deliver its first row."""
+        t0 = time.time()
+        while self.proc is not None and not self.rows and time.time() - t0 < seconds:
+            time.sleep(0.02)
 
     def __exit__(self, *exc):
         if self.proc is not None:
@@ -284,12 +292,18 @@ def gpu_arm(args, wl) -> None:
         torch.cuda.synchronize()
 
     # ---- device-resident leg: token ids already in HBM ------------------------------------------
+    # the clock sampler starts ahead of the warm-up steps (nvidia-smi needs a moment, longer on a box with many
+    # GPUs) and keeps sampling through the timed steps; the warm-up runs the same kernels, so every row is
+    # taken under the same load
+    clocks = ClockSampler(local if rank == 0 else None)
+    clocks.__enter__()
     for _ in range(W):
         dec.step(ids_dev[:, pos:pos + 1], pos)
         pos += 1
     barrier()
+    clocks.wait_first(3.0)
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    with ClockSampler(local) as clocks:
+    with clocks:
         if args.ncu_range:
             torch.cuda.profiler.start()
         start.record()

@@ -312,24 +312,32 @@ __global__ void __launch_bounds__(GEMV_THREADS) gemv_kernel(const GemvParams p) 
     }
 }
 
-// delta[B, N] = sum over ranks of an exchange's partials (for consumers that are not a product of this file)
+// delta[B, N] = sum over ranks of an exchange's partials, for consumers that are not a product of this file and
+// for groups whose partials are too many for every CTA of the consuming product to add up for itself.  Eight
+// lanes share a run of eight elements, one rank each, so that all ranks are polled at once; their values meet
+// in a fixed tree of shuffles (the same on every GPU, so all GPUs obtain the same bits).
 __global__ void __launch_bounds__(256) comm_reduce_kernel(const uint2 *data, const uint32_t *tick, int world, int seq,
                                                           int cap, int32_t *status, __nv_bfloat16 *delta, int total) {
     pdl_wait();
     pdl_trigger();
     const uint32_t epoch = epoch_of(tick, seq);
-    for (int v = blockIdx.x * 256 + threadIdx.x; v < total / 8; v += gridDim.x * 256) {
+    const int r = threadIdx.x & 7;
+    const int vecs = total / 8;
+    for (int v0 = (blockIdx.x * 256 + threadIdx.x) >> 3; v0 < ((vecs + 31) & ~31); v0 += (gridDim.x * 256) >> 3) {
         float d[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-        for (int r = 0; r < world; ++r) {
-            float part[8];
-            load_pairs8(data + (size_t)((seq & 1) * world + r) * cap + (size_t)v * 8, epoch, status, part);
+        const bool live = v0 < vecs;
+        if (live && r < world)
+            load_pairs8(data + (size_t)((seq & 1) * world + r) * cap + (size_t)v0 * 8, epoch, status, d);
 #pragma unroll
-            for (int i = 0; i < 8; ++i) d[i] += part[i];
+        for (int o = 1; o < 8; o <<= 1)
+#pragma unroll
+            for (int i = 0; i < 8; ++i) d[i] += __shfl_xor_sync(0xffffffffu, d[i], o);
+        if (live && r == 0) {
+            __align__(16) __nv_bfloat16 o[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) o[i] = __float2bfloat16(d[i]);
+            *reinterpret_cast<uint4 *>(delta + (size_t)v0 * 8) = *reinterpret_cast<const uint4 *>(o);
         }
-        __align__(16) __nv_bfloat16 o[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) o[i] = __float2bfloat16(d[i]);
-        *reinterpret_cast<uint4 *>(delta + (size_t)v * 8) = *reinterpret_cast<const uint4 *>(o);
     }
 }
 
@@ -533,8 +541,8 @@ extern "C" int skv_comm_reduce(const skv_comm *c, int seq, void *delta, int B, i
     if (rc) return rc;
     if (seq < 0 || seq > 254 || B < 1 || N < 8 || N % 8 || (int64_t)B * N > c->cap_elems) return SKV_E_RANGE;
     if (!aligned16(delta)) return SKV_E_ALIGN;
-    const int total = B * N, blocks = (total / 8 + 255) / 256;
-    SKV_CUDA_OK(launch_pdl(comm_reduce_kernel, dim3(blocks > 8 ? 8 : blocks), dim3(256), 0,
+    const int total = B * N, blocks = (total + 255) / 256;          // eight lanes per run of eight elements
+    SKV_CUDA_OK(launch_pdl(comm_reduce_kernel, dim3(blocks > 64 ? 64 : blocks), dim3(256), 0,
                            static_cast<cudaStream_t>(stream), static_cast<const uint2 *>(c->data[c->rank]),
                            (const uint32_t *)c->tick, c->world, seq, c->cap_elems, c->status,
                            static_cast<__nv_bfloat16 *>(delta), total));

@@ -277,7 +277,8 @@ class GraphDecoder:
             N, K = W.shape
             from_slot = isinstance(dl, int)
             own = bool(L.skv_gemv_supported(N, K, B, 3 if from_slot else mode))
-            if from_slot and not own:                      # the sum as a tensor, for the separate kernels below
+            # every CTA of the product adds the ranks' partials up for itself only while that is a few KB
+            if from_slot and (not own or peer.world * B * K * 8 > 65536):
                 red = torch.empty(B, K, dtype=dt, device=dev)
                 check(L.skv_comm_reduce(peer.ref(), dl, red.data_ptr(), B, K, st), "skv_comm_reduce")
                 dl, from_slot = red, False
