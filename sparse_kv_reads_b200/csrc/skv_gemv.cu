@@ -32,6 +32,7 @@ struct GemvParams {
     const __nv_bfloat16 *W;
     __nv_bfloat16 *y;
     int N, K, B, mode, rows_per_cta;
+    int nslabs, stages;            // slabs of rows_per_cta rows over the matrix; 1 or 2 slab buffers per CTA
     const __nv_bfloat16 *x;        // mode 0: [B, K]; mode 2: gate_up [B, 2K]
     const __nv_bfloat16 *h_in, *delta, *g;
     __nv_bfloat16 *h_out;
@@ -99,7 +100,8 @@ __device__ __forceinline__ void emit(const GemvParams &p, int b, int row, float 
         if (r < p.out_world) store_pair(p.out_data[r] + off, v, epoch);
 }
 
-template <int BP, bool TC>
+// MULTI: the CTA walks over several slabs with two buffers (else exactly one slab, and no loop to pay for)
+template <int BP, bool TC, bool MULTI>
 __global__ void __launch_bounds__(GEMV_THREADS) gemv_kernel(const GemvParams p) {
     extern __shared__ __align__(16) unsigned char smem[];
     __shared__ float s_part[8][GEMV_WARPS];
@@ -107,30 +109,34 @@ __global__ void __launch_bounds__(GEMV_THREADS) gemv_kernel(const GemvParams p) 
     const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
     const int K = p.K, kv = K >> 3;                         // 16-byte pieces per row
     const int xld = TC ? K + 8 : K;                         // input row stride: 16 bytes of padding spread the banks
-    const int r0 = blockIdx.x * p.rows_per_cta;
-    const int R = min(p.rows_per_cta, p.N - r0);
-    __nv_bfloat16 *ws = reinterpret_cast<__nv_bfloat16 *>(smem);                      // [rows_per_cta][K]
-    __nv_bfloat16 *xs = ws + (size_t)p.rows_per_cta * K;                              // [BP][xld]
+    __nv_bfloat16 *ws0 = reinterpret_cast<__nv_bfloat16 *>(smem);                     // [stages][rows_per_cta][K]
+    __nv_bfloat16 *xs = ws0 + (size_t)(MULTI ? 2 : 1) * p.rows_per_cta * K;           // [BP][xld]
     __nv_bfloat16 *gs = xs + (size_t)BP * xld;                                        // [K] (mode 1)
+    // A CTA takes slabs blockIdx.x, blockIdx.x + gridDim.x, ...: one when a wave of CTAs covers the matrix, else
+    // several, the next one streaming into the other buffer while this one is multiplied.
+    auto request_slab = [&](int slab, __nv_bfloat16 *ws) {
+        const int r0 = slab * p.rows_per_cta;
+        const int R = min(p.rows_per_cta, p.N - r0);
+        const __nv_bfloat16 *src = p.W + (size_t)r0 * K;
+        const int pieces = R * kv;
+        if (TC) {                                           // pieces swizzled by their row
+            const unsigned inv = (unsigned)((0x100000000ull + kv - 1) / kv);   // c / kv by multiplication: exact for c < 2^16
+            for (int c = tid; c < pieces; c += GEMV_THREADS) {
+                const int r = (int)__umulhi((unsigned)c, inv), col = c - r * kv;
+                cp_async16(ws + (size_t)r * K + ((col ^ (r & 7)) << 3), src + (size_t)c * 8, 16);
+            }
+        } else {
+            for (int c = tid; c < pieces; c += GEMV_THREADS) cp_async16(ws + (size_t)c * 8, src + (size_t)c * 8, 16);
+        }
+    };
 
     // 1. the slab (and the norm weights): requested before anything else, also before the producer ends
     {
         if (p.mode == 1 || p.mode == 3)
             for (int c = tid; c < kv; c += GEMV_THREADS) cp_async16(gs + c * 8, p.g + c * 8, 16);
         cp_async_commit();                                  // group 0: norm weights (empty otherwise)
-        const __nv_bfloat16 *src = p.W + (size_t)r0 * K;
-        if (TC) {                                           // pieces swizzled by their row
-            const unsigned inv = (unsigned)((0x100000000ull + kv - 1) / kv);   // c / kv by multiplication: exact for c < 2^16
-            const int pieces = R * kv;
-            for (int c = tid; c < pieces; c += GEMV_THREADS) {
-                const int r = (int)__umulhi((unsigned)c, inv), col = c - r * kv;
-                cp_async16(ws + (size_t)r * K + ((col ^ (r & 7)) << 3), src + (size_t)c * 8, 16);
-            }
-        } else {
-            const int pieces = R * kv;
-            for (int c = tid; c < pieces; c += GEMV_THREADS) cp_async16(ws + (size_t)c * 8, src + (size_t)c * 8, 16);
-        }
-        cp_async_commit();                                  // group 1: the slab
+        request_slab(blockIdx.x, ws0);
+        cp_async_commit();                                  // group 1: the first slab
     }
     pdl_wait();
     pdl_trigger();
@@ -229,10 +235,20 @@ __global__ void __launch_bounds__(GEMV_THREADS) gemv_kernel(const GemvParams p) 
             }
         }
     }
-    cp_async_wait<0>();
+    // 3. the slabs
+    int it = 0;
+    for (int slab = blockIdx.x; slab < (MULTI ? p.nslabs : (int)blockIdx.x + 1); slab += gridDim.x, ++it) {
+    const __nv_bfloat16 *ws = MULTI ? ws0 + (size_t)(it & 1) * p.rows_per_cta * K : ws0;
+    const int r0 = slab * p.rows_per_cta;
+    const int R = min(p.rows_per_cta, p.N - r0);
+    if (MULTI && slab + (int)gridDim.x < p.nslabs) {
+        request_slab(slab + gridDim.x, ws0 + (size_t)((it + 1) & 1) * p.rows_per_cta * K);
+        cp_async_commit();
+        cp_async_wait<1>();                                 // all but the slab just requested have landed
+    } else {
+        cp_async_wait<0>();
+    }
     __syncthreads();
-
-    // 3. rows of the slab
     if (TC) {
         const int ntiles = (R + 15) >> 4;
         const int ks = ntiles >= GEMV_WARPS ? 1 : GEMV_WARPS / ntiles;      // ranges of K per tile
@@ -310,6 +326,8 @@ __global__ void __launch_bounds__(GEMV_THREADS) gemv_kernel(const GemvParams p) 
             if (lane == 0 && b < p.B) emit(p, b, r0 + r, s, out_epoch);
         }
     }
+    if (MULTI) __syncthreads();                             // this buffer and s_red are free for the slab after next
+    }
 }
 
 // delta[B, N] = sum over ranks of an exchange's partials, for consumers that are not a product of this file and
@@ -344,15 +362,17 @@ __global__ void __launch_bounds__(256) comm_reduce_kernel(const uint2 *data, con
 __global__ void comm_tick_kernel(uint32_t *tick) { tick[0] += 1u; }
 
 struct GemvPlan {
-    int BP, rows;
+    int BP, rows, nslabs, stages, ctas;
     bool tc, worthwhile;
     size_t smem;
 };
 
-// Rows per CTA and shared memory.  Two CTAs share an SM so that one computes while the other loads; the slab
-// takes what the inputs leave, at most 96 KB, and one wave of CTAs covers the matrix where that is enough.
-// `worthwhile` is false when the inputs every CTA rebuilds outweigh the slab it multiplies them with (many
-// sequences of a long row): a library GEMM serves those shapes better.
+// Rows per slab, slabs per CTA and shared memory.  Where one CTA per SM covers the matrix with slabs of at most
+// 96 KB, every CTA takes one slab (all of it requested at once).  Larger matrices run two CTAs per SM that
+// each walk over several smaller slabs with two buffers, the next slab streaming in while this one is
+// multiplied; the inputs are then built once per CTA, not once per slab.  `worthwhile` is false when the inputs
+// every CTA rebuilds outweigh what it multiplies them with (many sequences of a long row, one slab per CTA):
+// a library GEMM serves those shapes better.
 static int plan_gemv(int N, int K, int B, int mode, GemvPlan &pl) {
     if (B < 1 || B > 8 || N < 1 || K < 8 || K % 8 || mode < 0 || mode > 3) return SKV_E_RANGE;
     pl.BP = B <= 1 ? 1 : (B <= 2 ? 2 : (B <= 4 ? 4 : 8));
@@ -361,27 +381,45 @@ static int plan_gemv(int N, int K, int B, int mode, GemvPlan &pl) {
     const size_t fixed = (size_t)pl.BP * (row + (pl.tc ? 16 : 0)) + (mode == 1 || mode == 3 ? row : 0);   // inputs (+ norm weights)
     const size_t optin = (size_t)device_max_smem_optin();
     const size_t per_cta = optin / 2 - 2048;
+    const int sms = device_sm_count();
     size_t slab = per_cta > fixed ? per_cta - fixed : 0;
     if (slab > (size_t)GEMV_SLAB_MAX) slab = GEMV_SLAB_MAX;
-    pl.worthwhile = slab >= 2 * fixed && slab >= row;
-    if (slab < row) slab = optin > fixed + row + 1024 ? row : 0;          // one row, one CTA per SM
-    if (!slab) return SKV_E_TOO_LARGE;
-    // One CTA per SM where the matrix fits one such wave; else whole rounds of two CTAs per SM, so that no
-    // round is left nearly empty.
-    const int sms = device_sm_count();
-    const int fit = (int)(slab / row);
     int rows = (N + sms - 1) / sms;
-    if (rows > fit) {
-        const int64_t round = 2LL * sms * fit;
-        const int k = (int)((N + round - 1) / round);
-        rows = (N + 2 * sms * k - 1) / (2 * sms * k);
-        // the CTAs of a round load together and compute together, so memory idles while they compute: beyond
-        // two rounds (one with several sequences) a library GEMM streamed faster when measured on B200
-        // (99.6 MB: 18 us against 25 us)
-        if (k > (pl.BP == 1 ? 2 : 1)) pl.worthwhile = false;
+    if (slab >= row && (size_t)rows * row <= slab) {                      // one slab per CTA, one CTA per SM
+        pl.stages = 1;
+        pl.rows = rows;
+        pl.nslabs = (N + rows - 1) / rows;
+        pl.ctas = pl.nslabs;
+        pl.smem = (size_t)rows * row + fixed;
+        pl.worthwhile = slab >= 2 * fixed;
+        return SKV_OK;
     }
-    pl.rows = rows;
-    pl.smem = (size_t)rows * row + fixed;
+    if (pl.BP > 1 && slab >= row && (int64_t)N <= 2LL * sms * (int64_t)(slab / row)) {
+        // several sequences, up to two such waves: still one (large) slab per CTA, two CTAs per SM - the tensor-core
+        // path pays per slab for its barriers and reduction, so few large slabs beat many small ones
+        pl.stages = 1;
+        pl.rows = (N + 2 * sms - 1) / (2 * sms);
+        pl.nslabs = (N + pl.rows - 1) / pl.rows;
+        pl.ctas = pl.nslabs;
+        pl.smem = (size_t)pl.rows * row + fixed;
+        pl.worthwhile = slab >= 2 * fixed;
+        return SKV_OK;
+    }
+    pl.stages = 2;
+    size_t half = per_cta > fixed ? (per_cta - fixed) / 2 : 0;            // two CTAs per SM, two buffers each
+    if (half > 48 * 1024) half = 48 * 1024;
+    if (half < row) {                                                     // long rows: one CTA per SM
+        half = optin > fixed + 2 * row + 2048 ? (optin - fixed - 2048) / 2 : 0;
+        if (half > 48 * 1024) half = 48 * 1024;
+    }
+    if (half < row) return SKV_E_TOO_LARGE;
+    pl.rows = (int)(half / row);
+    pl.nslabs = (N + pl.rows - 1) / pl.rows;
+    pl.ctas = pl.nslabs < 2 * sms ? pl.nslabs : 2 * sms;
+    pl.smem = 2 * (size_t)pl.rows * row + fixed;
+    // several sequences walk the slabs on the tensor-core path, whose per-slab barriers and reduction cost more than
+    // a library GEMM's tiles do (measured on B200: 31.5 MB x 4 sequences 12.4 us against 8.3 us); one sequence wins
+    pl.worthwhile = pl.BP == 1 && (size_t)pl.rows * row * (pl.nslabs / pl.ctas) >= fixed;
     return pl.smem > optin ? SKV_E_TOO_LARGE : SKV_OK;
 }
 
@@ -433,7 +471,7 @@ static int gemv_launch(const void *W, int N, int K, void *y, int B, int mode, co
     const size_t smem = pl.smem;
     GemvParams p = {};
     p.W = static_cast<const __nv_bfloat16 *>(W); p.y = static_cast<__nv_bfloat16 *>(y);
-    p.N = N; p.K = K; p.B = B; p.mode = mode; p.rows_per_cta = rows;
+    p.N = N; p.K = K; p.B = B; p.mode = mode; p.rows_per_cta = rows; p.nslabs = pl.nslabs; p.stages = pl.stages;
     p.x = static_cast<const __nv_bfloat16 *>(x); p.h_in = static_cast<const __nv_bfloat16 *>(h_in);
     p.delta = static_cast<const __nv_bfloat16 *>(delta); p.g = static_cast<const __nv_bfloat16 *>(norm_w);
     p.h_out = static_cast<__nv_bfloat16 *>(h_out); p.eps = eps;
@@ -447,10 +485,13 @@ static int gemv_launch(const void *W, int N, int K, void *y, int B, int mode, co
         p.in_world = in->world; p.in_seq = in_seq; p.in_cap = in->cap_elems; p.status = in->status;
     }
     typedef void (*Kern)(const GemvParams);
-    const int bi = (BP == 1 ? 0 : (BP == 2 ? 1 : (BP == 4 ? 2 : 3))) + (tc ? 4 : 0);
-    const Kern table[8] = {gemv_kernel<1, false>, gemv_kernel<2, false>, gemv_kernel<4, false>, gemv_kernel<8, false>,
-                           gemv_kernel<1, true>,  gemv_kernel<2, true>,  gemv_kernel<4, true>,  gemv_kernel<8, true>};
-    static size_t configured[64][8] = {};
+    const int bi = (BP == 1 ? 0 : (BP == 2 ? 1 : (BP == 4 ? 2 : 3))) + (tc ? 4 : 0) + (pl.stages > 1 ? 8 : 0);
+    const Kern table[16] = {
+        gemv_kernel<1, false, false>, gemv_kernel<2, false, false>, gemv_kernel<4, false, false>, gemv_kernel<8, false, false>,
+        gemv_kernel<1, true, false>,  gemv_kernel<2, true, false>,  gemv_kernel<4, true, false>,  gemv_kernel<8, true, false>,
+        gemv_kernel<1, false, true>,  gemv_kernel<2, false, true>,  gemv_kernel<4, false, true>,  gemv_kernel<8, false, true>,
+        gemv_kernel<1, true, true>,   gemv_kernel<2, true, true>,   gemv_kernel<4, true, true>,   gemv_kernel<8, true, true>};
+    static size_t configured[64][16] = {};
     int dev = 0;
     SKV_CUDA_OK(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64) return SKV_E_RANGE;
@@ -458,8 +499,7 @@ static int gemv_launch(const void *W, int N, int K, void *y, int B, int mode, co
         SKV_CUDA_OK(cudaFuncSetAttribute(table[bi], cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         configured[dev][bi] = smem;
     }
-    const int ctas = (N + rows - 1) / rows;
-    SKV_CUDA_OK(launch_pdl(table[bi], dim3(ctas), dim3(GEMV_THREADS), smem, static_cast<cudaStream_t>(stream), p));
+    SKV_CUDA_OK(launch_pdl(table[bi], dim3(pl.ctas), dim3(GEMV_THREADS), smem, static_cast<cudaStream_t>(stream), p));
     return SKV_OK;
 }
 

@@ -164,3 +164,35 @@ def test_state_dict_round_trip_on_the_cpu():
         SphereIndexGraph(C=32, window=4, capacity=64).load_state_dict(sd, dev)
     from sparse_kv_reads_b200.stamp import stamp
     assert {"time", "host_cores", "torch"} <= set(stamp())
+
+
+def test_matrix_vector_product_and_exchange_reject_bad_arguments(L):
+    ok = 0x1000
+    gemv = lambda **o: L.skv_gemv(o.get("W", ok), o.get("N", 64), o.get("K", 128), o.get("y", ok), o.get("B", 1),
+                                  o.get("mode", 0), o.get("x", ok), o.get("h_in", None), None, o.get("g", None), None,
+                                  1e-6, None)
+    assert gemv(W=None) == -1 and gemv(y=None) == -1 and gemv(x=None) == -1
+    assert gemv(mode=1) == -1                              # residual add + norm needs h_in and the norm weights
+    assert gemv(mode=3) == -5 and gemv(mode=7) == -5       # mode 3 only through skv_gemv_tp
+    assert gemv(B=0) == -5 and gemv(B=9) == -5 and gemv(K=12) == -5 and gemv(N=0) == -5
+    assert gemv(W=0x1008) == -4 and gemv(x=0x1004) == -4
+    assert L.skv_gemv_supported(64, 12, 1, 0) == 0 and L.skv_gemv_supported(64, 128, 9, 0) == 0
+    # exchange buffers: sizes and the regions of a view
+    assert L.skv_comm_bytes(0, 1024) == -5 and L.skv_comm_bytes(9, 1024) == -5 and L.skv_comm_bytes(2, 12) == -5
+    assert L.skv_comm_bytes(2, 1024) == 2 * 2 * 1024 * 8 + 256
+    bases = (ctypes.c_void_p * 2)(0x10000, 0x90000)
+    c = _lib.SkvComm()
+    assert L.skv_comm_view(ctypes.byref(c), bases, 2, 1, 1024) == 0
+    assert (c.world, c.rank, c.cap_elems) == (2, 1, 1024)
+    assert c.data[0] == 0x10000 and c.data[1] == 0x90000
+    assert c.tick == 0x90000 + 2 * 2 * 1024 * 8 and c.status == c.tick + 64
+    assert L.skv_comm_view(ctypes.byref(c), bases, 2, 2, 1024) == -5
+    assert L.skv_comm_view(None, bases, 2, 0, 1024) == -1
+    tp = lambda **o: L.skv_gemv_tp(ok, 64, 128, o.get("y", None), 1, o.get("mode", 0), ok, ok, ok, None, 1e-6,
+                                   o.get("cin", None), o.get("in_seq", 0), o.get("cout", None), o.get("out_seq", 0), None)
+    assert tp() == -1                                      # neither y nor an exchange to deliver to
+    assert tp(mode=3, y=ok) == -5 and tp(cin=ctypes.byref(c), y=ok) == -5     # mode 3 <=> an exchange to read from
+    assert tp(cout=ctypes.byref(c), out_seq=255) == -5 and tp(mode=3, cin=ctypes.byref(c), in_seq=-1, y=ok) == -5
+    assert L.skv_comm_reduce(None, 0, ok, 1, 128, None) == -1
+    assert L.skv_comm_reduce(ctypes.byref(c), 0, ok, 1, 12, None) == -5
+    assert L.skv_comm_tick(None, None) == -1
