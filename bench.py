@@ -300,8 +300,8 @@ def gpu_arm(args, wl) -> None:
     for _ in range(W):
         dec.step(ids_dev[:, pos:pos + 1], pos)
         pos += 1
+    clocks.wait_first(3.0)                               # rank 0 only; the barrier below lines the ranks up again
     barrier()
-    clocks.wait_first(3.0)
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with clocks:
         if args.ncu_range:
@@ -339,6 +339,8 @@ def gpu_arm(args, wl) -> None:
     status = 0
     for ix in dec.attn:
         status |= ix.check_status()
+    if getattr(dec, "_peer", None) is not None:          # a wait for another GPU's partial sums that gave up
+        status |= dec._peer.status()
     if rank == 0:
         peak, which = peaks()
         roof, layer = kernel_roofline(dec, pos, peak, which, NCU_TRAFFIC.get(args.workload) if world == 1 else None)

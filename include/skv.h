@@ -291,15 +291,15 @@ int skv_gemv(const void *W, int N, int K, void *y, int B, int mode, const void *
  * The producing product (skv_gemv_tp with `out` set) stores each of its float32 sums, paired with the epoch
  * tick x 256 + seq + 1, into slot seq % 2 / row `rank` of EVERY GPU's buffer with one aligned 8-byte store over
  * NVLink: no fence and no flag, a reader that finds the epoch has the value.  The consuming product (mode 3)
- * polls the `world` partials of each input element until they carry the epoch - a bounded wait of about a
- * second, after which it sets SKV_ST_WAIT_TIMEOUT in *status and carries on - and adds them in rank order, so
+ * polls the `world` partials of each input element until they carry the epoch - a bounded wait (wait_kpolls, about
+ * five seconds by default), after which it sets SKV_ST_WAIT_TIMEOUT in *status and carries on - and adds them in rank order, so
  * every GPU obtains the same bits.  `seq` numbers the exchanges of a step (0..254), the same on every GPU; two
  * slots are enough for a decoder layer (`o`, `down` alternate): a slot's next producer cannot start anywhere
  * before every GPU has consumed the other slot, which each does after its use of this one. */
 typedef struct skv_comm {
     int32_t world, rank;
     int32_t cap_elems;        /* pairs per (slot, source rank); a multiple of 8 */
-    int32_t reserved;
+    int32_t wait_kpolls;      /* polls (x 1024, a little under a microsecond each) before a wait gives up; 0 = 8192 */
     void     *data[8];        /* every rank's buffer, as mapped in this process */
     uint32_t *tick;           /* local */
     int32_t  *status;         /* local, one word */

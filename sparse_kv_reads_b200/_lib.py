@@ -30,7 +30,7 @@ class SkvError(RuntimeError):
 
 class SkvComm(C.Structure):
     """``skv_comm`` of include/skv.h: one rank's view of the exchange buffers of a tensor-parallel group."""
-    _fields_ = [("world", C.c_int32), ("rank", C.c_int32), ("cap_elems", C.c_int32), ("reserved", C.c_int32),
+    _fields_ = [("world", C.c_int32), ("rank", C.c_int32), ("cap_elems", C.c_int32), ("wait_kpolls", C.c_int32),
                 ("data", C.c_void_p * 8), ("tick", C.c_void_p), ("status", C.c_void_p)]
 
 

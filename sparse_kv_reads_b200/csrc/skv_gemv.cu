@@ -43,13 +43,13 @@ struct GemvParams {
     int out_world, out_rank, out_seq, out_cap;
     const uint2 *in_data;          // the local buffer
     const uint32_t *in_tick;
-    int in_world, in_seq, in_cap;
+    int in_world, in_seq, in_cap, wait_limit;
     int32_t *status;
 };
 
 __device__ __forceinline__ float bf16r(float x) { return __bfloat162float(__float2bfloat16(x)); }
 
-constexpr int WAIT_LIMIT = 1 << 20;     // polls of about a microsecond each: gives up after about a second
+constexpr int WAIT_KPOLLS_DEFAULT = 8192;   // x 1024 polls of a little under a microsecond each: about five seconds
 
 // Every exchanged value travels as one aligned 8-byte store {float bits, epoch}: the epoch names the decode step
 // (the buffer's tick) and the exchange within it, so a reader that finds the epoch it expects has the value too -
@@ -62,7 +62,8 @@ __device__ __forceinline__ void store_pair(uint2 *dst, float v, uint32_t epoch) 
 
 // Eight consecutive partial sums of one rank (64 bytes = four 16-byte loads of two pairs each), polled until
 // all eight carry `epoch`; bounded: on expiry *status gets SKV_ST_WAIT_TIMEOUT and whatever is there is used.
-__device__ __forceinline__ void load_pairs8(const uint2 *src, uint32_t epoch, int32_t *status, float (&out)[8]) {
+__device__ __forceinline__ void load_pairs8(const uint2 *src, uint32_t epoch, int32_t *status, int limit,
+                                            float (&out)[8]) {
     uint4 q[4];
     int it = 0;
     for (;;) {
@@ -75,7 +76,7 @@ __device__ __forceinline__ void load_pairs8(const uint2 *src, uint32_t epoch, in
 #pragma unroll
         for (int i = 0; i < 4; ++i) ok = ok && q[i].y == epoch && q[i].w == epoch;
         if (ok) break;
-        if (++it >= WAIT_LIMIT) {
+        if (++it >= limit) {
             if (status) atomicOr(status, SKV_ST_WAIT_TIMEOUT);
             break;
         }
@@ -190,7 +191,7 @@ __global__ void __launch_bounds__(GEMV_THREADS) gemv_kernel(const GemvParams p) 
                         for (int r = 0; r < p.in_world; ++r) {
                             float part[8];
                             load_pairs8(p.in_data + (size_t)((p.in_seq & 1) * p.in_world + r) * p.in_cap + (size_t)b * K + v * 8,
-                                        in_epoch, p.status, part);
+                                        in_epoch, p.status, p.wait_limit, part);
 #pragma unroll
                             for (int i = 0; i < 8; ++i) d[i] += part[i];
                         }
@@ -335,7 +336,8 @@ __global__ void __launch_bounds__(GEMV_THREADS) gemv_kernel(const GemvParams p) 
 // lanes share a run of eight elements, one rank each, so that all ranks are polled at once; their values meet
 // in a fixed tree of shuffles (the same on every GPU, so all GPUs obtain the same bits).
 __global__ void __launch_bounds__(256) comm_reduce_kernel(const uint2 *data, const uint32_t *tick, int world, int seq,
-                                                          int cap, int32_t *status, __nv_bfloat16 *delta, int total) {
+                                                          int cap, int32_t *status, int limit, __nv_bfloat16 *delta,
+                                                          int total) {
     pdl_wait();
     pdl_trigger();
     const uint32_t epoch = epoch_of(tick, seq);
@@ -345,7 +347,7 @@ __global__ void __launch_bounds__(256) comm_reduce_kernel(const uint2 *data, con
         float d[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
         const bool live = v0 < vecs;
         if (live && r < world)
-            load_pairs8(data + (size_t)((seq & 1) * world + r) * cap + (size_t)v0 * 8, epoch, status, d);
+            load_pairs8(data + (size_t)((seq & 1) * world + r) * cap + (size_t)v0 * 8, epoch, status, limit, d);
 #pragma unroll
         for (int o = 1; o < 8; o <<= 1)
 #pragma unroll
@@ -436,6 +438,11 @@ extern "C" int skv_gemv_supported(int N, int K, int B, int mode) {
 // status word of the owning rank
 static int64_t comm_data_bytes(int world, int cap) { return ((int64_t)2 * world * cap * 8 + 255) / 256 * 256; }
 
+static int wait_polls(const skv_comm *c) {
+    const int64_t k = c->wait_kpolls > 0 ? c->wait_kpolls : WAIT_KPOLLS_DEFAULT;
+    return (int)(k * 1024 > 0x7fffffff ? 0x7fffffff : k * 1024);
+}
+
 static int check_comm(const skv_comm *c) {
     if (c->world < 1 || c->world > 8 || c->rank < 0 || c->rank >= c->world || c->cap_elems < 8 || c->cap_elems % 8)
         return SKV_E_RANGE;
@@ -483,6 +490,7 @@ static int gemv_launch(const void *W, int N, int K, void *y, int B, int mode, co
     if (in) {
         p.in_data = static_cast<const uint2 *>(in->data[in->rank]); p.in_tick = in->tick;
         p.in_world = in->world; p.in_seq = in_seq; p.in_cap = in->cap_elems; p.status = in->status;
+        p.wait_limit = wait_polls(in);
     }
     typedef void (*Kern)(const GemvParams);
     const int bi = (BP == 1 ? 0 : (BP == 2 ? 1 : (BP == 4 ? 2 : 3))) + (tc ? 4 : 0) + (pl.stages > 1 ? 8 : 0);
@@ -584,7 +592,7 @@ extern "C" int skv_comm_reduce(const skv_comm *c, int seq, void *delta, int B, i
     const int total = B * N, blocks = (total + 255) / 256;          // eight lanes per run of eight elements
     SKV_CUDA_OK(launch_pdl(comm_reduce_kernel, dim3(blocks > 64 ? 64 : blocks), dim3(256), 0,
                            static_cast<cudaStream_t>(stream), static_cast<const uint2 *>(c->data[c->rank]),
-                           (const uint32_t *)c->tick, c->world, seq, c->cap_elems, c->status,
+                           (const uint32_t *)c->tick, c->world, seq, c->cap_elems, c->status, wait_polls(c),
                            static_cast<__nv_bfloat16 *>(delta), total));
     return SKV_OK;
 }

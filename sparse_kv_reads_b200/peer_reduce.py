@@ -19,7 +19,7 @@ from ._lib import SkvComm, check, lib
 
 
 class PeerExchange:
-    def __init__(self, group, cap_elems: int, device: torch.device):
+    def __init__(self, group, cap_elems: int, device: torch.device, wait_kpolls: int = 0):
         L = lib()
         self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
         self.cap_elems = -(-int(cap_elems) // 8) * 8
@@ -45,10 +45,11 @@ class PeerExchange:
             bases[r] = peer.value
         self.view = SkvComm()
         check(L.skv_comm_view(ctypes.byref(self.view), bases, self.world, self.rank, self.cap_elems), "skv_comm_view")
+        self.view.wait_kpolls = wait_kpolls                # 0: the library's default, about five seconds
         dist.barrier(group=group)                      # every rank has mapped every buffer before any use
 
     @classmethod
-    def emulated(cls, world: int, cap_elems: int, device: torch.device) -> list["PeerExchange"]:
+    def emulated(cls, world: int, cap_elems: int, device: torch.device, wait_kpolls: int = 0) -> list["PeerExchange"]:
         """``world`` views over buffers that all live on ``device`` (one process, for tests)."""
         L = lib()
         cap = -(-int(cap_elems) // 8) * 8
@@ -66,6 +67,7 @@ class PeerExchange:
             x._own, x._opened = bases[r], []
             x.view = SkvComm()
             check(L.skv_comm_view(ctypes.byref(x.view), bases, world, r, cap), "skv_comm_view")
+            x.view.wait_kpolls = wait_kpolls
             out.append(x)
         return out
 

@@ -171,13 +171,13 @@ def test_row_parallel_product_summed_through_exchange_buffers(B):
 
 
 def test_wait_for_a_rank_that_never_delivers_gives_up_and_reports():
-    """A bounded wait: rank 0 has produced, rank 1 never does; rank 0's consumer polls rank 1's values for about
-    a second, sets the time-out bit in its status word and finishes (nothing hangs, the context stays usable)."""
+    """A bounded wait: rank 0 has produced, rank 1 never does; rank 0's consumer polls rank 1's values for a fraction
+    of a second (the limit is set low here), sets the time-out bit in its status word and finishes (nothing hangs, the context stays usable)."""
     from sparse_kv_reads_b200._lib import ST_WAIT_TIMEOUT
     from sparse_kv_reads_b200.peer_reduce import PeerExchange
     L = lib()
     B, N, K = 1, 256, 512
-    ex = PeerExchange.emulated(2, B * N, DEV)
+    ex = PeerExchange.emulated(2, B * N, DEV, wait_kpolls=512)      # about a third of a second
     for e in ex:
         e.tick(stream())
     W = torch.randn(N, K, device=DEV).to(torch.bfloat16)
