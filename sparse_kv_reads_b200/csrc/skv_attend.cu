@@ -41,6 +41,9 @@ struct AttendParams {
 static unsigned long long *g_attend_probe = nullptr;
 
 __device__ __forceinline__ void stamp(const AttendParams &p, int slot) {
+#ifdef SKV_NO_STAMP
+    return;
+#endif
     if (p.probe && threadIdx.x == 0) {
         unsigned long long t;
         asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
@@ -258,8 +261,10 @@ __global__ void __launch_bounds__(WARPS * 32, 3) attend_labels_kernel(const Atte
         raw[v] = make_uint4(0u, 0u, 0u, 0u);
         if (p0 + tid * LPT + v * 8 < p1) raw[v] = __ldg(reinterpret_cast<const uint4 *>(lab + p0 + tid * LPT + v * 8));
     }
+#ifndef SKV_NO_PDLWAIT_ATTEND
     pdl_wait();                            // selection bits and query come from the kernels before this one
     pdl_trigger();
+#endif
     for (int i = tid; i < p.sel_words; i += WARPS * 32) s_bits[i] = p.selbits[(int64_t)head * p.sel_words + i];
     typename std::conditional<HI, WarpAttend<STAGES, true>, WarpAttendT<STAGES>>::type wa;
     wa.init(static_cast<const __nv_bfloat16 *>(p.q) + (int64_t)head * G * HEAD_DIM, G, smem + warp * (STAGES * 8192),
