@@ -181,7 +181,8 @@ void skv_debug_select_probe(void *dev_ptr);
  * the launch directly ahead of skv_select or skv_attend_labels.  Off by default; SKV_PDL=0 in the environment
  * keeps it off.  Process-wide switch, read at launch time. */
 void skv_set_overlap(int on);
-/* Same for skv_attend_labels: device uint64 [CTAs][8] phase stamps of every CTA (null = off). */
+/* Same for skv_attend_labels: device uint64 [CTAs][8] phase stamps of every CTA (null = off).  Takes effect only
+ * in a library built with -DSKV_ATTEND_PROBE (the stamps cost that kernel 3.5 % at large batch). */
 void skv_debug_attend_probe(void *dev_ptr);
 
 /* skv_attend without a row list: every CTA owns a range of positions, reads their int16 labels, keeps
@@ -234,13 +235,17 @@ int64_t skv_fit_workspace_bytes(int heads, int m, int C, int d);
  *   cap_keys > 0: absolute cap; else cap = split_factor * m / C_init when split_factor > 0; else no cap
  *   capk        growing cap (see skv_insert); var_factor > 0: state.vthr = var_factor x the mean spread of the
  *               fitted clusters (ssa/attn/sphere_gpu.py:214-217), else +inf
+ *   k_layers    optional device table of cache base pointers, one per heads_per_layer consecutive heads of st (K is
+ *               unused then): the states of several layers, stacked, are fitted in one call - one set of launches
+ *               and one host round trip per split round for the whole model instead of one per layer
  *   head_list   optional device int32 [n_list]: fit only these entries of st (a head that reached reset_at,
  *               SphereIndexGPU._reset_heads, sphere_gpu.py:283-293); null = all heads.  Workspace for n_list heads.
  */
 int skv_fit(const skv_state *st, const void *K, int dtype, int64_t k_head_stride, int64_t k_row_stride,
             int n, int window, int C_init, int iters, const int32_t *init_pos, float cap_keys,
             float split_factor, float capk, float var_factor, const int32_t *head_list, int n_list,
-            void *workspace, int64_t workspace_bytes, void *stream);
+            const void *const *k_layers, int heads_per_layer, void *workspace, int64_t workspace_bytes,
+            void *stream);
 
 /* Recentre and rebin selected heads with their centroids kept (new mean = ksum / (end-1)):
  * replaces the recentring branch of SphereIndexGPU._build (ssa/attn/sphere_gpu.py:187-219 with mu given;

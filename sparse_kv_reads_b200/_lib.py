@@ -86,7 +86,7 @@ def _declare(lib) -> None:
     lib.skv_fit_workspace_bytes.argtypes = [i32, i32, i32, i32]
     lib.skv_fit.restype = i32
     lib.skv_fit.argtypes = [C.POINTER(SkvState), vp, i32, i64, i64, i32, i32, i32, i32, vp, f32, f32, f32, f32, vp, i32,
-                            vp, i64, vp]
+                            vp, i32, vp, i64, vp]
     lib.skv_add_rmsnorm.restype = i32
     lib.skv_add_rmsnorm.argtypes = [vp, vp, vp, vp, i32, i32, f32, vp]
     lib.skv_qk_rope_cache.restype = i32

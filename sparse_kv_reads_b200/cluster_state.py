@@ -95,6 +95,53 @@ class ClusterArena:
         return s
 
 
+def fit_layers(layers: list["SphereIndexGraph"], caches: list[torch.Tensor], n: int,
+               max_workspace: int = 6 << 30) -> bool:
+    """Fit the states of several layers that share one arena with ONE ``skv_fit`` call per group of layers
+    (as many layers as fit ``max_workspace`` bytes of scratch): the k-means passes and every round of the
+    after-fit splits run once for the whole group, and the host waits once per round instead of once per
+    round and layer.  Returns False (nothing done) when the layers cannot be batched."""
+    first = layers[0]
+    if len(layers) < 2 or first._arena is None or first.partition != "kmeans":
+        return False
+    k0 = caches[0]
+    if any(k.stride() != k0.stride() or k.dtype != k0.dtype or k.shape != k0.shape for k in caches):
+        return False
+    for ix, K in zip(layers, caches):
+        ix._init(K, n, fit=False)
+    arena, h = first._arena, first.H_kv
+    if any(ix._arena is not arena or ix._layer != i or ix.H_kv != h for i, ix in enumerate(layers)):
+        for ix, K in zip(layers, caches):                   # not one stacked arena: layer by layer
+            ix._build_all(K, n)
+            ix.n = n
+        return True
+    m = first.end - 1
+    if m < 1:
+        return False
+    L = lib()
+    per_layer = L.skv_fit_workspace_bytes(h, m, first.C, first.d)
+    group = max(1, min(len(layers), max_workspace // max(per_layer, 1)))
+    g = torch.Generator(device="cpu").manual_seed(first.seed)
+    init = torch.randperm(m, generator=g)[torch.arange(first.C_init) % m].to(torch.int32).to(k0.device)
+    for lo in range(0, len(layers), group):
+        hi = min(lo + group, len(layers))
+        st = arena.struct(lo * h, hi * h)
+        table = torch.tensor([k.data_ptr() for k in caches[lo:hi]], dtype=torch.int64, device=k0.device)
+        nbytes = L.skv_fit_workspace_bytes((hi - lo) * h, m, first.C, first.d)
+        ws = _workspace(k0.device, nbytes)
+        check(L.skv_fit(ctypes.byref(st), None, dtype_code(k0.dtype), k0.stride(0), k0.stride(1), n, first.window,
+                        first.C_init, first.kmeans_iters, init.data_ptr(), first.cap_keys, first.split_factor,
+                        first.capk, first.var_factor, None, 0, table.data_ptr(), h, ws.data_ptr(), ws.numel(),
+                        stream_ptr(k0.device)), "skv_fit")
+    for ix in layers:
+        ix._fitted = True
+        ix._max_members = None
+        ix._splits_host += int(ix.nsplit.sum())
+        ix.nsplit.zero_()
+        ix.n = n
+    return True
+
+
 class SphereIndexGraph:
     """Cluster state of one layer for ``h`` (sequence, KV head) pairs, with the eager calls
     (``observe``, ``labels_and_weights``, ``attend``) and the graph-safe ones (``prepare``, ``step``,
@@ -199,7 +246,7 @@ class SphereIndexGraph:
             raise ValueError("the cache must be [heads, positions, d] with a unit last stride")
 
     # ---- prompt fit ------------------------------------------------------------------------------
-    def _init(self, K: torch.Tensor, n: int) -> None:
+    def _init(self, K: torch.Tensor, n: int, fit: bool = True) -> None:
         self._check_cache(K)
         if n > self.capacity:
             raise ValueError(f"n={n} exceeds capacity {self.capacity}")
@@ -210,7 +257,8 @@ class SphereIndexGraph:
         self.labels.fill_(self.C)
         self.n_c.zero_()
         self.end_dev.fill_(self.end)
-        self._build_all(K, n)
+        if fit:
+            self._build_all(K, n)
         self.initialized = True
 
     def _build_all(self, K: torch.Tensor, n: int, heads: torch.Tensor | None = None) -> None:
@@ -236,7 +284,7 @@ class SphereIndexGraph:
         check(L.skv_fit(ctypes.byref(self._st), K.data_ptr(), dtype_code(K.dtype), K.stride(0), K.stride(1), n,
                         self.window, self.C_init, self.kmeans_iters, ptr(init), self.cap_keys,
                         self.split_factor, self.capk, self.var_factor,
-                        None if hl is None else hl.data_ptr(), entries, ws.data_ptr(), ws.numel(),
+                        None if hl is None else hl.data_ptr(), entries, None, 0, ws.data_ptr(), ws.numel(),
                         stream_ptr(K.device)), "skv_fit")
         self._fitted = True
         self._max_members = None
@@ -435,10 +483,11 @@ class SphereIndexGraph:
         return self._attend(q, K, V), labels, w
 
     # ---- graph-safe calls --------------------------------------------------------------------------
-    def prepare(self, K: torch.Tensor, n: int, H: int) -> None:
+    def prepare(self, K: torch.Tensor, n: int, H: int, fitted: bool = False) -> None:
         """Build from the prefilled cache holding ``n`` positions (eager) and allocate the step's fixed
-        buffers (ssa/kernels/graph_kernels.py:204-218)."""
-        self.observe(K, n)
+        buffers (ssa/kernels/graph_kernels.py:204-218).  ``fitted``: ``fit_layers`` has built the state."""
+        if not (fitted and self._fitted and self.n == n):
+            self.observe(K, n)
         if not self._fitted:
             raise ValueError(f"n={n} leaves nothing to cluster behind a window of {self.window}")
         G = H // self.H_kv

@@ -23,6 +23,8 @@ struct FitView {
     int m;                    // end - 1
     int64_t ksh, ksr;
     const void *K;
+    const void *const *k_layers;   // optional device table: cache of layer head / hpl (then K is unused)
+    int hpl;                       // heads per layer of that table
     // workspace
     float *Xn;                // [entries, m, 128]
     float *mag;               // [entries, m]
@@ -40,12 +42,19 @@ struct FitView {
 
 __device__ __forceinline__ int head_of(const FitView &v, int e) { return v.list ? v.list[e] : e; }
 
+// First cached row of head h: in the one cache given, or in its layer's cache when a table of layers is given.
+template <typename T>
+__device__ __forceinline__ const T *keys_of(const FitView &v, int h) {
+    if (v.k_layers) return static_cast<const T *>(v.k_layers[h / v.hpl]) + (int64_t)(h % v.hpl) * v.ksh;
+    return static_cast<const T *>(v.K) + (int64_t)h * v.ksh;
+}
+
 // ---- column sums of the clustered keys (two levels, fixed order) -----------------------------------
 template <typename T>
 __global__ void __launch_bounds__(128) colsum_kernel(const FitView v) {
     const int e = blockIdx.y, chunk = blockIdx.x, t = threadIdx.x;
     const int h = head_of(v, e);
-    const T *Kh = static_cast<const T *>(v.K) + (int64_t)h * v.ksh;
+    const T *Kh = keys_of<T>(v, h);
     const int per = (v.m + MEAN_CHUNKS - 1) / MEAN_CHUNKS;
     const int i0 = chunk * per, i1 = min(i0 + per, v.m);
     float s = 0.f;
@@ -71,7 +80,7 @@ __global__ void __launch_bounds__(256) centre_kernel(const FitView v) {
     __shared__ float s_sq[8];
     const int e = blockIdx.y, chunk = blockIdx.x, lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
     const int h = head_of(v, e);
-    const T *Kh = static_cast<const T *>(v.K) + (int64_t)h * v.ksh;
+    const T *Kh = keys_of<T>(v, h);
     const float4 mu = *reinterpret_cast<const float4 *>(v.st.mu_ref + (int64_t)h * HEAD_DIM + lane * 4);
     const int per = (v.m + MEAN_CHUNKS - 1) / MEAN_CHUNKS;
     const int i0 = chunk * per, i1 = min(i0 + per, v.m);
@@ -733,10 +742,12 @@ extern "C" int64_t skv_fit_workspace_bytes(int heads, int m, int C, int d) {
 extern "C" int skv_fit(const skv_state *st, const void *K, int dtype, int64_t k_head_stride, int64_t k_row_stride,
                        int n, int window, int C_init, int iters, const int32_t *init_pos, float cap_keys,
                        float split_factor, float capk, float var_factor, const int32_t *head_list, int n_list,
-                       void *workspace, int64_t workspace_bytes, void *stream) {
+                       const void *const *k_layers, int heads_per_layer, void *workspace, int64_t workspace_bytes,
+                       void *stream) {
     int rc = check_state(st);
     if (rc) return rc;
-    if (!K || !workspace) return SKV_E_NULL;
+    if ((!K && !k_layers) || !workspace) return SKV_E_NULL;
+    if (k_layers && (heads_per_layer < 1 || st->heads % heads_per_layer)) return SKV_E_RANGE;
     if (!init_pos) iters = 0;                            // given centroids are kept: no Lloyd step
     if (dtype != SKV_BF16 && dtype != SKV_F32) return SKV_E_DTYPE;
     if (n < 0 || n > st->capacity || window < 0 || iters < 0 || C_init < 1 || C_init > st->C || cap_keys < 0.f ||
@@ -744,7 +755,7 @@ extern "C" int skv_fit(const skv_state *st, const void *K, int dtype, int64_t k_
         return SKV_E_RANGE;
     if (head_list && (n_list < 1 || n_list > st->heads)) return SKV_E_RANGE;
     const int esz = dtype == SKV_BF16 ? 2 : 4;
-    if (!aligned16(K) || !aligned16(workspace) || (k_row_stride * esz) % 16 || (k_head_stride * esz) % 16 ||
+    if ((K && !aligned16(K)) || !aligned16(workspace) || (k_row_stride * esz) % 16 || (k_head_stride * esz) % 16 ||
         k_row_stride < HEAD_DIM)
         return SKV_E_ALIGN;
     const int end = n - window > 1 ? n - window : 1;
@@ -755,7 +766,7 @@ extern "C" int skv_fit(const skv_state *st, const void *K, int dtype, int64_t k_
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     FitView v;
     v.st = *st; v.list = head_list; v.entries = entries; v.end = end; v.m = m;
-    v.ksh = k_head_stride; v.ksr = k_row_stride; v.K = K;
+    v.ksh = k_head_stride; v.ksr = k_row_stride; v.K = K; v.k_layers = k_layers; v.hpl = heads_per_layer;
     const int64_t used = carve(v, static_cast<char *>(workspace), entries, m, st->C);
     float *projbuf = reinterpret_cast<float *>(static_cast<char *>(workspace) + used);
     rc = dtype == SKV_BF16 ? centre_and_assign<__nv_bfloat16>(v, 0, s) : centre_and_assign<float>(v, 0, s);
@@ -792,7 +803,7 @@ extern "C" int skv_rebin(const skv_state *st, const int32_t *head_list, int n_li
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     FitView v;
     v.st = *st; v.list = head_list; v.entries = n_list; v.end = end; v.m = m;
-    v.ksh = k_head_stride; v.ksr = k_row_stride; v.K = K;
+    v.ksh = k_head_stride; v.ksr = k_row_stride; v.K = K; v.k_layers = nullptr; v.hpl = 1;
     carve(v, static_cast<char *>(workspace), n_list, m, st->C);
     rc = dtype == SKV_BF16 ? centre_and_assign<__nv_bfloat16>(v, 1, s) : centre_and_assign<float>(v, 1, s);
     if (rc) return rc;

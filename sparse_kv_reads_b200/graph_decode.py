@@ -20,7 +20,7 @@ import torch
 import torch.nn.functional as F
 
 from ._lib import check, dtype_code, lib, stream_ptr
-from .cluster_state import ClusterArena, SphereIndexGraph
+from .cluster_state import ClusterArena, SphereIndexGraph, fit_layers
 from .qwen3 import Qwen3Model, apply_rope
 
 
@@ -135,8 +135,13 @@ class GraphDecoder:
         """Build the attention state from the first ``n`` cached positions (after the prompt)."""
         if self.mode != "cluster":
             return
-        for i, idx in enumerate(self.attn):
-            idx.prepare(self._heads(self.cache.k[i]), n, self.B * self.H)
+        caches = [self._heads(self.cache.k[i]) for i in range(len(self.attn))]
+        same = all(getattr(a, k) == getattr(self.attn[0], k) for a in self.attn
+                   for k in ("C", "C_init", "window", "seed", "kmeans_iters", "cap_keys", "split_factor", "capk",
+                             "var_factor", "partition"))
+        fitted = same and fit_layers(self.attn, caches, n)         # one fit for all layers where they share an arena
+        for idx, K in zip(self.attn, caches):
+            idx.prepare(K, n, self.B * self.H, fitted=fitted)
         if self.fused_insert:
             self.insert_all = AllLayerInsert(self.attn, [self._heads(k) for k in self.cache.k[:len(self.attn)]])
 

@@ -103,8 +103,10 @@ def test_state_calls_reject_bad_arguments(L):
     assert L.skv_insert_max_members() >= 400
     fit = lambda s, **o: L.skv_fit(ctypes.byref(s), ok, 0, 128 * 64, 128, o.get("n", 64), o.get("window", 8),
                                    o.get("C_init", 16), 10, ok, 0.0, 0.0, o.get("capk", 0.0), o.get("vf", 0.0),
-                                   o.get("hl", None), o.get("nl", 0), ok, o.get("bytes", 1 << 40), None)
+                                   o.get("hl", None), o.get("nl", 0), o.get("kl", None), o.get("hpl", 0), ok,
+                                   o.get("bytes", 1 << 40), None)
     assert fit(st, n=100) == -5 and fit(st, C_init=128) == -5 and fit(st, n=8, window=8) == -5
+    assert fit(st, kl=ok, hpl=3) == -5 and fit(st, kl=ok, hpl=0) == -5      # heads of st must divide into layers
     assert fit(st, capk=-1.0) == -5 and fit(st, vf=-0.5) == -5 and fit(st, hl=ok, nl=0) == -5 and fit(st, hl=ok, nl=3) == -5
     assert fit(st, bytes=16) == -6
     assert L.skv_fit_workspace_bytes(2, 55, 64, 128) > 2 * 55 * 512

@@ -269,3 +269,30 @@ def test_recentring_follows_the_oracle():
     counts = torch.stack([torch.bincount(lab[i, 1:end].long(), minlength=64) for i in range(h)])
     torch.testing.assert_close(ix.count.cpu(), counts.float())
     torch.testing.assert_close(ix.mu_ref.cpu(), st.mu_ref, rtol=1e-4, atol=1e-4)
+
+
+def test_one_fit_for_all_layers_equals_a_fit_per_layer():
+    """Three layers sharing an arena, fitted by one call over their stacked states (a table of per-layer
+    caches), against the same three layers fitted one by one: identical labels, counts and caps."""
+    from sparse_kv_reads_b200.cluster_state import ClusterArena, fit_layers
+    h, n, layers = 2, 1500, 3
+    caps = -(-(n + 8) // 8) * 8
+    caches = [oc.clustered_keys(h, caps, 128, seed=60 + i)[0].to(torch.bfloat16).to(DEV) for i in range(layers)]
+    kw = dict(C=256, C_init=16, cap_keys=24.0, window=16, delta=math.inf, capacity=caps, summary_bits=8)
+    arena = ClusterArena(layers=layers, h=h, C=256, d=128, capacity=caps, summary_bits=8, device=DEV)
+    together = [SphereIndexGraph(arena=arena, layer=i, **kw) for i in range(layers)]
+    assert fit_layers(together, caches, n)
+    # a workspace limit that forces one layer per group must give the same state
+    arena2 = ClusterArena(layers=layers, h=h, C=256, d=128, capacity=caps, summary_bits=8, device=DEV)
+    grouped = [SphereIndexGraph(arena=arena2, layer=i, **kw) for i in range(layers)]
+    assert fit_layers(grouped, caches, n, max_workspace=1)
+    for i in range(layers):
+        alone = SphereIndexGraph(**kw)
+        alone.observe(caches[i], n)
+        for other in (together[i], grouped[i]):
+            assert other._fitted and other.n == n and other.end == alone.end
+            assert torch.equal(other.labels, alone.labels) and torch.equal(other.n_c, alone.n_c)
+            assert torch.equal(other.count, alone.count) and torch.equal(other.cap, alone.cap)
+            torch.testing.assert_close(other.sum_dir, alone.sum_dir, rtol=0, atol=0)
+            assert torch.equal(other.dir8, alone.dir8) and other.splits == alone.splits
+        assert int(alone.n_c.min()) > 16 and alone.check_status() == 0
