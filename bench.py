@@ -252,6 +252,9 @@ def own_launches(dec) -> int:
     selection and the attention, and with the bundled model's fused layers also QK-norm/rotary/cache write and
     either the four matrix-vector products (norms and activation folded in) or the three element-wise kernels
     around cuBLAS products; one more norm ahead of the vocabulary projection."""
+    counted = getattr(dec, "launches_per_step", 0)      # counted while the step was captured
+    if counted:
+        return counted
     per_layer = 2
     extra = 1
     if dec.fused_dense:

@@ -137,7 +137,17 @@ def lib():
     return _lib
 
 
+# entry points that launch exactly one kernel each: counted, so that a caller can tell how many of the library's
+# kernels a captured decode step holds (GraphDecoder.launches_per_step)
+_ONE_LAUNCH = {"skv_insert", "skv_select", "skv_attend", "skv_attend_labels", "skv_gemv", "skv_gemv_tp",
+               "skv_add_rmsnorm", "skv_qk_rope_cache", "skv_silu_mul", "skv_comm_reduce", "skv_comm_tick"}
+launches = 0
+
+
 def check(code: int, what: str) -> None:
+    global launches
+    if what in _ONE_LAUNCH:
+        launches += 1
     if code != 0:
         L = lib()
         msg = L.skv_error_string(code).decode()

@@ -19,6 +19,7 @@ import torch
 
 import torch.nn.functional as F
 
+from . import _lib
 from ._lib import check, dtype_code, lib, stream_ptr
 from .cluster_state import ClusterArena, SphereIndexGraph, fit_layers
 from .qwen3 import Qwen3Model, apply_rope
@@ -372,8 +373,10 @@ class GraphDecoder:
         if self.mode == "cluster":                     # the warm-up steps must not have advanced the clusters
             torch.cuda.synchronize()
         g = torch.cuda.CUDAGraph()
+        before = _lib.launches
         with torch.no_grad(), torch.cuda.graph(g):
             self.logits = self._body()
+        self.launches_per_step = _lib.launches - before     # this library's kernels in one replay
         self.graph = g
 
     @torch.no_grad()
