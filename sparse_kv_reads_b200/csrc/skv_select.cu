@@ -370,24 +370,55 @@ __global__ void __launch_bounds__(SEL_THREADS) score_pick_kernel(const SelectPar
     }
     stamp(p, h, 2);
     // ---- the head's picking CTA from here on ---------------------------------------------------------
-    for (int c = tid; c < C; c += SEL_THREADS) {
-        ci[c] = c < n_c ? (int)count[c] : 0;
-        sel[c] = 0;
+    // Everything this CTA needs from global memory - the slices' statistics, their exp values, the clusters'
+    // counts - is requested before any of it is used (four loads per thread at a time), so the prologue of
+    // the pick costs about one round trip to L2 instead of one per loop iteration.
+    float2 s0 = make_float2(-INFINITY, 0.f), s1 = s0;
+    const bool stat_warp = scoring && wid < G;               // one warp per query head; G <= 16 > SEL_WARPS loops below
+    if (stat_warp) {
+        if (lane < nb) s0 = __ldcg(reinterpret_cast<const float2 *>(ps + (lane * 16 + wid) * 2));
+        if (lane + 32 < nb) s1 = __ldcg(reinterpret_cast<const float2 *>(ps + ((lane + 32) * 16 + wid) * 2));
     }
-    for (int i = tid; i < 4 * 256; i += SEL_THREADS) hist[i] = 0;
+    if (scoring && nb > 1)
+        for (int g = 0; g < G; ++g)
+            for (int c = tid; c < n_c; c += 4 * SEL_THREADS) {
+                float v[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int cc = c + j * SEL_THREADS;
+                    v[j] = cc < n_c ? __ldcg(zg + g * C + cc) : 0.f;
+                }
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int cc = c + j * SEL_THREADS;
+                    if (cc < n_c) z[g * C + cc] = v[j];
+                }
+            }
+    for (int c = tid; c < C; c += 4 * SEL_THREADS) {
+        float v[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int cc = c + j * SEL_THREADS;
+            v[j] = cc < n_c ? count[cc] : 0.f;
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int cc = c + j * SEL_THREADS;
+            if (cc < C) { ci[cc] = (int)v[j]; sel[cc] = 0; }
+        }
+    }
     if (tid == 0) {
         sel[C] = 1;
         if (!p.idx) p.cnt[h] = 0;                     // the attention kernel adds the rows it reads
     }
     if (scoring) {
         // slice factors exp(max_b - max) / total per query head
-        if (nb > 1)
-            for (int g = 0; g < G; ++g)                // requested first: in flight during the combine below
-                for (int c = tid; c < n_c; c += SEL_THREADS) z[g * C + c] = __ldcg(zg + g * C + c);
-        for (int g = wid; g < G; g += SEL_WARPS) {     // one warp per query head; a lane holds up to two slices
-            float2 s0 = make_float2(-INFINITY, 0.f), s1 = s0;
-            if (lane < nb) s0 = __ldcg(reinterpret_cast<const float2 *>(ps + (lane * 16 + g) * 2));
-            if (lane + 32 < nb) s1 = __ldcg(reinterpret_cast<const float2 *>(ps + ((lane + 32) * 16 + g) * 2));
+        for (int g = wid; g < G; g += SEL_WARPS) {     // a lane holds up to two slices
+            if (g != wid) {                            // more query heads than warps: the later ones load here
+                s0 = s1 = make_float2(-INFINITY, 0.f);
+                if (lane < nb) s0 = __ldcg(reinterpret_cast<const float2 *>(ps + (lane * 16 + g) * 2));
+                if (lane + 32 < nb) s1 = __ldcg(reinterpret_cast<const float2 *>(ps + ((lane + 32) * 16 + g) * 2));
+            }
             const float m = warp_max(fmaxf(s0.x, s1.x));
             if (p.group != SKV_GROUP_SUM_SHARE) {          // only the head's best score is needed (max_rel)
                 if (lane == 0) fb[g] = m;
