@@ -1,10 +1,11 @@
-// Cluster scoring from summaries, shared (per KV head) softmax-sum score, top-budget selection by a
-// weighted radix select, and the ordered list of positions to read - one CTA per KV head, one launch.
+// Cluster scoring from summaries, shared (per KV head) score, top-budget selection by a weighted
+// select over order-preserving keys, and the ordered list of positions to read - one launch.
 //
 // Bytes per head: n_c summaries (128 B int8 or 512 B float32 direction + 12 B) and one int16 label
 // per cached position; everything else lives in shared memory.  The selection never sorts: it finds
-// the threshold key t with  sum(count | key > t) < need  by four 8-bit radix passes over
-// order-preserving integer keys, then settles exact ties in slot order, which reproduces "take
+// the threshold key t with  sum(count | key > t) < need  by binning order-preserving integer keys
+// over the range still in question (256 bins a pass, usually one pass) and ranking the last <= 32
+// candidates in a warp, then settles exact ties in slot order, which reproduces "take
 // clusters in decreasing score, lower slot first among equals, until the counts reach need".
 #include <cuda_fp16.h>
 
@@ -103,7 +104,7 @@ __device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
 // projection of the query on the cluster's mean direction, scaled by 1/sqrt(d); it then leaves
 // exp(z - slice max) in zbuf and its (max, sum) per query head in pstat.  The last CTA of the head to
 // finish (atomic ticket, no waiting) combines the slices' statistics into the shared score
-// sum_g softmax_g(z)[c] without another exponential, finds the threshold key by a weighted radix select
+// sum_g softmax_g(z)[c] without another exponential, finds the threshold key by an adaptive-range weighted select
 // and writes the weights and the selection bits.
 template <typename TQ, int GP>
 __global__ void __launch_bounds__(SEL_THREADS) score_pick_kernel(const SelectParams p) {
