@@ -435,8 +435,10 @@ __global__ void __launch_bounds__(SEL_THREADS) score_pick_kernel(const SelectPar
     stamp(p, h, 3);
     uint32_t kmin = 0xffffffffu, kmax = 0u;        // range of the keys of clusters with members, and their number
     int nvalid = 0;
+    const int kend = p.shared_out ? C : n_c;       // keys of spare slots matter only to a caller who asked for the scores
     if (scoring) {
-        for (int c = tid; c < C; c += SEL_THREADS) {
+#pragma unroll 2
+        for (int c = tid; c < kend; c += SEL_THREADS) {
             float s = -INFINITY;
             if (c < n_c && ci[c] > 0 && p.group != SKV_GROUP_SUM_SHARE) {
                 for (int g = 0; g < G; ++g)
@@ -455,7 +457,7 @@ __global__ void __launch_bounds__(SEL_THREADS) score_pick_kernel(const SelectPar
         }
     } else if (active) {
         const float *sin = p.shared_in + (int64_t)h * C;
-        for (int c = tid; c < C; c += SEL_THREADS) {
+        for (int c = tid; c < kend; c += SEL_THREADS) {
             const float s = c < n_c ? sin[c] : -INFINITY;
             const uint32_t k = float_key(s);
             key[c] = k;
