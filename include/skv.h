@@ -250,9 +250,14 @@ int skv_fit(const skv_state *st, const void *K, int dtype, int64_t k_head_stride
 /* Recentre and rebin selected heads with their centroids kept (new mean = ksum / (end-1)):
  * replaces the recentring branch of SphereIndexGPU._build (ssa/attn/sphere_gpu.py:187-219 with mu given;
  * callers ssa/kernels/sphere_fused.py:453-464).  `head_list` device int32 [n_list] entries of st;
- * `end`: clustered positions are [1, end) (the host's copy of state.end).  Workspace as for a fit of n_list heads. */
+ * `end`: clustered positions are [1, end) (the host's copy of state.end).  Workspace as for a fit of n_list heads.
+ * split_factor > 0: clusters the rebinning left over their cap are then divided two ways at a time (iters, capk as
+ * in skv_fit) - what the reference's PyTorch path does when such a cluster next receives a key; its kernels, and
+ * skv_insert, cannot stage a cluster much larger than the cap, so without this it would stay oversized.
+ * split_factor = 0: rebin only. */
 int skv_rebin(const skv_state *st, const int32_t *head_list, int n_list, int end, const void *K, int dtype,
-              int64_t k_head_stride, int64_t k_row_stride, void *workspace, int64_t workspace_bytes, void *stream);
+              int64_t k_head_stride, int64_t k_row_stride, float split_factor, int iters, float capk,
+              void *workspace, int64_t workspace_bytes, void *stream);
 
 /* ---- single-token forward around the attention (bf16) ------------------------------------------------
  * The decode graph of the reference runs the engine's modules one framework op at a time

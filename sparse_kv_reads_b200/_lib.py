@@ -121,7 +121,7 @@ def _declare(lib) -> None:
     lib.skv_gemv.restype = i32
     lib.skv_gemv.argtypes = [vp, i32, i32, vp, i32, i32, vp, vp, vp, vp, vp, f32, vp]
     lib.skv_rebin.restype = i32
-    lib.skv_rebin.argtypes = [C.POINTER(SkvState), vp, i32, i32, vp, i32, i64, i64, vp, i64, vp]
+    lib.skv_rebin.argtypes = [C.POINTER(SkvState), vp, i32, i32, vp, i32, i64, i64, f32, i32, f32, vp, i64, vp]
 
 
 def lib():

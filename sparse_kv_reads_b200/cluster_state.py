@@ -153,7 +153,8 @@ class SphereIndexGraph:
                  split_factor: float = 0.0, grow_cap: bool = False, reset_at: int = 0, cap_keys: float = 0.0,
                  var_factor: float = 0.0, var_min: int = 8, async_check: bool = True, max_lag: int = 2,
                  split_scratch: int = 8192, summary_bits: int = 8, block_n: int = 32, compact_block: int = 1024,
-                 refit_every: int = 0, arena: ClusterArena | None = None, layer: int = 0):
+                 refit_every: int = 0, arena: ClusterArena | None = None, layer: int = 0,
+                 split_after_rebin: bool = True):
         if partition not in ("kmeans", "random"):
             raise ValueError(f"unknown partition {partition!r}")
         if partition == "random" and kind != "random":
@@ -179,6 +180,7 @@ class SphereIndexGraph:
         self.check_every, self.seed, self.budget = check_every, seed, budget
         self.async_check, self.max_lag, self.split_scratch = async_check, max_lag, split_scratch
         self.summary_bits, self.refit_every = summary_bits, refit_every
+        self.split_after_rebin = split_after_rebin
         self.reset_at, self.var_min = (int(reset_at) if self.splitting else 0), int(var_min)
         self.initialized = False
         self.n = 0
@@ -389,9 +391,13 @@ class SphereIndexGraph:
         hl = heads.to(torch.int32).to(K.device)
         nbytes = L.skv_fit_workspace_bytes(int(hl.numel()), self.end - 1, self.C, self.d)
         ws = _workspace(K.device, nbytes)
+        # clusters the new mean pushes over their cap are divided at once (split_after_rebin): the insert's
+        # in-kernel split cannot stage a cluster much larger than the cap, so it would otherwise keep growing
+        sf = self.split_factor if self.split_factor > 0 and self.split_after_rebin else 0.0
         check(L.skv_rebin(ctypes.byref(self._st), hl.data_ptr(), int(hl.numel()), self.end, K.data_ptr(),
-                          dtype_code(K.dtype), K.stride(0), K.stride(1), ws.data_ptr(), ws.numel(),
-                          stream_ptr(K.device)), "skv_rebin")
+                          dtype_code(K.dtype), K.stride(0), K.stride(1), sf, self.kmeans_iters, self.capk,
+                          ws.data_ptr(), ws.numel(), stream_ptr(K.device)), "skv_rebin")
+        self._max_members = None
         self.rebuilds += int(hl.numel())
 
     # ---- selection -------------------------------------------------------------------------------

@@ -703,8 +703,8 @@ static int launch_assign(const FitView &v, cudaStream_t s) {
     return SKV_OK;
 }
 
-static int split_rounds(FitView &v, float *projbuf, float split_factor, int iters, float capk, cudaStream_t s) {
-    bool kway = true;
+static int split_rounds(FitView &v, float *projbuf, float split_factor, int iters, float capk, bool kway,
+                        cudaStream_t s) {
     for (int round = 0; round < 256; ++round) {
         int32_t host[4] = {0, 0, 0, 0};
         SKV_CUDA_OK(cudaMemsetAsync(v.counters, 0, 16, s));
@@ -780,20 +780,22 @@ extern "C" int skv_fit(const skv_state *st, const void *K, int dtype, int64_t k_
     accumulate_kernel<<<dim3((st->C + 7) / 8, entries), 256, 0, s>>>(v, 0, st->C);
     finish_fit_kernel<<<(entries + 127) / 128, 128, 0, s>>>(v, cap_keys, split_factor, C_init, 1, var_factor);
     SKV_CUDA_OK(cudaGetLastError());
-    if (split_factor > 0.f && (rc = split_rounds(v, projbuf, split_factor, iters, capk, s))) return rc;
+    if (split_factor > 0.f && (rc = split_rounds(v, projbuf, split_factor, iters, capk, true, s))) return rc;
     if (st->summary_bits == 8) refresh8_kernel<<<dim3((st->C + 7) / 8, entries), 256, 0, s>>>(v);
     SKV_CUDA_OK(cudaGetLastError());
     return SKV_OK;
 }
 
 extern "C" int skv_rebin(const skv_state *st, const int32_t *head_list, int n_list, int end, const void *K, int dtype,
-                         int64_t k_head_stride, int64_t k_row_stride, void *workspace, int64_t workspace_bytes,
-                         void *stream) {
+                         int64_t k_head_stride, int64_t k_row_stride, float split_factor, int iters, float capk,
+                         void *workspace, int64_t workspace_bytes, void *stream) {
     int rc = check_state(st);
     if (rc) return rc;
     if (!K || !workspace || !head_list) return SKV_E_NULL;
     if (dtype != SKV_BF16 && dtype != SKV_F32) return SKV_E_DTYPE;
-    if (n_list < 1 || n_list > st->heads || end < 2 || end > st->capacity) return SKV_E_RANGE;
+    if (n_list < 1 || n_list > st->heads || end < 2 || end > st->capacity || split_factor < 0.f || iters < 0 ||
+        capk < 0.f)
+        return SKV_E_RANGE;
     const int esz = dtype == SKV_BF16 ? 2 : 4;
     if (!aligned16(K) || !aligned16(workspace) || (k_row_stride * esz) % 16 || (k_head_stride * esz) % 16 ||
         k_row_stride < HEAD_DIM)
@@ -804,12 +806,18 @@ extern "C" int skv_rebin(const skv_state *st, const int32_t *head_list, int n_li
     FitView v;
     v.st = *st; v.list = head_list; v.entries = n_list; v.end = end; v.m = m;
     v.ksh = k_head_stride; v.ksr = k_row_stride; v.K = K; v.k_layers = nullptr; v.hpl = 1;
-    carve(v, static_cast<char *>(workspace), n_list, m, st->C);
+    const int64_t used = carve(v, static_cast<char *>(workspace), n_list, m, st->C);
+    float *projbuf = reinterpret_cast<float *>(static_cast<char *>(workspace) + used);
     rc = dtype == SKV_BF16 ? centre_and_assign<__nv_bfloat16>(v, 1, s) : centre_and_assign<float>(v, 1, s);
     if (rc) return rc;
     if ((rc = launch_assign(v, s))) return rc;
     accumulate_kernel<<<dim3((st->C + 7) / 8, n_list), 256, 0, s>>>(v, 0, st->C);
     finish_fit_kernel<<<(n_list + 127) / 128, 128, 0, s>>>(v, 0.f, 0.f, 1, 0, 0.f);
+    SKV_CUDA_OK(cudaGetLastError());
+    // Rebinning about a new mean can leave clusters over their cap, larger than the insert's in-kernel split
+    // stages; they are divided here, two ways at a time, as the reference's PyTorch path divides a cluster
+    // over the cap when it next receives a key (ssa/attn/sphere_gpu.py:247-249, :307-338).
+    if (split_factor > 0.f && (rc = split_rounds(v, projbuf, split_factor, iters, capk, false, s))) return rc;
     if (st->summary_bits == 8) refresh8_kernel<<<dim3((st->C + 7) / 8, n_list), 256, 0, s>>>(v);
     SKV_CUDA_OK(cudaGetLastError());
     return SKV_OK;

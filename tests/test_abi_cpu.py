@@ -110,7 +110,7 @@ def test_state_calls_reject_bad_arguments(L):
     assert fit(st, capk=-1.0) == -5 and fit(st, vf=-0.5) == -5 and fit(st, hl=ok, nl=0) == -5 and fit(st, hl=ok, nl=3) == -5
     assert fit(st, bytes=16) == -6
     assert L.skv_fit_workspace_bytes(2, 55, 64, 128) > 2 * 55 * 512
-    assert L.skv_rebin(ctypes.byref(st), ok, 3, 32, ok, 0, 128 * 64, 128, ok, 1 << 40, None) == -5
+    assert L.skv_rebin(ctypes.byref(st), ok, 3, 32, ok, 0, 128 * 64, 128, 0.0, 10, 0.0, ok, 1 << 40, None) == -5
     assert L.skv_merge(None, ok, ok, ok, 1, 1, 1, 128, None) == -1
 
 

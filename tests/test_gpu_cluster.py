@@ -296,3 +296,23 @@ def test_one_fit_for_all_layers_equals_a_fit_per_layer():
             torch.testing.assert_close(other.sum_dir, alone.sum_dir, rtol=0, atol=0)
             assert torch.equal(other.dir8, alone.dir8) and other.splits == alone.splits
         assert int(alone.n_c.min()) > 16 and alone.check_status() == 0
+
+
+def test_clusters_stay_under_the_cap_through_recentring():
+    """Rebinning about a new mean can pile keys onto a few centroids; the clusters it leaves over the cap are
+    divided at once, so that none outgrows what the in-kernel split can stage (no status bit, count <= cap)."""
+    h, n0, n1 = 2, 900, 1300
+    K, _ = oc.clustered_keys(h, 1304, 128, seed=31)
+    K[:, 1000:] += 0.8                                    # a shift of the keys' mean: drift flags, recentring
+    Kd = K.to(torch.bfloat16).to(DEV)
+    ix = SphereIndexGraph(C=256, C_init=16, cap_keys=24.0, window=8, delta=0.01, capacity=1304, check_every=4,
+                          summary_bits=8, async_check=False)
+    for n in range(n0, n1):
+        ix.observe(Kd, n)
+    assert ix.rebuilds > 0
+    end = ix.end
+    lab = ix.labels.cpu()
+    counts = torch.stack([torch.bincount(lab[i, 1:end].long(), minlength=256) for i in range(h)])
+    assert torch.equal(ix.count.cpu(), counts.float())
+    assert float(ix.count.max()) <= 24.0 and ix.check_status() == 0
+    assert int(ix.n_c.max()) < 256
