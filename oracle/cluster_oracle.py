@@ -441,9 +441,17 @@ class ClusterOracle:
     def select(self, q: torch.Tensor, *, n: int, budget: float, group: str = "sum_share"):
         """``labels [h, n]`` and 0/1 weights ``w [h, C+1]`` (column ``C`` = always-read rows)
         for the shared group modes (sphere_gpu.py:412-442)."""
+        need = self.need(budget)
+        if group == "per_head":                                     # every query head ranks for itself (:431-432)
+            G = q.shape[0] // self.h
+            w = torch.zeros(q.shape[0], self.C + 1)
+            w[:, self.C] = 1.0
+            if self.end > 1 and need > 0:
+                e = self.scores(q).reshape(q.shape[0], self.C)
+                w[:, :self.C] = self.take_until(e, self.count.repeat_interleave(G, 0), need).float()
+            return self.labels[:, :n], w
         w = torch.zeros(self.h, self.C + 1)
         w[:, self.C] = 1.0
-        need = self.need(budget)
         if self.end > 1 and need > 0:
             w[:, :self.C] = self.take_until(self.shared_score(self.scores(q), group), self.count, need).float()
         return self.labels[:, :n], w
@@ -465,7 +473,10 @@ def attend_labeled(q: torch.Tensor, K: torch.Tensor, V: torch.Tensor, labels: to
     H, d = q.shape
     h = K.shape[0]
     G = H // h
-    wr = torch.gather(w.to(dtype), 1, labels.long()).repeat_interleave(G, 0)
+    if w.shape[0] == H and G > 1:                                   # one row of weights per query head
+        wr = torch.gather(w.to(dtype), 1, labels.long().repeat_interleave(G, 0))
+    else:
+        wr = torch.gather(w.to(dtype), 1, labels.long()).repeat_interleave(G, 0)
     s = torch.einsum("hd,hnd->hn", q.to(dtype), K.to(dtype).repeat_interleave(G, 0)) / math.sqrt(d)
     logw = torch.where(wr > 0, wr.clamp_min(1e-300).log(), torch.full_like(wr, -math.inf))
     A = torch.softmax(s + logw, dim=-1)

@@ -4,7 +4,7 @@ Host-side mirror of the reference's state objects for this path, collapsed into 
 reference's names: ``SphereIndexGPU`` (ssa/attn/sphere_gpu.py:113-442), ``SphereIndexFused``
 (ssa/kernels/sphere_fused.py:316-518) and ``SphereIndexGraph`` (ssa/kernels/graph_kernels.py:192-279).
 Every computation is a call into the CUDA library through its C ABI; there is no PyTorch fallback.
-Built: the k-means and fixed-random-direction partitions, the shared selections (``sum_share``, ``max``, ``max_rel``), the size cap (fixed, or growing with
+Built: the k-means and fixed-random-direction partitions, the shared selections (``sum_share``, ``max``, ``max_rel``) and ``per_head``, the size cap (fixed, or growing with
 the context under ``grow_cap``), splits on the spread of a cluster (``var_factor``), the refit of a head
 that ran out of clusters (``reset_at``) and recentring; the reference's other options raise ``ValueError``.
 """
@@ -19,7 +19,7 @@ import torch
 from . import _lib
 from ._lib import SkvState, check, dtype_code, lib, ptr, stream_ptr
 
-GROUPS = {"sum_share": 0, "max": 1, "max_rel": 2}     # SKV_GROUP_* of the C ABI; "per_head" is not built
+GROUPS = {"sum_share": 0, "max": 1, "max_rel": 2}     # SKV_GROUP_* of the C ABI ("per_head" is G calls with "max")
 
 # state arrays: name -> (trailing shape as a function of (C, d, capacity), dtype, fill value)
 _FIELDS = {
@@ -219,6 +219,7 @@ class SphereIndexGraph:
         self.wbuf[:, self.C] = 1.0
         self.selbits = torch.zeros(h, self.C // 32 + 1, dtype=torch.int32, device=device)
         self._attn_ws = None
+        self._attn_kept, self._sel_kept = {}, {}
         self._sel_ws = None
         self._max_members = None
 
@@ -303,7 +304,7 @@ class SphereIndexGraph:
         """Bring the state up to ``n`` cached positions of ``K [h, >=n, d]`` (sphere_gpu.py:393-399)."""
         if not self.initialized or n < self.n or K.shape[0] != getattr(self, "H_kv", -1):
             self._init(K, n)
-        else:
+        elif n > self.n:                                    # the same length again: nothing arrived, no step counted
             self._advance(K, n)
         self.n = n
 
@@ -411,9 +412,16 @@ class SphereIndexGraph:
         if not q.is_contiguous():
             q = q.contiguous()
         if self._sel_ws is None or self._sel_G != G:
+            kept = getattr(self, "_sel_kept", None)
+            if kept is None:
+                kept = self._sel_kept = {}
+            if self._sel_ws is not None:
+                kept[self._sel_G] = self._sel_ws
             self._sel_G = G
-            self._sel_ws = torch.zeros(L.skv_select_workspace_bytes(self.H_kv, G, self.C), dtype=torch.uint8,
-                                       device=q.device)
+            self._sel_ws = kept.get(G)
+            if self._sel_ws is None:
+                self._sel_ws = torch.zeros(L.skv_select_workspace_bytes(self.H_kv, G, self.C), dtype=torch.uint8,
+                                           device=q.device)
         check(L.skv_select(ctypes.byref(self._st), q.data_ptr(), dtype_code(q.dtype), G, n_dev.data_ptr(),
                            self.wbuf.data_ptr(), self.selbits.data_ptr(), self.idx.data_ptr() if listed else None,
                            self.idx.stride(0), self.cnt.data_ptr(), ptr(shared_in), ptr(shared_out), ptr(e_out),
@@ -425,12 +433,33 @@ class SphereIndexGraph:
         """``labels [h, n]`` int16 (label ``C`` = always read) and the 0/1 weights ``w [h, C+1]``; also
         fills ``idx``/``cnt`` with the positions to read.  Persistent buffers, overwritten by the next
         call (ssa/attn/sphere_gpu.py:412-442, ssa/kernels/sphere_fused.py:466-492)."""
-        if group not in GROUPS:
+        if group not in GROUPS and group != "per_head":
             raise ValueError(f"unknown group mode {group!r}")
         self.need_dev.fill_(math.ceil(budget * (self.end - 1)) if self.end > 1 else 0)
         self._n_scalar.fill_(n)
+        if group == "per_head":
+            return self.labels[:, :n], self._per_head(q, None, None)[0]
         self._select(q, self._n_scalar, shared_in=shared_in, shared_out=shared_out, e_out=e_out, group=group)
         return self.labels[:, :n], self.wbuf
+
+    def _per_head(self, q: torch.Tensor, K, V):
+        """``group="per_head"``: every query head ranks the clusters by its own scores and reads its own rows
+        (ssa/attn/sphere_gpu.py:431-432, ssa/kernels/sphere_fused.py:466-492).  One selection (and, with ``K``,
+        one attention) per query head of the group, each with a single query head per KV head, for which the
+        "max" ranking is the head's own score; ``idx``/``cnt`` are left holding the last head's rows.
+        Returns ``(w [H, C+1], out [H, d] or None)``."""
+        H, d = q.shape
+        G = H // self.H_kv
+        qg = q.view(self.H_kv, G, d)
+        w = torch.empty(self.H_kv, G, self.C + 1, dtype=torch.float32, device=q.device)
+        out = torch.empty(self.H_kv, G, d, dtype=q.dtype, device=q.device) if K is not None else None
+        for g in range(G):
+            one = qg[:, g].contiguous()
+            self._select(one, self._n_scalar, group="max")
+            w[:, g] = self.wbuf
+            if K is not None:
+                out[:, g] = self._attend(one, K, V)
+        return w.view(H, self.C + 1), None if out is None else out.view(H, d)
 
     # ---- attention -------------------------------------------------------------------------------
     def _attend_buffers(self, q: torch.Tensor) -> int:
@@ -438,11 +467,19 @@ class SphereIndexGraph:
         G = H // self.H_kv
         if self._attn_ws is None or self.G != G:
             L = lib()
+            kept = getattr(self, "_attn_kept", None)
+            if kept is None:
+                kept = self._attn_kept = {}
+            if self._attn_ws is not None and self.G is not None:      # another group size was in use: keep its buffers
+                kept[(self.G, self.out.dtype)] = (self._attn_ws, self.out, self.num_splits)
             self.G = G
-            self.num_splits = L.skv_attend_splits(self.H_kv)
-            nbytes = L.skv_attend_workspace_bytes(self.H_kv, G, d, self.num_splits)
-            self._attn_ws = torch.zeros(nbytes, dtype=torch.uint8, device=q.device)
-            self.out = torch.empty(H, d, dtype=q.dtype, device=q.device)
+            if (G, q.dtype) in kept:
+                self._attn_ws, self.out, self.num_splits = kept[(G, q.dtype)]
+            else:
+                self.num_splits = L.skv_attend_splits(self.H_kv)
+                nbytes = L.skv_attend_workspace_bytes(self.H_kv, G, d, self.num_splits)
+                self._attn_ws = torch.zeros(nbytes, dtype=torch.uint8, device=q.device)
+                self.out = torch.empty(H, d, dtype=q.dtype, device=q.device)
         return G
 
     def _attend(self, q: torch.Tensor, K: torch.Tensor, V: torch.Tensor, *, dense_n=None, force_simple=False):
@@ -485,6 +522,11 @@ class SphereIndexGraph:
         rows.  ``K, V [h, >=n, d]`` in place.  Returns ``(out [H, d], labels, w)``
         (ssa/kernels/sphere_fused.py:494-501)."""
         self.observe(K, n)
+        if group == "per_head":
+            self.need_dev.fill_(math.ceil(budget * (self.end - 1)) if self.end > 1 else 0)
+            self._n_scalar.fill_(n)
+            w, out = self._per_head(q, K, V)
+            return out, self.labels[:, :n], w
         labels, w = self.labels_and_weights(q, n=n, budget=budget, group=group)
         return self._attend(q, K, V), labels, w
 

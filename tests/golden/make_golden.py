@@ -70,6 +70,10 @@ def case_stream(ref, *, h, G, n0, steps, C, C_init, cap_keys, split_factor, wind
             out = ref["label_weighted_attention"](Q[t].double(), K[:, :n].double(), V[:, :n].double(), labels, w.double())
             gold["probes"][t] = {"w": w.to(torch.uint8), "out": out.float(), "n_c": ix.n_c.clone(),
                                  "splits": ix.splits, "rebuilds": ix.rebuilds}
+            lab_ph, w_ph = ix.labels_and_weights(Q[t], n=n, budget=budget, group="per_head")
+            gold["probes"][t]["w_per_head"] = w_ph.to(torch.uint8)
+            gold["probes"][t]["out_per_head"] = ref["label_weighted_attention"](
+                Q[t].double(), K[:, :n].double(), V[:, :n].double(), lab_ph, w_ph.double()).float()
             for grp in ("max", "max_rel"):                  # the other shared ways of ranking clusters
                 gold["probes"][t]["w_" + grp] = ix.labels_and_weights(Q[t], n=n, budget=budget, group=grp)[1].to(torch.uint8)
     gold["final"] = snapshot(ix, full=full)

@@ -316,3 +316,24 @@ def test_clusters_stay_under_the_cap_through_recentring():
     assert torch.equal(ix.count.cpu(), counts.float())
     assert float(ix.count.max()) <= 24.0 and ix.check_status() == 0
     assert int(ix.n_c.max()) < 256
+
+
+@pytest.mark.parametrize("G", [2, 4])
+def test_every_query_head_ranks_for_itself(G):
+    """group="per_head": from the oracle's state, each query head's selection equals the oracle's bit for bit
+    and its attention reads exactly its own rows."""
+    h, n = 3, 1200
+    Q, K, V = isotropic_stream(h, 1208, h * G, seed=13 + G, dtype=torch.float32)
+    st = oc.ClusterOracle(C=128, C_init=32, cap_keys=24.0, window=16, delta=math.inf, capacity=1208)
+    st.observe(K, n)
+    ix = device_index_from_oracle(st, budget=0.25)
+    q = Q[0]
+    _, w_want = st.select(q, n=n, budget=0.25, group="per_head")
+    out, labels, w = ix.attend(q.to(DEV), K.to(DEV), V.to(DEV), n=n, budget=0.25, group="per_head")
+    assert w.shape == (h * G, 129) and torch.equal(w.cpu(), w_want)
+    assert not torch.equal(w_want.view(h, G, -1)[:, 0], w_want.view(h, G, -1)[:, 1])     # the heads do differ
+    want = oc.attend_labeled(q, K[:, :n], V[:, :n], labels.cpu(), w_want)
+    assert float((out.cpu().double() - want).abs().max()) <= 1e-5
+    # the shared modes still work afterwards (their buffers were kept)
+    _, w_sum = ix.labels_and_weights(q.to(DEV), n=n, budget=0.25)
+    assert torch.equal(w_sum.cpu(), st.select(q, n=n, budget=0.25)[1])

@@ -54,6 +54,11 @@ def test_cuda_stream_against_the_reference_golden_vectors(golden_small, golden_c
             boundary = max(boundary, diff)
             if diff == 0:                                   # same selection: the attention must match to fp32 accuracy
                 worst = max(worst, float((out.cpu() - p["out"]).abs().max()))
+            out_ph, _, w_ph = ix.attend(Q[t].to(DEV), Kd, Vd, n=n, budget=c["budget"], group="per_head")
+            d_ph = int((w_ph.cpu().to(torch.uint8) != p["w_per_head"]).sum(1).max())
+            boundary = max(boundary, d_ph)
+            if d_ph == 0:                                   # every query head reads its own rows
+                worst = max(worst, float((out_ph.cpu() - p["out_per_head"]).abs().max()))
             for grp in ("max", "max_rel"):                  # the other shared rankings (exact ties may fall either way)
                 _, wg = ix.labels_and_weights(Q[t].to(DEV), n=n, budget=c["budget"], group=grp)
                 boundary = max(boundary, int((wg.cpu().to(torch.uint8) != p["w_" + grp]).sum(1).max()))

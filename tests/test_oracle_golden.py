@@ -76,6 +76,10 @@ def test_stream_cases_reproduce_the_reference_bit_for_bit(golden_small, case):
         n = g["cfg"]["n0"] + t
         labels, w = st.select(q, n=n, budget=g["cfg"]["budget"])
         assert torch.equal(w.to(torch.uint8), p["w"])
+        lab_ph, w_ph = st.select(q, n=n, budget=g["cfg"]["budget"], group="per_head")
+        assert torch.equal(w_ph.to(torch.uint8), p["w_per_head"])
+        torch.testing.assert_close(oc.attend_labeled(q, K[:, :n], V[:, :n], lab_ph, w_ph).float(), p["out_per_head"],
+                                   rtol=0, atol=1e-6)
         for grp in ("max", "max_rel"):
             mine = st.select(q, n=n, budget=g["cfg"]["budget"], group=grp)[1].to(torch.uint8)
             _same_up_to_ties(mine, p["w_" + grp], st.shared_score(st.scores(q), grp))
