@@ -139,6 +139,24 @@ int skv_attend_static(const void *q, const void *K, const void *V, const int32_t
 int skv_merge(const float *m, const float *l, const float *a, float *out, int heads, int S, int G, int d,
               void *stream);
 
+/* QK-RMSNorm + rotary embedding + KV-cache write of the new token, folded into skv_select (optional): the selection
+ * needs the rotated queries first of all, so its CTAs compute them from the raw q/k/v product themselves instead of
+ * waiting for a separate launch (skv_qk_rope_cache, which this replaces on that path; same arithmetic and
+ * roundings).  Every scoring CTA rotates the G query heads of its KV head for its own use; the first CTA of each
+ * (sequence, KV head) also stores them to q_out (for the attention launch) and writes the new K and V rows. */
+typedef struct skv_rope {
+    const void *qkv;                 /* [B, (H + 2 H_kv) * 128] bf16: q heads, then k heads, then v heads */
+    const void *q_norm_w, *k_norm_w; /* [128] bf16 */
+    const void *cos_table, *sin_table; /* [positions, 128] bf16 */
+    const int64_t *pos;              /* device [1]: position of the new token */
+    void *q_out;                     /* [B * H, 128] bf16 */
+    void *k_cache, *v_cache;         /* bf16 caches of this layer */
+    int32_t H, H_kv;                 /* query and KV heads per sequence (state.heads = B * H_kv) */
+    int64_t cache_batch_stride, cache_head_stride, cache_row_stride;   /* elements */
+    float eps;
+    int32_t reserved;
+} skv_rope;
+
 /* How the G query heads of a KV head share one ranking of its clusters (ssa/attn/sphere_gpu.py:431-439) */
 #define SKV_GROUP_SUM_SHARE 0   /* sum over the heads of each head's softmax over clusters */
 #define SKV_GROUP_MAX       1   /* largest scaled score of any head */
@@ -164,12 +182,14 @@ int skv_merge(const float *m, const float *l, const float *a, float *out, int he
  *   e_out      optional [heads, G, C] float32: per-query-head cluster scores (before the 1/sqrt(d) scale)
  *   workspace  skv_select_workspace_bytes(heads, G, C) bytes, zero-initialised once by the caller
  *   group      SKV_GROUP_* (shared_in, when given, is ranked as it is)
+ *   rope       optional: compute the queries from the raw projection first (see skv_rope); q is then unused,
+ *              bf16 only, G = rope->H / rope->H_kv
  */
 int64_t skv_select_workspace_bytes(int heads, int G, int C);
 int skv_select(const skv_state *st, const void *q, int dtype, int G, const int32_t *n_dev,
                float *w, uint32_t *selbits, int32_t *idx, int64_t idx_stride, int32_t *cnt,
                const float *shared_in, float *shared_out, float *e_out, void *workspace, float scale, int group,
-               void *stream);
+               const skv_rope *rope, void *stream);
 
 /* Tuning aid without a counterpart in the reference: `dev_ptr` is a device array of 16 uint64 that receives
  * nanosecond time stamps of the phases of skv_select's kernel for head 0 (null switches it off). */

@@ -34,6 +34,15 @@ class SkvComm(C.Structure):
                 ("data", C.c_void_p * 8), ("tick", C.c_void_p), ("status", C.c_void_p)]
 
 
+class SkvRope(C.Structure):
+    """``skv_rope`` of include/skv.h: QK-norm + rotary + cache write folded into the selection launch."""
+    _fields_ = [("qkv", C.c_void_p), ("q_norm_w", C.c_void_p), ("k_norm_w", C.c_void_p), ("cos_table", C.c_void_p),
+                ("sin_table", C.c_void_p), ("pos", C.c_void_p), ("q_out", C.c_void_p), ("k_cache", C.c_void_p),
+                ("v_cache", C.c_void_p), ("H", C.c_int32), ("H_kv", C.c_int32), ("cache_batch_stride", C.c_int64),
+                ("cache_head_stride", C.c_int64), ("cache_row_stride", C.c_int64), ("eps", C.c_float),
+                ("reserved", C.c_int32)]
+
+
 class SkvState(C.Structure):
     """Mirror of ``struct skv_state``."""
     _fields_ = [("heads", C.c_int32), ("C", C.c_int32), ("d", C.c_int32), ("capacity", C.c_int32),
@@ -67,7 +76,8 @@ def _declare(lib) -> None:
     lib.skv_merge.restype = i32
     lib.skv_merge.argtypes = [vp, vp, vp, vp, i32, i32, i32, i32, vp]
     lib.skv_select.restype = i32
-    lib.skv_select.argtypes = [C.POINTER(SkvState), vp, i32, i32, vp, vp, vp, vp, i64, vp, vp, vp, vp, vp, f32, i32, vp]
+    lib.skv_select.argtypes = [C.POINTER(SkvState), vp, i32, i32, vp, vp, vp, vp, i64, vp, vp, vp, vp, vp, f32, i32,
+                               C.POINTER(SkvRope), vp]
     lib.skv_select_workspace_bytes.restype = i64
     lib.skv_select_workspace_bytes.argtypes = [i32, i32, i32]
     lib.skv_debug_select_probe.restype = None

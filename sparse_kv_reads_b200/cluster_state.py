@@ -403,7 +403,7 @@ class SphereIndexGraph:
 
     # ---- selection -------------------------------------------------------------------------------
     def _select(self, q: torch.Tensor, n_dev: torch.Tensor, *, shared_in=None, shared_out=None, e_out=None,
-                listed: bool = True, group: str = "sum_share") -> None:
+                listed: bool = True, group: str = "sum_share", rope=None) -> None:
         """Score and pick; with ``listed`` also build the ascending row list ``idx``/``cnt`` (otherwise
         ``cnt`` is zeroed and the label-driven attention kernel fills it)."""
         H, d = q.shape
@@ -425,8 +425,8 @@ class SphereIndexGraph:
         check(L.skv_select(ctypes.byref(self._st), q.data_ptr(), dtype_code(q.dtype), G, n_dev.data_ptr(),
                            self.wbuf.data_ptr(), self.selbits.data_ptr(), self.idx.data_ptr() if listed else None,
                            self.idx.stride(0), self.cnt.data_ptr(), ptr(shared_in), ptr(shared_out), ptr(e_out),
-                           self._sel_ws.data_ptr(), 1.0 / math.sqrt(d), GROUPS[group], stream_ptr(q.device)),
-              "skv_select")
+                           self._sel_ws.data_ptr(), 1.0 / math.sqrt(d), GROUPS[group],
+                           None if rope is None else ctypes.byref(rope), stream_ptr(q.device)), "skv_select")
 
     def labels_and_weights(self, q: torch.Tensor, *, n: int, budget: float, group: str = "sum_share",
                            shared_in=None, shared_out=None, e_out=None):
@@ -552,15 +552,20 @@ class SphereIndexGraph:
         self._ktable(K)
         assert self.G == G
 
-    def step(self, q: torch.Tensor, K: torch.Tensor, V: torch.Tensor, n_dev: torch.Tensor, insert: bool = True):
+    def step(self, q: torch.Tensor, K: torch.Tensor, V: torch.Tensor, n_dev: torch.Tensor, insert: bool = True,
+             rope=None):
         """One decode step with every length on the device; position ``n-1`` of ``K, V`` is already
         written.  ``insert=False`` when one launch inserted for all layers
         (ssa/kernels/graph_kernels.py:220-244)."""
         if insert:
             self._launch_insert(K, n_dev, self.budget)
         if self._fused_rows(K):
-            self._select(q, n_dev, listed=False)
+            # rope (an ``SkvRope``): the selection launch computes q from the raw projection, stores it to ``q``
+            # and writes the token's K/V rows, in place of a separate launch ahead of it
+            self._select(q, n_dev, listed=False, rope=rope)
             return self._attend_labels(q, K, V, n_dev)
+        if rope is not None:
+            raise ValueError("the folded rotary step needs the label-driven attention path (bf16 cache)")
         self._select(q, n_dev)
         return self._attend(q, K, V)
 

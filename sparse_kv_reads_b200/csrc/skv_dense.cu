@@ -2,11 +2,9 @@
 // residual add + RMSNorm, per-head QK-RMSNorm + rotary embedding + KV-cache write, SiLU(gate) * up.
 // Each replaces five to twenty element-wise launches of a framework-level forward; they are
 // latency-bound (a few KB per sequence), so the point is one launch instead of many.
-#include "skv_common.cuh"
+#include "skv_rope.cuh"
 
 namespace skv {
-
-__device__ __forceinline__ float bf16_round(float x) { return __bfloat162float(__float2bfloat16(x)); }
 
 // h += delta (when given), rounded to bf16 as the residual stream is stored; out = RMSNorm(h) * w.
 // One CTA per sequence; hidden a multiple of 8.
@@ -67,34 +65,17 @@ __global__ void __launch_bounds__(128) qk_rope_cache_kernel(const __nv_bfloat16 
     const int b = item / per, j = item % per;
     const int64_t pos = pos_dev[0];
     const __nv_bfloat16 *src = qkv + ((int64_t)b * per + j) * HEAD_DIM + lane * 4;
-    float4 x = load4(src);
     if (j >= H + H_kv) {                                              // value head: straight into the cache
         __nv_bfloat16 *dst = v_cache + b * cache_b_stride + (j - H - H_kv) * cache_h_stride + pos * cache_row_stride;
         *reinterpret_cast<uint2 *>(dst + lane * 4) = *reinterpret_cast<const uint2 *>(src);
         return;
     }
     const bool is_q = j < H;
-    const float ms = warp_sum(x.x * x.x + x.y * x.y + x.z * x.z + x.w * x.w) / (float)HEAD_DIM;
-    const float inv = rsqrtf(ms + eps);
-    const float4 g = load4((is_q ? qw : kw) + lane * 4);
-    // the normed head is a bf16 tensor in the unfused forward: round before rotating
-    x.x = bf16_round(x.x * inv * g.x); x.y = bf16_round(x.y * inv * g.y);
-    x.z = bf16_round(x.z * inv * g.z); x.w = bf16_round(x.w * inv * g.w);
-    const float4 c = load4(cos_t + pos * HEAD_DIM + lane * 4), s = load4(sin_t + pos * HEAD_DIM + lane * 4);
-    float4 o;                                                         // partner component i +- 64 sits 16 lanes away
-    o.x = __shfl_xor_sync(0xffffffffu, x.x, 16); o.y = __shfl_xor_sync(0xffffffffu, x.y, 16);
-    o.z = __shfl_xor_sync(0xffffffffu, x.z, 16); o.w = __shfl_xor_sync(0xffffffffu, x.w, 16);
-    const float sg = lane < 16 ? -1.f : 1.f;                          // rot(x) = cat(-x2, x1)
-    float4 r;
-    r.x = bf16_round(x.x * c.x) + bf16_round(sg * o.x * s.x);
-    r.y = bf16_round(x.y * c.y) + bf16_round(sg * o.y * s.y);
-    r.z = bf16_round(x.z * c.z) + bf16_round(sg * o.z * s.z);
-    r.w = bf16_round(x.w * c.w) + bf16_round(sg * o.w * s.w);
-    __align__(8) __nv_bfloat16 ob[4] = {__float2bfloat16(r.x), __float2bfloat16(r.y), __float2bfloat16(r.z),
-                                        __float2bfloat16(r.w)};
+    const float4 r = norm_rope_head(src - lane * 4, is_q ? qw : kw, cos_t + pos * HEAD_DIM, sin_t + pos * HEAD_DIM, eps,
+                                    lane);
     __nv_bfloat16 *dst = is_q ? q_out + ((int64_t)b * H + j) * HEAD_DIM
                               : k_cache + b * cache_b_stride + (j - H) * cache_h_stride + pos * cache_row_stride;
-    *reinterpret_cast<uint2 *>(dst + lane * 4) = *reinterpret_cast<const uint2 *>(ob);
+    store_bf16x4(dst + lane * 4, r);
 }
 
 // gate_up [B, 2*inter] (gate first) -> out [B, inter] = silu(gate) * up, rounded as the unfused forward does

@@ -9,7 +9,7 @@
 // clusters in decreasing score, lower slot first among equals, until the counts reach need".
 #include <cuda_fp16.h>
 
-#include "skv_common.cuh"
+#include "skv_rope.cuh"
 
 namespace skv {
 
@@ -35,6 +35,7 @@ struct SelectParams {
     float *pstat;             // [heads, SEL_MAX_CTAS, 16, 2] slice (max, sum of exp) per query head
     float scale;
     int group;                // how a group's query heads share one ranking: SKV_GROUP_*
+    skv_rope rope;            // rope.qkv != null: the queries are computed here from the raw projection
     unsigned long long *probe;  // optional [16] phase time stamps (ns) of head 0's picking CTA, for tuning
 };
 
@@ -100,6 +101,39 @@ __device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
     return *reinterpret_cast<const uint32_t *>(&v);
 }
 
+// QK-norm + rotary of KV head h's G query heads, a warp per head, into sq (when given); with `first` (the head's
+// first CTA) they are also stored for the attention launch and the token's K and V rows are written.
+__device__ __forceinline__ void rope_heads(const skv_rope &r, int h, bool first, int G, float *sq) {
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    const int seq = h / r.H_kv, hk = h % r.H_kv, per_seq = r.H + 2 * r.H_kv;
+    const int64_t pos = r.pos[0];
+    const __nv_bfloat16 *row = static_cast<const __nv_bfloat16 *>(r.qkv) + (int64_t)seq * per_seq * HEAD_DIM;
+    const __nv_bfloat16 *cs = static_cast<const __nv_bfloat16 *>(r.cos_table) + pos * HEAD_DIM;
+    const __nv_bfloat16 *sn = static_cast<const __nv_bfloat16 *>(r.sin_table) + pos * HEAD_DIM;
+    const int jobs = G + (first ? 2 : 0);
+    for (int j = wid; j < jobs; j += SEL_WARPS) {
+        if (j < G) {
+            const int qh = hk * G + j;
+            const float4 v = norm_rope_head(row + (int64_t)qh * HEAD_DIM, static_cast<const __nv_bfloat16 *>(r.q_norm_w),
+                                            cs, sn, r.eps, lane);
+            if (sq) *reinterpret_cast<float4 *>(sq + j * HEAD_DIM + lane * 4) = v;
+            if (first)
+                store_bf16x4(static_cast<__nv_bfloat16 *>(r.q_out) + ((int64_t)seq * r.H + qh) * HEAD_DIM + lane * 4, v);
+        } else {
+            const int64_t at = seq * r.cache_batch_stride + hk * r.cache_head_stride + pos * r.cache_row_stride;
+            if (j == G) {
+                const float4 v = norm_rope_head(row + (int64_t)(r.H + hk) * HEAD_DIM,
+                                                static_cast<const __nv_bfloat16 *>(r.k_norm_w), cs, sn, r.eps, lane);
+                store_bf16x4(static_cast<__nv_bfloat16 *>(r.k_cache) + at + lane * 4, v);
+            } else {
+                const __nv_bfloat16 *src = row + (int64_t)(r.H + r.H_kv + hk) * HEAD_DIM + lane * 4;
+                *reinterpret_cast<uint2 *>(static_cast<__nv_bfloat16 *>(r.v_cache) + at + lane * 4) =
+                    *reinterpret_cast<const uint2 *>(src);
+            }
+        }
+    }
+}
+
 // Grid (ctas, heads).  Every CTA scores a slice of the head's clusters: e = (longest or shortest key) x
 // projection of the query on the cluster's mean direction, scaled by 1/sqrt(d); it then leaves
 // exp(z - slice max) in zbuf and its (max, sum) per query head in pstat.  The last CTA of the head to
@@ -139,7 +173,11 @@ __global__ void __launch_bounds__(SEL_THREADS) score_pick_kernel(const SelectPar
     const int per = (((n_c + nb - 1) / nb) + 3) & ~3;              // clusters per scoring CTA
     const float inv_per = 1.0f / (float)max(per, 1);
     if (b == 0) stamp(p, h, 0);
-    if (!scoring) { pdl_wait(); pdl_trigger(); }
+    if (!scoring) {
+        pdl_wait();
+        pdl_trigger();
+        if (p.rope.qkv) rope_heads(p.rope, h, true, G, nullptr);   // nothing to score: the token's rows are still due
+    }
 
     if (scoring) {
         const int c_lo = min(b * per, n_c), c_hi = min(c_lo + per, n_c), mine = c_hi - c_lo;
@@ -198,7 +236,11 @@ __global__ void __launch_bounds__(SEL_THREADS) score_pick_kernel(const SelectPar
         }
         pdl_wait();                                        // the query comes from the kernel before this one
         pdl_trigger();
-        for (int i = tid; i < G * d; i += SEL_THREADS) sq[i] = load_as_float(q + i);
+        if (p.rope.qkv) {
+            rope_heads(p.rope, h, b == 0, G, sq);
+        } else {
+            for (int i = tid; i < G * d; i += SEL_THREADS) sq[i] = load_as_float(q + i);
+        }
         __syncthreads();
         if (q8 && TC) {
             // query fragments (A): rows = query heads, k permuted as described above
@@ -695,9 +737,23 @@ extern "C" int64_t skv_select_workspace_bytes(int heads, int G, int C) {
 
 extern "C" int skv_select(const skv_state *st, const void *q, int dtype, int G, const int32_t *n_dev, float *w,
                           uint32_t *selbits, int32_t *idx, int64_t idx_stride, int32_t *cnt, const float *shared_in,
-                          float *shared_out, float *e_out, void *workspace, float scale, int group, void *stream) {
+                          float *shared_out, float *e_out, void *workspace, float scale, int group,
+                          const skv_rope *rope, void *stream) {
     if (!st || !n_dev || !w || !cnt || !workspace) return SKV_E_NULL;
-    if (!shared_in && !q) return SKV_E_NULL;
+    if (!shared_in && !q && !rope) return SKV_E_NULL;
+    if (rope) {
+        if (shared_in) return SKV_E_RANGE;               // nothing to score, so nothing to rotate
+        if (!rope->qkv || !rope->q_norm_w || !rope->k_norm_w || !rope->cos_table || !rope->sin_table || !rope->pos ||
+            !rope->q_out || !rope->k_cache || !rope->v_cache)
+            return SKV_E_NULL;
+        if (dtype != SKV_BF16) return SKV_E_DTYPE;
+        if (rope->H_kv < 1 || rope->H < rope->H_kv || rope->H % rope->H_kv || rope->H / rope->H_kv != G ||
+            st->heads % rope->H_kv)
+            return SKV_E_RANGE;
+        if (!aligned16(rope->qkv) || !aligned16(rope->q_out) || !aligned16(rope->k_cache) || !aligned16(rope->v_cache) ||
+            rope->cache_row_stride % 8 || rope->cache_head_stride % 8 || rope->cache_batch_stride % 8)
+            return SKV_E_ALIGN;
+    }
     if (!st->count || !st->n_c || !st->end || !st->need || !st->labels || !st->mmax || !st->mmin) return SKV_E_NULL;
     if (st->d != HEAD_DIM) return SKV_E_DIM;
     if (st->C < 16 || (st->C & (st->C - 1)) || st->C > 16384) return SKV_E_DIM;
@@ -714,6 +770,7 @@ extern "C" int skv_select(const skv_state *st, const void *q, int dtype, int G, 
     SelectParams p;
     p.st = *st; p.q = q; p.G = G; p.n_dev = n_dev; p.w = w; p.idx = idx; p.idx_stride = idx_stride; p.cnt = cnt;
     p.shared_in = shared_in; p.shared_out = shared_out; p.e_out = e_out; p.scale = scale; p.group = group;
+    p.rope = rope ? *rope : skv_rope{};
     p.probe = g_probe;
     char *ws = static_cast<char *>(workspace);
     p.zbuf = reinterpret_cast<float *>(ws);

@@ -125,6 +125,7 @@ class GraphDecoder:
         # ... and, up to 8 sequences, its projections as the library's matrix-vector products
         self.own_gemv = own_gemv and os.environ.get("SKV_OWN_GEMV", "1") != "0"
         self._peer = None
+        self.fold_rope = os.environ.get("SKV_FOLD_ROPE", "1") != "0"
         self.fused_insert = fused_insert and mode == "cluster" and window >= 1
         self.insert_all = None
 
@@ -324,15 +325,25 @@ class GraphDecoder:
             h = res if res is not None else h
             h2 = buf_b if h is buf_a else buf_a
             kc, vc = self.cache.k[i], self.cache.v[i]
-            check(L.skv_qk_rope_cache(qkv.data_ptr(), a.q_norm.weight.data_ptr(), a.k_norm.weight.data_ptr(),
-                                      m.rope_cos.data_ptr(), m.rope_sin.data_ptr(), self.pos.data_ptr(),
-                                      qh.data_ptr(), kc.data_ptr(), vc.data_ptr(), B, H, H_kv, d, kc.stride(0),
-                                      kc.stride(1), kc.stride(2), a.q_norm.eps, st), "skv_qk_rope_cache")
-            if self.mode == "dense":
-                out = self.attn[i](qh, self._heads(kc), self._heads(vc), self.n_dev)
-            else:
+            fold = (self.mode == "cluster" and self.fold_rope and self.attn[i]._fused_rows(self._heads(kc)))
+            if fold:
+                # QK-norm, rotary and the cache write ride in the selection launch: six launches per layer
+                rope = _lib.SkvRope(qkv.data_ptr(), a.q_norm.weight.data_ptr(), a.k_norm.weight.data_ptr(),
+                                    m.rope_cos.data_ptr(), m.rope_sin.data_ptr(), self.pos.data_ptr(), qh.data_ptr(),
+                                    kc.data_ptr(), vc.data_ptr(), H, H_kv, kc.stride(0), kc.stride(1), kc.stride(2),
+                                    a.q_norm.eps, 0)
                 out = self.attn[i].step(qh, self._heads(kc), self._heads(vc), self.n_dev,
-                                        insert=self.insert_all is None)
+                                        insert=self.insert_all is None, rope=rope)
+            else:
+                check(L.skv_qk_rope_cache(qkv.data_ptr(), a.q_norm.weight.data_ptr(), a.k_norm.weight.data_ptr(),
+                                          m.rope_cos.data_ptr(), m.rope_sin.data_ptr(), self.pos.data_ptr(),
+                                          qh.data_ptr(), kc.data_ptr(), vc.data_ptr(), B, H, H_kv, d, kc.stride(0),
+                                          kc.stride(1), kc.stride(2), a.q_norm.eps, st), "skv_qk_rope_cache")
+                if self.mode == "dense":
+                    out = self.attn[i](qh, self._heads(kc), self._heads(vc), self.n_dev)
+                else:
+                    out = self.attn[i].step(qh, self._heads(kc), self._heads(vc), self.n_dev,
+                                            insert=self.insert_all is None)
             _, o_red = product(a.o.weight, o, 0, x=out, tp=a.tp,
                                slot_out=2 * i if peer_ok(a.o.weight, 0) else None)
             res, _ = product(self._wgu[i], gu, 1, h_in=h, dl=o_red, g=layer.norm2.weight, h_out=h2)

@@ -82,7 +82,8 @@ def test_state_calls_reject_bad_arguments(L):
     ok = 0x1000
     st = fake_state()
     sel = lambda s, **o: L.skv_select(ctypes.byref(s), o.get("q", ok), o.get("dtype", 0), o.get("G", 2), ok, ok, ok, ok,
-                                      o.get("istr", 64), ok, None, None, None, o.get("ws", ok), 0.1, o.get("group", 0), None)
+                                      o.get("istr", 64), ok, None, None, None, o.get("ws", ok), 0.1, o.get("group", 0),
+                                      o.get("rope", None), None)
     assert sel(fake_state(C=48)) == -2 and sel(fake_state(C=8)) == -2 and sel(st, G=0) == -2
     assert sel(st, q=None) == -1 and sel(st, dtype=5) == -3 and sel(st, istr=8) == -5
     assert sel(st, group=3) == -5 and sel(st, group=-1) == -5

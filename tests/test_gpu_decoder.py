@@ -165,3 +165,46 @@ def test_total_variation_distance_to_exact_attention_shrinks_to_zero_at_full_bud
     kw = dict(mode="cluster", C=128, C_init=16, cap_keys=32.0, window=16)
     d = {b: tvd(decode_logits(model, ids, P, T, budget=b, **kw), exact) for b in (0.1, 0.5, 1.0)}
     assert d[1.0] < 0.02 and d[1.0] <= d[0.5] + 0.01 and d[0.5] <= d[0.1] + 0.01, d
+
+
+def test_rotary_step_folded_into_the_selection_equals_the_separate_launch():
+    """skv_select with a rope description: queries, the new K/V rows and the selection itself are bit-identical
+    to skv_qk_rope_cache followed by a plain skv_select (two sequences, G = 2)."""
+    from sparse_kv_reads_b200 import _lib
+    from sparse_kv_reads_b200._lib import check, lib
+    L = lib()
+    g = torch.Generator().manual_seed(17)
+    B, H, H_kv, d, n = 2, 4, 2, 128, 900
+    cap = 912
+    K = oc.clustered_keys(B * H_kv, cap, d, seed=5)[0].to(torch.bfloat16).to(DEV).view(B, H_kv, cap, d)
+    V = torch.randn(B, H_kv, cap, d, generator=g).to(torch.bfloat16).to(DEV)
+    heads = lambda t: t.view(B * H_kv, cap, d)
+    ix = SphereIndexGraph(C=128, C_init=32, cap_keys=24.0, window=16, delta=math.inf, capacity=cap, budget=0.3)
+    ix.prepare(heads(K), n, B * H)
+    qkv = torch.randn(B, (H + 2 * H_kv) * d, generator=g).to(torch.bfloat16).to(DEV)
+    qw = (1 + 0.1 * torch.randn(d, generator=g)).to(torch.bfloat16).to(DEV)
+    kw = (1 + 0.1 * torch.randn(d, generator=g)).to(torch.bfloat16).to(DEV)
+    ang = torch.outer(torch.arange(cap, dtype=torch.float64), 1.0 / (1e6 ** (torch.arange(0, d, 2, dtype=torch.float64) / d)))
+    ang = torch.cat((ang, ang), -1)
+    cos, sin = ang.cos().to(torch.bfloat16).to(DEV), ang.sin().to(torch.bfloat16).to(DEV)
+    pos = torch.tensor([n], dtype=torch.long, device=DEV)
+    n_dev = torch.tensor([n + 1], dtype=torch.int32, device=DEV)
+    st = torch.cuda.current_stream().cuda_stream
+    # separate launches
+    K1, V1 = K.clone(), V.clone()
+    q1 = torch.empty(B * H, d, dtype=torch.bfloat16, device=DEV)
+    check(L.skv_qk_rope_cache(qkv.data_ptr(), qw.data_ptr(), kw.data_ptr(), cos.data_ptr(), sin.data_ptr(), pos.data_ptr(),
+                              q1.data_ptr(), K1.data_ptr(), V1.data_ptr(), B, H, H_kv, d, K1.stride(0), K1.stride(1),
+                              K1.stride(2), 1e-6, st), "skv_qk_rope_cache")
+    out1 = ix.step(q1, heads(K1), heads(V1), n_dev, insert=False).clone()
+    w1, cnt1 = ix.wbuf.clone(), ix.cnt.clone()
+    # folded
+    K2, V2 = K.clone(), V.clone()
+    q2 = torch.zeros(B * H, d, dtype=torch.bfloat16, device=DEV)
+    rope = _lib.SkvRope(qkv.data_ptr(), qw.data_ptr(), kw.data_ptr(), cos.data_ptr(), sin.data_ptr(), pos.data_ptr(),
+                        q2.data_ptr(), K2.data_ptr(), V2.data_ptr(), H, H_kv, K2.stride(0), K2.stride(1), K2.stride(2),
+                        1e-6, 0)
+    out2 = ix.step(q2, heads(K2), heads(V2), n_dev, insert=False, rope=rope).clone()
+    assert torch.equal(q1, q2) and torch.equal(K1, K2) and torch.equal(V1, V2)
+    assert not torch.equal(K2[:, :, n], K[:, :, n])                   # the row was written
+    assert torch.equal(ix.wbuf, w1) and torch.equal(ix.cnt, cnt1) and torch.equal(out1, out2)
