@@ -104,7 +104,9 @@ def case_partitions(ref) -> dict:
 
 
 def main() -> None:
-    src = sys.argv[1] if len(sys.argv) > 1 else "/root/reference/src"
+    src = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("SKV_REFERENCE_SRC")
+    if not src:
+        raise SystemExit("usage: make_golden.py /path/to/reference/src  (or set SKV_REFERENCE_SRC)")
     sys.path.insert(0, src)
     from ssa.attn.accounting import kv_read_fraction, overhead_rows
     from ssa.attn.clusterkv import spherical_kmeans
