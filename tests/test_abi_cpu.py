@@ -199,3 +199,18 @@ def test_matrix_vector_product_and_exchange_reject_bad_arguments(L):
     assert L.skv_comm_reduce(None, 0, ok, 1, 128, None) == -1
     assert L.skv_comm_reduce(ctypes.byref(c), 0, ok, 1, 12, None) == -5
     assert L.skv_comm_tick(None, None) == -1
+
+
+def test_header_is_plain_c(tmp_path):
+    """include/skv.h compiles as C99 with no framework headers: what a cgo / JNI / FFI binding needs."""
+    import shutil
+    import subprocess
+    gcc = shutil.which("gcc")
+    if gcc is None:
+        pytest.skip("no C compiler")
+    src = tmp_path / "use.c"
+    src.write_text('#include <stddef.h>\n#include "skv.h"\n'
+                   "int main(void) { skv_state s; skv_comm c; skv_rope r; (void)s; (void)c; (void)r;\n"
+                   "  return skv_version() == SKV_VERSION ? 0 : 1; }\n")
+    subprocess.check_call([gcc, "-std=c99", "-Wall", "-Wextra", "-pedantic", "-Werror", "-I",
+                           os.path.join(ROOT, "include"), "-c", str(src), "-o", str(tmp_path / "use.o")])
