@@ -397,7 +397,7 @@ class GraphDecoder:
     def step(self, token: torch.Tensor, pos: int) -> torch.Tensor:
         """Decode ``token [B, 1]`` at position ``pos``; returns logits ``[B, 1, vocab]`` (a buffer the
         next step overwrites)."""
-        self.tok.copy_(token)
+        self.tok.copy_(token, non_blocking=True)           # a pinned host tensor goes straight into the step's buffer
         self.pos.fill_(pos)
         if self.graph is not None:
             self.graph.replay()
