@@ -125,7 +125,11 @@ class GraphDecoder:
         # ... and, up to 8 sequences, its projections as the library's matrix-vector products
         self.own_gemv = own_gemv and os.environ.get("SKV_OWN_GEMV", "1") != "0"
         self._peer = None
-        self.fold_rope = os.environ.get("SKV_FOLD_ROPE", "1") != "0"
+        # QK-norm + rotary in the selection launch: every scoring CTA of a KV head rotates its G query heads, so the
+        # folding pays one launch with G x 16 small redundant jobs - even at G = 2 (0.6B: 583.6 against 583.0 tok/s),
+        # a loss at G = 4 (4B: 253 against 257 tok/s); SKV_FOLD_ROPE=0/1 overrides
+        fold = os.environ.get("SKV_FOLD_ROPE")
+        self.fold_rope = (self.H // self.H_kv <= 2) if fold is None else fold != "0"
         # up to this many bytes of partial sums every CTA of the consuming product adds up for itself; beyond it one
         # reduce launch does (4 GPUs x 4 sequences, 128 KB: 2,096 tok/s with the launch, 1,955 without)
         self.fuse_sum_bytes = 65536
