@@ -208,3 +208,22 @@ def test_rotary_step_folded_into_the_selection_equals_the_separate_launch():
     assert torch.equal(q1, q2) and torch.equal(K1, K2) and torch.equal(V1, V2)
     assert not torch.equal(K2[:, :, n], K[:, :, n])                   # the row was written
     assert torch.equal(ix.wbuf, w1) and torch.equal(ix.cnt, cnt1) and torch.equal(out1, out2)
+
+
+def test_head_reset_between_graph_replays_keeps_budget_one_exact():
+    """reset_at: a head whose cluster count reaches the threshold is refitted between replays (the flag travels
+    with the drift flags); at budget 1 every row is read whatever the clustering, so the logits still equal
+    dense attention, and the counts still match the labels."""
+    model = tiny_model(seed=12)
+    P, T = 260, 100
+    ids = torch.randint(0, 1000, (1, P + T + 1), generator=torch.Generator().manual_seed(9)).to(DEV)
+    dense, _ = run_decoder(model, ids, P, T, True, mode="dense")
+    got, dec = run_decoder(model, ids, P, T, True, mode="cluster", budget=1.0, C=64, C_init=8, cap_keys=12.0,
+                           reset_at=30, window=8, delta=float("inf"), check_every=2, summary_bits=8)
+    torch.testing.assert_close(got, dense, rtol=2e-2, atol=5e-2)
+    assert sum(i.resets for i in dec.attn) > 0
+    for i in dec.attn:
+        end = int(i.end_dev[0])
+        lab = i.labels.cpu()
+        counts = torch.stack([torch.bincount(lab[k, 1:end].long(), minlength=64) for k in range(i.H_kv)])
+        assert torch.equal(i.count.cpu(), counts.float())
