@@ -227,3 +227,22 @@ def test_head_reset_between_graph_replays_keeps_budget_one_exact():
         lab = i.labels.cpu()
         counts = torch.stack([torch.bincount(lab[k, 1:end].long(), minlength=64) for k in range(i.H_kv)])
         assert torch.equal(i.count.cpu(), counts.float())
+
+
+@pytest.mark.parametrize("opts", [dict(C_init=8, split_factor=1.1, grow_cap=True), dict(C_init=8, var_factor=0.9, var_min=4)])
+def test_growing_cap_and_spread_trigger_in_the_all_layer_insert(opts):
+    """The options that bound or redirect the splitting travel through the one insert launch of all layers: the
+    clusters split during decode, the counts match the labels, and at budget 1 the logits equal dense attention."""
+    model = tiny_model(seed=14)
+    P, T = 260, 120
+    ids = torch.randint(0, 1000, (1, P + T + 1), generator=torch.Generator().manual_seed(10)).to(DEV)
+    dense, _ = run_decoder(model, ids, P, T, True, mode="dense")
+    got, dec = run_decoder(model, ids, P, T, True, mode="cluster", budget=1.0, C=128, window=8, delta=float("inf"),
+                           summary_bits=8, **opts)
+    torch.testing.assert_close(got, dense, rtol=2e-2, atol=5e-2)
+    assert dec.insert_all is not None and sum(i.splits for i in dec.attn) > 0
+    for i in dec.attn:
+        end = int(i.end_dev[0])
+        lab = i.labels.cpu()
+        counts = torch.stack([torch.bincount(lab[k, 1:end].long(), minlength=128) for k in range(i.H_kv)])
+        assert torch.equal(i.count.cpu(), counts.float()) and i.check_status() == 0
