@@ -229,6 +229,10 @@ class SphereIndexGraph:
             lim = lib().skv_insert_max_members()
             cap = float(self.cap.max()) if self.splitting else 0.0
             cap = max(cap, self.capk * self.capacity)
+            if self.split_factor > 0 and not self.cap_keys and (self.refit_every or self.reset_at):
+                # a cap derived from the clustered keys (split_factor * m / C_init) is raised by every refit of a
+                # longer context; a captured insert launch keeps the size given here, so size it for a full cache
+                cap = max(cap, self.split_factor * self.capacity / self.C_init)
             want = int(cap) + 2 if math.isfinite(cap) else 2
             if self.var_factor > 0 and not math.isfinite(cap):
                 want = lim                                  # split on spread alone: no bound on a cluster's size

@@ -485,12 +485,12 @@ extern "C" int64_t skv_attend_workspace_bytes(int heads, int G, int d, int split
     return part + tk;
 }
 
-// mode bit 0 of `dtype >> 8` forces the CUDA-core path for bf16 (cross-checks)
-extern "C" int skv_attend(const void *q, const void *K, const void *V, const int32_t *idx, const int32_t *cnt,
-                          const int32_t *n_dev, void *out, void *workspace, int32_t *status, int heads, int G, int d,
-                          int dtype, int64_t k_head_stride, int64_t k_row_stride, int64_t v_head_stride,
-                          int64_t v_row_stride, int64_t idx_stride, int rows_limit, int splits, float scale,
-                          void *stream) {
+// Host-side checks of skv_attend's arguments (no CUDA call): shared with skv_attend_static so that both
+// reject the same calls with the same codes before anything is enqueued.
+static int attend_check(const void *q, const void *K, const void *V, const int32_t *idx, const int32_t *cnt,
+                        const int32_t *n_dev, const void *out, const void *workspace, int heads, int G, int d, int dtype,
+                        int64_t k_head_stride, int64_t k_row_stride, int64_t v_head_stride, int64_t v_row_stride,
+                        int rows_limit, int splits) {
     const int base = dtype & 0xff;
     const bool force_simple = (dtype >> 8) & 1;
     if (!q || !K || !V || !out || !workspace) return SKV_E_NULL;
@@ -504,6 +504,20 @@ extern "C" int skv_attend(const void *q, const void *K, const void *V, const int
     if ((k_row_stride * esz) % 16 || (v_row_stride * esz) % 16 || (k_head_stride * esz) % 16 ||
         (v_head_stride * esz) % 16 || k_row_stride < d || v_row_stride < d)
         return SKV_E_ALIGN;
+    return SKV_OK;
+}
+
+// mode bit 0 of `dtype >> 8` forces the CUDA-core path for bf16 (cross-checks)
+extern "C" int skv_attend(const void *q, const void *K, const void *V, const int32_t *idx, const int32_t *cnt,
+                          const int32_t *n_dev, void *out, void *workspace, int32_t *status, int heads, int G, int d,
+                          int dtype, int64_t k_head_stride, int64_t k_row_stride, int64_t v_head_stride,
+                          int64_t v_row_stride, int64_t idx_stride, int rows_limit, int splits, float scale,
+                          void *stream) {
+    const int base = dtype & 0xff;
+    const bool force_simple = (dtype >> 8) & 1;
+    const int rc = attend_check(q, K, V, idx, cnt, n_dev, out, workspace, heads, G, d, dtype, k_head_stride,
+                                k_row_stride, v_head_stride, v_row_stride, rows_limit, splits);
+    if (rc) return rc;
     AttendParams p;
     p.q = q; p.K = K; p.V = V; p.idx = idx; p.cnt = cnt; p.n_dev = n_dev; p.out = out; p.status = status;
     p.part = static_cast<float *>(workspace);
@@ -592,11 +606,16 @@ extern "C" int skv_attend_static(const void *q, const void *K, const void *V, co
                                  int64_t k_head_stride, int64_t k_row_stride, int64_t v_head_stride,
                                  int64_t v_row_stride, int64_t idx_stride, int rows_limit, int splits, float scale,
                                  void *stream) {
+    // the same argument checks as skv_attend, ahead of every CUDA call (any aligned non-null pointer stands in for
+    // the workspace, which is the library's own array here)
+    int rc = attend_check(q, K, V, idx, cnt, n_dev, out, q, heads, G, d, dtype, k_head_stride, k_row_stride,
+                          v_head_stride, v_row_stride, rows_limit, splits);
+    if (rc) return rc;
     const int64_t need = skv_attend_workspace_bytes(heads, G, d, splits);
     if (need < 0) return (int)need;
     if (need > (int64_t)SKV_STATIC_SCRATCH_BYTES) return SKV_E_TOO_LARGE;
     void *scratch = nullptr;
-    int rc = static_scratch(&scratch);
+    rc = static_scratch(&scratch);
     if (rc) return rc;
     // Earlier calls with other shapes left their partials here.  Only the ticket words have to start at
     // zero (partials are always written before they are read); they sit at the end of the layout.

@@ -495,6 +495,14 @@ __global__ void __launch_bounds__(256) partition_kernel(const FitView v, int kwa
         if (lane == 0) ired[0] = bi;
     }
     __syncthreads();
+    if ((unsigned)ired[0] >= (unsigned)cnt) {
+        // every similarity is NaN (a member with an Inf or NaN component): no farthest member, no split
+        if (tid == 0) {
+            v.extra[(int64_t)e * C + j] = 0;
+            if (v.st.status) atomicOr(v.st.status + h, SKV_ST_BAD_INDEX);
+        }
+        return;
+    }
     if (tid < HEAD_DIM) sb[tid] = X[(int64_t)mem[ired[0]] * HEAD_DIM + tid];
     __syncthreads();
     for (int it = 0; it <= 4; ++it) {

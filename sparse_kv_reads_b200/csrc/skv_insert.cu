@@ -129,6 +129,10 @@ __device__ bool split_cluster(const InsertParams &p, int e, const T *Kh, const f
     }
     __syncthreads();
     const int far = ired[0];
+    if ((unsigned)far >= (unsigned)m) {                   // NaN similarities (a non-finite member): leave the cluster whole
+        if (tid == 0 && p.st.status) atomicOr(p.st.status + e, SKV_ST_BAD_INDEX);
+        return false;
+    }
     if (tid < HEAD_DIM) sb[tid] = sm.U[far * HEAD_DIM + tid];
     __syncthreads();
     // 4. 2-means: four updates, then the final sides with the projections
@@ -266,7 +270,7 @@ __global__ void __launch_bounds__(INS_THREADS) insert_kernel(const InsertParams 
 
     const int n = p.n_dev[0];
     const int old_end = p.st.end[e];
-    int n_act = p.st.n_c[e];
+    int n_act = min(p.st.n_c[e], C);                      // a corrupt count must not index past the slots
     int new_end = max(max(n - p.window, 1), old_end);
     new_end = min(new_end, p.st.capacity);
     if (n_act <= 0) new_end = old_end;                    // nothing fitted yet: the host builds first
@@ -335,6 +339,16 @@ __global__ void __launch_bounds__(INS_THREADS) insert_kernel(const InsertParams 
         }
         __syncthreads();
         const int bi = s_dec[0];
+        if ((unsigned)bi >= (unsigned)n_act) {
+            // A key with an Inf or NaN component makes every dot product NaN, no slot beats the sentinel, and
+            // there is no nearest cluster: the position joins the always-read rows instead, and the head is flagged.
+            if (tid == 0) {
+                lab[pos] = (int16_t)C;
+                if (p.st.status) atomicOr(p.st.status + e, SKV_ST_BAD_INDEX);
+            }
+            __syncthreads();
+            continue;
+        }
         const int64_t row = (int64_t)e * C + bi;
         // fold the key into its cluster's summary
         float sd = 0.f;

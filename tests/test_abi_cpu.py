@@ -78,6 +78,29 @@ def test_attend_rejects_bad_arguments(L):
     assert L.skv_attend_workspace_bytes(8, 2, 64, 37) == -5
 
 
+def test_attend_static_rejects_the_same_calls_before_any_cuda_call(L):
+    """The no-allocation entry point validates like skv_attend and checks its size limit on the host: on a
+    machine without a GPU every rejected call returns its argument code, never SKV_E_CUDA."""
+    ok = 0x1000
+    args = dict(q=ok, K=ok, V=ok, idx=ok, cnt=ok, n_dev=None, out=ok, status=None, heads=2, G=2, d=128, dtype=0,
+                ksh=128 * 64, ksr=128, vsh=128 * 64, vsr=128, istr=64, lim=64, splits=4)
+
+    def call(**over):
+        a = {**args, **over}
+        return L.skv_attend_static(a["q"], a["K"], a["V"], a["idx"], a["cnt"], a["n_dev"], a["out"], a["status"],
+                                   a["heads"], a["G"], a["d"], a["dtype"], a["ksh"], a["ksr"], a["vsh"], a["vsr"],
+                                   a["istr"], a["lim"], a["splits"], 0.1, None)
+
+    assert call(q=None) == -1 and call(cnt=None) == -1 and call(idx=None, n_dev=None) == -1
+    assert call(d=64) == -2 and call(G=17) == -2
+    assert call(dtype=7) == -3
+    assert call(K=0x1008) == -4 and call(ksr=100) == -4
+    assert call(heads=0) == -5 and call(splits=0) == -5
+    assert call(heads=4096, G=8, splits=64) == -8
+    assert L.skv_attend_workspace_bytes(4096, 8, 128, 64) > 8 * 1024 * 1024
+    assert L.skv_error_string(-8).decode().startswith("request exceeds")
+
+
 def test_state_calls_reject_bad_arguments(L):
     ok = 0x1000
     st = fake_state()

@@ -58,12 +58,3 @@ def test_static_scratch_entry_point_matches_the_ordinary_one_twice_in_a_row():
         assert torch.isfinite(got.float()).all()
         assert float((got.double() - want.double()).abs().max()) <= 1e-2
         assert float((got.double() - ref).abs().max()) <= 1e-2
-
-
-def test_static_scratch_entry_point_rejects_what_does_not_fit():
-    L = lib()
-    ok = 0x1000
-    big = L.skv_attend_static(ok, ok, ok, ok, ok, None, ok, None, 4096, 8, 128, 0, 128 * 64, 128, 128 * 64, 128, 64, 64,
-                              64, 0.1, None)
-    assert big == -8 and L.skv_attend_workspace_bytes(4096, 8, 128, 64) > 8 * 1024 * 1024
-    assert L.skv_error_string(-8).decode().startswith("request exceeds")
