@@ -6,7 +6,9 @@ One "step" is one decode step of the whole model (every layer's insert / select 
 graph).  Default workload: Qwen3-0.6B architecture, random weights, bf16, batch 1, a 32,768-token random
 prompt, 20 % budget, 256 clusters per KV head fitted at the prompt, cap 64.  Prints one JSON line.
 With N > 1 (launched through torch.distributed.run) the KV heads, MLP columns and vocabulary are
-sharded over the ranks; the attention needs no communication, NCCL carries the o_proj / MLP all-reduces.
+sharded over the ranks; the attention needs no communication.  The sums after the row-parallel o_proj / down
+products travel through peer memory inside the products themselves for up to 8 sequences (NCCL all-reduces
+beyond that); NCCL gathers the vocabulary-parallel logits.
 """
 
 from __future__ import annotations

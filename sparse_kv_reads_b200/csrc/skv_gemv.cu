@@ -51,31 +51,38 @@ __device__ __forceinline__ float bf16r(float x) { return __bfloat162float(__floa
 
 constexpr int WAIT_KPOLLS_DEFAULT = 8192;   // x 1024 polls of a little under a microsecond each: about five seconds
 
-// Every exchanged value travels as one aligned 8-byte store {float bits, epoch}: the epoch names the decode step
-// (the buffer's tick) and the exchange within it, so a reader that finds the epoch it expects has the value too -
-// no fence, no separate flag, one NVLink flight.
+// Every exchanged value travels as ONE 64-bit word {float bits, epoch}, stored and loaded as a single 64-bit
+// access: the memory model makes each such access single-copy atomic, so value and epoch cannot be seen apart (a
+// vector access of two 32-bit halves would formally be two accesses in no given order).  The epoch names the
+// decode step (the buffer's tick) and the exchange within it, so a reader that finds the epoch it expects has the
+// value too - no fence, no separate flag, one NVLink flight.
 __device__ __forceinline__ uint32_t epoch_of(const uint32_t *tick, int seq) { return tick[0] * 256u + (uint32_t)seq + 1u; }
 
 __device__ __forceinline__ void store_pair(uint2 *dst, float v, uint32_t epoch) {
-    asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1, %2};" ::"l"(dst), "r"(__float_as_uint(v)), "r"(epoch) : "memory");
+    const unsigned long long w = (unsigned long long)__float_as_uint(v) | ((unsigned long long)epoch << 32);
+    asm volatile("st.relaxed.sys.global.b64 [%0], %1;" ::"l"(dst), "l"(w) : "memory");
 }
 
-// Eight consecutive partial sums of one rank (64 bytes = four 16-byte loads of two pairs each), polled until
-// all eight carry `epoch`; bounded: on expiry *status gets SKV_ST_WAIT_TIMEOUT and whatever is there is used.
+// Eight consecutive partial sums of one rank (64 bytes = four 16-byte loads of two 64-bit words each), polled
+// until all eight carry `epoch`; bounded: on expiry *status gets SKV_ST_WAIT_TIMEOUT and whatever is there is
+// used.  A wait that does not succeed at once looks at the status word first: once any wait of this GPU has
+// given up (the word is sticky until the host clears it), later waits give up after a single look instead of
+// each spending the full limit, so a lost peer costs one limit per step and not one per polled element.
 __device__ __forceinline__ void load_pairs8(const uint2 *src, uint32_t epoch, int32_t *status, int limit,
                                             float (&out)[8]) {
-    uint4 q[4];
+    unsigned long long q[8];
     int it = 0;
     for (;;) {
 #pragma unroll
         for (int i = 0; i < 4; ++i)
-            asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];"
-                         : "=r"(q[i].x), "=r"(q[i].y), "=r"(q[i].z), "=r"(q[i].w)
+            asm volatile("ld.relaxed.sys.global.v2.b64 {%0, %1}, [%2];"
+                         : "=l"(q[2 * i]), "=l"(q[2 * i + 1])
                          : "l"(reinterpret_cast<const uint4 *>(src) + i) : "memory");
         bool ok = true;
 #pragma unroll
-        for (int i = 0; i < 4; ++i) ok = ok && q[i].y == epoch && q[i].w == epoch;
+        for (int i = 0; i < 8; ++i) ok = ok && (uint32_t)(q[i] >> 32) == epoch;
         if (ok) break;
+        if (it == 0 && status && (*reinterpret_cast<volatile int32_t *>(status) & SKV_ST_WAIT_TIMEOUT)) break;
         if (++it >= limit) {
             if (status) atomicOr(status, SKV_ST_WAIT_TIMEOUT);
             break;
@@ -83,10 +90,7 @@ __device__ __forceinline__ void load_pairs8(const uint2 *src, uint32_t epoch, in
         __nanosleep(40);
     }
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        out[2 * i] = __uint_as_float(q[i].x);
-        out[2 * i + 1] = __uint_as_float(q[i].z);
-    }
+    for (int i = 0; i < 8; ++i) out[i] = __uint_as_float((uint32_t)q[i]);
 }
 
 // One output value: to y, or as a float partial into slot/rank of every GPU's buffer.

@@ -190,5 +190,19 @@ def test_wait_for_a_rank_that_never_delivers_gives_up_and_reports():
     assert ex[0].status() & ST_WAIT_TIMEOUT
     assert ex[1].status() == 0
     assert float(torch.ones(4, device=DEV).sum()) == 4.0      # the device still answers
+    # once a wait has given up, later waits on the same GPU look once and move on: a consumer that polls every
+    # element of the missing rank (a product with the sum folded in, then another reduce) ends in milliseconds,
+    # not in one full limit per polled element
+    import time
+    gw = torch.ones(N, dtype=torch.bfloat16, device=DEV)
+    h = torch.zeros(B, N, dtype=torch.bfloat16, device=DEV)
+    y = torch.empty(B, 64, dtype=torch.bfloat16, device=DEV)
+    W2 = torch.randn(64, N, device=DEV).to(torch.bfloat16)
+    t0 = time.perf_counter()
+    check(L.skv_gemv_tp(W2.data_ptr(), 64, N, y.data_ptr(), B, 3, None, h.data_ptr(), gw.data_ptr(), None, 1e-6,
+                        ex[0].ref(), 0, None, 0, stream()), "skv_gemv_tp")
+    check(L.skv_comm_reduce(ex[0].ref(), 0, delta.data_ptr(), B, N, stream()), "skv_comm_reduce")
+    torch.cuda.synchronize()
+    assert time.perf_counter() - t0 < 0.1
     for e in ex:
         e.close()

@@ -5,6 +5,7 @@ clustering cannot matter.  One process per GPU, rendezvous on 127.0.0.1."""
 from __future__ import annotations
 
 import os
+import socket
 
 import pytest
 import torch
@@ -39,7 +40,12 @@ def _rank_main(rank: int, world: int, port: int, out_path: str) -> None:
             dec.capture()
             outs = [dec.step(ids[:, t:t + 1], t)[:, -1].float().clone() for t in range(P, P + T)]
         status = dec._peer.status() if dec._peer is not None else 0
-        return torch.stack(outs, 1), status, dec._peer is not None
+        used = dec._peer is not None
+        if used:                                      # unmap the other rank's buffer and free this rank's
+            torch.cuda.synchronize()
+            dist.barrier()
+            dec._peer.close()
+        return torch.stack(outs, 1), status, used
 
     a, status, used = run(True)
     b, _, _ = run(False)
@@ -55,12 +61,20 @@ def test_peer_memory_sums_match_nccl_all_reduce(tmp_path):
     import torch.multiprocessing as mp
     out_path = str(tmp_path / "tp.pt")
     ctx = mp.get_context("spawn")
-    procs = [ctx.Process(target=_rank_main, args=(r, 2, 29541, out_path)) for r in range(2)]
+    with socket.socket() as sock:                 # a port nobody holds right now
+        sock.bind(("127.0.0.1", 0))
+        port = sock.getsockname()[1]
+    procs = [ctx.Process(target=_rank_main, args=(r, 2, port, out_path)) for r in range(2)]
     for p in procs:
         p.start()
     for p in procs:
         p.join(timeout=300)
-    assert all(p.exitcode == 0 for p in procs), [p.exitcode for p in procs]
+    codes = [p.exitcode for p in procs]
+    for p in procs:                               # a rank still running must not outlive the test on a shared box
+        if p.exitcode is None:
+            p.kill()
+            p.join()
+    assert all(c == 0 for c in codes), codes
     got = torch.load(out_path)
     assert got["used"] and got["status"] == 0
     torch.testing.assert_close(got["peer"], got["nccl"], rtol=3e-2, atol=6e-2)
