@@ -181,24 +181,26 @@ class ClusterOracle:
             self.dir8.copy_(to_int8_direction(self.sum_dir))
             self.cent8.copy_(to_int8_direction(self.cent))
 
-    def nearest(self, Kr: torch.Tensor, heads: torch.Tensor):
+    def nearest(self, Kr: torch.Tensor, heads: torch.Tensor, int8: bool = False):
         """Unit directions, lengths and nearest active centroid of centred keys ``Kr [len(heads), m, d]``
-        (sphere_gpu.py:168-177; with 8-bit summaries the un-normalised int8 centroids are searched,
-        sphere_fused.py:189-199)."""
+        (sphere_gpu.py:168-177).  ``int8``: the per-step insert of the 8-bit mode searches the un-normalised
+        int8 centroids (sphere_fused.py:189-199, ``_dirs_arg`` :384-389); the prompt fit and the recentring
+        rebuild are the float32 host path in both modes (``_build`` -> ``_bin``, sphere_fused.py:407-409), which
+        the reference pins with "the host fit does not depend on the copies" (tests/test_quant8.py:49)."""
         mag = Kr.norm(dim=-1)
         Kn = Kr / mag.clamp_min(1e-12).unsqueeze(-1)
         used = int(self.n_c[heads].max())
         spare = torch.arange(used).unsqueeze(0) >= self.n_c[heads].unsqueeze(1)
-        table = self.cent if self.cent8 is None else self.cent8.float()
+        table = self.cent8.float() if int8 and self.cent8 is not None else self.cent
         m = Kr.shape[1]
         lab = torch.cat([torch.einsum("hmd,hcd->hmc", Kn[:, i:i + 4096], table[heads, :used])
                          .masked_fill(spare.unsqueeze(1), -math.inf).argmax(-1)
                          for i in range(0, m, 4096)], dim=1) if m else torch.zeros(len(heads), 0, dtype=torch.long)
         return Kn, mag, lab
 
-    def _fold(self, Kr: torch.Tensor, heads: torch.Tensor) -> torch.Tensor:
+    def _fold(self, Kr: torch.Tensor, heads: torch.Tensor, int8: bool = False) -> torch.Tensor:
         """Assign centred keys and add them to their clusters' summaries (sphere_gpu.py:166-185)."""
-        Kn, mag, lab = self.nearest(Kr, heads)
+        Kn, mag, lab = self.nearest(Kr, heads, int8)
         flat = (lab + heads.unsqueeze(1) * self.C).reshape(-1)
         self.sum_dir.view(-1, self.d).index_add_(0, flat, Kn.reshape(-1, self.d))
         self.mmax.view(-1).scatter_reduce_(0, flat, mag.reshape(-1), reduce="amax")
@@ -376,7 +378,7 @@ class ClusterOracle:
         if new_end > self.end:
             Kn = K[:, self.end:new_end].float()
             self.ksum += Kn.sum(1)
-            lab = self._fold(Kn - self.mu_ref.unsqueeze(1), heads)
+            lab = self._fold(Kn - self.mu_ref.unsqueeze(1), heads, int8=True)
             self.labels[:, self.end:new_end] = lab.to(torch.int16)
             self.end = new_end
             if self.dir8 is not None:                               # sphere_fused.py:203-205

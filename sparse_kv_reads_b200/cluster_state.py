@@ -620,6 +620,8 @@ class SphereIndexGraph:
         if not self.initialized:
             raise ValueError("nothing to save before the first observe()/prepare()")
         self._host_end()
+        if self.end > 1:                                    # graph replays advance the device's end, not the host's n
+            self.n = max(self.n, self.end + self.window)
         arrays = {name: getattr(self, name).detach().cpu().clone() for name in _FIELDS
                   if getattr(self, name, None) is not None}
         return {"arrays": arrays, "host": {k: getattr(self, k) for k in self._HOST_FIELDS},

@@ -154,6 +154,32 @@ class GraphDecoder:
         if self.fused_insert:
             self.insert_all = AllLayerInsert(self.attn, [self._heads(k) for k in self.cache.k[:len(self.attn)]])
 
+    # ---- checkpoint / resume -----------------------------------------------------------------------
+    def state_dict(self) -> dict:
+        """The cluster state of every layer (device arrays copied to the CPU, host counters) and the number of
+        cached positions it describes.  Together with the KV cache itself (kept by the caller) this is all a
+        later process needs to go on decoding as if it had never stopped.  Synchronises."""
+        if self.mode != "cluster":
+            return {"n": self.cache.cur_len, "layers": []}
+        return {"n": self.cache.cur_len, "layers": [a.state_dict() for a in self.attn]}
+
+    def load_state_dict(self, sd: dict) -> None:
+        """Restore what ``state_dict`` saved, in place of ``prepare``: no fit runs.  The cache this decoder was
+        built on must already hold the ``sd["n"]`` positions the state describes; call ``capture`` afterwards."""
+        n = int(sd["n"])
+        self.cache.cur_len = n
+        if self.mode != "cluster":
+            return
+        if len(sd["layers"]) != len(self.attn):
+            raise ValueError("the saved state has a different number of layers")
+        dev = self.tok.device
+        for a, one in zip(self.attn, sd["layers"]):
+            a.load_state_dict(one, dev)
+        for i, a in enumerate(self.attn):
+            a.prepare(self._heads(self.cache.k[i]), n, self.B * self.H, fitted=True)
+        if self.fused_insert:
+            self.insert_all = AllLayerInsert(self.attn, [self._heads(k) for k in self.cache.k[:len(self.attn)]])
+
     def _body(self) -> torch.Tensor:
         if self.fused_dense:
             return self._body_fused()

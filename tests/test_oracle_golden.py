@@ -179,3 +179,15 @@ def test_8bit_mode_keeps_invariants_and_mostly_agrees():
     assert torch.equal(b.dir8, oc.to_int8_direction(b.sum_dir))
     assert (a.labels[:, :a.end] == b.labels[:, :b.end]).float().mean() > 0.9
     assert int(b.dir8.abs().max()) <= 127
+
+
+def test_8bit_mode_fits_like_the_float_mode():
+    """The prompt fit and its binning run on the float32 centroids in both modes ("the host fit does not depend
+    on the copies", the reference's tests/test_quant8.py:49): only the per-step insert searches the int8 copies."""
+    K, V = oc.clustered_keys(2, 900, 128, seed=6)
+    kw = dict(C=128, C_init=16, cap_keys=24.0, window=16, delta=math.inf, capacity=900)
+    a, b = oc.ClusterOracle(**kw, summary_bits=32), oc.ClusterOracle(**kw, summary_bits=8)
+    a.observe(K, 800)
+    b.observe(K, 800)
+    assert torch.equal(a.labels, b.labels) and torch.equal(a.n_c, b.n_c) and torch.equal(a.sum_dir, b.sum_dir)
+    assert torch.equal(b.cent8, oc.to_int8_direction(b.cent))
