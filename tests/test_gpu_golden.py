@@ -62,29 +62,16 @@ def test_cuda_stream_against_the_reference_golden_vectors(golden_small, golden_c
             for grp in ("max", "max_rel"):                  # the other shared rankings (exact ties may fall either way)
                 _, wg = ix.labels_and_weights(Q[t].to(DEV), n=n, budget=c["budget"], group=grp)
                 boundary = max(boundary, int((wg.cpu().to(torch.uint8) != p["w_" + grp]).sum(1).max()))
-            assert case == "small_drift" or int((ix.n_c.cpu() - p["n_c"]).abs().max()) <= 3
+            assert int((ix.n_c.cpu() - p["n_c"]).abs().max()) <= 3
     fin = g["final"]
     same = (ix.labels.cpu()[:, :n_end] == fin["labels"]).float().mean().item()
-    if case == "small_drift":
-        # Recentring with splitting: the reference's PyTorch class divides a cluster that the rebinning left over
-        # its cap when it next receives a key, as often as needed; the kernels divide every such cluster at the
-        # rebuild itself.  Same rule, other moment, so the slot numbers part ways after the first recentring and
-        # the bar is on what both must share: as many recentrings, clusters under the cap, counts that match the
-        # labels, selections that cover the budget.
-        print(f"GOLDEN small_drift labels={same:.4f} rebuilds={ix.rebuilds}/{fin['rebuilds']} "
-              f"splits={ix.splits}/{fin['splits']} boundary={boundary}")
-        assert abs(ix.rebuilds - fin["rebuilds"]) <= max(2, 0.1 * fin["rebuilds"]) and fin["rebuilds"] > 0
-        end = ix.end
-        lab = ix.labels.cpu()
-        counts = torch.stack([torch.bincount(lab[i, 1:end].long(), minlength=c["C"]) for i in range(c["h"])])
-        assert torch.equal(ix.count.cpu(), counts.float())
-        assert torch.all(ix.count.cpu() <= ix.cap.cpu().unsqueeze(1))
-        assert ix.check_status() & ~ST_NO_SLOT == 0
-        return
     assert same >= 0.999, same
     assert boundary <= 2 and worst <= 1e-5, (boundary, worst)
     assert abs(ix.splits - fin["splits"]) <= max(2, 0.02 * fin["splits"])
     assert ix.resets == fin["resets"]
+    assert abs(ix.rebuilds - fin["rebuilds"]) <= max(2, 0.05 * fin["rebuilds"])
+    if case == "small_drift":
+        assert fin["rebuilds"] > 0 and ix.rebuilds > 0
     # a head whose refit filled every slot may meet a cluster over the cap with no slot left: that is reported
     allowed = ST_NO_SLOT if c.get("reset_at") else 0
     assert ix.check_status() & ~allowed == 0

@@ -176,7 +176,8 @@ def test_golden_streams_in_8_bit_mode_follow_the_oracle(golden_small, case):
     assert same >= 0.999, same
     assert int((ix.n_c.cpu() - st.n_c).abs().max()) <= 3 and boundary <= 2
     assert int((ix.dir8.cpu().int() - st.dir8.int()).abs().max()) <= (1 if same == 1.0 else 127)
-    assert ix.splits > 0 and ix.check_status() == 0
+    assert abs(ix.splits - st.splits) <= max(2, 0.02 * st.splits) and ix.check_status() == 0
+    assert case != "small_cap" or ix.splits > 0
 
 
 # ---- refit between replays ------------------------------------------------------------------------
