@@ -216,6 +216,32 @@ int skv_attend_labels(const void *q, const void *K, const void *V, const int16_t
                       int64_t k_head_stride, int64_t k_row_stride, int64_t v_head_stride, int64_t v_row_stride,
                       int splits, float scale, void *stream);
 
+/* Selection and attention of one decode step in ONE launch, for launches with few heads (8 to about 36 on a
+ * B200), where two launches and their hand-offs through global memory cost more than the bytes they move.
+ * A head is served by `clusters` thread-block clusters of 8 CTAs: each CTA scores an eighth of the head's
+ * clusters and shares the scores with its cluster through distributed shared memory, every CTA then derives
+ * the selection for itself (the shared score and threshold rule of skv_select, group SKV_GROUP_SUM_SHARE),
+ * attends over its range of positions (rows straight from the labels, as skv_attend_labels) and the cluster's
+ * first CTA merges its 8 partials; only one partial per cluster passes through the workspace.
+ * Replaces SphereIndexGraph.step's launches after the insert - _score_kernel, _pick_dev_kernel,
+ * _compact_dev_kernel, _list_kernel, _merge_kernel (ssa/kernels/graph_kernels.py:229-244) - for bf16 caches,
+ * 8-bit summaries, G <= 8, 64 <= C <= 4096.
+ *   skv_step_clusters        clusters per head to launch with on the current device (1..8), or 0 when this
+ *                            shape is better served by skv_select + skv_attend_labels (many heads, other modes)
+ *   skv_step_workspace_bytes bytes of `workspace` (zero-initialised once by the caller)
+ *   q          [heads*G, d] bf16, or null with `rope` (the queries are then computed from the raw projection
+ *              as in skv_select; the CTA that reads the new token's position writes its K and V rows)
+ *   w, selbits optional outputs as in skv_select;  cnt [heads] receives the rows read per head
+ *   out        [heads*G, d] bf16 */
+int skv_step_clusters(int heads, int G, int C, int summary_bits);
+int64_t skv_step_workspace_bytes(int heads, int G, int clusters);
+int skv_step(const skv_state *st, const void *q, int G, const int32_t *n_dev, const void *K, const void *V,
+             int64_t k_head_stride, int64_t k_row_stride, int64_t v_head_stride, int64_t v_row_stride,
+             float *w, uint32_t *selbits, int32_t *cnt, void *out, void *workspace, int clusters,
+             float scale, const skv_rope *rope, void *stream);
+/* Tuning aid: device uint64 [CTAs][8] phase stamps of skv_step's kernel (builds with -DSKV_STEP_PROBE only). */
+void skv_debug_step_probe(void *dev_ptr);
+
 /* Insert the keys that left the recent window since the last call (positions [end, max(1, n-window)))
  * into their nearest clusters, one CTA per entry of `st` (all layers of a model in one launch),
  * splitting a cluster in two inside the kernel when it passes its head's cap; then update end, need,

@@ -13,6 +13,7 @@ from __future__ import annotations
 
 import ctypes
 import math
+import os
 
 import torch
 
@@ -222,6 +223,7 @@ class SphereIndexGraph:
         self._attn_kept, self._sel_kept = {}, {}
         self._sel_ws = None
         self._max_members = None
+        self._step_ncl, self._step_ws = {}, {}
 
     def _members_limit(self) -> int:
         """Largest cluster the in-kernel split has to stage: one key over the largest cap."""
@@ -516,6 +518,34 @@ class SphereIndexGraph:
                                       stream_ptr(q.device)), "skv_attend_labels")
         return self.out
 
+    def _step_clusters(self, G: int) -> int:
+        """Thread-block clusters per head for the one-launch step (``skv_step``), or 0 when the shape is served by
+        the selection and attention launches instead (many heads, float32 summaries, large groups)."""
+        got = self._step_ncl.get(G)
+        if got is None:
+            got = 0
+            if self.summary_bits == 8 and os.environ.get("SKV_ONE_LAUNCH_STEP", "1") != "0":
+                got = int(lib().skv_step_clusters(self.H_kv, G, self.C, self.summary_bits))
+            self._step_ncl[G] = got
+        return got
+
+    def _step_one_launch(self, q: torch.Tensor, K: torch.Tensor, V: torch.Tensor, n_dev: torch.Tensor, rope, ncl: int):
+        """Selection and attention in one launch (``skv_step``): fills ``wbuf``, ``selbits``, ``cnt`` and ``out``."""
+        H, d = q.shape
+        if not q.is_contiguous():
+            q = q.contiguous()
+        G = self._attend_buffers(q)
+        ws = self._step_ws.get(G)
+        if ws is None:
+            ws = self._step_ws[G] = torch.zeros(lib().skv_step_workspace_bytes(self.H_kv, G, ncl), dtype=torch.uint8,
+                                                device=q.device)
+        check(lib().skv_step(ctypes.byref(self._st), q.data_ptr(), G, n_dev.data_ptr(), K.data_ptr(), V.data_ptr(),
+                             K.stride(0), K.stride(1), V.stride(0), V.stride(1), self.wbuf.data_ptr(),
+                             self.selbits.data_ptr(), self.cnt.data_ptr(), self.out.data_ptr(), ws.data_ptr(), ncl,
+                             1.0 / math.sqrt(d), None if rope is None else ctypes.byref(rope), stream_ptr(q.device)),
+              "skv_step")
+        return self.out
+
     def _fused_rows(self, K: torch.Tensor) -> bool:
         """Whether the list-free attention applies (bf16 caches)."""
         return K.dtype == torch.bfloat16
@@ -552,6 +582,9 @@ class SphereIndexGraph:
         if self._fused_rows(K):
             self._select(q0, self._n_scalar, listed=False)
             self._attend_labels(q0, K, K, self._n_scalar)
+            ncl = self._step_clusters(G) if q0.dtype == torch.bfloat16 else 0
+            if ncl:                                          # configures the kernel ahead of any stream capture
+                self._step_one_launch(q0, K, K, self._n_scalar, None, ncl)
         self._members_limit()
         self._ktable(K)
         assert self.G == G
@@ -566,6 +599,9 @@ class SphereIndexGraph:
         if self._fused_rows(K):
             # rope (an ``SkvRope``): the selection launch computes q from the raw projection, stores it to ``q``
             # and writes the token's K/V rows, in place of a separate launch ahead of it
+            ncl = self._step_clusters(q.shape[0] // self.H_kv) if q.dtype == torch.bfloat16 else 0
+            if ncl:                                          # few heads: selection and attention in one launch
+                return self._step_one_launch(q, K, V, n_dev, rope, ncl)
             self._select(q, n_dev, listed=False, rope=rope)
             return self._attend_labels(q, K, V, n_dev)
         if rope is not None:

@@ -1,0 +1,161 @@
+// Top-budget selection over order-preserving keys, shared by the selection kernel and the one-launch decode step.
+#pragma once
+
+#include "skv_common.cuh"
+
+namespace skv {
+
+// Marks in sel[c] (c < n_c) the clusters taken in decreasing key (equal keys: lower slot first) until the member
+// counts ci[] of the taken ones reach `need`; the cluster that crosses `need` is taken.  Never sorts: it finds the
+// threshold key tau with  sum(count | key > tau) < need  and settles exact ties at tau in slot order.
+//   key[c]   order-preserving integer keys of the shared scores (float_key), c < n_c
+//   ci[c]    member counts; clusters with ci[c] <= 0 are never taken
+//   sel      bytes, zeroed by the caller for c < n_c
+//   hist     512 ints of shared scratch, ired 40 ints
+//   kmin, kmax, nvalid   this THREAD's partial range and count of the keys of clusters with members (the block
+//            reduction happens here); `active` false: nothing is taken (the reductions and barriers still run)
+// Block-wide: every thread of the NT-thread CTA calls it; sel is complete (and synchronised) on return.
+template <int NT>
+__device__ __forceinline__ void pick_by_threshold(const uint32_t *key, const int *ci, uint8_t *sel, int *hist,
+                                                  int *ired, int n_c, int need, bool active, uint32_t kmin,
+                                                  uint32_t kmax, int nvalid) {
+    constexpr int NW = NT / 32;
+    const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        kmin = min(kmin, __shfl_xor_sync(0xffffffffu, kmin, o));
+        kmax = max(kmax, __shfl_xor_sync(0xffffffffu, kmax, o));
+        nvalid += __shfl_xor_sync(0xffffffffu, nvalid, o);
+    }
+    if (lane == 0) { ired[8 + wid] = (int)kmin; ired[16 + wid] = (int)kmax; ired[24 + wid] = nvalid; }
+    __syncthreads();
+    if (active) {
+        // ---- threshold: the smallest key t with sum(count | key > t) < need.  The keys still in question are
+        // binned linearly over their range (256 bins, weighted by the clusters' counts); the bin in which the
+        // running count passes `need` becomes the new range, until at most 32 candidates are left, which a
+        // warp ranks against each other directly.  Scores crowd into a few octaves, so binning the range they
+        // span (instead of the keys' top bytes) usually needs a single pass.  Every warp scans the histogram
+        // for itself, so a pass costs two barriers.
+        kmin = 0xffffffffu; kmax = 0u; nvalid = 0;
+        for (int w = 0; w < NW; ++w) {
+            kmin = min(kmin, (uint32_t)ired[8 + w]);
+            kmax = max(kmax, (uint32_t)ired[16 + w]);
+            nvalid += ired[24 + w];
+        }
+        uint32_t lo = kmin, hi = kmax, tau = 0u;
+        int above = 0, cand = nvalid;
+        int *hw = hist, *hn = hist + 256;
+        for (int pass = 0; pass < 8 && cand > 32 && lo < hi; ++pass) {
+            for (int i = tid; i < 512; i += NT) hist[i] = 0;
+            __syncthreads();
+            const int shift = max(0, 24 - __clz(hi - lo));            // (hi - lo) >> shift <= 255
+            for (int c = tid; c < n_c; c += NT) {
+                const uint32_t k = key[c];
+                if (ci[c] > 0 && k >= lo && k <= hi) {
+                    const int bin = (int)((k - lo) >> shift);
+                    atomicAdd(&hw[bin], ci[c]);
+                    atomicAdd(&hn[bin], 1);
+                }
+            }
+            __syncthreads();
+            int loc[8], mine = 0;                     // lane owns bins [8*lane, 8*lane+8)
+#pragma unroll
+            for (int i = 0; i < 8; ++i) { loc[i] = hw[lane * 8 + i]; mine += loc[i]; }
+            int suf = mine;                           // inclusive suffix over lanes >= lane
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int t = __shfl_down_sync(0xffffffffu, suf, o);
+                if (lane + o < 32) suf += t;
+            }
+            int run = suf - mine;                     // counts in bins above this lane's range
+            int best = 256;                           // smallest bin b with above + count(bins > b) < need
+#pragma unroll
+            for (int i = 7; i >= 0; --i) {
+                if (above + run < need) best = lane * 8 + i;
+                run += loc[i];
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) best = min(best, __shfl_xor_sync(0xffffffffu, best, o));
+            best = min(best, 255);
+            int gt = 0;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) gt += (lane * 8 + i > best) ? loc[i] : 0;
+            gt = warp_sum_int(gt);
+            above += gt;
+            cand = hn[best];
+            const uint32_t nlo = lo + ((uint32_t)best << shift);
+            const uint32_t span = (1u << shift) - 1u;
+            hi = (hi - nlo > span) ? nlo + span : hi;
+            lo = nlo;
+            __syncthreads();                          // every warp has read the histogram before it is cleared
+        }
+        if (nvalid > 0 && lo >= hi) {
+            tau = lo;                                 // one key value left (possibly shared by several clusters)
+        } else if (nvalid > 0) {
+            // at most 32 candidates: list them, then every warp ranks them for itself
+            if (tid == 0) ired[1] = 0;
+            __syncthreads();
+            for (int c = tid; c < n_c; c += NT) {
+                const uint32_t k = key[c];
+                if (ci[c] > 0 && k >= lo && k <= hi) {
+                    const int j = atomicAdd(&ired[1], 1);
+                    if (j < 32) { hw[j] = (int)k; hn[j] = ci[c]; }
+                }
+            }
+            __syncthreads();
+            const int m = min(ired[1], 32);
+            const uint32_t kl = lane < m ? (uint32_t)hw[lane] : 0u;
+            const int nl = lane < m ? hn[lane] : 0;
+            int greater = 0;                          // members of candidates ranked ahead of this lane's
+            for (int j = 0; j < m; ++j) {
+                const uint32_t kj = __shfl_sync(0xffffffffu, kl, j);
+                const int nj = __shfl_sync(0xffffffffu, nl, j);
+                greater += kj > kl ? nj : 0;
+            }
+            uint32_t t = (lane < m && above + greater < need) ? kl : 0xffffffffu;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) t = min(t, __shfl_xor_sync(0xffffffffu, t, o));
+            tau = t == 0xffffffffu ? lo : t;
+            int gt = 0;
+            for (int j = 0; j < m; ++j) {
+                const uint32_t kj = __shfl_sync(0xffffffffu, kl, j);
+                const int nj = __shfl_sync(0xffffffffu, nl, j);
+                gt += kj > tau ? nj : 0;
+            }
+            above += gt;
+        }
+        int ties = 0;
+        for (int c = tid; c < n_c; c += NT) {
+            const uint32_t k = key[c];
+            sel[c] = k >= tau;                        // a lone cluster at the threshold is taken: above < need
+            ties += (k == tau);
+        }
+        ties = warp_sum_int(ties);
+        if (lane == 0) ired[2 + wid] = ties;
+        __syncthreads();
+        int t = 0;
+        for (int w = 0; w < NW; ++w) t += ired[2 + w];
+        if (t > 1 && wid == 0) {
+            // several clusters share the threshold key: slot order, each taken while the keys ranked before
+            // it stay under need
+            int running = above;
+            for (int base = 0; base < n_c; base += 32) {
+                const int c = base + lane;
+                const bool tie = c < n_c && key[c] == tau;
+                if (!__any_sync(0xffffffffu, tie)) continue;
+                const int mine = tie ? ci[c] : 0;
+                int inc = mine;
+#pragma unroll
+                for (int o = 1; o < 32; o <<= 1) {
+                    const int u = __shfl_up_sync(0xffffffffu, inc, o);
+                    if (lane >= o) inc += u;
+                }
+                if (tie) sel[c] = (running + inc - mine) < need;
+                running += __shfl_sync(0xffffffffu, inc, 31);
+            }
+        }
+        __syncthreads();
+    }
+}
+
+}  // namespace skv

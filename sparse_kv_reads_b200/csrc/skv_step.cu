@@ -1,0 +1,642 @@
+// Selection and attention of one decode step in ONE launch, for launches with few (sequence, KV head) pairs.
+//
+// With 8 to about 36 heads a step is a chain of latencies, not a stream: two launches, each with a hand-off
+// through global memory to the head's last CTA (the pick; the merge of the split partials).  Here a head is
+// served by thread-block clusters of 8 CTAs that talk through distributed shared memory instead:
+//   1. every CTA stages its eighth of the head's 8-bit cluster summaries (requested before the wait for the
+//      launch ahead), scores it on mma.sync f16 tiles and stores the scaled scores into the shared memory of
+//      all 8 CTAs of its cluster;
+//   2. after one cluster barrier every CTA holds all scores and derives the selection for itself - the same
+//      shared score (sum over the query heads of each head's softmax over the clusters) and the same
+//      threshold pick as the selection kernel - so no CTA waits for another one's pick;
+//   3. every CTA attends over its range of positions, rows taken straight from the labels;
+//   4. the 8 partials of a cluster meet in the shared memory of its first CTA, which merges them; only one
+//      partial per cluster (4 per head at 8 heads, none at 32 heads) goes through global memory and a ticket.
+// Remote shared memory is written with plain st.shared::cluster stores (this GPU's memory only, no multicast).
+// Every CTA of a cluster executes all three cluster barriers unconditionally; nothing spins.
+#include <cuda_fp16.h>
+
+#include "skv_attend_core.cuh"
+#include "skv_pick.cuh"
+#include "skv_rope.cuh"
+
+namespace skv {
+
+constexpr int STEP_THREADS = 128, STEP_WARPS = 4, STEP_CS = 8, STEP_LPT = 8, STEP_STAGES = 2;
+constexpr int STEP_SUB = STEP_THREADS * STEP_LPT;         // positions listed per pass
+constexpr int STEP_PART_LD = 132;                         // floats per partial row: 128 sums, max, sum, rows, unused
+
+struct StepParams {
+    skv_state st;
+    const void *q;             // [heads*G, 128] bf16 (unused with rope)
+    const void *K, *V;
+    const int32_t *n_dev;
+    void *out;
+    float *w;                  // [heads, C+1] or null
+    uint32_t *selbits;         // [heads, C/32+1] or null
+    int32_t *cnt;              // [heads] rows read
+    float *part;               // [heads, ncl, G, 132]
+    int32_t *ticket;           // [heads]
+    int G, ncl;
+    int64_t ksh, ksr, vsh, vsr;
+    float scale, scale_log2;
+    skv_rope rope;
+    unsigned long long *probe; // optional [CTAs][8] phase time stamps (probe builds only)
+};
+
+static unsigned long long *g_step_probe = nullptr;
+
+__device__ __forceinline__ void step_stamp(const StepParams &p, int slot) {
+#ifdef SKV_STEP_PROBE
+    if (p.probe && threadIdx.x == 0) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+        p.probe[(size_t)(blockIdx.y * gridDim.x + blockIdx.x) * 8 + slot] = t;
+    }
+#else
+    (void)p; (void)slot;
+#endif
+}
+
+// ---- thread-block cluster primitives ---------------------------------------------------------------------
+__device__ __forceinline__ unsigned cluster_rank() {
+    unsigned r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
+// shared::cluster address of `ptr` (a shared-memory pointer of this CTA) in the CTA of rank `rank`
+__device__ __forceinline__ uint32_t remote_addr(const void *ptr, unsigned rank) {
+    const uint32_t a = static_cast<uint32_t>(__cvta_generic_to_shared(ptr));
+    uint32_t out;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(out) : "r"(a), "r"(rank));
+    return out;
+}
+__device__ __forceinline__ void remote_store(uint32_t addr, float v) {
+    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
+}
+__device__ __forceinline__ void remote_store4(uint32_t addr, const float4 &v) {
+    asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w)
+                 : "memory");
+}
+
+__device__ __forceinline__ void step_mma_f16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+// two int8 (already biased by +128) -> packed fp16 pair of their signed values (exact)
+__device__ __forceinline__ uint32_t step_bytes_to_half2(uint32_t biased, uint32_t selector) {
+    uint32_t hh;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(hh) : "r"(biased), "r"(0x64646464u), "r"(selector));   // 1024 + u
+    const __half2 v = __hsub2(*reinterpret_cast<__half2 *>(&hh), __half2half2(__ushort_as_half((unsigned short)0x6480)));
+    return *reinterpret_cast<const uint32_t *>(&v);
+}
+__device__ __forceinline__ uint32_t step_pack_half2(float lo, float hi) {
+    const __half2 v = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t *>(&v);
+}
+
+// Reduce NV per-thread values over the 128-thread CTA; every thread gets the results.  red: [NV][4] floats.
+template <bool IS_MAX, int NV>
+__device__ __forceinline__ void step_reduce(float (&v)[NV], float *red) {
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+        for (int g = 0; g < NV; ++g) {
+            const float y = __shfl_xor_sync(0xffffffffu, v[g], o);
+            v[g] = IS_MAX ? fmaxf(v[g], y) : v[g] + y;
+        }
+    __syncthreads();                                   // red may still be read from an earlier reduction
+    if (lane == 0)
+#pragma unroll
+        for (int g = 0; g < NV; ++g) red[g * STEP_WARPS + wid] = v[g];
+    __syncthreads();
+#pragma unroll
+    for (int g = 0; g < NV; ++g) {
+        float r = red[g * STEP_WARPS];
+#pragma unroll
+        for (int w = 1; w < STEP_WARPS; ++w) r = IS_MAX ? fmaxf(r, red[g * STEP_WARPS + w]) : r + red[g * STEP_WARPS + w];
+        v[g] = r;
+    }
+}
+
+// QK-norm + rotary of KV head h's G query heads into sq (float values of the bf16 results) and sqb (bf16);
+// `store_q`: also to the caller's q buffer; `store_kv`: this CTA reads the new token's position, so it
+// writes the token's K and V rows itself before it gathers them.
+__device__ __forceinline__ void step_rope(const skv_rope &r, int h, bool store_q, bool store_kv, int G, float *sq,
+                                          __nv_bfloat16 *sqb) {
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    const int seq = h / r.H_kv, hk = h % r.H_kv, per_seq = r.H + 2 * r.H_kv;
+    const int64_t pos = r.pos[0];
+    const __nv_bfloat16 *row = static_cast<const __nv_bfloat16 *>(r.qkv) + (int64_t)seq * per_seq * HEAD_DIM;
+    const __nv_bfloat16 *cs = static_cast<const __nv_bfloat16 *>(r.cos_table) + pos * HEAD_DIM;
+    const __nv_bfloat16 *sn = static_cast<const __nv_bfloat16 *>(r.sin_table) + pos * HEAD_DIM;
+    const int jobs = G + (store_kv ? 2 : 0);
+    for (int j = wid; j < jobs; j += STEP_WARPS) {
+        if (j < G) {
+            const int qh = hk * G + j;
+            const float4 v = norm_rope_head(row + (int64_t)qh * HEAD_DIM, static_cast<const __nv_bfloat16 *>(r.q_norm_w),
+                                            cs, sn, r.eps, lane);
+            *reinterpret_cast<float4 *>(sq + j * HEAD_DIM + lane * 4) = v;
+            store_bf16x4(sqb + j * HEAD_DIM + lane * 4, v);
+            if (store_q)
+                store_bf16x4(static_cast<__nv_bfloat16 *>(r.q_out) + ((int64_t)seq * r.H + qh) * HEAD_DIM + lane * 4, v);
+        } else {
+            const int64_t at = seq * r.cache_batch_stride + hk * r.cache_head_stride + pos * r.cache_row_stride;
+            if (j == G) {
+                const float4 v = norm_rope_head(row + (int64_t)(r.H + hk) * HEAD_DIM,
+                                                static_cast<const __nv_bfloat16 *>(r.k_norm_w), cs, sn, r.eps, lane);
+                store_bf16x4(static_cast<__nv_bfloat16 *>(r.k_cache) + at + lane * 4, v);
+            } else {
+                const __nv_bfloat16 *src = row + (int64_t)(r.H + r.H_kv + hk) * HEAD_DIM + lane * 4;
+                *reinterpret_cast<uint2 *>(static_cast<__nv_bfloat16 *>(r.v_cache) + at + lane * 4) =
+                    *reinterpret_cast<const uint2 *>(src);
+            }
+        }
+    }
+}
+
+// Bytes of the selection's scratch, which shares the front of the dynamic shared memory with the gather rings.
+__host__ __device__ inline int step_per_max(int C) { return ((C / STEP_CS) + 7) & ~7; }
+__host__ __device__ inline size_t step_sel_bytes(int G, int C) {
+    return (size_t)step_per_max(C) * 128 + (size_t)G * C * 4 + (size_t)C * 4 + (size_t)step_per_max(C) * 8;
+}
+__host__ __device__ inline size_t step_front_bytes(int G, int C, int stages) {
+    const size_t ring = (size_t)STEP_WARPS * stages * 8192, sel = (step_sel_bytes(G, C) + 127) & ~size_t(127);
+    return ring > sel ? ring : sel;
+}
+__host__ __device__ inline size_t step_smem_bytes(int G, int C, int stages) {
+    size_t b = step_front_bytes(G, C, stages);
+    b += ((size_t)(C / 32 + 1) * 4 + 15) & ~size_t(15);       // selection bits
+    b += (size_t)G * HEAD_DIM * 4 + (size_t)G * HEAD_DIM * 2;  // query, float and bf16
+    b += (size_t)STEP_CS * G * STEP_PART_LD * 4;               // partials received by the cluster's first CTA
+    b += 512 * 4;                                              // histogram of the pick
+    return (b + 127) & ~size_t(127);
+}
+
+// Grid (8 * ncl, heads), clusters of 8 CTAs along x, 128 threads.
+template <int STAGES, int GP>
+__global__ void __launch_bounds__(STEP_THREADS, 2) step_kernel(const StepParams p) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    __shared__ uint32_t s_vmask[STEP_WARPS][STAGES];
+    __shared__ int s_flag;
+    __shared__ int s_scan[40];
+    __shared__ int ired[40];
+    __shared__ float fred[GP * STEP_WARPS];
+    __shared__ uint16_t s_rows[STEP_SUB];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int h = blockIdx.y, split = blockIdx.x, S = gridDim.x;
+    const unsigned rank = cluster_rank();
+    const int C = p.st.C, G = p.G;
+    cluster_arrive();                                      // barrier 0: "my shared memory exists"; waited for ahead of the first remote store
+    step_stamp(p, 0);
+
+    // ---- shared memory map ------------------------------------------------------------------------------
+    const int per_max = step_per_max(C);
+    unsigned char *sumst = smem;                                              // [per_max][128] this CTA's summaries
+    float *zall = reinterpret_cast<float *>(smem + (size_t)per_max * 128);    // [G][C] scaled scores of every cluster
+    int *cntv = reinterpret_cast<int *>(zall + (size_t)G * C);                // [C] member counts
+    float *smx = reinterpret_cast<float *>(cntv + C), *smn = smx + per_max;   // [per_max] key lengths of the slice
+    uint32_t *key = reinterpret_cast<uint32_t *>(smem);                       // [C], over sumst once it is scored
+    uint8_t *sel = reinterpret_cast<uint8_t *>(key + C);                      // [C + 1]
+    unsigned char *tail = smem + step_front_bytes(G, C, STAGES);
+    uint32_t *s_bits = reinterpret_cast<uint32_t *>(tail);
+    tail += ((size_t)(C / 32 + 1) * 4 + 15) & ~size_t(15);
+    float *sq = reinterpret_cast<float *>(tail);
+    tail += (size_t)G * HEAD_DIM * 4;
+    __nv_bfloat16 *sqb = reinterpret_cast<__nv_bfloat16 *>(tail);
+    tail += (size_t)G * HEAD_DIM * 2;
+    float *recv = reinterpret_cast<float *>(tail);                            // [8][G][132]
+    tail += (size_t)STEP_CS * G * STEP_PART_LD * 4;
+    int *hist = reinterpret_cast<int *>(tail);
+
+    // ---- what no kernel of this step writes is requested before the wait for the launch ahead -------------
+    const int n_c = min(max(p.st.n_c[h], 0), C);
+    const int end = p.st.end[h], need = p.st.need[h];
+    const bool active = end > 1 && need > 0 && n_c > 0;
+    const int per = (((n_c + STEP_CS - 1) / STEP_CS) + 7) & ~7;              // clusters scored per CTA
+    const int c_lo = min((int)rank * per, n_c), c_hi = min(c_lo + per, n_c), mine = active ? c_hi - c_lo : 0;
+    {
+        const int8_t *src = p.st.dir8 + ((int64_t)h * C + c_lo) * HEAD_DIM;
+        for (int i = tid; i < mine * 8; i += STEP_THREADS) {
+            const int c = i >> 3, k = i & 7;
+            cp_async16(sumst + c * 128 + ((k ^ (c & 7)) << 4), src + (int64_t)c * HEAD_DIM + k * 16, 16);
+        }
+        cp_async_commit();
+    }
+    const int n = min(max(p.n_dev[0], 0), p.st.capacity);
+    const int chunk = max(16, (((n + S - 1) / S + 15) >> 4) << 4);            // multiples of 16: aligned label loads
+    const int p0 = min(split * chunk, n), p1 = min(p0 + chunk, n);
+    const int16_t *lab = p.st.labels + (int64_t)h * p.st.capacity;
+    uint4 raw = make_uint4(0u, 0u, 0u, 0u);
+    if (p0 + tid * STEP_LPT < p1) raw = __ldg(reinterpret_cast<const uint4 *>(lab + p0 + tid * STEP_LPT));
+    {
+        const float *count = p.st.count + (int64_t)h * C;
+        for (int c = tid; c < C; c += STEP_THREADS) cntv[c] = c < n_c ? (int)count[c] : 0;
+        const float *mmax = p.st.mmax + (int64_t)h * C, *mmin = p.st.mmin + (int64_t)h * C;
+        for (int i = tid; i < mine; i += STEP_THREADS) {
+            smx[i] = mmax[c_lo + i];
+            smn[i] = mmin[c_lo + i];
+        }
+        // this CTA's stretch of the score table starts empty: slots past the head's last cluster stay -inf
+        if (mine > 0)
+            for (int i = tid; i < G * per; i += STEP_THREADS) zall[(i / per) * C + c_lo + (i % per)] = -INFINITY;
+    }
+    pdl_wait();                                            // the query comes from the launch ahead
+    pdl_trigger();
+    step_stamp(p, 1);
+    if (p.rope.qkv) {
+        const int64_t pos = p.rope.pos[0];
+        const int s_kv = (int)min((int64_t)(S - 1), max((int64_t)0, pos / chunk));
+        step_rope(p.rope, h, split == 0, split == s_kv, G, sq, sqb);
+    } else {
+        const __nv_bfloat16 *q = static_cast<const __nv_bfloat16 *>(p.q) + (int64_t)h * G * HEAD_DIM;
+        for (int i = tid; i < G * HEAD_DIM; i += STEP_THREADS) {
+            sqb[i] = q[i];
+            sq[i] = __bfloat162float(q[i]);
+        }
+    }
+    cp_async_wait<0>();
+    __syncthreads();
+
+    // ---- scores of this CTA's clusters: q . dir8 on f16 tiles, 8 clusters per warp and chain ---------------
+    if (mine > 0) {
+        const int nrow = lane >> 2, jq = lane & 3;
+        uint32_t qa[8][4];
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+            const float *q0 = sq + nrow * HEAD_DIM + 32 * jq + 4 * ks;
+            qa[ks][0] = nrow < G ? step_pack_half2(q0[0], q0[1]) : 0u;
+            qa[ks][2] = nrow < G ? step_pack_half2(q0[2], q0[3]) : 0u;
+            qa[ks][1] = qa[ks][3] = 0u;                                       // at most 8 query heads: rows 8..15 unused
+        }
+        for (int cb = warp * 8; cb < mine; cb += STEP_WARPS * 8) {
+            const int c = cb + nrow;
+            int4 ra = make_int4(0, 0, 0, 0), rb = ra;
+            if (c < mine) {
+                ra = *reinterpret_cast<const int4 *>(sumst + c * 128 + (((2 * jq) ^ (c & 7)) << 4));
+                rb = *reinterpret_cast<const int4 *>(sumst + c * 128 + (((2 * jq + 1) ^ (c & 7)) << 4));
+            }
+            const uint32_t wv[8] = {(uint32_t)ra.x, (uint32_t)ra.y, (uint32_t)ra.z, (uint32_t)ra.w,
+                                    (uint32_t)rb.x, (uint32_t)rb.y, (uint32_t)rb.z, (uint32_t)rb.w};
+            float acc[4] = {0.f, 0.f, 0.f, 0.f};
+            int n2i = 0;
+#pragma unroll
+            for (int ks = 0; ks < 8; ++ks) {
+                n2i = __dp4a((int)wv[ks], (int)wv[ks], n2i);
+                const uint32_t biased = wv[ks] ^ 0x80808080u;
+                step_mma_f16(acc, qa[ks], step_bytes_to_half2(biased, 0x4140u), step_bytes_to_half2(biased, 0x4342u));
+            }
+            n2i += __shfl_xor_sync(0xffffffffu, n2i, 1);
+            n2i += __shfl_xor_sync(0xffffffffu, n2i, 2);                      // |dir8|^2 of cluster cb + nrow
+            const int na = __shfl_sync(0xffffffffu, n2i, (2 * jq) * 4);
+            const int nb2 = __shfl_sync(0xffffffffu, n2i, (2 * jq + 1) * 4);
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                const int cl = cb + 2 * jq + i;
+                if (cl < mine && nrow < G) {
+                    const float inv = 1.0f / fmaxf(sqrtf((float)(i ? nb2 : na)), 1e-12f);
+                    const float pr = acc[i] * inv;
+                    float e = pr >= 0.f ? smx[cl] * pr : smn[cl] * pr;
+                    if (cntv[c_lo + cl] == 0) e = -INFINITY;
+                    zall[nrow * C + c_lo + cl] = e * p.scale;
+                }
+            }
+        }
+    }
+    __syncthreads();
+    step_stamp(p, 2);
+    cluster_wait();                                        // barrier 0: every CTA of the cluster is running
+    if (mine > 0) {
+        const int q4 = per >> 2;
+        for (int i = tid; i < G * q4; i += STEP_THREADS) {
+            const float *src = zall + (i / q4) * C + c_lo + 4 * (i % q4);
+            const float4 v = *reinterpret_cast<const float4 *>(src);
+#pragma unroll
+            for (unsigned dst = 0; dst < STEP_CS; ++dst)
+                if (dst != rank) remote_store4(remote_addr(src, dst), v);
+        }
+    }
+    cluster_arrive();                                      // barrier 1: all scores are everywhere
+    cluster_wait();
+    step_stamp(p, 3);
+
+    // ---- every CTA derives the selection for itself ---------------------------------------------------------
+    {
+        float zm[GP], tot[GP];
+#pragma unroll
+        for (int g = 0; g < GP; ++g) {
+            float m = -INFINITY;
+            if (active && g < G)
+                for (int c = tid; c < n_c; c += STEP_THREADS) m = fmaxf(m, zall[g * C + c]);
+            zm[g] = m;
+        }
+        step_reduce<true, GP>(zm, fred);
+#pragma unroll
+        for (int g = 0; g < GP; ++g) {
+            float s = 0.f;
+            if (active && g < G)
+                for (int c = tid; c < n_c; c += STEP_THREADS) {
+                    const float zz = zall[g * C + c];
+                    const float ex = zz > -INFINITY ? expf(zz - zm[g]) : 0.f;
+                    zall[g * C + c] = ex;
+                    s += ex;
+                }
+            tot[g] = s;
+        }
+        step_reduce<false, GP>(tot, fred);
+        uint32_t kmin = 0xffffffffu, kmax = 0u;
+        int nvalid = 0;
+        for (int c = tid; c < C; c += STEP_THREADS) sel[c] = 0;
+        if (tid == 0) sel[C] = 1;
+        if (active) {
+            float inv[GP];
+#pragma unroll
+            for (int g = 0; g < GP; ++g) inv[g] = tot[g] > 0.f ? 1.0f / tot[g] : 0.f;
+            for (int c = tid; c < n_c; c += STEP_THREADS) {
+                float s = -INFINITY;
+                if (cntv[c] > 0) {
+                    s = 0.f;
+#pragma unroll
+                    for (int g = 0; g < GP; ++g)
+                        if (g < G) s = fmaf(zall[g * C + c], inv[g], s);
+                }
+                const uint32_t k = float_key(s);
+                key[c] = k;
+                if (cntv[c] > 0) { kmin = min(kmin, k); kmax = max(kmax, k); ++nvalid; }
+            }
+        }
+        pick_by_threshold<STEP_THREADS>(key, cntv, sel, hist, ired, n_c, need, active, kmin, kmax, nvalid);
+        __syncthreads();
+        const int words = C / 32 + 1;
+        const bool publish = split == 0;
+        for (int wd = warp; wd < words; wd += STEP_WARPS) {
+            const int c = wd * 32 + lane;
+            const unsigned v = __ballot_sync(0xffffffffu, c <= C && sel[c]);
+            if (lane == 0) {
+                s_bits[wd] = v;
+                if (publish && p.selbits) p.selbits[(int64_t)h * words + wd] = v;
+            }
+        }
+        if (publish && p.w)
+            for (int c = tid; c <= C; c += STEP_THREADS) p.w[(int64_t)h * (C + 1) + c] = sel[c] ? 1.f : 0.f;
+    }
+    __syncthreads();                                       // the selection's scratch is free: the rings take its place
+    step_stamp(p, 4);
+
+    // ---- attention over this CTA's range of positions, rows taken straight from the labels ------------------
+    WarpAttendT<STAGES> wa;
+    wa.init(sqb, G, smem + warp * (STAGES * 8192), s_vmask[warp],
+            static_cast<const char *>(p.K) + (int64_t)h * p.ksh * 2, static_cast<const char *>(p.V) + (int64_t)h * p.vsh * 2,
+            p.ksr * 2, p.vsr * 2, p.scale_log2);
+    int read_rows = 0;
+    bool bad = false;
+    for (int sub0 = p0; sub0 < p1; sub0 += STEP_SUB) {
+        const int base = sub0 + tid * STEP_LPT;
+        uint32_t take = 0;
+        if (base < p1) {
+            const int16_t *l16 = reinterpret_cast<const int16_t *>(&raw);
+#pragma unroll
+            for (int i = 0; i < STEP_LPT; ++i) {
+                const unsigned l = (unsigned)(int)l16[i];
+                if (base + i < p1) {
+                    if (l <= (unsigned)C) take |= ((s_bits[l >> 5] >> (l & 31)) & 1u) << i;
+                    else bad = true;
+                }
+            }
+        }
+        if (base + STEP_SUB < p1) raw = __ldg(reinterpret_cast<const uint4 *>(lab + base + STEP_SUB));
+        int total;
+        int off = block_excl_scan(__popc(take), s_scan, total);
+        while (take) {
+            const int i = __ffs(take) - 1;
+            take &= take - 1;
+            s_rows[off++] = (uint16_t)(tid * STEP_LPT + i);
+        }
+        __syncthreads();
+        read_rows += total;
+        const int tiles = (total + TILE_ROWS - 1) / TILE_ROWS;
+        const int tper = (tiles + STEP_WARPS - 1) / STEP_WARPS;
+        const int t0 = min(warp * tper, tiles), t1 = min(t0 + tper, tiles);
+        wa.run(t0, t1, [&](int row) { return row < total ? sub0 + (int)s_rows[row] : -1; });
+        __syncthreads();                                   // the list is rewritten by the next pass
+    }
+    step_stamp(p, 5);
+    if (bad && p.st.status) atomicOr(p.st.status + h, SKV_ST_BAD_INDEX);
+    float *red = reinterpret_cast<float *>(smem);          // [warp][g][132] over the rings, which are drained
+    wa.store_partial(red, warp, G);
+    __syncthreads();
+    // this CTA's partial goes to the cluster's first CTA: thread t owns column t
+    for (int g = 0; g < G; ++g) {
+        float M = NEG_BIG;
+#pragma unroll
+        for (int w = 0; w < STEP_WARPS; ++w) M = fmaxf(M, red[(w * G + g) * 132 + 128]);
+        float dn = 0.f, nm = 0.f;
+#pragma unroll
+        for (int w = 0; w < STEP_WARPS; ++w) {
+            const float *r = red + (w * G + g) * 132;
+            const float f = fast_exp2(r[128] - M);
+            dn += f * r[129];
+            nm += f * r[tid];
+        }
+        float *dst = recv + ((size_t)rank * G + g) * STEP_PART_LD;
+        remote_store(remote_addr(dst + tid, 0), nm);
+        if (tid == 0) {
+            remote_store(remote_addr(dst + 128, 0), M);
+            remote_store(remote_addr(dst + 129, 0), dn);
+            remote_store(remote_addr(dst + 130, 0), (float)read_rows);
+        }
+    }
+    cluster_arrive();                                      // barrier 2: the cluster's partials are in its first CTA
+    cluster_wait();
+    step_stamp(p, 6);
+    if (rank != 0) return;
+
+    // ---- the cluster's first CTA folds the 8 partials; with several clusters per head the last one merges ---
+    __nv_bfloat16 *out = static_cast<__nv_bfloat16 *>(p.out);
+    const int kcl = split / STEP_CS;                        // this cluster among the head's
+    float rows_f = 0.f;
+#pragma unroll
+    for (int r = 0; r < STEP_CS; ++r) rows_f += recv[(size_t)r * G * STEP_PART_LD + 130];
+    for (int g = 0; g < G; ++g) {
+        float M = NEG_BIG;
+#pragma unroll
+        for (int r = 0; r < STEP_CS; ++r) M = fmaxf(M, recv[((size_t)r * G + g) * STEP_PART_LD + 128]);
+        float dn = 0.f, nm = 0.f;
+#pragma unroll
+        for (int r = 0; r < STEP_CS; ++r) {
+            const float *row = recv + ((size_t)r * G + g) * STEP_PART_LD;
+            const float f = fast_exp2(row[128] - M);
+            dn = fmaf(f, row[129], dn);
+            nm = fmaf(f, row[tid], nm);
+        }
+        if (p.ncl == 1) {
+            store_out(out + ((int64_t)h * G + g) * HEAD_DIM + tid, dn > 0.f ? nm / dn : 0.f);
+        } else {
+            float *pa = p.part + (((int64_t)h * p.ncl + kcl) * G + g) * STEP_PART_LD;
+            __stcg(pa + tid, nm);
+            if (tid == 0) {
+                __stcg(pa + 128, M);
+                __stcg(pa + 129, dn);
+                __stcg(pa + 130, rows_f);
+            }
+        }
+    }
+    if (p.ncl == 1) {
+        if (tid == 0 && p.cnt) p.cnt[h] = (int)rows_f;
+        step_stamp(p, 7);
+        return;
+    }
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) s_flag = atomicAdd(p.ticket + h, 1) == p.ncl - 1;
+    __syncthreads();
+    if (!s_flag) return;
+    __threadfence();
+    const float *src = p.part + (int64_t)h * p.ncl * G * STEP_PART_LD;
+    float total_rows = 0.f;
+    for (int g = 0; g < G; ++g) {
+        float M = NEG_BIG;
+        for (int k = 0; k < p.ncl; ++k) M = fmaxf(M, __ldcg(src + ((size_t)k * G + g) * STEP_PART_LD + 128));
+        float dn = 0.f, nm = 0.f;
+        for (int k = 0; k < p.ncl; ++k) {
+            const float *row = src + ((size_t)k * G + g) * STEP_PART_LD;
+            const float f = fast_exp2(__ldcg(row + 128) - M);
+            dn = fmaf(f, __ldcg(row + 129), dn);
+            nm = fmaf(f, __ldcg(row + tid), nm);
+            if (g == 0) total_rows += __ldcg(row + 130);
+        }
+        store_out(out + ((int64_t)h * G + g) * HEAD_DIM + tid, dn > 0.f ? nm / dn : 0.f);
+    }
+    if (tid == 0) {
+        if (p.cnt) p.cnt[h] = (int)total_rows;
+        p.ticket[h] = 0;                                   // ready for the next launch on this stream
+    }
+    step_stamp(p, 7);
+}
+
+using StepKern = void (*)(const StepParams);
+
+static StepKern step_kernel_for(int G) {
+    return G <= 2 ? step_kernel<STEP_STAGES, 2> : (G <= 4 ? step_kernel<STEP_STAGES, 4> : step_kernel<STEP_STAGES, 8>);
+}
+
+// Clusters of 8 CTAs that one launch can keep resident on this device for (G, C); cached per device and shape.
+static int step_resident_clusters(int G, int C) {
+    struct Entry { int dev, G, C, n; };
+    static Entry cache[16];
+    static int used = 0;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return 0;
+    for (int i = 0; i < used; ++i)
+        if (cache[i].dev == dev && cache[i].G == G && cache[i].C == C) return cache[i].n;
+    const size_t smem = step_smem_bytes(G, C, STEP_STAGES);
+    if ((int)smem > device_max_smem_optin()) return 0;
+    StepKern kern = step_kernel_for(G);
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return 0;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(STEP_CS * 64, 1, 1);
+    cfg.blockDim = dim3(STEP_THREADS, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = STEP_CS; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess) { cudaGetLastError(); n = 0; }
+    if (used < 16) cache[used++] = Entry{dev, G, C, n};
+    return n;
+}
+
+}  // namespace skv
+
+using namespace skv;
+
+extern "C" void skv_debug_step_probe(void *dev_ptr) { skv::g_step_probe = static_cast<unsigned long long *>(dev_ptr); }
+
+extern "C" int skv_step_clusters(int heads, int G, int C, int summary_bits) {
+    if (heads <= 0 || G < 1 || G > 8 || C < 64 || (C & (C - 1)) || C > 4096 || summary_bits != 8) return 0;
+    const int resident = step_resident_clusters(G, C);
+    if (resident < heads) return 0;                         // more than one wave of clusters: the two-launch path streams better
+    int ncl = resident / heads;
+    return ncl > 8 ? 8 : ncl;
+}
+
+extern "C" int64_t skv_step_workspace_bytes(int heads, int G, int clusters) {
+    if (heads <= 0 || G < 1 || G > 8 || clusters < 1 || clusters > 64) return SKV_E_RANGE;
+    const int64_t part = (((int64_t)heads * clusters * G * STEP_PART_LD * 4) + 255) / 256 * 256;
+    return part + (((int64_t)heads * 4) + 255) / 256 * 256;
+}
+
+extern "C" int skv_step(const skv_state *st, const void *q, int G, const int32_t *n_dev, const void *K, const void *V,
+                        int64_t k_head_stride, int64_t k_row_stride, int64_t v_head_stride, int64_t v_row_stride,
+                        float *w, uint32_t *selbits, int32_t *cnt, void *out, void *workspace, int clusters,
+                        float scale, const skv_rope *rope, void *stream) {
+    if (!st || !n_dev || !K || !V || !out || !workspace) return SKV_E_NULL;
+    if (!q && !rope) return SKV_E_NULL;
+    if (rope) {
+        if (!rope->qkv || !rope->q_norm_w || !rope->k_norm_w || !rope->cos_table || !rope->sin_table || !rope->pos ||
+            !rope->q_out || !rope->k_cache || !rope->v_cache)
+            return SKV_E_NULL;
+        if (rope->H_kv < 1 || rope->H < rope->H_kv || rope->H % rope->H_kv || rope->H / rope->H_kv != G ||
+            st->heads % rope->H_kv)
+            return SKV_E_RANGE;
+        if (!aligned16(rope->qkv) || !aligned16(rope->q_out) || !aligned16(rope->k_cache) || !aligned16(rope->v_cache) ||
+            rope->cache_row_stride % 8 || rope->cache_head_stride % 8 || rope->cache_batch_stride % 8)
+            return SKV_E_ALIGN;
+    }
+    if (!st->count || !st->n_c || !st->end || !st->need || !st->labels || !st->mmax || !st->mmin || !st->dir8)
+        return SKV_E_NULL;
+    if (st->d != HEAD_DIM || G < 1 || G > 8) return SKV_E_DIM;
+    if (st->C < 64 || (st->C & (st->C - 1)) || st->C > 4096) return SKV_E_DIM;
+    if (st->summary_bits != 8) return SKV_E_RANGE;
+    if (st->heads <= 0 || st->heads > 65535 || st->capacity <= 0 || clusters < 1 || clusters > 64) return SKV_E_RANGE;
+    if (st->capacity % 8 || !aligned16(st->labels) || !aligned16(st->dir8) || !aligned16(workspace) || !aligned16(K) ||
+        !aligned16(V) || !aligned16(out) || (q && !aligned16(q)))
+        return SKV_E_ALIGN;
+    if ((k_row_stride * 2) % 16 || (v_row_stride * 2) % 16 || (k_head_stride * 2) % 16 || (v_head_stride * 2) % 16 ||
+        k_row_stride < HEAD_DIM || v_row_stride < HEAD_DIM)
+        return SKV_E_ALIGN;
+    const size_t smem = step_smem_bytes(G, st->C, STEP_STAGES);
+    if ((int)smem > device_max_smem_optin()) return SKV_E_DIM;
+    StepParams p;
+    p.st = *st; p.q = q; p.K = K; p.V = V; p.n_dev = n_dev; p.out = out; p.w = w; p.selbits = selbits; p.cnt = cnt;
+    p.part = static_cast<float *>(workspace);
+    p.ticket = reinterpret_cast<int32_t *>(static_cast<char *>(workspace) +
+                                           (((int64_t)st->heads * clusters * G * STEP_PART_LD * 4) + 255) / 256 * 256);
+    p.G = G; p.ncl = clusters;
+    p.ksh = k_head_stride; p.ksr = k_row_stride; p.vsh = v_head_stride; p.vsr = v_row_stride;
+    p.scale = scale; p.scale_log2 = scale * LOG2E;
+    p.rope = rope ? *rope : skv_rope{};
+    p.probe = g_step_probe;
+    StepKern kern = step_kernel_for(G);
+    static size_t configured[64][3] = {};
+    const int gsel = G <= 2 ? 0 : (G <= 4 ? 1 : 2);
+    int dev = 0;
+    SKV_CUDA_OK(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return SKV_E_RANGE;
+    if (configured[dev][gsel] < smem) {
+        SKV_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        configured[dev][gsel] = smem;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(STEP_CS * clusters, st->heads, 1);
+    cfg.blockDim = dim3(STEP_THREADS, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = static_cast<cudaStream_t>(stream);
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = STEP_CS; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 2 : 1;
+    SKV_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, p));
+    SKV_CUDA_OK(cudaGetLastError());
+    return SKV_OK;
+}
