@@ -37,9 +37,9 @@ WORKLOADS = {
     "qwen3-0.6b_b1_4k_budget20": ("0.6b", 1, 4096, 0.20, 1024),          # quick check
 }
 DEFAULT = "qwen3-0.6b_b1_32k_budget20"
-# dram__bytes_read.sum + dram__bytes_write.sum of one attention launch from an `ncu --set full` capture of this
-# workload (profiles/attend_labels_kernel_qwen3-0.6b_b1_32k.md); other workloads have no capture yet
-NCU_TRAFFIC = {"qwen3-0.6b_b1_32k_budget20": 27.72e6}
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the workload's dominant kernel, from an ncu capture
+# of that workload (a constant copied from the capture's summary; workloads without a capture report null)
+NCU_TRAFFIC = {}
 
 
 def peaks() -> tuple[float, str]:
@@ -187,10 +187,13 @@ def build_decoder(wl, dev, tp_group, tp_size, tp_rank, decode_steps):
 
 
 def kernel_roofline(dec, n_now, peak_gbs, which, traffic=None):
-    """Per-launch duration of the attention kernel measured with CUDA events, layer by layer, outside the
-    graph (each layer's rows are cold: the layers' caches together are far larger than L2), and of the
-    three kernels of a layer step together.  Bytes: K and V rows read plus their 4-byte positions for the
-    attention kernel (plus the labels it scans); the full accounting formula for the layer step."""
+    """Per-launch duration of the layer's attention-side kernels measured with CUDA events, one launch per
+    layer back to back in a CUDA graph (each layer's rows are cold: the layers' caches together are far larger
+    than L2, and 512 MB are written before each replay).  The layer step is timed as the decoder runs it
+    (``SphereIndexGraph.step``): ONE launch (selection + attention by thread-block clusters) for few heads,
+    else the selection launch followed by the attention launch.  Bytes: for the dominant kernel what that
+    kernel has to read (K and V rows, the int16 label of every cached position, and - when it also selects -
+    the cluster summaries); for the layer step the full accounting formula."""
     from sparse_kv_reads_b200.accounting import step_bytes
     B, H, H_kv, d = dec.B, dec.H, dec.H_kv, dec.d
     dev = dec.tok.device
@@ -227,26 +230,66 @@ def kernel_roofline(dec, n_now, peak_gbs, which, traffic=None):
         out.sort()
         return out[len(out) // 2] * 1e-3 / len(layers)
 
-    # the two launches a layer step makes: score + pick, then attention straight from the labels
+    one_launch = bool(layers[0]._step_clusters(H // H_kv))
     sel_t = timed(graph_of(lambda ix, kv: ix._select(q, dec.n_dev, listed=False)))
     att_t = timed(graph_of(lambda ix, kv: ix._attend_labels(q, kv[0], kv[1], dec.n_dev)))
-    stp_t = timed(graph_of(lambda ix, kv: (ix._select(q, dec.n_dev, listed=False),
-                                           ix._attend_labels(q, kv[0], kv[1], dec.n_dev))))
+    stp_t = timed(graph_of(lambda ix, kv: ix.step(q, kv[0], kv[1], dec.n_dev, insert=False)))
     rows = torch.stack([ix.cnt for ix in layers]).float()              # [layers, heads]
     n_c = torch.stack([ix.n_c for ix in layers]).float()
     # attention kernel: K and V rows, the int16 label of every cached position, the selection bits
     att_bytes = float((rows * 2 * 256).sum(1).mean()) + rows.shape[1] * (2 * n_now + 4 * (layers[0].C // 32 + 1))
+    # one-launch step: the same rows and labels plus every cluster's summary (128-byte direction, lengths, count)
+    one_bytes = float((rows * 2 * 256 + n_c * (128 + 12)).sum(1).mean()) + rows.shape[1] * 2 * n_now
     stp_bytes = float(step_bytes(n=n_now, rows=rows, clusters=n_c, d=d, summary_bits=8).sum(1).mean())
-    roof = {"bound": "hbm", "kernel": "attend_labels_kernel", "achieved": att_bytes / att_t / 1e9, "peak": peak_gbs,
-            "unit": "GB/s", "frac": att_bytes / att_t / 1e9 / peak_gbs, "traffic": traffic, "peak_source": which,
-            "us_per_launch": att_t * 1e6, "bytes_per_launch": att_bytes}
-    layer = {"kernels": "select + attend (insert runs once for all layers)", "us_per_layer": stp_t * 1e6,
+    kernel, k_bytes, k_t = ("step_kernel", one_bytes, stp_t) if one_launch else ("attend_labels_kernel", att_bytes, att_t)
+    roof = {"bound": "hbm", "kernel": kernel, "achieved": k_bytes / k_t / 1e9, "peak": peak_gbs,
+            "unit": "GB/s", "frac": k_bytes / k_t / 1e9 / peak_gbs, "traffic": traffic,
+            "traffic_source": "constant from the committed ncu capture of this workload, not measured in this run",
+            "peak_source": which, "us_per_launch": k_t * 1e6, "bytes_per_launch": k_bytes}
+    layer = {"kernels": ("select + attend in one launch" if one_launch else "select, then attend") +
+                        " (insert runs once for all layers)",
+             "launches": 1 if one_launch else 2, "us_per_layer": stp_t * 1e6,
              "bytes_per_layer": stp_bytes, "achieved": stp_bytes / stp_t / 1e9, "unit": "GB/s",
              "frac": stp_bytes / stp_t / 1e9 / peak_gbs, "select_us": sel_t * 1e6, "attend_us": att_t * 1e6,
              "rows_per_head": float(rows.mean()),
              "clusters_per_head": float(n_c.mean())}
     del flush
     return roof, layer
+
+
+def batch32_roofline(G, peak_gbs, which, dev):
+    """The layer step at 256 (sequence, KV head) pairs - batch 32 - of 32,768 tokens at 20 %: one layer of
+    synthetic clustered keys (4.3 GB of cache), where the step is a stream rather than a chain of latencies."""
+    from sparse_kv_reads_b200.kernel_bench import run_case
+    r = run_case(256, 32768, 0.2, G, 10, peak_gbs, dev)
+    return {"heads": 256, "context": 32768, "budget": 0.2, "G": G, "us_select": r["select_us"],
+            "us_attend": r["attend_us"], "us_step": r["step_us"], "bytes": r["step_bytes"],
+            "achieved": r["step_gbs"], "unit": "GB/s", "peak": peak_gbs, "peak_source": which,
+            "frac": r["step_frac_of_peak"], "attend_frac": r["attend_frac_of_peak"],
+            "rows_per_head": r["rows_per_head"], "clusters_per_head": r["clusters_per_head"]}
+
+
+def exact_leg(model, cache, ids_dev, pos, steps, warmup):
+    """The reference publishes exact attention beside every sparse number (ssa/harness/decode_speed.py:128-137):
+    the same model and cache decoded with exact attention over every cached row (the gather kernel in its dense
+    mode), same graph loop, device-resident ids.  Returns (tokens/s, ms per step, next position)."""
+    from sparse_kv_reads_b200 import GraphDecoder
+    dec = GraphDecoder(model, cache, mode="dense")
+    cache.cur_len = pos
+    dec.capture()
+    for _ in range(warmup):
+        dec.step(ids_dev[:, pos:pos + 1], pos)
+        pos += 1
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(steps):
+        dec.step(ids_dev[:, pos:pos + 1], pos)
+        pos += 1
+    b.record()
+    torch.cuda.synchronize()
+    ms = a.elapsed_time(b) / steps
+    return ids_dev.shape[0] / (ms * 1e-3), ms, pos
 
 
 def own_launches(dec) -> int:
@@ -284,7 +327,7 @@ def gpu_arm(args, wl) -> None:
     B = B * world
     wl = (model_name, B, n, budget, slots)
     K_steps, W = args.steps, args.warmup
-    total = 2 * (K_steps + W) + 4
+    total = 3 * (K_steps + W) + 4                        # device leg, end-to-end leg, exact-attention leg
     model, cache, dec, ids, fit_s = build_decoder(wl, dev, group, world, rank, total)
     ids_dev = ids.to(dev)
     pinned = ids.pin_memory()
@@ -365,6 +408,13 @@ def gpu_arm(args, wl) -> None:
                 "clocks": clocks.summary(), "roofline": roof, "layer_step": layer,
                 "prompt_fit_s": fit_s, "device_status": status,
                 "splits": sum(ix.splits for ix in dec.attn)}
+        if world == 1:
+            xs, xw = min(K_steps, 32), min(W, 4)
+            tok_s, ms, _ = exact_leg(model, cache, ids_dev, pos, xs, xw)
+            line["exact"] = {"value": tok_s, "unit": "tok/s", "ms_per_step": ms, "steps": xs,
+                             "what": "same model and cache, exact attention over every cached row (dense mode of "
+                                     "the gather kernel), device-resident ids"}
+            line["roofline_b32"] = batch32_roofline(dec.H // dec.H_kv, peak, which, dev)
         if world == 1 and not args.no_cpu:
             per_layer, cfit, cores = cpu_attention_path(min(n, 32768), budget, slots, len(dec.attn), 4, 1,
                                                         h=8, G=dec.H // dec.H_kv)

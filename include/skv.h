@@ -225,14 +225,17 @@ int skv_attend_labels(const void *q, const void *K, const void *V, const int16_t
  * first CTA merges its 8 partials; only one partial per cluster passes through the workspace.
  * Replaces SphereIndexGraph.step's launches after the insert - _score_kernel, _pick_dev_kernel,
  * _compact_dev_kernel, _list_kernel, _merge_kernel (ssa/kernels/graph_kernels.py:229-244) - for bf16 caches,
- * 8-bit summaries, G <= 8, 64 <= C <= 4096.
+ * 8-bit summaries, G <= 8, 64 <= C <= 2048.
  *   skv_step_clusters        clusters per head to launch with on the current device (1..8), or 0 when this
  *                            shape is better served by skv_select + skv_attend_labels (many heads, other modes)
  *   skv_step_workspace_bytes bytes of `workspace` (zero-initialised once by the caller)
  *   q          [heads*G, d] bf16, or null with `rope` (the queries are then computed from the raw projection
  *              as in skv_select; the CTA that reads the new token's position writes its K and V rows)
  *   w, selbits optional outputs as in skv_select;  cnt [heads] receives the rows read per head
- *   out        [heads*G, d] bf16 */
+ *   out        [heads*G, d] bf16; or null: the last merge is left to the consumer - the workspace then holds, per
+ *              head, `clusters` partials [heads, clusters, G, 132] of float32 (128 weighted sums, their running
+ *              maximum in base-2 units, the sum of weights, the rows read) and cnt is not written; skv_gemv_attended
+ *              (the output product) merges them while it builds its input, which saves a hand-off through a ticket */
 int skv_step_clusters(int heads, int G, int C, int summary_bits);
 int64_t skv_step_workspace_bytes(int heads, int G, int clusters);
 int skv_step(const skv_state *st, const void *q, int G, const int32_t *n_dev, const void *K, const void *V,
@@ -382,6 +385,14 @@ int skv_gemv_tp(const void *W, int N, int K, void *y, int B, int mode, const voi
 int skv_comm_reduce(const skv_comm *c, int seq, void *delta, int B, int N, void *stream);
 /* The buffer's status word (SKV_ST_WAIT_TIMEOUT), read back with a synchronising copy; negative on error. */
 int skv_comm_status(const skv_comm *c);
+
+/* y[B, N] = attention output . W^T straight from the partials skv_step left with out == null: every CTA of the product
+ * merges the `clusters` partials of each query head (log-sum-exp) into its input row; CTA 0 also writes the rows read
+ * per head to `cnt` (may be null).  K = query heads per sequence x 128; partials [B * K / (128 G), clusters, G, 132].
+ * `out`/`out_seq` as in skv_gemv_tp (null: plain output to y).  Replaces _merge_kernel + the engine's o projection
+ * (ssa/kernels/labeled_attn.py:123-140, ssa/models/graph_decode.py:113-115). */
+int skv_gemv_attended(const void *W, int N, int K, void *y, int B, const float *partials, int clusters, int G,
+                      int32_t *cnt, const skv_comm *out, int out_seq, void *stream);
 
 /* 1 when skv_gemv serves this shape well; 0 when it cannot run it or when the inputs every CTA rebuilds would
  * outweigh the weights it multiplies them with (many sequences of a long row: use a library GEMM there). */

@@ -143,6 +143,14 @@ def fit_layers(layers: list["SphereIndexGraph"], caches: list[torch.Tensor], n: 
     return True
 
 
+class AttentionPartials:
+    """What ``skv_step`` leaves when the last merge is deferred: per head ``clusters`` partial outputs in
+    ``workspace`` ([heads, clusters, G, 132] float32) and the buffer that is to receive the rows read."""
+
+    def __init__(self, workspace: torch.Tensor, clusters: int, G: int, cnt: torch.Tensor):
+        self.workspace, self.clusters, self.G, self.cnt = workspace, clusters, G, cnt
+
+
 class SphereIndexGraph:
     """Cluster state of one layer for ``h`` (sequence, KV head) pairs, with the eager calls
     (``observe``, ``labels_and_weights``, ``attend``) and the graph-safe ones (``prepare``, ``step``,
@@ -529,8 +537,11 @@ class SphereIndexGraph:
             self._step_ncl[G] = got
         return got
 
-    def _step_one_launch(self, q: torch.Tensor, K: torch.Tensor, V: torch.Tensor, n_dev: torch.Tensor, rope, ncl: int):
-        """Selection and attention in one launch (``skv_step``): fills ``wbuf``, ``selbits``, ``cnt`` and ``out``."""
+    def _step_one_launch(self, q: torch.Tensor, K: torch.Tensor, V: torch.Tensor, n_dev: torch.Tensor, rope, ncl: int,
+                         defer_merge: bool = False):
+        """Selection and attention in one launch (``skv_step``): fills ``wbuf``, ``selbits``, ``cnt`` and ``out``.
+        ``defer_merge``: the clusters' partials stay in the workspace for the output product to merge
+        (``skv_gemv_attended``); returns ``AttentionPartials`` instead of ``out``."""
         H, d = q.shape
         if not q.is_contiguous():
             q = q.contiguous()
@@ -541,10 +552,11 @@ class SphereIndexGraph:
                                                 device=q.device)
         check(lib().skv_step(ctypes.byref(self._st), q.data_ptr(), G, n_dev.data_ptr(), K.data_ptr(), V.data_ptr(),
                              K.stride(0), K.stride(1), V.stride(0), V.stride(1), self.wbuf.data_ptr(),
-                             self.selbits.data_ptr(), self.cnt.data_ptr(), self.out.data_ptr(), ws.data_ptr(), ncl,
-                             1.0 / math.sqrt(d), None if rope is None else ctypes.byref(rope), stream_ptr(q.device)),
+                             self.selbits.data_ptr(), self.cnt.data_ptr(), None if defer_merge else self.out.data_ptr(),
+                             ws.data_ptr(), ncl, 1.0 / math.sqrt(d), None if rope is None else ctypes.byref(rope),
+                             stream_ptr(q.device)),
               "skv_step")
-        return self.out
+        return AttentionPartials(ws, ncl, G, self.cnt) if defer_merge else self.out
 
     def _fused_rows(self, K: torch.Tensor) -> bool:
         """Whether the list-free attention applies (bf16 caches)."""
@@ -590,7 +602,7 @@ class SphereIndexGraph:
         assert self.G == G
 
     def step(self, q: torch.Tensor, K: torch.Tensor, V: torch.Tensor, n_dev: torch.Tensor, insert: bool = True,
-             rope=None):
+             rope=None, defer_merge: bool = False):
         """One decode step with every length on the device; position ``n-1`` of ``K, V`` is already
         written.  ``insert=False`` when one launch inserted for all layers
         (ssa/kernels/graph_kernels.py:220-244)."""
@@ -601,7 +613,7 @@ class SphereIndexGraph:
             # and writes the token's K/V rows, in place of a separate launch ahead of it
             ncl = self._step_clusters(q.shape[0] // self.H_kv) if q.dtype == torch.bfloat16 else 0
             if ncl:                                          # few heads: selection and attention in one launch
-                return self._step_one_launch(q, K, V, n_dev, rope, ncl)
+                return self._step_one_launch(q, K, V, n_dev, rope, ncl, defer_merge)
             self._select(q, n_dev, listed=False, rope=rope)
             return self._attend_labels(q, K, V, n_dev)
         if rope is not None:

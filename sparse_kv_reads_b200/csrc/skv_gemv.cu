@@ -11,7 +11,9 @@
 //   mode 0  x as given;
 //   mode 1  residual add and RMSNorm: h_out = bf16(h_in + delta), x = bf16(h_out * rsqrt(mean(h_out^2) + eps) * g)
 //           (CTA 0 also stores h_out, out of place because the other CTAs still read h_in);
-//   mode 2  x = bf16(bf16(silu(gate)) * up) from gate_up[B, 2K].
+//   mode 2  x = bf16(bf16(silu(gate)) * up) from gate_up[B, 2K];
+//   mode 4  x = the attention output, merged here from the split partials the one-launch decode step left
+//           (skv_gemv_attended): the output product does the last log-sum-exp merge while it builds its input.
 // The roundings are those of the separate kernels (skv_dense.cu) and of the unfused module forward.
 // The products themselves run on the tensor cores where K is a multiple of 64: 16 rows of the slab x 16 inputs
 // are one mma.sync m16n8k16 A tile (ldmatrix from the slab, stored with its 16-byte pieces XOR-swizzled by the
@@ -45,6 +47,11 @@ struct GemvParams {
     const uint32_t *in_tick;
     int in_world, in_seq, in_cap, wait_limit;
     int32_t *status;
+    // mode 4: the input is the attention output, still in the split partials skv_step left ([heads, ncl, G, 132]
+    // floats: 128 sums, running maximum in base-2 units, sum of weights, rows read): every CTA merges them itself
+    const float *att_part;
+    int att_ncl, att_G;
+    int32_t *att_cnt;              // [heads] rows read per head, written by CTA 0 (may be null)
 };
 
 __device__ __forceinline__ float bf16r(float x) { return __bfloat162float(__float2bfloat16(x)); }
@@ -149,7 +156,63 @@ __global__ void __launch_bounds__(GEMV_THREADS) gemv_kernel(const GemvParams p) 
     const uint32_t in_epoch = p.mode == 3 ? epoch_of(p.in_tick, p.in_seq) : 0u;
 
     // 2. the input of every sequence, in shared memory as bf16
-    if (p.mode == 0) {
+    if (p.mode == 4) {
+        // log-sum-exp merge of the attention partials, eight output components at a time; element e of the input
+        // row-major over (sequence, query head, component) belongs to query head e / 128 of the partials
+        const int ncl = p.att_ncl, G = p.att_G;
+        for (int c = tid; c < BP * kv; c += GEMV_THREADS) {
+            const int b = c / kv, v = c - b * kv;
+            __align__(16) __nv_bfloat16 o[8];
+#pragma unroll
+            for (int k = 0; k < 8; ++k) o[k] = __float2bfloat16(0.f);
+            if (b < p.B) {
+                const size_t e0 = (size_t)b * K + (size_t)v * 8;
+                const size_t qh = e0 >> 7;                   // flat query head: (sequence, KV head, head of the group)
+                const int t0 = (int)(e0 & 127);
+                const size_t head = qh / G;
+                const int g = (int)(qh - head * G);
+                float4 a0[8], a1[8];
+                float pm[8], pd[8];
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {                // every load goes out before any value is used
+                    pm[k] = NEG_BIG; pd[k] = 0.f;
+                    a0[k] = a1[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (k < ncl) {
+                        const float *row = p.att_part + ((head * ncl + k) * G + g) * 132;
+                        pm[k] = __ldcg(row + 128);
+                        pd[k] = __ldcg(row + 129);
+                        a0[k] = __ldcg(reinterpret_cast<const float4 *>(row + t0));
+                        a1[k] = __ldcg(reinterpret_cast<const float4 *>(row + t0 + 4));
+                    }
+                }
+                float M = NEG_BIG;
+#pragma unroll
+                for (int k = 0; k < 8; ++k) M = fmaxf(M, pm[k]);
+                float dn = 0.f, nm[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                    const float f = fast_exp2(pm[k] - M);
+                    dn = fmaf(f, pd[k], dn);
+                    nm[0] = fmaf(f, a0[k].x, nm[0]); nm[1] = fmaf(f, a0[k].y, nm[1]);
+                    nm[2] = fmaf(f, a0[k].z, nm[2]); nm[3] = fmaf(f, a0[k].w, nm[3]);
+                    nm[4] = fmaf(f, a1[k].x, nm[4]); nm[5] = fmaf(f, a1[k].y, nm[5]);
+                    nm[6] = fmaf(f, a1[k].z, nm[6]); nm[7] = fmaf(f, a1[k].w, nm[7]);
+                }
+                const float inv = dn > 0.f ? 1.0f / dn : 0.f;
+#pragma unroll
+                for (int k = 0; k < 8; ++k) o[k] = __float2bfloat16(nm[k] * inv);
+            }
+            *reinterpret_cast<uint4 *>(xs + (size_t)b * xld + v * 8) = *reinterpret_cast<const uint4 *>(o);
+        }
+        if (blockIdx.x == 0 && p.att_cnt) {
+            const int heads = (int)(((size_t)p.B * K) >> 7) / G;
+            for (int hd = tid; hd < heads; hd += GEMV_THREADS) {
+                float rows = 0.f;
+                for (int k = 0; k < ncl; ++k) rows += __ldcg(p.att_part + (((size_t)hd * ncl + k) * G) * 132 + 130);
+                p.att_cnt[hd] = (int)rows;
+            }
+        }
+    } else if (p.mode == 0) {
         for (int c = tid; c < BP * kv; c += GEMV_THREADS) {
             const int b = c / kv, v = c - b * kv;
             uint4 val = make_uint4(0u, 0u, 0u, 0u);
@@ -456,12 +519,22 @@ static int check_comm(const skv_comm *c) {
     return SKV_OK;
 }
 
+struct AttentionPartials {
+    const float *part;
+    int ncl, G;
+    int32_t *cnt;
+};
+
 static int gemv_launch(const void *W, int N, int K, void *y, int B, int mode, const void *x, const void *h_in,
                        const void *delta, const void *norm_w, void *h_out, float eps, const skv_comm *in, int in_seq,
-                       const skv_comm *out, int out_seq, void *stream) {
+                       const skv_comm *out, int out_seq, void *stream, const AttentionPartials *att = nullptr) {
     if (!W || (!y && !out)) return SKV_E_NULL;
-    if (mode < 0 || mode > 3 || (mode == 3) != (in != nullptr)) return SKV_E_RANGE;
-    if (mode == 1 || mode == 3 ? (!h_in || !norm_w) : !x) return SKV_E_NULL;
+    if (mode < 0 || mode > 4 || (mode == 3) != (in != nullptr) || (mode == 4) != (att != nullptr)) return SKV_E_RANGE;
+    if (mode == 4) {
+        if (!att->part) return SKV_E_NULL;
+        if (att->ncl < 1 || att->ncl > 8 || att->G < 1 || att->G > 16 || K % (128 * att->G)) return SKV_E_RANGE;
+        if (!aligned16(att->part)) return SKV_E_ALIGN;
+    } else if (mode == 1 || mode == 3 ? (!h_in || !norm_w) : !x) return SKV_E_NULL;
     if (B < 1 || B > 8 || N < 1 || K < 8 || K % 8) return SKV_E_RANGE;
     if (!aligned16(W) || (y && !aligned16(y)) || (x && !aligned16(x)) || (h_in && !aligned16(h_in)) ||
         (delta && !aligned16(delta)) || (norm_w && !aligned16(norm_w)) || (h_out && !aligned16(h_out)))
@@ -475,7 +548,7 @@ static int gemv_launch(const void *W, int N, int K, void *y, int B, int mode, co
         (out && (out_seq < 0 || out_seq > 254 || (int64_t)B * N > out->cap_elems)))
         return SKV_E_RANGE;
     GemvPlan pl;
-    const int rc = plan_gemv(N, K, B, mode, pl);
+    const int rc = plan_gemv(N, K, B, mode == 4 ? 0 : mode, pl);
     if (rc) return rc;
     const int BP = pl.BP, rows = pl.rows;
     const bool tc = pl.tc;
@@ -486,6 +559,7 @@ static int gemv_launch(const void *W, int N, int K, void *y, int B, int mode, co
     p.x = static_cast<const __nv_bfloat16 *>(x); p.h_in = static_cast<const __nv_bfloat16 *>(h_in);
     p.delta = static_cast<const __nv_bfloat16 *>(delta); p.g = static_cast<const __nv_bfloat16 *>(norm_w);
     p.h_out = static_cast<__nv_bfloat16 *>(h_out); p.eps = eps;
+    if (att) { p.att_part = att->part; p.att_ncl = att->ncl; p.att_G = att->G; p.att_cnt = att->cnt; }
     if (out) {
         for (int r = 0; r < out->world; ++r) p.out_data[r] = static_cast<uint2 *>(out->data[r]);
         p.out_tick = out->tick;
@@ -517,14 +591,22 @@ static int gemv_launch(const void *W, int N, int K, void *y, int B, int mode, co
 
 extern "C" int skv_gemv(const void *W, int N, int K, void *y, int B, int mode, const void *x, const void *h_in,
                         const void *delta, const void *norm_w, void *h_out, float eps, void *stream) {
-    if (mode == 3) return SKV_E_RANGE;
+    if (mode == 3 || mode == 4) return SKV_E_RANGE;
     return gemv_launch(W, N, K, y, B, mode, x, h_in, delta, norm_w, h_out, eps, nullptr, 0, nullptr, 0, stream);
 }
 
 extern "C" int skv_gemv_tp(const void *W, int N, int K, void *y, int B, int mode, const void *x, const void *h_in,
                            const void *norm_w, void *h_out, float eps, const skv_comm *in, int in_seq,
                            const skv_comm *out, int out_seq, void *stream) {
+    if (mode == 4) return SKV_E_RANGE;
     return gemv_launch(W, N, K, y, B, mode, x, h_in, nullptr, norm_w, h_out, eps, in, in_seq, out, out_seq, stream);
+}
+
+extern "C" int skv_gemv_attended(const void *W, int N, int K, void *y, int B, const float *partials, int clusters, int G,
+                                 int32_t *cnt, const skv_comm *out, int out_seq, void *stream) {
+    const AttentionPartials att = {partials, clusters, G, cnt};
+    return gemv_launch(W, N, K, y, B, 4, nullptr, nullptr, nullptr, nullptr, nullptr, 0.f, nullptr, 0, out, out_seq,
+                       stream, &att);
 }
 
 extern "C" int64_t skv_comm_bytes(int world, int cap_elems) {

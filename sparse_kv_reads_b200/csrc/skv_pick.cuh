@@ -9,14 +9,14 @@ namespace skv {
 // counts ci[] of the taken ones reach `need`; the cluster that crosses `need` is taken.  Never sorts: it finds the
 // threshold key tau with  sum(count | key > tau) < need  and settles exact ties at tau in slot order.
 //   key[c]   order-preserving integer keys of the shared scores (float_key), c < n_c
-//   ci[c]    member counts; clusters with ci[c] <= 0 are never taken
+//   ci[c]    member counts (int, or float holding whole numbers); clusters with ci[c] <= 0 are never taken
 //   sel      bytes, zeroed by the caller for c < n_c
 //   hist     512 ints of shared scratch, ired 40 ints
 //   kmin, kmax, nvalid   this THREAD's partial range and count of the keys of clusters with members (the block
 //            reduction happens here); `active` false: nothing is taken (the reductions and barriers still run)
 // Block-wide: every thread of the NT-thread CTA calls it; sel is complete (and synchronised) on return.
-template <int NT>
-__device__ __forceinline__ void pick_by_threshold(const uint32_t *key, const int *ci, uint8_t *sel, int *hist,
+template <int NT, typename CT>
+__device__ __forceinline__ void pick_by_threshold(const uint32_t *key, const CT *ci, uint8_t *sel, int *hist,
                                                   int *ired, int n_c, int need, bool active, uint32_t kmin,
                                                   uint32_t kmax, int nvalid) {
     constexpr int NW = NT / 32;
@@ -53,7 +53,7 @@ __device__ __forceinline__ void pick_by_threshold(const uint32_t *key, const int
                 const uint32_t k = key[c];
                 if (ci[c] > 0 && k >= lo && k <= hi) {
                     const int bin = (int)((k - lo) >> shift);
-                    atomicAdd(&hw[bin], ci[c]);
+                    atomicAdd(&hw[bin], (int)ci[c]);
                     atomicAdd(&hn[bin], 1);
                 }
             }
@@ -99,7 +99,7 @@ __device__ __forceinline__ void pick_by_threshold(const uint32_t *key, const int
                 const uint32_t k = key[c];
                 if (ci[c] > 0 && k >= lo && k <= hi) {
                     const int j = atomicAdd(&ired[1], 1);
-                    if (j < 32) { hw[j] = (int)k; hn[j] = ci[c]; }
+                    if (j < 32) { hw[j] = (int)k; hn[j] = (int)ci[c]; }
                 }
             }
             __syncthreads();
@@ -143,7 +143,7 @@ __device__ __forceinline__ void pick_by_threshold(const uint32_t *key, const int
                 const int c = base + lane;
                 const bool tie = c < n_c && key[c] == tau;
                 if (!__any_sync(0xffffffffu, tie)) continue;
-                const int mine = tie ? ci[c] : 0;
+                const int mine = tie ? (int)ci[c] : 0;
                 int inc = mine;
 #pragma unroll
                 for (int o = 1; o < 32; o <<= 1) {

@@ -509,7 +509,7 @@ __global__ void __launch_bounds__(SEL_THREADS) score_pick_kernel(const SelectPar
         }
     }
     stamp(p, h, 4);
-    pick_by_threshold<SEL_THREADS>(key, ci, sel, hist, ired, n_c, need, active, kmin, kmax, nvalid);
+    pick_by_threshold<SEL_THREADS, int>(key, ci, sel, hist, ired, n_c, need, active, kmin, kmax, nvalid);
     stamp(p, h, 6);
     // ---- weights and selection bits out ---------------------------------------------------------
     float *w = p.w + (int64_t)h * (C + 1);

@@ -24,6 +24,9 @@ namespace skv {
 
 constexpr int STEP_THREADS = 128, STEP_WARPS = 4, STEP_CS = 8, STEP_LPT = 8, STEP_STAGES = 2;
 constexpr int STEP_SUB = STEP_THREADS * STEP_LPT;         // positions listed per pass
+constexpr int STEP_SLICES = STEP_CS * STEP_WARPS;         // (CTA, warp) pairs that score a head's clusters
+constexpr int STEP_GROUPS = 8;                            // 8-cluster groups a warp scores at most (2,048 slots)
+static_assert(STEP_SLICES == 32, "a warp's lanes stand for the slices when their statistics are combined");
 constexpr int STEP_PART_LD = 132;                         // floats per partial row: 128 sums, max, sum, rows, unused
 
 struct StepParams {
@@ -41,7 +44,8 @@ struct StepParams {
     int64_t ksh, ksr, vsh, vsr;
     float scale, scale_log2;
     skv_rope rope;
-    unsigned long long *probe; // optional [CTAs][8] phase time stamps (probe builds only)
+    int dbg;
+    unsigned long long *probe; // optional [CTAs][16] phase time stamps (probe builds only)
 };
 
 static unsigned long long *g_step_probe = nullptr;
@@ -51,7 +55,7 @@ __device__ __forceinline__ void step_stamp(const StepParams &p, int slot) {
     if (p.probe && threadIdx.x == 0) {
         unsigned long long t;
         asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-        p.probe[(size_t)(blockIdx.y * gridDim.x + blockIdx.x) * 8 + slot] = t;
+        p.probe[(size_t)(blockIdx.y * gridDim.x + blockIdx.x) * 16 + slot] = t;
     }
 #else
     (void)p; (void)slot;
@@ -163,7 +167,8 @@ __device__ __forceinline__ void step_rope(const skv_rope &r, int h, bool store_q
 // Bytes of the selection's scratch, which shares the front of the dynamic shared memory with the gather rings.
 __host__ __device__ inline int step_per_max(int C) { return ((C / STEP_CS) + 7) & ~7; }
 __host__ __device__ inline size_t step_sel_bytes(int G, int C) {
-    return (size_t)step_per_max(C) * 128 + (size_t)G * C * 4 + (size_t)C * 4 + (size_t)step_per_max(C) * 8;
+    return (size_t)step_per_max(C) * 128 + (size_t)G * C * 4 + (size_t)C * 4 + (size_t)step_per_max(C) * 8 +
+           (size_t)STEP_SLICES * 8 * 3 * 4;                 // + slice statistics and factors
 }
 __host__ __device__ inline size_t step_front_bytes(int G, int C, int stages) {
     const size_t ring = (size_t)STEP_WARPS * stages * 8192, sel = (step_sel_bytes(G, C) + 127) & ~size_t(127);
@@ -186,21 +191,23 @@ __global__ void __launch_bounds__(STEP_THREADS, 2) step_kernel(const StepParams 
     __shared__ int s_flag;
     __shared__ int s_scan[40];
     __shared__ int ired[40];
-    __shared__ float fred[GP * STEP_WARPS];
     __shared__ uint16_t s_rows[STEP_SUB];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int h = blockIdx.y, split = blockIdx.x, S = gridDim.x;
     const unsigned rank = cluster_rank();
     const int C = p.st.C, G = p.G;
+    if (p.dbg & 1) pdl_wait();
     cluster_arrive();                                      // barrier 0: "my shared memory exists"; waited for ahead of the first remote store
     step_stamp(p, 0);
 
     // ---- shared memory map ------------------------------------------------------------------------------
     const int per_max = step_per_max(C);
     unsigned char *sumst = smem;                                              // [per_max][128] this CTA's summaries
-    float *zall = reinterpret_cast<float *>(smem + (size_t)per_max * 128);    // [G][C] scaled scores of every cluster
-    int *cntv = reinterpret_cast<int *>(zall + (size_t)G * C);                // [C] member counts
-    float *smx = reinterpret_cast<float *>(cntv + C), *smn = smx + per_max;   // [per_max] key lengths of the slice
+    float *zall = reinterpret_cast<float *>(smem + (size_t)per_max * 128);    // [G][C] exp(score - slice max) of every cluster
+    float *cntf = zall + (size_t)G * C;                                       // [C] member counts
+    float *smx = cntf + C, *smn = smx + per_max;                              // [per_max] key lengths of this CTA's clusters
+    float *stat = smn + per_max;                                              // [32 slices][GP][2] (max, sum of exp)
+    float *fac = stat + STEP_SLICES * GP * 2;                                 // [32 slices][GP] exp(max - M) / T
     uint32_t *key = reinterpret_cast<uint32_t *>(smem);                       // [C], over sumst once it is scored
     uint8_t *sel = reinterpret_cast<uint8_t *>(key + C);                      // [C + 1]
     unsigned char *tail = smem + step_front_bytes(G, C, STAGES);
@@ -214,9 +221,22 @@ __global__ void __launch_bounds__(STEP_THREADS, 2) step_kernel(const StepParams 
     tail += (size_t)STEP_CS * G * STEP_PART_LD * 4;
     int *hist = reinterpret_cast<int *>(tail);
 
-    // ---- what no kernel of this step writes is requested before the wait for the launch ahead -------------
+    // ---- every load that depends on nothing goes out first, the ones sized by the cluster count right after ----
     const int n_c = min(max(p.st.n_c[h], 0), C);
     const int end = p.st.end[h], need = p.st.need[h];
+    const int n = min(max(p.n_dev[0], 0), p.st.capacity);
+    uint2 qraw[2] = {make_uint2(0u, 0u), make_uint2(0u, 0u)};                 // four query components per piece
+    if (!p.rope.qkv) {
+        const uint2 *qsrc = reinterpret_cast<const uint2 *>(static_cast<const __nv_bfloat16 *>(p.q) + (int64_t)h * G * HEAD_DIM);
+#pragma unroll
+        for (int j = 0; j < 2; ++j)
+            if (tid + j * STEP_THREADS < G * 32) qraw[j] = __ldg(qsrc + tid + j * STEP_THREADS);
+    }
+    const int chunk = max(16, (((n + S - 1) / S + 15) >> 4) << 4);            // multiples of 16: aligned label loads
+    const int p0 = min(split * chunk, n), p1 = min(p0 + chunk, n);
+    const int16_t *lab = p.st.labels + (int64_t)h * p.st.capacity;
+    uint4 raw = make_uint4(0u, 0u, 0u, 0u);
+    if (p0 + tid * STEP_LPT < p1) raw = __ldg(reinterpret_cast<const uint4 *>(lab + p0 + tid * STEP_LPT));
     const bool active = end > 1 && need > 0 && n_c > 0;
     const int per = (((n_c + STEP_CS - 1) / STEP_CS) + 7) & ~7;              // clusters scored per CTA
     const int c_lo = min((int)rank * per, n_c), c_hi = min(c_lo + per, n_c), mine = active ? c_hi - c_lo : 0;
@@ -226,26 +246,18 @@ __global__ void __launch_bounds__(STEP_THREADS, 2) step_kernel(const StepParams 
             const int c = i >> 3, k = i & 7;
             cp_async16(sumst + c * 128 + ((k ^ (c & 7)) << 4), src + (int64_t)c * HEAD_DIM + k * 16, 16);
         }
+        // counts of all the head's clusters, key lengths of this CTA's (both 16-byte aligned: c_lo is a multiple of 8)
+        const float *count = p.st.count + (int64_t)h * C;
+        if (active)
+            for (int i = tid; i < (n_c + 3) >> 2; i += STEP_THREADS) cp_async16(cntf + 4 * i, count + 4 * i, 16);
+        const float *mmax = p.st.mmax + (int64_t)h * C + c_lo, *mmin = p.st.mmin + (int64_t)h * C + c_lo;
+        for (int i = tid; i < (mine + 3) >> 2; i += STEP_THREADS) {
+            cp_async16(smx + 4 * i, mmax + 4 * i, 16);
+            cp_async16(smn + 4 * i, mmin + 4 * i, 16);
+        }
         cp_async_commit();
     }
-    const int n = min(max(p.n_dev[0], 0), p.st.capacity);
-    const int chunk = max(16, (((n + S - 1) / S + 15) >> 4) << 4);            // multiples of 16: aligned label loads
-    const int p0 = min(split * chunk, n), p1 = min(p0 + chunk, n);
-    const int16_t *lab = p.st.labels + (int64_t)h * p.st.capacity;
-    uint4 raw = make_uint4(0u, 0u, 0u, 0u);
-    if (p0 + tid * STEP_LPT < p1) raw = __ldg(reinterpret_cast<const uint4 *>(lab + p0 + tid * STEP_LPT));
-    {
-        const float *count = p.st.count + (int64_t)h * C;
-        for (int c = tid; c < C; c += STEP_THREADS) cntv[c] = c < n_c ? (int)count[c] : 0;
-        const float *mmax = p.st.mmax + (int64_t)h * C, *mmin = p.st.mmin + (int64_t)h * C;
-        for (int i = tid; i < mine; i += STEP_THREADS) {
-            smx[i] = mmax[c_lo + i];
-            smn[i] = mmin[c_lo + i];
-        }
-        // this CTA's stretch of the score table starts empty: slots past the head's last cluster stay -inf
-        if (mine > 0)
-            for (int i = tid; i < G * per; i += STEP_THREADS) zall[(i / per) * C + c_lo + (i % per)] = -INFINITY;
-    }
+    for (int i = tid; i < 512; i += STEP_THREADS) hist[i] = 0;                // the pick's first pass finds it cleared
     pdl_wait();                                            // the query comes from the launch ahead
     pdl_trigger();
     step_stamp(p, 1);
@@ -254,18 +266,28 @@ __global__ void __launch_bounds__(STEP_THREADS, 2) step_kernel(const StepParams 
         const int s_kv = (int)min((int64_t)(S - 1), max((int64_t)0, pos / chunk));
         step_rope(p.rope, h, split == 0, split == s_kv, G, sq, sqb);
     } else {
-        const __nv_bfloat16 *q = static_cast<const __nv_bfloat16 *>(p.q) + (int64_t)h * G * HEAD_DIM;
-        for (int i = tid; i < G * HEAD_DIM; i += STEP_THREADS) {
-            sqb[i] = q[i];
-            sq[i] = __bfloat162float(q[i]);
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            const int i = tid + j * STEP_THREADS;
+            if (i < G * 32) {
+                *reinterpret_cast<uint2 *>(sqb + i * 4) = qraw[j];
+                const __nv_bfloat162 *hh = reinterpret_cast<const __nv_bfloat162 *>(&qraw[j]);
+                const float2 a = __bfloat1622float2(hh[0]), b = __bfloat1622float2(hh[1]);
+                *reinterpret_cast<float4 *>(sq + i * 4) = make_float4(a.x, a.y, b.x, b.y);
+            }
         }
     }
     cp_async_wait<0>();
     __syncthreads();
 
-    // ---- scores of this CTA's clusters: q . dir8 on f16 tiles, 8 clusters per warp and chain ---------------
-    if (mine > 0) {
-        const int nrow = lane >> 2, jq = lane & 3;
+    // ---- scores of this CTA's clusters: q . dir8 on f16 tiles, 8 clusters per warp and chain.  A warp keeps the
+    // scores of the clusters it scored in registers, takes their maximum and the sum of exp(score - maximum) per
+    // query head with shuffles, and leaves exp(score - maximum): its clusters are one of the head's 32 "slices"
+    // (8 CTAs x 4 warps), whose statistics every CTA later combines into the softmax over all clusters.
+    const int nrow = lane >> 2, jq = lane & 3;
+    float zr[STEP_GROUPS][2];
+    float w_max = -INFINITY, w_sum = 0.f;
+    {
         uint32_t qa[8][4];
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks) {
@@ -274,7 +296,11 @@ __global__ void __launch_bounds__(STEP_THREADS, 2) step_kernel(const StepParams 
             qa[ks][2] = nrow < G ? step_pack_half2(q0[2], q0[3]) : 0u;
             qa[ks][1] = qa[ks][3] = 0u;                                       // at most 8 query heads: rows 8..15 unused
         }
-        for (int cb = warp * 8; cb < mine; cb += STEP_WARPS * 8) {
+#pragma unroll
+        for (int gi = 0; gi < STEP_GROUPS; ++gi) {
+            const int cb = (gi * STEP_WARPS + warp) * 8;
+            zr[gi][0] = zr[gi][1] = -INFINITY;
+            if (cb >= mine) continue;                                         // warp-uniform
             const int c = cb + nrow;
             int4 ra = make_int4(0, 0, 0, 0), rb = ra;
             if (c < mine) {
@@ -283,13 +309,14 @@ __global__ void __launch_bounds__(STEP_THREADS, 2) step_kernel(const StepParams 
             }
             const uint32_t wv[8] = {(uint32_t)ra.x, (uint32_t)ra.y, (uint32_t)ra.z, (uint32_t)ra.w,
                                     (uint32_t)rb.x, (uint32_t)rb.y, (uint32_t)rb.z, (uint32_t)rb.w};
-            float acc[4] = {0.f, 0.f, 0.f, 0.f};
+            float acc[4] = {0.f, 0.f, 0.f, 0.f}, acd[4] = {0.f, 0.f, 0.f, 0.f};   // two chains of four: half the latency
             int n2i = 0;
 #pragma unroll
             for (int ks = 0; ks < 8; ++ks) {
                 n2i = __dp4a((int)wv[ks], (int)wv[ks], n2i);
                 const uint32_t biased = wv[ks] ^ 0x80808080u;
-                step_mma_f16(acc, qa[ks], step_bytes_to_half2(biased, 0x4140u), step_bytes_to_half2(biased, 0x4342u));
+                if (ks & 1) step_mma_f16(acd, qa[ks], step_bytes_to_half2(biased, 0x4140u), step_bytes_to_half2(biased, 0x4342u));
+                else step_mma_f16(acc, qa[ks], step_bytes_to_half2(biased, 0x4140u), step_bytes_to_half2(biased, 0x4342u));
             }
             n2i += __shfl_xor_sync(0xffffffffu, n2i, 1);
             n2i += __shfl_xor_sync(0xffffffffu, n2i, 2);                      // |dir8|^2 of cluster cb + nrow
@@ -300,25 +327,56 @@ __global__ void __launch_bounds__(STEP_THREADS, 2) step_kernel(const StepParams 
                 const int cl = cb + 2 * jq + i;
                 if (cl < mine && nrow < G) {
                     const float inv = 1.0f / fmaxf(sqrtf((float)(i ? nb2 : na)), 1e-12f);
-                    const float pr = acc[i] * inv;
+                    const float pr = (acc[i] + acd[i]) * inv;
                     float e = pr >= 0.f ? smx[cl] * pr : smn[cl] * pr;
-                    if (cntv[c_lo + cl] == 0) e = -INFINITY;
-                    zall[nrow * C + c_lo + cl] = e * p.scale;
+                    if (cntf[c_lo + cl] == 0.f) e = -INFINITY;
+                    zr[gi][i] = e * p.scale;
+                    w_max = fmaxf(w_max, zr[gi][i]);
                 }
             }
         }
+        w_max = fmaxf(w_max, __shfl_xor_sync(0xffffffffu, w_max, 1));         // over the four lanes of a query head
+        w_max = fmaxf(w_max, __shfl_xor_sync(0xffffffffu, w_max, 2));
+#pragma unroll
+        for (int gi = 0; gi < STEP_GROUPS; ++gi) {
+            const int cb = (gi * STEP_WARPS + warp) * 8;
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                const int cl = cb + 2 * jq + i;
+                if (cl < mine && nrow < G) {
+                    const float ex = zr[gi][i] > -INFINITY ? expf(zr[gi][i] - w_max) : 0.f;
+                    zall[nrow * C + c_lo + cl] = ex;
+                    w_sum += ex;
+                }
+            }
+        }
+        w_sum += __shfl_xor_sync(0xffffffffu, w_sum, 1);
+        w_sum += __shfl_xor_sync(0xffffffffu, w_sum, 2);
     }
     __syncthreads();
     step_stamp(p, 2);
     cluster_wait();                                        // barrier 0: every CTA of the cluster is running
-    if (mine > 0) {
-        const int q4 = per >> 2;
-        for (int i = tid; i < G * q4; i += STEP_THREADS) {
-            const float *src = zall + (i / q4) * C + c_lo + 4 * (i % q4);
-            const float4 v = *reinterpret_cast<const float4 *>(src);
+    {
+        // this warp's statistics and this CTA's exp values go to all 8 CTAs of the cluster (its own included)
+        const int slice = (int)rank * STEP_WARPS + warp;
+        if (jq == 0 && nrow < G) {
+            float *dst = stat + ((size_t)slice * GP + nrow) * 2;
 #pragma unroll
-            for (unsigned dst = 0; dst < STEP_CS; ++dst)
-                if (dst != rank) remote_store4(remote_addr(src, dst), v);
+            for (unsigned r = 0; r < STEP_CS; ++r) {
+                const uint32_t a = remote_addr(dst, r);
+                remote_store(a, w_max);
+                remote_store(a + 4, w_sum);
+            }
+        }
+        if (mine > 0) {
+            const int q4 = (mine + 3) >> 2;
+            for (int i = tid; i < G * q4; i += STEP_THREADS) {
+                const float *src = zall + (i / q4) * C + c_lo + 4 * (i % q4);
+                const float4 v = *reinterpret_cast<const float4 *>(src);
+#pragma unroll
+                for (unsigned dst = 0; dst < STEP_CS; ++dst)
+                    if (dst != rank) remote_store4(remote_addr(src, dst), v);
+            }
         }
     }
     cluster_arrive();                                      // barrier 1: all scores are everywhere
@@ -327,51 +385,44 @@ __global__ void __launch_bounds__(STEP_THREADS, 2) step_kernel(const StepParams 
 
     // ---- every CTA derives the selection for itself ---------------------------------------------------------
     {
-        float zm[GP], tot[GP];
-#pragma unroll
-        for (int g = 0; g < GP; ++g) {
-            float m = -INFINITY;
-            if (active && g < G)
-                for (int c = tid; c < n_c; c += STEP_THREADS) m = fmaxf(m, zall[g * C + c]);
-            zm[g] = m;
+        // slice factors exp(max_s - M) / T per query head: lane = slice, warp g (and g + 4) = query head
+        for (int g = warp; g < G; g += STEP_WARPS) {
+            const float2 st = *reinterpret_cast<const float2 *>(stat + ((size_t)lane * GP + g) * 2);
+            const float M = warp_max(st.x);
+            const float e0 = st.x > -INFINITY ? expf(st.x - M) : 0.f;
+            const float T = warp_sum(e0 * st.y);
+            fac[lane * GP + g] = T > 0.f ? e0 / T : 0.f;
         }
-        step_reduce<true, GP>(zm, fred);
-#pragma unroll
-        for (int g = 0; g < GP; ++g) {
-            float s = 0.f;
-            if (active && g < G)
-                for (int c = tid; c < n_c; c += STEP_THREADS) {
-                    const float zz = zall[g * C + c];
-                    const float ex = zz > -INFINITY ? expf(zz - zm[g]) : 0.f;
-                    zall[g * C + c] = ex;
-                    s += ex;
-                }
-            tot[g] = s;
-        }
-        step_reduce<false, GP>(tot, fred);
-        uint32_t kmin = 0xffffffffu, kmax = 0u;
-        int nvalid = 0;
         for (int c = tid; c < C; c += STEP_THREADS) sel[c] = 0;
         if (tid == 0) sel[C] = 1;
-        if (active) {
-            float inv[GP];
-#pragma unroll
-            for (int g = 0; g < GP; ++g) inv[g] = tot[g] > 0.f ? 1.0f / tot[g] : 0.f;
-            for (int c = tid; c < n_c; c += STEP_THREADS) {
-                float s = -INFINITY;
-                if (cntv[c] > 0) {
-                    s = 0.f;
-#pragma unroll
-                    for (int g = 0; g < GP; ++g)
-                        if (g < G) s = fmaf(zall[g * C + c], inv[g], s);
-                }
-                const uint32_t k = float_key(s);
-                key[c] = k;
-                if (cntv[c] > 0) { kmin = min(kmin, k); kmax = max(kmax, k); ++nvalid; }
-            }
-        }
-        pick_by_threshold<STEP_THREADS>(key, cntv, sel, hist, ired, n_c, need, active, kmin, kmax, nvalid);
         __syncthreads();
+        step_stamp(p, 8);
+        uint32_t kmin = 0xffffffffu, kmax = 0u;
+        int nvalid = 0;
+        if (active) {
+            // cluster c of CTA r's stretch [r * per, (r + 1) * per) was scored by warp ((c - r * per) / 8) % 4
+            for (int r = 0; r < STEP_CS; ++r)
+                for (int i = tid; i < per; i += STEP_THREADS) {
+                    const int c = r * per + i;
+                    if (c >= n_c) break;
+                    const float *f = fac + (r * STEP_WARPS + ((i >> 3) & (STEP_WARPS - 1))) * GP;
+                    float sc = -INFINITY;
+                    const bool live = cntf[c] > 0.f;
+                    if (live) {
+                        sc = 0.f;
+#pragma unroll
+                        for (int g = 0; g < GP; ++g)
+                            if (g < G) sc = fmaf(zall[g * C + c], f[g], sc);
+                    }
+                    const uint32_t k = float_key(sc);
+                    key[c] = k;
+                    if (live) { kmin = min(kmin, k); kmax = max(kmax, k); ++nvalid; }
+                }
+        }
+        step_stamp(p, 10);
+        pick_by_threshold<STEP_THREADS, float>(key, cntf, sel, hist, ired, n_c, need, active, kmin, kmax, nvalid);
+        __syncthreads();
+        step_stamp(p, 11);
         const int words = C / 32 + 1;
         const bool publish = split == 0;
         for (int wd = warp; wd < words; wd += STEP_WARPS) {
@@ -451,6 +502,7 @@ __global__ void __launch_bounds__(STEP_THREADS, 2) step_kernel(const StepParams 
             remote_store(remote_addr(dst + 130, 0), (float)read_rows);
         }
     }
+    if (p.dbg & 2) pdl_trigger();
     cluster_arrive();                                      // barrier 2: the cluster's partials are in its first CTA
     cluster_wait();
     step_stamp(p, 6);
@@ -474,7 +526,7 @@ __global__ void __launch_bounds__(STEP_THREADS, 2) step_kernel(const StepParams 
             dn = fmaf(f, row[129], dn);
             nm = fmaf(f, row[tid], nm);
         }
-        if (p.ncl == 1) {
+        if (p.ncl == 1 && out) {
             store_out(out + ((int64_t)h * G + g) * HEAD_DIM + tid, dn > 0.f ? nm / dn : 0.f);
         } else {
             float *pa = p.part + (((int64_t)h * p.ncl + kcl) * G + g) * STEP_PART_LD;
@@ -486,29 +538,49 @@ __global__ void __launch_bounds__(STEP_THREADS, 2) step_kernel(const StepParams 
             }
         }
     }
-    if (p.ncl == 1) {
+    if (p.ncl == 1 && out) {
         if (tid == 0 && p.cnt) p.cnt[h] = (int)rows_f;
         step_stamp(p, 7);
         return;
     }
-    __threadfence();
-    __syncthreads();
-    if (tid == 0) s_flag = atomicAdd(p.ticket + h, 1) == p.ncl - 1;
+    if (!out) {                                            // the output product merges the clusters' partials itself
+        step_stamp(p, 7);
+        return;
+    }
+    __syncthreads();                                       // every thread's partial stores are ordered before thread 0's fence
+    if (tid == 0) {
+        __threadfence();                                   // cumulative: the CTA's stores are visible before the ticket moves
+        s_flag = atomicAdd(p.ticket + h, 1) == p.ncl - 1;
+    }
     __syncthreads();
     if (!s_flag) return;
     __threadfence();
+    // the last of the head's clusters merges them all: every value is requested before any is used
     const float *src = p.part + (int64_t)h * p.ncl * G * STEP_PART_LD;
     float total_rows = 0.f;
     for (int g = 0; g < G; ++g) {
+        float pm[STEP_CS], pd[STEP_CS], pn[STEP_CS], pr[STEP_CS];
+#pragma unroll
+        for (int k = 0; k < STEP_CS; ++k) {
+            pm[k] = NEG_BIG; pd[k] = pn[k] = pr[k] = 0.f;
+            if (k < p.ncl) {
+                const float *row = src + ((size_t)k * G + g) * STEP_PART_LD;
+                pm[k] = __ldcg(row + 128);
+                pd[k] = __ldcg(row + 129);
+                pn[k] = __ldcg(row + tid);
+                if (g == 0) pr[k] = __ldcg(row + 130);
+            }
+        }
         float M = NEG_BIG;
-        for (int k = 0; k < p.ncl; ++k) M = fmaxf(M, __ldcg(src + ((size_t)k * G + g) * STEP_PART_LD + 128));
+#pragma unroll
+        for (int k = 0; k < STEP_CS; ++k) M = fmaxf(M, pm[k]);
         float dn = 0.f, nm = 0.f;
-        for (int k = 0; k < p.ncl; ++k) {
-            const float *row = src + ((size_t)k * G + g) * STEP_PART_LD;
-            const float f = fast_exp2(__ldcg(row + 128) - M);
-            dn = fmaf(f, __ldcg(row + 129), dn);
-            nm = fmaf(f, __ldcg(row + tid), nm);
-            if (g == 0) total_rows += __ldcg(row + 130);
+#pragma unroll
+        for (int k = 0; k < STEP_CS; ++k) {
+            const float f = fast_exp2(pm[k] - M);
+            dn = fmaf(f, pd[k], dn);
+            nm = fmaf(f, pn[k], nm);
+            total_rows += pr[k];
         }
         store_out(out + ((int64_t)h * G + g) * HEAD_DIM + tid, dn > 0.f ? nm / dn : 0.f);
     }
@@ -521,8 +593,29 @@ __global__ void __launch_bounds__(STEP_THREADS, 2) step_kernel(const StepParams 
 
 using StepKern = void (*)(const StepParams);
 
+static int step_stages() {
+    static const int st = [] { const char *e = getenv("SKV_STEP_STAGES"); return e && e[0] == '3' ? 3 : STEP_STAGES; }();
+    return st;
+}
 static StepKern step_kernel_for(int G) {
+    if (step_stages() == 3)
+        return G <= 2 ? step_kernel<3, 2> : (G <= 4 ? step_kernel<3, 4> : step_kernel<3, 8>);
     return G <= 2 ? step_kernel<STEP_STAGES, 2> : (G <= 4 ? step_kernel<STEP_STAGES, 4> : step_kernel<STEP_STAGES, 8>);
+}
+
+// The kernel's dynamic shared memory limit only ever grows: one record per device and kernel variant, shared by
+// the occupancy query and the launch (a smaller request must not lower what a larger shape configured).
+static int step_configure(StepKern kern, int G, size_t smem) {
+    static size_t configured[64][3] = {};
+    const int gsel = G <= 2 ? 0 : (G <= 4 ? 1 : 2);
+    int dev = 0;
+    SKV_CUDA_OK(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return SKV_E_RANGE;
+    if (configured[dev][gsel] < smem) {
+        SKV_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        configured[dev][gsel] = smem;
+    }
+    return SKV_OK;
 }
 
 // Clusters of 8 CTAs that one launch can keep resident on this device for (G, C); cached per device and shape.
@@ -534,10 +627,10 @@ static int step_resident_clusters(int G, int C) {
     if (cudaGetDevice(&dev) != cudaSuccess) return 0;
     for (int i = 0; i < used; ++i)
         if (cache[i].dev == dev && cache[i].G == G && cache[i].C == C) return cache[i].n;
-    const size_t smem = step_smem_bytes(G, C, STEP_STAGES);
+    const size_t smem = step_smem_bytes(G, C, step_stages());
     if ((int)smem > device_max_smem_optin()) return 0;
     StepKern kern = step_kernel_for(G);
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return 0;
+    if (step_configure(kern, G, smem) != SKV_OK) return 0;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(STEP_CS * 64, 1, 1);
     cfg.blockDim = dim3(STEP_THREADS, 1, 1);
@@ -560,7 +653,7 @@ using namespace skv;
 extern "C" void skv_debug_step_probe(void *dev_ptr) { skv::g_step_probe = static_cast<unsigned long long *>(dev_ptr); }
 
 extern "C" int skv_step_clusters(int heads, int G, int C, int summary_bits) {
-    if (heads <= 0 || G < 1 || G > 8 || C < 64 || (C & (C - 1)) || C > 4096 || summary_bits != 8) return 0;
+    if (heads <= 0 || G < 1 || G > 8 || C < 64 || (C & (C - 1)) || C > 2048 || summary_bits != 8) return 0;
     const int resident = step_resident_clusters(G, C);
     if (resident < heads) return 0;                         // more than one wave of clusters: the two-launch path streams better
     int ncl = resident / heads;
@@ -577,7 +670,7 @@ extern "C" int skv_step(const skv_state *st, const void *q, int G, const int32_t
                         int64_t k_head_stride, int64_t k_row_stride, int64_t v_head_stride, int64_t v_row_stride,
                         float *w, uint32_t *selbits, int32_t *cnt, void *out, void *workspace, int clusters,
                         float scale, const skv_rope *rope, void *stream) {
-    if (!st || !n_dev || !K || !V || !out || !workspace) return SKV_E_NULL;
+    if (!st || !n_dev || !K || !V || !workspace) return SKV_E_NULL;
     if (!q && !rope) return SKV_E_NULL;
     if (rope) {
         if (!rope->qkv || !rope->q_norm_w || !rope->k_norm_w || !rope->cos_table || !rope->sin_table || !rope->pos ||
@@ -593,16 +686,16 @@ extern "C" int skv_step(const skv_state *st, const void *q, int G, const int32_t
     if (!st->count || !st->n_c || !st->end || !st->need || !st->labels || !st->mmax || !st->mmin || !st->dir8)
         return SKV_E_NULL;
     if (st->d != HEAD_DIM || G < 1 || G > 8) return SKV_E_DIM;
-    if (st->C < 64 || (st->C & (st->C - 1)) || st->C > 4096) return SKV_E_DIM;
+    if (st->C < 64 || (st->C & (st->C - 1)) || st->C > 2048 || clusters > STEP_CS) return SKV_E_DIM;
     if (st->summary_bits != 8) return SKV_E_RANGE;
     if (st->heads <= 0 || st->heads > 65535 || st->capacity <= 0 || clusters < 1 || clusters > 64) return SKV_E_RANGE;
     if (st->capacity % 8 || !aligned16(st->labels) || !aligned16(st->dir8) || !aligned16(workspace) || !aligned16(K) ||
-        !aligned16(V) || !aligned16(out) || (q && !aligned16(q)))
+        !aligned16(V) || (out && !aligned16(out)) || (q && !aligned16(q)))
         return SKV_E_ALIGN;
     if ((k_row_stride * 2) % 16 || (v_row_stride * 2) % 16 || (k_head_stride * 2) % 16 || (v_head_stride * 2) % 16 ||
         k_row_stride < HEAD_DIM || v_row_stride < HEAD_DIM)
         return SKV_E_ALIGN;
-    const size_t smem = step_smem_bytes(G, st->C, STEP_STAGES);
+    const size_t smem = step_smem_bytes(G, st->C, step_stages());
     if ((int)smem > device_max_smem_optin()) return SKV_E_DIM;
     StepParams p;
     p.st = *st; p.q = q; p.K = K; p.V = V; p.n_dev = n_dev; p.out = out; p.w = w; p.selbits = selbits; p.cnt = cnt;
@@ -614,15 +707,11 @@ extern "C" int skv_step(const skv_state *st, const void *q, int G, const int32_t
     p.scale = scale; p.scale_log2 = scale * LOG2E;
     p.rope = rope ? *rope : skv_rope{};
     p.probe = g_step_probe;
+    { static const int dbg = [] { const char *e = getenv("SKV_STEP_DBG"); return e ? atoi(e) : 0; }(); p.dbg = dbg; }
     StepKern kern = step_kernel_for(G);
-    static size_t configured[64][3] = {};
-    const int gsel = G <= 2 ? 0 : (G <= 4 ? 1 : 2);
-    int dev = 0;
-    SKV_CUDA_OK(cudaGetDevice(&dev));
-    if (dev < 0 || dev >= 64) return SKV_E_RANGE;
-    if (configured[dev][gsel] < smem) {
-        SKV_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        configured[dev][gsel] = smem;
+    {
+        const int rc = step_configure(kern, G, smem);
+        if (rc) return rc;
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(STEP_CS * clusters, st->heads, 1);
@@ -635,7 +724,11 @@ extern "C" int skv_step(const skv_state *st, const void *q, int G, const int32_t
     attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = pdl_enabled() ? 2 : 1;
+    // The launch does not ask for programmatic serialization itself: measured on B200, a cluster launch scheduled
+    // while the kernel ahead still runs costs the decode step 10 us per layer (its clusters start late), far more
+    // than the early loads save.  It still triggers its dependents early (SKV_STEP_PDL=1 restores the attribute).
+    static const bool step_pdl = [] { const char *e = getenv("SKV_STEP_PDL"); return e && e[0] == '1'; }();
+    cfg.numAttrs = pdl_enabled() && step_pdl ? 2 : 1;
     SKV_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, p));
     SKV_CUDA_OK(cudaGetLastError());
     return SKV_OK;

@@ -21,7 +21,7 @@ import torch.nn.functional as F
 
 from . import _lib
 from ._lib import check, dtype_code, lib, stream_ptr
-from .cluster_state import ClusterArena, SphereIndexGraph, fit_layers
+from .cluster_state import AttentionPartials, ClusterArena, SphereIndexGraph, fit_layers
 from .qwen3 import Qwen3Model, apply_rope
 
 
@@ -133,6 +133,8 @@ class GraphDecoder:
         # up to this many bytes of partial sums every CTA of the consuming product adds up for itself; beyond it one
         # reduce launch does (4 GPUs x 4 sequences, 128 KB: 2,096 tok/s with the launch, 1,955 without)
         self.fuse_sum_bytes = 65536
+        # the attention's last log-sum-exp merge rides in the output product (SKV_DEFER_MERGE=0: in the attention launch)
+        self.defer_merge = os.environ.get("SKV_DEFER_MERGE", "1") != "0"
         self.fused_insert = fused_insert and mode == "cluster" and window >= 1
         self.insert_all = None
 
@@ -315,6 +317,15 @@ class GraphDecoder:
             that exchange number instead of ``y`` (returns the number), else all-reduce ``y`` over ``tp`` when
             given.  Returns (residual buffer now current, result: tensor or exchange number)."""
             N, K = W.shape
+            if isinstance(x, AttentionPartials):            # the attention's last merge happens inside this product
+                to_slot = slot_out is not None
+                check(L.skv_gemv_attended(W.data_ptr(), N, K, None if to_slot else y.data_ptr(), B,
+                                          x.workspace.data_ptr(), x.clusters, x.G, x.cnt.data_ptr(),
+                                          peer.ref() if to_slot else None, slot_out if to_slot else 0, st),
+                      "skv_gemv_attended")
+                if to_slot:
+                    return h_out, slot_out
+                return h_out, (tp.all_reduce(y) if tp is not None else y)
             from_slot = isinstance(dl, int)
             own = bool(L.skv_gemv_supported(N, K, B, 3 if from_slot else mode))
             # every CTA of the product adds the ranks' partials up for itself only while that is a few KB
@@ -358,6 +369,9 @@ class GraphDecoder:
             h = res if res is not None else h
             h2 = buf_b if h is buf_a else buf_a
             kc, vc = self.cache.k[i], self.cache.v[i]
+            # the output product merges the attention's split partials itself where it is the library's own product
+            defer = self.mode == "cluster" and self.defer_merge and bool(
+                L.skv_gemv_supported(a.o.weight.shape[0], a.o.weight.shape[1], B, 0))
             fold = (self.mode == "cluster" and self.fold_rope and self.attn[i]._fused_rows(self._heads(kc)))
             if fold:
                 # QK-norm, rotary and the cache write ride in the selection launch: six launches per layer
@@ -366,7 +380,7 @@ class GraphDecoder:
                                     kc.data_ptr(), vc.data_ptr(), H, H_kv, kc.stride(0), kc.stride(1), kc.stride(2),
                                     a.q_norm.eps, 0)
                 out = self.attn[i].step(qh, self._heads(kc), self._heads(vc), self.n_dev,
-                                        insert=self.insert_all is None, rope=rope)
+                                        insert=self.insert_all is None, rope=rope, defer_merge=defer)
             else:
                 check(L.skv_qk_rope_cache(qkv.data_ptr(), a.q_norm.weight.data_ptr(), a.k_norm.weight.data_ptr(),
                                           m.rope_cos.data_ptr(), m.rope_sin.data_ptr(), self.pos.data_ptr(),
@@ -376,7 +390,7 @@ class GraphDecoder:
                     out = self.attn[i](qh, self._heads(kc), self._heads(vc), self.n_dev)
                 else:
                     out = self.attn[i].step(qh, self._heads(kc), self._heads(vc), self.n_dev,
-                                            insert=self.insert_all is None)
+                                            insert=self.insert_all is None, defer_merge=defer)
             _, o_red = product(a.o.weight, o, 0, x=out, tp=a.tp,
                                slot_out=2 * i if peer_ok(a.o.weight, 0) else None)
             res, _ = product(self._wgu[i], gu, 1, h_in=h, dl=o_red, g=layer.norm2.weight, h_out=h2)

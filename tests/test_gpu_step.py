@@ -9,7 +9,7 @@ import pytest
 import torch
 
 from oracle import cluster_oracle as oc
-from sparse_kv_reads_b200._lib import lib
+from sparse_kv_reads_b200._lib import check, lib
 from sparse_kv_reads_b200.cluster_state import SphereIndexGraph
 from _helpers import DEV, device_index_from_oracle, isotropic_stream
 
@@ -63,6 +63,18 @@ def test_one_launch_step_equals_the_two_launches_and_the_oracle(h, G, n, C, budg
         if torch.equal(w1, w2):
             assert torch.equal(cnt1, cnt2) and torch.equal(bits1, bits2)
             assert float((one.float() - two.float()).abs().max()) <= 1e-2
+        # the last merge left to the output product: y = out . W^T straight from the clusters' partials
+        ix.cnt.fill_(-3)
+        parts = ix._step_one_launch(q, Kd, Vd, n_dev, None, ncl, defer_merge=True)
+        Kin, N = h * G * 128, 192
+        W = (torch.randn(N, Kin, generator=torch.Generator().manual_seed(t)) / Kin ** 0.5).to(torch.bfloat16).to(DEV)
+        y = torch.empty(1, N, dtype=torch.bfloat16, device=DEV)
+        check(lib().skv_gemv_attended(W.data_ptr(), N, Kin, y.data_ptr(), 1, parts.workspace.data_ptr(), parts.clusters,
+                                      parts.G, parts.cnt.data_ptr(), None, 0, torch.cuda.current_stream().cuda_stream),
+              "skv_gemv_attended")
+        want = one.view(1, Kin).float() @ W.float().T
+        torch.testing.assert_close(y.float(), want, rtol=2e-2, atol=2e-2)
+        assert torch.equal(ix.cnt, cnt1)
     assert ix.check_status() == 0
 
 
