@@ -25,7 +25,6 @@ namespace skv {
 constexpr int STEP_THREADS = 128, STEP_WARPS = 4, STEP_CS = 8, STEP_LPT = 8, STEP_STAGES = 2;
 constexpr int STEP_SUB = STEP_THREADS * STEP_LPT;         // positions listed per pass
 constexpr int STEP_SLICES = STEP_CS * STEP_WARPS;         // (CTA, warp) pairs that score a head's clusters
-constexpr int STEP_GROUPS = 8;                            // 8-cluster groups a warp scores at most (2,048 slots)
 static_assert(STEP_SLICES == 32, "a warp's lanes stand for the slices when their statistics are combined");
 constexpr int STEP_PART_LD = 132;                         // floats per partial row: 128 sums, max, sum, rows, unused
 
@@ -44,7 +43,6 @@ struct StepParams {
     int64_t ksh, ksr, vsh, vsr;
     float scale, scale_log2;
     skv_rope rope;
-    int dbg;
     unsigned long long *probe; // optional [CTAs][16] phase time stamps (probe builds only)
 };
 
@@ -196,7 +194,6 @@ __global__ void __launch_bounds__(STEP_THREADS, 2) step_kernel(const StepParams 
     const int h = blockIdx.y, split = blockIdx.x, S = gridDim.x;
     const unsigned rank = cluster_rank();
     const int C = p.st.C, G = p.G;
-    if (p.dbg & 1) pdl_wait();
     cluster_arrive();                                      // barrier 0: "my shared memory exists"; waited for ahead of the first remote store
     step_stamp(p, 0);
 
@@ -208,8 +205,6 @@ __global__ void __launch_bounds__(STEP_THREADS, 2) step_kernel(const StepParams 
     float *smx = cntf + C, *smn = smx + per_max;                              // [per_max] key lengths of this CTA's clusters
     float *stat = smn + per_max;                                              // [32 slices][GP][2] (max, sum of exp)
     float *fac = stat + STEP_SLICES * GP * 2;                                 // [32 slices][GP] exp(max - M) / T
-    uint32_t *key = reinterpret_cast<uint32_t *>(smem);                       // [C], over sumst once it is scored
-    uint8_t *sel = reinterpret_cast<uint8_t *>(key + C);                      // [C + 1]
     unsigned char *tail = smem + step_front_bytes(G, C, STAGES);
     uint32_t *s_bits = reinterpret_cast<uint32_t *>(tail);
     tail += ((size_t)(C / 32 + 1) * 4 + 15) & ~size_t(15);
@@ -285,7 +280,6 @@ __global__ void __launch_bounds__(STEP_THREADS, 2) step_kernel(const StepParams 
     // query head with shuffles, and leaves exp(score - maximum): its clusters are one of the head's 32 "slices"
     // (8 CTAs x 4 warps), whose statistics every CTA later combines into the softmax over all clusters.
     const int nrow = lane >> 2, jq = lane & 3;
-    float zr[STEP_GROUPS][2];
     float w_max = -INFINITY, w_sum = 0.f;
     {
         uint32_t qa[8][4];
@@ -296,11 +290,9 @@ __global__ void __launch_bounds__(STEP_THREADS, 2) step_kernel(const StepParams 
             qa[ks][2] = nrow < G ? step_pack_half2(q0[2], q0[3]) : 0u;
             qa[ks][1] = qa[ks][3] = 0u;                                       // at most 8 query heads: rows 8..15 unused
         }
-#pragma unroll
-        for (int gi = 0; gi < STEP_GROUPS; ++gi) {
-            const int cb = (gi * STEP_WARPS + warp) * 8;
-            zr[gi][0] = zr[gi][1] = -INFINITY;
-            if (cb >= mine) continue;                                         // warp-uniform
+        // (rolled on purpose: the kernel runs every phase once, so its speed follows its code size)
+#pragma unroll 1
+        for (int cb = warp * 8; cb < mine; cb += STEP_WARPS * 8) {
             const int c = cb + nrow;
             int4 ra = make_int4(0, 0, 0, 0), rb = ra;
             if (c < mine) {
@@ -330,21 +322,22 @@ __global__ void __launch_bounds__(STEP_THREADS, 2) step_kernel(const StepParams 
                     const float pr = (acc[i] + acd[i]) * inv;
                     float e = pr >= 0.f ? smx[cl] * pr : smn[cl] * pr;
                     if (cntf[c_lo + cl] == 0.f) e = -INFINITY;
-                    zr[gi][i] = e * p.scale;
-                    w_max = fmaxf(w_max, zr[gi][i]);
+                    const float zz = e * p.scale;
+                    zall[nrow * C + c_lo + cl] = zz;                          // read back below by this same thread
+                    w_max = fmaxf(w_max, zz);
                 }
             }
         }
         w_max = fmaxf(w_max, __shfl_xor_sync(0xffffffffu, w_max, 1));         // over the four lanes of a query head
         w_max = fmaxf(w_max, __shfl_xor_sync(0xffffffffu, w_max, 2));
-#pragma unroll
-        for (int gi = 0; gi < STEP_GROUPS; ++gi) {
-            const int cb = (gi * STEP_WARPS + warp) * 8;
+#pragma unroll 1
+        for (int cb = warp * 8; cb < mine; cb += STEP_WARPS * 8) {
 #pragma unroll
             for (int i = 0; i < 2; ++i) {
                 const int cl = cb + 2 * jq + i;
                 if (cl < mine && nrow < G) {
-                    const float ex = zr[gi][i] > -INFINITY ? expf(zr[gi][i] - w_max) : 0.f;
+                    const float zz = zall[nrow * C + c_lo + cl];
+                    const float ex = zz > -INFINITY ? expf(zz - w_max) : 0.f;
                     zall[nrow * C + c_lo + cl] = ex;
                     w_sum += ex;
                 }
@@ -393,6 +386,8 @@ __global__ void __launch_bounds__(STEP_THREADS, 2) step_kernel(const StepParams 
             const float T = warp_sum(e0 * st.y);
             fac[lane * GP + g] = T > 0.f ? e0 / T : 0.f;
         }
+        uint32_t *key = reinterpret_cast<uint32_t *>(smem);                   // [C], over sumst once it is scored
+        uint8_t *sel = reinterpret_cast<uint8_t *>(key + C);                  // [C + 1]
         for (int c = tid; c < C; c += STEP_THREADS) sel[c] = 0;
         if (tid == 0) sel[C] = 1;
         __syncthreads();
@@ -502,7 +497,6 @@ __global__ void __launch_bounds__(STEP_THREADS, 2) step_kernel(const StepParams 
             remote_store(remote_addr(dst + 130, 0), (float)read_rows);
         }
     }
-    if (p.dbg & 2) pdl_trigger();
     cluster_arrive();                                      // barrier 2: the cluster's partials are in its first CTA
     cluster_wait();
     step_stamp(p, 6);
@@ -593,13 +587,9 @@ __global__ void __launch_bounds__(STEP_THREADS, 2) step_kernel(const StepParams 
 
 using StepKern = void (*)(const StepParams);
 
-static int step_stages() {
-    static const int st = [] { const char *e = getenv("SKV_STEP_STAGES"); return e && e[0] == '3' ? 3 : STEP_STAGES; }();
-    return st;
-}
+// (a ring of three tiles per warp was measured: 35.0 against 35.2 us per layer at 8 heads, not worth 32 KB per CTA)
+static int step_stages() { return STEP_STAGES; }
 static StepKern step_kernel_for(int G) {
-    if (step_stages() == 3)
-        return G <= 2 ? step_kernel<3, 2> : (G <= 4 ? step_kernel<3, 4> : step_kernel<3, 8>);
     return G <= 2 ? step_kernel<STEP_STAGES, 2> : (G <= 4 ? step_kernel<STEP_STAGES, 4> : step_kernel<STEP_STAGES, 8>);
 }
 
@@ -707,7 +697,6 @@ extern "C" int skv_step(const skv_state *st, const void *q, int G, const int32_t
     p.scale = scale; p.scale_log2 = scale * LOG2E;
     p.rope = rope ? *rope : skv_rope{};
     p.probe = g_step_probe;
-    { static const int dbg = [] { const char *e = getenv("SKV_STEP_DBG"); return e ? atoi(e) : 0; }(); p.dbg = dbg; }
     StepKern kern = step_kernel_for(G);
     {
         const int rc = step_configure(kern, G, smem);

@@ -119,3 +119,38 @@ def test_one_launch_step_at_the_benchmark_shape():
     dense = oc.attend_rows(q, Kb[:, :256], Vb[:, :256], [torch.arange(40)] * h)
     assert float((got.cpu().double() - dense).abs().max()) <= 1e-2
     assert short.cnt.cpu().tolist() == [40] * h
+
+
+def test_one_launch_step_takes_exact_ties_in_slot_order():
+    """Eight clusters with identical summaries (scored by one warp, so their shared scores are the same bits) and a
+    budget that ends inside them: the lower slots are taken first, as the oracle's stable ranking does."""
+    h, G, n, C = 4, 2, 3000, 256
+    cap = -(-(n + 16) // 8) * 8
+    Q, K, V = isotropic_stream(h, cap, h * G, seed=41)
+    st = oc.ClusterOracle(C=C, C_init=64, cap_keys=40.0, window=64, delta=math.inf, capacity=cap, summary_bits=8)
+    st.observe(K, n)
+    for name in ("sum_dir", "dir8", "mmax", "mmin"):
+        t = getattr(st, name)
+        t[:, 8:16] = t[:, 8:9]
+    st.count[:, 8:16] = torch.tensor([7.0, 3.0, 9.0, 4.0, 6.0, 5.0, 8.0, 2.0])
+    ix = device_index_from_oracle(st, budget=0.3)
+    ncl = lib().skv_step_clusters(h, G, C, 8)
+    Kd, Vd = K.to(DEV), V.to(DEV)
+    n_dev = torch.tensor([n], dtype=torch.int32, device=DEV)
+    q = Q[0]
+    shared = st.shared_score(st.scores(q.float()))
+    assert all(len(set(shared[i, 8:16].tolist())) == 1 for i in range(h))
+    for into in (1, 12, 25, 40):                            # keys of the tied clusters the budget reaches into
+        # per head the need differs; the kernel takes one need per head from need_dev
+        needs = []
+        for i in range(h):
+            ahead = float(st.count[i][shared[i] > shared[i, 8]].sum())
+            needs.append(int(ahead) + into)
+        ix.need_dev.copy_(torch.tensor(needs, dtype=torch.int32))
+        ix._step_one_launch(q.to(DEV), Kd, Vd, n_dev, None, ncl)
+        w = ix.wbuf.cpu()
+        for i in range(h):
+            want = oc.ClusterOracle.take_until(shared[i:i + 1], st.count[i:i + 1], needs[i])[0]
+            assert torch.equal(w[i, :C] > 0, want), (into, i)
+            tied = (w[i, 8:16] > 0).tolist()
+            assert tied == sorted(tied, reverse=True) and any(tied) and not all(tied)
