@@ -39,7 +39,7 @@ WORKLOADS = {
 DEFAULT = "qwen3-0.6b_b1_32k_budget20"
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the workload's dominant kernel, from an ncu capture
 # of that workload (a constant copied from the capture's summary; workloads without a capture report null)
-NCU_TRAFFIC = {}
+NCU_TRAFFIC = {"qwen3-0.6b_b1_32k_budget20": 29.04e6}
 
 
 def peaks() -> tuple[float, str]:
@@ -408,7 +408,7 @@ def gpu_arm(args, wl) -> None:
                 "clocks": clocks.summary(), "roofline": roof, "layer_step": layer,
                 "prompt_fit_s": fit_s, "device_status": status,
                 "splits": sum(ix.splits for ix in dec.attn)}
-        if world == 1:
+        if world == 1 and not args.no_extra:
             xs, xw = min(K_steps, 32), min(W, 4)
             tok_s, ms, _ = exact_leg(model, cache, ids_dev, pos, xs, xw)
             line["exact"] = {"value": tok_s, "unit": "tok/s", "ms_per_step": ms, "steps": xs,
@@ -441,6 +441,7 @@ def main() -> None:
     ap.add_argument("--workload", default=DEFAULT, choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-extra", action="store_true", help="skip the exact-attention and batch-32 legs (profiling runs)")
     ap.add_argument("--ncu-range", action="store_true",
                     help="bracket the timed device leg with cudaProfilerStart/Stop (for ncu --profile-from-start off)")
     args = ap.parse_args()

@@ -110,6 +110,19 @@ int skv_attend(const void *q, const void *K, const void *V, const int32_t *idx, 
                int64_t k_head_stride, int64_t k_row_stride, int64_t v_head_stride, int64_t v_row_stride,
                int64_t idx_stride, int rows_limit, int splits, float scale, void *stream);
 
+/* Attention over the cached rows [0, n_dev[0]) with a WEIGHT per cluster: a row whose label is l enters the
+ * softmax with weight w[l] (log w[l] is added to its score); rows of weight 0 are not read.  With 0/1 weights this
+ * is skv_attend over the selected rows; fractional weights carry the clusters drawn among the ones the selection
+ * left out (ssa/attn/tail_sample.py:35-63), each weighted draws / (S x probability).  Replaces the label-weighted
+ * attention of attend_sampled (ssa/kernels/sphere_fused.py:503-518; spec ssa/attn/labeled.py:24-44).
+ *   labels [heads, label_stride] int16, w [heads, C+1] float32 (column C = the always-read rows); G <= 8;
+ *   q, K, V, out, workspace, splits as in skv_attend (float32 arithmetic on the CUDA cores: an eager-API call). */
+int skv_attend_weighted(const void *q, const void *K, const void *V, const int16_t *labels, int64_t label_stride,
+                        const float *w, int C, const int32_t *n_dev, void *out, void *workspace, int32_t *status,
+                        int heads, int G, int d, int dtype,
+                        int64_t k_head_stride, int64_t k_row_stride, int64_t v_head_stride, int64_t v_row_stride,
+                        int splits, float scale, void *stream);
+
 /* Fixed capacity, in bytes, of the scratch array behind skv_attend_static. */
 #define SKV_STATIC_SCRATCH_BYTES (8 * 1024 * 1024)
 

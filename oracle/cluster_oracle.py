@@ -458,11 +458,61 @@ class ClusterOracle:
             w[:, :self.C] = self.take_until(self.shared_score(self.scores(q), group), self.count, need).float()
         return self.labels[:, :n], w
 
+    def select_sampled(self, q: torch.Tensor, *, n: int, budget: float, S: int, alpha: float,
+                       generator: torch.Generator | None = None):
+        """The selection plus ``S`` draws among the clusters it left out, as fractional weights
+        (``attend_sampled``, ssa/kernels/sphere_fused.py:503-518).  Returns ``(labels, w [h, C+1])``."""
+        labels, w = self.select(q, n=n, budget=budget)
+        w = w.clone()
+        if S > 0 and self.end > 1 and self.need(budget) > 0:
+            prop = sampling_proposal(self.scores(q), self.count, scale=1.0 / math.sqrt(self.d))
+            w[:, :self.C] = sampled_weights(prop, self.count, w[:, :self.C] > 0, S=S, alpha=alpha, generator=generator)
+        return labels, w
+
     def positions(self, w: torch.Tensor, n: int) -> list[torch.Tensor]:
         """Ascending positions read per head: rows whose label has positive weight
         (the set that ssa/kernels/graph_kernels.py:144-155 lists, in position order)."""
         lab = self.labels[:, :n].long()
         return [(w[i][lab[i]] > 0).nonzero().squeeze(1) for i in range(self.h)]
+
+
+# --------------------------------------------------------------------------------------------
+# sampling the clusters that were not selected                    (ssa/attn/tail_sample.py:24-63)
+# --------------------------------------------------------------------------------------------
+def sampling_proposal(e: torch.Tensor, count: torch.Tensor, *, scale: float) -> torch.Tensor:
+    """Probability of drawing each cluster, ``[h, C]``, rows summing to 1: per query head the estimated mass
+    ``count x exp(scale x e)`` normalised over the clusters, then the mean over the group's query heads
+    (``proposal_from_scores``, tail_sample.py:24-32).  ``e [h, G, C]`` with -inf for empty clusters."""
+    z = e * scale
+    z = z - z.amax(dim=2, keepdim=True)
+    mass = torch.nan_to_num(count.unsqueeze(1) * z.exp(), nan=0.0)
+    return (mass / mass.sum(dim=2, keepdim=True).clamp_min(1e-300)).mean(dim=1)
+
+
+def sampled_weights(prop: torch.Tensor, count: torch.Tensor, taken: torch.Tensor, *, S: int, alpha: float,
+                    generator: torch.Generator | None = None) -> torch.Tensor:
+    """Cluster weights ``[h, C]`` when ``S`` of the clusters that were not taken are drawn by systematic sampling
+    (``tail_sample_weights``, tail_sample.py:35-63): 1 for a taken, non-empty cluster; ``draws / (S x pi)`` for a
+    drawn one, where ``pi`` mixes the proposal restricted to the rest with a uniform floor ``alpha``; 0 otherwise.
+    One uniform number per head (drawn on the CPU from ``generator``) places the S equally spaced probes."""
+    live = count > 0
+    w_taken = (taken & live).to(prop.dtype)
+    rest = live & ~taken
+    if S <= 0:
+        return w_taken
+    n_rest = rest.sum(1, keepdim=True).clamp_min(1)
+    p = prop * rest
+    p = p / p.sum(1, keepdim=True).clamp_min(1e-300)
+    pi = ((1 - alpha) * p + alpha / n_rest) * rest
+    cdf = pi.cumsum(1)
+    h, C = pi.shape
+    u = torch.rand(h, 1, generator=generator, dtype=prop.dtype, device="cpu").to(prop.device) / S
+    probes = (u + torch.arange(S, dtype=prop.dtype, device=prop.device) / S) * cdf[:, -1:]
+    hit = torch.searchsorted(cdf.contiguous(), probes.contiguous()).clamp_(max=C - 1)
+    draws = torch.zeros_like(prop).scatter_add_(1, hit, torch.ones_like(probes))
+    draws = draws * rest.any(1, keepdim=True)
+    w_drawn = torch.where(rest & (draws > 0), draws / (S * pi.clamp_min(1e-300)), torch.zeros_like(prop))
+    return w_taken + w_drawn
 
 
 # --------------------------------------------------------------------------------------------

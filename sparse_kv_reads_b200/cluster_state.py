@@ -576,6 +576,36 @@ class SphereIndexGraph:
         labels, w = self.labels_and_weights(q, n=n, budget=budget, group=group)
         return self._attend(q, K, V), labels, w
 
+    def attend_sampled(self, q: torch.Tensor, K: torch.Tensor, V: torch.Tensor, *, n: int, budget: float, S: int,
+                       alpha: float, generator: torch.Generator | None = None):
+        """``attend`` plus ``S`` clusters drawn among the ones the selection left out; a drawn cluster is read in
+        full and weighted ``draws / (S pi)`` (``tail_sample``), which keeps the attention sums unbiased.
+        Returns ``(out [H, d], labels, w [h, C+1])`` (ssa/kernels/sphere_fused.py:503-518)."""
+        from .tail_sample import proposal_from_scores, tail_sample_weights
+        self.observe(K, n)
+        H, d = q.shape
+        G = H // self.H_kv
+        if G > 8:
+            raise ValueError("attend_sampled serves groups of at most 8 query heads")
+        e = torch.empty(self.H_kv, G, self.C, dtype=torch.float32, device=q.device)
+        labels, w = self.labels_and_weights(q, n=n, budget=budget, e_out=e)
+        w2 = w.clone()
+        if S > 0 and self.end > 1 and math.ceil(budget * (self.end - 1)) > 0:
+            prop = proposal_from_scores(e, self.count, scale=1.0 / math.sqrt(d))
+            w2[:, :self.C] = tail_sample_weights(prop, self.count, w[:, :self.C] > 0, S=S, alpha=alpha,
+                                                 generator=generator)
+        if not q.is_contiguous():
+            q = q.contiguous()
+        self._attend_buffers(q)
+        self._n_scalar.fill_(n)
+        check(lib().skv_attend_weighted(q.data_ptr(), K.data_ptr(), V.data_ptr(), self.labels.data_ptr(),
+                                        self.labels.stride(0), w2.data_ptr(), self.C, self._n_scalar.data_ptr(),
+                                        self.out.data_ptr(), self._attn_ws.data_ptr(), self.status.data_ptr(),
+                                        self.H_kv, G, d, dtype_code(K.dtype), K.stride(0), K.stride(1), V.stride(0),
+                                        V.stride(1), self.num_splits, 1.0 / math.sqrt(d), stream_ptr(q.device)),
+              "skv_attend_weighted")
+        return self.out, labels, w2
+
     # ---- graph-safe calls --------------------------------------------------------------------------
     def prepare(self, K: torch.Tensor, n: int, H: int, fitted: bool = False) -> None:
         """Build from the prefilled cache holding ``n`` positions (eager) and allocate the step's fixed

@@ -36,6 +36,9 @@ struct AttendParams {
     int64_t lab_stride;
     int sel_words, C;
     unsigned long long *probe;  // optional [CTAs][8] phase time stamps (ns), for tuning
+    // fractional cluster weights (rows of sampled clusters): a row of label l enters the softmax with weight wl[l],
+    // i.e. log2(wl[l]) is added to its score; rows of weight 0 are not read.  Needs labels, lab_stride and C.
+    const float *wl;           // [heads, C + 1] or null
 };
 
 static unsigned long long *g_attend_probe = nullptr;
@@ -352,10 +355,18 @@ __global__ void __launch_bounds__(128) attend_simple_kernel(const AttendParams p
             for (int i = 0; i < 8; ++i) qr[g][i] = 0.f;
     }
     for (int t = sh.t0; t < sh.t1; ++t) {
-        const int mypos = fetch_pos(p, head, t * TILE_ROWS + sub, sh.count);
+        int mypos = fetch_pos(p, head, t * TILE_ROWS + sub, sh.count);
+        float mylw = 0.f;
+        if (p.wl && mypos >= 0) {                           // the row's weight, by its label
+            const unsigned l = (unsigned)(int)p.labels[(int64_t)head * p.lab_stride + mypos];
+            const float wgt = l <= (unsigned)p.C ? p.wl[(int64_t)head * (p.C + 1) + l] : 0.f;
+            if (wgt > 0.f) mylw = log2f(wgt);
+            else mypos = -1;
+        }
 #pragma unroll 2
         for (int i = 0; i < 8; ++i) {
             const int pos = __shfl_sync(0xffffffffu, mypos, half + 2 * i);
+            const float lw = __shfl_sync(0xffffffffu, mylw, half + 2 * i);
             if (pos < 0) continue;                          // uniform within the half warp
             float kv[8], vv[8];
             load8(Kb + (int64_t)pos * p.ksr + sub * 8, kv);
@@ -367,7 +378,7 @@ __global__ void __launch_bounds__(128) attend_simple_kernel(const AttendParams p
                 for (int e = 0; e < 8; ++e) s = fmaf(qr[g][e], kv[e], s);
 #pragma unroll
                 for (int o = 8; o > 0; o >>= 1) s += __shfl_xor_sync(hmask, s, o, 16);
-                const float z = s * p.scale_log2;
+                const float z = fmaf(s, p.scale_log2, lw);
                 const float mn = fmaxf(m[g], z);
                 const float al = exp2f(m[g] - mn), pr = exp2f(z - mn);
                 m[g] = mn;
@@ -527,7 +538,7 @@ extern "C" int skv_attend(const void *q, const void *K, const void *V, const int
     p.idx_stride = idx_stride; p.rows_limit = rows_limit; p.splits = splits;
     p.scale_log2 = scale * LOG2E;
     p.labels = nullptr; p.selbits = nullptr; p.cnt_out = nullptr; p.lab_stride = 0; p.sel_words = 0; p.C = 0;
-    p.probe = nullptr;
+    p.probe = nullptr; p.wl = nullptr;
     dim3 grid(splits, heads);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (base == SKV_F32) return launch_simple<float>(p, grid, st);
@@ -559,12 +570,38 @@ extern "C" int skv_attend_labels(const void *q, const void *K, const void *V, co
     p.ksh = k_head_stride; p.ksr = k_row_stride; p.vsh = v_head_stride; p.vsr = v_row_stride;
     p.idx_stride = 0; p.rows_limit = 0; p.splits = splits;
     p.scale_log2 = scale * LOG2E;
-    p.probe = g_attend_probe;
+    p.probe = g_attend_probe; p.wl = nullptr;
     p.labels = labels; p.selbits = selbits; p.cnt_out = cnt; p.lab_stride = label_stride;
     p.sel_words = C / 32 + 1; p.C = C;
     dim3 grid(splits, heads);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     return G > 8 ? launch_labels<true>(p, grid, st) : launch_labels<false>(p, grid, st);
+}
+
+extern "C" int skv_attend_weighted(const void *q, const void *K, const void *V, const int16_t *labels,
+                                   int64_t label_stride, const float *w, int C, const int32_t *n_dev, void *out,
+                                   void *workspace, int32_t *status, int heads, int G, int d, int dtype,
+                                   int64_t k_head_stride, int64_t k_row_stride, int64_t v_head_stride,
+                                   int64_t v_row_stride, int splits, float scale, void *stream) {
+    const int rc = attend_check(q, K, V, nullptr, nullptr, n_dev, out, workspace, heads, G, d, dtype, k_head_stride,
+                                k_row_stride, v_head_stride, v_row_stride, 0, splits);
+    if (rc) return rc;
+    if (!labels || !w) return SKV_E_NULL;
+    if (G > 8 || C < 16 || (C & (C - 1)) || C > 16384) return SKV_E_DIM;
+    if (label_stride <= 0) return SKV_E_RANGE;
+    AttendParams p;
+    p.q = q; p.K = K; p.V = V; p.idx = nullptr; p.cnt = nullptr; p.n_dev = n_dev; p.out = out; p.status = status;
+    p.part = static_cast<float *>(workspace);
+    p.ticket = reinterpret_cast<int32_t *>(p.part + (int64_t)heads * splits * G * PART_LD);
+    p.heads = heads; p.G = G;
+    p.ksh = k_head_stride; p.ksr = k_row_stride; p.vsh = v_head_stride; p.vsr = v_row_stride;
+    p.idx_stride = 0; p.rows_limit = 0; p.splits = splits;
+    p.scale_log2 = scale * LOG2E;
+    p.labels = labels; p.selbits = nullptr; p.cnt_out = nullptr; p.lab_stride = label_stride; p.sel_words = 0; p.C = C;
+    p.probe = nullptr; p.wl = w;
+    dim3 grid(splits, heads);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    return (dtype & 0xff) == SKV_F32 ? launch_simple<float>(p, grid, st) : launch_simple<__nv_bfloat16>(p, grid, st);
 }
 
 extern "C" int skv_merge(const float *m, const float *l, const float *a, float *out, int heads, int S, int G, int d,

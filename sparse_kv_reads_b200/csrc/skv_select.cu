@@ -157,9 +157,10 @@ __global__ void __launch_bounds__(SEL_THREADS) score_pick_kernel(const SelectPar
     int *hist = reinterpret_cast<int *>(red + 16 * SEL_WARPS);      // [4][256]
     int *ired = hist + 4 * 256;                                     // [40]
     float *fb = reinterpret_cast<float *>(ired + 40);               // [SEL_MAX_CTAS][16] slice factors
-    float *scn = fb + SEL_MAX_CTAS * 16;                            // [C] member counts of the slice being scored
-    uint8_t *sel = reinterpret_cast<uint8_t *>(scn + C);            // [C + 1]
-    // while a slice is scored, key and ci hold its longest and shortest key lengths (the pick fills them later)
+    uint8_t *sel = reinterpret_cast<uint8_t *>(fb + SEL_MAX_CTAS * 16);   // [C + 1]
+    // while a slice is scored, key and ci hold its longest and shortest key lengths (the pick fills them later);
+    // an empty cluster is marked by a longest length of -inf, so that no third array of counts is needed
+    // (8,192 slots x 4 query heads would not fit the shared memory of an SM with one)
     float *smx = reinterpret_cast<float *>(key), *smn = reinterpret_cast<float *>(ci);
 
     const int n_c = min(max(p.st.n_c[h], 0), C);
@@ -231,9 +232,8 @@ __global__ void __launch_bounds__(SEL_THREADS) score_pick_kernel(const SelectPar
         // the slice's lengths and counts go to shared memory up front: read in the scoring loop from global memory
         // they cost a dependent round trip per eight clusters (30 us of a 38 us launch with one CTA per head)
         for (int i = tid; i < mine; i += SEL_THREADS) {
-            smx[i] = mmax[c_lo + i];
+            smx[i] = count[c_lo + i] == 0.f ? -INFINITY : mmax[c_lo + i];
             smn[i] = mmin[c_lo + i];
-            scn[i] = count[c_lo + i];
         }
         pdl_wait();                                        // the query comes from the kernel before this one
         pdl_trigger();
@@ -286,14 +286,14 @@ __global__ void __launch_bounds__(SEL_THREADS) score_pick_kernel(const SelectPar
                         const int c = cbase + 2 * jq + i;
                         if (c < c_hi) {
                             const float inv = 1.0f / fmaxf(sqrtf((float)(i ? nb2 : na)), 1e-12f);
-                            const float cn = scn[c - c_lo], mx = smx[c - c_lo], mn = smn[c - c_lo];
+                            const float mx = smx[c - c_lo], mn = smn[c - c_lo];
 #pragma unroll
                             for (int r = 0; r < (GP > 8 ? 2 : 1); ++r) {
                                 const int g = nrow + 8 * r;
                                 if (g < G) {
                                     const float pr = acc[2 * r + i] * inv;
                                     float e = pr >= 0.f ? mx * pr : mn * pr;
-                                    if (cn == 0.f) e = -INFINITY;
+                                    if (mx == -INFINITY) e = -INFINITY;       // empty cluster
                                     z[g * C + (c - c_lo)] = e * p.scale;
                                     if (p.e_out) p.e_out[((int64_t)h * G + g) * C + c] = e;
                                 }
@@ -576,7 +576,6 @@ static size_t select_smem(int G, int C, bool scored) {
     b += (size_t)C * 4 * 2;                 // key, ci
     b += (size_t)G * HEAD_DIM * 4;          // sq
     b += 16 * SEL_WARPS * 4 + 4 * 256 * 4 + 40 * 4 + SEL_MAX_CTAS * 16 * 4;
-    b += (size_t)C * 4;                     // scn
     b += C + 1 + 16;
     return (b + 15) & ~size_t(15);
 }

@@ -37,3 +37,9 @@ def golden_small():
 def golden_config1():
     import torch
     return torch.load(os.path.join(GOLDEN, "config1.pt"), weights_only=False)
+
+
+@pytest.fixture(scope="session")
+def golden_sampled():
+    import torch
+    return torch.load(os.path.join(GOLDEN, "sampled.pt"), weights_only=False)

@@ -103,6 +103,37 @@ def case_partitions(ref) -> dict:
     return {"input_sum": float(U.double().sum()), "side": side.to(torch.uint8), "part": part.to(torch.uint8)}
 
 
+def case_sampled(ref) -> dict:
+    """ssa.attn.tail_sample (proposal_from_scores, tail_sample_weights) and the label-weighted attention with the
+    fractional weights they give, on the state of SphereIndexGPU after a fit and 40 inserted keys.  The per-head
+    score estimates are the reference's own formula (sphere_gpu.py:426-430), evaluated here on its state."""
+    h, G, d, n0, steps, C = 2, 2, 128, 600, 40, 64
+    K, V = clustered_keys(h, n0 + steps, d, seed=31)
+    Q = queries(h * G, d, 3, 1031)
+    ix = ref["SphereIndexGPU"](C=C, C_init=16, cap_keys=24.0, split_factor=0.0, window=16, delta=math.inf,
+                               capacity=n0 + steps, check_every=16, seed=0, kmeans_iters=10, partition="kmeans")
+    ix.observe(K, n0)
+    for t in range(1, steps + 1):
+        ix.observe(K, n0 + t)
+    n = n0 + steps
+    gold = {"input_sum": float(K.double().sum()), "cfg": dict(h=h, G=G, n0=n0, steps=steps, C=C, S=6, alpha=0.1,
+                                                              budget=0.2, seed=31), "probes": []}
+    for t in range(3):
+        q = Q[t]
+        labels, w = ix.labels_and_weights(q, n=n, budget=0.2, group="sum_share")
+        cdir = ix.sum_dir / ix.sum_dir.norm(dim=-1, keepdim=True).clamp_min(1e-12)
+        p = torch.einsum("hgd,hcd->hgc", q.view(h, G, d), cdir)
+        e = torch.where(p >= 0, ix.mmax.unsqueeze(1) * p, ix.mmin.unsqueeze(1) * p)
+        e = e.masked_fill((ix.count == 0).unsqueeze(1), -math.inf)
+        prop = ref["proposal_from_scores"](e, ix.count, scale=1.0 / math.sqrt(d))
+        w2 = w.clone()
+        w2[:, :C] = ref["tail_sample_weights"](prop, ix.count, w[:, :C] > 0, S=6, alpha=0.1,
+                                               generator=torch.Generator().manual_seed(100 + t))
+        out = ref["label_weighted_attention"](q.double(), K[:, :n].double(), V[:, :n].double(), labels, w2.double())
+        gold["probes"].append({"prop": prop.clone(), "w": w.clone(), "w2": w2.clone(), "out": out.float()})
+    return gold
+
+
 def main() -> None:
     src = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("SKV_REFERENCE_SRC")
     if not src:
@@ -112,9 +143,11 @@ def main() -> None:
     from ssa.attn.clusterkv import spherical_kmeans
     from ssa.attn.labeled import label_weighted_attention
     from ssa.attn.sphere_gpu import SphereIndexGPU, _bisect_padded, _kmeans_padded
+    from ssa.attn.tail_sample import proposal_from_scores, tail_sample_weights
     ref = dict(spherical_kmeans=spherical_kmeans, SphereIndexGPU=SphereIndexGPU, _bisect_padded=_bisect_padded,
                _kmeans_padded=_kmeans_padded, label_weighted_attention=label_weighted_attention,
-               overhead_rows=overhead_rows, kv_read_fraction=kv_read_fraction)
+               overhead_rows=overhead_rows, kv_read_fraction=kv_read_fraction,
+               proposal_from_scores=proposal_from_scores, tail_sample_weights=tail_sample_weights)
     torch.manual_seed(0)
     gold = {
         "torch": torch.__version__,
@@ -153,7 +186,8 @@ def main() -> None:
     cfg1 = case_stream(ref, h=8, G=2, n0=4096, steps=512, C=1024, C_init=256, cap_keys=64.0, split_factor=0.0,
                        window=64, delta=math.inf, check_every=16, seed=1, budget=0.2, full=False, probe_every=128)
     torch.save({"torch": torch.__version__, "config1": cfg1}, os.path.join(HERE, "config1.pt"))
-    for f in ("small.pt", "config1.pt"):
+    torch.save({"torch": torch.__version__, "sampled": case_sampled(ref)}, os.path.join(HERE, "sampled.pt"))
+    for f in ("small.pt", "config1.pt", "sampled.pt"):
         print(f, os.path.getsize(os.path.join(HERE, f)) // 1024, "KiB")
 
 

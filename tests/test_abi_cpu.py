@@ -237,3 +237,40 @@ def test_header_is_plain_c(tmp_path):
                    "  return skv_version() == SKV_VERSION ? 0 : 1; }\n")
     subprocess.check_call([gcc, "-std=c99", "-Wall", "-Wextra", "-pedantic", "-Werror", "-I",
                            os.path.join(ROOT, "include"), "-c", str(src), "-o", str(tmp_path / "use.o")])
+
+
+def test_weighted_attention_rejects_bad_arguments(L):
+    ok = 0x1000
+
+    def call(**over):
+        a = dict(q=ok, K=ok, V=ok, labels=ok, lstr=64, w=ok, C=64, n_dev=ok, out=ok, ws=ok, heads=2, G=2, d=128, dtype=0,
+                 ksr=128, splits=4)
+        a.update(over)
+        return L.skv_attend_weighted(a["q"], a["K"], a["V"], a["labels"], a["lstr"], a["w"], a["C"], a["n_dev"],
+                                     a["out"], a["ws"], None, a["heads"], a["G"], a["d"], a["dtype"], 128 * 64, a["ksr"],
+                                     128 * 64, 128, a["splits"], 0.1, None)
+
+    assert call(labels=None) == -1 and call(w=None) == -1 and call(n_dev=None) == -1
+    assert call(G=9) == -2 and call(C=48) == -2 and call(d=64) == -2
+    assert call(dtype=5) == -3 and call(ksr=100) == -4 and call(lstr=0) == -5 and call(splits=0) == -5
+
+
+def test_one_launch_step_rejects_bad_arguments(L):
+    st = fake_state(C=256, cap=4096, bits=8, heads=8)
+    ok = 0x1000
+
+    def call(state=st, **over):
+        a = dict(q=ok, G=2, n_dev=ok, K=ok, V=ok, ksr=128, cnt=ok, out=ok, ws=ok, clusters=4)
+        a.update(over)
+        return L.skv_step(ctypes.byref(state), a["q"], a["G"], a["n_dev"], a["K"], a["V"], 128 * 4096, a["ksr"],
+                          128 * 4096, 128, None, None, a["cnt"], a["out"], a["ws"], a["clusters"], 0.1, None, None)
+
+    assert call(q=None) == -1 and call(K=None) == -1 and call(ws=None) == -1
+    assert call(G=9) == -2 and call(clusters=9) == -2
+    assert call(state=fake_state(C=4096, cap=4096, bits=8, heads=8)) == -2        # more than 2,048 slots
+    assert call(state=fake_state(C=256, cap=4096, bits=32, heads=8)) in (-1, -5)  # float32 summaries: not served
+    assert call(ksr=100) == -4 and call(clusters=0) == -5
+    assert L.skv_step_workspace_bytes(8, 2, 4) == 8 * 4 * 2 * 132 * 4 + 256
+    assert L.skv_step_clusters(8, 2, 4096, 8) == 0 and L.skv_step_clusters(8, 2, 256, 32) == 0
+    assert L.skv_gemv_attended(ok, 64, 256, ok, 1, None, 4, 2, None, None, 0, None) == -1
+    assert L.skv_gemv_attended(ok, 64, 256, ok, 1, ok, 9, 2, None, None, 0, None) == -5

@@ -337,3 +337,48 @@ def test_every_query_head_ranks_for_itself(G):
     # the shared modes still work afterwards (their buffers were kept)
     _, w_sum = ix.labels_and_weights(q.to(DEV), n=n, budget=0.25)
     assert torch.equal(w_sum.cpu(), st.select(q, n=n, budget=0.25)[1])
+
+
+def test_sampled_clusters_follow_the_reference_golden(golden_sampled):
+    """attend_sampled (ssa/kernels/sphere_fused.py:503-518) against the golden made with the reference's own
+    proposal_from_scores / tail_sample_weights / label_weighted_attention: same generator seed, so the same
+    clusters are drawn; fractional weights to 1e-4 (the scores are the kernel's), output to 1e-2 (in fact 1e-4)."""
+    g = golden_sampled["sampled"]
+    c = g["cfg"]
+    n = c["n0"] + c["steps"]
+    K, V = oc.clustered_keys(c["h"], n, 128, seed=c["seed"])
+    Q = torch.randn(3, c["h"] * c["G"], 128, generator=torch.Generator().manual_seed(c["seed"] + 1000))
+    ix = SphereIndexGraph(C=c["C"], C_init=16, cap_keys=24.0, window=16, delta=math.inf, capacity=-(-n // 8) * 8,
+                          summary_bits=32, async_check=False)
+    Kd, Vd = K.to(DEV), V.to(DEV)
+    for m in range(c["n0"], n):
+        ix.observe(Kd, m)
+    for t, p in enumerate(g["probes"]):
+        out, labels, w2 = ix.attend_sampled(Q[t].to(DEV), Kd, Vd, n=n, budget=c["budget"], S=c["S"], alpha=c["alpha"],
+                                            generator=torch.Generator().manual_seed(100 + t))
+        assert torch.equal(w2.cpu() > 0, p["w2"] > 0)
+        torch.testing.assert_close(w2.cpu(), p["w2"], rtol=1e-4, atol=1e-6)
+        assert float((out.cpu() - p["out"]).abs().max()) <= 1e-4
+        drawn = (w2[:, :c["C"]] > 0) & (ix.wbuf[:, :c["C"]] == 0)
+        assert int(drawn.sum()) >= c["h"] and float(w2[:, :c["C"]][drawn].min()) > 0
+    # no draws: the plain selection, and the weighted kernel equals the list-driven one
+    out0, _, w0 = ix.attend_sampled(Q[0].to(DEV), Kd, Vd, n=n, budget=c["budget"], S=0, alpha=0.1)
+    out0 = out0.clone()
+    plain, _, w = ix.attend(Q[0].to(DEV), Kd, Vd, n=n, budget=c["budget"])
+    assert torch.equal(w0, w) and float((out0 - plain).abs().max()) <= 1e-5
+
+
+def test_weighted_attention_in_bf16_against_the_oracle():
+    h, G, n = 4, 2, 3000
+    Q, K, V = isotropic_stream(h, 3008, h * G, seed=19)
+    st = oc.ClusterOracle(C=256, C_init=64, cap_keys=32.0, window=64, delta=math.inf, capacity=3008, summary_bits=8)
+    st.observe(K, n)
+    ix = device_index_from_oracle(st)
+    labels, w2 = st.select_sampled(Q[0].float(), n=n, budget=0.1, S=12, alpha=0.2,
+                                   generator=torch.Generator().manual_seed(3))
+    got, _, wd = ix.attend_sampled(Q[0].to(DEV), K.to(DEV), V.to(DEV), n=n, budget=0.1, S=12, alpha=0.2,
+                                   generator=torch.Generator().manual_seed(3))
+    same = torch.equal(wd.cpu() > 0, w2 > 0)
+    want = oc.attend_labeled(Q[0], K[:, :n], V[:, :n], labels, wd.cpu().double() if not same else w2)
+    assert float((got.cpu().double() - want).abs().max()) <= 1e-2
+    assert int(((wd.cpu() > 0) != (w2 > 0)).sum()) <= 4          # a boundary cluster may move a probe

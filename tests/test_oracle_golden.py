@@ -191,3 +191,45 @@ def test_8bit_mode_fits_like_the_float_mode():
     b.observe(K, 800)
     assert torch.equal(a.labels, b.labels) and torch.equal(a.n_c, b.n_c) and torch.equal(a.sum_dir, b.sum_dir)
     assert torch.equal(b.cent8, oc.to_int8_direction(b.cent))
+
+
+def test_sampled_selection_reproduces_the_reference(golden_sampled):
+    """Proposal, fractional weights of the drawn clusters and the weighted attention against the reference's
+    ssa.attn.tail_sample functions, same generator seeds."""
+    g = golden_sampled["sampled"]
+    c = g["cfg"]
+    n = c["n0"] + c["steps"]
+    K, V = oc.clustered_keys(c["h"], n, 128, seed=c["seed"])
+    assert abs(float(K.double().sum()) - g["input_sum"]) < 1e-6
+    Q = torch.randn(3, c["h"] * c["G"], 128, generator=torch.Generator().manual_seed(c["seed"] + 1000))
+    st = oc.ClusterOracle(C=c["C"], C_init=16, cap_keys=24.0, window=16, delta=math.inf, capacity=n)
+    for m in range(c["n0"], n + 1):
+        st.observe(K, m)
+    for t, p in enumerate(g["probes"]):
+        prop = oc.sampling_proposal(st.scores(Q[t]), st.count, scale=1.0 / math.sqrt(128))
+        torch.testing.assert_close(prop, p["prop"], rtol=0, atol=0)
+        labels, w2 = st.select_sampled(Q[t], n=n, budget=c["budget"], S=c["S"], alpha=c["alpha"],
+                                       generator=torch.Generator().manual_seed(100 + t))
+        torch.testing.assert_close(w2, p["w2"], rtol=0, atol=0)
+        drawn = (w2[:, :c["C"]] > 0) & (p["w"][:, :c["C"]] == 0)
+        assert 1 <= int(drawn.sum(1).min()) and int(drawn.sum(1).max()) <= c["S"]
+        out = oc.attend_labeled(Q[t], K[:, :n], V[:, :n], labels, w2)
+        torch.testing.assert_close(out.float(), p["out"], rtol=0, atol=1e-6)
+
+
+def test_sampled_weights_properties():
+    """The reference's own checks of the sampler (tests/test_tail_sample.py:18-47): taken clusters weigh 1, empty
+    ones 0, the draws add up to S, and no draw means the plain selection."""
+    g = torch.Generator().manual_seed(5)
+    count = torch.randint(0, 6, (3, 40), generator=g).double()
+    taken = torch.rand(3, 40, generator=g) < 0.2
+    prop = torch.rand(3, 40, generator=g, dtype=torch.float64) ** 3
+    w = oc.sampled_weights(prop, count, taken, S=7, alpha=0.3, generator=torch.Generator().manual_seed(6))
+    assert torch.all(w[taken & (count > 0)] == 1.0) and torch.all(w[count == 0] == 0.0)
+    rest = ~taken & (count > 0)
+    n_rest = rest.sum(1, keepdim=True)
+    p = prop * rest
+    pi = ((1 - 0.3) * p / p.sum(1, keepdim=True) + 0.3 / n_rest) * rest
+    torch.testing.assert_close((w * pi * 7 * rest).sum(1), torch.full((3,), 7.0, dtype=torch.float64))
+    none = oc.sampled_weights(prop, count, taken, S=0, alpha=0.3)
+    torch.testing.assert_close(none, (taken & (count > 0)).double())
