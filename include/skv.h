@@ -3,7 +3,12 @@
  * Every entry point takes raw device pointers, element strides and sizes; none takes a framework
  * type.  Unless stated otherwise a call allocates nothing, never synchronises and reads nothing back
  * to the host, so it can be recorded into a CUDA graph; all work is ordered on the `stream` argument
- * (a cudaStream_t passed as void*).  Return value: 0 on success, a negative SKV_E_* code when an
+ * (a cudaStream_t passed as void*).
+ * Lengths live in device memory.  `n_dev` holds the number of cached positions; `n_group` says how heads map to its
+ * entries: head h reads n_dev[h / n_group], so a batch whose sequences differ in length passes one entry per sequence
+ * and n_group = KV heads per sequence; n_group = 0 means every head reads n_dev[0] (all sequences equally long, the
+ * reference's own limit: README.md:62).
+ * Return value: 0 on success, a negative SKV_E_* code when an
  * argument is rejected on the host (nothing is launched then).  Problems met on the device (no spare
  * slot, a cluster too large to split, an index out of range) are recorded per head in the
  * caller-owned `status` words of skv_state and never fault.
@@ -20,7 +25,7 @@
 extern "C" {
 #endif
 
-#define SKV_VERSION 100
+#define SKV_VERSION 101
 
 /* host-side argument errors */
 #define SKV_OK            0
@@ -105,7 +110,7 @@ int64_t skv_attend_workspace_bytes(int heads, int G, int d, int splits);
  *   rows_limit                   positions >= rows_limit are skipped and flagged in status (may be null)
  */
 int skv_attend(const void *q, const void *K, const void *V, const int32_t *idx, const int32_t *cnt,
-               const int32_t *n_dev, void *out, void *workspace, int32_t *status,
+               const int32_t *n_dev, int n_group, void *out, void *workspace, int32_t *status,
                int heads, int G, int d, int dtype,
                int64_t k_head_stride, int64_t k_row_stride, int64_t v_head_stride, int64_t v_row_stride,
                int64_t idx_stride, int rows_limit, int splits, float scale, void *stream);
@@ -118,7 +123,8 @@ int skv_attend(const void *q, const void *K, const void *V, const int32_t *idx, 
  *   labels [heads, label_stride] int16, w [heads, C+1] float32 (column C = the always-read rows); G <= 8;
  *   q, K, V, out, workspace, splits as in skv_attend (float32 arithmetic on the CUDA cores: an eager-API call). */
 int skv_attend_weighted(const void *q, const void *K, const void *V, const int16_t *labels, int64_t label_stride,
-                        const float *w, int C, const int32_t *n_dev, void *out, void *workspace, int32_t *status,
+                        const float *w, int C, const int32_t *n_dev, int n_group, void *out, void *workspace,
+                        int32_t *status,
                         int heads, int G, int d, int dtype,
                         int64_t k_head_stride, int64_t k_row_stride, int64_t v_head_stride, int64_t v_row_stride,
                         int splits, float scale, void *stream);
@@ -141,7 +147,7 @@ int skv_attend_weighted(const void *q, const void *K, const void *V, const int16
  * All calls share the one array: two calls whose kernels overlap on the GPU (different streams, or
  * several host threads) race on it and give wrong results - serialise them. */
 int skv_attend_static(const void *q, const void *K, const void *V, const int32_t *idx, const int32_t *cnt,
-                      const int32_t *n_dev, void *out, int32_t *status,
+                      const int32_t *n_dev, int n_group, void *out, int32_t *status,
                       int heads, int G, int d, int dtype,
                       int64_t k_head_stride, int64_t k_row_stride, int64_t v_head_stride, int64_t v_row_stride,
                       int64_t idx_stride, int rows_limit, int splits, float scale, void *stream);
@@ -161,13 +167,13 @@ typedef struct skv_rope {
     const void *qkv;                 /* [B, (H + 2 H_kv) * 128] bf16: q heads, then k heads, then v heads */
     const void *q_norm_w, *k_norm_w; /* [128] bf16 */
     const void *cos_table, *sin_table; /* [positions, 128] bf16 */
-    const int64_t *pos;              /* device [1]: position of the new token */
+    const int64_t *pos;              /* device: position of the new token, [1] or one per sequence (pos_per_seq) */
     void *q_out;                     /* [B * H, 128] bf16 */
     void *k_cache, *v_cache;         /* bf16 caches of this layer */
     int32_t H, H_kv;                 /* query and KV heads per sequence (state.heads = B * H_kv) */
     int64_t cache_batch_stride, cache_head_stride, cache_row_stride;   /* elements */
     float eps;
-    int32_t reserved;
+    int32_t pos_per_seq;             /* 0: every sequence writes at pos[0]; 1: sequence s at pos[s] */
 } skv_rope;
 
 /* How the G query heads of a KV head share one ranking of its clusters (ssa/attn/sphere_gpu.py:431-439) */
@@ -185,7 +191,7 @@ typedef struct skv_rope {
  * ssa/kernels/graph_kernels.py:133-141) and _compact_dev_kernel (graph_kernels.py:144-155);
  * selection rule of SphereIndexGPU._rank_mask (ssa/attn/sphere_gpu.py:402-410).
  *   q          [heads*G, d] dtype
- *   n_dev      [1] cached positions (all heads)
+ *   n_dev      cached positions, n_group as described at the top of this file
  *   w          [heads, C+1] float32 0/1 weights out (column C = 1)
  *   selbits    [heads, C/32+1] uint32 out, or null (kept in the workspace then)
  *   idx, cnt   idx [heads, idx_stride] int32 or null; cnt [heads]: rows listed, or 0 when idx is null
@@ -199,7 +205,7 @@ typedef struct skv_rope {
  *              bf16 only, G = rope->H / rope->H_kv
  */
 int64_t skv_select_workspace_bytes(int heads, int G, int C);
-int skv_select(const skv_state *st, const void *q, int dtype, int G, const int32_t *n_dev,
+int skv_select(const skv_state *st, const void *q, int dtype, int G, const int32_t *n_dev, int n_group,
                float *w, uint32_t *selbits, int32_t *idx, int64_t idx_stride, int32_t *cnt,
                const float *shared_in, float *shared_out, float *e_out, void *workspace, float scale, int group,
                const skv_rope *rope, void *stream);
@@ -224,7 +230,7 @@ void skv_debug_attend_probe(void *dev_ptr);
  * _compact_dev_kernel + _list_kernel + _merge_kernel (ssa/kernels/graph_kernels.py:144-155,
  * ssa/kernels/labeled_attn.py:202-245, :123-140) in one launch.  label_stride a multiple of 8. */
 int skv_attend_labels(const void *q, const void *K, const void *V, const int16_t *labels, int64_t label_stride,
-                      const uint32_t *selbits, int C, const int32_t *n_dev, void *out, void *workspace,
+                      const uint32_t *selbits, int C, const int32_t *n_dev, int n_group, void *out, void *workspace,
                       int32_t *cnt, int32_t *status, int heads, int G, int d, int dtype,
                       int64_t k_head_stride, int64_t k_row_stride, int64_t v_head_stride, int64_t v_row_stride,
                       int splits, float scale, void *stream);
@@ -251,7 +257,7 @@ int skv_attend_labels(const void *q, const void *K, const void *V, const int16_t
  *              (the output product) merges them while it builds its input, which saves a hand-off through a ticket */
 int skv_step_clusters(int heads, int G, int C, int summary_bits);
 int64_t skv_step_workspace_bytes(int heads, int G, int clusters);
-int skv_step(const skv_state *st, const void *q, int G, const int32_t *n_dev, const void *K, const void *V,
+int skv_step(const skv_state *st, const void *q, int G, const int32_t *n_dev, int n_group, const void *K, const void *V,
              int64_t k_head_stride, int64_t k_row_stride, int64_t v_head_stride, int64_t v_row_stride,
              float *w, uint32_t *selbits, int32_t *cnt, void *out, void *workspace, int clusters,
              float scale, const skv_rope *rope, void *stream);
@@ -275,7 +281,7 @@ void skv_debug_step_probe(void *dev_ptr);
  *   var_min         fewest keys a cluster must hold to split on the spread threshold state.vthr
  */
 int skv_insert(const skv_state *st, const void *const *k_layers, int heads_per_layer, int dtype,
-               int64_t k_head_stride, int64_t k_row_stride, const int32_t *n_dev, int window,
+               int64_t k_head_stride, int64_t k_row_stride, const int32_t *n_dev, int n_group, int window,
                double budget, float delta, int reset_at, int max_members, float capk, int var_min, void *stream);
 int skv_insert_max_members(void);
 
@@ -332,10 +338,11 @@ int skv_add_rmsnorm(void *h, const void *delta, const void *w, void *out, int B,
 
 /* qkv [B, (H + 2*H_kv) * d] (query heads, then key heads, then value heads) -> q_out [B*H, d] with the per-head
  * RMSNorm and the rotary embedding applied, and the new key (normed, rotated) and value written into the caches
- * [B, H_kv, L, d] at row pos_dev[0].  cos/sin tables [positions, d] bf16.  Replaces q_norm, k_norm, apply_rope
+ * [B, H_kv, L, d] at row pos_dev[0] (pos_per_seq = 0) or pos_dev[sequence] (1).  cos/sin tables [positions, d] bf16.  Replaces q_norm, k_norm, apply_rope
  * and the two index_copy_ calls (graph_decode.py:101-108). */
 int skv_qk_rope_cache(const void *qkv, const void *q_norm_w, const void *k_norm_w, const void *cos_table,
-                      const void *sin_table, const int64_t *pos_dev, void *q_out, void *k_cache, void *v_cache,
+                      const void *sin_table, const int64_t *pos_dev, int pos_per_seq, void *q_out, void *k_cache,
+                      void *v_cache,
                       int B, int H, int H_kv, int d, int64_t cache_batch_stride, int64_t cache_head_stride,
                       int64_t cache_row_stride, float eps, void *stream);
 

@@ -40,7 +40,7 @@ class SkvRope(C.Structure):
                 ("sin_table", C.c_void_p), ("pos", C.c_void_p), ("q_out", C.c_void_p), ("k_cache", C.c_void_p),
                 ("v_cache", C.c_void_p), ("H", C.c_int32), ("H_kv", C.c_int32), ("cache_batch_stride", C.c_int64),
                 ("cache_head_stride", C.c_int64), ("cache_row_stride", C.c_int64), ("eps", C.c_float),
-                ("reserved", C.c_int32)]
+                ("pos_per_seq", C.c_int32)]
 
 
 class SkvState(C.Structure):
@@ -68,18 +68,18 @@ def _declare(lib) -> None:
     lib.skv_attend_workspace_bytes.restype = i64
     lib.skv_attend_workspace_bytes.argtypes = [i32, i32, i32, i32]
     lib.skv_attend.restype = i32
-    lib.skv_attend.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i64, i64, i64, i64, i64, i32,
+    lib.skv_attend.argtypes = [vp, vp, vp, vp, vp, vp, i32, vp, vp, vp, i32, i32, i32, i32, i64, i64, i64, i64, i64, i32,
                                i32, f32, vp]
     lib.skv_attend_static.restype = i32
-    lib.skv_attend_static.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i64, i64, i64, i64, i64, i32,
-                                      i32, f32, vp]
+    lib.skv_attend_static.argtypes = [vp, vp, vp, vp, vp, vp, i32, vp, vp, i32, i32, i32, i32, i64, i64, i64, i64, i64,
+                                      i32, i32, f32, vp]
     lib.skv_attend_weighted.restype = i32
-    lib.skv_attend_weighted.argtypes = [vp, vp, vp, vp, i64, vp, i32, vp, vp, vp, vp, i32, i32, i32, i32, i64, i64, i64,
-                                        i64, i32, f32, vp]
+    lib.skv_attend_weighted.argtypes = [vp, vp, vp, vp, i64, vp, i32, vp, i32, vp, vp, vp, i32, i32, i32, i32, i64, i64,
+                                        i64, i64, i32, f32, vp]
     lib.skv_merge.restype = i32
     lib.skv_merge.argtypes = [vp, vp, vp, vp, i32, i32, i32, i32, vp]
     lib.skv_select.restype = i32
-    lib.skv_select.argtypes = [C.POINTER(SkvState), vp, i32, i32, vp, vp, vp, vp, i64, vp, vp, vp, vp, vp, f32, i32,
+    lib.skv_select.argtypes = [C.POINTER(SkvState), vp, i32, i32, vp, i32, vp, vp, vp, i64, vp, vp, vp, vp, vp, f32, i32,
                                C.POINTER(SkvRope), vp]
     lib.skv_select_workspace_bytes.restype = i64
     lib.skv_select_workspace_bytes.argtypes = [i32, i32, i32]
@@ -90,19 +90,19 @@ def _declare(lib) -> None:
     lib.skv_debug_attend_probe.restype = None
     lib.skv_debug_attend_probe.argtypes = [vp]
     lib.skv_attend_labels.restype = i32
-    lib.skv_attend_labels.argtypes = [vp, vp, vp, vp, i64, vp, i32, vp, vp, vp, vp, vp, i32, i32, i32, i32, i64, i64,
+    lib.skv_attend_labels.argtypes = [vp, vp, vp, vp, i64, vp, i32, vp, i32, vp, vp, vp, vp, i32, i32, i32, i32, i64, i64,
                                       i64, i64, i32, f32, vp]
     lib.skv_step_clusters.restype = i32
     lib.skv_step_clusters.argtypes = [i32, i32, i32, i32]
     lib.skv_step_workspace_bytes.restype = i64
     lib.skv_step_workspace_bytes.argtypes = [i32, i32, i32]
     lib.skv_step.restype = i32
-    lib.skv_step.argtypes = [C.POINTER(SkvState), vp, i32, vp, vp, vp, i64, i64, i64, i64, vp, vp, vp, vp, vp, i32, f32,
+    lib.skv_step.argtypes = [C.POINTER(SkvState), vp, i32, vp, i32, vp, vp, i64, i64, i64, i64, vp, vp, vp, vp, vp, i32, f32,
                              C.POINTER(SkvRope), vp]
     lib.skv_debug_step_probe.restype = None
     lib.skv_debug_step_probe.argtypes = [vp]
     lib.skv_insert.restype = i32
-    lib.skv_insert.argtypes = [C.POINTER(SkvState), vp, i32, i32, i64, i64, vp, i32, f64, f32, i32, i32, f32, i32, vp]
+    lib.skv_insert.argtypes = [C.POINTER(SkvState), vp, i32, i32, i64, i64, vp, i32, i32, f64, f32, i32, i32, f32, i32, vp]
     lib.skv_insert_max_members.restype = i32
     lib.skv_fit_workspace_bytes.restype = i64
     lib.skv_fit_workspace_bytes.argtypes = [i32, i32, i32, i32]
@@ -112,7 +112,7 @@ def _declare(lib) -> None:
     lib.skv_add_rmsnorm.restype = i32
     lib.skv_add_rmsnorm.argtypes = [vp, vp, vp, vp, i32, i32, f32, vp]
     lib.skv_qk_rope_cache.restype = i32
-    lib.skv_qk_rope_cache.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i64, i64, i64, f32, vp]
+    lib.skv_qk_rope_cache.argtypes = [vp, vp, vp, vp, vp, vp, i32, vp, vp, vp, i32, i32, i32, i32, i64, i64, i64, f32, vp]
     lib.skv_silu_mul.restype = i32
     lib.skv_silu_mul.argtypes = [vp, vp, i32, i32, vp]
     lib.skv_gemv_tp.restype = i32

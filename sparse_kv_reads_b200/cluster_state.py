@@ -143,6 +143,47 @@ def fit_layers(layers: list["SphereIndexGraph"], caches: list[torch.Tensor], n: 
     return True
 
 
+def fit_layers_ragged(layers: list["SphereIndexGraph"], caches: list[torch.Tensor], lengths: list[int],
+                      heads_per_seq: int) -> None:
+    """Prompt fit of a batch whose sequences differ in length: one ``skv_fit`` per sequence, over the heads of that
+    sequence in EVERY layer (a head list into the stacked states plus the table of per-layer caches), each with
+    its own number of cached positions.  The layers must share one arena (``GraphDecoder`` allocates them so)."""
+    first = layers[0]
+    arena, h = first._arena, caches[0].shape[0]
+    k0 = caches[0]
+    if first.partition != "kmeans" or any(ix._arena is not arena or ix._layer != i for i, ix in enumerate(layers)):
+        raise ValueError("a variable-length batch needs the k-means partition and layers stacked in one arena")
+    if len(lengths) * heads_per_seq != h:
+        raise ValueError("one length per sequence is needed")
+    for ix, K in zip(layers, caches):
+        ix._init(K, max(lengths), fit=False)
+        ix.n_group = heads_per_seq
+    L = lib()
+    st = arena.struct(0, len(layers) * h)
+    table = torch.tensor([k.data_ptr() for k in caches], dtype=torch.int64, device=k0.device)
+    for b, n in enumerate(lengths):
+        m = max(1, n - first.window) - 1
+        if m < 1:
+            raise ValueError(f"sequence {b}: n={n} leaves nothing to cluster behind a window of {first.window}")
+        g = torch.Generator(device="cpu").manual_seed(first.seed)
+        init = torch.randperm(m, generator=g)[torch.arange(first.C_init) % m].to(torch.int32).to(k0.device)
+        hl = torch.tensor([layer * h + b * heads_per_seq + j for layer in range(len(layers))
+                           for j in range(heads_per_seq)], dtype=torch.int32, device=k0.device)
+        nbytes = L.skv_fit_workspace_bytes(int(hl.numel()), m, first.C, first.d)
+        ws = _workspace(k0.device, nbytes)
+        check(L.skv_fit(ctypes.byref(st), None, dtype_code(k0.dtype), k0.stride(0), k0.stride(1), n, first.window,
+                        first.C_init, first.kmeans_iters, init.data_ptr(), first.cap_keys, first.split_factor,
+                        first.capk, first.var_factor, hl.data_ptr(), int(hl.numel()), table.data_ptr(), h,
+                        ws.data_ptr(), ws.numel(), stream_ptr(k0.device)), "skv_fit")
+    for ix in layers:
+        ix._fitted = True
+        ix._max_members = None
+        ix._splits_host += int(ix.nsplit.sum())
+        ix.nsplit.zero_()
+        ix.n = max(lengths)
+        ix._host_end()
+
+
 class AttentionPartials:
     """What ``skv_step`` leaves when the last merge is deferred: per head ``clusters`` partial outputs in
     ``workspace`` ([heads, clusters, G, 132] float32) and the buffer that is to receive the rows read."""
@@ -202,6 +243,9 @@ class SphereIndexGraph:
         self._waited = 0
         self._ktab = {}
         self.G = None
+        # heads that share one entry of the device-side lengths: 0 = all sequences equally long (one entry); a batch
+        # of sequences of different lengths passes one entry per sequence and its KV heads per sequence here
+        self.n_group = 0
 
     # ---- allocation ------------------------------------------------------------------------------
     def _alloc(self, h: int, d: int, device) -> None:
@@ -324,7 +368,7 @@ class SphereIndexGraph:
 
     def _launch_insert(self, K: torch.Tensor, n_dev: torch.Tensor, budget: float) -> None:
         check(lib().skv_insert(ctypes.byref(self._st), self._ktable(K).data_ptr(), self.H_kv, dtype_code(K.dtype),
-                               K.stride(0), K.stride(1), n_dev.data_ptr(), self.window, float(budget),
+                               K.stride(0), K.stride(1), n_dev.data_ptr(), self.n_group, self.window, float(budget),
                                float(min(self.delta, 3.0e38)), self.reset_at, self._members_limit(), self.capk,
                                self.var_min, stream_ptr(K.device)),
               "skv_insert")
@@ -387,33 +431,49 @@ class SphereIndexGraph:
         """Fit ``heads`` again from all their clustered keys, back to ``C_init`` clusters and then the
         after-fit splits (ssa/attn/sphere_gpu.py:283-293)."""
         self._host_end()
-        if self.end < 2:
-            return
-        self._build_all(K, self.end + self.window, heads)
-        self.resets += int(heads.numel())
+        for end, group in self._by_end(heads):
+            if end < 2:
+                continue
+            self.end = end
+            self._build_all(K, end + self.window, group)
+            self.resets += int(group.numel())
+        self.end = int(self._ends[0])
 
     def _host_end(self) -> None:
-        """Refresh the host copy of ``end`` from the device (a synchronisation; only before host work)."""
-        self.end = int(self.end_dev[0])
+        """Refresh the host copies of ``end`` from the device (a synchronisation; only before host work): ``end``
+        is the first head's, ``_ends`` every head's (they differ in a batch of sequences of different lengths)."""
+        self._ends = self.end_dev.cpu().tolist()
+        self.end = int(self._ends[0])
+
+    def _by_end(self, heads: torch.Tensor):
+        """``heads`` grouped by their number of clustered positions: ``[(end, heads with that end), ...]``."""
+        ends = getattr(self, "_ends", None)
+        if not ends or len(set(ends)) == 1:
+            return [(self.end, heads)]
+        groups: dict[int, list[int]] = {}
+        for hd in heads.tolist():
+            groups.setdefault(int(ends[hd]), []).append(hd)
+        return [(e, torch.tensor(v, dtype=heads.dtype)) for e, v in sorted(groups.items())]
 
     def _rebuild(self, K: torch.Tensor, heads: torch.Tensor) -> None:
         """Recentre ``heads`` about their running mean and rebin their keys, centroids kept
         (ssa/attn/sphere_gpu.py:187-219 with the mean given; ssa/kernels/sphere_fused.py:459-464)."""
         self._host_end()
-        if self.end < 2:
-            return
         L = lib()
-        hl = heads.to(torch.int32).to(K.device)
-        nbytes = L.skv_fit_workspace_bytes(int(hl.numel()), self.end - 1, self.C, self.d)
-        ws = _workspace(K.device, nbytes)
         # clusters the new mean pushes over their cap are divided at once (split_after_rebin): the insert's
         # in-kernel split cannot stage a cluster much larger than the cap, so it would otherwise keep growing
         sf = self.split_factor if self.split_factor > 0 and self.split_after_rebin else 0.0
-        check(L.skv_rebin(ctypes.byref(self._st), hl.data_ptr(), int(hl.numel()), self.end, K.data_ptr(),
-                          dtype_code(K.dtype), K.stride(0), K.stride(1), sf, self.kmeans_iters, self.capk,
-                          ws.data_ptr(), ws.numel(), stream_ptr(K.device)), "skv_rebin")
+        for end, group in self._by_end(heads):              # one call per sequence length
+            if end < 2:
+                continue
+            hl = group.to(torch.int32).to(K.device)
+            nbytes = L.skv_fit_workspace_bytes(int(hl.numel()), end - 1, self.C, self.d)
+            ws = _workspace(K.device, nbytes)
+            check(L.skv_rebin(ctypes.byref(self._st), hl.data_ptr(), int(hl.numel()), end, K.data_ptr(),
+                              dtype_code(K.dtype), K.stride(0), K.stride(1), sf, self.kmeans_iters, self.capk,
+                              ws.data_ptr(), ws.numel(), stream_ptr(K.device)), "skv_rebin")
+            self.rebuilds += int(hl.numel())
         self._max_members = None
-        self.rebuilds += int(hl.numel())
 
     # ---- selection -------------------------------------------------------------------------------
     def _select(self, q: torch.Tensor, n_dev: torch.Tensor, *, shared_in=None, shared_out=None, e_out=None,
@@ -436,7 +496,7 @@ class SphereIndexGraph:
             if self._sel_ws is None:
                 self._sel_ws = torch.zeros(L.skv_select_workspace_bytes(self.H_kv, G, self.C), dtype=torch.uint8,
                                            device=q.device)
-        check(L.skv_select(ctypes.byref(self._st), q.data_ptr(), dtype_code(q.dtype), G, n_dev.data_ptr(),
+        check(L.skv_select(ctypes.byref(self._st), q.data_ptr(), dtype_code(q.dtype), G, n_dev.data_ptr(), self.n_group,
                            self.wbuf.data_ptr(), self.selbits.data_ptr(), self.idx.data_ptr() if listed else None,
                            self.idx.stride(0), self.cnt.data_ptr(), ptr(shared_in), ptr(shared_out), ptr(e_out),
                            self._sel_ws.data_ptr(), 1.0 / math.sqrt(d), GROUPS[group],
@@ -505,7 +565,7 @@ class SphereIndexGraph:
         code = dtype_code(K.dtype) | (256 if force_simple else 0)
         check(lib().skv_attend(q.data_ptr(), K.data_ptr(), V.data_ptr(),
                                None if dense_n is not None else self.idx.data_ptr(),
-                               None if dense_n is not None else self.cnt.data_ptr(), ptr(dense_n),
+                               None if dense_n is not None else self.cnt.data_ptr(), ptr(dense_n), self.n_group,
                                self.out.data_ptr(), self._attn_ws.data_ptr(), self.status.data_ptr(), self.H_kv, G, d,
                                code, K.stride(0), K.stride(1), V.stride(0), V.stride(1), self.idx.stride(0),
                                K.shape[1], self.num_splits, 1.0 / math.sqrt(d), stream_ptr(q.device)), "skv_attend")
@@ -519,7 +579,7 @@ class SphereIndexGraph:
             q = q.contiguous()
         G = self._attend_buffers(q)
         check(lib().skv_attend_labels(q.data_ptr(), K.data_ptr(), V.data_ptr(), self.labels.data_ptr(),
-                                      self.labels.stride(0), self.selbits.data_ptr(), self.C, n_dev.data_ptr(),
+                                      self.labels.stride(0), self.selbits.data_ptr(), self.C, n_dev.data_ptr(), self.n_group,
                                       self.out.data_ptr(), self._attn_ws.data_ptr(), self.cnt.data_ptr(),
                                       self.status.data_ptr(), self.H_kv, G, d, dtype_code(K.dtype), K.stride(0),
                                       K.stride(1), V.stride(0), V.stride(1), self.num_splits, 1.0 / math.sqrt(d),
@@ -550,7 +610,7 @@ class SphereIndexGraph:
         if ws is None:
             ws = self._step_ws[G] = torch.zeros(lib().skv_step_workspace_bytes(self.H_kv, G, ncl), dtype=torch.uint8,
                                                 device=q.device)
-        check(lib().skv_step(ctypes.byref(self._st), q.data_ptr(), G, n_dev.data_ptr(), K.data_ptr(), V.data_ptr(),
+        check(lib().skv_step(ctypes.byref(self._st), q.data_ptr(), G, n_dev.data_ptr(), self.n_group, K.data_ptr(), V.data_ptr(),
                              K.stride(0), K.stride(1), V.stride(0), V.stride(1), self.wbuf.data_ptr(),
                              self.selbits.data_ptr(), self.cnt.data_ptr(), None if defer_merge else self.out.data_ptr(),
                              ws.data_ptr(), ncl, 1.0 / math.sqrt(d), None if rope is None else ctypes.byref(rope),
@@ -599,7 +659,7 @@ class SphereIndexGraph:
         self._attend_buffers(q)
         self._n_scalar.fill_(n)
         check(lib().skv_attend_weighted(q.data_ptr(), K.data_ptr(), V.data_ptr(), self.labels.data_ptr(),
-                                        self.labels.stride(0), w2.data_ptr(), self.C, self._n_scalar.data_ptr(),
+                                        self.labels.stride(0), w2.data_ptr(), self.C, self._n_scalar.data_ptr(), 0,
                                         self.out.data_ptr(), self._attn_ws.data_ptr(), self.status.data_ptr(),
                                         self.H_kv, G, d, dtype_code(K.dtype), K.stride(0), K.stride(1), V.stride(0),
                                         V.stride(1), self.num_splits, 1.0 / math.sqrt(d), stream_ptr(q.device)),
@@ -607,18 +667,23 @@ class SphereIndexGraph:
         return self.out, labels, w2
 
     # ---- graph-safe calls --------------------------------------------------------------------------
-    def prepare(self, K: torch.Tensor, n: int, H: int, fitted: bool = False) -> None:
+    def prepare(self, K: torch.Tensor, n: int, H: int, fitted: bool = False, lengths: torch.Tensor | None = None) -> None:
         """Build from the prefilled cache holding ``n`` positions (eager) and allocate the step's fixed
-        buffers (ssa/kernels/graph_kernels.py:204-218).  ``fitted``: ``fit_layers`` has built the state."""
-        if not (fitted and self._fitted and self.n == n):
+        buffers (ssa/kernels/graph_kernels.py:204-218).  ``fitted``: ``fit_layers`` has built the state.
+        ``lengths``: device int32 lengths, one per sequence, of a batch fitted by ``fit_layers_ragged``."""
+        if lengths is None and not (fitted and self._fitted and self.n == n):
             self.observe(K, n)
         if not self._fitted:
             raise ValueError(f"n={n} leaves nothing to cluster behind a window of {self.window}")
         G = H // self.H_kv
         self.G = None
         q0 = torch.zeros(H, self.d, dtype=K.dtype, device=K.device)
-        self._n_scalar.fill_(n)
-        self.need_dev.fill_(math.ceil(self.budget * (self.end - 1)))
+        if lengths is not None:
+            self._n_scalar = lengths.clone()                 # one entry per sequence (n_group heads each)
+            self.need_dev.copy_(torch.ceil(self.budget * (self.end_dev - 1).double()).to(torch.int32))
+        else:
+            self._n_scalar.fill_(n)
+            self.need_dev.fill_(math.ceil(self.budget * (self.end - 1)))
         self._select(q0, self._n_scalar)
         self._attend(q0, K, K)                               # sizes the workspaces and the output
         if self._fused_rows(K):
@@ -664,9 +729,11 @@ class SphereIndexGraph:
     def _refit(self, K: torch.Tensor) -> None:
         """Fit again on every clustered key with a fresh mean (graph_kernels.py:271-279)."""
         self._host_end()
-        n = self.end + self.window
-        self.labels[:, 1:self.end].fill_(self.C)
-        self._build_all(K, n)
+        for end, group in self._by_end(torch.arange(self.H_kv)):
+            self.end = end
+            self.labels[group.to(self.labels.device), 1:end] = self.C
+            self._build_all(K, end + self.window, group if len(set(self._ends)) > 1 else None)
+        self.end = int(self._ends[0])
         self.flags.zero_()
         self._pending = None
         self.refits += 1

@@ -25,7 +25,7 @@ struct AttendParams {
     float *part;       // [heads, splits, G, 132]: 128 sums, max (base-2 units), sum of weights, 2 unused
     int32_t *ticket;   // [heads]
     int32_t *status;   // [heads] or null
-    int heads, G;
+    int heads, G, n_group;
     int64_t ksh, ksr, vsh, vsr, idx_stride;
     int rows_limit, splits;
     float scale_log2;  // softmax scale * log2(e)
@@ -63,7 +63,7 @@ struct Share {
 };
 __device__ __forceinline__ Share my_share(const AttendParams &p, int head, int split, int warp, int warps) {
     Share s;
-    s.count = p.idx ? p.cnt[head] : p.n_dev[0];
+    s.count = p.idx ? p.cnt[head] : positions_of(p.n_dev, p.n_group, head);
     if (s.count < 0) s.count = 0;
     const int tiles = (s.count + TILE_ROWS - 1) / TILE_ROWS;
     s.s_eff = min(p.splits, max(1, (tiles + warps - 1) / warps));
@@ -250,7 +250,7 @@ __global__ void __launch_bounds__(WARPS * 32, 3) attend_labels_kernel(const Atte
     const int warp = threadIdx.x >> 5, tid = threadIdx.x;
     const int head = blockIdx.y, split = blockIdx.x;
     const int G = p.G, C = p.C;
-    const int n = min(max(p.n_dev[0], 0), (int)p.lab_stride);
+    const int n = min(max(positions_of(p.n_dev, p.n_group, head), 0), (int)p.lab_stride);
     // position ranges: multiples of 16 so that a thread's 16 labels are two aligned 16-byte loads
     const int chunk = max(16, (((n + p.splits - 1) / p.splits + 15) >> 4) << 4);
     const int s_eff = max(1, (n + chunk - 1) / chunk);
@@ -499,7 +499,8 @@ extern "C" int64_t skv_attend_workspace_bytes(int heads, int G, int d, int split
 // Host-side checks of skv_attend's arguments (no CUDA call): shared with skv_attend_static so that both
 // reject the same calls with the same codes before anything is enqueued.
 static int attend_check(const void *q, const void *K, const void *V, const int32_t *idx, const int32_t *cnt,
-                        const int32_t *n_dev, const void *out, const void *workspace, int heads, int G, int d, int dtype,
+                        const int32_t *n_dev, int n_group, const void *out, const void *workspace, int heads, int G, int d,
+                        int dtype,
                         int64_t k_head_stride, int64_t k_row_stride, int64_t v_head_stride, int64_t v_row_stride,
                         int rows_limit, int splits) {
     const int base = dtype & 0xff;
@@ -508,7 +509,7 @@ static int attend_check(const void *q, const void *K, const void *V, const int32
     if (idx ? !cnt : !n_dev) return SKV_E_NULL;
     if (d != HEAD_DIM) return SKV_E_DIM;
     if (base != SKV_BF16 && base != SKV_F32) return SKV_E_DTYPE;
-    if (heads <= 0 || heads > 65535 || splits <= 0 || splits > 65535 || rows_limit < 0) return SKV_E_RANGE;
+    if (heads <= 0 || heads > 65535 || splits <= 0 || splits > 65535 || rows_limit < 0 || n_group < 0) return SKV_E_RANGE;
     if (G < 1 || G > 16 || ((base == SKV_F32 || force_simple) && G > 8)) return SKV_E_DIM;
     const int esz = base == SKV_BF16 ? 2 : 4;
     if (!aligned16(q) || !aligned16(K) || !aligned16(V) || !aligned16(out) || !aligned16(workspace)) return SKV_E_ALIGN;
@@ -520,20 +521,20 @@ static int attend_check(const void *q, const void *K, const void *V, const int32
 
 // mode bit 0 of `dtype >> 8` forces the CUDA-core path for bf16 (cross-checks)
 extern "C" int skv_attend(const void *q, const void *K, const void *V, const int32_t *idx, const int32_t *cnt,
-                          const int32_t *n_dev, void *out, void *workspace, int32_t *status, int heads, int G, int d,
-                          int dtype, int64_t k_head_stride, int64_t k_row_stride, int64_t v_head_stride,
+                          const int32_t *n_dev, int n_group, void *out, void *workspace, int32_t *status, int heads,
+                          int G, int d, int dtype, int64_t k_head_stride, int64_t k_row_stride, int64_t v_head_stride,
                           int64_t v_row_stride, int64_t idx_stride, int rows_limit, int splits, float scale,
                           void *stream) {
     const int base = dtype & 0xff;
     const bool force_simple = (dtype >> 8) & 1;
-    const int rc = attend_check(q, K, V, idx, cnt, n_dev, out, workspace, heads, G, d, dtype, k_head_stride,
+    const int rc = attend_check(q, K, V, idx, cnt, n_dev, n_group, out, workspace, heads, G, d, dtype, k_head_stride,
                                 k_row_stride, v_head_stride, v_row_stride, rows_limit, splits);
     if (rc) return rc;
     AttendParams p;
     p.q = q; p.K = K; p.V = V; p.idx = idx; p.cnt = cnt; p.n_dev = n_dev; p.out = out; p.status = status;
     p.part = static_cast<float *>(workspace);
     p.ticket = reinterpret_cast<int32_t *>(p.part + (int64_t)heads * splits * G * PART_LD);
-    p.heads = heads; p.G = G;
+    p.heads = heads; p.G = G; p.n_group = n_group;
     p.ksh = k_head_stride; p.ksr = k_row_stride; p.vsh = v_head_stride; p.vsr = v_row_stride;
     p.idx_stride = idx_stride; p.rows_limit = rows_limit; p.splits = splits;
     p.scale_log2 = scale * LOG2E;
@@ -547,7 +548,8 @@ extern "C" int skv_attend(const void *q, const void *K, const void *V, const int
 }
 
 extern "C" int skv_attend_labels(const void *q, const void *K, const void *V, const int16_t *labels,
-                                 int64_t label_stride, const uint32_t *selbits, int C, const int32_t *n_dev, void *out,
+                                 int64_t label_stride, const uint32_t *selbits, int C, const int32_t *n_dev, int n_group,
+                                 void *out,
                                  void *workspace, int32_t *cnt, int32_t *status, int heads, int G, int d, int dtype,
                                  int64_t k_head_stride, int64_t k_row_stride, int64_t v_head_stride,
                                  int64_t v_row_stride, int splits, float scale, void *stream) {
@@ -555,7 +557,7 @@ extern "C" int skv_attend_labels(const void *q, const void *K, const void *V, co
     if (d != HEAD_DIM) return SKV_E_DIM;
     if (dtype != SKV_BF16) return SKV_E_DTYPE;                   // float32 caches take the list path
     if (G < 1 || G > 16 || C < 16 || (C & (C - 1)) || C > 16384) return SKV_E_DIM;
-    if (heads <= 0 || heads > 65535 || splits <= 0 || splits > 65535 || label_stride <= 0) return SKV_E_RANGE;
+    if (heads <= 0 || heads > 65535 || splits <= 0 || splits > 65535 || label_stride <= 0 || n_group < 0) return SKV_E_RANGE;
     if (!aligned16(q) || !aligned16(K) || !aligned16(V) || !aligned16(out) || !aligned16(workspace) ||
         !aligned16(labels) || label_stride % 8)
         return SKV_E_ALIGN;
@@ -566,7 +568,7 @@ extern "C" int skv_attend_labels(const void *q, const void *K, const void *V, co
     p.q = q; p.K = K; p.V = V; p.idx = nullptr; p.cnt = nullptr; p.n_dev = n_dev; p.out = out; p.status = status;
     p.part = static_cast<float *>(workspace);
     p.ticket = reinterpret_cast<int32_t *>(p.part + (int64_t)heads * splits * G * PART_LD);
-    p.heads = heads; p.G = G;
+    p.heads = heads; p.G = G; p.n_group = n_group;
     p.ksh = k_head_stride; p.ksr = k_row_stride; p.vsh = v_head_stride; p.vsr = v_row_stride;
     p.idx_stride = 0; p.rows_limit = 0; p.splits = splits;
     p.scale_log2 = scale * LOG2E;
@@ -579,11 +581,12 @@ extern "C" int skv_attend_labels(const void *q, const void *K, const void *V, co
 }
 
 extern "C" int skv_attend_weighted(const void *q, const void *K, const void *V, const int16_t *labels,
-                                   int64_t label_stride, const float *w, int C, const int32_t *n_dev, void *out,
+                                   int64_t label_stride, const float *w, int C, const int32_t *n_dev, int n_group,
+                                   void *out,
                                    void *workspace, int32_t *status, int heads, int G, int d, int dtype,
                                    int64_t k_head_stride, int64_t k_row_stride, int64_t v_head_stride,
                                    int64_t v_row_stride, int splits, float scale, void *stream) {
-    const int rc = attend_check(q, K, V, nullptr, nullptr, n_dev, out, workspace, heads, G, d, dtype, k_head_stride,
+    const int rc = attend_check(q, K, V, nullptr, nullptr, n_dev, n_group, out, workspace, heads, G, d, dtype, k_head_stride,
                                 k_row_stride, v_head_stride, v_row_stride, 0, splits);
     if (rc) return rc;
     if (!labels || !w) return SKV_E_NULL;
@@ -593,7 +596,7 @@ extern "C" int skv_attend_weighted(const void *q, const void *K, const void *V, 
     p.q = q; p.K = K; p.V = V; p.idx = nullptr; p.cnt = nullptr; p.n_dev = n_dev; p.out = out; p.status = status;
     p.part = static_cast<float *>(workspace);
     p.ticket = reinterpret_cast<int32_t *>(p.part + (int64_t)heads * splits * G * PART_LD);
-    p.heads = heads; p.G = G;
+    p.heads = heads; p.G = G; p.n_group = n_group;
     p.ksh = k_head_stride; p.ksr = k_row_stride; p.vsh = v_head_stride; p.vsr = v_row_stride;
     p.idx_stride = 0; p.rows_limit = 0; p.splits = splits;
     p.scale_log2 = scale * LOG2E;
@@ -639,13 +642,14 @@ static int static_scratch(void **out) {
 }
 
 extern "C" int skv_attend_static(const void *q, const void *K, const void *V, const int32_t *idx, const int32_t *cnt,
-                                 const int32_t *n_dev, void *out, int32_t *status, int heads, int G, int d, int dtype,
+                                 const int32_t *n_dev, int n_group, void *out, int32_t *status, int heads, int G, int d,
+                                 int dtype,
                                  int64_t k_head_stride, int64_t k_row_stride, int64_t v_head_stride,
                                  int64_t v_row_stride, int64_t idx_stride, int rows_limit, int splits, float scale,
                                  void *stream) {
     // the same argument checks as skv_attend, ahead of every CUDA call (any aligned non-null pointer stands in for
     // the workspace, which is the library's own array here)
-    int rc = attend_check(q, K, V, idx, cnt, n_dev, out, q, heads, G, d, dtype, k_head_stride, k_row_stride,
+    int rc = attend_check(q, K, V, idx, cnt, n_dev, n_group, out, q, heads, G, d, dtype, k_head_stride, k_row_stride,
                           v_head_stride, v_row_stride, rows_limit, splits);
     if (rc) return rc;
     const int64_t need = skv_attend_workspace_bytes(heads, G, d, splits);
@@ -658,6 +662,6 @@ extern "C" int skv_attend_static(const void *q, const void *K, const void *V, co
     // zero (partials are always written before they are read); they sit at the end of the layout.
     unsigned char *tickets = static_cast<unsigned char *>(scratch) + (int64_t)heads * splits * G * PART_LD * 4;
     SKV_CUDA_OK(cudaMemsetAsync(tickets, 0, (size_t)heads * 4, static_cast<cudaStream_t>(stream)));
-    return skv_attend(q, K, V, idx, cnt, n_dev, out, scratch, status, heads, G, d, dtype, k_head_stride, k_row_stride,
+    return skv_attend(q, K, V, idx, cnt, n_dev, n_group, out, scratch, status, heads, G, d, dtype, k_head_stride, k_row_stride,
                       v_head_stride, v_row_stride, idx_stride, rows_limit, splits, scale, stream);
 }

@@ -54,6 +54,12 @@ static inline cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 blo
     return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
 }
 
+// Cached positions of head `head`: runs of `n_group` consecutive heads share one entry of n_dev (a batch whose
+// sequences differ in length: n_group = KV heads per sequence); n_group 0 = every head reads n_dev[0].
+__device__ __forceinline__ int positions_of(const int32_t *n_dev, int n_group, int head) {
+    return n_dev[n_group > 0 ? head / n_group : 0];
+}
+
 // ---------------------------------------------------------------------------------------------
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll

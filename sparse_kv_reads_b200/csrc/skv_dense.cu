@@ -47,12 +47,12 @@ __global__ void __launch_bounds__(256) add_rmsnorm_kernel(__nv_bfloat16 *h, cons
     }
 }
 
-// qkv [B, (H + 2*H_kv) * 128] -> q_out [B*H, 128] (normed, rotated), K/V cache rows at position pos[0].
+// qkv [B, (H + 2*H_kv) * 128] -> q_out [B*H, 128] (normed, rotated), K/V cache rows at the new token's position (pos[0], or pos[sequence]).
 // One warp per (sequence, head); lane l owns components 4l..4l+3; the rotation pairs i with i+64.
 __global__ void __launch_bounds__(128) qk_rope_cache_kernel(const __nv_bfloat16 *qkv, const __nv_bfloat16 *qw,
                                                             const __nv_bfloat16 *kw, const __nv_bfloat16 *cos_t,
                                                             const __nv_bfloat16 *sin_t, const int64_t *pos_dev,
-                                                            __nv_bfloat16 *q_out, __nv_bfloat16 *k_cache,
+                                                            int pos_per_seq, __nv_bfloat16 *q_out, __nv_bfloat16 *k_cache,
                                                             __nv_bfloat16 *v_cache, int B, int H, int H_kv,
                                                             int64_t cache_b_stride, int64_t cache_h_stride,
                                                             int64_t cache_row_stride, float eps) {
@@ -63,7 +63,7 @@ __global__ void __launch_bounds__(128) qk_rope_cache_kernel(const __nv_bfloat16 
     const int per = H + 2 * H_kv;
     if (item >= B * per) return;
     const int b = item / per, j = item % per;
-    const int64_t pos = pos_dev[0];
+    const int64_t pos = pos_dev[pos_per_seq ? b : 0];
     const __nv_bfloat16 *src = qkv + ((int64_t)b * per + j) * HEAD_DIM + lane * 4;
     if (j >= H + H_kv) {                                              // value head: straight into the cache
         __nv_bfloat16 *dst = v_cache + b * cache_b_stride + (j - H - H_kv) * cache_h_stride + pos * cache_row_stride;
@@ -111,7 +111,7 @@ extern "C" int skv_add_rmsnorm(void *h, const void *delta, const void *w, void *
 }
 
 extern "C" int skv_qk_rope_cache(const void *qkv, const void *q_norm_w, const void *k_norm_w, const void *cos_table,
-                                 const void *sin_table, const int64_t *pos_dev, void *q_out, void *k_cache,
+                                 const void *sin_table, const int64_t *pos_dev, int pos_per_seq, void *q_out, void *k_cache,
                                  void *v_cache, int B, int H, int H_kv, int d, int64_t cache_batch_stride,
                                  int64_t cache_head_stride, int64_t cache_row_stride, float eps, void *stream) {
     if (!qkv || !q_norm_w || !k_norm_w || !cos_table || !sin_table || !pos_dev || !q_out || !k_cache || !v_cache)
@@ -125,7 +125,7 @@ extern "C" int skv_qk_rope_cache(const void *qkv, const void *q_norm_w, const vo
     SKV_CUDA_OK(launch_pdl(qk_rope_cache_kernel, dim3((items + 3) / 4), dim3(128), 0, static_cast<cudaStream_t>(stream),
         static_cast<const __nv_bfloat16 *>(qkv), static_cast<const __nv_bfloat16 *>(q_norm_w),
         static_cast<const __nv_bfloat16 *>(k_norm_w), static_cast<const __nv_bfloat16 *>(cos_table),
-        static_cast<const __nv_bfloat16 *>(sin_table), pos_dev, static_cast<__nv_bfloat16 *>(q_out),
+        static_cast<const __nv_bfloat16 *>(sin_table), pos_dev, pos_per_seq, static_cast<__nv_bfloat16 *>(q_out),
         static_cast<__nv_bfloat16 *>(k_cache), static_cast<__nv_bfloat16 *>(v_cache), B, H, H_kv, cache_batch_stride,
         cache_head_stride, cache_row_stride, eps));
     SKV_CUDA_OK(cudaGetLastError());

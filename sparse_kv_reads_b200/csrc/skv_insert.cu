@@ -19,6 +19,7 @@ struct InsertParams {
     int hpl;
     int64_t ksh, ksr;
     const int32_t *n_dev;
+    int n_group;
     int window;
     double budget;
     float delta;
@@ -268,7 +269,7 @@ __global__ void __launch_bounds__(INS_THREADS) insert_kernel(const InsertParams 
     sm.mem = reinterpret_cast<int *>(sm.proj + p.max_members);
     sm.side = reinterpret_cast<uint8_t *>(sm.mem + p.max_members);
 
-    const int n = p.n_dev[0];
+    const int n = positions_of(p.n_dev, p.n_group, hh);
     const int old_end = p.st.end[e];
     int n_act = min(p.st.n_c[e], C);                      // a corrupt count must not index past the slots
     int new_end = max(max(n - p.window, 1), old_end);
@@ -411,7 +412,8 @@ extern "C" int skv_insert_max_members(void) {
 }
 
 extern "C" int skv_insert(const skv_state *st, const void *const *k_layers, int heads_per_layer, int dtype,
-                          int64_t k_head_stride, int64_t k_row_stride, const int32_t *n_dev, int window, double budget,
+                          int64_t k_head_stride, int64_t k_row_stride, const int32_t *n_dev, int n_group, int window,
+                          double budget,
                           float delta, int reset_at, int max_members, float capk, int var_min, void *stream) {
     if (!st || !k_layers || !n_dev) return SKV_E_NULL;
     if (!st->sum_dir || !st->cent || !st->mmax || !st->mmin || !st->count || !st->n_c || !st->cap || !st->rbar ||
@@ -423,7 +425,7 @@ extern "C" int skv_insert(const skv_state *st, const void *const *k_layers, int 
     if (st->summary_bits != 8 && st->summary_bits != 32) return SKV_E_RANGE;
     if (st->summary_bits == 8 && (!st->dir8 || !st->cent8)) return SKV_E_NULL;
     if (st->heads <= 0 || heads_per_layer <= 0 || st->heads % heads_per_layer || window < 0 || budget < 0.0 ||
-        st->capacity <= 0 || reset_at < 0 || capk < 0.f || var_min < 0)
+        st->capacity <= 0 || reset_at < 0 || capk < 0.f || var_min < 0 || n_group < 0)
         return SKV_E_RANGE;
     if (max_members < 2 || max_members > skv_insert_max_members()) return SKV_E_RANGE;
     const int esz = dtype == SKV_BF16 ? 2 : 4;
@@ -432,7 +434,7 @@ extern "C" int skv_insert(const skv_state *st, const void *const *k_layers, int 
     if (st->summary_bits == 8 && !aligned16(st->cent8)) return SKV_E_ALIGN;
     InsertParams p;
     p.st = *st; p.k_layers = k_layers; p.hpl = heads_per_layer; p.ksh = k_head_stride; p.ksr = k_row_stride;
-    p.n_dev = n_dev; p.window = window; p.budget = budget; p.delta = delta; p.reset_at = reset_at;
+    p.n_dev = n_dev; p.n_group = n_group; p.window = window; p.budget = budget; p.delta = delta; p.reset_at = reset_at;
     p.max_members = max_members; p.capk = capk; p.var_min = var_min;
     const size_t smem = insert_smem(max_members);
     auto kern = dtype == SKV_BF16 ? insert_kernel<__nv_bfloat16> : insert_kernel<float>;

@@ -23,6 +23,7 @@ struct SelectParams {
     const void *q;
     int G;
     const int32_t *n_dev;
+    int n_group;
     float *w;
     uint32_t *selbits;        // [heads, C/32 + 1]
     int32_t *idx;             // null: no row list is built
@@ -107,7 +108,7 @@ __device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
 __device__ __forceinline__ void rope_heads(const skv_rope &r, int h, bool first, int G, float *sq) {
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
     const int seq = h / r.H_kv, hk = h % r.H_kv, per_seq = r.H + 2 * r.H_kv;
-    const int64_t pos = r.pos[0];
+    const int64_t pos = r.pos[r.pos_per_seq ? seq : 0];
     const __nv_bfloat16 *row = static_cast<const __nv_bfloat16 *>(r.qkv) + (int64_t)seq * per_seq * HEAD_DIM;
     const __nv_bfloat16 *cs = static_cast<const __nv_bfloat16 *>(r.cos_table) + pos * HEAD_DIM;
     const __nv_bfloat16 *sn = static_cast<const __nv_bfloat16 *>(r.sin_table) + pos * HEAD_DIM;
@@ -534,7 +535,7 @@ __global__ void __launch_bounds__(512) list_kernel(const SelectParams p) {
     for (int i = tid; i < words; i += 512) bits[i] = p.selbits[(int64_t)h * words + i];
     __syncthreads();
     const int16_t *lab = p.st.labels + (int64_t)h * p.st.capacity;
-    const int nn = min(max(p.n_dev[0], 0), p.st.capacity);
+    const int nn = min(max(positions_of(p.n_dev, p.n_group, h), 0), p.st.capacity);
     const int vecs = (nn + 7) >> 3;
     const int per = (vecs + 511) / 512;
     const int v0 = min(tid * per, vecs), v1 = min(v0 + per, vecs);
@@ -600,7 +601,7 @@ extern "C" int64_t skv_select_workspace_bytes(int heads, int G, int C) {
     return select_ws_bytes(heads, G, C);
 }
 
-extern "C" int skv_select(const skv_state *st, const void *q, int dtype, int G, const int32_t *n_dev, float *w,
+extern "C" int skv_select(const skv_state *st, const void *q, int dtype, int G, const int32_t *n_dev, int n_group, float *w,
                           uint32_t *selbits, int32_t *idx, int64_t idx_stride, int32_t *cnt, const float *shared_in,
                           float *shared_out, float *e_out, void *workspace, float scale, int group,
                           const skv_rope *rope, void *stream) {
@@ -625,7 +626,7 @@ extern "C" int skv_select(const skv_state *st, const void *q, int dtype, int G, 
     if (G < 1 || G > 16) return SKV_E_DIM;
     if (dtype != SKV_BF16 && dtype != SKV_F32) return SKV_E_DTYPE;
     if (st->summary_bits != 8 && st->summary_bits != 32) return SKV_E_RANGE;
-    if (group < SKV_GROUP_SUM_SHARE || group > SKV_GROUP_MAX_REL) return SKV_E_RANGE;
+    if (group < SKV_GROUP_SUM_SHARE || group > SKV_GROUP_MAX_REL || n_group < 0) return SKV_E_RANGE;
     if (st->summary_bits == 8 ? !st->dir8 : !st->sum_dir) return SKV_E_NULL;
     if (st->heads <= 0 || st->heads > 65535 || st->capacity <= 0 || (idx && idx_stride < st->capacity)) return SKV_E_RANGE;
     if (st->capacity % 8 || !aligned16(st->labels) || !aligned16(workspace)) return SKV_E_ALIGN;
@@ -633,7 +634,7 @@ extern "C" int skv_select(const skv_state *st, const void *q, int dtype, int G, 
     const size_t smem = select_smem(G, st->C, shared_in == nullptr);
     if ((int)smem > device_max_smem_optin()) return SKV_E_DIM;
     SelectParams p;
-    p.st = *st; p.q = q; p.G = G; p.n_dev = n_dev; p.w = w; p.idx = idx; p.idx_stride = idx_stride; p.cnt = cnt;
+    p.st = *st; p.q = q; p.G = G; p.n_dev = n_dev; p.n_group = n_group; p.w = w; p.idx = idx; p.idx_stride = idx_stride; p.cnt = cnt;
     p.shared_in = shared_in; p.shared_out = shared_out; p.e_out = e_out; p.scale = scale; p.group = group;
     p.rope = rope ? *rope : skv_rope{};
     p.probe = g_probe;

@@ -33,6 +33,7 @@ struct StepParams {
     const void *q;             // [heads*G, 128] bf16 (unused with rope)
     const void *K, *V;
     const int32_t *n_dev;
+    int n_group;
     void *out;
     float *w;                  // [heads, C+1] or null
     uint32_t *selbits;         // [heads, C/32+1] or null
@@ -133,7 +134,7 @@ __device__ __forceinline__ void step_rope(const skv_rope &r, int h, bool store_q
                                           __nv_bfloat16 *sqb) {
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
     const int seq = h / r.H_kv, hk = h % r.H_kv, per_seq = r.H + 2 * r.H_kv;
-    const int64_t pos = r.pos[0];
+    const int64_t pos = r.pos[r.pos_per_seq ? seq : 0];
     const __nv_bfloat16 *row = static_cast<const __nv_bfloat16 *>(r.qkv) + (int64_t)seq * per_seq * HEAD_DIM;
     const __nv_bfloat16 *cs = static_cast<const __nv_bfloat16 *>(r.cos_table) + pos * HEAD_DIM;
     const __nv_bfloat16 *sn = static_cast<const __nv_bfloat16 *>(r.sin_table) + pos * HEAD_DIM;
@@ -219,7 +220,7 @@ __global__ void __launch_bounds__(STEP_THREADS, 2) step_kernel(const StepParams 
     // ---- every load that depends on nothing goes out first, the ones sized by the cluster count right after ----
     const int n_c = min(max(p.st.n_c[h], 0), C);
     const int end = p.st.end[h], need = p.st.need[h];
-    const int n = min(max(p.n_dev[0], 0), p.st.capacity);
+    const int n = min(max(positions_of(p.n_dev, p.n_group, h), 0), p.st.capacity);
     uint2 qraw[2] = {make_uint2(0u, 0u), make_uint2(0u, 0u)};                 // four query components per piece
     if (!p.rope.qkv) {
         const uint2 *qsrc = reinterpret_cast<const uint2 *>(static_cast<const __nv_bfloat16 *>(p.q) + (int64_t)h * G * HEAD_DIM);
@@ -257,7 +258,7 @@ __global__ void __launch_bounds__(STEP_THREADS, 2) step_kernel(const StepParams 
     pdl_trigger();
     step_stamp(p, 1);
     if (p.rope.qkv) {
-        const int64_t pos = p.rope.pos[0];
+        const int64_t pos = p.rope.pos[p.rope.pos_per_seq ? h / p.rope.H_kv : 0];
         const int s_kv = (int)min((int64_t)(S - 1), max((int64_t)0, pos / chunk));
         step_rope(p.rope, h, split == 0, split == s_kv, G, sq, sqb);
     } else {
@@ -656,7 +657,8 @@ extern "C" int64_t skv_step_workspace_bytes(int heads, int G, int clusters) {
     return part + (((int64_t)heads * 4) + 255) / 256 * 256;
 }
 
-extern "C" int skv_step(const skv_state *st, const void *q, int G, const int32_t *n_dev, const void *K, const void *V,
+extern "C" int skv_step(const skv_state *st, const void *q, int G, const int32_t *n_dev, int n_group, const void *K,
+                        const void *V,
                         int64_t k_head_stride, int64_t k_row_stride, int64_t v_head_stride, int64_t v_row_stride,
                         float *w, uint32_t *selbits, int32_t *cnt, void *out, void *workspace, int clusters,
                         float scale, const skv_rope *rope, void *stream) {
@@ -678,7 +680,8 @@ extern "C" int skv_step(const skv_state *st, const void *q, int G, const int32_t
     if (st->d != HEAD_DIM || G < 1 || G > 8) return SKV_E_DIM;
     if (st->C < 64 || (st->C & (st->C - 1)) || st->C > 2048 || clusters > STEP_CS) return SKV_E_DIM;
     if (st->summary_bits != 8) return SKV_E_RANGE;
-    if (st->heads <= 0 || st->heads > 65535 || st->capacity <= 0 || clusters < 1 || clusters > 64) return SKV_E_RANGE;
+    if (st->heads <= 0 || st->heads > 65535 || st->capacity <= 0 || clusters < 1 || clusters > 64 || n_group < 0)
+        return SKV_E_RANGE;
     if (st->capacity % 8 || !aligned16(st->labels) || !aligned16(st->dir8) || !aligned16(workspace) || !aligned16(K) ||
         !aligned16(V) || (out && !aligned16(out)) || (q && !aligned16(q)))
         return SKV_E_ALIGN;
@@ -688,7 +691,7 @@ extern "C" int skv_step(const skv_state *st, const void *q, int G, const int32_t
     const size_t smem = step_smem_bytes(G, st->C, step_stages());
     if ((int)smem > device_max_smem_optin()) return SKV_E_DIM;
     StepParams p;
-    p.st = *st; p.q = q; p.K = K; p.V = V; p.n_dev = n_dev; p.out = out; p.w = w; p.selbits = selbits; p.cnt = cnt;
+    p.st = *st; p.q = q; p.K = K; p.V = V; p.n_dev = n_dev; p.n_group = n_group; p.out = out; p.w = w; p.selbits = selbits; p.cnt = cnt;
     p.part = static_cast<float *>(workspace);
     p.ticket = reinterpret_cast<int32_t *>(static_cast<char *>(workspace) +
                                            (((int64_t)st->heads * clusters * G * STEP_PART_LD * 4) + 255) / 256 * 256);

@@ -21,7 +21,7 @@ import torch.nn.functional as F
 
 from . import _lib
 from ._lib import check, dtype_code, lib, stream_ptr
-from .cluster_state import AttentionPartials, ClusterArena, SphereIndexGraph, fit_layers
+from .cluster_state import AttentionPartials, ClusterArena, SphereIndexGraph, fit_layers, fit_layers_ragged
 from .qwen3 import Qwen3Model, apply_rope
 
 
@@ -32,6 +32,7 @@ class DenseAttentionGraph:
     def __init__(self, *, H: int, H_kv: int, d: int, dtype, device):
         L = lib()
         self.H, self.H_kv, self.d, self.G = H, H_kv, d, H // H_kv
+        self.n_group = 0                                   # heads per entry of the device-side lengths (0: one length)
         self.num_splits = L.skv_attend_splits(H_kv)
         self.ws = torch.zeros(L.skv_attend_workspace_bytes(H_kv, self.G, d, self.num_splits), dtype=torch.uint8,
                               device=device)
@@ -40,7 +41,7 @@ class DenseAttentionGraph:
     def __call__(self, q: torch.Tensor, K: torch.Tensor, V: torch.Tensor, n_dev: torch.Tensor) -> torch.Tensor:
         if not q.is_contiguous():
             q = q.contiguous()
-        check(lib().skv_attend(q.data_ptr(), K.data_ptr(), V.data_ptr(), None, None, n_dev.data_ptr(),
+        check(lib().skv_attend(q.data_ptr(), K.data_ptr(), V.data_ptr(), None, None, n_dev.data_ptr(), self.n_group,
                                self.out.data_ptr(), self.ws.data_ptr(), None, self.H_kv, self.G, self.d,
                                dtype_code(K.dtype), K.stride(0), K.stride(1), V.stride(0), V.stride(1), 0, K.shape[1],
                                self.num_splits, 1.0 / math.sqrt(self.d), stream_ptr(q.device)), "skv_attend")
@@ -69,7 +70,7 @@ class AllLayerInsert:
     def __call__(self, n_dev: torch.Tensor) -> None:
         f = self.layers[0]
         check(lib().skv_insert(ctypes.byref(self.st), self.table.data_ptr(), f.H_kv, dtype_code(self.k0.dtype),
-                               self.k0.stride(0), self.k0.stride(1), n_dev.data_ptr(), f.window, float(f.budget),
+                               self.k0.stride(0), self.k0.stride(1), n_dev.data_ptr(), f.n_group, f.window, float(f.budget),
                                float(min(f.delta, 3.0e38)), f.reset_at, self.max_members, f.capk, f.var_min,
                                stream_ptr(self.k0.device)),
               "skv_insert")
@@ -117,6 +118,7 @@ class GraphDecoder:
                          for i in range(nl)]
         self.graph = None
         self.logits = None
+        self.ragged = False                                # True once prepare() was given one length per sequence
         # the bundled bf16 model runs its element-wise decode ops as three fused launches per layer
         self.fused_dense = fused_dense and isinstance(model, Qwen3Model) and dtype == torch.bfloat16 \
             and dev.type == "cuda"
@@ -142,8 +144,13 @@ class GraphDecoder:
         """Cache ``[B, H_kv, L, d]`` -> ``[B*H_kv, L, d]`` (a view)."""
         return c.view(-1, c.shape[2], c.shape[3])
 
-    def prepare(self, n: int) -> None:
-        """Build the attention state from the first ``n`` cached positions (after the prompt)."""
+    def prepare(self, n) -> None:
+        """Build the attention state from the first ``n`` cached positions (after the prompt).  ``n`` may be a
+        list with one length per sequence: the batch then decodes sequences of different lengths (each head reads
+        its own sequence's length and position from device memory), which lifts the reference's equal-length limit
+        (README.md:62); ``step`` then takes one position per sequence."""
+        if not isinstance(n, int):
+            return self._prepare_ragged([int(x) for x in n])
         if self.mode != "cluster":
             return
         caches = [self._heads(self.cache.k[i]) for i in range(len(self.attn))]
@@ -156,11 +163,33 @@ class GraphDecoder:
         if self.fused_insert:
             self.insert_all = AllLayerInsert(self.attn, [self._heads(k) for k in self.cache.k[:len(self.attn)]])
 
+    def _prepare_ragged(self, lengths: list[int]) -> None:
+        if len(lengths) != self.B:
+            raise ValueError("one length per sequence is needed")
+        if not self.fused_dense:
+            raise ValueError("a variable-length batch needs the bundled bf16 model's fused layers")
+        dev = self.tok.device
+        self.ragged = True
+        self.pos = torch.tensor(lengths, dtype=torch.long, device=dev)
+        self.n_dev = torch.tensor(lengths, dtype=torch.int32, device=dev)
+        for a in self.attn:
+            a.n_group = self.H_kv                          # KV heads per sequence share one length
+        if self.mode != "cluster":
+            return
+        caches = [self._heads(self.cache.k[i]) for i in range(len(self.attn))]
+        fit_layers_ragged(self.attn, caches, lengths, self.H_kv)
+        for idx, K in zip(self.attn, caches):
+            idx.prepare(K, max(lengths), self.B * self.H, fitted=True, lengths=self.n_dev)
+        if self.fused_insert:
+            self.insert_all = AllLayerInsert(self.attn, caches)
+
     # ---- checkpoint / resume -----------------------------------------------------------------------
     def state_dict(self) -> dict:
         """The cluster state of every layer (device arrays copied to the CPU, host counters) and the number of
         cached positions it describes.  Together with the KV cache itself (kept by the caller) this is all a
         later process needs to go on decoding as if it had never stopped.  Synchronises."""
+        if self.ragged:
+            raise ValueError("saving the state of a variable-length batch is not supported")
         if self.mode != "cluster":
             return {"n": self.cache.cur_len, "layers": []}
         return {"n": self.cache.cur_len, "layers": [a.state_dict() for a in self.attn]}
@@ -185,6 +214,7 @@ class GraphDecoder:
     def _body(self) -> torch.Tensor:
         if self.fused_dense:
             return self._body_fused()
+        assert not self.ragged
         m, H, H_kv, d, B = self.model, self.H, self.H_kv, self.d, self.B
         torch.add(self.pos, 1, out=self.n_dev)
         if self.insert_all is not None:
@@ -261,8 +291,8 @@ class GraphDecoder:
             kc, vc = self.cache.k[i], self.cache.v[i]
             check(L.skv_qk_rope_cache(qkv.data_ptr(), a.q_norm.weight.data_ptr(), a.k_norm.weight.data_ptr(),
                                       m.rope_cos.data_ptr(), m.rope_sin.data_ptr(), self.pos.data_ptr(),
-                                      qh.data_ptr(), kc.data_ptr(), vc.data_ptr(), B, H, H_kv, d, kc.stride(0),
-                                      kc.stride(1), kc.stride(2), a.q_norm.eps, st), "skv_qk_rope_cache")
+                                      int(self.ragged), qh.data_ptr(), kc.data_ptr(), vc.data_ptr(), B, H, H_kv, d,
+                                      kc.stride(0), kc.stride(1), kc.stride(2), a.q_norm.eps, st), "skv_qk_rope_cache")
             if self.mode == "dense":
                 out = self.attn[i](qh, self._heads(kc), self._heads(vc), self.n_dev)
             else:
@@ -378,14 +408,15 @@ class GraphDecoder:
                 rope = _lib.SkvRope(qkv.data_ptr(), a.q_norm.weight.data_ptr(), a.k_norm.weight.data_ptr(),
                                     m.rope_cos.data_ptr(), m.rope_sin.data_ptr(), self.pos.data_ptr(), qh.data_ptr(),
                                     kc.data_ptr(), vc.data_ptr(), H, H_kv, kc.stride(0), kc.stride(1), kc.stride(2),
-                                    a.q_norm.eps, 0)
+                                    a.q_norm.eps, int(self.ragged))
                 out = self.attn[i].step(qh, self._heads(kc), self._heads(vc), self.n_dev,
                                         insert=self.insert_all is None, rope=rope, defer_merge=defer)
             else:
                 check(L.skv_qk_rope_cache(qkv.data_ptr(), a.q_norm.weight.data_ptr(), a.k_norm.weight.data_ptr(),
                                           m.rope_cos.data_ptr(), m.rope_sin.data_ptr(), self.pos.data_ptr(),
-                                          qh.data_ptr(), kc.data_ptr(), vc.data_ptr(), B, H, H_kv, d, kc.stride(0),
-                                          kc.stride(1), kc.stride(2), a.q_norm.eps, st), "skv_qk_rope_cache")
+                                          int(self.ragged), qh.data_ptr(), kc.data_ptr(), vc.data_ptr(), B, H, H_kv, d,
+                                          kc.stride(0), kc.stride(1), kc.stride(2), a.q_norm.eps, st),
+                      "skv_qk_rope_cache")
                 if self.mode == "dense":
                     out = self.attn[i](qh, self._heads(kc), self._heads(vc), self.n_dev)
                 else:
@@ -421,7 +452,10 @@ class GraphDecoder:
     def capture(self) -> None:
         """Record one decode step.  Call after ``prepare`` and before the first ``step``; the warm-up
         runs write a placeholder at the current position, which the first real step overwrites."""
-        self.pos.fill_(self.cache.cur_len)
+        if self.ragged:
+            self.pos.copy_(torch.tensor(self.cache.cur_len, dtype=torch.long))
+        else:
+            self.pos.fill_(self.cache.cur_len)
         s = torch.cuda.Stream()
         s.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(s), torch.no_grad():
@@ -438,11 +472,17 @@ class GraphDecoder:
         self.graph = g
 
     @torch.no_grad()
-    def step(self, token: torch.Tensor, pos: int) -> torch.Tensor:
-        """Decode ``token [B, 1]`` at position ``pos``; returns logits ``[B, 1, vocab]`` (a buffer the
-        next step overwrites)."""
+    def step(self, token: torch.Tensor, pos) -> torch.Tensor:
+        """Decode ``token [B, 1]`` at position ``pos`` (one position per sequence, a list or tensor ``[B]``, for a
+        batch prepared with one length per sequence); returns logits ``[B, 1, vocab]`` (a buffer the next step
+        overwrites)."""
         self.tok.copy_(token, non_blocking=True)           # a pinned host tensor goes straight into the step's buffer
-        self.pos.fill_(pos)
+        if self.ragged:
+            if not torch.is_tensor(pos):
+                pos = torch.tensor([int(x) for x in pos], dtype=torch.long)
+            self.pos.copy_(pos, non_blocking=True)
+        else:
+            self.pos.fill_(pos)
         if self.graph is not None:
             self.graph.replay()
         else:
@@ -450,5 +490,5 @@ class GraphDecoder:
         if self.mode == "cluster":
             for i, idx in enumerate(self.attn):
                 idx.after_replay(self._heads(self.cache.k[i]))
-        self.cache.cur_len = pos + 1
+        self.cache.cur_len = (pos + 1).tolist() if self.ragged else pos + 1
         return self.logits

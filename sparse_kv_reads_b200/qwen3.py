@@ -231,6 +231,20 @@ class Qwen3Model(nn.Module):
         return self.logits(h)
 
     @torch.no_grad()
+    def prefill_ragged(self, prompts: list[torch.Tensor], cache: KVCache, chunk: int = 2048) -> list[torch.Tensor]:
+        """Prompts of different lengths, one per sequence of the cache: sequence ``b`` is prefilled on its own rows
+        of the cache (a view of batch 1).  Returns the last-position logits of each; ``cache.cur_len`` becomes the
+        list of lengths."""
+        outs = []
+        for b, ids in enumerate(prompts):
+            view = KVCache.__new__(KVCache)
+            view.k, view.v = [k[b:b + 1] for k in cache.k], [v[b:b + 1] for v in cache.v]
+            view.cur_len, view.max_seq_len = 0, cache.max_seq_len
+            outs.append(self.prefill(ids.view(1, -1), view, chunk=chunk))
+        cache.cur_len = [int(p.numel()) for p in prompts]
+        return outs
+
+    @torch.no_grad()
     def prefill(self, ids: torch.Tensor, cache: KVCache, chunk: int = 2048) -> torch.Tensor:
         """Run the prompt through the model in chunks; returns the logits of the last position."""
         out = None

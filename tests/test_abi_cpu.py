@@ -35,7 +35,7 @@ def test_every_declared_entry_point_is_exported(L):
     for name in names:
         assert hasattr(L, name), name
     assert set(names) == set(_lib.EXPORTS)
-    assert L.skv_version() == 100
+    assert L.skv_version() == 101
     assert L.skv_error_string(-4).decode().startswith("pointer or stride")
 
 
@@ -63,7 +63,7 @@ def test_attend_rejects_bad_arguments(L):
 
     def call(**over):
         a = {**args, **over}
-        return L.skv_attend(a["q"], a["K"], a["V"], a["idx"], a["cnt"], a["n_dev"], a["out"], a["ws"], a["status"],
+        return L.skv_attend(a["q"], a["K"], a["V"], a["idx"], a["cnt"], a["n_dev"], 0, a["out"], a["ws"], a["status"],
                             a["heads"], a["G"], a["d"], a["dtype"], a["ksh"], a["ksr"], a["vsh"], a["vsr"], a["istr"],
                             a["lim"], a["splits"], 0.1, None)
 
@@ -87,7 +87,7 @@ def test_attend_static_rejects_the_same_calls_before_any_cuda_call(L):
 
     def call(**over):
         a = {**args, **over}
-        return L.skv_attend_static(a["q"], a["K"], a["V"], a["idx"], a["cnt"], a["n_dev"], a["out"], a["status"],
+        return L.skv_attend_static(a["q"], a["K"], a["V"], a["idx"], a["cnt"], a["n_dev"], 0, a["out"], a["status"],
                                    a["heads"], a["G"], a["d"], a["dtype"], a["ksh"], a["ksr"], a["vsh"], a["vsr"],
                                    a["istr"], a["lim"], a["splits"], 0.1, None)
 
@@ -104,26 +104,28 @@ def test_attend_static_rejects_the_same_calls_before_any_cuda_call(L):
 def test_state_calls_reject_bad_arguments(L):
     ok = 0x1000
     st = fake_state()
-    sel = lambda s, **o: L.skv_select(ctypes.byref(s), o.get("q", ok), o.get("dtype", 0), o.get("G", 2), ok, ok, ok, ok,
-                                      o.get("istr", 64), ok, None, None, None, o.get("ws", ok), 0.1, o.get("group", 0),
+    sel = lambda s, **o: L.skv_select(ctypes.byref(s), o.get("q", ok), o.get("dtype", 0), o.get("G", 2), ok, o.get("ng", 0), ok, ok,
+                                      ok, o.get("istr", 64), ok, None, None, None, o.get("ws", ok), 0.1, o.get("group", 0),
                                       o.get("rope", None), None)
     assert sel(fake_state(C=48)) == -2 and sel(fake_state(C=8)) == -2 and sel(st, G=0) == -2
     assert sel(st, q=None) == -1 and sel(st, dtype=5) == -3 and sel(st, istr=8) == -5
-    assert sel(st, group=3) == -5 and sel(st, group=-1) == -5
+    assert sel(st, group=3) == -5 and sel(st, group=-1) == -5 and sel(st, ng=-1) == -5
     assert sel(fake_state(cap=60)) == -4 and sel(fake_state(bits=16)) == -5
     bad = fake_state(bits=8)
     bad.dir8 = None
     assert sel(bad) == -1 and sel(st, ws=None) == -1
     assert L.skv_select_workspace_bytes(8, 2, 2048) == 8 * 2 * 2048 * 4 + 256 + 2304 + 8 * 64 * 32 * 4
     assert L.skv_select_workspace_bytes(8, 2, 100) == -5
-    lab = lambda **o: L.skv_attend_labels(ok, ok, ok, ok, o.get("ls", 64), ok, o.get("C", 64), ok, ok, ok, None, None, 2,
+    lab = lambda **o: L.skv_attend_labels(ok, ok, ok, ok, o.get("ls", 64), ok, o.get("C", 64), ok, o.get("ng", 0), ok, ok,
+                                          None, None, 2,
                                           o.get("G", 2), 128, o.get("dtype", 0), 128 * 64, 128, 128 * 64, 128, 4, 0.1, None)
+    assert lab(ng=-2) == -5
     assert lab(ls=36) == -4 and lab(C=48) == -2 and lab(dtype=1) == -3 and lab(G=17) == -2
-    ins = lambda s, **o: L.skv_insert(ctypes.byref(s), ok, o.get("hpl", 2), 0, 128 * 64, o.get("ksr", 128), ok, 64, 0.2,
-                                      0.03, o.get("reset_at", 0), o.get("mm", 66), o.get("capk", 0.0),
+    ins = lambda s, **o: L.skv_insert(ctypes.byref(s), ok, o.get("hpl", 2), 0, 128 * 64, o.get("ksr", 128), ok, o.get("ng", 0), 64,
+                                      0.2, 0.03, o.get("reset_at", 0), o.get("mm", 66), o.get("capk", 0.0),
                                       o.get("var_min", 8), None)
     assert ins(st, hpl=3) == -5 and ins(st, mm=1) == -5 and ins(st, mm=10 ** 6) == -5 and ins(st, ksr=120) == -4
-    assert ins(st, capk=-1.0) == -5 and ins(st, var_min=-1) == -5 and ins(st, reset_at=-1) == -5
+    assert ins(st, capk=-1.0) == -5 and ins(st, var_min=-1) == -5 and ins(st, reset_at=-1) == -5 and ins(st, ng=-1) == -5
     assert L.skv_insert_max_members() >= 400
     fit = lambda s, **o: L.skv_fit(ctypes.byref(s), ok, 0, 128 * 64, 128, o.get("n", 64), o.get("window", 8),
                                    o.get("C_init", 16), 10, ok, 0.0, 0.0, o.get("capk", 0.0), o.get("vf", 0.0),
@@ -246,7 +248,7 @@ def test_weighted_attention_rejects_bad_arguments(L):
         a = dict(q=ok, K=ok, V=ok, labels=ok, lstr=64, w=ok, C=64, n_dev=ok, out=ok, ws=ok, heads=2, G=2, d=128, dtype=0,
                  ksr=128, splits=4)
         a.update(over)
-        return L.skv_attend_weighted(a["q"], a["K"], a["V"], a["labels"], a["lstr"], a["w"], a["C"], a["n_dev"],
+        return L.skv_attend_weighted(a["q"], a["K"], a["V"], a["labels"], a["lstr"], a["w"], a["C"], a["n_dev"], 0,
                                      a["out"], a["ws"], None, a["heads"], a["G"], a["d"], a["dtype"], 128 * 64, a["ksr"],
                                      128 * 64, 128, a["splits"], 0.1, None)
 
@@ -262,7 +264,8 @@ def test_one_launch_step_rejects_bad_arguments(L):
     def call(state=st, **over):
         a = dict(q=ok, G=2, n_dev=ok, K=ok, V=ok, ksr=128, cnt=ok, out=ok, ws=ok, clusters=4)
         a.update(over)
-        return L.skv_step(ctypes.byref(state), a["q"], a["G"], a["n_dev"], a["K"], a["V"], 128 * 4096, a["ksr"],
+        return L.skv_step(ctypes.byref(state), a["q"], a["G"], a["n_dev"], a.get("ng", 0), a["K"], a["V"], 128 * 4096,
+                          a["ksr"],
                           128 * 4096, 128, None, None, a["cnt"], a["out"], a["ws"], a["clusters"], 0.1, None, None)
 
     assert call(q=None) == -1 and call(K=None) == -1 and call(ws=None) == -1

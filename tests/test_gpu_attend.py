@@ -36,7 +36,7 @@ def run_attend(q, K, V, rows, *, splits=None, force_simple=False, dense_n=None, 
     code = dtype_code(K.dtype) | (256 if force_simple else 0)
     for _ in range(2):            # twice: the ticket words must come back to zero
         check(Lb.skv_attend(qd.data_ptr(), Kd.data_ptr(), Vd.data_ptr(), None if rows is None else idx.data_ptr(),
-                            None if rows is None else cnt.data_ptr(), None if nd is None else nd.data_ptr(),
+                            None if rows is None else cnt.data_ptr(), None if nd is None else nd.data_ptr(), 0,
                             out.data_ptr(), ws.data_ptr(), status.data_ptr(), h, G, d, code, Kd.stride(0),
                             Kd.stride(1), Vd.stride(0), Vd.stride(1), idx.stride(0),
                             L if rows_limit is None else rows_limit, S, 1.0 / math.sqrt(d),
@@ -131,7 +131,7 @@ def test_strided_cache_views_are_read_in_place():
     S = 5
     ws = torch.zeros(Lb.skv_attend_workspace_bytes(h, 2, 128, S), dtype=torch.uint8, device=DEV)
     out = torch.empty(H, 128, dtype=torch.bfloat16, device=DEV)
-    check(Lb.skv_attend(q.to(DEV).data_ptr(), Kd.data_ptr(), Vd.data_ptr(), idx.data_ptr(), cnt.data_ptr(), None,
+    check(Lb.skv_attend(q.to(DEV).data_ptr(), Kd.data_ptr(), Vd.data_ptr(), idx.data_ptr(), cnt.data_ptr(), None, 0,
                         out.data_ptr(), ws.data_ptr(), None, h, 2, 128, 0, Kd.stride(0), Kd.stride(1), Vd.stride(0),
                         Vd.stride(1), 512, 500, S, 1.0 / math.sqrt(128), torch.cuda.current_stream().cuda_stream),
           "skv_attend")

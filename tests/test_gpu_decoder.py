@@ -194,7 +194,7 @@ def test_rotary_step_folded_into_the_selection_equals_the_separate_launch():
     K1, V1 = K.clone(), V.clone()
     q1 = torch.empty(B * H, d, dtype=torch.bfloat16, device=DEV)
     check(L.skv_qk_rope_cache(qkv.data_ptr(), qw.data_ptr(), kw.data_ptr(), cos.data_ptr(), sin.data_ptr(), pos.data_ptr(),
-                              q1.data_ptr(), K1.data_ptr(), V1.data_ptr(), B, H, H_kv, d, K1.stride(0), K1.stride(1),
+                              0, q1.data_ptr(), K1.data_ptr(), V1.data_ptr(), B, H, H_kv, d, K1.stride(0), K1.stride(1),
                               K1.stride(2), 1e-6, st), "skv_qk_rope_cache")
     out1 = ix.step(q1, heads(K1), heads(V1), n_dev, insert=False).clone()
     w1, cnt1 = ix.wbuf.clone(), ix.cnt.clone()
@@ -246,3 +246,48 @@ def test_growing_cap_and_spread_trigger_in_the_all_layer_insert(opts):
         lab = i.labels.cpu()
         counts = torch.stack([torch.bincount(lab[k, 1:end].long(), minlength=128) for k in range(i.H_kv)])
         assert torch.equal(i.count.cpu(), counts.float()) and i.check_status() == 0
+
+
+@pytest.mark.parametrize("mode", ["cluster", "dense"])
+def test_a_batch_of_different_lengths_equals_separate_sequences(mode):
+    """Three sequences with prompts of 300, 217 and 260 tokens decode in one batch - every head reads its own
+    sequence's length and position from device memory - and give what three separate decoders give; the graph
+    replay equals the eager step bit for bit."""
+    model = tiny_model(seed=21)
+    lengths, T = [300, 217, 260], 24
+    g = torch.Generator().manual_seed(14)
+    ids = [torch.randint(0, 1000, (n + T + 1,), generator=g).to(DEV) for n in lengths]
+    kw = dict(mode=mode, budget=0.3, C=64, C_init=16, cap_keys=24.0, window=16, delta=0.03, summary_bits=8)
+    cap = -(-(max(lengths) + T + 2) // 16) * 16
+
+    def ragged(capture):
+        cache = model.alloc_cache(cap, max_batch=3)
+        out = []
+        with torch.no_grad():
+            model.prefill_ragged([x[:n] for x, n in zip(ids, lengths)], cache, chunk=128)
+            dec = GraphDecoder(model, cache, **kw)
+            dec.prepare(lengths)
+            if capture:
+                dec.capture()
+            for t in range(T):
+                tok = torch.stack([x[n + t] for x, n in zip(ids, lengths)]).view(3, 1)
+                out.append(dec.step(tok, [n + t for n in lengths])[:, -1].float().clone())
+        return torch.stack(out, 1), dec
+
+    both, dec = ragged(True)
+    eager, _ = ragged(False)
+    assert torch.equal(both, eager)
+    assert dec.cache.cur_len == [n + T for n in lengths]
+    for b, n in enumerate(lengths):
+        one, _ = run_decoder(model, ids[b].view(1, -1), n, T, True, **kw)
+        torch.testing.assert_close(both[b:b + 1], one, rtol=2e-2, atol=2e-2)
+    if mode == "cluster":
+        for a in dec.attn:
+            ends = a.end_dev.cpu().tolist()
+            assert ends == [n + T - 16 for n in lengths for _ in range(2)]
+            lab = a.labels.cpu()
+            for k, e in enumerate(ends):
+                counts = torch.bincount(lab[k, 1:e].long(), minlength=64)
+                assert torch.equal(a.count[k].cpu(), counts.float())
+                assert torch.all(lab[k, e:] == 64)
+            assert a.check_status() in (0, 1)

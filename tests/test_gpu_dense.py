@@ -52,7 +52,7 @@ def test_qk_norm_rope_and_cache_write():
     vc = torch.zeros_like(kc)
     q_out = torch.empty(B * H, d, dtype=torch.bfloat16, device=DEV)
     check(lib().skv_qk_rope_cache(qkv.data_ptr(), qn.weight.data_ptr(), kn.weight.data_ptr(), cos.data_ptr(),
-                                  sin.data_ptr(), pos.data_ptr(), q_out.data_ptr(), kc.data_ptr(), vc.data_ptr(), B, H,
+                                  sin.data_ptr(), pos.data_ptr(), 0, q_out.data_ptr(), kc.data_ptr(), vc.data_ptr(), B, H,
                                   H_kv, d, kc.stride(0), kc.stride(1), kc.stride(2), 1e-6, stream()), "skv_qk_rope_cache")
     q = qn(qkv[:, :H * d].view(B, 1, H, d)).transpose(1, 2)
     k = kn(qkv[:, H * d:(H + H_kv) * d].view(B, 1, H_kv, d)).transpose(1, 2)

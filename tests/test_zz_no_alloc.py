@@ -42,10 +42,10 @@ def both_ways(h, G, n, frac, splits, seed):
               stream)
     ws = torch.zeros(L.skv_attend_workspace_bytes(h, G, 128, splits), dtype=torch.uint8, device=dev)
     want = torch.empty(h * G, 128, dtype=torch.bfloat16, device=dev)
-    check(L.skv_attend(qd.data_ptr(), Kd.data_ptr(), Vd.data_ptr(), idx.data_ptr(), cnt.data_ptr(), None,
+    check(L.skv_attend(qd.data_ptr(), Kd.data_ptr(), Vd.data_ptr(), idx.data_ptr(), cnt.data_ptr(), None, 0,
                        want.data_ptr(), ws.data_ptr(), None, *common), "skv_attend")
     got = torch.full_like(want, float("nan"))
-    check(L.skv_attend_static(qd.data_ptr(), Kd.data_ptr(), Vd.data_ptr(), idx.data_ptr(), cnt.data_ptr(), None,
+    check(L.skv_attend_static(qd.data_ptr(), Kd.data_ptr(), Vd.data_ptr(), idx.data_ptr(), cnt.data_ptr(), None, 0,
                               got.data_ptr(), None, *common), "skv_attend_static")
     torch.cuda.synchronize()
     ref = oc.attend_rows(q, K, V, rows)
