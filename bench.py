@@ -35,7 +35,16 @@ WORKLOADS = {
     "qwen3-4b_b1_32k_budget20": ("4b", 1, 32768, 0.20, 2048),
     "qwen3-4b_b4_8k_budget10": ("4b", 4, 8192, 0.10, 1024),
     "qwen3-0.6b_b1_4k_budget20": ("0.6b", 1, 4096, 0.20, 1024),          # quick check
+    # the scaling configuration: the batch is fixed (strong scaling over the KV heads); on one GPU the cache of 32
+    # sequences does not fit (155 GB of keys and values + 27 GB of cluster state + weights), so N = 1 runs 16
+    "qwen3-4b_b32_32k_budget20": ("4b", 32, 32768, 0.20, 2048),
+    "qwen3-4b_b32_32k_budget5": ("4b", 32, 32768, 0.05, 2048),
+    # long generation: an 8,192-token prompt continued to 32,768 tokens, clusters growing with the context
+    "qwen3-4b_b1_8k_to_32k_budget20": ("4b", 1, 8192, 0.20, 2048),
+    "qwen3-0.6b_b1_8k_to_32k_budget20": ("0.6b", 1, 8192, 0.20, 2048),
 }
+FIXED_BATCH = {"qwen3-4b_b32_32k_budget20": {1: 16}, "qwen3-4b_b32_32k_budget5": {1: 16}}   # batch at N GPUs, else as named
+LONG_GENERATION = {"qwen3-4b_b1_8k_to_32k_budget20": 32768, "qwen3-0.6b_b1_8k_to_32k_budget20": 32768}
 DEFAULT = "qwen3-0.6b_b1_32k_budget20"
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the workload's dominant kernel, from an ncu capture
 # of that workload (a constant copied from the capture's summary; workloads without a capture report null)
@@ -142,7 +151,10 @@ def reference_arm(args, wl) -> None:
     if rank != 0:
         return
     model, B, n, budget, slots = wl
-    B *= max(1, args.gpus)                               # the GPU arm serves one more sequence per GPU
+    if args.workload in FIXED_BATCH:
+        B = FIXED_BATCH[args.workload].get(max(1, args.gpus), B)
+    else:
+        B *= max(1, args.gpus)                           # the GPU arm serves one more sequence per GPU
     layers = 28 if model == "0.6b" else 36
     G = 2 if model == "0.6b" else 4
     steps, warmup = max(1, min(args.steps, 8)), max(1, min(args.warmup, 2))
@@ -154,7 +166,7 @@ def reference_arm(args, wl) -> None:
     line = {"impl": "reference", "metric": "qwen3_decode_tokens_per_s", "value": value, "unit": "tok/s",
             "n_gpus": args.gpus, "steps": steps, "warmup": warmup, "ms_per_step": ms, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": args.workload, "batch": B, "prompt": n, "budget": budget},
+            "config": {"workload": workload_name(args.workload, B), "batch": B, "prompt": n, "budget": budget},
             "cpu_baseline": {"value": value, "unit": "tok/s", "cores": cores, "kind": "port", "sample": sample},
             "e2e": {"value": value, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line), flush=True)
@@ -163,7 +175,7 @@ def reference_arm(args, wl) -> None:
 # ---------------------------------------------------------------------------------------------
 # GPU arm
 # ---------------------------------------------------------------------------------------------
-def build_decoder(wl, dev, tp_group, tp_size, tp_rank, decode_steps):
+def build_decoder(wl, dev, tp_group, tp_size, tp_rank, decode_steps, synthetic_cache=False):
     from sparse_kv_reads_b200 import GraphDecoder, Qwen3Config, Qwen3Model
     model_name, B, n, budget, slots = wl
     cfg = Qwen3Config.qwen3_0_6b() if model_name == "0.6b" else Qwen3Config.qwen3_4b()
@@ -174,8 +186,19 @@ def build_decoder(wl, dev, tp_group, tp_size, tp_rank, decode_steps):
     cap = -(-(n + decode_steps + 8) // 16) * 16
     cache = model.alloc_cache(cap, max_batch=B)
     ids = torch.randint(0, cfg.vocab_size, (B, n + decode_steps + 1), generator=torch.Generator().manual_seed(1))
-    with torch.no_grad():
-        model.prefill(ids[:, :n].to(dev), cache, chunk=2048)
+    if synthetic_cache:
+        # the prompt's keys and values are drawn directly (clustered keys of the CPU-runnable configuration, a new
+        # draw per layer) instead of being computed by a prefill: the decode step costs the same, the set-up far less
+        from sparse_kv_reads_b200.kernel_bench import synthetic_cache as draw
+        for i in range(len(cache.k)):
+            K, V = draw(B * cache.k[i].shape[1], cap, seed=1000 * tp_rank + i, device=dev)
+            cache.k[i].copy_(K.view_as(cache.k[i]))
+            cache.v[i].copy_(V.view_as(cache.v[i]))
+            del K, V
+        cache.cur_len = n
+    else:
+        with torch.no_grad():
+            model.prefill(ids[:, :n].to(dev), cache, chunk=2048)
     dec = GraphDecoder(model, cache, mode="cluster", budget=budget, C=slots, C_init=256, cap_keys=64.0, window=64,
                        summary_bits=8)
     t0 = time.perf_counter()
@@ -292,6 +315,12 @@ def exact_leg(model, cache, ids_dev, pos, steps, warmup):
     return ids_dev.shape[0] / (ms * 1e-3), ms, pos
 
 
+def workload_name(name: str, batch: int) -> str:
+    """The workload's name with the batch actually run (the scaling runs change it with the GPU count)."""
+    import re
+    return re.sub(r"_b\d+_", f"_b{batch}_", name, count=1)
+
+
 def own_launches(dec) -> int:
     """Launches of this library's kernels in one decode step: the all-layer insert, then per layer the
     selection and the attention, and with the bundled model's fused layers also QK-norm/rotary/cache write and
@@ -306,6 +335,66 @@ def own_launches(dec) -> int:
         per_layer += 1 + (4 if dec.own_gemv and dec.B <= 8 else 3)
         extra += 1
     return extra + per_layer * len(dec.attn)
+
+
+def long_generation(args, wl) -> None:
+    """An 8,192-token prompt continued to 32,768 tokens (one GPU): every step inserts a key, clusters split at the
+    cap and the state recentres between replays, so the cluster count grows with the context.  Counterpart of the
+    reference's long generation (docs/results.md:67-69: ms per step and clusters at the end).  Prints one JSON line:
+    whole-run throughput, and per window of 2,048 steps the ms per step and the clusters per head."""
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the kernels have no CPU fallback")
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    model_name, B, n, budget, slots = wl
+    target = LONG_GENERATION[args.workload]
+    steps = target - n
+    model, cache, dec, ids, fit_s = build_decoder(wl, dev, None, 1, 0, steps + 8)
+    ids_dev = ids.to(dev)
+    clocks = ClockSampler(0)
+    windows, pos = [], n
+    start_clusters = float(torch.stack([a.n_c.float().mean() for a in dec.attn]).mean())
+    t_all0 = torch.cuda.Event(enable_timing=True)
+    with clocks:
+        for _ in range(8):                                # warm-up steps (they advance the context too)
+            dec.step(ids_dev[:, pos:pos + 1], pos)
+            pos += 1
+        torch.cuda.synchronize()
+        t_all0.record()
+        while pos < target:
+            w = min(2048, target - pos)
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(w):
+                dec.step(ids_dev[:, pos:pos + 1], pos)
+                pos += 1
+            b.record()
+            torch.cuda.synchronize()
+            windows.append({"context": pos, "ms_per_step": a.elapsed_time(b) / w,
+                            "clusters_per_head": float(torch.stack([x.n_c.float().mean() for x in dec.attn]).mean())})
+        t_all1 = torch.cuda.Event(enable_timing=True)
+        t_all1.record()
+        torch.cuda.synchronize()
+    total_ms = t_all0.elapsed_time(t_all1)
+    done = target - n - 8
+    status = 0
+    for ix in dec.attn:
+        status |= ix.check_status()
+    line = {"metric": "qwen3_decode_tokens_per_s", "value": B * done / (total_ms * 1e-3), "unit": "tok/s", "n_gpus": 1,
+            "steps": done, "warmup": 8, "ms_per_step": total_ms / done, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": args.workload, "model": f"qwen3-{model_name} architecture, random weights", "batch": B,
+                       "prompt": n, "generated_to": target, "budget": budget, "slots": slots, "clusters_fitted": 256,
+                       "cap_keys": 64, "window": 64, "summary_bits": 8,
+                       "timing": "device time of the whole generation, host recentring between replays included"},
+            "gpu_launches": done * own_launches(dec), "clocks": clocks.summary(),
+            "long_generation": {"windows": windows, "clusters_per_head_start": start_clusters,
+                                "clusters_per_head_end": windows[-1]["clusters_per_head"],
+                                "splits": sum(ix.splits for ix in dec.attn),
+                                "recentrings": sum(ix.rebuilds for ix in dec.attn),
+                                "largest_cluster": float(max(float(ix.count.max()) for ix in dec.attn))},
+            "prompt_fit_s": fit_s, "device_status": status}
+    print(json.dumps(line), flush=True)
 
 
 def gpu_arm(args, wl) -> None:
@@ -324,11 +413,15 @@ def gpu_arm(args, wl) -> None:
     model_name, B, n, budget, slots = wl
     # Weak scaling over the path's independent units, the (sequence, KV head) pairs: every GPU added brings one
     # more sequence while it takes over its share of the 8 KV heads, so a GPU always serves 8 pairs per layer.
-    B = B * world
+    fixed = args.workload in FIXED_BATCH
+    if fixed:
+        B = FIXED_BATCH[args.workload].get(world, B)     # strong scaling: the batch the workload names, split by KV head
+    else:
+        B = B * world
     wl = (model_name, B, n, budget, slots)
     K_steps, W = args.steps, args.warmup
     total = 3 * (K_steps + W) + 4                        # device leg, end-to-end leg, exact-attention leg
-    model, cache, dec, ids, fit_s = build_decoder(wl, dev, group, world, rank, total)
+    model, cache, dec, ids, fit_s = build_decoder(wl, dev, group, world, rank, total, args.synthetic_cache)
     ids_dev = ids.to(dev)
     pinned = ids.pin_memory()
     result_host = torch.zeros(B, dtype=torch.long).pin_memory()
@@ -394,13 +487,16 @@ def gpu_arm(args, wl) -> None:
         roof, layer = kernel_roofline(dec, pos, peak, which, NCU_TRAFFIC.get(args.workload) if world == 1 else None)
         line = {"metric": "qwen3_decode_tokens_per_s", "value": B * K_steps / (dev_ms * 1e-3), "unit": "tok/s",
                 "n_gpus": world, "steps": K_steps, "warmup": W, "ms_per_step": dev_ms / K_steps,
-                "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
-                "data": "synthetic",
-                "config": {"workload": args.workload, "model": f"qwen3-{model_name} architecture, random weights",
+                "higher_is_better": True, "scaling": "strong" if fixed else "weak", "vs_baseline": None, "dtype": "bf16",
+                "data": "synthetic" + (" (keys and values of the prompt drawn directly, no prefill)" if args.synthetic_cache
+                                       else ""),
+                "config": {"workload": workload_name(args.workload, B), "model": f"qwen3-{model_name} architecture, random weights",
                            "batch": B, "prompt": n, "budget": budget, "slots": slots, "clusters_fitted": 256,
                            "cap_keys": 64, "window": 64, "summary_bits": 8,
-                           "parallelism": (f"tp{world}: KV heads sharded, batch x{world} (8 sequence-head pairs per "
-                                           f"GPU), sums through peer memory") if world > 1 else "single GPU",
+                           "parallelism": (f"tp{world}: KV heads sharded, batch {B} ({B * 8 // world} sequence-head pairs "
+                                           f"per GPU), sums through " +
+                                           ("peer memory" if B <= 8 else "NCCL all-reduces")) if world > 1
+                           else "single GPU",
                            "l2": "per-layer caches total far more than L2; the kernel leg also flushes 512 MB"},
                 "e2e": {"value": B * K_steps / (e2e_ms * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": 8 * B,
                         "d2h_bytes_per_step": 8 * B, "ms_per_step": e2e_ms / K_steps},
@@ -441,6 +537,8 @@ def main() -> None:
     ap.add_argument("--workload", default=DEFAULT, choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--synthetic-cache", action="store_true",
+                    help="draw the prompt's keys and values directly instead of running a prefill (large workloads)")
     ap.add_argument("--no-extra", action="store_true", help="skip the exact-attention and batch-32 legs (profiling runs)")
     ap.add_argument("--ncu-range", action="store_true",
                     help="bracket the timed device leg with cudaProfilerStart/Stop (for ncu --profile-from-start off)")
@@ -448,6 +546,8 @@ def main() -> None:
     wl = WORKLOADS[args.workload]
     if args.impl == "reference":
         reference_arm(args, wl)
+    elif args.workload in LONG_GENERATION:
+        long_generation(args, wl)
     else:
         gpu_arm(args, wl)
 
