@@ -521,11 +521,25 @@ def gpu_arm(args, wl) -> None:
                                               f"excluded; CPU fit {cfit:.2f}s"}
         print(json.dumps(line), flush=True)
     if world > 1:
-        # The captured decode graph holds NCCL collectives; tearing the communicator down under it can block for
-        # good.  Every rank is done once the barrier returns, so leave without the teardown.
         dist.barrier()
         torch.cuda.synchronize()
         sys.stdout.flush()
+        if os.environ.get("SKV_BENCH_TEARDOWN") == "1":
+            # orderly teardown: the captured graph (it holds NCCL kernels) goes first, then the exchange buffers,
+            # then the communicator
+            import gc
+            peer = getattr(dec, "_peer", None)
+            dec.graph = None
+            del dec
+            gc.collect()
+            torch.cuda.synchronize()
+            if peer is not None:
+                dist.barrier()
+                peer.close()
+            dist.destroy_process_group()
+            return
+        # The captured decode graph holds NCCL collectives; tearing the communicator down while the graph object
+        # is alive can block.  Every rank is done once the barrier has returned, so leave without the teardown.
         os._exit(0)
 
 

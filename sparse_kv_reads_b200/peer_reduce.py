@@ -85,7 +85,15 @@ class PeerExchange:
             check(rc, "skv_comm_status")
         return rc
 
+    def __del__(self):
+        try:                                               # unmap and free if the owner forgot to
+            self.close()
+        except Exception:
+            pass
+
     def close(self) -> None:
+        """Unmap the other ranks' buffers and free this rank's (idempotent).  Call it once no kernel that uses the
+        exchange is in flight on any rank."""
         L = lib()
         for p in self._opened:
             L.skv_comm_close(p)
