@@ -129,10 +129,13 @@ __global__ void __launch_bounds__(128) seed_kernel(const FitView v, const int32_
 }
 
 // ---- nearest centroid of every clustered key: float32 GEMM tile with a fused arg-max ---------------
-// CTA = 64 keys x all n_c centroids in chunks of 64; 256 threads, each 4 keys x 4 centroids.
-// Both tiles sit in shared memory k-contiguous (row stride 132 floats); a thread's centroids are
-// tx, tx+16, tx+32, tx+48 so that a quarter-warp's 128-bit loads cover all banks.
-constexpr int AS_ROWS = 64, AS_COLS = 64, AS_LD = 132;
+// CTA = 128 keys x all n_c centroids in chunks of 64; 256 threads, each 8 keys x 4 centroids: per four steps of k
+// a thread issues 12 128-bit shared loads for 128 FFMA, which keeps the shared-memory pipe (the limit of the
+// 4 x 4 tiling this replaces: 8 loads per 64 FFMA) behind the FMA pipe.  Both tiles sit in shared memory
+// k-contiguous (row stride 132 floats); a thread's centroids are tx, tx+16, tx+32, tx+48 so that a quarter-warp's
+// 128-bit loads cover all banks; its keys are rows 8 ty .. 8 ty + 7 (a warp reads two rows at a time: broadcasts).
+// Every dot product is a sequential-k chain of float32 FMAs, as before: the arithmetic is unchanged.
+constexpr int AS_ROWS = 128, AS_COLS = 64, AS_LD = 132, AS_RPT = 8;
 constexpr int AS_SMEM = (AS_ROWS + AS_COLS) * AS_LD * 4;
 
 struct Arg {
@@ -143,7 +146,7 @@ __device__ __forceinline__ void arg_take(Arg &a, float v, int i) {
     if (v > a.v || (v == a.v && i < a.i)) { a.v = v; a.i = i; }
 }
 
-__global__ void __launch_bounds__(256) assign_kernel(const FitView v) {
+__global__ void __launch_bounds__(256, 2) assign_kernel(const FitView v) {
     extern __shared__ __align__(16) float smem_f[];
     float *Xs = smem_f, *Cs = smem_f + AS_ROWS * AS_LD;
     const int e = blockIdx.y, tile = blockIdx.x, tid = threadIdx.x;
@@ -159,9 +162,9 @@ __global__ void __launch_bounds__(256) assign_kernel(const FitView v) {
         if (r < rows) x = *reinterpret_cast<const float4 *>(X + (int64_t)r * HEAD_DIM + k4 * 4);
         *reinterpret_cast<float4 *>(Xs + r * AS_LD + k4 * 4) = x;
     }
-    Arg best[4];
+    Arg best[AS_RPT];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) best[i] = Arg{-INFINITY, 0x7fffffff};
+    for (int i = 0; i < AS_RPT; ++i) best[i] = Arg{-INFINITY, 0x7fffffff};
     const float *cent = v.st.cent + (int64_t)h * v.st.C * HEAD_DIM;
     for (int c0 = 0; c0 < n_c; c0 += AS_COLS) {
         __syncthreads();
@@ -172,20 +175,20 @@ __global__ void __launch_bounds__(256) assign_kernel(const FitView v) {
             *reinterpret_cast<float4 *>(Cs + c * AS_LD + k4 * 4) = x;
         }
         __syncthreads();
-        float acc[4][4];
+        float acc[AS_RPT][4];
 #pragma unroll
-        for (int i = 0; i < 4; ++i)
+        for (int i = 0; i < AS_RPT; ++i)
 #pragma unroll
             for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
-#pragma unroll 4
+#pragma unroll 2
         for (int k = 0; k < HEAD_DIM; k += 4) {
-            float4 xr[4], cr[4];
+            float4 xr[AS_RPT], cr[4];
 #pragma unroll
-            for (int i = 0; i < 4; ++i) xr[i] = *reinterpret_cast<const float4 *>(Xs + (ty * 4 + i) * AS_LD + k);
+            for (int i = 0; i < AS_RPT; ++i) xr[i] = *reinterpret_cast<const float4 *>(Xs + (ty * AS_RPT + i) * AS_LD + k);
 #pragma unroll
             for (int j = 0; j < 4; ++j) cr[j] = *reinterpret_cast<const float4 *>(Cs + (tx + 16 * j) * AS_LD + k);
 #pragma unroll
-            for (int i = 0; i < 4; ++i)
+            for (int i = 0; i < AS_RPT; ++i)
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     acc[i][j] = fmaf(xr[i].x, cr[j].x, acc[i][j]);
@@ -199,12 +202,12 @@ __global__ void __launch_bounds__(256) assign_kernel(const FitView v) {
             const int c = c0 + tx + 16 * j;
             if (c < n_c)
 #pragma unroll
-                for (int i = 0; i < 4; ++i) arg_take(best[i], acc[i][j], c);
+                for (int i = 0; i < AS_RPT; ++i) arg_take(best[i], acc[i][j], c);
         }
     }
     int16_t *lab = v.st.labels + (int64_t)h * v.st.capacity + 1;
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
+    for (int i = 0; i < AS_RPT; ++i) {
         Arg b = best[i];
 #pragma unroll
         for (int o = 8; o > 0; o >>= 1) {
@@ -212,7 +215,7 @@ __global__ void __launch_bounds__(256) assign_kernel(const FitView v) {
             const int oi = __shfl_xor_sync(0xffffffffu, b.i, o);
             arg_take(b, ov, oi);
         }
-        const int r = ty * 4 + i;
+        const int r = ty * AS_RPT + i;
         if (tx == 0 && r < rows) lab[r0 + r] = (int16_t)(b.i == 0x7fffffff ? 0 : b.i);
     }
 }
