@@ -524,23 +524,24 @@ def gpu_arm(args, wl) -> None:
         dist.barrier()
         torch.cuda.synchronize()
         sys.stdout.flush()
-        if os.environ.get("SKV_BENCH_TEARDOWN") == "1":
-            # orderly teardown: the captured graph (it holds NCCL kernels) goes first, then the exchange buffers,
-            # then the communicator
-            import gc
-            peer = getattr(dec, "_peer", None)
-            dec.graph = None
-            del dec
-            gc.collect()
-            torch.cuda.synchronize()
-            if peer is not None:
-                dist.barrier()
-                peer.close()
-            dist.destroy_process_group()
-            return
-        # The captured decode graph holds NCCL collectives; tearing the communicator down while the graph object
-        # is alive can block.  Every rank is done once the barrier has returned, so leave without the teardown.
-        os._exit(0)
+        # Orderly teardown: the captured graph (it holds NCCL kernels) goes first, then the exchange buffers, then
+        # the communicator.  Destroying the communicator while the graph object is alive blocked in earlier builds;
+        # in this order it returns (2 GPUs, measured).  A watchdog leaves the process after 20 s regardless, so a
+        # teardown that blocks on some other pool cannot hold a finished measurement hostage.
+        import gc
+        watchdog = threading.Timer(20.0, lambda: os._exit(0))
+        watchdog.daemon = True
+        watchdog.start()
+        peer = getattr(dec, "_peer", None)
+        dec.graph = None
+        del dec
+        gc.collect()
+        torch.cuda.synchronize()
+        if peer is not None:
+            dist.barrier()
+            peer.close()
+        dist.destroy_process_group()
+        watchdog.cancel()
 
 
 def main() -> None:
