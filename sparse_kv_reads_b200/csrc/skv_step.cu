@@ -253,7 +253,6 @@ __global__ void __launch_bounds__(STEP_THREADS, 2) step_kernel(const StepParams 
         }
         cp_async_commit();
     }
-    for (int i = tid; i < 512; i += STEP_THREADS) hist[i] = 0;                // the pick's first pass finds it cleared
     pdl_wait();                                            // the query comes from the launch ahead
     pdl_trigger();
     step_stamp(p, 1);
@@ -389,48 +388,58 @@ __global__ void __launch_bounds__(STEP_THREADS, 2) step_kernel(const StepParams 
         }
         uint32_t *key = reinterpret_cast<uint32_t *>(smem);                   // [C], over sumst once it is scored
         uint8_t *sel = reinterpret_cast<uint8_t *>(key + C);                  // [C + 1]
-        for (int c = tid; c < C; c += STEP_THREADS) sel[c] = 0;
-        if (tid == 0) sel[C] = 1;
+        // only the slots in use are looked at below (the pick marks every one of them), so nothing is cleared here
+        // except when nothing is selected at all
+        if (!active)
+            for (int c = tid; c < n_c; c += STEP_THREADS) sel[c] = 0;
         __syncthreads();
         step_stamp(p, 8);
         uint32_t kmin = 0xffffffffu, kmax = 0u;
         int nvalid = 0;
         if (active) {
-            // cluster c of CTA r's stretch [r * per, (r + 1) * per) was scored by warp ((c - r * per) / 8) % 4
-            for (int r = 0; r < STEP_CS; ++r)
-                for (int i = tid; i < per; i += STEP_THREADS) {
-                    const int c = r * per + i;
-                    if (c >= n_c) break;
-                    const float *f = fac + (r * STEP_WARPS + ((i >> 3) & (STEP_WARPS - 1))) * GP;
-                    float sc = -INFINITY;
-                    const bool live = cntf[c] > 0.f;
-                    if (live) {
-                        sc = 0.f;
+            // cluster c lies in CTA r's stretch [r * per, (r + 1) * per), r = c / per (by a multiplication: exact for
+            // c < 2^16), and was scored by warp ((c - r * per) / 8) % 4 of that CTA
+            const unsigned inv_per = (unsigned)((0x100000000ull + per - 1) / per);
+            for (int c = tid; c < n_c; c += STEP_THREADS) {
+                const int r = (int)__umulhi((unsigned)c, inv_per);
+                const float *f = fac + (r * STEP_WARPS + (((c - r * per) >> 3) & (STEP_WARPS - 1))) * GP;
+                float sc = -INFINITY;
+                const bool live = cntf[c] > 0.f;
+                if (live) {
+                    sc = 0.f;
 #pragma unroll
-                        for (int g = 0; g < GP; ++g)
-                            if (g < G) sc = fmaf(zall[g * C + c], f[g], sc);
-                    }
-                    const uint32_t k = float_key(sc);
-                    key[c] = k;
-                    if (live) { kmin = min(kmin, k); kmax = max(kmax, k); ++nvalid; }
+                    for (int g = 0; g < GP; ++g)
+                        if (g < G) sc = fmaf(zall[g * C + c], f[g], sc);
                 }
+                const uint32_t k = float_key(sc);
+                key[c] = k;
+                if (live) { kmin = min(kmin, k); kmax = max(kmax, k); ++nvalid; }
+            }
         }
         step_stamp(p, 10);
         pick_by_threshold<STEP_THREADS, float>(key, cntf, sel, hist, ired, n_c, need, active, kmin, kmax, nvalid);
         __syncthreads();
         step_stamp(p, 11);
-        const int words = C / 32 + 1;
+        // selection bits: the words that hold slots in use, the rest zero, bit C (the always-read rows) set
+        const int words = C / 32 + 1, used = (n_c + 31) >> 5;
         const bool publish = split == 0;
         for (int wd = warp; wd < words; wd += STEP_WARPS) {
-            const int c = wd * 32 + lane;
-            const unsigned v = __ballot_sync(0xffffffffu, c <= C && sel[c]);
+            unsigned v = 0u;
+            if (wd < used) {                                                  // warp-uniform
+                const int c = wd * 32 + lane;
+                v = __ballot_sync(0xffffffffu, c < n_c && sel[c]);
+            }
+            if (wd == words - 1) v |= 1u;                                     // C is a multiple of 32: bit 0 of the last word
             if (lane == 0) {
                 s_bits[wd] = v;
                 if (publish && p.selbits) p.selbits[(int64_t)h * words + wd] = v;
             }
         }
-        if (publish && p.w)
-            for (int c = tid; c <= C; c += STEP_THREADS) p.w[(int64_t)h * (C + 1) + c] = sel[c] ? 1.f : 0.f;
+        if (publish && p.w) {
+            __syncthreads();
+            for (int c = tid; c <= C; c += STEP_THREADS)
+                p.w[(int64_t)h * (C + 1) + c] = (float)((s_bits[c >> 5] >> (c & 31)) & 1u);
+        }
     }
     __syncthreads();                                       // the selection's scratch is free: the rings take its place
     step_stamp(p, 4);
