@@ -285,6 +285,13 @@ int skv_insert(const skv_state *st, const void *const *k_layers, int heads_per_l
                double budget, float delta, int reset_at, int max_members, float capk, int var_min, void *stream);
 int skv_insert_max_members(void);
 
+/* The nearest-centroid passes of skv_fit / skv_rebin are float32 FMA chains on the CUDA cores (42 TFLOP/s on B200).
+ * skv_fit_tensor_cores(1) runs them on the tensor cores instead: three TF32 products of a two-term split with
+ * float32 accumulation, and every key whose two best centroids are closer than that value can tell apart is
+ * recomputed with the float32 chain, so the labels are the same bit for bit (tests compare the two).  Measured equal
+ * in speed (0.188 s against 0.184 s for a 32k prompt x 28 layers), hence off by default; process-wide switch. */
+void skv_fit_tensor_cores(int on);
+
 /* Workspace bytes of skv_fit / skv_rebin for `heads` heads of `m` clustered keys. */
 int64_t skv_fit_workspace_bytes(int heads, int m, int C, int d);
 

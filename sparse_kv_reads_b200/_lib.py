@@ -19,7 +19,7 @@ ST_NO_SLOT, ST_SPLIT_TOO_BIG, ST_BAD_INDEX, ST_WAIT_TIMEOUT = 1, 2, 4, 8
 
 EXPORTS = ("skv_version", "skv_error_string", "skv_last_cuda_error", "skv_attend_splits",
            "skv_attend_workspace_bytes", "skv_attend", "skv_attend_static", "skv_attend_weighted", "skv_attend_labels", "skv_step", "skv_step_clusters", "skv_step_workspace_bytes", "skv_debug_step_probe", "skv_merge", "skv_select_workspace_bytes", "skv_select", "skv_debug_select_probe", "skv_debug_attend_probe", "skv_set_overlap", "skv_insert",
-           "skv_insert_max_members", "skv_fit_workspace_bytes", "skv_fit", "skv_rebin",
+           "skv_insert_max_members", "skv_fit_tensor_cores", "skv_fit_workspace_bytes", "skv_fit", "skv_rebin",
            "skv_add_rmsnorm", "skv_qk_rope_cache", "skv_silu_mul", "skv_gemv", "skv_gemv_attended", "skv_gemv_supported", "skv_gemv_tp", "skv_comm_bytes", "skv_comm_alloc",
            "skv_comm_export", "skv_comm_open", "skv_comm_close", "skv_comm_free", "skv_comm_view", "skv_comm_tick", "skv_comm_reduce", "skv_comm_status")
 
@@ -104,6 +104,8 @@ def _declare(lib) -> None:
     lib.skv_insert.restype = i32
     lib.skv_insert.argtypes = [C.POINTER(SkvState), vp, i32, i32, i64, i64, vp, i32, i32, f64, f32, i32, i32, f32, i32, vp]
     lib.skv_insert_max_members.restype = i32
+    lib.skv_fit_tensor_cores.restype = None
+    lib.skv_fit_tensor_cores.argtypes = [i32]
     lib.skv_fit_workspace_bytes.restype = i64
     lib.skv_fit_workspace_bytes.argtypes = [i32, i32, i32, i32]
     lib.skv_fit.restype = i32

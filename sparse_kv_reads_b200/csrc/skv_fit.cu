@@ -220,6 +220,156 @@ __global__ void __launch_bounds__(256, 2) assign_kernel(const FitView v) {
     }
 }
 
+// ---- the same assignment on the tensor cores ---------------------------------------------------------------
+// x . c as three TF32 products of a two-term split (x = xh + xl, c = ch + cl with xh = tf32(x), xl = tf32(x - xh)):
+// xl ch + xh cl + xh ch, accumulated in float32 by mma.sync m16n8k8.  For unit vectors the split loses at most
+// 3 x 2^-22 and the accumulation a few 2^-23 per step - small, but not below the 1e-7 at which Lloyd steps start
+// to diverge, so the tensor-core value only DECIDES rows whose two best centroids
+// are further apart than ASSIGN_MARGIN (twice a generous bound on |tensor-core value - FFMA chain value|); the few
+// rows inside the margin (about one in 10^4) are recomputed by their warp with the sequential float32 chain of
+// assign_kernel, centroid by centroid, first maximum wins.  The labels are therefore those of assign_kernel, bit
+// for bit (tests compare the two).  CTA = 128 keys x chunks of 64 centroids, warp w owns rows 16 w .. 16 w + 15.
+constexpr float ASSIGN_MARGIN = 4.0e-5f;
+
+__device__ __forceinline__ uint32_t to_tf32(float x) {
+    uint32_t r;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+    return r;
+}
+__device__ __forceinline__ void mma_tf32_1688(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// best and second-best value of a row (with the best's index; equal values: the lower index is "better")
+struct Top2 {
+    float v1, v2;
+    int i1;
+};
+__device__ __forceinline__ void top2_take(Top2 &t, float v, int i) {
+    if (v > t.v1 || (v == t.v1 && i < t.i1)) { t.v2 = t.v1; t.v1 = v; t.i1 = i; }
+    else if (v > t.v2) t.v2 = v;
+}
+__device__ __forceinline__ void top2_merge(Top2 &t, float v1, float v2, int i1) {
+    top2_take(t, v1, i1);
+    if (v2 > t.v2) t.v2 = v2;
+}
+
+__global__ void __launch_bounds__(256, 2) assign_tc_kernel(const FitView v) {
+    extern __shared__ __align__(16) float smem_f[];
+    float *Xs = smem_f, *Cs = smem_f + AS_ROWS * AS_LD;
+    const int e = blockIdx.y, tile = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int h = head_of(v, e);
+    const int g = lane >> 2, t = lane & 3;
+    const int n_c = min(max(v.st.n_c[h], 0), v.st.C);
+    const int r0 = tile * AS_ROWS;
+    const float *X = v.Xn + ((int64_t)e * v.m + r0) * HEAD_DIM;
+    const int rows = min(AS_ROWS, v.m - r0);
+    for (int i = tid; i < AS_ROWS * 32; i += 256) {
+        const int r = i >> 5, k4 = i & 31;
+        float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (r < rows) x = *reinterpret_cast<const float4 *>(X + (int64_t)r * HEAD_DIM + k4 * 4);
+        *reinterpret_cast<float4 *>(Xs + r * AS_LD + k4 * 4) = x;
+    }
+    Top2 best[2] = {{-INFINITY, -INFINITY, 0x7fffffff}, {-INFINITY, -INFINITY, 0x7fffffff}};   // rows 16 w + g, + 8
+    const float *cent = v.st.cent + (int64_t)h * v.st.C * HEAD_DIM;
+    const float *xa = Xs + (warp * 16 + g) * AS_LD + t, *xb = xa + 8 * AS_LD;
+    for (int c0 = 0; c0 < n_c; c0 += AS_COLS) {
+        __syncthreads();
+        for (int i = tid; i < AS_COLS * 32; i += 256) {
+            const int c = i >> 5, k4 = i & 31;
+            float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (c0 + c < n_c) x = *reinterpret_cast<const float4 *>(cent + (int64_t)(c0 + c) * HEAD_DIM + k4 * 4);
+            *reinterpret_cast<float4 *>(Cs + c * AS_LD + k4 * 4) = x;
+        }
+        __syncthreads();
+        float acc[8][4];
+#pragma unroll
+        for (int nt = 0; nt < 8; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
+#pragma unroll 2
+        for (int k0 = 0; k0 < HEAD_DIM; k0 += 8) {
+            const float af[4] = {xa[k0], xb[k0], xa[k0 + 4], xb[k0 + 4]};
+            uint32_t ah[4], al[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                ah[i] = to_tf32(af[i]);
+                al[i] = to_tf32(af[i] - __uint_as_float(ah[i]));
+            }
+#pragma unroll
+            for (int nt = 0; nt < 8; ++nt) {
+                const float *cb = Cs + (nt * 8 + g) * AS_LD + k0 + t;
+                const float b0 = cb[0], b1 = cb[4];
+                const uint32_t bh0 = to_tf32(b0), bh1 = to_tf32(b1);
+                const uint32_t bl0 = to_tf32(b0 - __uint_as_float(bh0)), bl1 = to_tf32(b1 - __uint_as_float(bh1));
+                mma_tf32_1688(acc[nt], al, bh0, bh1);                        // the small terms first
+                mma_tf32_1688(acc[nt], ah, bl0, bl1);
+                mma_tf32_1688(acc[nt], ah, bh0, bh1);
+            }
+        }
+#pragma unroll
+        for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                const int c = c0 + nt * 8 + 2 * t + j;
+                if (c < n_c) {
+                    top2_take(best[0], acc[nt][j], c);
+                    top2_take(best[1], acc[nt][2 + j], c);
+                }
+            }
+    }
+    // the four lanes of a row hold the top two of their own columns: merge them
+#pragma unroll
+    for (int r = 0; r < 2; ++r)
+#pragma unroll
+        for (int o = 1; o < 4; o <<= 1) {
+            const float v1 = __shfl_xor_sync(0xffffffffu, best[r].v1, o);
+            const float v2 = __shfl_xor_sync(0xffffffffu, best[r].v2, o);
+            const int i1 = __shfl_xor_sync(0xffffffffu, best[r].i1, o);
+            top2_merge(best[r], v1, v2, i1);
+        }
+    int16_t *lab = v.st.labels + (int64_t)h * v.st.capacity + 1;
+    unsigned redo = 0u;                                    // rows of this warp (bit = row within its 16) to recompute
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const int row = warp * 16 + g + 8 * r;
+        const bool decided = best[r].v1 - best[r].v2 > ASSIGN_MARGIN;     // false for NaN and for a single centroid's -inf rival? (inf - -inf = inf: decided)
+        const unsigned bal = __ballot_sync(0xffffffffu, t == 0 && row < rows && !decided);
+        if (t == 0 && row < rows && decided) lab[r0 + row] = (int16_t)best[r].i1;
+        // ballot bit 4 g marks row g (+ 8 r)
+#pragma unroll
+        for (int gg = 0; gg < 8; ++gg) redo |= ((bal >> (4 * gg)) & 1u) << (gg + 8 * r);
+    }
+    while (redo) {                                         // warp-uniform: every lane built the same mask
+        const int rr = __ffs(redo) - 1;
+        redo &= redo - 1;
+        const float *xr = Xs + (warp * 16 + rr) * AS_LD;
+        Arg b{-INFINITY, 0x7fffffff};
+        for (int c = lane; c < n_c; c += 32) {
+            const float *cr = cent + (int64_t)c * HEAD_DIM;
+            float a = 0.f;
+#pragma unroll 8
+            for (int k = 0; k < HEAD_DIM; k += 4) {        // the sequential chain of assign_kernel, same order
+                const float4 x = *reinterpret_cast<const float4 *>(xr + k);
+                const float4 cc = *reinterpret_cast<const float4 *>(cr + k);
+                a = fmaf(x.x, cc.x, a);
+                a = fmaf(x.y, cc.y, a);
+                a = fmaf(x.z, cc.z, a);
+                a = fmaf(x.w, cc.w, a);
+            }
+            arg_take(b, a, c);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, b.v, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, b.i, o);
+            arg_take(b, ov, oi);
+        }
+        if (lane == 0) lab[r0 + warp * 16 + rr] = (int16_t)(b.i == 0x7fffffff ? 0 : b.i);
+    }
+}
+
 // ---- summaries of every slot from the labels, members taken in position order by one warp --------------
 // lloyd != 0: write cent = unit(sum) where the slot has members (a Lloyd update) instead of the summaries.
 __global__ void __launch_bounds__(256) accumulate_kernel(const FitView v, int lloyd, int slots) {
@@ -234,22 +384,39 @@ __global__ void __launch_bounds__(256) accumulate_kernel(const FitView v, int ll
     float mx = 0.f, mn = INFINITY;
     int cnt = 0;
     const bool live = c < v.st.n_c[h];
-    if (live)
-        for (int i0 = 0; i0 < v.m; i0 += 32) {
-            const int i = i0 + lane;
-            const bool hit = i < v.m && lab[i] == c;
-            unsigned b = __ballot_sync(0xffffffffu, hit);
-            cnt += __popc(b);
-            while (b) {
-                const int j = i0 + __ffs(b) - 1;
-                b &= b - 1;
-                const float4 x = *reinterpret_cast<const float4 *>(X + (int64_t)j * HEAD_DIM + lane * 4);
-                s.x += x.x; s.y += x.y; s.z += x.z; s.w += x.w;
-                const float g = mg[j];
-                mx = fmaxf(mx, g);
-                mn = fminf(mn, g);
+    if (live) {
+        // A lane tests eight labels per step (one 16-byte load where the labels are aligned; clustered position i
+        // is element i + 1 of the head's labels, so the aligned groups start at i = 7, 15, ...), the members are
+        // then taken lane by lane and label by label, i.e. in position order, as the sums require.
+        const int16_t *lab0 = lab - 1;                       // element p = position p; lab0 is 16-byte aligned
+        const int last = v.m + 1;                            // positions [1, last)
+        for (int p0 = 0; p0 < last; p0 += 256) {
+            const int pb = p0 + lane * 8;
+            unsigned mask = 0u;
+            if (pb < last) {
+                const uint4 raw = *reinterpret_cast<const uint4 *>(lab0 + pb);
+                const int16_t *l8 = reinterpret_cast<const int16_t *>(&raw);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) mask |= (unsigned)(pb + j >= 1 && pb + j < last && l8[j] == c) << j;
+            }
+            unsigned lanes = __ballot_sync(0xffffffffu, mask != 0u);
+            while (lanes) {
+                const int l = __ffs(lanes) - 1;
+                lanes &= lanes - 1;
+                unsigned m8 = __shfl_sync(0xffffffffu, mask, l);
+                cnt += __popc(m8);
+                while (m8) {
+                    const int j = p0 + l * 8 + (__ffs(m8) - 1) - 1;      // clustered-key index of the member
+                    m8 &= m8 - 1;
+                    const float4 x = *reinterpret_cast<const float4 *>(X + (int64_t)j * HEAD_DIM + lane * 4);
+                    s.x += x.x; s.y += x.y; s.z += x.z; s.w += x.w;
+                    const float g = mg[j];
+                    mx = fmaxf(mx, g);
+                    mn = fminf(mn, g);
+                }
             }
         }
+    }
     const int64_t row = (int64_t)h * v.st.C + c;
     if (lloyd) {
         if (cnt > 0) {
@@ -700,6 +867,11 @@ static int centre_and_assign(FitView &v, int recentre, cudaStream_t s) {
     return SKV_OK;
 }
 
+// process-wide switch (skv_fit_tensor_cores); SKV_FIT_TC=1 in the environment starts with the tensor-core kernel.
+// Off by default: measured on B200 the two are equally fast (the float32 kernel reaches 42 TFLOP/s) and give the same
+// labels, so the simpler one runs.
+static bool g_fit_tensor_cores = [] { const char *e = getenv("SKV_FIT_TC"); return e && e[0] == '1'; }();
+
 static int launch_assign(const FitView &v, cudaStream_t s) {
     static bool configured[64] = {};
     int dev = 0;
@@ -707,9 +879,12 @@ static int launch_assign(const FitView &v, cudaStream_t s) {
     if (dev < 0 || dev >= 64) return SKV_E_RANGE;
     if (!configured[dev]) {
         SKV_CUDA_OK(cudaFuncSetAttribute(assign_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AS_SMEM));
+        SKV_CUDA_OK(cudaFuncSetAttribute(assign_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AS_SMEM));
         configured[dev] = true;
     }
-    assign_kernel<<<dim3((v.m + AS_ROWS - 1) / AS_ROWS, v.entries), 256, AS_SMEM, s>>>(v);
+    const dim3 grid((v.m + AS_ROWS - 1) / AS_ROWS, v.entries);
+    if (!g_fit_tensor_cores) assign_kernel<<<grid, 256, AS_SMEM, s>>>(v);
+    else assign_tc_kernel<<<grid, 256, AS_SMEM, s>>>(v);
     SKV_CUDA_OK(cudaGetLastError());
     return SKV_OK;
 }
@@ -744,6 +919,8 @@ static int split_rounds(FitView &v, float *projbuf, float split_factor, int iter
 }  // namespace skv
 
 using namespace skv;
+
+extern "C" void skv_fit_tensor_cores(int on) { skv::g_fit_tensor_cores = on != 0; }
 
 extern "C" int64_t skv_fit_workspace_bytes(int heads, int m, int C, int d) {
     if (heads <= 0 || m < 0 || C < 16 || d != HEAD_DIM) return SKV_E_RANGE;
