@@ -300,14 +300,18 @@ struct WarpAttendT {
         const uint32_t vm = vmask[stage];
         float s[4] = {0.f, 0.f, 0.f, 0.f};
         {
+            float s2[4] = {0.f, 0.f, 0.f, 0.f};          // two chains of four products: half the dependent latency
             const int mi = lane >> 3;
             const int row = (lane & 7) + ((mi & 1) << 3), csel = mi >> 1;
 #pragma unroll
             for (int ks = 0; ks < 8; ++ks) {
                 uint32_t a[4];
                 ldmatrix_x4(a, kb + row * 256 + (((2 * ks + csel) ^ (row & 7)) << 4));
-                mma_bf16_16816(s, a, qb[ks][0], qb[ks][1]);
+                if (ks & 1) mma_bf16_16816(s2, a, qb[ks][0], qb[ks][1]);
+                else mma_bf16_16816(s, a, qb[ks][0], qb[ks][1]);
             }
+#pragma unroll
+            for (int i = 0; i < 4; ++i) s[i] += s2[i];
         }
         const int k0 = lane >> 2;                        // this lane's keys: k0 and k0 + 8
         const bool ok0 = (vm >> k0) & 1u, ok1 = (vm >> (k0 + 8)) & 1u;

@@ -10,15 +10,17 @@ namespace skv {
 // threshold key tau with  sum(count | key > tau) < need  and settles exact ties at tau in slot order.
 //   key[c]   order-preserving integer keys of the shared scores (float_key), c < n_c
 //   ci[c]    member counts (int, or float holding whole numbers); clusters with ci[c] <= 0 are never taken
-//   sel      bytes, zeroed by the caller for c < n_c
+//   sel      BITS false: one byte per cluster, zeroed by the caller for c < n_c
+//   bits     BITS true: the selection as bit c % 32 of word c / 32 instead; every word that holds a slot < n_c is
+//            written (the caller zeroes them when `active` is false)
 //   hist     512 ints of shared scratch, ired 40 ints
 //   kmin, kmax, nvalid   this THREAD's partial range and count of the keys of clusters with members (the block
 //            reduction happens here); `active` false: nothing is taken (the reductions and barriers still run)
 // Block-wide: every thread of the NT-thread CTA calls it; sel is complete (and synchronised) on return.
-template <int NT, typename CT>
+template <int NT, typename CT, bool BITS = false>
 __device__ __forceinline__ void pick_by_threshold(const uint32_t *key, const CT *ci, uint8_t *sel, int *hist,
                                                   int *ired, int n_c, int need, bool active, uint32_t kmin,
-                                                  uint32_t kmax, int nvalid) {
+                                                  uint32_t kmax, int nvalid, uint32_t *bits = nullptr) {
     constexpr int NW = NT / 32;
     const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
 #pragma unroll
@@ -113,28 +115,44 @@ __device__ __forceinline__ void pick_by_threshold(const uint32_t *key, const CT 
                 greater += kj > kl ? nj : 0;
             }
             uint32_t t = (lane < m && above + greater < need) ? kl : 0xffffffffu;
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) t = min(t, __shfl_xor_sync(0xffffffffu, t, o));
-            tau = t == 0xffffffffu ? lo : t;
-            int gt = 0;
-            for (int j = 0; j < m; ++j) {
-                const uint32_t kj = __shfl_sync(0xffffffffu, kl, j);
-                const int nj = __shfl_sync(0xffffffffu, nl, j);
-                gt += kj > tau ? nj : 0;
+            t = __reduce_min_sync(0xffffffffu, t);
+            if (t != 0xffffffffu) {
+                // the members ranked ahead of the threshold's candidate are what its lane just counted
+                tau = t;
+                const unsigned at = __ballot_sync(0xffffffffu, lane < m && kl == t);
+                above += __shfl_sync(0xffffffffu, greater, __ffs(at) - 1);
+            } else {
+                tau = lo;
+                int gt = 0;
+                for (int j = 0; j < m; ++j) {
+                    const uint32_t kj = __shfl_sync(0xffffffffu, kl, j);
+                    const int nj = __shfl_sync(0xffffffffu, nl, j);
+                    gt += kj > tau ? nj : 0;
+                }
+                above += gt;
             }
-            above += gt;
         }
         int ties = 0;
-        for (int c = tid; c < n_c; c += NT) {
-            const uint32_t k = key[c];
-            sel[c] = k >= tau;                        // a lone cluster at the threshold is taken: above < need
-            ties += (k == tau);
+        if (BITS) {
+            for (int base = wid * 32; base < n_c; base += NT) {       // a warp's 32 slots are one word
+                const int c = base + lane;
+                const uint32_t k = c < n_c ? key[c] : 0u;
+                const unsigned v = __ballot_sync(0xffffffffu, c < n_c && k >= tau);
+                if (lane == 0) bits[base >> 5] = v;
+                ties += (c < n_c && k == tau);
+            }
+        } else {
+            for (int c = tid; c < n_c; c += NT) {
+                const uint32_t k = key[c];
+                sel[c] = k >= tau;                    // a lone cluster at the threshold is taken: above < need
+                ties += (k == tau);
+            }
         }
         ties = warp_sum_int(ties);
-        if (lane == 0) ired[2 + wid] = ties;
+        if (lane == 0) ired[32 + wid] = ties;            // (its own words: warps may still be reading the ranges)
         __syncthreads();
         int t = 0;
-        for (int w = 0; w < NW; ++w) t += ired[2 + w];
+        for (int w = 0; w < NW; ++w) t += ired[32 + w];
         if (t > 1 && wid == 0) {
             // several clusters share the threshold key: slot order, each taken while the keys ranked before
             // it stay under need
@@ -150,7 +168,13 @@ __device__ __forceinline__ void pick_by_threshold(const uint32_t *key, const CT 
                     const int u = __shfl_up_sync(0xffffffffu, inc, o);
                     if (lane >= o) inc += u;
                 }
-                if (tie) sel[c] = (running + inc - mine) < need;
+                const bool keep = (running + inc - mine) < need;
+                if (BITS) {
+                    const unsigned drop = __ballot_sync(0xffffffffu, tie && !keep);
+                    if (lane == 0 && drop) bits[base >> 5] &= ~drop;
+                } else if (tie) {
+                    sel[c] = keep;
+                }
                 running += __shfl_sync(0xffffffffu, inc, 31);
             }
         }

@@ -22,10 +22,12 @@
 
 namespace skv {
 
-constexpr int STEP_THREADS = 128, STEP_WARPS = 4, STEP_CS = 8, STEP_LPT = 8, STEP_STAGES = 2;
-constexpr int STEP_SUB = STEP_THREADS * STEP_LPT;         // positions listed per pass
-constexpr int STEP_SLICES = STEP_CS * STEP_WARPS;         // (CTA, warp) pairs that score a head's clusters
-static_assert(STEP_SLICES == 32, "a warp's lanes stand for the slices when their statistics are combined");
+// CTAs of NW = 4 warps (two per SM) or 8 warps (one per SM, for launches with very few heads: the phases every CTA
+// runs for itself - scoring its eighth of the summaries, the pick - then take half as many instructions per warp).
+constexpr int STEP_CS = 8, STEP_LPT = 8, STEP_STAGES = 2;
+constexpr int STEP_GROUPS = 2;                            // label groups of STEP_LPT per thread and pass
+__host__ __device__ constexpr int step_pass(int nw) { return nw * 32 * STEP_LPT * STEP_GROUPS; }   // positions per pass
+__host__ __device__ constexpr int step_slices(int nw) { return STEP_CS * nw; }   // (CTA, warp) pairs that score a head
 constexpr int STEP_PART_LD = 132;                         // floats per partial row: 128 sums, max, sum, rows, unused
 
 struct StepParams {
@@ -102,36 +104,11 @@ __device__ __forceinline__ uint32_t step_pack_half2(float lo, float hi) {
     return *reinterpret_cast<const uint32_t *>(&v);
 }
 
-// Reduce NV per-thread values over the 128-thread CTA; every thread gets the results.  red: [NV][4] floats.
-template <bool IS_MAX, int NV>
-__device__ __forceinline__ void step_reduce(float (&v)[NV], float *red) {
-    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1)
-#pragma unroll
-        for (int g = 0; g < NV; ++g) {
-            const float y = __shfl_xor_sync(0xffffffffu, v[g], o);
-            v[g] = IS_MAX ? fmaxf(v[g], y) : v[g] + y;
-        }
-    __syncthreads();                                   // red may still be read from an earlier reduction
-    if (lane == 0)
-#pragma unroll
-        for (int g = 0; g < NV; ++g) red[g * STEP_WARPS + wid] = v[g];
-    __syncthreads();
-#pragma unroll
-    for (int g = 0; g < NV; ++g) {
-        float r = red[g * STEP_WARPS];
-#pragma unroll
-        for (int w = 1; w < STEP_WARPS; ++w) r = IS_MAX ? fmaxf(r, red[g * STEP_WARPS + w]) : r + red[g * STEP_WARPS + w];
-        v[g] = r;
-    }
-}
-
 // QK-norm + rotary of KV head h's G query heads into sq (float values of the bf16 results) and sqb (bf16);
 // `store_q`: also to the caller's q buffer; `store_kv`: this CTA reads the new token's position, so it
 // writes the token's K and V rows itself before it gathers them.
 __device__ __forceinline__ void step_rope(const skv_rope &r, int h, bool store_q, bool store_kv, int G, float *sq,
-                                          __nv_bfloat16 *sqb) {
+                                          __nv_bfloat16 *sqb, int nw) {
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
     const int seq = h / r.H_kv, hk = h % r.H_kv, per_seq = r.H + 2 * r.H_kv;
     const int64_t pos = r.pos[r.pos_per_seq ? seq : 0];
@@ -139,7 +116,7 @@ __device__ __forceinline__ void step_rope(const skv_rope &r, int h, bool store_q
     const __nv_bfloat16 *cs = static_cast<const __nv_bfloat16 *>(r.cos_table) + pos * HEAD_DIM;
     const __nv_bfloat16 *sn = static_cast<const __nv_bfloat16 *>(r.sin_table) + pos * HEAD_DIM;
     const int jobs = G + (store_kv ? 2 : 0);
-    for (int j = wid; j < jobs; j += STEP_WARPS) {
+    for (int j = wid; j < jobs; j += nw) {
         if (j < G) {
             const int qh = hk * G + j;
             const float4 v = norm_rope_head(row + (int64_t)qh * HEAD_DIM, static_cast<const __nv_bfloat16 *>(r.q_norm_w),
@@ -165,16 +142,16 @@ __device__ __forceinline__ void step_rope(const skv_rope &r, int h, bool store_q
 
 // Bytes of the selection's scratch, which shares the front of the dynamic shared memory with the gather rings.
 __host__ __device__ inline int step_per_max(int C) { return ((C / STEP_CS) + 7) & ~7; }
-__host__ __device__ inline size_t step_sel_bytes(int G, int C) {
+__host__ __device__ inline size_t step_sel_bytes(int G, int C, int nw) {
     return (size_t)step_per_max(C) * 128 + (size_t)G * C * 4 + (size_t)C * 4 + (size_t)step_per_max(C) * 8 +
-           (size_t)STEP_SLICES * 8 * 3 * 4;                 // + slice statistics and factors
+           (size_t)step_slices(nw) * 8 * 3 * 4;             // + slice statistics and factors
 }
-__host__ __device__ inline size_t step_front_bytes(int G, int C, int stages) {
-    const size_t ring = (size_t)STEP_WARPS * stages * 8192, sel = (step_sel_bytes(G, C) + 127) & ~size_t(127);
+__host__ __device__ inline size_t step_front_bytes(int G, int C, int stages, int nw) {
+    const size_t ring = (size_t)nw * stages * 8192, sel = (step_sel_bytes(G, C, nw) + 127) & ~size_t(127);
     return ring > sel ? ring : sel;
 }
-__host__ __device__ inline size_t step_smem_bytes(int G, int C, int stages) {
-    size_t b = step_front_bytes(G, C, stages);
+__host__ __device__ inline size_t step_smem_bytes(int G, int C, int stages, int nw) {
+    size_t b = step_front_bytes(G, C, stages, nw);
     b += ((size_t)(C / 32 + 1) * 4 + 15) & ~size_t(15);       // selection bits
     b += (size_t)G * HEAD_DIM * 4 + (size_t)G * HEAD_DIM * 2;  // query, float and bf16
     b += (size_t)STEP_CS * G * STEP_PART_LD * 4;               // partials received by the cluster's first CTA
@@ -182,15 +159,17 @@ __host__ __device__ inline size_t step_smem_bytes(int G, int C, int stages) {
     return (b + 127) & ~size_t(127);
 }
 
-// Grid (8 * ncl, heads), clusters of 8 CTAs along x, 128 threads.
-template <int STAGES, int GP>
-__global__ void __launch_bounds__(STEP_THREADS, 2) step_kernel(const StepParams p) {
+// Grid (8 * ncl, heads), clusters of 8 CTAs along x, NW warps.
+template <int STAGES, int GP, int NW>
+__global__ void __launch_bounds__(NW * 32, 2) step_kernel(const StepParams p) {
+    constexpr int STEP_THREADS = NW * 32, STEP_WARPS = NW, STEP_SUB = STEP_THREADS * STEP_LPT;
+    constexpr int STEP_SLICES = step_slices(NW), SPL = STEP_SLICES / 32;    // slices per lane when they are combined
     extern __shared__ __align__(128) unsigned char smem[];
     __shared__ uint32_t s_vmask[STEP_WARPS][STAGES];
     __shared__ int s_flag;
     __shared__ int s_scan[40];
     __shared__ int ired[40];
-    __shared__ uint16_t s_rows[STEP_SUB];
+    __shared__ uint16_t s_rows[step_pass(NW)];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int h = blockIdx.y, split = blockIdx.x, S = gridDim.x;
     const unsigned rank = cluster_rank();
@@ -206,7 +185,7 @@ __global__ void __launch_bounds__(STEP_THREADS, 2) step_kernel(const StepParams 
     float *smx = cntf + C, *smn = smx + per_max;                              // [per_max] key lengths of this CTA's clusters
     float *stat = smn + per_max;                                              // [32 slices][GP][2] (max, sum of exp)
     float *fac = stat + STEP_SLICES * GP * 2;                                 // [32 slices][GP] exp(max - M) / T
-    unsigned char *tail = smem + step_front_bytes(G, C, STAGES);
+    unsigned char *tail = smem + step_front_bytes(G, C, STAGES, NW);
     uint32_t *s_bits = reinterpret_cast<uint32_t *>(tail);
     tail += ((size_t)(C / 32 + 1) * 4 + 15) & ~size_t(15);
     float *sq = reinterpret_cast<float *>(tail);
@@ -231,8 +210,15 @@ __global__ void __launch_bounds__(STEP_THREADS, 2) step_kernel(const StepParams 
     const int chunk = max(16, (((n + S - 1) / S + 15) >> 4) << 4);            // multiples of 16: aligned label loads
     const int p0 = min(split * chunk, n), p1 = min(p0 + chunk, n);
     const int16_t *lab = p.st.labels + (int64_t)h * p.st.capacity;
-    uint4 raw = make_uint4(0u, 0u, 0u, 0u);
-    if (p0 + tid * STEP_LPT < p1) raw = __ldg(reinterpret_cast<const uint4 *>(lab + p0 + tid * STEP_LPT));
+    // a pass lists STEP_GROUPS groups of 8 labels per thread, so that the few positions by which a range exceeds
+    // 8 labels per thread (n is rarely a multiple of the grid) do not cost a pass of their own
+    uint4 raw[STEP_GROUPS];
+#pragma unroll
+    for (int j = 0; j < STEP_GROUPS; ++j) {
+        raw[j] = make_uint4(0u, 0u, 0u, 0u);
+        const int at = p0 + j * STEP_SUB + tid * STEP_LPT;
+        if (at < p1) raw[j] = __ldg(reinterpret_cast<const uint4 *>(lab + at));
+    }
     const bool active = end > 1 && need > 0 && n_c > 0;
     const int per = (((n_c + STEP_CS - 1) / STEP_CS) + 7) & ~7;              // clusters scored per CTA
     const int c_lo = min((int)rank * per, n_c), c_hi = min(c_lo + per, n_c), mine = active ? c_hi - c_lo : 0;
@@ -259,7 +245,7 @@ __global__ void __launch_bounds__(STEP_THREADS, 2) step_kernel(const StepParams 
     if (p.rope.qkv) {
         const int64_t pos = p.rope.pos[p.rope.pos_per_seq ? h / p.rope.H_kv : 0];
         const int s_kv = (int)min((int64_t)(S - 1), max((int64_t)0, pos / chunk));
-        step_rope(p.rope, h, split == 0, split == s_kv, G, sq, sqb);
+        step_rope(p.rope, h, split == 0, split == s_kv, G, sq, sqb, STEP_WARPS);
     } else {
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
@@ -274,6 +260,7 @@ __global__ void __launch_bounds__(STEP_THREADS, 2) step_kernel(const StepParams 
     }
     cp_async_wait<0>();
     __syncthreads();
+    step_stamp(p, 9);
 
     // ---- scores of this CTA's clusters: q . dir8 on f16 tiles, 8 clusters per warp and chain.  A warp keeps the
     // scores of the clusters it scored in registers, takes their maximum and the sum of exp(score - maximum) per
@@ -380,18 +367,29 @@ __global__ void __launch_bounds__(STEP_THREADS, 2) step_kernel(const StepParams 
     {
         // slice factors exp(max_s - M) / T per query head: lane = slice, warp g (and g + 4) = query head
         for (int g = warp; g < G; g += STEP_WARPS) {
-            const float2 st = *reinterpret_cast<const float2 *>(stat + ((size_t)lane * GP + g) * 2);
-            const float M = warp_max(st.x);
-            const float e0 = st.x > -INFINITY ? expf(st.x - M) : 0.f;
-            const float T = warp_sum(e0 * st.y);
-            fac[lane * GP + g] = T > 0.f ? e0 / T : 0.f;
+            float2 st[SPL];
+            float M = -INFINITY;
+#pragma unroll
+            for (int k = 0; k < SPL; ++k) {
+                st[k] = *reinterpret_cast<const float2 *>(stat + ((size_t)(lane + 32 * k) * GP + g) * 2);
+                M = fmaxf(M, st[k].x);
+            }
+            M = warp_max(M);
+            float e0[SPL], T = 0.f;
+#pragma unroll
+            for (int k = 0; k < SPL; ++k) {
+                e0[k] = st[k].x > -INFINITY ? expf(st[k].x - M) : 0.f;
+                T = fmaf(e0[k], st[k].y, T);
+            }
+            T = warp_sum(T);
+#pragma unroll
+            for (int k = 0; k < SPL; ++k) fac[(lane + 32 * k) * GP + g] = T > 0.f ? e0[k] / T : 0.f;
         }
         uint32_t *key = reinterpret_cast<uint32_t *>(smem);                   // [C], over sumst once it is scored
-        uint8_t *sel = reinterpret_cast<uint8_t *>(key + C);                  // [C + 1]
-        // only the slots in use are looked at below (the pick marks every one of them), so nothing is cleared here
-        // except when nothing is selected at all
-        if (!active)
-            for (int c = tid; c < n_c; c += STEP_THREADS) sel[c] = 0;
+        // selection bits: the pick writes the words that hold slots in use (nothing selected: cleared here), the
+        // rest are zero, bit C (the always-read rows; C is a multiple of 32: bit 0 of the last word) is set
+        const int words = C / 32 + 1, used = (n_c + 31) >> 5;
+        for (int wd = (active ? used : 0) + tid; wd < words; wd += STEP_THREADS) s_bits[wd] = wd == words - 1 ? 1u : 0u;
         __syncthreads();
         step_stamp(p, 8);
         uint32_t kmin = 0xffffffffu, kmax = 0u;
@@ -417,29 +415,9 @@ __global__ void __launch_bounds__(STEP_THREADS, 2) step_kernel(const StepParams 
             }
         }
         step_stamp(p, 10);
-        pick_by_threshold<STEP_THREADS, float>(key, cntf, sel, hist, ired, n_c, need, active, kmin, kmax, nvalid);
-        __syncthreads();
+        pick_by_threshold<STEP_THREADS, float, true>(key, cntf, nullptr, hist, ired, n_c, need, active, kmin, kmax, nvalid,
+                                                     s_bits);
         step_stamp(p, 11);
-        // selection bits: the words that hold slots in use, the rest zero, bit C (the always-read rows) set
-        const int words = C / 32 + 1, used = (n_c + 31) >> 5;
-        const bool publish = split == 0;
-        for (int wd = warp; wd < words; wd += STEP_WARPS) {
-            unsigned v = 0u;
-            if (wd < used) {                                                  // warp-uniform
-                const int c = wd * 32 + lane;
-                v = __ballot_sync(0xffffffffu, c < n_c && sel[c]);
-            }
-            if (wd == words - 1) v |= 1u;                                     // C is a multiple of 32: bit 0 of the last word
-            if (lane == 0) {
-                s_bits[wd] = v;
-                if (publish && p.selbits) p.selbits[(int64_t)h * words + wd] = v;
-            }
-        }
-        if (publish && p.w) {
-            __syncthreads();
-            for (int c = tid; c <= C; c += STEP_THREADS)
-                p.w[(int64_t)h * (C + 1) + c] = (float)((s_bits[c >> 5] >> (c & 31)) & 1u);
-        }
     }
     __syncthreads();                                       // the selection's scratch is free: the rings take its place
     step_stamp(p, 4);
@@ -451,34 +429,39 @@ __global__ void __launch_bounds__(STEP_THREADS, 2) step_kernel(const StepParams 
             p.ksr * 2, p.vsr * 2, p.scale_log2);
     int read_rows = 0;
     bool bad = false;
-    for (int sub0 = p0; sub0 < p1; sub0 += STEP_SUB) {
-        const int base = sub0 + tid * STEP_LPT;
+    for (int sub0 = p0; sub0 < p1; sub0 += step_pass(NW)) {
         uint32_t take = 0;
-        if (base < p1) {
-            const int16_t *l16 = reinterpret_cast<const int16_t *>(&raw);
 #pragma unroll
-            for (int i = 0; i < STEP_LPT; ++i) {
-                const unsigned l = (unsigned)(int)l16[i];
-                if (base + i < p1) {
-                    if (l <= (unsigned)C) take |= ((s_bits[l >> 5] >> (l & 31)) & 1u) << i;
-                    else bad = true;
+        for (int j = 0; j < STEP_GROUPS; ++j) {
+            const int base = sub0 + j * STEP_SUB + tid * STEP_LPT;
+            if (base < p1) {
+                const int16_t *l16 = reinterpret_cast<const int16_t *>(&raw[j]);
+#pragma unroll
+                for (int i = 0; i < STEP_LPT; ++i) {
+                    const unsigned l = (unsigned)(int)l16[i];
+                    if (base + i < p1) {
+                        if (l <= (unsigned)C) take |= ((s_bits[l >> 5] >> (l & 31)) & 1u) << (j * STEP_LPT + i);
+                        else bad = true;
+                    }
                 }
             }
+            if (base + step_pass(NW) < p1) raw[j] = __ldg(reinterpret_cast<const uint4 *>(lab + base + step_pass(NW)));
         }
-        if (base + STEP_SUB < p1) raw = __ldg(reinterpret_cast<const uint4 *>(lab + base + STEP_SUB));
         int total;
         int off = block_excl_scan(__popc(take), s_scan, total);
         while (take) {
             const int i = __ffs(take) - 1;
             take &= take - 1;
-            s_rows[off++] = (uint16_t)(tid * STEP_LPT + i);
+            s_rows[off++] = (uint16_t)((i >> 3) * STEP_SUB + tid * STEP_LPT + (i & 7));
         }
         __syncthreads();
+        if (sub0 == p0) step_stamp(p, 12);
         read_rows += total;
         const int tiles = (total + TILE_ROWS - 1) / TILE_ROWS;
         const int tper = (tiles + STEP_WARPS - 1) / STEP_WARPS;
         const int t0 = min(warp * tper, tiles), t1 = min(t0 + tper, tiles);
         wa.run(t0, t1, [&](int row) { return row < total ? sub0 + (int)s_rows[row] : -1; });
+        if (sub0 == p0) step_stamp(p, 13);
         __syncthreads();                                   // the list is rewritten by the next pass
     }
     step_stamp(p, 5);
@@ -487,6 +470,8 @@ __global__ void __launch_bounds__(STEP_THREADS, 2) step_kernel(const StepParams 
     wa.store_partial(red, warp, G);
     __syncthreads();
     // this CTA's partial goes to the cluster's first CTA: thread t owns column t
+    const bool col = tid < HEAD_DIM;                       // thread t < 128 owns column t of the partials
+    const int tc = col ? tid : 0;
     for (int g = 0; g < G; ++g) {
         float M = NEG_BIG;
 #pragma unroll
@@ -497,10 +482,10 @@ __global__ void __launch_bounds__(STEP_THREADS, 2) step_kernel(const StepParams 
             const float *r = red + (w * G + g) * 132;
             const float f = fast_exp2(r[128] - M);
             dn += f * r[129];
-            nm += f * r[tid];
+            nm += f * r[tc];
         }
         float *dst = recv + ((size_t)rank * G + g) * STEP_PART_LD;
-        remote_store(remote_addr(dst + tid, 0), nm);
+        if (col) remote_store(remote_addr(dst + tid, 0), nm);
         if (tid == 0) {
             remote_store(remote_addr(dst + 128, 0), M);
             remote_store(remote_addr(dst + 129, 0), dn);
@@ -508,6 +493,15 @@ __global__ void __launch_bounds__(STEP_THREADS, 2) step_kernel(const StepParams 
         }
     }
     cluster_arrive();                                      // barrier 2: the cluster's partials are in its first CTA
+    if (split == STEP_CS - 1) {
+        // the selection for callers who look at it, written by a CTA that has nothing to merge, while it waits
+        const int words = C / 32 + 1;
+        if (p.selbits)
+            for (int wd = tid; wd < words; wd += STEP_THREADS) p.selbits[(int64_t)h * words + wd] = s_bits[wd];
+        if (p.w)
+            for (int c = tid; c <= C; c += STEP_THREADS)
+                p.w[(int64_t)h * (C + 1) + c] = (float)((s_bits[c >> 5] >> (c & 31)) & 1u);
+    }
     cluster_wait();
     step_stamp(p, 6);
     if (rank != 0) return;
@@ -528,13 +522,13 @@ __global__ void __launch_bounds__(STEP_THREADS, 2) step_kernel(const StepParams 
             const float *row = recv + ((size_t)r * G + g) * STEP_PART_LD;
             const float f = fast_exp2(row[128] - M);
             dn = fmaf(f, row[129], dn);
-            nm = fmaf(f, row[tid], nm);
+            nm = fmaf(f, row[tc], nm);
         }
         if (p.ncl == 1 && out) {
-            store_out(out + ((int64_t)h * G + g) * HEAD_DIM + tid, dn > 0.f ? nm / dn : 0.f);
+            if (col) store_out(out + ((int64_t)h * G + g) * HEAD_DIM + tid, dn > 0.f ? nm / dn : 0.f);
         } else {
             float *pa = p.part + (((int64_t)h * p.ncl + kcl) * G + g) * STEP_PART_LD;
-            __stcg(pa + tid, nm);
+            if (col) __stcg(pa + tid, nm);
             if (tid == 0) {
                 __stcg(pa + 128, M);
                 __stcg(pa + 129, dn);
@@ -571,7 +565,7 @@ __global__ void __launch_bounds__(STEP_THREADS, 2) step_kernel(const StepParams 
                 const float *row = src + ((size_t)k * G + g) * STEP_PART_LD;
                 pm[k] = __ldcg(row + 128);
                 pd[k] = __ldcg(row + 129);
-                pn[k] = __ldcg(row + tid);
+                pn[k] = __ldcg(row + tc);
                 if (g == 0) pr[k] = __ldcg(row + 130);
             }
         }
@@ -586,7 +580,7 @@ __global__ void __launch_bounds__(STEP_THREADS, 2) step_kernel(const StepParams 
             nm = fmaf(f, pn[k], nm);
             total_rows += pr[k];
         }
-        store_out(out + ((int64_t)h * G + g) * HEAD_DIM + tid, dn > 0.f ? nm / dn : 0.f);
+        if (col) store_out(out + ((int64_t)h * G + g) * HEAD_DIM + tid, dn > 0.f ? nm / dn : 0.f);
     }
     if (tid == 0) {
         if (p.cnt) p.cnt[h] = (int)total_rows;
@@ -598,42 +592,45 @@ __global__ void __launch_bounds__(STEP_THREADS, 2) step_kernel(const StepParams 
 using StepKern = void (*)(const StepParams);
 
 // (a ring of three tiles per warp was measured: 35.0 against 35.2 us per layer at 8 heads, not worth 32 KB per CTA)
-static int step_stages() { return STEP_STAGES; }
-static StepKern step_kernel_for(int G) {
-    return G <= 2 ? step_kernel<STEP_STAGES, 2> : (G <= 4 ? step_kernel<STEP_STAGES, 4> : step_kernel<STEP_STAGES, 8>);
+// 4 warps with a ring of two tiles each, or 8 warps with one tile each: the same 64 KB of rings, two CTAs per SM
+static int step_stages(int nw) { return nw == 8 ? 1 : STEP_STAGES; }
+static StepKern step_kernel_for(int G, int nw) {
+    if (nw == 8) return G <= 2 ? step_kernel<1, 2, 8> : (G <= 4 ? step_kernel<1, 4, 8> : step_kernel<1, 8, 8>);
+    return G <= 2 ? step_kernel<STEP_STAGES, 2, 4> : (G <= 4 ? step_kernel<STEP_STAGES, 4, 4> : step_kernel<STEP_STAGES, 8, 4>);
 }
 
 // The kernel's dynamic shared memory limit only ever grows: one record per device and kernel variant, shared by
 // the occupancy query and the launch (a smaller request must not lower what a larger shape configured).
-static int step_configure(StepKern kern, int G, size_t smem) {
-    static size_t configured[64][3] = {};
-    const int gsel = G <= 2 ? 0 : (G <= 4 ? 1 : 2);
+static int step_configure(StepKern kern, int G, int nw, size_t smem) {
+    static size_t configured[64][3][2] = {};
+    const int gsel = G <= 2 ? 0 : (G <= 4 ? 1 : 2), wsel = nw == 8;
     int dev = 0;
     SKV_CUDA_OK(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64) return SKV_E_RANGE;
-    if (configured[dev][gsel] < smem) {
+    if (configured[dev][gsel][wsel] < smem) {
         SKV_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        configured[dev][gsel] = smem;
+        configured[dev][gsel][wsel] = smem;
     }
     return SKV_OK;
 }
 
-// Clusters of 8 CTAs that one launch can keep resident on this device for (G, C); cached per device and shape.
-static int step_resident_clusters(int G, int C) {
-    struct Entry { int dev, G, C, n; };
-    static Entry cache[16];
+// Clusters of 8 CTAs of `nw` warps that one launch can keep resident on this device for (G, C); cached per device
+// and shape.
+static int step_resident_clusters(int G, int C, int nw) {
+    struct Entry { int dev, G, C, nw, n; };
+    static Entry cache[32];
     static int used = 0;
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess) return 0;
     for (int i = 0; i < used; ++i)
-        if (cache[i].dev == dev && cache[i].G == G && cache[i].C == C) return cache[i].n;
-    const size_t smem = step_smem_bytes(G, C, step_stages());
+        if (cache[i].dev == dev && cache[i].G == G && cache[i].C == C && cache[i].nw == nw) return cache[i].n;
+    const size_t smem = step_smem_bytes(G, C, step_stages(nw), nw);
     if ((int)smem > device_max_smem_optin()) return 0;
-    StepKern kern = step_kernel_for(G);
-    if (step_configure(kern, G, smem) != SKV_OK) return 0;
+    StepKern kern = step_kernel_for(G, nw);
+    if (step_configure(kern, G, nw, smem) != SKV_OK) return 0;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(STEP_CS * 64, 1, 1);
-    cfg.blockDim = dim3(STEP_THREADS, 1, 1);
+    cfg.blockDim = dim3(nw * 32, 1, 1);
     cfg.dynamicSmemBytes = smem;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -642,8 +639,16 @@ static int step_resident_clusters(int G, int C) {
     cfg.numAttrs = 1;
     int n = 0;
     if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess) { cudaGetLastError(); n = 0; }
-    if (used < 16) cache[used++] = Entry{dev, G, C, n};
+    if (used < 32) cache[used++] = Entry{dev, G, C, nw, n};
     return n;
+}
+
+// Warps per CTA for a launch of `heads` heads: 8 (one CTA per SM) while two clusters per head stay resident, which
+// only the smallest launches allow, else 4 (two CTAs per SM).  SKV_STEP_WARPS=4|8 in the environment forces one.
+static int step_warps_for(int heads, int G, int C) {
+    static const int forced = [] { const char *e = getenv("SKV_STEP_WARPS"); return e ? atoi(e) : 0; }();
+    if (forced == 4 || forced == 8) return forced;
+    return 4;
 }
 
 }  // namespace skv
@@ -654,7 +659,7 @@ extern "C" void skv_debug_step_probe(void *dev_ptr) { skv::g_step_probe = static
 
 extern "C" int skv_step_clusters(int heads, int G, int C, int summary_bits) {
     if (heads <= 0 || G < 1 || G > 8 || C < 64 || (C & (C - 1)) || C > 2048 || summary_bits != 8) return 0;
-    const int resident = step_resident_clusters(G, C);
+    const int resident = step_resident_clusters(G, C, step_warps_for(heads, G, C));
     if (resident < heads) return 0;                         // more than one wave of clusters: the two-launch path streams better
     int ncl = resident / heads;
     return ncl > 8 ? 8 : ncl;
@@ -697,7 +702,8 @@ extern "C" int skv_step(const skv_state *st, const void *q, int G, const int32_t
     if ((k_row_stride * 2) % 16 || (v_row_stride * 2) % 16 || (k_head_stride * 2) % 16 || (v_head_stride * 2) % 16 ||
         k_row_stride < HEAD_DIM || v_row_stride < HEAD_DIM)
         return SKV_E_ALIGN;
-    const size_t smem = step_smem_bytes(G, st->C, step_stages());
+    const int nw = step_warps_for(st->heads, G, st->C);
+    const size_t smem = step_smem_bytes(G, st->C, step_stages(nw), nw);
     if ((int)smem > device_max_smem_optin()) return SKV_E_DIM;
     StepParams p;
     p.st = *st; p.q = q; p.K = K; p.V = V; p.n_dev = n_dev; p.n_group = n_group; p.out = out; p.w = w; p.selbits = selbits; p.cnt = cnt;
@@ -709,14 +715,14 @@ extern "C" int skv_step(const skv_state *st, const void *q, int G, const int32_t
     p.scale = scale; p.scale_log2 = scale * LOG2E;
     p.rope = rope ? *rope : skv_rope{};
     p.probe = g_step_probe;
-    StepKern kern = step_kernel_for(G);
+    StepKern kern = step_kernel_for(G, nw);
     {
-        const int rc = step_configure(kern, G, smem);
+        const int rc = step_configure(kern, G, nw, smem);
         if (rc) return rc;
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(STEP_CS * clusters, st->heads, 1);
-    cfg.blockDim = dim3(STEP_THREADS, 1, 1);
+    cfg.blockDim = dim3(nw * 32, 1, 1);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = static_cast<cudaStream_t>(stream);
     cudaLaunchAttribute attr[2];
