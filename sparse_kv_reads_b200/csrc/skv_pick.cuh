@@ -13,43 +13,54 @@ namespace skv {
 //   sel      BITS false: one byte per cluster, zeroed by the caller for c < n_c
 //   bits     BITS true: the selection as bit c % 32 of word c / 32 instead; every word that holds a slot < n_c is
 //            written (the caller zeroes them when `active` is false)
-//   hist     512 ints of shared scratch, ired 40 ints
+//   hist     576 ints of shared scratch, 16-byte aligned; ired 40 ints
 //   kmin, kmax, nvalid   this THREAD's partial range and count of the keys of clusters with members (the block
-//            reduction happens here); `active` false: nothing is taken (the reductions and barriers still run)
+//            reduction happens here); `active` false: nothing is taken (the reductions and barriers still run).
+//            READY true: they are the whole block's values already, and hist is zero on entry (no reduction, and
+//            the first pass does not clear)
 // Block-wide: every thread of the NT-thread CTA calls it; sel is complete (and synchronised) on return.
-template <int NT, typename CT, bool BITS = false>
+template <int NT, typename CT, bool BITS = false, bool READY = false>
 __device__ __forceinline__ void pick_by_threshold(const uint32_t *key, const CT *ci, uint8_t *sel, int *hist,
                                                   int *ired, int n_c, int need, bool active, uint32_t kmin,
                                                   uint32_t kmax, int nvalid, uint32_t *bits = nullptr) {
     constexpr int NW = NT / 32;
     const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
+    if (tid == 0) ired[1] = 0;                        // the candidates' counter (a barrier lies before its first use)
+    if (!READY) {
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-        kmin = min(kmin, __shfl_xor_sync(0xffffffffu, kmin, o));
-        kmax = max(kmax, __shfl_xor_sync(0xffffffffu, kmax, o));
-        nvalid += __shfl_xor_sync(0xffffffffu, nvalid, o);
+        for (int o = 16; o > 0; o >>= 1) {
+            kmin = min(kmin, __shfl_xor_sync(0xffffffffu, kmin, o));
+            kmax = max(kmax, __shfl_xor_sync(0xffffffffu, kmax, o));
+            nvalid += __shfl_xor_sync(0xffffffffu, nvalid, o);
+        }
+        if (lane == 0) { ired[8 + wid] = (int)kmin; ired[16 + wid] = (int)kmax; ired[24 + wid] = nvalid; }
+        __syncthreads();
     }
-    if (lane == 0) { ired[8 + wid] = (int)kmin; ired[16 + wid] = (int)kmax; ired[24 + wid] = nvalid; }
-    __syncthreads();
     if (active) {
         // ---- threshold: the smallest key t with sum(count | key > t) < need.  The keys still in question are
         // binned linearly over their range (256 bins, weighted by the clusters' counts); the bin in which the
         // running count passes `need` becomes the new range, until at most 32 candidates are left, which a
         // warp ranks against each other directly.  Scores crowd into a few octaves, so binning the range they
         // span (instead of the keys' top bytes) usually needs a single pass.  Every warp scans the histogram
-        // for itself, so a pass costs two barriers.
-        kmin = 0xffffffffu; kmax = 0u; nvalid = 0;
-        for (int w = 0; w < NW; ++w) {
-            kmin = min(kmin, (uint32_t)ired[8 + w]);
-            kmax = max(kmax, (uint32_t)ired[16 + w]);
-            nvalid += ired[24 + w];
+        // for itself, and the candidates have words of their own, so the usual course costs three barriers.
+        if (!READY) {
+            kmin = 0xffffffffu; kmax = 0u; nvalid = 0;
+            for (int w = 0; w < NW; ++w) {
+                kmin = min(kmin, (uint32_t)ired[8 + w]);
+                kmax = max(kmax, (uint32_t)ired[16 + w]);
+                nvalid += ired[24 + w];
+            }
         }
         uint32_t lo = kmin, hi = kmax, tau = 0u;
         int above = 0, cand = nvalid;
-        int *hw = hist, *hn = hist + 256;
-        for (int pass = 0; pass < 8 && cand > 32 && lo < hi; ++pass) {
-            for (int i = tid; i < 512; i += NT) hist[i] = 0;
-            __syncthreads();
+        int *hw = hist, *hn = hist + 256, *cw = hist + 512, *cn = hist + 544;
+        int pass = 0;
+        for (; pass < 8 && cand > 32 && lo < hi; ++pass) {
+            if (!READY || pass > 0) {
+                if (pass > 0) __syncthreads();        // every warp has read the histogram before it is cleared
+                for (int i = tid; i < 512; i += NT) hist[i] = 0;
+                __syncthreads();
+            }
             const int shift = max(0, 24 - __clz(hi - lo));            // (hi - lo) >> shift <= 255
             for (int c = tid; c < n_c; c += NT) {
                 const uint32_t k = key[c];
@@ -61,8 +72,12 @@ __device__ __forceinline__ void pick_by_threshold(const uint32_t *key, const CT 
             }
             __syncthreads();
             int loc[8], mine = 0;                     // lane owns bins [8*lane, 8*lane+8)
+            {
+                const int4 a = reinterpret_cast<const int4 *>(hw)[lane * 2], b = reinterpret_cast<const int4 *>(hw)[lane * 2 + 1];
+                loc[0] = a.x; loc[1] = a.y; loc[2] = a.z; loc[3] = a.w; loc[4] = b.x; loc[5] = b.y; loc[6] = b.z; loc[7] = b.w;
+            }
 #pragma unroll
-            for (int i = 0; i < 8; ++i) { loc[i] = hw[lane * 8 + i]; mine += loc[i]; }
+            for (int i = 0; i < 8; ++i) mine += loc[i];
             int suf = mine;                           // inclusive suffix over lanes >= lane
 #pragma unroll
             for (int o = 1; o < 32; o <<= 1) {
@@ -76,51 +91,48 @@ __device__ __forceinline__ void pick_by_threshold(const uint32_t *key, const CT 
                 if (above + run < need) best = lane * 8 + i;
                 run += loc[i];
             }
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) best = min(best, __shfl_xor_sync(0xffffffffu, best, o));
-            best = min(best, 255);
+            best = min(__reduce_min_sync(0xffffffffu, best), 255);
             int gt = 0;
 #pragma unroll
             for (int i = 0; i < 8; ++i) gt += (lane * 8 + i > best) ? loc[i] : 0;
-            gt = warp_sum_int(gt);
-            above += gt;
+            above += __reduce_add_sync(0xffffffffu, gt);
             cand = hn[best];
             const uint32_t nlo = lo + ((uint32_t)best << shift);
             const uint32_t span = (1u << shift) - 1u;
             hi = (hi - nlo > span) ? nlo + span : hi;
             lo = nlo;
-            __syncthreads();                          // every warp has read the histogram before it is cleared
         }
+        int t = -1;                                   // clusters whose key is the threshold; -1: still to be counted
         if (nvalid > 0 && lo >= hi) {
             tau = lo;                                 // one key value left (possibly shared by several clusters)
         } else if (nvalid > 0) {
             // at most 32 candidates: list them, then every warp ranks them for itself
-            if (tid == 0) ired[1] = 0;
-            __syncthreads();
+            if (READY && pass == 0) __syncthreads();  // the counter's reset, when no pass put a barrier after it
             for (int c = tid; c < n_c; c += NT) {
                 const uint32_t k = key[c];
                 if (ci[c] > 0 && k >= lo && k <= hi) {
                     const int j = atomicAdd(&ired[1], 1);
-                    if (j < 32) { hw[j] = (int)k; hn[j] = (int)ci[c]; }
+                    if (j < 32) { cw[j] = (int)k; cn[j] = (int)ci[c]; }
                 }
             }
             __syncthreads();
             const int m = min(ired[1], 32);
-            const uint32_t kl = lane < m ? (uint32_t)hw[lane] : 0u;
-            const int nl = lane < m ? hn[lane] : 0;
+            const uint32_t kl = lane < m ? (uint32_t)cw[lane] : 0u;
+            const int nl = lane < m ? cn[lane] : 0;
             int greater = 0;                          // members of candidates ranked ahead of this lane's
             for (int j = 0; j < m; ++j) {
                 const uint32_t kj = __shfl_sync(0xffffffffu, kl, j);
                 const int nj = __shfl_sync(0xffffffffu, nl, j);
                 greater += kj > kl ? nj : 0;
             }
-            uint32_t t = (lane < m && above + greater < need) ? kl : 0xffffffffu;
-            t = __reduce_min_sync(0xffffffffu, t);
-            if (t != 0xffffffffu) {
-                // the members ranked ahead of the threshold's candidate are what its lane just counted
-                tau = t;
-                const unsigned at = __ballot_sync(0xffffffffu, lane < m && kl == t);
+            const uint32_t tmin = __reduce_min_sync(0xffffffffu, (lane < m && above + greater < need) ? kl : 0xffffffffu);
+            if (tmin != 0xffffffffu) {
+                // the members ranked ahead of the threshold's candidate are what its lane just counted; every
+                // cluster with the threshold's key is among the candidates
+                tau = tmin;
+                const unsigned at = __ballot_sync(0xffffffffu, lane < m && kl == tmin);
                 above += __shfl_sync(0xffffffffu, greater, __ffs(at) - 1);
+                t = __popc(at);
             } else {
                 tau = lo;
                 int gt = 0;
@@ -148,11 +160,15 @@ __device__ __forceinline__ void pick_by_threshold(const uint32_t *key, const CT 
                 ties += (k == tau);
             }
         }
-        ties = warp_sum_int(ties);
-        if (lane == 0) ired[32 + wid] = ties;            // (its own words: warps may still be reading the ranges)
-        __syncthreads();
-        int t = 0;
-        for (int w = 0; w < NW; ++w) t += ired[32 + w];
+        if (t < 0) {                                  // (the same branch in every thread)
+            ties = __reduce_add_sync(0xffffffffu, ties);
+            if (lane == 0) ired[32 + wid] = ties;
+            __syncthreads();
+            t = 0;
+            for (int w = 0; w < NW; ++w) t += ired[32 + w];
+        } else if (t > 1) {
+            __syncthreads();                          // the marks above are complete before the ties are settled
+        }
         if (t > 1 && wid == 0) {
             // several clusters share the threshold key: slot order, each taken while the keys ranked before
             // it stay under need

@@ -4,16 +4,20 @@
 // through global memory to the head's last CTA (the pick; the merge of the split partials).  Here a head is
 // served by thread-block clusters of 8 CTAs that talk through distributed shared memory instead:
 //   1. every CTA stages its eighth of the head's 8-bit cluster summaries (requested before the wait for the
-//      launch ahead), scores it on mma.sync f16 tiles and stores the scaled scores into the shared memory of
-//      all 8 CTAs of its cluster;
-//   2. after one cluster barrier every CTA holds all scores and derives the selection for itself - the same
-//      shared score (sum over the query heads of each head's softmax over the clusters) and the same
-//      threshold pick as the selection kernel - so no CTA waits for another one's pick;
+//      launch ahead) and scores it on mma.sync f16 tiles; each warp keeps the maximum and the sum of
+//      exp(score - maximum) of the clusters it scored, per query head, and stores that pair into the shared
+//      memory of all 8 CTAs of its cluster;
+//   2. after a cluster barrier every warp combines the 32 pairs into the softmax's maximum and total, every
+//      CTA turns the scores of ITS clusters into shared scores (sum over the query heads of each head's
+//      softmax share) and order-preserving keys, and stores those into all 8 CTAs; after a second barrier
+//      every CTA holds all keys and runs the same threshold pick as the selection kernel for itself, so no
+//      CTA waits for another one's pick;
 //   3. every CTA attends over its range of positions, rows taken straight from the labels;
 //   4. the 8 partials of a cluster meet in the shared memory of its first CTA, which merges them; only one
-//      partial per cluster (4 per head at 8 heads, none at 32 heads) goes through global memory and a ticket.
+//      partial per cluster (4 per head at 8 heads, none at 32 heads) goes through global memory, where the
+//      output product or the head's last cluster (a ticket) merges them.
 // Remote shared memory is written with plain st.shared::cluster stores (this GPU's memory only, no multicast).
-// Every CTA of a cluster executes all three cluster barriers unconditionally; nothing spins.
+// Every CTA of a cluster executes all four cluster barriers unconditionally; nothing spins.
 #include <cuda_fp16.h>
 
 #include "skv_attend_core.cuh"
@@ -22,8 +26,8 @@
 
 namespace skv {
 
-// CTAs of NW = 4 warps (two per SM) or 8 warps (one per SM, for launches with very few heads: the phases every CTA
-// runs for itself - scoring its eighth of the summaries, the pick - then take half as many instructions per warp).
+// CTAs of NW = 4 warps, two per SM.  (8 warps with a ring of one tile each - the same shared memory, 16 warps per
+// SM - were measured at batch 1, 32k: 690 against 697 tok/s, no gain; the kernel stays generic in NW.)
 constexpr int STEP_CS = 8, STEP_LPT = 8, STEP_STAGES = 2;
 constexpr int STEP_GROUPS = 2;                            // label groups of STEP_LPT per thread and pass
 __host__ __device__ constexpr int step_pass(int nw) { return nw * 32 * STEP_LPT * STEP_GROUPS; }   // positions per pass
@@ -104,6 +108,30 @@ __device__ __forceinline__ uint32_t step_pack_half2(float lo, float hi) {
     return *reinterpret_cast<const uint32_t *>(&v);
 }
 
+// Exclusive scan of one int per thread over the CTA's NW warps with a single barrier; every thread gets `total`.
+// `buf` (NW ints) must not have been read since the last barrier but one, which two passes of the row list satisfy.
+template <int NW>
+__device__ __forceinline__ int step_excl_scan(int v, int *buf, int &total) {
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    int inc = v;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const int t = __shfl_up_sync(0xffffffffu, inc, o);
+        if (lane >= o) inc += t;
+    }
+    if (lane == 31) buf[wid] = inc;
+    __syncthreads();
+    int base = 0;
+    total = 0;
+#pragma unroll
+    for (int w = 0; w < NW; ++w) {
+        const int t = buf[w];
+        base += w < wid ? t : 0;
+        total += t;
+    }
+    return base + inc - v;
+}
+
 // QK-norm + rotary of KV head h's G query heads into sq (float values of the bf16 results) and sqb (bf16);
 // `store_q`: also to the caller's q buffer; `store_kv`: this CTA reads the new token's position, so it
 // writes the token's K and V rows itself before it gathers them.
@@ -143,8 +171,8 @@ __device__ __forceinline__ void step_rope(const skv_rope &r, int h, bool store_q
 // Bytes of the selection's scratch, which shares the front of the dynamic shared memory with the gather rings.
 __host__ __device__ inline int step_per_max(int C) { return ((C / STEP_CS) + 7) & ~7; }
 __host__ __device__ inline size_t step_sel_bytes(int G, int C, int nw) {
-    return (size_t)step_per_max(C) * 128 + (size_t)G * C * 4 + (size_t)C * 4 + (size_t)step_per_max(C) * 8 +
-           (size_t)step_slices(nw) * 8 * 3 * 4;             // + slice statistics and factors
+    return (size_t)step_per_max(C) * 128 + (size_t)G * step_per_max(C) * 4 + (size_t)C * 4 + (size_t)step_per_max(C) * 8 +
+           (size_t)step_slices(nw) * (8 * 2 + 4) * 4;       // + the slices' statistics (scores, keys)
 }
 __host__ __device__ inline size_t step_front_bytes(int G, int C, int stages, int nw) {
     const size_t ring = (size_t)nw * stages * 8192, sel = (step_sel_bytes(G, C, nw) + 127) & ~size_t(127);
@@ -155,7 +183,7 @@ __host__ __device__ inline size_t step_smem_bytes(int G, int C, int stages, int 
     b += ((size_t)(C / 32 + 1) * 4 + 15) & ~size_t(15);       // selection bits
     b += (size_t)G * HEAD_DIM * 4 + (size_t)G * HEAD_DIM * 2;  // query, float and bf16
     b += (size_t)STEP_CS * G * STEP_PART_LD * 4;               // partials received by the cluster's first CTA
-    b += 512 * 4;                                              // histogram of the pick
+    b += 576 * 4;                                              // histogram and candidates of the pick
     return (b + 127) & ~size_t(127);
 }
 
@@ -180,11 +208,12 @@ __global__ void __launch_bounds__(NW * 32, 2) step_kernel(const StepParams p) {
     // ---- shared memory map ------------------------------------------------------------------------------
     const int per_max = step_per_max(C);
     unsigned char *sumst = smem;                                              // [per_max][128] this CTA's summaries
-    float *zall = reinterpret_cast<float *>(smem + (size_t)per_max * 128);    // [G][C] exp(score - slice max) of every cluster
-    float *cntf = zall + (size_t)G * C;                                       // [C] member counts
+    uint32_t *key = reinterpret_cast<uint32_t *>(smem);                       // [C] keys of all clusters, over sumst once it is scored
+    float *zown = reinterpret_cast<float *>(smem + (size_t)per_max * 128);    // [G][per_max] scaled scores of this CTA's clusters
+    float *cntf = zown + (size_t)G * per_max;                                 // [C] member counts
     float *smx = cntf + C, *smn = smx + per_max;                              // [per_max] key lengths of this CTA's clusters
-    float *stat = smn + per_max;                                              // [32 slices][GP][2] (max, sum of exp)
-    float *fac = stat + STEP_SLICES * GP * 2;                                 // [32 slices][GP] exp(max - M) / T
+    float *stat = smn + per_max;                                              // [slices][GP][2] (max, sum of exp) per query head
+    int *stat2 = reinterpret_cast<int *>(stat + STEP_SLICES * GP * 2);        // [slices][4] smallest / largest key, clusters with members
     unsigned char *tail = smem + step_front_bytes(G, C, STAGES, NW);
     uint32_t *s_bits = reinterpret_cast<uint32_t *>(tail);
     tail += ((size_t)(C / 32 + 1) * 4 + 15) & ~size_t(15);
@@ -301,6 +330,7 @@ __global__ void __launch_bounds__(NW * 32, 2) step_kernel(const StepParams p) {
             n2i += __shfl_xor_sync(0xffffffffu, n2i, 2);                      // |dir8|^2 of cluster cb + nrow
             const int na = __shfl_sync(0xffffffffu, n2i, (2 * jq) * 4);
             const int nb2 = __shfl_sync(0xffffffffu, n2i, (2 * jq + 1) * 4);
+            float zz[2] = {-INFINITY, -INFINITY};
 #pragma unroll
             for (int i = 0; i < 2; ++i) {
                 const int cl = cb + 2 * jq + i;
@@ -309,114 +339,136 @@ __global__ void __launch_bounds__(NW * 32, 2) step_kernel(const StepParams p) {
                     const float pr = (acc[i] + acd[i]) * inv;
                     float e = pr >= 0.f ? smx[cl] * pr : smn[cl] * pr;
                     if (cntf[c_lo + cl] == 0.f) e = -INFINITY;
-                    const float zz = e * p.scale;
-                    zall[nrow * C + c_lo + cl] = zz;                          // read back below by this same thread
-                    w_max = fmaxf(w_max, zz);
+                    zz[i] = e * p.scale;
+                    zown[nrow * per_max + cl] = zz[i];
                 }
             }
+            // running maximum and sum of exp(score - maximum) of the clusters this lane has seen
+            const float mt = fmaxf(w_max, fmaxf(zz[0], zz[1]));
+            if (mt > -INFINITY) {
+                w_sum = w_sum * expf(w_max - mt) + expf(zz[0] - mt) + expf(zz[1] - mt);   // exp(-inf) = 0
+                w_max = mt;
+            }
         }
-        w_max = fmaxf(w_max, __shfl_xor_sync(0xffffffffu, w_max, 1));         // over the four lanes of a query head
-        w_max = fmaxf(w_max, __shfl_xor_sync(0xffffffffu, w_max, 2));
-#pragma unroll 1
-        for (int cb = warp * 8; cb < mine; cb += STEP_WARPS * 8) {
 #pragma unroll
-            for (int i = 0; i < 2; ++i) {
-                const int cl = cb + 2 * jq + i;
-                if (cl < mine && nrow < G) {
-                    const float zz = zall[nrow * C + c_lo + cl];
-                    const float ex = zz > -INFINITY ? expf(zz - w_max) : 0.f;
-                    zall[nrow * C + c_lo + cl] = ex;
-                    w_sum += ex;
-                }
+        for (int o = 1; o <= 2; o <<= 1) {                                    // over the four lanes of a query head
+            const float om = __shfl_xor_sync(0xffffffffu, w_max, o), os = __shfl_xor_sync(0xffffffffu, w_sum, o);
+            const float mt = fmaxf(w_max, om);
+            if (mt > -INFINITY) {
+                w_sum = w_sum * expf(w_max - mt) + os * expf(om - mt);
+                w_max = mt;
             }
         }
-        w_sum += __shfl_xor_sync(0xffffffffu, w_sum, 1);
-        w_sum += __shfl_xor_sync(0xffffffffu, w_sum, 2);
     }
-    __syncthreads();
     step_stamp(p, 2);
     cluster_wait();                                        // barrier 0: every CTA of the cluster is running
     {
-        // this warp's statistics and this CTA's exp values go to all 8 CTAs of the cluster (its own included)
+        // this warp's statistics go to all 8 CTAs of the cluster (its own included): lane r < 8 stores to CTA r
         const int slice = (int)rank * STEP_WARPS + warp;
-        if (jq == 0 && nrow < G) {
-            float *dst = stat + ((size_t)slice * GP + nrow) * 2;
+        const int g_src = lane >> 3;                                          // lanes 8 j .. 8 j + 7 carry query heads 4 k + j
 #pragma unroll
-            for (unsigned r = 0; r < STEP_CS; ++r) {
-                const uint32_t a = remote_addr(dst, r);
-                remote_store(a, w_max);
-                remote_store(a + 4, w_sum);
-            }
-        }
-        if (mine > 0) {
-            const int q4 = (mine + 3) >> 2;
-            for (int i = tid; i < G * q4; i += STEP_THREADS) {
-                const float *src = zall + (i / q4) * C + c_lo + 4 * (i % q4);
-                const float4 v = *reinterpret_cast<const float4 *>(src);
-#pragma unroll
-                for (unsigned dst = 0; dst < STEP_CS; ++dst)
-                    if (dst != rank) remote_store4(remote_addr(src, dst), v);
+        for (int g0 = 0; g0 < GP; g0 += 4) {
+            const int g = g0 + g_src;
+            const float vm = __shfl_sync(0xffffffffu, w_max, (g & 7) * 4), vs = __shfl_sync(0xffffffffu, w_sum, (g & 7) * 4);
+            if (g < G) {
+                const uint32_t a = remote_addr(stat + ((size_t)slice * GP + g) * 2, lane & 7);
+                remote_store(a, vm);
+                remote_store(a + 4, vs);
             }
         }
     }
-    cluster_arrive();                                      // barrier 1: all scores are everywhere
+    for (int i = tid; i < 512; i += STEP_THREADS) hist[i] = 0;               // for the pick's first pass
+    cluster_arrive();                                      // barrier 1: the statistics of all slices are everywhere
     cluster_wait();
     step_stamp(p, 3);
 
-    // ---- every CTA derives the selection for itself ---------------------------------------------------------
+    // ---- shared scores of this CTA's clusters -> keys, to all 8 CTAs --------------------------------------
     {
-        // slice factors exp(max_s - M) / T per query head: lane = slice, warp g (and g + 4) = query head
-        for (int g = warp; g < G; g += STEP_WARPS) {
-            float2 st[SPL];
-            float M = -INFINITY;
+        // softmax over ALL the head's clusters per query head: maximum M and total T from the slices' statistics
+        // (lane = slice); every warp derives them for itself
+        float Mg[GP], iT[GP];
 #pragma unroll
-            for (int k = 0; k < SPL; ++k) {
-                st[k] = *reinterpret_cast<const float2 *>(stat + ((size_t)(lane + 32 * k) * GP + g) * 2);
-                M = fmaxf(M, st[k].x);
+        for (int g = 0; g < GP; ++g) {
+            Mg[g] = 0.f; iT[g] = 0.f;
+            if (g < G) {
+                float2 st[SPL];
+                float M = -INFINITY;
+#pragma unroll
+                for (int k = 0; k < SPL; ++k) {
+                    st[k] = *reinterpret_cast<const float2 *>(stat + ((size_t)(lane + 32 * k) * GP + g) * 2);
+                    M = fmaxf(M, st[k].x);
+                }
+                M = warp_max(M);
+                float T = 0.f;
+#pragma unroll
+                for (int k = 0; k < SPL; ++k) T = fmaf(st[k].x > -INFINITY ? expf(st[k].x - M) : 0.f, st[k].y, T);
+                T = warp_sum(T);
+                Mg[g] = M > -INFINITY ? M : 0.f;
+                iT[g] = T > 0.f ? 1.0f / T : 0.f;
             }
-            M = warp_max(M);
-            float e0[SPL], T = 0.f;
-#pragma unroll
-            for (int k = 0; k < SPL; ++k) {
-                e0[k] = st[k].x > -INFINITY ? expf(st[k].x - M) : 0.f;
-                T = fmaf(e0[k], st[k].y, T);
-            }
-            T = warp_sum(T);
-#pragma unroll
-            for (int k = 0; k < SPL; ++k) fac[(lane + 32 * k) * GP + g] = T > 0.f ? e0[k] / T : 0.f;
         }
-        uint32_t *key = reinterpret_cast<uint32_t *>(smem);                   // [C], over sumst once it is scored
-        // selection bits: the pick writes the words that hold slots in use (nothing selected: cleared here), the
-        // rest are zero, bit C (the always-read rows; C is a multiple of 32: bit 0 of the last word) is set
-        const int words = C / 32 + 1, used = (n_c + 31) >> 5;
-        for (int wd = (active ? used : 0) + tid; wd < words; wd += STEP_THREADS) s_bits[wd] = wd == words - 1 ? 1u : 0u;
-        __syncthreads();
-        step_stamp(p, 8);
+        // four consecutive clusters per thread: sum over the query heads of each head's softmax share
         uint32_t kmin = 0xffffffffu, kmax = 0u;
         int nvalid = 0;
-        if (active) {
-            // cluster c lies in CTA r's stretch [r * per, (r + 1) * per), r = c / per (by a multiplication: exact for
-            // c < 2^16), and was scored by warp ((c - r * per) / 8) % 4 of that CTA
-            const unsigned inv_per = (unsigned)((0x100000000ull + per - 1) / per);
-            for (int c = tid; c < n_c; c += STEP_THREADS) {
-                const int r = (int)__umulhi((unsigned)c, inv_per);
-                const float *f = fac + (r * STEP_WARPS + (((c - r * per) >> 3) & (STEP_WARPS - 1))) * GP;
-                float sc = -INFINITY;
-                const bool live = cntf[c] > 0.f;
-                if (live) {
-                    sc = 0.f;
+        const int c4 = tid * 4;
+        if (c4 < mine) {
+            float sc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-                    for (int g = 0; g < GP; ++g)
-                        if (g < G) sc = fmaf(zall[g * C + c], f[g], sc);
+            for (int g = 0; g < GP; ++g)
+                if (g < G) {
+                    const float4 z = *reinterpret_cast<const float4 *>(zown + g * per_max + c4);
+                    sc[0] = fmaf(expf(z.x - Mg[g]), iT[g], sc[0]);
+                    sc[1] = fmaf(expf(z.y - Mg[g]), iT[g], sc[1]);
+                    sc[2] = fmaf(expf(z.z - Mg[g]), iT[g], sc[2]);
+                    sc[3] = fmaf(expf(z.w - Mg[g]), iT[g], sc[3]);
                 }
-                const uint32_t k = float_key(sc);
-                key[c] = k;
-                if (live) { kmin = min(kmin, k); kmax = max(kmax, k); ++nvalid; }
+            const float4 cn = *reinterpret_cast<const float4 *>(cntf + c_lo + c4);
+            const float cnv[4] = {cn.x, cn.y, cn.z, cn.w};
+            uint32_t kk[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const bool live = c4 + i < mine && cnv[i] > 0.f;
+                kk[i] = float_key(live ? sc[i] : -INFINITY);
+                if (live) { kmin = min(kmin, kk[i]); kmax = max(kmax, kk[i]); ++nvalid; }
             }
+            const float4 kv = make_float4(__uint_as_float(kk[0]), __uint_as_float(kk[1]), __uint_as_float(kk[2]),
+                                          __uint_as_float(kk[3]));
+#pragma unroll
+            for (unsigned dst = 0; dst < STEP_CS; ++dst) remote_store4(remote_addr(key + c_lo + c4, dst), kv);
         }
-        step_stamp(p, 10);
-        pick_by_threshold<STEP_THREADS, float, true>(key, cntf, nullptr, hist, ired, n_c, need, active, kmin, kmax, nvalid,
-                                                     s_bits);
+        kmin = __reduce_min_sync(0xffffffffu, kmin);
+        kmax = __reduce_max_sync(0xffffffffu, kmax);
+        nvalid = __reduce_add_sync(0xffffffffu, nvalid);
+        if (lane < STEP_CS) {
+            const uint32_t a = remote_addr(stat2 + ((int)rank * STEP_WARPS + warp) * 4, lane);
+            asm volatile("st.shared::cluster.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(a), "r"(kmin), "r"(kmax), "r"((uint32_t)nvalid), "r"(0u)
+                         : "memory");
+        }
+    }
+    // selection bits: the pick writes the words that hold slots in use (nothing selected: cleared here), the rest are
+    // zero, bit C (the always-read rows; C is a multiple of 32: bit 0 of the last word) is set
+    {
+        const int words = C / 32 + 1, used = (n_c + 31) >> 5;
+        for (int wd = (active ? used : 0) + tid; wd < words; wd += STEP_THREADS) s_bits[wd] = wd == words - 1 ? 1u : 0u;
+    }
+    cluster_arrive();                                      // barrier 2: the keys of all clusters are everywhere
+    cluster_wait();
+    step_stamp(p, 10);
+
+    // ---- every CTA derives the selection for itself ---------------------------------------------------------
+    {
+        uint32_t kmin = 0xffffffffu, kmax = 0u;
+        int nvalid = 0;
+#pragma unroll
+        for (int k = 0; k < SPL; ++k) {
+            const int4 v = *reinterpret_cast<const int4 *>(stat2 + (lane + 32 * k) * 4);
+            kmin = min(kmin, (uint32_t)v.x); kmax = max(kmax, (uint32_t)v.y); nvalid += v.z;
+        }
+        kmin = __reduce_min_sync(0xffffffffu, kmin);
+        kmax = __reduce_max_sync(0xffffffffu, kmax);
+        nvalid = __reduce_add_sync(0xffffffffu, nvalid);
+        pick_by_threshold<STEP_THREADS, float, true, true>(key, cntf, nullptr, hist, ired, n_c, need, active, kmin, kmax,
+                                                           nvalid, s_bits);
         step_stamp(p, 11);
     }
     __syncthreads();                                       // the selection's scratch is free: the rings take its place
@@ -448,7 +500,7 @@ __global__ void __launch_bounds__(NW * 32, 2) step_kernel(const StepParams p) {
             if (base + step_pass(NW) < p1) raw[j] = __ldg(reinterpret_cast<const uint4 *>(lab + base + step_pass(NW)));
         }
         int total;
-        int off = block_excl_scan(__popc(take), s_scan, total);
+        int off = step_excl_scan<STEP_WARPS>(__popc(take), s_scan, total);
         while (take) {
             const int i = __ffs(take) - 1;
             take &= take - 1;
@@ -492,7 +544,7 @@ __global__ void __launch_bounds__(NW * 32, 2) step_kernel(const StepParams p) {
             remote_store(remote_addr(dst + 130, 0), (float)read_rows);
         }
     }
-    cluster_arrive();                                      // barrier 2: the cluster's partials are in its first CTA
+    cluster_arrive();                                      // barrier 3: the cluster's partials are in its first CTA
     if (split == STEP_CS - 1) {
         // the selection for callers who look at it, written by a CTA that has nothing to merge, while it waits
         const int words = C / 32 + 1;
@@ -592,10 +644,8 @@ __global__ void __launch_bounds__(NW * 32, 2) step_kernel(const StepParams p) {
 using StepKern = void (*)(const StepParams);
 
 // (a ring of three tiles per warp was measured: 35.0 against 35.2 us per layer at 8 heads, not worth 32 KB per CTA)
-// 4 warps with a ring of two tiles each, or 8 warps with one tile each: the same 64 KB of rings, two CTAs per SM
-static int step_stages(int nw) { return nw == 8 ? 1 : STEP_STAGES; }
-static StepKern step_kernel_for(int G, int nw) {
-    if (nw == 8) return G <= 2 ? step_kernel<1, 2, 8> : (G <= 4 ? step_kernel<1, 4, 8> : step_kernel<1, 8, 8>);
+static int step_stages(int) { return STEP_STAGES; }
+static StepKern step_kernel_for(int G, int) {
     return G <= 2 ? step_kernel<STEP_STAGES, 2, 4> : (G <= 4 ? step_kernel<STEP_STAGES, 4, 4> : step_kernel<STEP_STAGES, 8, 4>);
 }
 
@@ -643,13 +693,7 @@ static int step_resident_clusters(int G, int C, int nw) {
     return n;
 }
 
-// Warps per CTA for a launch of `heads` heads: 8 (one CTA per SM) while two clusters per head stay resident, which
-// only the smallest launches allow, else 4 (two CTAs per SM).  SKV_STEP_WARPS=4|8 in the environment forces one.
-static int step_warps_for(int heads, int G, int C) {
-    static const int forced = [] { const char *e = getenv("SKV_STEP_WARPS"); return e ? atoi(e) : 0; }();
-    if (forced == 4 || forced == 8) return forced;
-    return 4;
-}
+static int step_warps_for(int, int, int) { return 4; }
 
 }  // namespace skv
 
