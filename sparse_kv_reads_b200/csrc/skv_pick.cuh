@@ -13,7 +13,7 @@ namespace skv {
 //   sel      BITS false: one byte per cluster, zeroed by the caller for c < n_c
 //   bits     BITS true: the selection as bit c % 32 of word c / 32 instead; every word that holds a slot < n_c is
 //            written (the caller zeroes them when `active` is false)
-//   hist     576 ints of shared scratch, 16-byte aligned; ired 40 ints
+//   hist     608 ints of shared scratch, 16-byte aligned; ired 40 ints
 //   kmin, kmax, nvalid   this THREAD's partial range and count of the keys of clusters with members (the block
 //            reduction happens here); `active` false: nothing is taken (the reductions and barriers still run).
 //            READY true: they are the whole block's values already, and hist is zero on entry (no reduction, and
@@ -42,7 +42,8 @@ __device__ __forceinline__ void pick_by_threshold(const uint32_t *key, const CT 
         // running count passes `need` becomes the new range, until at most 32 candidates are left, which a
         // warp ranks against each other directly.  Scores crowd into a few octaves, so binning the range they
         // span (instead of the keys' top bytes) usually needs a single pass.  Every warp scans the histogram
-        // for itself, and the candidates have words of their own, so the usual course costs three barriers.
+        // for itself, and the candidates have words of their own, so the usual course costs three barriers and
+        // two passes over the keys.
         if (!READY) {
             kmin = 0xffffffffu; kmax = 0u; nvalid = 0;
             for (int w = 0; w < NW; ++w) {
@@ -53,7 +54,7 @@ __device__ __forceinline__ void pick_by_threshold(const uint32_t *key, const CT 
         }
         uint32_t lo = kmin, hi = kmax, tau = 0u;
         int above = 0, cand = nvalid;
-        int *hw = hist, *hn = hist + 256, *cw = hist + 512, *cn = hist + 544;
+        int *hw = hist, *hn = hist + 256, *cw = hist + 512, *cn = hist + 544, *cs = hist + 576;
         int pass = 0;
         for (; pass < 8 && cand > 32 && lo < hi; ++pass) {
             if (!READY || pass > 0) {
@@ -102,96 +103,97 @@ __device__ __forceinline__ void pick_by_threshold(const uint32_t *key, const CT 
             hi = (hi - nlo > span) ? nlo + span : hi;
             lo = nlo;
         }
-        int t = -1;                                   // clusters whose key is the threshold; -1: still to be counted
-        if (nvalid > 0 && lo >= hi) {
-            tau = lo;                                 // one key value left (possibly shared by several clusters)
-        } else if (nvalid > 0) {
-            // at most 32 candidates: list them, then every warp ranks them for itself
+        if (nvalid > 0 && lo < hi) {
+            // At most 32 candidates are left in [lo, hi].  Every cluster above that range is taken, none below it
+            // is, and a candidate is taken while the members ranked before it - larger key, or the same key in a
+            // lower slot - stay under `need` (the one that crosses it is taken).  One pass over the keys marks the
+            // clusters above the range and lists the candidates; every warp ranks them for itself.
             if (READY && pass == 0) __syncthreads();  // the counter's reset, when no pass put a barrier after it
-            for (int c = tid; c < n_c; c += NT) {
-                const uint32_t k = key[c];
-                if (ci[c] > 0 && k >= lo && k <= hi) {
-                    const int j = atomicAdd(&ired[1], 1);
-                    if (j < 32) { cw[j] = (int)k; cn[j] = (int)ci[c]; }
+            if (BITS) {
+                for (int base = wid * 32; base < n_c; base += NT) {   // a warp's 32 slots are one word
+                    const int c = base + lane;
+                    const uint32_t k = c < n_c ? key[c] : 0u;
+                    const unsigned v = __ballot_sync(0xffffffffu, c < n_c && k > hi);
+                    if (lane == 0) bits[base >> 5] = v;
+                    if (c < n_c && k >= lo && k <= hi && ci[c] > 0) {
+                        const int j = atomicAdd(&ired[1], 1);
+                        if (j < 32) { cw[j] = (int)k; cn[j] = (int)ci[c]; cs[j] = c; }
+                    }
+                }
+            } else {
+                for (int c = tid; c < n_c; c += NT) {
+                    const uint32_t k = key[c];
+                    sel[c] = k > hi;
+                    if (k >= lo && k <= hi && ci[c] > 0) {
+                        const int j = atomicAdd(&ired[1], 1);
+                        if (j < 32) { cw[j] = (int)k; cn[j] = (int)ci[c]; cs[j] = c; }
+                    }
                 }
             }
             __syncthreads();
-            const int m = min(ired[1], 32);
-            const uint32_t kl = lane < m ? (uint32_t)cw[lane] : 0u;
-            const int nl = lane < m ? cn[lane] : 0;
-            int greater = 0;                          // members of candidates ranked ahead of this lane's
-            for (int j = 0; j < m; ++j) {
-                const uint32_t kj = __shfl_sync(0xffffffffu, kl, j);
-                const int nj = __shfl_sync(0xffffffffu, nl, j);
-                greater += kj > kl ? nj : 0;
-            }
-            const uint32_t tmin = __reduce_min_sync(0xffffffffu, (lane < m && above + greater < need) ? kl : 0xffffffffu);
-            if (tmin != 0xffffffffu) {
-                // the members ranked ahead of the threshold's candidate are what its lane just counted; every
-                // cluster with the threshold's key is among the candidates
-                tau = tmin;
-                const unsigned at = __ballot_sync(0xffffffffu, lane < m && kl == tmin);
-                above += __shfl_sync(0xffffffffu, greater, __ffs(at) - 1);
-                t = __popc(at);
-            } else {
-                tau = lo;
-                int gt = 0;
+            if (wid == 0) {
+                const int m = min(ired[1], 32);
+                const uint32_t kl = lane < m ? (uint32_t)cw[lane] : 0u;
+                const int nl = lane < m ? cn[lane] : 0, sl = lane < m ? cs[lane] : 0;
+                int before = 0;                       // members of the candidates ranked ahead of this lane's
                 for (int j = 0; j < m; ++j) {
                     const uint32_t kj = __shfl_sync(0xffffffffu, kl, j);
-                    const int nj = __shfl_sync(0xffffffffu, nl, j);
-                    gt += kj > tau ? nj : 0;
+                    const int nj = __shfl_sync(0xffffffffu, nl, j), sj = __shfl_sync(0xffffffffu, sl, j);
+                    before += (kj > kl || (kj == kl && sj < sl)) ? nj : 0;
                 }
-                above += gt;
-            }
-        }
-        int ties = 0;
-        if (BITS) {
-            for (int base = wid * 32; base < n_c; base += NT) {       // a warp's 32 slots are one word
-                const int c = base + lane;
-                const uint32_t k = c < n_c ? key[c] : 0u;
-                const unsigned v = __ballot_sync(0xffffffffu, c < n_c && k >= tau);
-                if (lane == 0) bits[base >> 5] = v;
-                ties += (c < n_c && k == tau);
+                if (lane < m && above + before < need) {
+                    if (BITS) atomicOr(&bits[sl >> 5], 1u << (sl & 31));
+                    else sel[sl] = 1;
+                }
             }
         } else {
-            for (int c = tid; c < n_c; c += NT) {
-                const uint32_t k = key[c];
-                sel[c] = k >= tau;                    // a lone cluster at the threshold is taken: above < need
-                ties += (k == tau);
+            // one key value left, possibly shared by many clusters (or no cluster has members: everything is marked)
+            if (nvalid > 0) tau = lo;
+            int ties = 0;
+            if (BITS) {
+                for (int base = wid * 32; base < n_c; base += NT) {
+                    const int c = base + lane;
+                    const uint32_t k = c < n_c ? key[c] : 0u;
+                    const unsigned v = __ballot_sync(0xffffffffu, c < n_c && k >= tau);
+                    if (lane == 0) bits[base >> 5] = v;
+                    ties += (c < n_c && k == tau);
+                }
+            } else {
+                for (int c = tid; c < n_c; c += NT) {
+                    const uint32_t k = key[c];
+                    sel[c] = k >= tau;                // a lone cluster at the threshold is taken: above < need
+                    ties += (k == tau);
+                }
             }
-        }
-        if (t < 0) {                                  // (the same branch in every thread)
             ties = __reduce_add_sync(0xffffffffu, ties);
             if (lane == 0) ired[32 + wid] = ties;
             __syncthreads();
-            t = 0;
+            int t = 0;
             for (int w = 0; w < NW; ++w) t += ired[32 + w];
-        } else if (t > 1) {
-            __syncthreads();                          // the marks above are complete before the ties are settled
-        }
-        if (t > 1 && wid == 0) {
-            // several clusters share the threshold key: slot order, each taken while the keys ranked before
-            // it stay under need
-            int running = above;
-            for (int base = 0; base < n_c; base += 32) {
-                const int c = base + lane;
-                const bool tie = c < n_c && key[c] == tau;
-                if (!__any_sync(0xffffffffu, tie)) continue;
-                const int mine = tie ? (int)ci[c] : 0;
-                int inc = mine;
+            if (t > 1 && wid == 0) {
+                // several clusters share the threshold key: slot order, each taken while the keys ranked before
+                // it stay under need
+                int running = above;
+                for (int base = 0; base < n_c; base += 32) {
+                    const int c = base + lane;
+                    const bool tie = c < n_c && key[c] == tau;
+                    if (!__any_sync(0xffffffffu, tie)) continue;
+                    const int mine = tie ? (int)ci[c] : 0;
+                    int inc = mine;
 #pragma unroll
-                for (int o = 1; o < 32; o <<= 1) {
-                    const int u = __shfl_up_sync(0xffffffffu, inc, o);
-                    if (lane >= o) inc += u;
+                    for (int o = 1; o < 32; o <<= 1) {
+                        const int u = __shfl_up_sync(0xffffffffu, inc, o);
+                        if (lane >= o) inc += u;
+                    }
+                    const bool keep = (running + inc - mine) < need;
+                    if (BITS) {
+                        const unsigned drop = __ballot_sync(0xffffffffu, tie && !keep);
+                        if (lane == 0 && drop) bits[base >> 5] &= ~drop;
+                    } else if (tie) {
+                        sel[c] = keep;
+                    }
+                    running += __shfl_sync(0xffffffffu, inc, 31);
                 }
-                const bool keep = (running + inc - mine) < need;
-                if (BITS) {
-                    const unsigned drop = __ballot_sync(0xffffffffu, tie && !keep);
-                    if (lane == 0 && drop) bits[base >> 5] &= ~drop;
-                } else if (tie) {
-                    sel[c] = keep;
-                }
-                running += __shfl_sync(0xffffffffu, inc, 31);
             }
         }
         __syncthreads();

@@ -183,7 +183,7 @@ __host__ __device__ inline size_t step_smem_bytes(int G, int C, int stages, int 
     b += ((size_t)(C / 32 + 1) * 4 + 15) & ~size_t(15);       // selection bits
     b += (size_t)G * HEAD_DIM * 4 + (size_t)G * HEAD_DIM * 2;  // query, float and bf16
     b += (size_t)STEP_CS * G * STEP_PART_LD * 4;               // partials received by the cluster's first CTA
-    b += 576 * 4;                                              // histogram and candidates of the pick
+    b += 608 * 4;                                              // histogram and candidates of the pick
     return (b + 127) & ~size_t(127);
 }
 

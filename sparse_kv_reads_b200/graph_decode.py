@@ -139,6 +139,16 @@ class GraphDecoder:
         self.defer_merge = os.environ.get("SKV_DEFER_MERGE", "1") != "0"
         self.fused_insert = fused_insert and mode == "cluster" and window >= 1
         self.insert_all = None
+        # The all-layer insert of a step depends on nothing the step computes (the key that leaves the window was
+        # written `window` steps ago), only on the step's length.  It therefore runs at the END of the step before,
+        # for the length the next step will have, on a second stream beside the vocabulary projection, instead of
+        # ahead of the first layer where nothing can overlap it: between steps the cluster state is one key ahead
+        # of where ssa/kernels/graph_kernels.py:286-325 leaves it (prepare() inserts for the first step), and what
+        # a step selects from is the same.  SKV_INSERT_AHEAD=0: ahead of the first layer, as the reference does.
+        self.insert_ahead = os.environ.get("SKV_INSERT_AHEAD", "1") != "0"
+        self.n_next = torch.zeros(1, dtype=torch.int32, device=dev)
+        self._side = None
+        self._warming = False
 
     def _heads(self, c: torch.Tensor) -> torch.Tensor:
         """Cache ``[B, H_kv, L, d]`` -> ``[B*H_kv, L, d]`` (a view)."""
@@ -162,6 +172,34 @@ class GraphDecoder:
             idx.prepare(K, n, self.B * self.H, fitted=fitted)
         if self.fused_insert:
             self.insert_all = AllLayerInsert(self.attn, [self._heads(k) for k in self.cache.k[:len(self.attn)]])
+            self._insert_for_first_step(n)
+
+    def _insert_for_first_step(self, n: int | None) -> None:
+        """With the insert running at the end of each step for the next one, the first step's insert happens here:
+        for ``n + 1`` positions (``n`` None: one more than each sequence's length in ``n_dev``).  A second call
+        for the same length inserts nothing, the kernel only moves ``end`` forward."""
+        if self.insert_all is None or not self.insert_ahead:
+            return
+        if n is None:
+            torch.add(self.n_dev, 1, out=self.n_next)
+        else:
+            self.n_next.fill_(n + 1)
+        self.insert_all(self.n_next)
+
+    def _finish(self, xn: torch.Tensor) -> torch.Tensor:
+        """Final hidden state -> logits; the next step's all-layer insert runs beside the vocabulary projection."""
+        if self.insert_all is None or not self.insert_ahead or self._warming:
+            return self.model.logits(xn)
+        main = torch.cuda.current_stream()
+        if self._side is None:
+            self._side = torch.cuda.Stream()
+        torch.add(self.pos, 2, out=self.n_next)
+        self._side.wait_stream(main)
+        with torch.cuda.stream(self._side):
+            self.insert_all(self.n_next)
+        out = self.model.logits(xn)
+        main.wait_stream(self._side)
+        return out
 
     def _prepare_ragged(self, lengths: list[int]) -> None:
         if len(lengths) != self.B:
@@ -172,6 +210,7 @@ class GraphDecoder:
         self.ragged = True
         self.pos = torch.tensor(lengths, dtype=torch.long, device=dev)
         self.n_dev = torch.tensor(lengths, dtype=torch.int32, device=dev)
+        self.n_next = torch.zeros_like(self.n_dev)
         for a in self.attn:
             a.n_group = self.H_kv                          # KV heads per sequence share one length
         if self.mode != "cluster":
@@ -182,6 +221,7 @@ class GraphDecoder:
             idx.prepare(K, max(lengths), self.B * self.H, fitted=True, lengths=self.n_dev)
         if self.fused_insert:
             self.insert_all = AllLayerInsert(self.attn, caches)
+            self._insert_for_first_step(None)
 
     # ---- checkpoint / resume -----------------------------------------------------------------------
     def state_dict(self) -> dict:
@@ -207,9 +247,11 @@ class GraphDecoder:
         for a, one in zip(self.attn, sd["layers"]):
             a.load_state_dict(one, dev)
         for i, a in enumerate(self.attn):
-            a.prepare(self._heads(self.cache.k[i]), n, self.B * self.H, fitted=True)
+            # (a state saved between steps may already hold the next step's insert: its own length is one more)
+            a.prepare(self._heads(self.cache.k[i]), max(n, a.n), self.B * self.H, fitted=True)
         if self.fused_insert:
             self.insert_all = AllLayerInsert(self.attn, [self._heads(k) for k in self.cache.k[:len(self.attn)]])
+            self._insert_for_first_step(n)
 
     def _body(self) -> torch.Tensor:
         if self.fused_dense:
@@ -217,7 +259,7 @@ class GraphDecoder:
         assert not self.ragged
         m, H, H_kv, d, B = self.model, self.H, self.H_kv, self.d, self.B
         torch.add(self.pos, 1, out=self.n_dev)
-        if self.insert_all is not None:
+        if self.insert_all is not None and not self.insert_ahead:
             self.insert_all(self.n_dev)
         h = m.embed(self.tok)
         cos = m.rope_cos.index_select(0, self.pos)
@@ -240,7 +282,7 @@ class GraphDecoder:
                                         insert=self.insert_all is None)
             h = h + a.tp.all_reduce(a.o(out.view(B, 1, H * d)))
             h = h + layer.ffn(layer.norm2(h))
-        return m.logits(m.final_norm(h))
+        return self._finish(m.final_norm(h))
 
     def _fuse_weights(self) -> None:
         """Lay q/k/v and gate/up weights of every layer out as one matrix each (the modules keep working:
@@ -275,7 +317,7 @@ class GraphDecoder:
         L = lib()
         st = stream_ptr(self.tok.device)
         torch.add(self.pos, 1, out=self.n_dev)
-        if self.insert_all is not None:
+        if self.insert_all is not None and not self.insert_ahead:
             self.insert_all(self.n_dev)
         h = m.embed(self.tok).view(B, -1).contiguous()
         hidden = h.shape[1]
@@ -307,7 +349,7 @@ class GraphDecoder:
             delta = f.tp.all_reduce(F.linear(act, f.down.weight))
         check(L.skv_add_rmsnorm(h.data_ptr(), delta.data_ptr(), m.final_norm.weight.data_ptr(), xn.data_ptr(), B,
                                 hidden, eps, st), "skv_add_rmsnorm")
-        return m.logits(xn.view(B, 1, hidden))
+        return self._finish(xn.view(B, 1, hidden))
 
     def _layers_gemv(self) -> torch.Tensor:
         """The layers with the library's own matrix-vector products (up to 8 sequences): a layer is seven
@@ -320,7 +362,7 @@ class GraphDecoder:
         L = lib()
         st = stream_ptr(self.tok.device)
         torch.add(self.pos, 1, out=self.n_dev)
-        if self.insert_all is not None:
+        if self.insert_all is not None and not self.insert_ahead:
             self.insert_all(self.n_dev)
         h = m.embed(self.tok).view(B, -1).contiguous()
         hidden = h.shape[1]
@@ -436,7 +478,7 @@ class GraphDecoder:
             delta = red
         check(L.skv_add_rmsnorm(h.data_ptr(), delta.data_ptr(), m.final_norm.weight.data_ptr(), xn.data_ptr(), B,
                                 hidden, eps, st), "skv_add_rmsnorm")
-        return m.logits(xn.view(B, 1, hidden))
+        return self._finish(xn.view(B, 1, hidden))
 
     def _exchange(self):
         """The tensor-parallel group's exchange buffers (made on first use), or None on a single GPU."""
@@ -458,9 +500,13 @@ class GraphDecoder:
             self.pos.fill_(self.cache.cur_len)
         s = torch.cuda.Stream()
         s.wait_stream(torch.cuda.current_stream())
-        with torch.cuda.stream(s), torch.no_grad():
-            for _ in range(2):
-                self._body()
+        self._warming = True                           # (the next step's insert must not run in the warm-up steps)
+        try:
+            with torch.cuda.stream(s), torch.no_grad():
+                for _ in range(2):
+                    self._body()
+        finally:
+            self._warming = False
         torch.cuda.current_stream().wait_stream(s)
         if self.mode == "cluster":                     # the warm-up steps must not have advanced the clusters
             torch.cuda.synchronize()
