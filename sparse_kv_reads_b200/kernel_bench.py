@@ -38,7 +38,7 @@ def synthetic_cache(heads: int, n: int, *, seed: int, device, centres: int = 64)
     return K, V
 
 
-def graph_time(fn, flush, reps: int) -> float:
+def graph_time(fn, flush, reps: int, before=None) -> float:
     s = torch.cuda.Stream()
     s.wait_stream(torch.cuda.current_stream())
     with torch.cuda.stream(s):
@@ -51,6 +51,8 @@ def graph_time(fn, flush, reps: int) -> float:
     out = []
     for _ in range(reps):
         flush.zero_()
+        if before is not None:
+            before()
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record()
         g.replay()
@@ -133,9 +135,10 @@ def main() -> None:
                     r = time_case(ix, K, V, n, b, G, args.reps, peak, flush)
                     rows.append(r)
                     print(json.dumps(r), flush=True)
-            # the insert advances the state, so it is timed last, one real step
+            # the insert advances the state, so it is timed last: the length grows by one ahead of every replay, so
+            # that each timed launch inserts one key per head (the cache holds 80 positions beyond n)
             n_dev = torch.tensor([n + 1], dtype=torch.int32, device=device)
-            t_ins = graph_time(lambda: ix._launch_insert(K, n_dev, ix.budget), flush, 3)
+            t_ins = graph_time(lambda: ix._launch_insert(K, n_dev, ix.budget), flush, 9, before=lambda: n_dev.add_(1))
             print(json.dumps({"heads": heads, "n": n, "insert_us": t_ins * 1e6}), flush=True)
             rows.append({"heads": heads, "n": n, "insert_us": t_ins * 1e6})
             del ix, K, V
