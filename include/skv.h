@@ -408,6 +408,11 @@ int skv_comm_tick(const skv_comm *c, void *stream);
 int skv_gemv_tp(const void *W, int N, int K, void *y, int B, int mode, const void *x, const void *h_in,
                 const void *norm_w, void *h_out, float eps, const skv_comm *in, int in_seq,
                 const skv_comm *out, int out_seq, void *stream);
+/* The write side for producers other than skv_gemv (a library GEMM at batches beyond 8): this rank's partial sums
+ * y[B, N] (bf16) go into its place in every GPU's buffer as exchange `seq`; skv_comm_reduce on every GPU then gives
+ * the sum, the same bits everywhere.  The pair stands where a tensor-parallel host would call an all-reduce (the
+ * reference decodes on one GPU). */
+int skv_comm_push(const skv_comm *c, int seq, const void *y, int B, int N, void *stream);
 /* delta[B, N] (bf16) = sum over ranks of exchange `seq`, after the same wait: for consumers other than skv_gemv. */
 int skv_comm_reduce(const skv_comm *c, int seq, void *delta, int B, int N, void *stream);
 /* The buffer's status word (SKV_ST_WAIT_TIMEOUT), read back with a synchronising copy; negative on error. */

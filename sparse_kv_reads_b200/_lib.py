@@ -21,7 +21,7 @@ EXPORTS = ("skv_version", "skv_error_string", "skv_last_cuda_error", "skv_attend
            "skv_attend_workspace_bytes", "skv_attend", "skv_attend_static", "skv_attend_weighted", "skv_attend_labels", "skv_step", "skv_step_clusters", "skv_step_workspace_bytes", "skv_debug_step_probe", "skv_merge", "skv_select_workspace_bytes", "skv_select", "skv_debug_select_probe", "skv_debug_attend_probe", "skv_set_overlap", "skv_insert",
            "skv_insert_max_members", "skv_fit_tensor_cores", "skv_fit_workspace_bytes", "skv_fit", "skv_rebin",
            "skv_add_rmsnorm", "skv_qk_rope_cache", "skv_silu_mul", "skv_gemv", "skv_gemv_attended", "skv_gemv_supported", "skv_gemv_tp", "skv_comm_bytes", "skv_comm_alloc",
-           "skv_comm_export", "skv_comm_open", "skv_comm_close", "skv_comm_free", "skv_comm_view", "skv_comm_tick", "skv_comm_reduce", "skv_comm_status")
+           "skv_comm_export", "skv_comm_open", "skv_comm_close", "skv_comm_free", "skv_comm_view", "skv_comm_tick", "skv_comm_push", "skv_comm_reduce", "skv_comm_status")
 
 
 class SkvError(RuntimeError):
@@ -140,6 +140,8 @@ def _declare(lib) -> None:
     lib.skv_comm_status.argtypes = [C.POINTER(SkvComm)]
     lib.skv_comm_reduce.restype = i32
     lib.skv_comm_reduce.argtypes = [C.POINTER(SkvComm), i32, vp, i32, i32, vp]
+    lib.skv_comm_push.restype = i32
+    lib.skv_comm_push.argtypes = [C.POINTER(SkvComm), i32, vp, i32, i32, vp]
     lib.skv_gemv_attended.restype = i32
     lib.skv_gemv_attended.argtypes = [vp, i32, i32, vp, i32, vp, i32, i32, vp, C.POINTER(SkvComm), i32, vp]
     lib.skv_gemv_supported.restype = i32
@@ -166,7 +168,7 @@ def lib():
 # entry points that launch exactly one kernel each: counted, so that a caller can tell how many of the library's
 # kernels a captured decode step holds (GraphDecoder.launches_per_step)
 _ONE_LAUNCH = {"skv_insert", "skv_select", "skv_attend", "skv_attend_weighted", "skv_attend_labels", "skv_step", "skv_gemv", "skv_gemv_tp", "skv_gemv_attended",
-               "skv_add_rmsnorm", "skv_qk_rope_cache", "skv_silu_mul", "skv_comm_reduce", "skv_comm_tick"}
+               "skv_add_rmsnorm", "skv_qk_rope_cache", "skv_silu_mul", "skv_comm_push", "skv_comm_reduce", "skv_comm_tick"}
 launches = 0
 
 

@@ -398,6 +398,36 @@ __global__ void __launch_bounds__(GEMV_THREADS) gemv_kernel(const GemvParams p) 
     }
 }
 
+// The write side of an exchange for producers that are not a product of this file (a library GEMM at batches beyond
+// 8): this rank's partial sums y[total] (bf16) go, as float values paired with the epoch, into its place in every
+// GPU's buffer - two pairs per 16-byte store, each 64-bit pair single-copy atomic.
+struct PushTargets {
+    uint2 *data[8];
+};
+__global__ void __launch_bounds__(256) comm_push_kernel(const __nv_bfloat16 *y, int total, PushTargets out,
+                                                        const uint32_t *tick, int world, int rank, int seq, int cap) {
+    pdl_wait();
+    pdl_trigger();
+    const uint32_t epoch = epoch_of(tick, seq);
+    const size_t base = (size_t)((seq & 1) * world + rank) * cap;
+    for (int v = blockIdx.x * 256 + threadIdx.x; v < total / 8; v += gridDim.x * 256) {
+        float f[8];
+        load8(y + (size_t)v * 8, f);
+        unsigned long long w[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) w[i] = (unsigned long long)__float_as_uint(f[i]) | ((unsigned long long)epoch << 32);
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {
+            if (r >= world) break;
+            uint2 *dst = out.data[r] + base + (size_t)v * 8;
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+                asm volatile("st.relaxed.sys.global.v2.b64 [%0], {%1, %2};" ::"l"(dst + 2 * i), "l"(w[2 * i]), "l"(w[2 * i + 1])
+                             : "memory");
+        }
+    }
+}
+
 // delta[B, N] = sum over ranks of an exchange's partials, for consumers that are not a product of this file and
 // for groups whose partials are too many for every CTA of the consuming product to add up for itself.  Eight
 // lanes share a run of eight elements, one rank each, so that all ranks are polled at once; their values meet
@@ -678,10 +708,26 @@ extern "C" int skv_comm_reduce(const skv_comm *c, int seq, void *delta, int B, i
     if (seq < 0 || seq > 254 || B < 1 || N < 8 || N % 8 || (int64_t)B * N > c->cap_elems) return SKV_E_RANGE;
     if (!aligned16(delta)) return SKV_E_ALIGN;
     const int total = B * N, blocks = (total + 255) / 256;          // eight lanes per run of eight elements
-    SKV_CUDA_OK(launch_pdl(comm_reduce_kernel, dim3(blocks > 64 ? 64 : blocks), dim3(256), 0,
+    const int cap_blocks = 2 * device_sm_count();
+    SKV_CUDA_OK(launch_pdl(comm_reduce_kernel, dim3(blocks > cap_blocks ? cap_blocks : blocks), dim3(256), 0,
                            static_cast<cudaStream_t>(stream), static_cast<const uint2 *>(c->data[c->rank]),
                            (const uint32_t *)c->tick, c->world, seq, c->cap_elems, c->status, wait_polls(c),
                            static_cast<__nv_bfloat16 *>(delta), total));
+    return SKV_OK;
+}
+
+extern "C" int skv_comm_push(const skv_comm *c, int seq, const void *y, int B, int N, void *stream) {
+    if (!c || !y) return SKV_E_NULL;
+    const int rc = check_comm(c);
+    if (rc) return rc;
+    if (seq < 0 || seq > 254 || B < 1 || N < 8 || N % 8 || (int64_t)B * N > c->cap_elems) return SKV_E_RANGE;
+    if (!aligned16(y)) return SKV_E_ALIGN;
+    PushTargets out = {};
+    for (int r = 0; r < c->world; ++r) out.data[r] = static_cast<uint2 *>(c->data[r]);
+    const int total = B * N, blocks = (total / 8 + 255) / 256, cap_blocks = 2 * device_sm_count();
+    SKV_CUDA_OK(launch_pdl(comm_push_kernel, dim3(blocks > cap_blocks ? cap_blocks : blocks), dim3(256), 0,
+                           static_cast<cudaStream_t>(stream), static_cast<const __nv_bfloat16 *>(y), total, out,
+                           (const uint32_t *)c->tick, c->world, c->rank, seq, c->cap_elems));
     return SKV_OK;
 }
 

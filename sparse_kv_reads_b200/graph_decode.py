@@ -135,6 +135,12 @@ class GraphDecoder:
         # up to this many bytes of partial sums every CTA of the consuming product adds up for itself; beyond it one
         # reduce launch does (4 GPUs x 4 sequences, 128 KB: 2,096 tok/s with the launch, 1,955 without)
         self.fuse_sum_bytes = 65536
+        # beyond 8 sequences the products are library GEMMs; their partial results go through the exchange buffers
+        # (skv_comm_push + skv_comm_reduce) while every GPU receives at most this many bytes per sum, else through the
+        # group's all-reduce: every rank writes to every GPU, 8 bytes per value, so the traffic grows with the group
+        # (measured, 32 sequences of a 2,560-wide model: 2 GPUs, 1.3 MB: 4,417 against 4,333 tok/s with NCCL;
+        # 8 GPUs, 5.2 MB: 5,661 against 6,321)
+        self.push_sum_bytes = 1_500_000
         # the attention's last log-sum-exp merge rides in the output product (SKV_DEFER_MERGE=0: in the attention launch)
         self.defer_merge = os.environ.get("SKV_DEFER_MERGE", "1") != "0"
         self.fused_insert = fused_insert and mode == "cluster" and window >= 1
@@ -325,6 +331,24 @@ class GraphDecoder:
         delta = None
         xn = torch.empty_like(h)
         qh = torch.empty(B * H, d, dtype=h.dtype, device=h.device)
+        world = m.layers[0].attn.tp.size
+        peer = None
+        if world > 1 and hidden % 8 == 0 and 2 * len(m.layers) <= 254 and world * B * hidden * 8 <= self.push_sum_bytes:
+            peer = self._exchange()
+        if peer is not None:
+            peer.tick(st)                                  # stamps this step's exchanges
+
+        def summed(y: torch.Tensor, tp, seq: int) -> torch.Tensor:
+            """Sum of the ranks' partial results ``y [B, hidden]``: through the peer-memory exchange - every rank
+            stores its values into every GPU's buffer, then adds the ranks' values up for itself, in rank order -
+            or, on one GPU or with the exchange switched off, the group's all-reduce."""
+            if peer is None:
+                return tp.all_reduce(y)
+            check(L.skv_comm_push(peer.ref(), seq, y.data_ptr(), B, hidden, st), "skv_comm_push")
+            red = torch.empty_like(y)
+            check(L.skv_comm_reduce(peer.ref(), seq, red.data_ptr(), B, hidden, st), "skv_comm_reduce")
+            return red
+
         for i, layer in enumerate(m.layers):
             a, f = layer.attn, layer.ffn
             check(L.skv_add_rmsnorm(h.data_ptr(), None if delta is None else delta.data_ptr(),
@@ -340,13 +364,13 @@ class GraphDecoder:
             else:
                 out = self.attn[i].step(qh, self._heads(kc), self._heads(vc), self.n_dev,
                                         insert=self.insert_all is None)
-            o = a.tp.all_reduce(F.linear(out.view(B, H * d), a.o.weight))
+            o = summed(F.linear(out.view(B, H * d), a.o.weight), a.tp, 2 * i)
             check(L.skv_add_rmsnorm(h.data_ptr(), o.data_ptr(), layer.norm2.weight.data_ptr(), xn.data_ptr(), B,
                                     hidden, eps, st), "skv_add_rmsnorm")
             gu = F.linear(xn, self._wgu[i])
             act = torch.empty(B, gu.shape[1] // 2, dtype=gu.dtype, device=gu.device)
             check(L.skv_silu_mul(gu.data_ptr(), act.data_ptr(), B, act.shape[1], st), "skv_silu_mul")
-            delta = f.tp.all_reduce(F.linear(act, f.down.weight))
+            delta = summed(F.linear(act, f.down.weight), f.tp, 2 * i + 1)
         check(L.skv_add_rmsnorm(h.data_ptr(), delta.data_ptr(), m.final_norm.weight.data_ptr(), xn.data_ptr(), B,
                                 hidden, eps, st), "skv_add_rmsnorm")
         return self._finish(xn.view(B, 1, hidden))

@@ -223,6 +223,10 @@ def test_matrix_vector_product_and_exchange_reject_bad_arguments(L):
     assert tp(cout=ctypes.byref(c), out_seq=255) == -5 and tp(mode=3, cin=ctypes.byref(c), in_seq=-1, y=ok) == -5
     assert L.skv_comm_reduce(None, 0, ok, 1, 128, None) == -1
     assert L.skv_comm_reduce(ctypes.byref(c), 0, ok, 1, 12, None) == -5
+    assert L.skv_comm_push(None, 0, ok, 1, 128, None) == -1 and L.skv_comm_push(ctypes.byref(c), 0, None, 1, 128, None) == -1
+    assert L.skv_comm_push(ctypes.byref(c), 0, ok, 1, 12, None) == -5 and L.skv_comm_push(ctypes.byref(c), 255, ok, 1, 128, None) == -5
+    assert L.skv_comm_push(ctypes.byref(c), 0, ok, 9, 128, None) == -5        # more than the buffers hold
+    assert L.skv_comm_push(ctypes.byref(c), 0, 0x1004, 1, 128, None) == -4
     assert L.skv_comm_tick(None, None) == -1
 
 

@@ -118,6 +118,37 @@ def _rms(x, g, eps=1e-6):
     return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps) * g.float()).to(torch.bfloat16)
 
 
+@pytest.mark.parametrize("world,B,N", [(2, 12, 256), (4, 32, 2560), (8, 3, 64)])
+def test_partial_sums_pushed_into_every_buffer_add_up_to_the_same_bits(world, B, N):
+    """The exchange for producers that are not this library's products (batches beyond 8): every emulated rank pushes
+    its partial results, every rank then reads the same sum; several steps, both slots."""
+    from sparse_kv_reads_b200.peer_reduce import PeerExchange
+    L = lib()
+    g = torch.Generator().manual_seed(7 * world + B)
+    ex = PeerExchange.emulated(world, B * N, DEV)
+    for use in range(5):
+        for e in ex:
+            e.tick(stream())
+        parts = [torch.randn(B, N, generator=g).to(torch.bfloat16).to(DEV) for _ in range(world)]
+        for r in range(world):
+            check(L.skv_comm_push(ex[r].ref(), use, parts[r].data_ptr(), B, N, stream()), "skv_comm_push")
+        want = torch.stack([x.float() for x in parts]).sum(0)
+        got = []
+        for r in range(world):
+            delta = torch.empty(B, N, dtype=torch.bfloat16, device=DEV)
+            check(L.skv_comm_reduce(ex[r].ref(), use, delta.data_ptr(), B, N, stream()), "skv_comm_reduce")
+            got.append(delta)
+        torch.testing.assert_close(got[0].float(), want, rtol=1e-2, atol=2e-2)
+        assert all(torch.equal(got[0], x) for x in got[1:])
+    assert all(e.status() == 0 for e in ex)
+    y = torch.zeros(B, N, dtype=torch.bfloat16, device=DEV)
+    assert L.skv_comm_push(ex[0].ref(), 255, y.data_ptr(), B, N, stream()) == -5       # exchange numbers end at 254
+    assert L.skv_comm_push(ex[0].ref(), 0, y.data_ptr(), B + 1, N, stream()) == -5     # more than the buffers hold
+    assert L.skv_comm_push(ex[0].ref(), 0, None, B, N, stream()) == -1
+    for e in ex:
+        e.close()
+
+
 @pytest.mark.parametrize("B", [1, 4])
 def test_row_parallel_product_summed_through_exchange_buffers(B):
     """Two ranks emulated on one device (their kernels run one after the other): each multiplies its half of

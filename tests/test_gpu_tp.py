@@ -16,7 +16,7 @@ TINY = dict(vocab_size=1000, hidden_size=256, intermediate_size=512, num_hidden_
             num_key_value_heads=4, head_dim=128, max_position_embeddings=4096)
 
 
-def _rank_main(rank: int, world: int, port: int, out_path: str) -> None:
+def _rank_main(rank: int, world: int, port: int, out_path: str, batch: int) -> None:
     import torch.distributed as dist
     from sparse_kv_reads_b200 import GraphDecoder, Qwen3Config, Qwen3Model
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
@@ -24,14 +24,14 @@ def _rank_main(rank: int, world: int, port: int, out_path: str) -> None:
     torch.cuda.set_device(dev)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
     P, T = 300, 24
-    ids = torch.randint(0, 1000, (2, P + T + 1), generator=torch.Generator().manual_seed(3)).to(dev)
+    ids = torch.randint(0, 1000, (batch, P + T + 1), generator=torch.Generator().manual_seed(3)).to(dev)
 
     def run(peer: bool):
         os.environ["SKV_PEER_REDUCE"] = "1" if peer else "0"
         with torch.device(dev):
             model = Qwen3Model(Qwen3Config(**TINY), tp_group=dist.group.WORLD, tp_size=world, tp_rank=rank)
         model = model.to(torch.bfloat16).eval().init_random(seed=5, std=0.05)
-        cache = model.alloc_cache(336, max_batch=2)
+        cache = model.alloc_cache(336, max_batch=batch)
         with torch.no_grad():
             model.prefill(ids[:, :P], cache, chunk=128)
             dec = GraphDecoder(model, cache, mode="cluster", budget=1.0, C=64, C_init=16, split_factor=2.0, window=4,
@@ -56,15 +56,18 @@ def _rank_main(rank: int, world: int, port: int, out_path: str) -> None:
     os._exit(0)                                   # captured graphs hold NCCL work: leave without the teardown
 
 
+# two sequences run the library's own products with the sums inside them; twelve run library GEMMs with the
+# partial results pushed into the exchange buffers and added up by a reduce launch
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_peer_memory_sums_match_nccl_all_reduce(tmp_path):
+@pytest.mark.parametrize("batch", [2, 12])
+def test_peer_memory_sums_match_nccl_all_reduce(tmp_path, batch):
     import torch.multiprocessing as mp
     out_path = str(tmp_path / "tp.pt")
     ctx = mp.get_context("spawn")
     with socket.socket() as sock:                 # a port nobody holds right now
         sock.bind(("127.0.0.1", 0))
         port = sock.getsockname()[1]
-    procs = [ctx.Process(target=_rank_main, args=(r, 2, port, out_path)) for r in range(2)]
+    procs = [ctx.Process(target=_rank_main, args=(r, 2, port, out_path, batch)) for r in range(2)]
     for p in procs:
         p.start()
     for p in procs:
