@@ -82,7 +82,7 @@ class GraphDecoder:
                  C_init: int | None = None, split_factor: float | None = None, refit_every: int = 0,
                  grow_cap: bool = False, reset_at: int = 0, summary_bits: int = 8, cap_keys: float = 0.0,
                  fused_insert: bool = True, var_factor: float = 0.0, var_min: int = 8, fused_dense: bool = True,
-                 own_gemv: bool = True, **_):
+                 own_gemv: bool = True, insert_ahead: bool | None = None, **_):
         cfg = model.cfg
         # no slot count given: 1,024 slots, 256 fitted at the prompt, split over twice the mean size
         # (ssa/models/graph_decode.py:38-43)
@@ -150,8 +150,9 @@ class GraphDecoder:
         # for the length the next step will have, on a second stream beside the vocabulary projection, instead of
         # ahead of the first layer where nothing can overlap it: between steps the cluster state is one key ahead
         # of where ssa/kernels/graph_kernels.py:286-325 leaves it (prepare() inserts for the first step), and what
-        # a step selects from is the same.  SKV_INSERT_AHEAD=0: ahead of the first layer, as the reference does.
-        self.insert_ahead = os.environ.get("SKV_INSERT_AHEAD", "1") != "0"
+        # a step selects from is the same.  ``insert_ahead=False`` (or SKV_INSERT_AHEAD=0): ahead of the first layer, as
+        # the reference does.
+        self.insert_ahead = (os.environ.get("SKV_INSERT_AHEAD", "1") != "0") if insert_ahead is None else bool(insert_ahead)
         self.n_next = torch.zeros(1, dtype=torch.int32, device=dev)
         self._side = None
         self._warming = False

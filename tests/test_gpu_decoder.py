@@ -68,6 +68,25 @@ def run_decoder(model, ids, P, T, capture, **kw):
     return torch.stack(out, 1), dec
 
 
+@pytest.mark.parametrize("batch", [1, 3])
+def test_insert_at_the_end_of_the_step_before_gives_the_same_decode(batch):
+    """The all-layer insert of a step runs at the end of the step before it, beside the vocabulary projection; ahead
+    of the first layer (the reference's order) every step selects from the same state, so the logits are the same
+    bits - with splits happening and at a budget where the selection matters."""
+    model = tiny_model(seed=23)
+    P, T = 280, 60
+    ids = torch.randint(0, 1000, (batch, P + T + 1), generator=torch.Generator().manual_seed(17)).to(DEV)
+    kw = dict(mode="cluster", budget=0.3, C=64, C_init=16, cap_keys=24.0, window=8, delta=float("inf"), summary_bits=8)
+    ahead, d1 = run_decoder(model, ids, P, T, True, insert_ahead=True, **kw)
+    first, d0 = run_decoder(model, ids, P, T, True, insert_ahead=False, **kw)
+    assert d1.insert_ahead and not d0.insert_ahead and d1.insert_all is not None
+    assert torch.equal(ahead, first)
+    assert sum(i.splits for i in d1.attn) > 0
+    for a, b in zip(d1.attn, d0.attn):
+        assert [x - 1 for x in a.end_dev.cpu().tolist()] == b.end_dev.cpu().tolist()     # one key ahead between steps
+        assert a.check_status() == 0 and b.check_status() == 0
+
+
 def test_budget_one_equals_dense_and_graph_equals_eager():
     model = tiny_model()
     P, T = 300, 80
