@@ -34,6 +34,7 @@ struct GemvParams {
     const __nv_bfloat16 *W;
     __nv_bfloat16 *y;
     int N, K, B, mode, rows_per_cta;
+    int row_group;                 // float path: rows a warp takes at a time (1 or 2)
     int nslabs, stages;            // slabs of rows_per_cta rows over the matrix; 1 or 2 slab buffers per CTA
     const __nv_bfloat16 *x;        // mode 0: [B, K]; mode 2: gate_up [B, 2K]
     const __nv_bfloat16 *h_in, *delta, *g;
@@ -110,6 +111,46 @@ __device__ __forceinline__ void emit(const GemvParams &p, int b, int row, float 
 #pragma unroll
     for (int r = 0; r < 8; ++r)
         if (r < p.out_world) store_pair(p.out_data[r] + off, v, epoch);
+}
+
+// The float path of a slab: a warp takes NR rows at a time, so that the input is read and unpacked once for all of
+// them and their sums are independent chains (each row's sum is added up in the same order as it would be alone).
+template <int BP, int NR>
+__device__ __forceinline__ void rows_dot(const GemvParams &p, const __nv_bfloat16 *ws, const __nv_bfloat16 *xs, int R,
+                                         int r0, int K, int kv, uint32_t out_epoch) {
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    for (int r = wid * NR; r < R; r += GEMV_WARPS * NR) {
+        float acc[NR][BP];
+        const __nv_bfloat16 *wr[NR];
+#pragma unroll
+        for (int j = 0; j < NR; ++j) {
+            wr[j] = ws + (size_t)min(r + j, R - 1) * K;   // rows past the slab repeat its last row; their sums are dropped
+#pragma unroll
+            for (int b = 0; b < BP; ++b) acc[j][b] = 0.f;
+        }
+#pragma unroll 2
+        for (int v = lane; v < kv; v += 32) {
+            float w[NR][8];
+#pragma unroll
+            for (int j = 0; j < NR; ++j) load8(wr[j] + v * 8, w[j]);
+#pragma unroll
+            for (int b = 0; b < BP; ++b) {
+                float xv[8];
+                load8(xs + (size_t)b * K + v * 8, xv);
+#pragma unroll
+                for (int i = 0; i < 8; ++i)
+#pragma unroll
+                    for (int j = 0; j < NR; ++j) acc[j][b] = fmaf(w[j][i], xv[i], acc[j][b]);
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < NR; ++j)
+#pragma unroll
+            for (int b = 0; b < BP; ++b) {
+                const float sum = warp_sum(acc[j][b]);
+                if (lane == 0 && b < p.B && r + j < R) emit(p, b, r0 + r + j, sum, out_epoch);
+            }
+    }
 }
 
 // MULTI: the CTA walks over several slabs with two buffers (else exactly one slab, and no loop to pay for)
@@ -371,29 +412,8 @@ __global__ void __launch_bounds__(GEMV_THREADS) gemv_kernel(const GemvParams p) 
             }
         }
     } else
-    for (int r = wid; r < R; r += GEMV_WARPS) {
-        float acc[BP];
-#pragma unroll
-        for (int b = 0; b < BP; ++b) acc[b] = 0.f;
-        const __nv_bfloat16 *wr = ws + (size_t)r * K;
-#pragma unroll 2
-        for (int v = lane; v < kv; v += 32) {
-            float w[8];
-            load8(wr + v * 8, w);
-#pragma unroll
-            for (int b = 0; b < BP; ++b) {
-                float xv[8];
-                load8(xs + (size_t)b * K + v * 8, xv);
-#pragma unroll
-                for (int i = 0; i < 8; ++i) acc[b] = fmaf(w[i], xv[i], acc[b]);
-            }
-        }
-#pragma unroll
-        for (int b = 0; b < BP; ++b) {
-            const float s = warp_sum(acc[b]);
-            if (lane == 0 && b < p.B) emit(p, b, r0 + r, s, out_epoch);
-        }
-    }
+    if (p.row_group == 2) rows_dot<BP, 2>(p, ws, xs, R, r0, K, kv, out_epoch);
+    else rows_dot<BP, 1>(p, ws, xs, R, r0, K, kv, out_epoch);
     if (MULTI) __syncthreads();                             // this buffer and s_red are free for the slab after next
     }
 }
@@ -588,6 +608,17 @@ static int gemv_launch(const void *W, int N, int K, void *y, int B, int mode, co
     GemvParams p = {};
     p.W = static_cast<const __nv_bfloat16 *>(W); p.y = static_cast<__nv_bfloat16 *>(y);
     p.N = N; p.K = K; p.B = B; p.mode = mode; p.rows_per_cta = rows; p.nslabs = pl.nslabs; p.stages = pl.stages;
+    {
+        // rows per warp and pass: two where that leaves the busiest warp no more rows than one at a time does (a single
+        // sequence only).  Measured in the decode step at batch 1: pairs 727-731 tok/s, one row 714, groups of up to
+        // four 720.
+        int best = 1, best_rows = (rows + GEMV_WARPS - 1) / GEMV_WARPS;
+        for (int g = 2; g <= 2 && BP == 1; ++g) {
+            const int groups = (rows + g - 1) / g, most = (groups + GEMV_WARPS - 1) / GEMV_WARPS * g;
+            if (most <= best_rows) { best = g; best_rows = most; }
+        }
+        p.row_group = best;
+    }
     p.x = static_cast<const __nv_bfloat16 *>(x); p.h_in = static_cast<const __nv_bfloat16 *>(h_in);
     p.delta = static_cast<const __nv_bfloat16 *>(delta); p.g = static_cast<const __nv_bfloat16 *>(norm_w);
     p.h_out = static_cast<__nv_bfloat16 *>(h_out); p.eps = eps;
