@@ -146,6 +146,7 @@ template <typename TQ, int GP>
 __global__ void __launch_bounds__(SEL_THREADS) score_pick_kernel(const SelectParams p) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __shared__ int s_last;
+    __shared__ float s_stat[32];                                    // a lone CTA's own statistics: [G][2]
     const int C = p.st.C, G = p.G, d = HEAD_DIM;
     const int h = blockIdx.y, b = blockIdx.x, nb = gridDim.x;
     const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
@@ -397,8 +398,13 @@ __global__ void __launch_bounds__(SEL_THREADS) score_pick_kernel(const SelectPar
 #pragma unroll
             for (int g = 0; g < GP; ++g)
                 if (g < G) {
-                    __stcg(ps + (b * 16 + g) * 2, zm[g]);
-                    __stcg(ps + (b * 16 + g) * 2 + 1, tot[g]);
+                    if (nb > 1) {
+                        __stcg(ps + (b * 16 + g) * 2, zm[g]);
+                        __stcg(ps + (b * 16 + g) * 2 + 1, tot[g]);
+                    } else {                               // one CTA per head: nothing goes through global memory
+                        s_stat[2 * g] = zm[g];
+                        s_stat[2 * g + 1] = tot[g];
+                    }
                 }
         if (b == 0) stamp(p, h, 1);
         if (nb > 1) {
@@ -421,8 +427,12 @@ __global__ void __launch_bounds__(SEL_THREADS) score_pick_kernel(const SelectPar
     float2 s0 = make_float2(-INFINITY, 0.f), s1 = s0;
     const bool stat_warp = scoring && wid < G;               // one warp per query head; G <= 16 > SEL_WARPS loops below
     if (stat_warp) {
-        if (lane < nb) s0 = __ldcg(reinterpret_cast<const float2 *>(ps + (lane * 16 + wid) * 2));
-        if (lane + 32 < nb) s1 = __ldcg(reinterpret_cast<const float2 *>(ps + ((lane + 32) * 16 + wid) * 2));
+        if (nb == 1) {
+            if (lane == 0) s0 = make_float2(s_stat[2 * wid], s_stat[2 * wid + 1]);
+        } else {
+            if (lane < nb) s0 = __ldcg(reinterpret_cast<const float2 *>(ps + (lane * 16 + wid) * 2));
+            if (lane + 32 < nb) s1 = __ldcg(reinterpret_cast<const float2 *>(ps + ((lane + 32) * 16 + wid) * 2));
+        }
     }
     if (scoring && nb > 1)
         for (int g = 0; g < G; ++g)
@@ -439,7 +449,7 @@ __global__ void __launch_bounds__(SEL_THREADS) score_pick_kernel(const SelectPar
                     if (cc < n_c) z[g * C + cc] = v[j];
                 }
             }
-    for (int c = tid; c < C; c += 4 * SEL_THREADS) {
+    for (int c = tid; c < n_c; c += 4 * SEL_THREADS) {    // (only the slots in use are looked at below)
         float v[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
@@ -449,20 +459,26 @@ __global__ void __launch_bounds__(SEL_THREADS) score_pick_kernel(const SelectPar
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const int cc = c + j * SEL_THREADS;
-            if (cc < C) { ci[cc] = (int)v[j]; sel[cc] = 0; }
+            if (cc < n_c) ci[cc] = (int)v[j];
         }
     }
-    if (tid == 0) {
-        sel[C] = 1;
-        if (!p.idx) p.cnt[h] = 0;                     // the attention kernel adds the rows it reads
-    }
+    // the selection as bits: the pick writes the words that hold slots in use (nothing selected: cleared here), the
+    // rest are zero; bit C (the always-read rows) is added on the way out (C need not be a multiple of 32 here)
+    uint32_t *sbits = reinterpret_cast<uint32_t *>(sel);
+    const int words = C / 32 + 1;
+    for (int wd = (active ? (n_c + 31) >> 5 : 0) + tid; wd < words; wd += SEL_THREADS) sbits[wd] = 0u;
+    if (tid == 0 && !p.idx) p.cnt[h] = 0;             // the attention kernel adds the rows it reads
     if (scoring) {
         // slice factors exp(max_b - max) / total per query head
         for (int g = wid; g < G; g += SEL_WARPS) {     // a lane holds up to two slices
             if (g != wid) {                            // more query heads than warps: the later ones load here
                 s0 = s1 = make_float2(-INFINITY, 0.f);
-                if (lane < nb) s0 = __ldcg(reinterpret_cast<const float2 *>(ps + (lane * 16 + g) * 2));
-                if (lane + 32 < nb) s1 = __ldcg(reinterpret_cast<const float2 *>(ps + ((lane + 32) * 16 + g) * 2));
+                if (nb == 1) {
+                    if (lane == 0) s0 = make_float2(s_stat[2 * g], s_stat[2 * g + 1]);
+                } else {
+                    if (lane < nb) s0 = __ldcg(reinterpret_cast<const float2 *>(ps + (lane * 16 + g) * 2));
+                    if (lane + 32 < nb) s1 = __ldcg(reinterpret_cast<const float2 *>(ps + ((lane + 32) * 16 + g) * 2));
+                }
             }
             const float m = warp_max(fmaxf(s0.x, s1.x));
             if (p.group != SKV_GROUP_SUM_SHARE) {          // only the head's best score is needed (max_rel)
@@ -510,18 +526,13 @@ __global__ void __launch_bounds__(SEL_THREADS) score_pick_kernel(const SelectPar
         }
     }
     stamp(p, h, 4);
-    pick_by_threshold<SEL_THREADS, int>(key, ci, sel, hist, ired, n_c, need, active, kmin, kmax, nvalid);
+    pick_by_threshold<SEL_THREADS, int, true>(key, ci, nullptr, hist, ired, n_c, need, active, kmin, kmax, nvalid, sbits);
     stamp(p, h, 6);
     // ---- weights and selection bits out ---------------------------------------------------------
     float *w = p.w + (int64_t)h * (C + 1);
-    for (int c = tid; c <= C; c += SEL_THREADS) w[c] = sel[c] ? 1.f : 0.f;
-    const int words = C / 32 + 1;
+    for (int c = tid; c <= C; c += SEL_THREADS) w[c] = c == C ? 1.f : (float)((sbits[c >> 5] >> (c & 31)) & 1u);
     uint32_t *bits = p.selbits + (int64_t)h * words;
-    for (int wd = wid; wd < words; wd += SEL_WARPS) {
-        const int c = wd * 32 + lane;
-        const unsigned v = __ballot_sync(0xffffffffu, c <= C && sel[c]);
-        if (lane == 0) bits[wd] = v;
-    }
+    for (int wd = tid; wd < words; wd += SEL_THREADS) bits[wd] = sbits[wd] | (wd == (C >> 5) ? 1u << (C & 31) : 0u);
     stamp(p, h, 7);
 }
 
