@@ -548,6 +548,8 @@ __global__ void __launch_bounds__(256) members_kernel(const FitView v) {
     }
 }
 
+constexpr int PART_CH = 32;                 // members staged per chunk in partition_kernel (a multiple of 8)
+
 struct PartSmem {
     float *cents;   // [k][128]
     float *sums;    // [k][128]
@@ -578,7 +580,8 @@ __global__ void __launch_bounds__(256) partition_kernel(const FitView v, int kwa
         const float cap = fmaxf(v.st.cap[h], capk * (float)v.m);
         int k = (int)ceilf((float)cnt * split_factor / cap);
         k = min(max(k, 2), kcap);
-        float *cents = reinterpret_cast<float *>(smem_raw);
+        float *stage = reinterpret_cast<float *>(smem_raw);          // [PART_CH][128]: a chunk of members' directions
+        float *cents = stage + PART_CH * HEAD_DIM;
         float *sums = cents + (size_t)kcap * HEAD_DIM;
         int *sizes = reinterpret_cast<int *>(sums + (size_t)kcap * HEAD_DIM);
         int *newid = sizes + kcap;
@@ -589,29 +592,49 @@ __global__ void __launch_bounds__(256) partition_kernel(const FitView v, int kwa
         }
         __syncthreads();
         for (int it = 0; it <= iters; ++it) {
-            for (int r = wid; r < cnt; r += 8) {
-                const float4 x = *reinterpret_cast<const float4 *>(X + (int64_t)mem[r] * HEAD_DIM + lane * 4);
-                float bv = -INFINITY;
-                int bi = 0;
-                for (int jj = 0; jj < k; ++jj) {
-                    const float4 cc = *reinterpret_cast<const float4 *>(cents + jj * HEAD_DIM + lane * 4);
-                    const float dot = warp_sum(x.x * cc.x + x.y * cc.y + x.z * cc.z + x.w * cc.w);
-                    if (dot > bv) { bv = dot; bi = jj; }
+            const bool last = it == iters;
+            if (!last) {
+                for (int i = tid; i < k * HEAD_DIM; i += 256) sums[i] = 0.f;
+                for (int i = tid; i < k; i += 256) sizes[i] = 0;
+            }
+            // The members go by in chunks of PART_CH: a warp fetches its rows of the chunk (all requested at once),
+            // assigns them, and leaves them in shared memory, from where thread t adds component t of the chunk's
+            // members to their parts' sums in member order - the order of the additions is that of a single pass over
+            // all members, so the sums are the same bits, without one dependent global load per member.
+            for (int c0 = 0; c0 < cnt; c0 += PART_CH) {
+                float4 x[PART_CH / 8];
+#pragma unroll
+                for (int q = 0; q < PART_CH / 8; ++q) {
+                    const int r = c0 + wid + 8 * q;
+                    x[q] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (r < cnt) x[q] = *reinterpret_cast<const float4 *>(X + (int64_t)mem[r] * HEAD_DIM + lane * 4);
                 }
-                if (lane == 0) prt[r] = (int16_t)bi;
+#pragma unroll
+                for (int q = 0; q < PART_CH / 8; ++q) {
+                    const int r = c0 + wid + 8 * q;
+                    if (r >= cnt) continue;                      // warp-uniform
+                    float bv = -INFINITY;
+                    int bi = 0;
+                    for (int jj = 0; jj < k; ++jj) {
+                        const float4 cc = *reinterpret_cast<const float4 *>(cents + jj * HEAD_DIM + lane * 4);
+                        const float dot = warp_sum(x[q].x * cc.x + x[q].y * cc.y + x[q].z * cc.z + x[q].w * cc.w);
+                        if (dot > bv) { bv = dot; bi = jj; }
+                    }
+                    if (lane == 0) prt[r] = (int16_t)bi;
+                    if (!last) *reinterpret_cast<float4 *>(stage + (wid + 8 * q) * HEAD_DIM + lane * 4) = x[q];
+                }
+                if (last) continue;
+                __syncthreads();
+                const int rows = min(PART_CH, cnt - c0);
+                if (tid < HEAD_DIM) {
+                    for (int r = 0; r < rows; ++r) sums[prt[c0 + r] * HEAD_DIM + tid] += stage[r * HEAD_DIM + tid];
+                } else if (tid == HEAD_DIM) {
+                    for (int r = 0; r < rows; ++r) sizes[prt[c0 + r]] += 1;
+                }
+                __syncthreads();
             }
             __syncthreads();
-            if (it == iters) break;
-            for (int i = tid; i < k * HEAD_DIM; i += 256) sums[i] = 0.f;
-            for (int i = tid; i < k; i += 256) sizes[i] = 0;
-            __syncthreads();
-            if (tid < HEAD_DIM) {
-#pragma unroll 4
-                for (int r = 0; r < cnt; ++r) sums[prt[r] * HEAD_DIM + tid] += X[(int64_t)mem[r] * HEAD_DIM + tid];
-            } else if (tid == HEAD_DIM) {
-                for (int r = 0; r < cnt; ++r) sizes[prt[r]] += 1;
-            }
-            __syncthreads();
+            if (last) break;
             for (int jj = wid; jj < k; jj += 8) {
                 const float4 s = *reinterpret_cast<const float4 *>(sums + jj * HEAD_DIM + lane * 4);
                 const float n2 = warp_sum(s.x * s.x + s.y * s.y + s.z * s.z + s.w * s.w);
@@ -637,7 +660,8 @@ __global__ void __launch_bounds__(256) partition_kernel(const FitView v, int kwa
         return;
     }
     // ---- two-way split -------------------------------------------------------------------------
-    float *sa = reinterpret_cast<float *>(smem_raw), *sb = sa + HEAD_DIM, *sdiff = sb + HEAD_DIM;
+    float *stage = reinterpret_cast<float *>(smem_raw);              // [PART_CH][128]
+    float *sa = stage + PART_CH * HEAD_DIM, *sb = sa + HEAD_DIM, *sdiff = sb + HEAD_DIM;
     if (tid < HEAD_DIM) sa[tid] = X[(int64_t)mem[0] * HEAD_DIM + tid];
     __syncthreads();
     {
@@ -678,32 +702,49 @@ __global__ void __launch_bounds__(256) partition_kernel(const FitView v, int kwa
     for (int it = 0; it <= 4; ++it) {
         if (it == 4 && tid < HEAD_DIM) sdiff[tid] = sb[tid] - sa[tid];
         if (it == 4) __syncthreads();
+        float s0 = 0.f, s1 = 0.f;
+        int n1 = 0;
         {
+            // members in chunks, as in the k-way path: fetched by the warp that assigns them, then added up per
+            // component in member order from shared memory
             const float4 a4 = *reinterpret_cast<const float4 *>(sa + lane * 4);
             const float4 b4 = *reinterpret_cast<const float4 *>(sb + lane * 4);
             const float4 d4 = *reinterpret_cast<const float4 *>(sdiff + lane * 4);
-            for (int r = wid; r < cnt; r += 8) {
-                const float4 x = *reinterpret_cast<const float4 *>(X + (int64_t)mem[r] * HEAD_DIM + lane * 4);
-                const float da = warp_sum(x.x * a4.x + x.y * a4.y + x.z * a4.z + x.w * a4.w);
-                const float db = warp_sum(x.x * b4.x + x.y * b4.y + x.z * b4.z + x.w * b4.w);
-                if (it == 4) {
-                    const float pj = warp_sum(x.x * d4.x + x.y * d4.y + x.z * d4.z + x.w * d4.w);
-                    if (lane == 0) proj[r] = pj;
+            for (int c0 = 0; c0 < cnt; c0 += PART_CH) {
+                float4 x[PART_CH / 8];
+#pragma unroll
+                for (int q = 0; q < PART_CH / 8; ++q) {
+                    const int r = c0 + wid + 8 * q;
+                    x[q] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (r < cnt) x[q] = *reinterpret_cast<const float4 *>(X + (int64_t)mem[r] * HEAD_DIM + lane * 4);
                 }
-                if (lane == 0) prt[r] = db > da;
+#pragma unroll
+                for (int q = 0; q < PART_CH / 8; ++q) {
+                    const int r = c0 + wid + 8 * q;
+                    if (r >= cnt) continue;                      // warp-uniform
+                    const float da = warp_sum(x[q].x * a4.x + x[q].y * a4.y + x[q].z * a4.z + x[q].w * a4.w);
+                    const float db = warp_sum(x[q].x * b4.x + x[q].y * b4.y + x[q].z * b4.z + x[q].w * b4.w);
+                    if (it == 4) {
+                        const float pj = warp_sum(x[q].x * d4.x + x[q].y * d4.y + x[q].z * d4.z + x[q].w * d4.w);
+                        if (lane == 0) proj[r] = pj;
+                    }
+                    if (lane == 0) prt[r] = db > da;
+                    if (it < 4) *reinterpret_cast<float4 *>(stage + (wid + 8 * q) * HEAD_DIM + lane * 4) = x[q];
+                }
+                if (it == 4) continue;
+                __syncthreads();
+                const int rows = min(PART_CH, cnt - c0);
+                if (tid < HEAD_DIM) {
+                    for (int r = 0; r < rows; ++r) {
+                        const float u = stage[r * HEAD_DIM + tid];
+                        if (prt[c0 + r]) { s1 += u; ++n1; } else s0 += u;
+                    }
+                }
+                __syncthreads();
             }
         }
         __syncthreads();
         if (it == 4) break;
-        float s0 = 0.f, s1 = 0.f;
-        int n1 = 0;
-        if (tid < HEAD_DIM) {
-#pragma unroll 4
-            for (int r = 0; r < cnt; ++r) {
-                const float u = X[(int64_t)mem[r] * HEAD_DIM + tid];
-                if (prt[r]) { s1 += u; ++n1; } else s0 += u;
-            }
-        }
         const float q0 = block_sum(tid < HEAD_DIM ? s0 * s0 : 0.f, fred);
         const float q1 = block_sum(tid < HEAD_DIM ? s1 * s1 : 0.f, fred);
         if (tid == 0) ired[1] = n1;
@@ -901,7 +942,7 @@ static int split_rounds(FitView &v, float *projbuf, float split_factor, int iter
         const int maxc = host[2];
         const int kcap = kway ? (host[3] < 2 ? 2 : (host[3] > KWAY_MAX ? KWAY_MAX : host[3])) : 2;
         members_kernel<<<dim3((maxc + 7) / 8, v.entries), 256, 0, s>>>(v);
-        const size_t smem = kway ? (size_t)kcap * (2 * HEAD_DIM * 4 + 8) + 64 : 3 * HEAD_DIM * 4;
+        const size_t smem = (size_t)PART_CH * HEAD_DIM * 4 + (kway ? (size_t)kcap * (2 * HEAD_DIM * 4 + 8) + 64 : 3 * HEAD_DIM * 4);
         if (smem > 48 * 1024)
             SKV_CUDA_OK(cudaFuncSetAttribute(partition_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         partition_kernel<<<dim3(maxc, v.entries), 256, smem, s>>>(v, kway ? 1 : 0, split_factor, iters, kcap, projbuf,
