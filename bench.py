@@ -256,7 +256,13 @@ def kernel_roofline(dec, n_now, peak_gbs, which, traffic=None):
     one_launch = bool(layers[0]._step_clusters(H // H_kv))
     sel_t = timed(graph_of(lambda ix, kv: ix._select(q, dec.n_dev, listed=False)))
     att_t = timed(graph_of(lambda ix, kv: ix._attend_labels(q, kv[0], kv[1], dec.n_dev)))
-    stp_t = timed(graph_of(lambda ix, kv: ix.step(q, kv[0], kv[1], dec.n_dev, insert=False)))
+    # the step as the decoder launches it: with its own products the last merge of the one-launch step rides in the
+    # output product
+    defer = one_launch and dec.merge_deferred
+    stp_t = timed(graph_of(lambda ix, kv: ix.step(q, kv[0], kv[1], dec.n_dev, insert=False, defer_merge=defer)))
+    for ix, kv in zip(layers, heads):                                  # one untimed step that writes the rows read
+        ix.step(q, kv[0], kv[1], dec.n_dev, insert=False)
+    torch.cuda.synchronize()
     rows = torch.stack([ix.cnt for ix in layers]).float()              # [layers, heads]
     n_c = torch.stack([ix.n_c for ix in layers]).float()
     # attention kernel: K and V rows, the int16 label of every cached position, the selection bits
@@ -272,6 +278,7 @@ def kernel_roofline(dec, n_now, peak_gbs, which, traffic=None):
     layer = {"kernels": ("select + attend in one launch" if one_launch else "select, then attend") +
                         " (insert runs once for all layers)",
              "launches": 1 if one_launch else 2, "us_per_layer": stp_t * 1e6,
+             "last_merge": "in the output product, as in the decode step" if defer else "in the launch",
              "bytes_per_layer": stp_bytes, "achieved": stp_bytes / stp_t / 1e9, "unit": "GB/s",
              "frac": stp_bytes / stp_t / 1e9 / peak_gbs, "select_us": sel_t * 1e6, "attend_us": att_t * 1e6,
              "rows_per_head": float(rows.mean()),

@@ -157,6 +157,15 @@ class GraphDecoder:
         self._side = None
         self._warming = False
 
+    @property
+    def merge_deferred(self) -> bool:
+        """Whether the one-launch step leaves the merge of its clusters' partials to the output product: the case
+        when the library's own matrix-vector products serve this batch."""
+        if not (self.mode == "cluster" and self.defer_merge and self.fused_dense and self.own_gemv and self.B <= 8):
+            return False
+        w = self.model.layers[0].attn.o.weight
+        return bool(lib().skv_gemv_supported(w.shape[0], w.shape[1], self.B, 0))
+
     def _heads(self, c: torch.Tensor) -> torch.Tensor:
         """Cache ``[B, H_kv, L, d]`` -> ``[B*H_kv, L, d]`` (a view)."""
         return c.view(-1, c.shape[2], c.shape[3])
